@@ -1,0 +1,199 @@
+"""torch-tensor front end over the C ABI (used by tests, smoke check and benchmark).
+
+torch is plumbing here: it owns device memory and streams.  Every function fills an
+``ltca_attn_params`` block with raw pointers and strides and calls libltc_attn.so; nothing is
+computed in Python and nothing falls back to torch operators.
+
+Tensor convention: ``[batch, heads, seq, head_dim]`` views with ``head_dim`` contiguous (any
+batch/head/seq strides), float32 or bfloat16 -- e.g. ``x.view(B, S, H, D).transpose(1, 2)``
+addresses an un-permuted ``[B*S, H*D]`` projection output directly.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+from ._lib import AttnParams, Strides
+
+
+class LtcaError(RuntimeError):
+    def __init__(self, code: int, message: str):
+        super().__init__(f"{_lib.STATUS_NAMES.get(code, code)}: {message}")
+        self.code = code
+
+
+def _dtype_code(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return _lib.LTCA_F32
+    if t.dtype == torch.bfloat16:
+        return _lib.LTCA_BF16
+    raise TypeError(f"unsupported dtype {t.dtype}")
+
+
+def _strides(t: torch.Tensor) -> Strides:
+    assert t.dim() == 4 and (t.stride(3) == 1 or t.shape[3] == 1), "head_dim must be contiguous"
+    return Strides(t.stride(0), t.stride(1), t.stride(2))
+
+
+class Context:
+    """One (device, stream) binding of the library."""
+
+    def __init__(self, device: int = 0, stream: Optional[torch.cuda.Stream] = None):
+        self.lib = _lib.load()
+        self.device = int(device)
+        handle = C.c_void_p()
+        sptr = C.c_void_p(stream.cuda_stream) if stream is not None else C.c_void_p(
+            torch.cuda.current_stream(self.device).cuda_stream)
+        rc = self.lib.ltca_ctx_create(self.device, sptr, C.byref(handle))
+        if rc != 0:
+            raise LtcaError(rc, "ltca_ctx_create failed (is this an sm_100 GPU?)")
+        self.handle = handle
+        self._ws = None
+
+    def close(self):
+        if getattr(self, "handle", None):
+            self.lib.ltca_ctx_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def set_stream(self, stream: torch.cuda.Stream):
+        self.lib.ltca_ctx_set_stream(self.handle, C.c_void_p(stream.cuda_stream))
+
+    def check(self, rc: int):
+        if rc != 0:
+            raise LtcaError(rc, self.lib.ltca_last_error(self.handle).decode())
+
+    def device_status(self) -> int:
+        v = C.c_uint32(0)
+        self.lib.ltca_device_status(self.handle, C.byref(v))
+        return int(v.value)
+
+    def workspace(self, nbytes: int) -> Optional[torch.Tensor]:
+        """A cached scratch buffer of at least ``nbytes`` (grown on demand, 256-byte aligned)."""
+        if nbytes == 0:
+            return None
+        if self._ws is None or self._ws.numel() < nbytes:
+            self._ws = torch.empty(nbytes, dtype=torch.uint8, device=f"cuda:{self.device}")
+        return self._ws
+
+    # ---- parameter block -----------------------------------------------------------------
+    def _params(self, q, k, v, o, lse, scale, causal, keep_mask, kv_len, score_clamp, mode) -> AttnParams:
+        B, H, Sq, D = q.shape
+        Sk = k.shape[2]
+        assert k.shape == (B, H, Sk, D) and v.shape == (B, H, Sk, D) and o.shape == (B, H, Sq, D)
+        assert q.dtype == k.dtype == v.dtype == o.dtype
+        p = AttnParams()
+        p.B, p.H, p.Sq, p.Sk, p.D = B, H, Sq, Sk, D
+        p.dtype, p.mode, p.causal = _dtype_code(q), int(mode), int(bool(causal))
+        p.scale, p.score_clamp = float(scale), float(score_clamp or 0.0)
+        p.q, p.q_strides = q.data_ptr(), _strides(q)
+        p.k, p.k_strides = k.data_ptr(), _strides(k)
+        p.v, p.v_strides = v.data_ptr(), _strides(v)
+        p.o, p.o_strides = o.data_ptr(), _strides(o)
+        p.lse = lse.data_ptr() if lse is not None else None
+        if keep_mask is not None:
+            assert keep_mask.dtype == torch.float32 and keep_mask.is_contiguous()
+            assert keep_mask.shape == (B, Sq, Sk)
+            p.keep_mask = keep_mask.data_ptr()
+        if kv_len is not None:
+            assert kv_len.dtype == torch.int32 and kv_len.is_contiguous() and kv_len.shape == (B,)
+            p.kv_len = kv_len.data_ptr()
+        return p
+
+    def _attach_workspace(self, p: AttnParams, backward: int, fixed: Optional[int] = None):
+        need = C.c_size_t(0)
+        if fixed is None:
+            self.lib.ltca_attn_workspace_bytes(C.byref(p), backward, C.byref(need))
+            n = need.value
+        else:
+            n = fixed
+        ws = self.workspace(n)
+        if ws is not None:
+            p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel()
+        return ws
+
+    # ---- calls ---------------------------------------------------------------------------
+    def attn_fwd(self, q, k, v, scale=None, causal=False, keep_mask=None, kv_len=None,
+                 score_clamp=0.0, mode=_lib.MODE_AUTO, out=None, lse=None
+                 ) -> Tuple[torch.Tensor, torch.Tensor]:
+        B, H, Sq, D = q.shape
+        scale = 1.0 / math.sqrt(D) if scale is None else scale
+        o = torch.empty((B, H, Sq, D), dtype=q.dtype, device=q.device) if out is None else out
+        lse = torch.empty((B, H, Sq), dtype=torch.float32, device=q.device) if lse is None else lse
+        p = self._params(q, k, v, o, lse, scale, causal, keep_mask, kv_len, score_clamp, mode)
+        ws = self._attach_workspace(p, 0)
+        self.check(self.lib.ltca_attn_fwd(self.handle, C.byref(p)))
+        del ws
+        return o, lse
+
+    def attn_bwd(self, q, k, v, o, lse, dout, scale=None, causal=False, keep_mask=None,
+                 kv_len=None, score_clamp=0.0, mode=_lib.MODE_AUTO, dq=None, dk=None, dv=None):
+        D = q.shape[3]
+        scale = 1.0 / math.sqrt(D) if scale is None else scale
+        dq = torch.empty(q.shape, dtype=q.dtype, device=q.device) if dq is None else dq
+        dk = torch.empty(k.shape, dtype=k.dtype, device=k.device) if dk is None else dk
+        dv = torch.empty(v.shape, dtype=v.dtype, device=v.device) if dv is None else dv
+        p = self._params(q, k, v, o, lse, scale, causal, keep_mask, kv_len, score_clamp, mode)
+        p.dout, p.do_strides = dout.data_ptr(), _strides(dout)
+        p.dq, p.dq_strides = dq.data_ptr(), _strides(dq)
+        p.dk, p.dk_strides = dk.data_ptr(), _strides(dk)
+        p.dv, p.dv_strides = dv.data_ptr(), _strides(dv)
+        ws = self._attach_workspace(p, 1)
+        self.check(self.lib.ltca_attn_bwd(self.handle, C.byref(p)))
+        del ws
+        return dq, dk, dv
+
+    def attn_decode(self, q, k, v, kv_len=None, scale=None, keep_mask=None, score_clamp=0.0,
+                    out=None, lse=None):
+        B, H, Sq, D = q.shape
+        scale = 1.0 / math.sqrt(D) if scale is None else scale
+        o = torch.empty((B, H, 1, D), dtype=q.dtype, device=q.device) if out is None else out
+        lse = torch.empty((B, H, 1), dtype=torch.float32, device=q.device) if lse is None else lse
+        p = self._params(q, k, v, o, lse, scale, False, keep_mask, kv_len, score_clamp, _lib.MODE_FP32)
+        need = C.c_size_t(0)
+        self.lib.ltca_attn_decode_workspace_bytes(C.byref(p), C.byref(need))
+        ws = self._attach_workspace(p, 0, fixed=need.value)
+        self.check(self.lib.ltca_attn_decode(self.handle, C.byref(p)))
+        del ws
+        return o, lse
+
+    def uses_tensor_pipe(self, q, k, v, causal=False, mode=_lib.MODE_AUTO, backward=False) -> bool:
+        o = q
+        p = self._params(q, k, v, o, None, 1.0, causal, None, None, 0.0, mode)
+        return bool(self.lib.ltca_attn_uses_tensor_pipe(C.byref(p), int(backward)))
+
+
+_default: dict = {}
+
+
+def _ctx_for(t: torch.Tensor) -> Context:
+    dev = t.device.index if t.device.index is not None else torch.cuda.current_device()
+    if dev not in _default:
+        _default[dev] = Context(dev)
+    ctx = _default[dev]
+    ctx.set_stream(torch.cuda.current_stream(dev))
+    return ctx
+
+
+def attention_forward(q, k, v, **kw):
+    """O, lse = attention(q, k, v).  See :meth:`Context.attn_fwd`."""
+    return _ctx_for(q).attn_fwd(q, k, v, **kw)
+
+
+def attention_backward(q, k, v, o, lse, dout, **kw):
+    """dq, dk, dv.  See :meth:`Context.attn_bwd`."""
+    return _ctx_for(q).attn_bwd(q, k, v, o, lse, dout, **kw)
+
+
+def attention_decode(q, k, v, kv_len=None, **kw):
+    """Single-query step over a key/value cache.  See :meth:`Context.attn_decode`."""
+    return _ctx_for(q).attn_decode(q, k, v, kv_len=kv_len, **kw)

@@ -1,0 +1,469 @@
+// Attention forward on the sm_100a tensor pipe.
+//
+//   O = softmax(mask(scale * Q K^T)) V,   lse = log sum exp of the masked, scaled scores
+//
+// replaces flashAttentionKernel of the reference (src/ml/flash_attention.cu:18-272): the same
+// contract (scale, keep-mask with 0 = hidden, optional score clamp), plus a causal flag and
+// per-sequence key lengths, computed as a true online softmax.
+//
+// Shape of the kernel
+//   - one CTA per (256 query rows, head, batch): two 128-row query tiles share every K/V tile
+//     that TMA brings in, which halves the L2 -> shared traffic per FLOP;
+//   - warps 0-3 / 4-7: softmax of query tile 0 / 1 (one query row per thread, so row maxima
+//     and sums need no shuffles), also rescale O when the running maximum moved and write the
+//     final O and lse;  warp 8: issues every tcgen05.mma;  warp 9: TMA producer;
+//   - S = Q K^T accumulates in tensor memory (128 fp32 columns per tile), the softmax warps read
+//     it with tcgen05.ld, write P back as packed bf16 (tcgen05.st, aliasing S) and the second
+//     contraction O += P V takes P straight from tensor memory; O (D fp32 columns per tile)
+//     never leaves tensor memory until the epilogue;
+//   - K and V tiles travel through one ring of shared-memory slots in the order
+//     K0 V0 K1 V1 ..., each slot guarded by a full/empty mbarrier pair;
+//   - the MMA warp interleaves the two tiles (PV0, QK0', PV1, QK1') so that one tile's
+//     softmax overlaps the other tile's contractions.
+//
+// Tensor-memory map (512 columns): S0 [0,128) S1 [128,256) O0 [256,256+D) O1 [256+D,256+2D);
+// P_t occupies the upper 64 columns of S_t (128 bf16 packed two per column).
+#include "host_common.h"
+#include "sm100_ptx.cuh"
+
+namespace ltca {
+
+namespace {
+
+constexpr int kBlockM = 128;        // query rows per tile
+constexpr int kBlockN = 128;        // keys per step
+constexpr int kFwdThreads = 384;
+constexpr int kMmaWarp = 8;
+constexpr int kTmaWarp = 9;
+constexpr uint32_t kTmemCols = 512;
+
+struct FwdArgs {
+    int B, H, Sq, Sk;
+    int causal, causal_off;
+    float scale;            // score scale
+    float scale_log2;       // scale * log2(e)
+    float clamp_raw;        // score clamp divided by scale (raw QK^T units); +inf when unused
+    int use_clamp;
+    void* o;
+    int64_t o_sb, o_sh, o_ss;
+    float* lse;
+    const float* keep_mask;
+    const int32_t* kv_len;
+    uint32_t* status;
+};
+
+template <int D>
+struct FwdSmem {
+    static constexpr int kDimBlocks = D / 64;                  // 64-element (128 B) column blocks
+    static constexpr int kTileBytes = kBlockN * D * 2;         // one Q/K/V tile
+    static constexpr int kStages = (D == 64) ? 8 : 4;          // ring slots
+    static constexpr int kQOff = 0;
+    static constexpr int kRingOff = 2 * kTileBytes;
+    static constexpr int kBarOff = kRingOff + kStages * kTileBytes;
+    // barriers: q_full, kv_full[kStages], kv_empty[kStages], s_full[2], p_full[2], o_done[2]
+    static constexpr int kNumBars = 1 + 2 * kStages + 6;
+    static constexpr int kMiscOff = kBarOff + kNumBars * 8;    // tmem base, abort flag
+    static constexpr int kBytes = kMiscOff + 16;
+    static constexpr int kDynBytes = kBytes + 1024;            // room to align to 1024 B
+};
+
+__device__ __forceinline__ float neg_inf() { return __int_as_float(0xff800000); }
+
+template <int D, typename OutT>
+__global__ void __launch_bounds__(kFwdThreads, 1)
+attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
+                      const __grid_constant__ CUtensorMap tmap_k,
+                      const __grid_constant__ CUtensorMap tmap_v, const FwdArgs a) {
+    using L = FwdSmem<D>;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+
+    const uint32_t q_smem = smem_base + L::kQOff;
+    const uint32_t ring_smem = smem_base + L::kRingOff;
+    const uint32_t bar_base = smem_base + L::kBarOff;
+    auto bar_q_full = [&]() { return bar_base; };
+    auto bar_kv_full = [&](int s) { return bar_base + 8u * (1 + s); };
+    auto bar_kv_empty = [&](int s) { return bar_base + 8u * (1 + L::kStages + s); };
+    auto bar_s_full = [&](int t) { return bar_base + 8u * (1 + 2 * L::kStages + t); };
+    auto bar_p_full = [&](int t) { return bar_base + 8u * (3 + 2 * L::kStages + t); };
+    auto bar_o_done = [&](int t) { return bar_base + 8u * (5 + 2 * L::kStages + t); };
+    volatile uint32_t* misc = reinterpret_cast<volatile uint32_t*>(smem_gen + L::kMiscOff);
+    // misc[0] = tensor-memory base address, misc[1] = abort flag
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int m_block = gridDim.x - 1 - blockIdx.x;     // heavy (late) causal blocks first
+    const int h = blockIdx.y;
+    const int b = blockIdx.z;
+
+    int kvlen = a.Sk;
+    if (a.kv_len) kvlen = min(max(a.kv_len[b], 0), a.Sk);
+    int n_tiles[2];
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+        const int q0 = m_block * 2 * kBlockM + t * kBlockM;
+        int lim = 0;
+        if (q0 < a.Sq) {
+            lim = kvlen;
+            if (a.causal) lim = min(lim, min(q0 + kBlockM - 1, a.Sq - 1) + a.causal_off + 1);
+        }
+        n_tiles[t] = lim > 0 ? (lim + kBlockN - 1) / kBlockN : 0;
+    }
+    const int n_max = max(n_tiles[0], n_tiles[1]);
+
+    if (threadIdx.x == 0) {
+        mbar_init(bar_q_full(), 1);
+        for (int s = 0; s < L::kStages; ++s) {
+            mbar_init(bar_kv_full(s), 1);
+            mbar_init(bar_kv_empty(s), 1);
+        }
+        for (int t = 0; t < 2; ++t) {
+            mbar_init(bar_s_full(t), 1);
+            mbar_init(bar_p_full(t), kBlockM);
+            mbar_init(bar_o_done(t), 1);
+        }
+        misc[1] = 0u;
+        mbar_fence_init();
+    }
+    if (warp == kMmaWarp) {
+        tmem_alloc(smem_u32(const_cast<uint32_t*>(&misc[0])), kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = misc[0];
+    const WaitCtx wc{&misc[1], a.status};
+
+    if (warp == kTmaWarp) {
+        // ------------------------------ TMA producer ------------------------------------------
+        if (lane == 0 && n_max > 0) {
+            tma_prefetch_desc(&tmap_q);
+            tma_prefetch_desc(&tmap_k);
+            tma_prefetch_desc(&tmap_v);
+            mbar_arrive_expect_tx(bar_q_full(), 2u * L::kTileBytes);
+            for (int t = 0; t < 2; ++t)
+                for (int kb = 0; kb < L::kDimBlocks; ++kb)
+                    tma_load_4d(q_smem + t * L::kTileBytes + kb * (kBlockM * 128), &tmap_q,
+                                bar_q_full(), kb * 64, m_block * 2 * kBlockM + t * kBlockM, h, b);
+            bool ok = true;
+            for (int j = 0; j < n_max && ok; ++j) {
+#pragma unroll
+                for (int which = 0; which < 2; ++which) {     // 0: K_j, 1: V_j
+                    const int item = 2 * j + which;
+                    const int slot = item % L::kStages;
+                    const uint32_t phase = (item / L::kStages) & 1;
+                    ok = ok && mbar_wait(bar_kv_empty(slot), phase ^ 1u, wc, 0x10 + which);
+                    if (!ok) break;
+                    mbar_arrive_expect_tx(bar_kv_full(slot), (uint32_t)L::kTileBytes);
+                    for (int kb = 0; kb < L::kDimBlocks; ++kb)
+                        tma_load_4d(ring_smem + slot * L::kTileBytes + kb * (kBlockN * 128),
+                                    which == 0 ? &tmap_k : &tmap_v, bar_kv_full(slot), kb * 64,
+                                    j * kBlockN, h, b);
+                }
+            }
+        }
+    } else if (warp == kMmaWarp) {
+        // ------------------------------ MMA issuer --------------------------------------------
+        if (lane == 0 && n_max > 0) {
+            constexpr uint32_t idesc_qk = make_idesc_bf16(kBlockM, kBlockN, 0, 0);
+            constexpr uint32_t idesc_pv = make_idesc_bf16(kBlockM, D, 0, 1);
+            auto issue_qk = [&](int t, int slot) {
+                const uint32_t qa = q_smem + t * L::kTileBytes;
+                const uint32_t ka = ring_smem + slot * L::kTileBytes;
+#pragma unroll
+                for (int k = 0; k < D / 16; ++k) {
+                    const uint32_t off = (k / 4) * (kBlockM * 128) + (k % 4) * 32;
+                    mma_ss(tmem_base + t * kBlockN, make_smem_desc_sw128(qa + off, 16, 1024),
+                           make_smem_desc_sw128(ka + off, 16, 1024), idesc_qk, k > 0 ? 1u : 0u);
+                }
+            };
+            auto issue_pv = [&](int t, int slot, bool acc) {
+                const uint32_t va = ring_smem + slot * L::kTileBytes;
+#pragma unroll
+                for (int k = 0; k < kBlockN / 16; ++k) {
+                    mma_ts(tmem_base + 2 * kBlockN + t * D, tmem_base + t * kBlockN + 64 + k * 8,
+                           make_smem_desc_sw128(va + k * 2048, kBlockN * 128, 1024), idesc_pv,
+                           (acc || k > 0) ? 1u : 0u);
+                }
+            };
+            auto slot_of = [&](int item) { return item % L::kStages; };
+            auto phase_of = [&](int item) { return (uint32_t)((item / L::kStages) & 1); };
+
+            bool ok = mbar_wait(bar_q_full(), 0, wc, 0x20);
+            ok = ok && mbar_wait(bar_kv_full(slot_of(0)), phase_of(0), wc, 0x21);
+            if (ok) {
+                tc_fence_after_sync();
+                for (int t = 0; t < 2; ++t)
+                    if (n_tiles[t] > 0) {
+                        issue_qk(t, slot_of(0));
+                        mma_commit(bar_s_full(t));
+                    }
+                mma_commit(bar_kv_empty(slot_of(0)));
+            }
+            for (int j = 0; j < n_max && ok; ++j) {
+                const int item_v = 2 * j + 1, item_k = 2 * j + 2;
+                const bool have_next = (j + 1 < n_max);
+                ok = ok && mbar_wait(bar_kv_full(slot_of(item_v)), phase_of(item_v), wc, 0x22);
+                if (have_next)
+                    ok = ok && mbar_wait(bar_kv_full(slot_of(item_k)), phase_of(item_k), wc, 0x23);
+                if (!ok) break;
+                for (int t = 0; t < 2; ++t) {
+                    if (j < n_tiles[t]) {
+                        ok = ok && mbar_wait(bar_p_full(t), (uint32_t)(j & 1), wc, 0x24 + t);
+                        if (!ok) break;
+                        tc_fence_after_sync();
+                        issue_pv(t, slot_of(item_v), j > 0);
+                        mma_commit(bar_o_done(t));
+                    }
+                    if (j + 1 < n_tiles[t]) {
+                        issue_qk(t, slot_of(item_k));
+                        mma_commit(bar_s_full(t));
+                    }
+                }
+                if (!ok) break;
+                mma_commit(bar_kv_empty(slot_of(item_v)));
+                if (have_next) mma_commit(bar_kv_empty(slot_of(item_k)));
+            }
+            // everything this thread issued has to be complete before tensor memory is released
+            for (int t = 0; t < 2 && ok; ++t)
+                if (n_tiles[t] > 0)
+                    ok = mbar_wait(bar_o_done(t), (uint32_t)((n_tiles[t] - 1) & 1), wc, 0x28 + t);
+        }
+    } else if (warp < 8) {
+        // ------------------------------ softmax / correction / epilogue ------------------------
+        const int t = warp >> 2;
+        const int wq = warp & 3;
+        const int row = wq * 32 + lane;
+        const int q0 = m_block * 2 * kBlockM + t * kBlockM;
+        const int qi = q0 + row;
+        const int n_t = n_tiles[t];
+        const uint32_t lane_base = (uint32_t)(wq * 32) << 16;
+        const uint32_t tS = tmem_base + lane_base + t * kBlockN;
+        const uint32_t tP = tS + 64;
+        const uint32_t tO = tmem_base + lane_base + 2 * kBlockN + t * D;
+        const float c2 = a.scale_log2;
+        const bool general = (a.keep_mask != nullptr) || (a.use_clamp != 0);
+
+        float m_run = neg_inf();
+        float l_run = 0.f;
+        bool ok = true;
+        for (int j = 0; j < n_t; ++j) {
+            ok = __all_sync(0xffffffffu, mbar_wait(bar_s_full(t), (uint32_t)(j & 1), wc, 0x30 + t));
+            if (!ok) break;
+            tc_fence_after_sync();
+            uint32_t su[kBlockN];
+            tmem_ld32(tS + 0, reinterpret_cast<uint32_t(&)[32]>(su[0]));
+            tmem_ld32(tS + 32, reinterpret_cast<uint32_t(&)[32]>(su[32]));
+            tmem_ld32(tS + 64, reinterpret_cast<uint32_t(&)[32]>(su[64]));
+            tmem_ld32(tS + 96, reinterpret_cast<uint32_t(&)[32]>(su[96]));
+            tmem_wait_ld();
+#define S_(c) __uint_as_float(su[(c)])
+            const int k0 = j * kBlockN;
+            const bool edge = (k0 + kBlockN > kvlen) ||
+                              (a.causal && (k0 + kBlockN - 1 > q0 + a.causal_off));
+            if (edge || general) {
+                int lim = kvlen;
+                if (a.causal) lim = min(lim, qi + a.causal_off + 1);
+                lim -= k0;                              // columns c < lim are visible
+                const float* mrow = nullptr;
+                if (a.keep_mask && qi < a.Sq)
+                    mrow = a.keep_mask + ((int64_t)b * a.Sq + qi) * a.Sk + k0;
+#pragma unroll
+                for (int c = 0; c < kBlockN; ++c) {
+                    float v = S_(c);
+                    if (a.use_clamp) v = fminf(v, a.clamp_raw);
+                    bool vis = c < lim;
+                    if (mrow && vis) vis = (__ldg(mrow + c) != 0.0f);
+                    su[c] = __float_as_uint(vis ? v : neg_inf());
+                }
+            }
+            float mx0 = S_(0), mx1 = S_(1), mx2 = S_(2), mx3 = S_(3);
+#pragma unroll
+            for (int c = 4; c < kBlockN; c += 4) {
+                mx0 = fmaxf(mx0, S_(c));
+                mx1 = fmaxf(mx1, S_(c + 1));
+                mx2 = fmaxf(mx2, S_(c + 2));
+                mx3 = fmaxf(mx3, S_(c + 3));
+            }
+            const float mt = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+
+            // Lazy rescale: keep the stale maximum while the new one exceeds it by less than
+            // 2^8 in the exponent; P stays below 256 and fp32 sums keep their accuracy.
+            float factor = 1.0f;
+            bool need = false;
+            if (j == 0) {
+                m_run = mt;
+            } else if ((mt - m_run) * c2 > 8.0f) {
+                factor = fast_exp2((m_run - mt) * c2);
+                m_run = mt;
+                need = true;
+            }
+            if (j > 0 && __any_sync(0xffffffffu, need)) {
+                ok = __all_sync(0xffffffffu,
+                                mbar_wait(bar_o_done(t), (uint32_t)((j - 1) & 1), wc, 0x32 + t));
+                if (!ok) break;
+                tc_fence_after_sync();
+#pragma unroll
+                for (int c0 = 0; c0 < D; c0 += 32) {
+                    uint32_t o[32];
+                    tmem_ld32(tO + c0, o);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * factor);
+                    tmem_st32(tO + c0, o);
+                }
+                l_run *= factor;
+            }
+            const float m_safe = (m_run == neg_inf()) ? 0.f : m_run;
+            const float mneg = -m_safe * c2;
+            float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
+            uint32_t pk[kBlockN / 2];
+#pragma unroll
+            for (int c = 0; c < kBlockN; c += 4) {
+                const float p0 = fast_exp2(fmaf(S_(c), c2, mneg));
+                const float p1 = fast_exp2(fmaf(S_(c + 1), c2, mneg));
+                const float p2 = fast_exp2(fmaf(S_(c + 2), c2, mneg));
+                const float p3 = fast_exp2(fmaf(S_(c + 3), c2, mneg));
+                sum0 += p0; sum1 += p1; sum2 += p2; sum3 += p3;
+                pk[c / 2] = pack_bf16x2(p0, p1);
+                pk[c / 2 + 1] = pack_bf16x2(p2, p3);
+            }
+            l_run += (sum0 + sum1) + (sum2 + sum3);
+            tmem_st32(tP + 0, reinterpret_cast<uint32_t(&)[32]>(pk[0]));
+            tmem_st32(tP + 32, reinterpret_cast<uint32_t(&)[32]>(pk[32]));
+            tmem_wait_st();
+            tc_fence_before_sync();
+            mbar_arrive(bar_p_full(t));
+#undef S_
+        }
+
+        // epilogue: O / l and lse
+        if (ok && q0 < a.Sq) {
+            float inv = 0.f;
+            float lse = neg_inf();
+            if (n_t > 0) {
+                ok = __all_sync(0xffffffffu,
+                                mbar_wait(bar_o_done(t), (uint32_t)((n_t - 1) & 1), wc, 0x34 + t));
+                tc_fence_after_sync();
+                if (l_run > 0.f) {
+                    inv = 1.0f / l_run;
+                    lse = m_run * a.scale + __logf(l_run);
+                }
+            }
+            OutT* orow = reinterpret_cast<OutT*>(a.o) + b * a.o_sb + h * a.o_sh + (int64_t)qi * a.o_ss;
+#pragma unroll
+            for (int c0 = 0; c0 < D; c0 += 32) {
+                uint32_t o[32];
+                if (n_t > 0 && ok) {
+                    tmem_ld32(tO + c0, o);
+                    tmem_wait_ld();
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) o[c] = 0u;
+                }
+                if (qi < a.Sq) {
+                    if constexpr (sizeof(OutT) == 2) {
+                        uint4* dst = reinterpret_cast<uint4*>(orow + c0);
+#pragma unroll
+                        for (int v = 0; v < 4; ++v) {
+                            uint4 w;
+                            w.x = pack_bf16x2(__uint_as_float(o[8 * v + 0]) * inv, __uint_as_float(o[8 * v + 1]) * inv);
+                            w.y = pack_bf16x2(__uint_as_float(o[8 * v + 2]) * inv, __uint_as_float(o[8 * v + 3]) * inv);
+                            w.z = pack_bf16x2(__uint_as_float(o[8 * v + 4]) * inv, __uint_as_float(o[8 * v + 5]) * inv);
+                            w.w = pack_bf16x2(__uint_as_float(o[8 * v + 6]) * inv, __uint_as_float(o[8 * v + 7]) * inv);
+                            dst[v] = w;
+                        }
+                    } else {
+                        float4* dst = reinterpret_cast<float4*>(orow + c0);
+#pragma unroll
+                        for (int v = 0; v < 8; ++v)
+                            dst[v] = make_float4(__uint_as_float(o[4 * v + 0]) * inv,
+                                                 __uint_as_float(o[4 * v + 1]) * inv,
+                                                 __uint_as_float(o[4 * v + 2]) * inv,
+                                                 __uint_as_float(o[4 * v + 3]) * inv);
+                    }
+                }
+            }
+            if (a.lse && qi < a.Sq) a.lse[((int64_t)b * a.H + h) * a.Sq + qi] = lse;
+        }
+    }
+
+    // ------------------------------ tear-down -------------------------------------------------
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == kMmaWarp) {
+        __syncwarp();
+        if (misc[1]) __nanosleep(200000);    // aborted: give copies and MMAs in flight time to land
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+template <int D, typename OutT>
+int launch_fwd(ltca_ctx* ctx, const ltca_attn_params* p, const void* q, const void* k,
+               const void* v, const ltca_strides& qs, const ltca_strides& ks,
+               const ltca_strides& vs) {
+    using L = FwdSmem<D>;
+    CUtensorMap tq, tk, tv;
+    int rc;
+    if ((rc = make_tmap_bhsd(ctx, &tq, q, 2, p->B, p->H, p->Sq, D, qs, 64, kBlockM))) return rc;
+    if ((rc = make_tmap_bhsd(ctx, &tk, k, 2, p->B, p->H, p->Sk, D, ks, 64, kBlockN))) return rc;
+    if ((rc = make_tmap_bhsd(ctx, &tv, v, 2, p->B, p->H, p->Sk, D, vs, 64, kBlockN))) return rc;
+
+    FwdArgs a;
+    a.B = p->B; a.H = p->H; a.Sq = p->Sq; a.Sk = p->Sk;
+    a.causal = p->causal ? 1 : 0;
+    a.causal_off = p->Sk - p->Sq;
+    a.scale = p->scale;
+    a.scale_log2 = p->scale * 1.4426950408889634f;
+    a.use_clamp = (p->score_clamp > 0.f) ? 1 : 0;
+    a.clamp_raw = a.use_clamp ? p->score_clamp / p->scale : __builtin_inff();
+    a.o = p->o;
+    a.o_sb = p->o_strides.batch; a.o_sh = p->o_strides.head; a.o_ss = p->o_strides.seq;
+    a.lse = p->lse;
+    a.keep_mask = p->keep_mask;
+    a.kv_len = p->kv_len;
+    a.status = ctx->d_status;
+
+    auto kern = attn_fwd_sm100_kernel<D, OutT>;
+    static bool attr_done = false;
+    if (!attr_done) {
+        LTCA_CUDA_OK(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               L::kDynBytes));
+        attr_done = true;
+    }
+    dim3 grid((p->Sq + 2 * kBlockM - 1) / (2 * kBlockM), p->H, p->B);
+    kern<<<grid, kFwdThreads, L::kDynBytes, ctx->stream>>>(tq, tk, tv, a);
+    LTCA_LAUNCH_OK(ctx, "attn_fwd_sm100_kernel");
+    return LTCA_OK;
+}
+
+}  // namespace
+
+bool attn_fwd_sm100_supported(const ltca_attn_params* p) {
+    if (p->D != 64 && p->D != 128) return false;
+    if (p->Sq < 1 || p->Sk < 1) return false;
+    if (!(p->scale > 0.f)) return false;
+    if (p->H > 65535 || p->B > 65535) return false;
+    return true;
+}
+
+// Expects bf16 Q, K, V (already converted when the caller's storage is fp32).
+int launch_attn_fwd_sm100_bf16in(ltca_ctx* ctx, const ltca_attn_params* p, const void* q,
+                                 const void* k, const void* v, const ltca_strides& qs,
+                                 const ltca_strides& ks, const ltca_strides& vs) {
+    const int oes = elem_size(p->dtype);
+    if ((reinterpret_cast<uintptr_t>(p->o) & 15) || ((p->o_strides.seq * oes) & 15) ||
+        ((p->o_strides.head * oes) & 15) || ((p->o_strides.batch * oes) & 15))
+        return fail(ctx, LTCA_ERR_INVALID, "output base and strides must be 16-byte aligned");
+    if (p->D == 64) {
+        return p->dtype == LTCA_BF16 ? launch_fwd<64, __nv_bfloat16>(ctx, p, q, k, v, qs, ks, vs)
+                                     : launch_fwd<64, float>(ctx, p, q, k, v, qs, ks, vs);
+    }
+    return p->dtype == LTCA_BF16 ? launch_fwd<128, __nv_bfloat16>(ctx, p, q, k, v, qs, ks, vs)
+                                 : launch_fwd<128, float>(ctx, p, q, k, v, qs, ks, vs);
+}
+
+}  // namespace ltca

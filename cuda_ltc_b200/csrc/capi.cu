@@ -1,0 +1,356 @@
+// C-ABI entry points declared in include/ltc_attn.h: context handling, argument checks,
+// dispatch between the tensor-pipe kernels and the fp32 kernels, and the small elementwise
+// helpers that sit on the attention path of the reference (tensor add, LayerNorm, finite check).
+#include <new>
+
+#include "host_common.h"
+
+namespace ltca {
+int launch_attn_fwd_sm100_bf16in(ltca_ctx* ctx, const ltca_attn_params* p, const void* q,
+                                 const void* k, const void* v, const ltca_strides& qs,
+                                 const ltca_strides& ks, const ltca_strides& vs);
+
+namespace {
+
+// ---- elementwise kernels ----------------------------------------------------------------------
+__global__ void add_kernel(const float* __restrict__ a, const float* __restrict__ b,
+                           float* __restrict__ r, size_t n) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    const size_t n4 = n / 4;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
+        const float4 x = reinterpret_cast<const float4*>(a)[i];
+        const float4 y = reinterpret_cast<const float4*>(b)[i];
+        reinterpret_cast<float4*>(r)[i] = make_float4(x.x + y.x, x.y + y.y, x.z + y.z, x.w + y.w);
+    }
+    for (size_t i = n4 * 4 + (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
+        r[i] = a[i] + b[i];
+}
+__global__ void add_scalar_kernel(const float* a, const float* b, float* r, size_t n) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) r[i] = a[i] + b[i];
+}
+
+// One warp per row: two-pass mean / biased variance in registers, shuffle reductions.
+__global__ void layer_norm_kernel(float* x, const float* __restrict__ gamma,
+                                  const float* __restrict__ beta, int64_t rows, int E, float eps) {
+    const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const int lane = threadIdx.x & 31;
+    float* xr = x + row * E;
+    float sum = 0.f;
+    for (int i = lane; i < E; i += 32) sum += xr[i];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    const float mean = sum / E;
+    float var = 0.f;
+    for (int i = lane; i < E; i += 32) {
+        const float d = xr[i] - mean;
+        var = fmaf(d, d, var);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) var += __shfl_xor_sync(0xffffffffu, var, o);
+    const float inv_std = rsqrtf(var / E + eps);
+    for (int i = lane; i < E; i += 32)
+        xr[i] = (xr[i] - mean) * inv_std * (gamma ? gamma[i] : 1.f) + (beta ? beta[i] : 0.f);
+}
+
+__global__ void validate_finite_kernel(const float* __restrict__ x, size_t n, int32_t* flag) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    bool bad = false;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        const float v = x[i];
+        bad |= !(fabsf(v) <= 3.402823466e38f);      // false for NaN and Inf
+    }
+    if (__any_sync(0xffffffffu, bad) && (threadIdx.x & 31) == 0) atomicExch(flag, 1);
+}
+
+__global__ void f32_to_bf16_kernel(const float* __restrict__ s, __nv_bfloat16* __restrict__ d, size_t n) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
+        d[i] = __float2bfloat16_rn(s[i]);
+}
+__global__ void bf16_to_f32_kernel(const __nv_bfloat16* __restrict__ s, float* __restrict__ d, size_t n) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
+        d[i] = __bfloat162float(s[i]);
+}
+
+// Strided fp32 [B,H,S,D] -> contiguous bf16 [B,H,S,D]; one thread per 4 elements (D % 4 == 0).
+__global__ void pack_bf16_kernel(const float* __restrict__ src, ltca_strides st,
+                                 __nv_bfloat16* __restrict__ dst, int H, int S, int D, size_t n4) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    const int d4 = D / 4;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
+        const int dd = (int)(i % d4);
+        size_t r = i / d4;
+        const int s = (int)(r % S); r /= S;
+        const int h = (int)(r % H);
+        const int64_t b = (int64_t)(r / H);
+        const float4 v = *reinterpret_cast<const float4*>(src + b * st.batch + h * st.head + (int64_t)s * st.seq + 4 * dd);
+        __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+        uint2 u;
+        u.x = *reinterpret_cast<uint32_t*>(&lo);
+        u.y = *reinterpret_cast<uint32_t*>(&hi);
+        reinterpret_cast<uint2*>(dst)[i] = u;
+    }
+}
+
+inline int blocks_for(size_t n, int threads, int sm_count) {
+    size_t b = (n + threads - 1) / threads;
+    const size_t cap = (size_t)(sm_count > 0 ? sm_count : 148) * 16;
+    if (b > cap) b = cap;
+    if (b < 1) b = 1;
+    return (int)b;
+}
+
+int check_common(ltca_ctx* ctx, const ltca_attn_params* p) {
+    if (!ctx) return LTCA_ERR_INVALID;
+    if (!p) return fail(ctx, LTCA_ERR_INVALID, "null parameter block");
+    if (p->B < 1 || p->H < 1 || p->Sq < 1 || p->Sk < 1 || p->D < 1)
+        return fail(ctx, LTCA_ERR_INVALID, "B, H, Sq, Sk, D must be positive (got %d %d %d %d %d)",
+                    p->B, p->H, p->Sq, p->Sk, p->D);
+    if (p->dtype != LTCA_F32 && p->dtype != LTCA_BF16)
+        return fail(ctx, LTCA_ERR_INVALID, "unknown dtype %d", p->dtype);
+    if (p->mode != LTCA_MODE_AUTO && p->mode != LTCA_MODE_BF16 && p->mode != LTCA_MODE_FP32)
+        return fail(ctx, LTCA_ERR_INVALID, "unknown mode %d", p->mode);
+    if (!p->q || !p->k || !p->v || !p->o)
+        return fail(ctx, LTCA_ERR_INVALID, "q, k, v and o must be non-null");
+    if (!(p->scale > 0.f) || !isfinite(p->scale))
+        return fail(ctx, LTCA_ERR_INVALID, "scale must be positive and finite");
+    return LTCA_OK;
+}
+
+bool tensor_path(const ltca_attn_params* p, bool backward) {
+    if (p->mode == LTCA_MODE_FP32) return false;
+    const bool ok = backward ? attn_bwd_sm100_supported(p) : attn_fwd_sm100_supported(p);
+    if (!ok) return false;
+    if (p->dtype == LTCA_F32 && (p->D % 4)) return false;
+    return true;
+}
+
+size_t packed_bytes(const ltca_attn_params* p, int S) {
+    return align_up((size_t)p->B * p->H * S * p->D * 2, 256);
+}
+
+ltca_strides contiguous_strides(int H, int S, int D) {
+    ltca_strides s;
+    s.seq = D;
+    s.head = (int64_t)S * D;
+    s.batch = (int64_t)H * S * D;
+    return s;
+}
+
+int pack_to_bf16(ltca_ctx* ctx, const void* src, const ltca_strides& st, void* dst, int B, int H,
+                 int S, int D) {
+    if ((reinterpret_cast<uintptr_t>(src) & 15) || (st.seq % 4) || (st.head % 4) || (st.batch % 4))
+        return fail(ctx, LTCA_ERR_INVALID, "fp32 tensors need 16-byte aligned rows for the bf16 mode");
+    const size_t n4 = (size_t)B * H * S * D / 4;
+    pack_bf16_kernel<<<blocks_for(n4, 256, ctx->sm_count), 256, 0, ctx->stream>>>(
+        reinterpret_cast<const float*>(src), st, reinterpret_cast<__nv_bfloat16*>(dst), H, S, D, n4);
+    LTCA_LAUNCH_OK(ctx, "pack_bf16_kernel");
+    return LTCA_OK;
+}
+
+}  // namespace
+}  // namespace ltca
+
+using namespace ltca;
+
+extern "C" {
+
+int ltca_version(void) { return LTCA_VERSION; }
+
+int ltca_ctx_create(int device, void* stream, ltca_ctx** out) {
+    if (!out) return LTCA_ERR_INVALID;
+    *out = nullptr;
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || count <= 0 || device < 0 || device >= count) {
+        cudaGetLastError();
+        return LTCA_ERR_NO_DEVICE;
+    }
+    ltca_ctx* ctx = new (std::nothrow) ltca_ctx();
+    if (!ctx) return LTCA_ERR_CUDA;
+    ctx->device = device;
+    ctx->stream = reinterpret_cast<cudaStream_t>(stream);
+    cudaDeviceProp prop;
+    if (cudaSetDevice(device) != cudaSuccess || cudaGetDeviceProperties(&prop, device) != cudaSuccess) {
+        delete ctx;
+        return LTCA_ERR_CUDA;
+    }
+    ctx->sm_count = prop.multiProcessorCount;
+    ctx->cc_major = prop.major;
+    ctx->cc_minor = prop.minor;
+    if (prop.major != 10) {
+        delete ctx;
+        return LTCA_ERR_NO_DEVICE;       // the kernels are built for sm_100a only
+    }
+    if (cudaMalloc(&ctx->d_status, sizeof(uint32_t)) != cudaSuccess ||
+        cudaMemset(ctx->d_status, 0, sizeof(uint32_t)) != cudaSuccess) {
+        delete ctx;
+        return LTCA_ERR_CUDA;
+    }
+    *out = ctx;
+    return LTCA_OK;
+}
+
+int ltca_ctx_set_stream(ltca_ctx* ctx, void* stream) {
+    if (!ctx) return LTCA_ERR_INVALID;
+    ctx->stream = reinterpret_cast<cudaStream_t>(stream);
+    return LTCA_OK;
+}
+
+void ltca_ctx_destroy(ltca_ctx* ctx) {
+    if (!ctx) return;
+    if (ctx->d_status) cudaFree(ctx->d_status);
+    delete ctx;
+}
+
+const char* ltca_last_error(const ltca_ctx* ctx) { return ctx ? ctx->err : "null context"; }
+
+int ltca_device_status(ltca_ctx* ctx, uint32_t* status_out) {
+    if (!ctx || !status_out) return LTCA_ERR_INVALID;
+    uint32_t v = 0;
+    LTCA_CUDA_OK(ctx, cudaMemcpyAsync(&v, ctx->d_status, sizeof(v), cudaMemcpyDeviceToHost, ctx->stream));
+    LTCA_CUDA_OK(ctx, cudaStreamSynchronize(ctx->stream));
+    if (v) LTCA_CUDA_OK(ctx, cudaMemsetAsync(ctx->d_status, 0, sizeof(v), ctx->stream));
+    *status_out = v;
+    if (v) return fail(ctx, LTCA_ERR_DEVICE, "device status word 0x%08x", v);
+    return LTCA_OK;
+}
+
+int ltca_attn_uses_tensor_pipe(const ltca_attn_params* p, int backward) {
+    if (!p) return 0;
+    return tensor_path(p, backward != 0) ? 1 : 0;
+}
+
+int ltca_attn_workspace_bytes(const ltca_attn_params* p, int backward, size_t* bytes_out) {
+    if (!p || !bytes_out) return LTCA_ERR_INVALID;
+    size_t n = 0;
+    if (tensor_path(p, backward != 0)) {
+        if (p->dtype == LTCA_F32) {
+            n += packed_bytes(p, p->Sq) + 2 * packed_bytes(p, p->Sk);     // q, k, v as bf16
+            if (backward) n += packed_bytes(p, p->Sq);                     // dO as bf16
+        }
+        if (backward) n += attn_bwd_sm100_workspace(p);
+    } else if (backward) {
+        n += attn_bwd_fp32_workspace(p);
+    }
+    *bytes_out = n;
+    return LTCA_OK;
+}
+
+int ltca_attn_fwd(ltca_ctx* ctx, const ltca_attn_params* p) {
+    int rc = check_common(ctx, p);
+    if (rc) return rc;
+    LTCA_CUDA_OK(ctx, cudaSetDevice(ctx->device));
+    if (p->mode == LTCA_MODE_BF16 && !tensor_path(p, false))
+        return fail(ctx, LTCA_ERR_UNSUPPORTED,
+                    "the tensor-pipe forward needs head_dim 64 or 128 (got %d)", p->D);
+    if (!tensor_path(p, false)) return launch_attn_fwd_fp32(ctx, p);
+    if (p->dtype == LTCA_BF16)
+        return launch_attn_fwd_sm100_bf16in(ctx, p, p->q, p->k, p->v, p->q_strides, p->k_strides,
+                                            p->v_strides);
+    size_t need = 0;
+    ltca_attn_workspace_bytes(p, 0, &need);
+    if (!p->workspace || p->workspace_bytes < need)
+        return fail(ctx, LTCA_ERR_WORKSPACE, "forward needs %zu bytes of workspace", need);
+    if (reinterpret_cast<uintptr_t>(p->workspace) & 255)
+        return fail(ctx, LTCA_ERR_INVALID, "workspace must be 256-byte aligned");
+    char* w = reinterpret_cast<char*>(p->workspace);
+    void* qb = w;  w += packed_bytes(p, p->Sq);
+    void* kb = w;  w += packed_bytes(p, p->Sk);
+    void* vb = w;
+    if ((rc = pack_to_bf16(ctx, p->q, p->q_strides, qb, p->B, p->H, p->Sq, p->D))) return rc;
+    if ((rc = pack_to_bf16(ctx, p->k, p->k_strides, kb, p->B, p->H, p->Sk, p->D))) return rc;
+    if ((rc = pack_to_bf16(ctx, p->v, p->v_strides, vb, p->B, p->H, p->Sk, p->D))) return rc;
+    return launch_attn_fwd_sm100_bf16in(ctx, p, qb, kb, vb, contiguous_strides(p->H, p->Sq, p->D),
+                                        contiguous_strides(p->H, p->Sk, p->D),
+                                        contiguous_strides(p->H, p->Sk, p->D));
+}
+
+int ltca_attn_bwd(ltca_ctx* ctx, const ltca_attn_params* p) {
+    int rc = check_common(ctx, p);
+    if (rc) return rc;
+    if (!p->dout || !p->dq || !p->dk || !p->dv || !p->lse)
+        return fail(ctx, LTCA_ERR_INVALID, "backward needs dout, dq, dk, dv and lse");
+    LTCA_CUDA_OK(ctx, cudaSetDevice(ctx->device));
+    if (p->workspace && (reinterpret_cast<uintptr_t>(p->workspace) & 255))
+        return fail(ctx, LTCA_ERR_INVALID, "workspace must be 256-byte aligned");
+    if (p->mode == LTCA_MODE_BF16 && !tensor_path(p, true))
+        return fail(ctx, LTCA_ERR_UNSUPPORTED, "the tensor-pipe backward does not cover this problem");
+    if (!tensor_path(p, true)) return launch_attn_bwd_fp32(ctx, p);
+    return launch_attn_bwd_sm100(ctx, p);
+}
+
+int ltca_attn_decode(ltca_ctx* ctx, const ltca_attn_params* p) {
+    int rc = check_common(ctx, p);
+    if (rc) return rc;
+    LTCA_CUDA_OK(ctx, cudaSetDevice(ctx->device));
+    if (p->workspace && (reinterpret_cast<uintptr_t>(p->workspace) & 255))
+        return fail(ctx, LTCA_ERR_INVALID, "workspace must be 256-byte aligned");
+    return launch_attn_decode(ctx, p);
+}
+
+int ltca_attn_decode_workspace_bytes(const ltca_attn_params* p, size_t* bytes_out) {
+    if (!p || !bytes_out) return LTCA_ERR_INVALID;
+    *bytes_out = attn_decode_workspace(p);
+    return LTCA_OK;
+}
+
+int ltca_add_tensors(ltca_ctx* ctx, const float* a, const float* b, float* r, size_t n) {
+    if (!ctx) return LTCA_ERR_INVALID;
+    if (!a || !b || !r) return fail(ctx, LTCA_ERR_INVALID, "null tensor");
+    if (n == 0) return LTCA_OK;
+    const bool aligned = !((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) |
+                            reinterpret_cast<uintptr_t>(r)) & 15);
+    if (aligned)
+        add_kernel<<<blocks_for(n / 4 + 1, 256, ctx->sm_count), 256, 0, ctx->stream>>>(a, b, r, n);
+    else
+        add_scalar_kernel<<<blocks_for(n, 256, ctx->sm_count), 256, 0, ctx->stream>>>(a, b, r, n);
+    LTCA_LAUNCH_OK(ctx, "add_kernel");
+    return LTCA_OK;
+}
+
+int ltca_layer_norm(ltca_ctx* ctx, float* x, const float* gamma, const float* beta, int64_t rows,
+                    int32_t E) {
+    if (!ctx) return LTCA_ERR_INVALID;
+    if (!x || rows < 0 || E < 1) return fail(ctx, LTCA_ERR_INVALID, "bad LayerNorm arguments");
+    if (rows == 0) return LTCA_OK;
+    const int wpb = 8;
+    layer_norm_kernel<<<(unsigned)((rows + wpb - 1) / wpb), wpb * 32, 0, ctx->stream>>>(
+        x, gamma, beta, rows, E, 1e-5f);
+    LTCA_LAUNCH_OK(ctx, "layer_norm_kernel");
+    return LTCA_OK;
+}
+
+int ltca_validate_finite(ltca_ctx* ctx, const float* x, size_t n, int32_t* flag_out) {
+    if (!ctx) return LTCA_ERR_INVALID;
+    if (!x || !flag_out) return fail(ctx, LTCA_ERR_INVALID, "null argument");
+    LTCA_CUDA_OK(ctx, cudaMemsetAsync(flag_out, 0, sizeof(int32_t), ctx->stream));
+    if (n == 0) return LTCA_OK;
+    validate_finite_kernel<<<blocks_for(n, 256, ctx->sm_count), 256, 0, ctx->stream>>>(x, n, flag_out);
+    LTCA_LAUNCH_OK(ctx, "validate_finite_kernel");
+    return LTCA_OK;
+}
+
+int ltca_f32_to_bf16(ltca_ctx* ctx, const float* src, void* dst, size_t n) {
+    if (!ctx) return LTCA_ERR_INVALID;
+    if (!src || !dst) return fail(ctx, LTCA_ERR_INVALID, "null argument");
+    if (n == 0) return LTCA_OK;
+    f32_to_bf16_kernel<<<blocks_for(n, 256, ctx->sm_count), 256, 0, ctx->stream>>>(
+        src, reinterpret_cast<__nv_bfloat16*>(dst), n);
+    LTCA_LAUNCH_OK(ctx, "f32_to_bf16_kernel");
+    return LTCA_OK;
+}
+
+int ltca_bf16_to_f32(ltca_ctx* ctx, const void* src, float* dst, size_t n) {
+    if (!ctx) return LTCA_ERR_INVALID;
+    if (!src || !dst) return fail(ctx, LTCA_ERR_INVALID, "null argument");
+    if (n == 0) return LTCA_OK;
+    bf16_to_f32_kernel<<<blocks_for(n, 256, ctx->sm_count), 256, 0, ctx->stream>>>(
+        reinterpret_cast<const __nv_bfloat16*>(src), dst, n);
+    LTCA_LAUNCH_OK(ctx, "bf16_to_f32_kernel");
+    return LTCA_OK;
+}
+
+}  // extern "C"

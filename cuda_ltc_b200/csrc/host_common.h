@@ -1,0 +1,116 @@
+// Host-side plumbing shared by the C-ABI translation units: the context object, error
+// reporting, TMA tensor-map construction through the driver entry point, small helpers.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdarg.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string.h>
+
+#include "../../include/ltc_attn.h"
+
+struct ltca_ctx {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    int sm_count = 0;
+    int cc_major = 0, cc_minor = 0;
+    uint32_t* d_status = nullptr;     // device status word (allocated once at context creation)
+    char err[512] = {0};
+};
+
+namespace ltca {
+
+inline int fail(ltca_ctx* ctx, int code, const char* fmt, ...) {
+    if (ctx) {
+        va_list ap;
+        va_start(ap, fmt);
+        vsnprintf(ctx->err, sizeof(ctx->err), fmt, ap);
+        va_end(ap);
+    }
+    return code;
+}
+
+#define LTCA_CUDA_OK(ctx, expr)                                                             \
+    do {                                                                                    \
+        cudaError_t e__ = (expr);                                                           \
+        if (e__ != cudaSuccess)                                                             \
+            return ::ltca::fail((ctx), LTCA_ERR_CUDA, "%s failed: %s", #expr,               \
+                                cudaGetErrorString(e__));                                   \
+    } while (0)
+
+#define LTCA_LAUNCH_OK(ctx, what)                                                           \
+    do {                                                                                    \
+        cudaError_t e__ = cudaGetLastError();                                               \
+        if (e__ != cudaSuccess)                                                             \
+            return ::ltca::fail((ctx), LTCA_ERR_CUDA, "launch of %s failed: %s", (what),    \
+                                cudaGetErrorString(e__));                                   \
+    } while (0)
+
+inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+inline int elem_size(int dtype) { return dtype == LTCA_BF16 ? 2 : 4; }
+
+// cuTensorMapEncodeTiled fetched at run time, so the library links against the CUDA runtime only.
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = []() -> EncodeTiledFn {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) !=
+                cudaSuccess || q != cudaDriverEntryPointSuccess)
+            return nullptr;
+        return reinterpret_cast<EncodeTiledFn>(p);
+    }();
+    return fn;
+}
+
+// Tensor map over a [batch, head, seq, dim] tensor (dim contiguous) with a (box_dim x box_rows)
+// tile, 128-byte swizzle.  `es` is the element size in bytes (2 = bf16, 4 = fp32).
+inline int make_tmap_bhsd(ltca_ctx* ctx, CUtensorMap* map, const void* base, int es,
+                          int B, int H, int S, int D, const ltca_strides& st,
+                          int box_dim, int box_rows) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return fail(ctx, LTCA_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
+    if ((reinterpret_cast<uintptr_t>(base) & 15) != 0)
+        return fail(ctx, LTCA_ERR_INVALID, "tensor base must be 16-byte aligned for TMA");
+    const int64_t sb = st.batch * es, sh = st.head * es, ss = st.seq * es;
+    if ((ss & 15) || (H > 1 && (sh & 15)) || (B > 1 && (sb & 15)))
+        return fail(ctx, LTCA_ERR_INVALID, "tensor strides must be multiples of 16 bytes for TMA");
+    cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)S, (cuuint64_t)H, (cuuint64_t)B};
+    // a stride of an extent-1 dimension is never used for addressing, but must still be valid
+    cuuint64_t strides[3] = {(cuuint64_t)ss, (cuuint64_t)(H > 1 ? sh : ss * S),
+                             (cuuint64_t)(B > 1 ? sb : (H > 1 ? sh * H : ss * S))};
+    for (int i = 0; i < 3; ++i)
+        if (strides[i] == 0 || (strides[i] & 15)) strides[i] = 16;
+    cuuint32_t box[4] = {(cuuint32_t)box_dim, (cuuint32_t)box_rows, 1, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = fn(map, es == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32,
+                    4, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return fail(ctx, LTCA_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    return LTCA_OK;
+}
+
+}  // namespace ltca
+
+// Kernel launchers implemented in the .cu files of this directory (internal, not exported).
+namespace ltca {
+int launch_attn_fwd_sm100(ltca_ctx* ctx, const ltca_attn_params* p);
+bool attn_fwd_sm100_supported(const ltca_attn_params* p);
+int launch_attn_bwd_sm100(ltca_ctx* ctx, const ltca_attn_params* p);
+bool attn_bwd_sm100_supported(const ltca_attn_params* p);
+size_t attn_bwd_sm100_workspace(const ltca_attn_params* p);
+int launch_attn_fwd_fp32(ltca_ctx* ctx, const ltca_attn_params* p);
+int launch_attn_bwd_fp32(ltca_ctx* ctx, const ltca_attn_params* p);
+size_t attn_bwd_fp32_workspace(const ltca_attn_params* p);
+int launch_attn_decode(ltca_ctx* ctx, const ltca_attn_params* p);
+size_t attn_decode_workspace(const ltca_attn_params* p);
+}  // namespace ltca

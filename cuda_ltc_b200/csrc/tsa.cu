@@ -1,0 +1,331 @@
+// TimeSelfAttention module: out = LayerNorm(x + MHA(x)) and its backward, as the reference's
+// CuDNNTimeSelfAttention computes them (reference src/ml/cudnn_time_self_attention.cu:211-368
+// with the attention configured by include/cuDNN_ops.h:152-178).
+//
+// Data flow of the forward (all buffers fp32, row = one (batch, time) position):
+//   x [rows,E] --Wq,Wk,Wv--> q,k,v [rows,H*W] --attention core--> ctx [rows,H*W] --Wo--> y [rows,E]
+//   out = LayerNorm(y + x)        (residual and LayerNorm fused into one row pass)
+// The attention core reads q/k/v and writes ctx through strided [B,H,S,W] views of the
+// row-major projection buffers, so the reference's reshape kernels
+// (src/ml/flash_attention.cu:402-455) have no counterpart here.
+//
+// The projections run on an fp32 FMA GEMM (exact mode).  Backward follows the reference:
+// the incoming gradient passes through LayerNorm and the residual unchanged
+// (src/ml/cudnn_time_self_attention.cu:291-299), dx = dQ Wq^T + dK Wk^T + dV Wv^T.
+#include "host_common.h"
+
+namespace ltca {
+
+namespace {
+
+constexpr int kGT = 64;     // GEMM tile (M and N)
+constexpr int kGK = 16;     // GEMM K step
+
+// C[M,N] (+)= op(A) op(B) (+ bias[N]); row-major storage.
+//   ta == 0: A is [M,K] (lda = K-extent stride), ta == 1: A is stored [K,M].
+//   tb == 0: B is [K,N],                          tb == 1: B is stored [N,K].
+struct GemmArgs {
+    const float *A, *B, *bias;
+    float* C;
+    int M, N, K;
+    int lda, ldb, ldc;
+    int ta, tb, accumulate;
+};
+
+__global__ void __launch_bounds__(256) gemm_fp32_kernel(const GemmArgs g) {
+    __shared__ float As[kGK][kGT + 1];
+    __shared__ float Bs[kGK][kGT + 1];
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    const int m0 = blockIdx.y * kGT, n0 = blockIdx.x * kGT;
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+
+    for (int k0 = 0; k0 < g.K; k0 += kGK) {
+        for (int idx = threadIdx.x; idx < kGT * kGK; idx += 256) {
+            int m, k;
+            if (g.ta) { m = idx % kGT; k = idx / kGT; } else { k = idx % kGK; m = idx / kGK; }
+            const int gm = m0 + m, gk = k0 + k;
+            float v = 0.f;
+            if (gm < g.M && gk < g.K)
+                v = g.ta ? g.A[(int64_t)gk * g.lda + gm] : g.A[(int64_t)gm * g.lda + gk];
+            As[k][m] = v;
+        }
+        for (int idx = threadIdx.x; idx < kGT * kGK; idx += 256) {
+            int n, k;
+            if (g.tb) { k = idx % kGK; n = idx / kGK; } else { n = idx % kGT; k = idx / kGT; }
+            const int gn = n0 + n, gk = k0 + k;
+            float v = 0.f;
+            if (gn < g.N && gk < g.K)
+                v = g.tb ? g.B[(int64_t)gn * g.ldb + gk] : g.B[(int64_t)gk * g.ldb + gn];
+            Bs[k][n] = v;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < kGK; ++k) {
+            float a[4], b[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) a[i] = As[k][ty + 16 * i];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) b[j] = Bs[k][tx + 16 * j];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int gm = m0 + ty + 16 * i;
+        if (gm >= g.M) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int gn = n0 + tx + 16 * j;
+            if (gn >= g.N) continue;
+            float v = acc[i][j];
+            if (g.bias) v += g.bias[gn];
+            float* c = g.C + (int64_t)gm * g.ldc + gn;
+            *c = g.accumulate ? *c + v : v;
+        }
+    }
+}
+
+int gemm(ltca_ctx* ctx, const float* A, const float* B, const float* bias, float* C, int M, int N,
+         int K, int lda, int ldb, int ldc, int ta, int tb, int accumulate) {
+    GemmArgs g{A, B, bias, C, M, N, K, lda, ldb, ldc, ta, tb, accumulate};
+    dim3 grid((N + kGT - 1) / kGT, (M + kGT - 1) / kGT);
+    gemm_fp32_kernel<<<grid, 256, 0, ctx->stream>>>(g);
+    LTCA_LAUNCH_OK(ctx, "gemm_fp32_kernel");
+    return LTCA_OK;
+}
+
+// out[row] = LayerNorm(y[row] (+ x[row])) or just the sum / a copy; one warp per row.
+__global__ void residual_layer_norm_kernel(const float* __restrict__ y, const float* __restrict__ x,
+                                           const float* __restrict__ gamma,
+                                           const float* __restrict__ beta, float* __restrict__ out,
+                                           int64_t rows, int E, int use_res, int use_ln, float eps) {
+    const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const int lane = threadIdx.x & 31;
+    const float* yr = y + row * E;
+    const float* xr = x + row * E;
+    float* outr = out + row * E;
+    float sum = 0.f;
+    for (int i = lane; i < E; i += 32) {
+        const float v = yr[i] + (use_res ? xr[i] : 0.f);
+        outr[i] = v;
+        sum += v;
+    }
+    if (!use_ln) return;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    const float mean = sum / E;
+    float var = 0.f;
+    for (int i = lane; i < E; i += 32) {
+        const float d = outr[i] - mean;
+        var = fmaf(d, d, var);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) var += __shfl_xor_sync(0xffffffffu, var, o);
+    const float inv_std = rsqrtf(var / E + eps);
+    for (int i = lane; i < E; i += 32)
+        outr[i] = (outr[i] - mean) * inv_std * (gamma ? gamma[i] : 1.f) + (beta ? beta[i] : 0.f);
+}
+
+struct Plan {
+    int64_t rows;
+    int HW;
+    size_t buf;          // bytes of one [rows, HW] fp32 buffer
+    size_t lse;          // bytes of lse
+    size_t y;            // bytes of one [rows, E] buffer
+    size_t attn_fwd, attn_bwd;
+};
+
+void fill_attn(const ltca_tsa_params* t, ltca_attn_params* a) {
+    memset(a, 0, sizeof(*a));
+    const int HW = t->H * t->head_width;
+    a->B = t->B; a->H = t->H; a->Sq = t->S; a->Sk = t->S; a->D = t->head_width;
+    a->dtype = LTCA_F32;
+    a->mode = t->mode;
+    a->causal = t->causal;
+    a->scale = t->scale;
+    a->score_clamp = t->score_clamp;
+    ltca_strides st;
+    st.head = t->head_width;
+    if (t->time_major) { st.batch = HW; st.seq = (int64_t)t->B * HW; }
+    else               { st.batch = (int64_t)t->S * HW; st.seq = HW; }
+    a->q_strides = a->k_strides = a->v_strides = a->o_strides = st;
+    a->do_strides = a->dq_strides = a->dk_strides = a->dv_strides = st;
+    a->keep_mask = t->keep_mask;
+    a->kv_len = t->kv_len;
+}
+
+int make_plan(const ltca_tsa_params* t, Plan* pl) {
+    pl->rows = (int64_t)t->B * t->S;
+    pl->HW = t->H * t->head_width;
+    pl->buf = align_up((size_t)pl->rows * pl->HW * sizeof(float), 256);
+    pl->lse = align_up((size_t)t->B * t->H * t->S * sizeof(float), 256);
+    pl->y = align_up((size_t)pl->rows * t->E * sizeof(float), 256);
+    ltca_attn_params a;
+    fill_attn(t, &a);
+    // pointers only need to be non-null for the size queries
+    int rc = ltca_attn_workspace_bytes(&a, 0, &pl->attn_fwd);
+    if (rc) return rc;
+    return ltca_attn_workspace_bytes(&a, 1, &pl->attn_bwd);
+}
+
+int check(ltca_ctx* ctx, const ltca_tsa_params* t) {
+    if (!ctx) return LTCA_ERR_INVALID;
+    if (!t) return fail(ctx, LTCA_ERR_INVALID, "null parameter block");
+    if (t->B < 1 || t->S < 1 || t->E < 1 || t->H < 1 || t->head_width < 1)
+        return fail(ctx, LTCA_ERR_INVALID, "B, S, E, H, head_width must be positive");
+    // same validation as the reference constructor (src/ml/time_self_attention.cu:25-35)
+    if (t->E % t->H != 0)
+        return fail(ctx, LTCA_ERR_INVALID, "input_dim (%d) must be divisible by num_heads (%d)",
+                    t->E, t->H);
+    if (!t->x || !t->wq || !t->wk || !t->wv || !t->wo)
+        return fail(ctx, LTCA_ERR_INVALID, "x and the four weight matrices must be non-null");
+    if (!(t->scale > 0.f)) return fail(ctx, LTCA_ERR_INVALID, "scale must be positive");
+    if (reinterpret_cast<uintptr_t>(t->workspace) & 255)
+        return fail(ctx, LTCA_ERR_INVALID, "workspace must be 256-byte aligned");
+    return LTCA_OK;
+}
+
+// Projections + attention forward into workspace; returns pointers into it.
+struct FwdBufs { float *q, *k, *v, *ctx, *lse; char* rest; };
+
+int forward_core(ltca_ctx* ctx, const ltca_tsa_params* t, const Plan& pl, char* w, FwdBufs* fb,
+                 size_t attn_ws_bytes) {
+    fb->q = reinterpret_cast<float*>(w);   w += pl.buf;
+    fb->k = reinterpret_cast<float*>(w);   w += pl.buf;
+    fb->v = reinterpret_cast<float*>(w);   w += pl.buf;
+    fb->ctx = reinterpret_cast<float*>(w); w += pl.buf;
+    fb->lse = reinterpret_cast<float*>(w); w += pl.lse;
+    fb->rest = w;
+    const int rows = (int)pl.rows, E = t->E, HW = pl.HW;
+    int rc;
+    if ((rc = gemm(ctx, t->x, t->wq, t->bq, fb->q, rows, HW, E, E, HW, HW, 0, 0, 0))) return rc;
+    if ((rc = gemm(ctx, t->x, t->wk, t->bk, fb->k, rows, HW, E, E, HW, HW, 0, 0, 0))) return rc;
+    if ((rc = gemm(ctx, t->x, t->wv, t->bv, fb->v, rows, HW, E, E, HW, HW, 0, 0, 0))) return rc;
+    ltca_attn_params a;
+    fill_attn(t, &a);
+    a.q = fb->q; a.k = fb->k; a.v = fb->v; a.o = fb->ctx; a.lse = fb->lse;
+    a.workspace = attn_ws_bytes ? fb->rest : nullptr;
+    a.workspace_bytes = attn_ws_bytes;
+    rc = ltca_attn_fwd(ctx, &a);
+    return rc;
+}
+
+}  // namespace
+}  // namespace ltca
+
+using namespace ltca;
+
+extern "C" {
+
+int ltca_tsa_workspace_bytes(const ltca_tsa_params* t, int which, size_t* bytes_out) {
+    if (!t || !bytes_out || which < 0 || which > 3) return LTCA_ERR_INVALID;
+    Plan pl;
+    int rc = make_plan(t, &pl);
+    if (rc) return rc;
+    size_t n = 4 * pl.buf + pl.lse;                       // q, k, v, ctx, lse
+    if (which == 0) {
+        n += pl.y;                                        // y before residual / LayerNorm
+        n += pl.attn_fwd;
+    } else {
+        n += 4 * pl.buf;                                  // dctx, dq, dk, dv
+        n += pl.attn_fwd > pl.attn_bwd ? pl.attn_fwd : pl.attn_bwd;
+    }
+    *bytes_out = n;
+    return LTCA_OK;
+}
+
+int ltca_tsa_fwd(ltca_ctx* ctx, const ltca_tsa_params* t) {
+    int rc = check(ctx, t);
+    if (rc) return rc;
+    if (!t->out) return fail(ctx, LTCA_ERR_INVALID, "out must be non-null");
+    if (t->use_layer_norm && (!t->ln_gamma || !t->ln_beta))
+        return fail(ctx, LTCA_ERR_INVALID, "LayerNorm needs gamma and beta");
+    Plan pl;
+    if ((rc = make_plan(t, &pl))) return rc;
+    size_t need = 0;
+    ltca_tsa_workspace_bytes(t, 0, &need);
+    if (!t->workspace || t->workspace_bytes < need)
+        return fail(ctx, LTCA_ERR_WORKSPACE, "forward needs %zu bytes of workspace", need);
+    char* w = reinterpret_cast<char*>(t->workspace);
+    float* y = reinterpret_cast<float*>(w);
+    w += pl.y;
+    FwdBufs fb;
+    if ((rc = forward_core(ctx, t, pl, w, &fb, pl.attn_fwd))) return rc;
+    const int rows = (int)pl.rows;
+    if ((rc = gemm(ctx, fb.ctx, t->wo, t->bo, y, rows, t->E, pl.HW, pl.HW, t->E, t->E, 0, 0, 0)))
+        return rc;
+    const int wpb = 8;
+    residual_layer_norm_kernel<<<(unsigned)((pl.rows + wpb - 1) / wpb), wpb * 32, 0, ctx->stream>>>(
+        y, t->x, t->ln_gamma, t->ln_beta, t->out, pl.rows, t->E, t->use_residual, t->use_layer_norm,
+        1e-5f);
+    LTCA_LAUNCH_OK(ctx, "residual_layer_norm_kernel");
+    return LTCA_OK;
+}
+
+static int tsa_backward(ltca_ctx* ctx, const ltca_tsa_params* t, bool want_dx, bool want_dw) {
+    int rc = check(ctx, t);
+    if (rc) return rc;
+    if (!t->dy) return fail(ctx, LTCA_ERR_INVALID, "dy must be non-null");
+    if (want_dx && !t->dx) return fail(ctx, LTCA_ERR_INVALID, "dx must be non-null");
+    if (want_dw && (!t->dwq || !t->dwk || !t->dwv || !t->dwo))
+        return fail(ctx, LTCA_ERR_INVALID, "dwq, dwk, dwv, dwo must be non-null");
+    Plan pl;
+    if ((rc = make_plan(t, &pl))) return rc;
+    size_t need = 0;
+    ltca_tsa_workspace_bytes(t, 1, &need);
+    if (!t->workspace || t->workspace_bytes < need)
+        return fail(ctx, LTCA_ERR_WORKSPACE, "backward needs %zu bytes of workspace", need);
+    char* w = reinterpret_cast<char*>(t->workspace);
+    float* dctx = reinterpret_cast<float*>(w); w += pl.buf;
+    float* dq = reinterpret_cast<float*>(w);   w += pl.buf;
+    float* dk = reinterpret_cast<float*>(w);   w += pl.buf;
+    float* dv = reinterpret_cast<float*>(w);   w += pl.buf;
+    FwdBufs fb;
+    // the forward is recomputed, as the reference's caller does before each backward
+    // (src/ml/ml_liquid_net.cu:715-721)
+    if ((rc = forward_core(ctx, t, pl, w, &fb, pl.attn_fwd))) return rc;
+    const int rows = (int)pl.rows, E = t->E, HW = pl.HW;
+    // dctx = dy Wo^T
+    if ((rc = gemm(ctx, t->dy, t->wo, nullptr, dctx, rows, HW, E, E, E, HW, 0, 1, 0))) return rc;
+    ltca_attn_params a;
+    fill_attn(t, &a);
+    a.q = fb.q; a.k = fb.k; a.v = fb.v; a.o = fb.ctx; a.lse = fb.lse;
+    a.dout = dctx; a.dq = dq; a.dk = dk; a.dv = dv;
+    a.workspace = pl.attn_bwd ? fb.rest : nullptr;
+    a.workspace_bytes = pl.attn_bwd;
+    if ((rc = ltca_attn_bwd(ctx, &a))) return rc;
+    if (want_dx) {
+        if ((rc = gemm(ctx, dq, t->wq, nullptr, t->dx, rows, E, HW, HW, HW, E, 0, 1, 0))) return rc;
+        if ((rc = gemm(ctx, dk, t->wk, nullptr, t->dx, rows, E, HW, HW, HW, E, 0, 1, 1))) return rc;
+        if ((rc = gemm(ctx, dv, t->wv, nullptr, t->dx, rows, E, HW, HW, HW, E, 0, 1, 1))) return rc;
+    }
+    if (want_dw) {
+        // dW = x^T dQ  ([E, rows] x [rows, HW]),  dWo = ctx^T dy  ([HW, rows] x [rows, E])
+        if ((rc = gemm(ctx, t->x, dq, nullptr, t->dwq, E, HW, rows, E, HW, HW, 1, 0, 0))) return rc;
+        if ((rc = gemm(ctx, t->x, dk, nullptr, t->dwk, E, HW, rows, E, HW, HW, 1, 0, 0))) return rc;
+        if ((rc = gemm(ctx, t->x, dv, nullptr, t->dwv, E, HW, rows, E, HW, HW, 1, 0, 0))) return rc;
+        if ((rc = gemm(ctx, fb.ctx, t->dy, nullptr, t->dwo, HW, E, rows, HW, E, E, 1, 0, 0))) return rc;
+    }
+    return LTCA_OK;
+}
+
+int ltca_tsa_bwd_data(ltca_ctx* ctx, const ltca_tsa_params* t) {
+    return tsa_backward(ctx, t, true, false);
+}
+int ltca_tsa_bwd_weights(ltca_ctx* ctx, const ltca_tsa_params* t) {
+    return tsa_backward(ctx, t, false, true);
+}
+int ltca_tsa_bwd(ltca_ctx* ctx, const ltca_tsa_params* t) {
+    return tsa_backward(ctx, t, true, true);
+}
+
+}  // extern "C"

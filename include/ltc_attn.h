@@ -1,0 +1,211 @@
+/*
+ * ltc_attn.h -- C ABI of the B200 (sm_100a) attention path that replaces the attention
+ * hot path of Sirius437/CUDA_LTC.
+ *
+ * The library is a plain C-ABI shared object (libltc_attn.so): pointers, sizes and status
+ * codes only.  The C++ classes in ltc_attn_shim.hpp (cudatrader::FlashAttention,
+ * cudatrader::TimeSelfAttention) are header-only wrappers over these entry points and keep
+ * the reference's signatures.  Every entry point below names the reference interface it
+ * replaces (paths are inside the reference project).
+ *
+ * General rules
+ *   - All pointers are DEVICE pointers unless a comment says "host".
+ *   - Outputs and workspace come from the caller (ltca_*_workspace_bytes tells how much); the
+ *     only device allocation the library makes is the 4-byte status word of a context, made
+ *     in ltca_ctx_create and released in ltca_ctx_destroy.  Work is enqueued on the context's
+ *     stream; nothing synchronises the device unless stated.
+ *   - Return value: 0 on success, a negative ltca_status otherwise; ltca_last_error() gives
+ *     the text of the last failure on that context.  Nothing throws, prints or exits.
+ *   - There is no CPU fallback: on a machine without an sm_100 GPU ltca_ctx_create fails.
+ */
+#ifndef LTC_ATTN_H_
+#define LTC_ATTN_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define LTCA_VERSION 100
+
+typedef enum {
+    LTCA_OK              =  0,
+    LTCA_ERR_INVALID     = -1,  /* bad argument (shape, null pointer, stride, alignment)      */
+    LTCA_ERR_UNSUPPORTED = -2,  /* valid request outside what the kernels implement            */
+    LTCA_ERR_CUDA        = -3,  /* a CUDA runtime/driver call failed                           */
+    LTCA_ERR_WORKSPACE   = -4,  /* workspace missing or too small                              */
+    LTCA_ERR_DEVICE      = -5,  /* a kernel reported a problem through its device status word  */
+    LTCA_ERR_NO_DEVICE   = -6   /* no sm_100 device                                            */
+} ltca_status;
+
+/* Storage type of Q, K, V, O, dO, dQ, dK, dV. */
+typedef enum { LTCA_F32 = 0, LTCA_BF16 = 1 } ltca_dtype;
+
+/*
+ * Arithmetic of the two contractions.
+ *   LTCA_MODE_BF16 : bf16 operands on the tcgen05 tensor pipe, fp32 accumulation in tensor
+ *                    memory, fp32 softmax.  fp32 storage is rounded to bf16 on the fly.
+ *   LTCA_MODE_FP32 : fp32 FMA arithmetic end to end (the 1e-5 mode).
+ *   LTCA_MODE_AUTO : BF16 when the shape is supported by the tensor-pipe kernels, else FP32.
+ */
+typedef enum { LTCA_MODE_AUTO = 0, LTCA_MODE_BF16 = 1, LTCA_MODE_FP32 = 3 } ltca_mode;
+
+typedef struct ltca_ctx ltca_ctx;
+
+/* Element strides of a [batch, head, seq, head_dim] tensor; head_dim is contiguous.  This one
+ * description covers the reference's [B,H,S,D] buffers (src/ml/flash_attention.cu:19-23) and
+ * the un-permuted [B*S, H*D] projection outputs, so the reshape kernels
+ * (src/ml/flash_attention.cu:402-455) are not needed. */
+typedef struct {
+    int64_t batch;
+    int64_t head;
+    int64_t seq;
+} ltca_strides;
+
+/*
+ * One attention problem: O = softmax(mask(scale * Q K^T)) V per (batch, head).
+ * Replaces the argument list of flashAttentionKernel / FlashAttention::flashAttention
+ * (src/ml/flash_attention.cu:18-28, :994-1046; include/flash_attention.h:213-230).
+ */
+typedef struct {
+    int32_t B, H, Sq, Sk, D;
+    int32_t dtype;              /* ltca_dtype */
+    int32_t mode;               /* ltca_mode */
+    int32_t causal;             /* key j visible to query i iff j <= i + (Sk - Sq) */
+    float   scale;              /* the reference uses 1/sqrt(D) (flash_attention.cu:998) */
+    float   score_clamp;        /* > 0: s = min(s, score_clamp) after scaling; the reference
+                                   clamps at 10 (flash_attention.cu:167).  <= 0: no clamp */
+    const void* q;  ltca_strides q_strides;    /* [B,H,Sq,D] */
+    const void* k;  ltca_strides k_strides;    /* [B,H,Sk,D] */
+    const void* v;  ltca_strides v_strides;    /* [B,H,Sk,D] */
+    void*       o;  ltca_strides o_strides;    /* [B,H,Sq,D] */
+    float*      lse;                           /* [B,H,Sq] natural-log sum-exp; required by
+                                                  backward, may be NULL for forward only */
+    const float*   keep_mask;   /* optional dense [B,Sq,Sk] fp32; value 0 hides the key
+                                   (flash_attention.cu:161-164); NULL: none */
+    const int32_t* kv_len;      /* optional [B]: keys j >= kv_len[b] are hidden; NULL: all Sk */
+    /* backward only */
+    const void* dout; ltca_strides do_strides; /* [B,H,Sq,D] */
+    void* dq; ltca_strides dq_strides;         /* [B,H,Sq,D] */
+    void* dk; ltca_strides dk_strides;         /* [B,H,Sk,D] */
+    void* dv; ltca_strides dv_strides;         /* [B,H,Sk,D] */
+    void*  workspace;           /* scratch, 256-byte aligned */
+    size_t workspace_bytes;
+} ltca_attn_params;
+
+/* ---- context ---------------------------------------------------------------------------- */
+
+/* Binds a device and a stream (cudaStream_t passed as void*; NULL = default stream).
+ * Replaces the per-object handle set-up of FlashAttention::FlashAttention
+ * (src/ml/flash_attention.cu:485-549) and cudnn_ops::CuDNNHandle (include/cuDNN_ops.h:95-115). */
+int ltca_ctx_create(int device, void* stream, ltca_ctx** out);
+int ltca_ctx_set_stream(ltca_ctx* ctx, void* stream);
+void ltca_ctx_destroy(ltca_ctx* ctx);
+/* Text of the last error on this context (host string, valid until the next call). */
+const char* ltca_last_error(const ltca_ctx* ctx);
+int ltca_version(void);
+
+/* Reads and clears the device status word that kernels set when a bounded wait ran out or an
+ * internal check failed.  Synchronises the context's stream.  0 = clean. */
+int ltca_device_status(ltca_ctx* ctx, uint32_t* status_out);
+
+/* ---- attention core --------------------------------------------------------------------- */
+
+/* Scratch needed by ltca_attn_fwd (backward = 0) or ltca_attn_bwd (backward = 1). */
+int ltca_attn_workspace_bytes(const ltca_attn_params* p, int backward, size_t* bytes_out);
+
+/* 1 if the tensor-pipe (tcgen05) kernels cover this problem, 0 if it runs on the fp32 path. */
+int ltca_attn_uses_tensor_pipe(const ltca_attn_params* p, int backward);
+
+/* Forward.  Replaces flashAttentionKernel and its launch
+ * (src/ml/flash_attention.cu:18-272, :994-1046). */
+int ltca_attn_fwd(ltca_ctx* ctx, const ltca_attn_params* p);
+
+/* Backward of the core: dQ, dK, dV from dO with recomputation of P from Q, K and lse.
+ * The reference reaches this arithmetic through cudnnMultiHeadAttnBackwardData
+ * (src/ml/cuDNN_ops.cu:240-337); FlashAttention itself has no backward. */
+int ltca_attn_bwd(ltca_ctx* ctx, const ltca_attn_params* p);
+
+/* Single-query step over a key/value cache: Sq must be 1, kv_len gives the live length of
+ * each sequence.  The reference has no such call; the closest hook is the currIdx argument
+ * of cudnnMultiHeadAttnForward, always -1 there (src/ml/cuDNN_ops.cu:206). */
+int ltca_attn_decode(ltca_ctx* ctx, const ltca_attn_params* p);
+/* Scratch needed by ltca_attn_decode: zero when batch x heads alone fills the GPU, otherwise
+ * room for the partial results of the key-range split. */
+int ltca_attn_decode_workspace_bytes(const ltca_attn_params* p, size_t* bytes_out);
+
+/* ---- TimeSelfAttention module ----------------------------------------------------------- */
+
+/*
+ * out = LayerNorm( x + MHA(x) ) as CuDNNTimeSelfAttention::forward computes it
+ * (src/ml/cudnn_time_self_attention.cu:211-252) with the attention configured by
+ * AttentionDescriptor::configure (include/cuDNN_ops.h:152-178).
+ *
+ * x, out, dy, dx : [rows = B*S, E] fp32.  Row r is (b, t): r = b*S + t, or r = t*B + b when
+ * time_major is set (the order the reference gives cuDNN, include/cuDNN_ops.h:322-328).
+ * wq, wk, wv : [E, H*W] row-major, y = x w.   wo : [H*W, E].   W = head_width:
+ * E (reference-compatible, include/cuDNN_ops.h:166-169) or E/H (benchmark form).
+ * Biases are optional (FlashAttention form, src/ml/flash_attention.cu:458-470).
+ */
+typedef struct {
+    int32_t B, S, E, H;
+    int32_t head_width;         /* W */
+    int32_t causal;
+    int32_t time_major;
+    int32_t use_residual;       /* cudnn_time_self_attention.cu:240-243 */
+    int32_t use_layer_norm;     /* cudnn_time_self_attention.cu:246-249, eps 1e-5 */
+    int32_t mode;               /* ltca_mode for projections and attention */
+    float   scale;              /* the reference passes 1.0 (cudnn_time_self_attention.cu:149) */
+    float   score_clamp;
+    const float* x;
+    const float *wq, *wk, *wv, *wo;
+    const float *bq, *bk, *bv, *bo;            /* optional */
+    const float *ln_gamma, *ln_beta;           /* [E], required when use_layer_norm */
+    const float*   keep_mask;                  /* optional [B,S,S], 0 hides */
+    const int32_t* kv_len;                     /* optional [B] */
+    float* out;                                /* forward output [rows, E] */
+    /* backward */
+    const float* dy;                           /* gradient at the module output; LayerNorm
+                                                  and residual pass it through unchanged
+                                                  (cudnn_time_self_attention.cu:291-299) */
+    float* dx;                                 /* bwd_data output [rows, E] */
+    float *dwq, *dwk, *dwv, *dwo;              /* bwd_weights outputs, overwritten
+                                                  (CUDNN_WGRAD_MODE_SET, cuDNN_ops.cu:366-385) */
+    void*  workspace;
+    size_t workspace_bytes;
+} ltca_tsa_params;
+
+/* which: 0 forward, 1 backward-data, 2 backward-weights, 3 both backward passes. */
+int ltca_tsa_workspace_bytes(const ltca_tsa_params* p, int which, size_t* bytes_out);
+/* Replaces CuDNNTimeSelfAttention::forward (src/ml/cudnn_time_self_attention.cu:211-252). */
+int ltca_tsa_fwd(ltca_ctx* ctx, const ltca_tsa_params* p);
+/* Replaces CuDNNTimeSelfAttention::backward (src/ml/cudnn_time_self_attention.cu:254-302). */
+int ltca_tsa_bwd_data(ltca_ctx* ctx, const ltca_tsa_params* p);
+/* Replaces CuDNNTimeSelfAttention::backwardWeights (src/ml/cudnn_time_self_attention.cu:304-368). */
+int ltca_tsa_bwd_weights(ltca_ctx* ctx, const ltca_tsa_params* p);
+/* Both of the above in one pass (one recomputation of the forward instead of two); the order
+ * backwardWeights-then-backward of the reference's training step
+ * (src/ml/ml_liquid_net.cu:734-737) collapses into this call. */
+int ltca_tsa_bwd(ltca_ctx* ctx, const ltca_tsa_params* p);
+
+/* ---- small tensor helpers on the path ---------------------------------------------------- */
+
+/* r = a + b, n fp32 elements.  Replaces cudatrader::addTensors (src/cuda_tensor_utils.cu:25-41). */
+int ltca_add_tensors(ltca_ctx* ctx, const float* a, const float* b, float* r, size_t n);
+/* In-place LayerNorm of [rows, E] fp32, biased variance, eps 1e-5.
+ * Replaces applyLayerNorm / layerNormKernel (src/ml/cudnn_time_self_attention.cu:9-68, :496-508). */
+int ltca_layer_norm(ltca_ctx* ctx, float* x, const float* gamma, const float* beta,
+                    int64_t rows, int32_t E);
+/* Sets *flag_out (device int) to 1 if any of n values is NaN or Inf, else 0.
+ * Replaces validateGradientsKernel (src/cuda_tensor_utils.cu:14-22). */
+int ltca_validate_finite(ltca_ctx* ctx, const float* x, size_t n, int32_t* flag_out);
+/* fp32 <-> bf16 conversion of n elements (round to nearest even). */
+int ltca_f32_to_bf16(ltca_ctx* ctx, const float* src, void* dst, size_t n);
+int ltca_bf16_to_f32(ltca_ctx* ctx, const void* src, float* dst, size_t n);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LTC_ATTN_H_ */

@@ -1,0 +1,222 @@
+"""GPU parity tests of the attention core, through the C ABI, against the fp64 oracle.
+
+Tolerances (north_star): fp32 mode max-abs 1e-5; tensor-pipe (bf16 operand) mode max-abs 2e-3
+and rel-L2 1e-3, with the oracle consuming the bf16-rounded inputs.  When the OUTPUT is stored
+as bf16 its own rounding (half an ulp = 2^-9 relative) is allowed on top, and written as such.
+"""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from cuda_ltc_b200 import _lib
+from util import bf16_round, keep_mask, max_abs, randn, rel_l2
+
+pytestmark = pytest.mark.gpu
+
+FP32_TOL = 1e-5
+TC_MAX_ABS, TC_REL_L2 = 2e-3, 1e-3
+
+
+def dev(a, dtype=torch.float32):
+    return torch.from_numpy(np.ascontiguousarray(a)).to("cuda", dtype)
+
+
+def make_case(B, H, Sq, Sk, D, seed, scale_in=1.0):
+    q = randn((B, H, Sq, D), seed, scale_in)
+    k = randn((B, H, Sk, D), seed + 1, scale_in)
+    v = randn((B, H, Sk, D), seed + 2, scale_in)
+    do = randn((B, H, Sq, D), seed + 3, scale_in)
+    return q, k, v, do
+
+
+FP32_CASES = [
+    # B, H, Sq, Sk, D, causal, mask, kvlen, clamp
+    (2, 4, 64, 64, 32, False, False, False, 0.0),      # config 1 of the benchmark
+    (2, 2, 8, 8, 16, False, False, False, 10.0),       # the reference test fixture
+    (2, 4, 16, 16, 16, True, True, False, 10.0),
+    (1, 2, 1, 1, 16, False, False, False, 0.0),
+    (1, 2, 7, 7, 20, True, False, False, 0.0),
+    (2, 1, 17, 17, 64, True, False, True, 0.0),
+    (1, 2, 129, 129, 128, True, False, False, 0.0),
+    (2, 2, 33, 70, 24, False, True, True, 0.7),
+    (1, 1, 70, 33, 8, True, False, False, 0.0),        # more queries than keys: early rows see nothing
+    (2, 8, 256, 256, 64, True, False, False, 0.0),     # per-head shape of config 2
+]
+
+
+@pytest.mark.parametrize("case", FP32_CASES)
+def test_fp32_forward_backward(ctx, case):
+    B, H, Sq, Sk, D, causal, use_mask, use_len, clamp = case
+    q, k, v, do = make_case(B, H, Sq, Sk, D, 100)
+    m = keep_mask(B, Sq, Sk, 5) if use_mask else None
+    L = np.random.default_rng(6).integers(0, Sk + 1, size=B).astype(np.int32) if use_len else None
+    sc = 1.0 / math.sqrt(D)
+    o_ref, lse_ref = oracle.attn_fwd(q, k, v, sc, causal, m, L, clamp)
+    dm = dev(m) if m is not None else None
+    dL = torch.from_numpy(L).cuda() if L is not None else None
+    tq, tk, tv, tdo = dev(q), dev(k), dev(v), dev(do)
+    o, lse = ctx.attn_fwd(tq, tk, tv, scale=sc, causal=causal, keep_mask=dm, kv_len=dL,
+                          score_clamp=clamp, mode=_lib.MODE_FP32)
+    assert max_abs(o.cpu().numpy(), o_ref) < FP32_TOL
+    lse_h = lse.cpu().numpy().astype(np.float64)
+    fin = np.isfinite(lse_ref)
+    assert (np.isfinite(lse_h) == fin).all()
+    assert max_abs(lse_h[fin], lse_ref[fin]) < 1e-5
+    dq_ref, dk_ref, dv_ref = oracle.attn_bwd(q, k, v, do, sc, causal, m, L, clamp)
+    dq, dk, dv = ctx.attn_bwd(tq, tk, tv, o, lse, tdo, scale=sc, causal=causal, keep_mask=dm,
+                              kv_len=dL, score_clamp=clamp, mode=_lib.MODE_FP32)
+    for got, ref in ((dq, dq_ref), (dk, dk_ref), (dv, dv_ref)):
+        assert max_abs(got.cpu().numpy(), ref) < FP32_TOL * max(1.0, float(np.abs(ref).max()))
+
+
+def test_fp32_strided_projection_layout(ctx):
+    """q, k, v addressed in place inside a [B*S, 3*H*D] projection buffer (no reshape copies)."""
+    B, H, S, D = 2, 4, 40, 32
+    x = randn((B, S, 3, H, D), 7)
+    tx = dev(x)
+    views = [tx[:, :, i].permute(0, 2, 1, 3) for i in range(3)]
+    o, _ = ctx.attn_fwd(*views, causal=True, mode=_lib.MODE_FP32)
+    o_ref, _ = oracle.attn_fwd(*(x[:, :, i].transpose(0, 2, 1, 3) for i in range(3)), 1 / math.sqrt(D), True)
+    assert max_abs(o.cpu().numpy(), o_ref) < FP32_TOL
+
+
+def test_fp32_backward_is_repeatable(ctx):
+    """The reference pins backward repeatability at 1e-6 (time_self_attention_test.cu:799-838);
+    the fp32 backward has no atomics, so two runs agree bit for bit."""
+    q, k, v, do = (dev(a) for a in make_case(2, 2, 100, 100, 32, 300))
+    o, lse = ctx.attn_fwd(q, k, v, causal=True, mode=_lib.MODE_FP32)
+    a = ctx.attn_bwd(q, k, v, o, lse, do, causal=True, mode=_lib.MODE_FP32)
+    b = ctx.attn_bwd(q, k, v, o, lse, do, causal=True, mode=_lib.MODE_FP32)
+    for x, y in zip(a, b):
+        assert torch.equal(x, y)
+
+
+TC_CASES = [
+    # B, H, Sq, Sk, D, causal, kvlen, mask, clamp
+    (1, 1, 128, 128, 64, False, False, False, 0.0),
+    (1, 2, 256, 256, 64, True, False, False, 0.0),
+    (2, 2, 384, 384, 64, True, False, False, 0.0),
+    (2, 3, 257, 257, 64, True, False, False, 0.0),
+    (1, 2, 1000, 1000, 64, False, True, False, 0.0),
+    (2, 2, 130, 515, 64, True, True, False, 0.0),
+    (1, 2, 200, 200, 64, True, False, True, 5.0),
+    (32, 8, 256, 256, 64, True, False, False, 0.0),     # config 2 core
+    (1, 2, 512, 512, 128, True, False, False, 0.0),
+    (1, 1, 300, 300, 128, False, True, False, 0.0),
+]
+
+
+@pytest.mark.parametrize("storage", ["bf16", "f32"])
+@pytest.mark.parametrize("case", TC_CASES)
+def test_tensor_pipe_forward(ctx, case, storage):
+    B, H, Sq, Sk, D, causal, use_len, use_mask, clamp = case
+    q, k, v, _ = make_case(B, H, Sq, Sk, D, 200, 0.5 if storage == "bf16" else 1.0)
+    qr, kr, vr = bf16_round(q), bf16_round(k), bf16_round(v)
+    L = np.random.default_rng(8).integers(1, Sk + 1, size=B).astype(np.int32) if use_len else None
+    m = keep_mask(B, Sq, Sk, 9, 0.8, dead_rows=((0, 3),)) if use_mask else None
+    sc = 1.0 / math.sqrt(D)
+    o_ref, lse_ref = oracle.attn_fwd(qr, kr, vr, sc, causal, m, L, clamp)
+    dt = torch.bfloat16 if storage == "bf16" else torch.float32
+    tq, tk, tv = dev(q, dt), dev(k, dt), dev(v, dt)
+    dL = torch.from_numpy(L).cuda() if L is not None else None
+    dm = dev(m) if m is not None else None
+    assert ctx.uses_tensor_pipe(tq, tk, tv, causal=causal, mode=_lib.MODE_BF16)
+    o, lse = ctx.attn_fwd(tq, tk, tv, scale=sc, causal=causal, kv_len=dL, keep_mask=dm,
+                          score_clamp=clamp, mode=_lib.MODE_BF16)
+    torch.cuda.synchronize()
+    assert ctx.device_status() == 0
+    got = o.float().cpu().numpy()
+    err = np.abs(got.astype(np.float64) - o_ref)
+    if storage == "bf16":
+        allowed = TC_MAX_ABS + np.abs(o_ref) * 2.0 ** -8     # + half-ulp of the bf16 output
+        assert (err <= allowed).all(), f"max excess {(err - allowed).max()}"
+        assert rel_l2(got, o_ref) < TC_REL_L2 + 2.0 ** -9
+    else:
+        assert err.max() < TC_MAX_ABS
+        assert rel_l2(got, o_ref) < TC_REL_L2
+    lse_h = lse.cpu().numpy().astype(np.float64)
+    fin = np.isfinite(lse_ref)
+    assert (np.isfinite(lse_h) == fin).all()
+    assert max_abs(lse_h[fin], lse_ref[fin]) < 2e-3
+
+
+def test_tensor_pipe_full_size_properties(ctx):
+    """Config 3 (B=8 H=16 S=4096 D=64 causal bf16) at full size: size-independent properties
+    (V = const gives O = const; row 0 returns v_0; lse of row 0 is its single score) plus an
+    oracle check of a subset of (batch, head) pairs."""
+    B, H, S, D = 8, 16, 4096, 64
+    g = torch.Generator(device="cuda").manual_seed(3)
+    q = (torch.randn((B, H, S, D), generator=g, device="cuda") * 0.5).bfloat16()
+    k = (torch.randn((B, H, S, D), generator=g, device="cuda") * 0.5).bfloat16()
+    v = (torch.randn((B, H, S, D), generator=g, device="cuda") * 0.5).bfloat16()
+    o, lse = ctx.attn_fwd(q, k, v, causal=True, mode=_lib.MODE_BF16)
+    torch.cuda.synchronize()
+    assert ctx.device_status() == 0
+    assert torch.equal(o[:, :, 0], v[:, :, 0])
+    s00 = (q[:, :, 0].float() * k[:, :, 0].float()).sum(-1) / 8.0
+    assert (lse[:, :, 0] - s00).abs().max().item() < 1e-3
+    ones = torch.ones_like(v)
+    o1, _ = ctx.attn_fwd(q, k, ones, causal=True, mode=_lib.MODE_BF16)
+    assert (o1.float() - 1.0).abs().max().item() <= 2.0 ** -7
+    for (b, h) in ((0, 0), (3, 7), (7, 15)):
+        qs, ks, vs = (t[b:b + 1, h:h + 1].float().cpu().numpy() for t in (q, k, v))
+        o_ref, lse_ref = oracle.attn_fwd(qs, ks, vs, 0.125, True)
+        got = o[b, h].float().cpu().numpy()[None, None]
+        err = np.abs(got - o_ref)
+        assert (err <= TC_MAX_ABS + np.abs(o_ref) * 2.0 ** -8).all()
+        assert max_abs(lse[b, h].cpu().numpy()[None, None], lse_ref) < 2e-3
+
+
+DECODE_CASES = [
+    # B, H, Smax, D, dtype, mask
+    (256, 8, 1024, 64, torch.float32, False),     # config 4
+    (3, 2, 77, 16, torch.float32, True),
+    (2, 4, 300, 32, torch.float32, False),
+    (2, 2, 2048, 128, torch.float32, False),      # few (batch, head) pairs: split over keys
+    (4, 8, 512, 64, torch.bfloat16, False),
+]
+
+
+@pytest.mark.parametrize("case", DECODE_CASES)
+def test_decode(ctx, case):
+    B, H, Smax, D, dt, use_mask = case
+    q, k, v, _ = make_case(B, H, 1, Smax, D, 400)
+    if dt == torch.bfloat16:
+        q, k, v = bf16_round(q), bf16_round(k), bf16_round(v)
+    L = np.random.default_rng(10).integers(1, Smax + 1, size=B).astype(np.int32)
+    L[0] = Smax
+    if B > 2:
+        L[1] = 1
+    m = keep_mask(B, 1, Smax, 11, 0.6, dead_rows=()) if use_mask else None
+    sc = 1.0 / math.sqrt(D)
+    o_ref, lse_ref = oracle.attn_fwd(q, k, v, sc, False, m, L)
+    o, lse = ctx.attn_decode(dev(q, dt), dev(k, dt), dev(v, dt), kv_len=torch.from_numpy(L).cuda(),
+                             scale=sc, keep_mask=dev(m) if m is not None else None)
+    tol = FP32_TOL if dt == torch.float32 else 2.0 ** -8
+    assert max_abs(o.float().cpu().numpy(), o_ref) < tol * max(1.0, float(np.abs(o_ref).max()))
+    assert max_abs(lse.cpu().numpy(), lse_ref) < 1e-5 * max(1.0, float(np.abs(lse_ref).max()))
+
+
+def test_decode_zero_length(ctx):
+    B, H, Smax, D = 2, 2, 64, 64
+    q, k, v, _ = (dev(a) for a in make_case(B, H, 1, Smax, D, 500))
+    L = torch.tensor([0, 5], dtype=torch.int32, device="cuda")
+    o, lse = ctx.attn_decode(q, k, v, kv_len=L)
+    assert (o[0] == 0).all() and torch.isneginf(lse[0]).all() and torch.isfinite(lse[1]).all()
+
+
+def test_argument_errors(ctx):
+    from cuda_ltc_b200 import LtcaError
+    q = torch.zeros((1, 1, 4, 24), device="cuda")
+    with pytest.raises(LtcaError) as e:
+        ctx.attn_fwd(q, q, q, mode=_lib.MODE_BF16)       # head_dim 24 is outside the tensor path
+    assert e.value.code == -2
+    with pytest.raises(LtcaError) as e:
+        ctx.attn_fwd(q, q, q, scale=-1.0)
+    assert e.value.code == -1
+    big = torch.zeros((1, 1, 4, 256), device="cuda")
+    with pytest.raises(LtcaError):
+        ctx.attn_fwd(big, big, big, mode=_lib.MODE_FP32)
