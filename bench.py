@@ -1,0 +1,312 @@
+#!/usr/bin/env python
+"""Benchmark of the attention hot path (forward + backward of the attention core).
+
+Workload (BASELINE.json configs[2], the configuration the headline target is quoted on):
+B=8 H=16 S=4096 D=64, causal, bf16 storage with fp32 accumulation, Q/K/V/dO = 0.5*N(0,1) from a
+seed.  A step is one forward and one backward over the whole batch.  With N GPUs every rank
+processes its own B=8 slice of a global batch of 8*N sequences (batch x head partition, no
+collective on the data path), so scaling is weak.
+
+    python bench.py --gpus 1 --steps 20 --warmup 3
+    python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N ...
+    python bench.py --impl reference          # CPU arm: the fp64 oracle port on the host cores
+
+Prints ONE JSON line (rank 0).  FLOP accounting: forward = 4*B*H*S*S*D/2 (causal half),
+backward = 2.5x forward; recomputation and softmax are not counted.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+CFG = dict(B=8, H=16, S=4096, D=64, causal=True)
+SEED = 20241
+
+
+def flops_fwd(B, H, S, D, causal=True):
+    return 4.0 * B * H * S * S * D * (0.5 if causal else 1.0)
+
+
+def measured_peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return json.load(f), "measured"
+    except Exception:
+        return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU through NVML while the timed region runs."""
+
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self._nv = None
+
+    def _run(self):
+        nv = self._nv
+        names = {
+            "hw_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwSlowdown", 0x8),
+            "hw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40),
+            "sw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20),
+            "sw_power_cap": getattr(nv, "nvmlClocksThrottleReasonSwPowerCap", 0x4),
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM))
+                r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._h)
+                for n, bit in names.items():
+                    if r & bit:
+                        self.reasons.add(n)
+            except Exception:
+                pass
+            self._stop.wait(0.02)
+
+    def start(self):
+        if self._nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+
+    def stop(self):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons)}
+
+
+def physical_gpu_index(local_rank: int) -> int:
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        try:
+            return int(vis.split(",")[local_rank])
+        except Exception:
+            return local_rank
+    return local_rank
+
+
+def run_cpu_sample(n_bh: int, threads: int | None = None):
+    """fp64 oracle forward + backward on `n_bh` (batch, head) pairs of the workload."""
+    import numpy as np
+    import oracle
+    if threads:
+        oracle.set_num_threads(threads)
+    S, D = CFG["S"], CFG["D"]
+    rng = np.random.default_rng(SEED)
+    q, k, v, do = ((rng.standard_normal((1, n_bh, S, D)) * 0.5).astype(np.float32) for _ in range(4))
+    t0 = time.perf_counter()
+    oracle.attn_fwd(q, k, v, 1.0 / math.sqrt(D), True)
+    oracle.attn_bwd(q, k, v, do, 1.0 / math.sqrt(D), True)
+    dt = time.perf_counter() - t0
+    fl = 3.5 * flops_fwd(1, n_bh, S, D)
+    return fl / dt / 1e12, dt, oracle.num_threads()
+
+
+def reference_arm(args):
+    """CPU arm: the reference has no CPU implementation of this path (all of it is CUDA and its
+    own kernels cannot run this configuration), so the timed code is the repository's fp64
+    OpenMP port of the same arithmetic, on all host threads, on a bounded sample per step."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cores = os.cpu_count() or 1
+    n_bh = max(8, min(cores, 64))
+    for _ in range(args.warmup if args.warmup < 2 else 1):
+        run_cpu_sample(max(2, n_bh // 4))
+    t_total, fl_total = 0.0, 0.0
+    threads = 1
+    for _ in range(args.steps):
+        tf, dt, threads = run_cpu_sample(n_bh)
+        t_total += dt
+        fl_total += tf * dt
+    value = fl_total / t_total
+    sample = f"{n_bh} of {CFG['B'] * CFG['H']} (batch, head) pairs per step, forward + backward, fp64"
+    line = {
+        "impl": "reference", "metric": "attention fwd+bwd TFLOP/s", "value": value, "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": 1000.0 * t_total / max(1, args.steps), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f64", "data": "synthetic",
+        "config": workload_config(args.gpus),
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(n_gpus):
+    return {"workload": "attention core fwd+bwd, B=8 H=16 S=4096 D=64 causal, bf16 storage / fp32 accumulate "
+                        "(BASELINE configs[2]); per GPU",
+            "global_batch": CFG["B"] * n_gpus, "heads": CFG["H"], "seq_len": CFG["S"], "head_dim": CFG["D"],
+            "parallelism": f"batch x head partition over {n_gpus} GPU(s), no collective",
+            "l2": "inputs (256 MB per step) exceed the 126 MB L2; no explicit flush"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        reference_arm(args)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    import cuda_ltc_b200 as ltc
+    from cuda_ltc_b200 import _lib
+
+    W = max(3, args.warmup)
+    K = args.steps
+    B, H, S, D = CFG["B"], CFG["H"], CFG["S"], CFG["D"]
+    dev = torch.device("cuda", local_rank)
+    g = torch.Generator(device=dev).manual_seed(SEED + rank)
+    mk = lambda: (torch.randn((B, H, S, D), generator=g, device=dev) * 0.5).bfloat16()
+    q, k, v, do = mk(), mk(), mk(), mk()
+    o = torch.empty_like(q)
+    lse = torch.empty((B, H, S), dtype=torch.float32, device=dev)
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+
+    stream = torch.cuda.Stream(device=dev)
+    ctx = ltc.Context(local_rank, stream)
+    bwd_tensor = ctx.uses_tensor_pipe(q, k, v, causal=True, backward=True)
+    kernels_per_step = 1 + (3 if not bwd_tensor else int(os.environ.get("LTCA_BWD_LAUNCHES", "3")))
+
+    def step():
+        ctx.attn_fwd(q, k, v, causal=True, mode=_lib.MODE_BF16, out=o, lse=lse)
+        ctx.attn_bwd(q, k, v, o, lse, do, causal=True, mode=_lib.MODE_AUTO, dq=dq, dk=dk, dv=dv)
+
+    def barrier():
+        torch.cuda.synchronize(dev)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    with torch.cuda.stream(stream):
+        for _ in range(W):
+            step()
+    barrier()
+
+    sampler = ClockSampler(physical_gpu_index(local_rank))
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(K)]
+    sampler.start()
+    with torch.cuda.stream(stream):
+        for i in range(K):
+            ev[i][0].record(stream)
+            ctx.attn_fwd(q, k, v, causal=True, mode=_lib.MODE_BF16, out=o, lse=lse)
+            ev[i][1].record(stream)
+            ctx.attn_bwd(q, k, v, o, lse, do, causal=True, mode=_lib.MODE_AUTO, dq=dq, dk=dk, dv=dv)
+            ev[i][2].record(stream)
+    barrier()
+    clocks = sampler.stop()
+    total_ms = ev[0][0].elapsed_time(ev[-1][2])
+    fwd_ms = sum(e[0].elapsed_time(e[1]) for e in ev) / K
+    bwd_ms = sum(e[1].elapsed_time(e[2]) for e in ev) / K
+    status = ctx.device_status()
+
+    # ---- end to end: host buffers in, results back, through the same public call ---------------
+    e2e = None
+    if not args.no_e2e:
+        hq, hk, hv, hdo = (t.cpu().pin_memory() for t in (q, k, v, do))
+        ho, hdq, hdk, hdv = (torch.empty_like(t).pin_memory() for t in (hq, hq, hk, hv))
+        Ke = max(2, min(K, 5))
+
+        def e2e_step():
+            q.copy_(hq, non_blocking=True); k.copy_(hk, non_blocking=True)
+            v.copy_(hv, non_blocking=True); do.copy_(hdo, non_blocking=True)
+            step()
+            ho.copy_(o, non_blocking=True); hdq.copy_(dq, non_blocking=True)
+            hdk.copy_(dk, non_blocking=True); hdv.copy_(dv, non_blocking=True)
+
+        with torch.cuda.stream(stream):
+            e2e_step()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(stream):
+            e0.record(stream)
+            for _ in range(Ke):
+                e2e_step()
+            e1.record(stream)
+        barrier()
+        e2e_ms = e0.elapsed_time(e1) / Ke
+        nbytes = q.numel() * 2
+        e2e = (e2e_ms, 4 * nbytes, 4 * nbytes)
+
+    # ---- max over ranks --------------------------------------------------------------------------
+    vals = torch.tensor([total_ms, fwd_ms, bwd_ms, e2e[0] if e2e else 0.0, float(status)],
+                        dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(vals, op=dist.ReduceOp.MAX)
+    total_ms, fwd_ms, bwd_ms, e2e_ms, status = vals.tolist()
+
+    if rank == 0:
+        f_fwd = flops_fwd(B, H, S, D)
+        f_step = 3.5 * f_fwd
+        ms_per_step = total_ms / K
+        value = world * f_step / (ms_per_step * 1e-3) / 1e12
+        peaks, peak_kind = measured_peaks()
+        peak = peaks.get("bf16_tflops_sustained") or peaks.get("bf16_tflops")
+        dom_bwd = bwd_ms >= fwd_ms
+        dom_ms = bwd_ms if dom_bwd else fwd_ms
+        dom_fl = 2.5 * f_fwd if dom_bwd else f_fwd
+        achieved = dom_fl / (dom_ms * 1e-3) / 1e12
+        line = {
+            "metric": "attention fwd+bwd TFLOP/s", "value": value, "unit": "TFLOP/s",
+            "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms_per_step,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic", "config": workload_config(world),
+            "fwd": {"ms": fwd_ms, "tflops_per_gpu": f_fwd / (fwd_ms * 1e-3) / 1e12},
+            "bwd": {"ms": bwd_ms, "tflops_per_gpu": 2.5 * f_fwd / (bwd_ms * 1e-3) / 1e12,
+                    "tensor_pipe": bool(bwd_tensor)},
+            "roofline": {"bound": "tensor", "kernel": "attention backward" if dom_bwd else "attention forward",
+                         "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                         "peak_source": f"{peak_kind} bf16_tflops_sustained", "traffic": None},
+            "gpu_launches": kernels_per_step * K,
+            "clocks": clocks, "device_status": int(status),
+        }
+        if e2e:
+            line["e2e"] = {"value": world * f_step / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+                           "ms_per_step": e2e_ms, "h2d_bytes_per_step": e2e[1], "d2h_bytes_per_step": e2e[2]}
+        if world == 1 and not args.no_cpu_baseline:
+            cores = os.cpu_count() or 1
+            n_bh = max(8, min(cores, 64))
+            tf, dt, threads = run_cpu_sample(n_bh)
+            line["cpu_baseline"] = {"value": tf, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+                                    "sample": f"{n_bh} of {B * H} (batch, head) pairs, forward + backward, "
+                                              f"fp64, {dt:.1f} s"}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -22,7 +22,8 @@
 //     softmax overlaps the other tile's contractions.
 //
 // Tensor-memory map (512 columns): S0 [0,128) S1 [128,256) O0 [256,256+D) O1 [256+D,256+2D);
-// P_t occupies the upper 64 columns of S_t (128 bf16 packed two per column).
+// P_t occupies the upper 64 columns of S_t (128 bf16 packed two per column); in the split-P
+// variant its low-order term occupies the lower 64 columns.
 #include "host_common.h"
 #include "sm100_ptx.cuh"
 
@@ -69,7 +70,10 @@ struct FwdSmem {
 
 __device__ __forceinline__ float neg_inf() { return __int_as_float(0xff800000); }
 
-template <int D, typename OutT>
+// kSplitP: P is written as two bf16 terms (p = hi + lo, 16 mantissa bits in total) and the
+// second contraction runs once per term; used when the output is stored as fp32, where the
+// 2^-9 rounding of a single bf16 P would be the largest error left.
+template <int D, typename OutT, bool kSplitP>
 __global__ void __launch_bounds__(kFwdThreads, 1)
 attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
                       const __grid_constant__ CUtensorMap tmap_k,
@@ -186,6 +190,12 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
                     mma_ts(tmem_base + 2 * kBlockN + t * D, tmem_base + t * kBlockN + 64 + k * 8,
                            make_smem_desc_sw128(va + k * 2048, kBlockN * 128, 1024), idesc_pv,
                            (acc || k > 0) ? 1u : 0u);
+                }
+                if constexpr (kSplitP) {
+#pragma unroll
+                    for (int k = 0; k < kBlockN / 16; ++k)
+                        mma_ts(tmem_base + 2 * kBlockN + t * D, tmem_base + t * kBlockN + k * 8,
+                               make_smem_desc_sw128(va + k * 2048, kBlockN * 128, 1024), idesc_pv, 1u);
                 }
             };
             auto slot_of = [&](int item) { return item % L::kStages; };
@@ -319,20 +329,31 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
             const float m_safe = (m_run == neg_inf()) ? 0.f : m_run;
             const float mneg = -m_safe * c2;
             float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
-            uint32_t pk[kBlockN / 2];
 #pragma unroll
-            for (int c = 0; c < kBlockN; c += 4) {
-                const float p0 = fast_exp2(fmaf(S_(c), c2, mneg));
-                const float p1 = fast_exp2(fmaf(S_(c + 1), c2, mneg));
-                const float p2 = fast_exp2(fmaf(S_(c + 2), c2, mneg));
-                const float p3 = fast_exp2(fmaf(S_(c + 3), c2, mneg));
-                sum0 += p0; sum1 += p1; sum2 += p2; sum3 += p3;
-                pk[c / 2] = pack_bf16x2(p0, p1);
-                pk[c / 2 + 1] = pack_bf16x2(p2, p3);
+            for (int half = 0; half < 2; ++half) {
+                uint32_t hi[32], lo[32];
+#pragma unroll
+                for (int cc = 0; cc < 64; cc += 4) {
+                    const int c = half * 64 + cc;
+                    const float p0 = fast_exp2(fmaf(S_(c), c2, mneg));
+                    const float p1 = fast_exp2(fmaf(S_(c + 1), c2, mneg));
+                    const float p2 = fast_exp2(fmaf(S_(c + 2), c2, mneg));
+                    const float p3 = fast_exp2(fmaf(S_(c + 3), c2, mneg));
+                    sum0 += p0; sum1 += p1; sum2 += p2; sum3 += p3;
+                    const uint32_t h01 = pack_bf16x2(p0, p1), h23 = pack_bf16x2(p2, p3);
+                    hi[cc / 2] = h01;
+                    hi[cc / 2 + 1] = h23;
+                    if constexpr (kSplitP) {
+                        lo[cc / 2] = pack_bf16x2(p0 - __uint_as_float(h01 << 16),
+                                                 p1 - __uint_as_float(h01 & 0xffff0000u));
+                        lo[cc / 2 + 1] = pack_bf16x2(p2 - __uint_as_float(h23 << 16),
+                                                     p3 - __uint_as_float(h23 & 0xffff0000u));
+                    }
+                }
+                tmem_st32(tP + half * 32, hi);
+                if constexpr (kSplitP) tmem_st32(tS + half * 32, lo);
             }
             l_run += (sum0 + sum1) + (sum2 + sum3);
-            tmem_st32(tP + 0, reinterpret_cast<uint32_t(&)[32]>(pk[0]));
-            tmem_st32(tP + 32, reinterpret_cast<uint32_t(&)[32]>(pk[32]));
             tmem_wait_st();
             tc_fence_before_sync();
             mbar_arrive(bar_p_full(t));
@@ -427,7 +448,7 @@ int launch_fwd(ltca_ctx* ctx, const ltca_attn_params* p, const void* q, const vo
     a.kv_len = p->kv_len;
     a.status = ctx->d_status;
 
-    auto kern = attn_fwd_sm100_kernel<D, OutT>;
+    auto kern = attn_fwd_sm100_kernel<D, OutT, sizeof(OutT) == 4>;
     static bool attr_done = false;
     if (!attr_done) {
         LTCA_CUDA_OK(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
