@@ -75,6 +75,7 @@ EXPORTS = {
     "ltca_attn_bwd": (C.c_int, [C.c_void_p, C.POINTER(AttnParams)]),
     "ltca_attn_decode": (C.c_int, [C.c_void_p, C.POINTER(AttnParams)]),
     "ltca_attn_decode_workspace_bytes": (C.c_int, [C.POINTER(AttnParams), C.POINTER(C.c_size_t)]),
+    "ltca_attn_decode_static": (C.c_int, [C.c_void_p, C.POINTER(AttnParams), C.c_char_p, C.c_size_t]),
     "ltca_tsa_bwd": (C.c_int, [C.c_void_p, C.POINTER(TsaParams)]),
     "ltca_tsa_workspace_bytes": (C.c_int, [C.POINTER(TsaParams), C.c_int, C.POINTER(C.c_size_t)]),
     "ltca_tsa_fwd": (C.c_int, [C.c_void_p, C.POINTER(TsaParams)]),

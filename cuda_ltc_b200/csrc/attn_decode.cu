@@ -246,3 +246,73 @@ int launch_attn_decode(ltca_ctx* ctx, const ltca_attn_params* p) {
 }
 
 }  // namespace ltca
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free variant of the decode step.
+//
+// The regular entry point needs a context (whose creation makes one small device allocation)
+// and, when the key range is split, a scratch buffer that the caller has to allocate.  Code
+// that runs where device allocation is off limits -- a plug-in called from inside another
+// framework's memory pool or arena, a real-time loop that forbids driver allocations after
+// start-up, a host that hands out all device memory up front -- cannot provide either.  For
+// those callers the split's partial results live in a fixed array that is part of the loaded
+// library image, so the call touches no allocator at all.
+// ---------------------------------------------------------------------------------------------
+namespace {
+
+constexpr size_t kStaticScratchBytes = 256u << 10;   // 256 KiB, resident on every GPU that loads the library
+static __device__ __align__(256) unsigned char g_decode_static_scratch[kStaticScratchBytes];
+
+constexpr int kMaxDevices = 64;
+void* g_static_scratch_ptr[kMaxDevices] = {nullptr};
+
+void set_err(char* buf, size_t len, const char* msg) {
+    if (buf && len) snprintf(buf, len, "%s", msg);
+}
+
+}  // namespace
+
+extern "C" int ltca_attn_decode_static(void* stream, const ltca_attn_params* p, char* err,
+                                       size_t err_len) {
+    if (!p) { set_err(err, err_len, "null parameter block"); return LTCA_ERR_INVALID; }
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+        set_err(err, err_len, "no current CUDA device (or device index above 63)");
+        return LTCA_ERR_NO_DEVICE;
+    }
+    // One-time set-up per device, with that device current: in host code the array's name is
+    // only a stand-in, the kernel needs the address the symbol has on THIS device.
+    if (!g_static_scratch_ptr[dev]) {
+        void* ptr = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&ptr, g_decode_static_scratch);
+        if (e != cudaSuccess || !ptr) {
+            set_err(err, err_len, cudaGetErrorString(e));
+            return LTCA_ERR_CUDA;
+        }
+        g_static_scratch_ptr[dev] = ptr;
+    }
+    const size_t need = ltca::attn_decode_workspace(p);
+    if (need > kStaticScratchBytes) {
+        char msg[200];
+        snprintf(msg, sizeof(msg),
+                 "this decode shape needs %zu bytes of split scratch, the built-in array holds %zu; "
+                 "use ltca_attn_decode with a caller-provided workspace", need, kStaticScratchBytes);
+        set_err(err, err_len, msg);
+        return LTCA_ERR_WORKSPACE;
+    }
+    if (p->B < 1 || p->H < 1 || p->Sk < 1 || p->D < 1 || !p->q || !p->k || !p->v || !p->o ||
+        !(p->scale > 0.f) || (p->dtype != LTCA_F32 && p->dtype != LTCA_BF16)) {
+        set_err(err, err_len, "bad decode arguments (shape, null pointer, scale or dtype)");
+        return LTCA_ERR_INVALID;
+    }
+    ltca_ctx tmp;                       // host-only bookkeeping: stream and error text
+    tmp.device = dev;
+    tmp.stream = reinterpret_cast<cudaStream_t>(stream);
+    tmp.sm_count = 148;
+    ltca_attn_params q = *p;
+    q.workspace = g_static_scratch_ptr[dev];
+    q.workspace_bytes = kStaticScratchBytes;
+    const int rc = ltca::launch_attn_decode(&tmp, &q);
+    if (rc) set_err(err, err_len, tmp.err);
+    return rc;
+}

@@ -136,6 +136,31 @@ int ltca_attn_decode(ltca_ctx* ctx, const ltca_attn_params* p);
  * room for the partial results of the key-range split. */
 int ltca_attn_decode_workspace_bytes(const ltca_attn_params* p, size_t* bytes_out);
 
+/*
+ * Decode step for callers that must not allocate.  (No counterpart in the reference.)
+ *
+ * Who needs it: code that runs where cudaMalloc is not an option -- a plug-in living inside
+ * another framework's memory arena, a latency-critical loop that bans driver allocations once
+ * it has started, a host process that has already handed out all device memory.  Such callers
+ * can neither create an ltca_ctx (its creation allocates a status word) nor supply the scratch
+ * buffer that the split over the key range wants.  This entry point takes no context, and the
+ * split's partial results go to a 256 KiB array built into the library image (every GPU that
+ * loads the library carries those 256 KiB until the process exits).  It calls no cudaMalloc,
+ * cudaFree or any allocating routine.
+ *
+ *  - Works on the calling thread's CURRENT device and enqueues on `stream` (cudaStream_t as void*).
+ *  - The first call on each device looks up the device address of the built-in array
+ *    (cudaGetSymbolAddress); make that first call before starting any stream capture.
+ *  - Shapes whose split scratch (ltca_attn_decode_workspace_bytes) exceeds 256 KiB are refused
+ *    with LTCA_ERR_WORKSPACE and a message in `err`; nothing is launched.
+ *  - All calls share the one array.  Each call overwrites every slot it later reads, so stale
+ *    contents of an earlier call are harmless and nothing has to be cleared, but two calls
+ *    that overlap on the GPU (different streams, no ordering between them) race on it.
+ *  - Arguments as for ltca_attn_decode (Sq = 1; workspace fields of `p` are ignored).
+ *    `err` (host buffer, may be NULL) receives the text of a failure.
+ */
+int ltca_attn_decode_static(void* stream, const ltca_attn_params* p, char* err, size_t err_len);
+
 /* ---- TimeSelfAttention module ----------------------------------------------------------- */
 
 /*
