@@ -151,11 +151,11 @@ def reference_arm(args):
 
 
 def workload_config(n_gpus):
-    return {"workload": "attention core fwd+bwd, B=8 H=16 S=4096 D=64 causal, bf16 storage / fp32 accumulate "
-                        "(BASELINE configs[2]); per GPU",
+    return {"workload": f"attention core fwd+bwd, B={CFG['B']} H=16 S=4096 D=64 causal, bf16 storage / fp32 "
+                        "accumulate (BASELINE configs[2]" + ("" if CFG["B"] == 8 else ", reduced batch") + "); per GPU",
             "global_batch": CFG["B"] * n_gpus, "heads": CFG["H"], "seq_len": CFG["S"], "head_dim": CFG["D"],
             "parallelism": f"batch x head partition over {n_gpus} GPU(s), no collective",
-            "l2": "inputs (256 MB per step) exceed the 126 MB L2; no explicit flush"}
+            "l2": f"inputs ({32 * CFG['B']} MB per step) exceed the 126 MB L2; no explicit flush"}
 
 
 def main():
@@ -166,7 +166,14 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--batch", type=int, default=CFG["B"],
+                    help="sequences per GPU; anything but the default is a reduced case for profiler captures")
+    ap.add_argument("--profile", action="store_true",
+                    help="profiler capture mode: 1 warm-up, 1 step, no end-to-end or CPU legs (not a bench value)")
     args = ap.parse_args()
+    if args.profile:
+        args.steps, args.warmup, args.no_e2e, args.no_cpu_baseline = 1, 1, True, True
+    CFG["B"] = args.batch
     if args.impl == "reference":
         reference_arm(args)
         return
@@ -185,7 +192,7 @@ def main():
     import cuda_ltc_b200 as ltc
     from cuda_ltc_b200 import _lib
 
-    W = max(3, args.warmup)
+    W = args.warmup if args.profile else max(3, args.warmup)
     K = args.steps
     B, H, S, D = CFG["B"], CFG["H"], CFG["S"], CFG["D"]
     dev = torch.device("cuda", local_rank)

@@ -1,13 +1,863 @@
-// Attention backward on the sm_100a tensor pipe (placeholder translation unit while the kernel
-// is brought up: every problem is routed to the fp32 backward).
+// Attention backward on the sm_100a tensor pipe (head_dim 64, bf16 operands, fp32 accumulation).
+//
+// With P = softmax(scale * Q K^T) recomputed from Q, K and the forward's log-sum-exp:
+//   delta_i = sum_d dO[i,d] O[i,d]        dP = dO V^T        dS = P o (dP - delta)
+//   dV = P^T dO        dK = scale * dS^T Q        dQ = scale * dS K
+// The reference reaches this arithmetic through cudnnMultiHeadAttnBackwardData
+// (reference src/ml/cuDNN_ops.cu:240-337); its FlashAttention class has no backward.
+//
+// Three launches, no atomics (two runs give identical bits; the reference's tests pin backward
+// repeatability, src/ml/time_self_attention_test.cu:799-838):
+//   1. attn_bwd_stats_kernel: delta and lse * log2(e) into padded [B*H, Sq_pad] fp32 rows
+//      (padding and fully hidden rows get lse = +inf so that their P is exactly 0).
+//   2. attn_bwd_dq_sm100_kernel: one CTA per 256 query rows; Q and dO tiles stay in shared
+//      memory, K/V stream through a ring in 64-key steps.  Per step and 128-row tile:
+//      S = Q K^T and dP = dO V^T into tensor memory, the elementwise warps (one query row per
+//      thread) turn them into dS (bf16, written back over S), and dQ += dS K takes dS from
+//      tensor memory and K as an MN-major operand from shared memory.
+//   3. attn_bwd_dkv_sm100_kernel: the transposed problem, one CTA per 256 keys; K and V tiles
+//      stay in shared memory, Q/dO (and the per-row statistics) stream in 64-query steps.
+//      S^T = K Q^T and dP^T = V dO^T put one KEY per tensor-memory lane, so P^T and dS^T are
+//      directly the A operands of dV += P^T dO and dK += dS^T Q.
+// Both main kernels share the forward's structure: warps 0-3 / 4-7 elementwise for tile 0 / 1,
+// warp 8 issues tcgen05.mma, warp 9 drives TMA; the two tiles are interleaved so one tile's
+// elementwise work overlaps the other's contractions.  Every wait is bounded.
 #include "host_common.h"
+#include "sm100_ptx.cuh"
 
 namespace ltca {
 
-bool attn_bwd_sm100_supported(const ltca_attn_params*) { return false; }
-size_t attn_bwd_sm100_workspace(const ltca_attn_params*) { return 0; }
-int launch_attn_bwd_sm100(ltca_ctx* ctx, const ltca_attn_params*) {
-    return fail(ctx, LTCA_ERR_UNSUPPORTED, "tensor-pipe backward not available");
+namespace {
+
+constexpr int kTile = 128;          // rows of a resident tile (queries in dQ, keys in dKV)
+constexpr int kStep = 64;           // streamed rows per step
+constexpr int kD = 64;
+constexpr int kThreads = 384;
+constexpr int kMmaWarp = 8;
+constexpr int kTmaWarp = 9;
+constexpr uint32_t kTmemCols = 512;
+constexpr int kBigTile = kTile * kD * 2;      // 16 KB
+constexpr int kSmallTile = kStep * kD * 2;    // 8 KB
+
+struct BwdArgs {
+    int B, H, Sq, Sk, Sq_pad;
+    int causal, causal_off;
+    float scale, scale_log2;
+    float clamp_raw, clamp_log2;     // clamp / scale ; clamp * log2(e)
+    int use_clamp;
+    const float* lse2;               // [B*H, Sq_pad]
+    const float* delta;              // [B*H, Sq_pad]
+    void *dq, *dk, *dv;
+    ltca_strides dqs, dks, dvs;
+    const float* keep_mask;
+    const int32_t* kv_len;
+    uint32_t* status;
+};
+
+__device__ __forceinline__ float neg_inf() { return __int_as_float(0xff800000); }
+__device__ __forceinline__ float pos_inf() { return __int_as_float(0x7f800000); }
+
+// ---------------------------------------------------------------------------------------------
+// 1. statistics: 8 lanes per query row, 8 elements per lane (head_dim 64)
+// ---------------------------------------------------------------------------------------------
+struct StatsArgs {
+    int B, H, Sq, Sq_pad;
+    const void *o, *dout;
+    ltca_strides os, dos;
+    const float* lse;
+    float *lse2, *delta;
+};
+
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&f)[8]) {
+    const uint4 u = __ldg(reinterpret_cast<const uint4*>(p));
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        f[2 * i] = __uint_as_float(w[i] << 16);
+        f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+}
+__device__ __forceinline__ void load8(const float* p, float (&f)[8]) {
+    const float4 a = __ldg(reinterpret_cast<const float4*>(p));
+    const float4 b = __ldg(reinterpret_cast<const float4*>(p) + 1);
+    f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w;
+    f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) attn_bwd_stats_kernel(const StatsArgs a) {
+    const int64_t row = (int64_t)blockIdx.x * 32 + (threadIdx.x >> 3);
+    const int sub = threadIdx.x & 7;
+    const int64_t total = (int64_t)a.B * a.H * a.Sq_pad;
+    if (row >= total) return;                    // whole 8-lane groups leave together
+    const int qi = (int)(row % a.Sq_pad);
+    const int64_t bh = row / a.Sq_pad;
+    const int h = (int)(bh % a.H), b = (int)(bh / a.H);
+    float acc = 0.f;
+    if (qi < a.Sq) {
+        const T* o = reinterpret_cast<const T*>(a.o) + b * a.os.batch + h * a.os.head + (int64_t)qi * a.os.seq + 8 * sub;
+        const T* g = reinterpret_cast<const T*>(a.dout) + b * a.dos.batch + h * a.dos.head + (int64_t)qi * a.dos.seq + 8 * sub;
+        float fo[8], fg[8];
+        load8(o, fo);
+        load8(g, fg);
+        // fp32 storage: the contractions see dO rounded to bf16, and sum_j P_ij dP_ij equals
+        // delta_i only when delta is formed from the same rounded dO
+        if constexpr (sizeof(T) == 4) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) fg[i] = __bfloat162float(__float2bfloat16_rn(fg[i]));
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc = fmaf(fo[i], fg[i], acc);
+    }
+    acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+    acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+    acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+    if (sub == 0) {
+        float l2 = pos_inf();
+        if (qi < a.Sq) {
+            const float l = a.lse[bh * a.Sq + qi];
+            l2 = (l == neg_inf()) ? pos_inf() : l * 1.4426950408889634f;
+        }
+        a.lse2[row] = l2;
+        a.delta[row] = acc;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// shared-memory plans
+// ---------------------------------------------------------------------------------------------
+struct DqSmem {
+    static constexpr int kStages = 8;                         // ring of 8 KB K / V step tiles
+    static constexpr int kQOff = 0;                           // Q0, Q1
+    static constexpr int kDoOff = 2 * kBigTile;               // dO0, dO1
+    static constexpr int kRingOff = 4 * kBigTile;
+    static constexpr int kBarOff = kRingOff + kStages * kSmallTile;
+    // bars: qdo_full, ring_full[S], ring_empty[S], sdp_full[2], ds_full[2], dq_done[2]
+    static constexpr int kNumBars = 1 + 2 * kStages + 6;
+    static constexpr int kMiscOff = kBarOff + kNumBars * 8;
+    static constexpr int kDynBytes = kMiscOff + 16 + 1024;
+};
+
+struct DkvSmem {
+    static constexpr int kStages = 6;                         // ring of (Q_j, dO_j, lse2_j, delta_j)
+    static constexpr int kStageBytes = 2 * kSmallTile + 1024; // stats padded to keep 1024-B alignment
+    static constexpr int kKOff = 0;                           // K0, K1
+    static constexpr int kVOff = 2 * kBigTile;                // V0, V1
+    static constexpr int kRingOff = 4 * kBigTile;
+    static constexpr int kBarOff = kRingOff + kStages * kStageBytes;
+    // bars: kv_full, ring_full[S], ring_empty[S], sdp_full[2], pds_full[2], acc_done[2]
+    static constexpr int kNumBars = 1 + 2 * kStages + 6;
+    static constexpr int kMiscOff = kBarOff + kNumBars * 8;
+    static constexpr int kDynBytes = kMiscOff + 16 + 1024;
+};
+
+template <typename OutT>
+__device__ __forceinline__ void store_row32(OutT* dst, const uint32_t (&o)[32], float mul) {
+    if constexpr (sizeof(OutT) == 2) {
+        uint4* d = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+            uint4 w;
+            w.x = pack_bf16x2(__uint_as_float(o[8 * v + 0]) * mul, __uint_as_float(o[8 * v + 1]) * mul);
+            w.y = pack_bf16x2(__uint_as_float(o[8 * v + 2]) * mul, __uint_as_float(o[8 * v + 3]) * mul);
+            w.z = pack_bf16x2(__uint_as_float(o[8 * v + 4]) * mul, __uint_as_float(o[8 * v + 5]) * mul);
+            w.w = pack_bf16x2(__uint_as_float(o[8 * v + 6]) * mul, __uint_as_float(o[8 * v + 7]) * mul);
+            d[v] = w;
+        }
+    } else {
+        float4* d = reinterpret_cast<float4*>(dst);
+#pragma unroll
+        for (int v = 0; v < 8; ++v)
+            d[v] = make_float4(__uint_as_float(o[4 * v + 0]) * mul, __uint_as_float(o[4 * v + 1]) * mul,
+                               __uint_as_float(o[4 * v + 2]) * mul, __uint_as_float(o[4 * v + 3]) * mul);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// 2. dQ
+// tensor memory per tile t (base t*192): S [0,64)  dP [64,128)  dQ [128,192); dS (bf16) over S [0,32)
+// ---------------------------------------------------------------------------------------------
+// kSplit (fp32 gradients out): dS is written as two bf16 terms (hi over S [0,32), lo over S [32,64))
+// and the dQ contraction runs once per term, so that the 2^-9 rounding of a single bf16 dS does
+// not dominate the error of an fp32 result.
+template <typename OutT, bool kSplit>
+__global__ void __launch_bounds__(kThreads, 1)
+attn_bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
+                         const __grid_constant__ CUtensorMap tmap_do,
+                         const __grid_constant__ CUtensorMap tmap_k,
+                         const __grid_constant__ CUtensorMap tmap_v, const BwdArgs a) {
+    using L = DqSmem;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    const uint32_t q_smem = smem_base + L::kQOff, do_smem = smem_base + L::kDoOff;
+    const uint32_t ring_smem = smem_base + L::kRingOff, bar_base = smem_base + L::kBarOff;
+    auto bar_qdo_full = [&]() { return bar_base; };
+    auto bar_ring_full = [&](int s) { return bar_base + 8u * (1 + s); };
+    auto bar_ring_empty = [&](int s) { return bar_base + 8u * (1 + L::kStages + s); };
+    auto bar_sdp_full = [&](int t) { return bar_base + 8u * (1 + 2 * L::kStages + t); };
+    auto bar_ds_full = [&](int t) { return bar_base + 8u * (3 + 2 * L::kStages + t); };
+    auto bar_dq_done = [&](int t) { return bar_base + 8u * (5 + 2 * L::kStages + t); };
+    volatile uint32_t* misc = reinterpret_cast<volatile uint32_t*>(smem_gen + L::kMiscOff);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m_block = gridDim.x - 1 - blockIdx.x;
+    const int h = blockIdx.y, b = blockIdx.z;
+
+    int kvlen = a.Sk;
+    if (a.kv_len) kvlen = min(max(a.kv_len[b], 0), a.Sk);
+    int n_steps[2];
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+        const int q0 = m_block * 2 * kTile + t * kTile;
+        int lim = 0;
+        if (q0 < a.Sq) {
+            lim = kvlen;
+            if (a.causal) lim = min(lim, min(q0 + kTile - 1, a.Sq - 1) + a.causal_off + 1);
+        }
+        n_steps[t] = lim > 0 ? (lim + kStep - 1) / kStep : 0;
+    }
+    const int n_max = max(n_steps[0], n_steps[1]);
+
+    if (threadIdx.x == 0) {
+        mbar_init(bar_qdo_full(), 1);
+        for (int s = 0; s < L::kStages; ++s) { mbar_init(bar_ring_full(s), 1); mbar_init(bar_ring_empty(s), 1); }
+        for (int t = 0; t < 2; ++t) {
+            mbar_init(bar_sdp_full(t), 1);
+            mbar_init(bar_ds_full(t), kTile);
+            mbar_init(bar_dq_done(t), 1);
+        }
+        misc[1] = 0u;
+        mbar_fence_init();
+    }
+    if (warp == kMmaWarp) { tmem_alloc(smem_u32(const_cast<uint32_t*>(&misc[0])), kTmemCols); tmem_relinquish(); }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = misc[0];
+    const WaitCtx wc{&misc[1], a.status};
+    auto slot_of = [&](int item) { return item % L::kStages; };
+    auto phase_of = [&](int item) { return (uint32_t)((item / L::kStages) & 1); };
+
+    if (warp == kTmaWarp) {
+        if (lane == 0 && n_max > 0) {
+            mbar_arrive_expect_tx(bar_qdo_full(), 4u * kBigTile);
+            for (int t = 0; t < 2; ++t) {
+                const int q0 = m_block * 2 * kTile + t * kTile;
+                tma_load_4d(q_smem + t * kBigTile, &tmap_q, bar_qdo_full(), 0, q0, h, b);
+                tma_load_4d(do_smem + t * kBigTile, &tmap_do, bar_qdo_full(), 0, q0, h, b);
+            }
+            bool ok = true;
+            for (int j = 0; j < n_max && ok; ++j) {
+#pragma unroll
+                for (int which = 0; which < 2; ++which) {          // 0: K_j, 1: V_j
+                    const int item = 2 * j + which;
+                    ok = ok && mbar_wait(bar_ring_empty(slot_of(item)), phase_of(item) ^ 1u, wc, 0x40 + which);
+                    if (!ok) break;
+                    mbar_arrive_expect_tx(bar_ring_full(slot_of(item)), (uint32_t)kSmallTile);
+                    tma_load_4d(ring_smem + slot_of(item) * kSmallTile, which == 0 ? &tmap_k : &tmap_v,
+                                bar_ring_full(slot_of(item)), 0, j * kStep, h, b);
+                }
+            }
+        }
+    } else if (warp == kMmaWarp) {
+        if (lane == 0 && n_max > 0) {
+            constexpr uint32_t idesc_s = make_idesc_bf16(kTile, kStep, 0, 0);
+            constexpr uint32_t idesc_dq = make_idesc_bf16(kTile, kD, 0, 1);
+            // S_t = Q_t K_j^T and dP_t = dO_t V_j^T
+            auto issue_sdp = [&](int t, int slot_k, int slot_v) {
+                const uint32_t tb = tmem_base + t * 192;
+#pragma unroll
+                for (int k = 0; k < kD / 16; ++k)
+                    mma_ss(tb, make_smem_desc_sw128(q_smem + t * kBigTile + k * 32, 16, 1024),
+                           make_smem_desc_sw128(ring_smem + slot_k * kSmallTile + k * 32, 16, 1024), idesc_s, k > 0);
+#pragma unroll
+                for (int k = 0; k < kD / 16; ++k)
+                    mma_ss(tb + 64, make_smem_desc_sw128(do_smem + t * kBigTile + k * 32, 16, 1024),
+                           make_smem_desc_sw128(ring_smem + slot_v * kSmallTile + k * 32, 16, 1024), idesc_s, k > 0);
+            };
+            // dQ_t += dS_t K_j   (dS from tensor memory, K_j rows as the contraction index)
+            auto issue_dq = [&](int t, int slot_k, bool acc) {
+                const uint32_t tb = tmem_base + t * 192;
+#pragma unroll
+                for (int k = 0; k < kStep / 16; ++k)
+                    mma_ts(tb + 128, tb + k * 8,
+                           make_smem_desc_sw128(ring_smem + slot_k * kSmallTile + k * 2048, 8192, 1024), idesc_dq,
+                           (acc || k > 0) ? 1u : 0u);
+                if constexpr (kSplit) {
+#pragma unroll
+                    for (int k = 0; k < kStep / 16; ++k)
+                        mma_ts(tb + 128, tb + 32 + k * 8,
+                               make_smem_desc_sw128(ring_smem + slot_k * kSmallTile + k * 2048, 8192, 1024),
+                               idesc_dq, 1u);
+                }
+            };
+            bool ok = mbar_wait(bar_qdo_full(), 0, wc, 0x50);
+            ok = ok && mbar_wait(bar_ring_full(slot_of(0)), phase_of(0), wc, 0x51);
+            ok = ok && mbar_wait(bar_ring_full(slot_of(1)), phase_of(1), wc, 0x52);
+            if (ok) {
+                tc_fence_after_sync();
+                for (int t = 0; t < 2; ++t)
+                    if (n_steps[t] > 0) { issue_sdp(t, slot_of(0), slot_of(1)); mma_commit(bar_sdp_full(t)); }
+                mma_commit(bar_ring_empty(slot_of(1)));            // V_0 is consumed
+            }
+            for (int j = 0; j < n_max && ok; ++j) {
+                const int item_k = 2 * j, item_k1 = 2 * j + 2, item_v1 = 2 * j + 3;
+                const bool have_next = (j + 1 < n_max);
+                if (have_next) {
+                    ok = ok && mbar_wait(bar_ring_full(slot_of(item_k1)), phase_of(item_k1), wc, 0x53);
+                    ok = ok && mbar_wait(bar_ring_full(slot_of(item_v1)), phase_of(item_v1), wc, 0x54);
+                }
+                if (!ok) break;
+                for (int t = 0; t < 2; ++t) {
+                    if (j < n_steps[t]) {
+                        ok = ok && mbar_wait(bar_ds_full(t), (uint32_t)(j & 1), wc, 0x55 + t);
+                        if (!ok) break;
+                        tc_fence_after_sync();
+                        issue_dq(t, slot_of(item_k), j > 0);
+                        mma_commit(bar_dq_done(t));
+                    }
+                    if (j + 1 < n_steps[t]) {
+                        issue_sdp(t, slot_of(item_k1), slot_of(item_v1));
+                        mma_commit(bar_sdp_full(t));
+                    }
+                }
+                if (!ok) break;
+                mma_commit(bar_ring_empty(slot_of(item_k)));
+                if (have_next) mma_commit(bar_ring_empty(slot_of(item_v1)));
+            }
+            for (int t = 0; t < 2 && ok; ++t)
+                if (n_steps[t] > 0)
+                    ok = mbar_wait(bar_dq_done(t), (uint32_t)((n_steps[t] - 1) & 1), wc, 0x58 + t);
+        }
+    } else if (warp < 8) {
+        const int t = warp >> 2, wq = warp & 3;
+        const int row = wq * 32 + lane;
+        const int q0 = m_block * 2 * kTile + t * kTile;
+        const int qi = q0 + row;
+        const int n_t = n_steps[t];
+        const uint32_t lane_base = (uint32_t)(wq * 32) << 16;
+        const uint32_t tS = tmem_base + lane_base + t * 192;
+        const uint32_t tDP = tS + 64, tDQ = tS + 128;
+        const float c2 = a.scale_log2;
+        const bool general = (a.keep_mask != nullptr) || (a.use_clamp != 0);
+        const int64_t srow = ((int64_t)b * a.H + h) * a.Sq_pad + qi;      // qi < Sq_pad by construction
+        const float lse2 = a.lse2[srow];
+        const float dlt = a.delta[srow];
+
+        bool ok = true;
+        for (int j = 0; j < n_t; ++j) {
+            ok = __all_sync(0xffffffffu, mbar_wait(bar_sdp_full(t), (uint32_t)(j & 1), wc, 0x60 + t));
+            if (!ok) break;
+            tc_fence_after_sync();
+            uint32_t s[64], dp[64];
+            tmem_ld32(tS, reinterpret_cast<uint32_t(&)[32]>(s[0]));
+            tmem_ld32(tS + 32, reinterpret_cast<uint32_t(&)[32]>(s[32]));
+            tmem_ld32(tDP, reinterpret_cast<uint32_t(&)[32]>(dp[0]));
+            tmem_ld32(tDP + 32, reinterpret_cast<uint32_t(&)[32]>(dp[32]));
+            tmem_wait_ld();
+            const int k0 = j * kStep;
+            const bool edge = (k0 + kStep > kvlen) || (a.causal && (k0 + kStep - 1 > q0 + a.causal_off));
+            int lim = kvlen;
+            if (a.causal) lim = min(lim, qi + a.causal_off + 1);
+            lim -= k0;
+            const float* mrow = nullptr;
+            if (a.keep_mask && qi < a.Sq) mrow = a.keep_mask + ((int64_t)b * a.Sq + qi) * a.Sk + k0;
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                uint32_t hi[16], lo[16];
+#pragma unroll
+                for (int cc = 0; cc < 32; cc += 2) {
+                    float v[2];
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const int c = half * 32 + cc + e;
+                        const float sv = __uint_as_float(s[c]);
+                        const float p = fast_exp2(fmaf(sv, c2, -lse2));
+                        float d = p * (__uint_as_float(dp[c]) - dlt);
+                        if (edge || general) {
+                            bool vis = c < lim;
+                            if (mrow && vis) vis = (__ldg(mrow + c) != 0.0f);
+                            if (a.use_clamp && sv >= a.clamp_raw) d = 0.f;
+                            if (!vis) d = 0.f;
+                        }
+                        v[e] = d;
+                    }
+                    const uint32_t h01 = pack_bf16x2(v[0], v[1]);
+                    hi[cc / 2] = h01;
+                    if constexpr (kSplit)
+                        lo[cc / 2] = pack_bf16x2(v[0] - __uint_as_float(h01 << 16),
+                                                 v[1] - __uint_as_float(h01 & 0xffff0000u));
+                }
+                tmem_st16(tS + half * 16, hi);
+                if constexpr (kSplit) tmem_st16(tS + 32 + half * 16, lo);
+            }
+            tmem_wait_st();
+            tc_fence_before_sync();
+            mbar_arrive(bar_ds_full(t));
+        }
+        if (ok && q0 < a.Sq) {
+            if (n_t > 0) {
+                ok = __all_sync(0xffffffffu, mbar_wait(bar_dq_done(t), (uint32_t)((n_t - 1) & 1), wc, 0x62 + t));
+                tc_fence_after_sync();
+            }
+            OutT* drow = reinterpret_cast<OutT*>(a.dq) + b * a.dqs.batch + h * a.dqs.head + (int64_t)qi * a.dqs.seq;
+#pragma unroll
+            for (int c0 = 0; c0 < kD; c0 += 32) {
+                uint32_t o[32];
+                if (n_t > 0 && ok) { tmem_ld32(tDQ + c0, o); tmem_wait_ld(); }
+                else {
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) o[c] = 0u;
+                }
+                if (qi < a.Sq) store_row32<OutT>(drow + c0, o, a.scale);
+            }
+        }
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == kMmaWarp) {
+        __syncwarp();
+        if (misc[1]) __nanosleep(200000);
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// 3. dK, dV (transposed problem: one KEY per tensor-memory lane)
+// tensor memory per tile t (base t*256): S^T [0,64) dP^T [64,128) dV [128,192) dK [192,256);
+// P^T (bf16) over S^T [0,32), dS^T (bf16) over dP^T [64,96)
+// ---------------------------------------------------------------------------------------------
+// kSplit as above: P^T hi/lo over S^T [0,32)/[32,64), dS^T hi/lo over dP^T [64,96)/[96,128).
+template <typename OutT, bool kSplit>
+__global__ void __launch_bounds__(kThreads, 1)
+attn_bwd_dkv_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
+                          const __grid_constant__ CUtensorMap tmap_do,
+                          const __grid_constant__ CUtensorMap tmap_k,
+                          const __grid_constant__ CUtensorMap tmap_v, const BwdArgs a) {
+    using L = DkvSmem;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    const uint32_t k_smem = smem_base + L::kKOff, v_smem = smem_base + L::kVOff;
+    const uint32_t ring_smem = smem_base + L::kRingOff, bar_base = smem_base + L::kBarOff;
+    auto bar_kv_full = [&]() { return bar_base; };
+    auto bar_ring_full = [&](int s) { return bar_base + 8u * (1 + s); };
+    auto bar_ring_empty = [&](int s) { return bar_base + 8u * (1 + L::kStages + s); };
+    auto bar_sdp_full = [&](int t) { return bar_base + 8u * (1 + 2 * L::kStages + t); };
+    auto bar_pds_full = [&](int t) { return bar_base + 8u * (3 + 2 * L::kStages + t); };
+    auto bar_acc_done = [&](int t) { return bar_base + 8u * (5 + 2 * L::kStages + t); };
+    volatile uint32_t* misc = reinterpret_cast<volatile uint32_t*>(smem_gen + L::kMiscOff);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n_block = blockIdx.x;                 // early key blocks carry the most causal work
+    const int h = blockIdx.y, b = blockIdx.z;
+
+    int kvlen = a.Sk;
+    if (a.kv_len) kvlen = min(max(a.kv_len[b], 0), a.Sk);
+    const int n_q = (a.Sq + kStep - 1) / kStep;     // query steps in total
+    int j_begin[2];                                 // first query step that can see the tile's keys
+    bool active[2];
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+        const int k0 = n_block * 2 * kTile + t * kTile;
+        active[t] = (k0 < kvlen);
+        int jb = 0;
+        if (a.causal) jb = max(0, k0 - a.causal_off) / kStep;
+        j_begin[t] = jb;
+        if (jb >= n_q) active[t] = false;
+    }
+    const bool any_active = active[0] || active[1];
+    const int j_first = min(active[0] ? j_begin[0] : n_q, active[1] ? j_begin[1] : n_q);
+
+    if (threadIdx.x == 0) {
+        mbar_init(bar_kv_full(), 1);
+        for (int s = 0; s < L::kStages; ++s) { mbar_init(bar_ring_full(s), 1); mbar_init(bar_ring_empty(s), 1); }
+        for (int t = 0; t < 2; ++t) {
+            mbar_init(bar_sdp_full(t), 1);
+            mbar_init(bar_pds_full(t), kTile);
+            mbar_init(bar_acc_done(t), 1);
+        }
+        misc[1] = 0u;
+        mbar_fence_init();
+    }
+    if (warp == kMmaWarp) { tmem_alloc(smem_u32(const_cast<uint32_t*>(&misc[0])), kTmemCols); tmem_relinquish(); }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = misc[0];
+    const WaitCtx wc{&misc[1], a.status};
+    // ring items are numbered from the first streamed step of this CTA
+    auto slot_of = [&](int j) { return (j - j_first) % L::kStages; };
+    auto phase_of = [&](int j) { return (uint32_t)(((j - j_first) / L::kStages) & 1); };
+
+    if (warp == kTmaWarp) {
+        if (lane == 0 && any_active) {
+            mbar_arrive_expect_tx(bar_kv_full(), 4u * kBigTile);
+            for (int t = 0; t < 2; ++t) {
+                const int k0 = n_block * 2 * kTile + t * kTile;
+                tma_load_4d(k_smem + t * kBigTile, &tmap_k, bar_kv_full(), 0, k0, h, b);
+                tma_load_4d(v_smem + t * kBigTile, &tmap_v, bar_kv_full(), 0, k0, h, b);
+            }
+            const float* lse2_row = a.lse2 + ((int64_t)b * a.H + h) * a.Sq_pad;
+            const float* dlt_row = a.delta + ((int64_t)b * a.H + h) * a.Sq_pad;
+            bool ok = true;
+            for (int j = j_first; j < n_q && ok; ++j) {
+                ok = mbar_wait(bar_ring_empty(slot_of(j)), phase_of(j) ^ 1u, wc, 0x70);
+                if (!ok) break;
+                const uint32_t st = ring_smem + slot_of(j) * L::kStageBytes;
+                mbar_arrive_expect_tx(bar_ring_full(slot_of(j)), 2u * kSmallTile + 512u);
+                tma_load_4d(st, &tmap_q, bar_ring_full(slot_of(j)), 0, j * kStep, h, b);
+                tma_load_4d(st + kSmallTile, &tmap_do, bar_ring_full(slot_of(j)), 0, j * kStep, h, b);
+                asm volatile(
+                    "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], 256, [%2];"
+                    ::"r"(st + 2 * kSmallTile), "l"(reinterpret_cast<uint64_t>(lse2_row + j * kStep)),
+                      "r"(bar_ring_full(slot_of(j))) : "memory");
+                asm volatile(
+                    "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], 256, [%2];"
+                    ::"r"(st + 2 * kSmallTile + 256), "l"(reinterpret_cast<uint64_t>(dlt_row + j * kStep)),
+                      "r"(bar_ring_full(slot_of(j))) : "memory");
+            }
+        }
+    } else if (warp == kMmaWarp) {
+        if (lane == 0 && any_active) {
+            constexpr uint32_t idesc_s = make_idesc_bf16(kTile, kStep, 0, 0);
+            constexpr uint32_t idesc_acc = make_idesc_bf16(kTile, kD, 0, 1);
+            // S^T_t = K_t Q_j^T and dP^T_t = V_t dO_j^T
+            auto issue_sdp = [&](int t, int slot) {
+                const uint32_t tb = tmem_base + t * 256;
+                const uint32_t st = ring_smem + slot * L::kStageBytes;
+#pragma unroll
+                for (int k = 0; k < kD / 16; ++k)
+                    mma_ss(tb, make_smem_desc_sw128(k_smem + t * kBigTile + k * 32, 16, 1024),
+                           make_smem_desc_sw128(st + k * 32, 16, 1024), idesc_s, k > 0);
+#pragma unroll
+                for (int k = 0; k < kD / 16; ++k)
+                    mma_ss(tb + 64, make_smem_desc_sw128(v_smem + t * kBigTile + k * 32, 16, 1024),
+                           make_smem_desc_sw128(st + kSmallTile + k * 32, 16, 1024), idesc_s, k > 0);
+            };
+            // dV_t += P^T_t dO_j and dK_t += dS^T_t Q_j   (query rows are the contraction index)
+            auto issue_acc = [&](int t, int slot, bool acc) {
+                const uint32_t tb = tmem_base + t * 256;
+                const uint32_t st = ring_smem + slot * L::kStageBytes;
+#pragma unroll
+                for (int k = 0; k < kStep / 16; ++k)
+                    mma_ts(tb + 128, tb + k * 8,
+                           make_smem_desc_sw128(st + kSmallTile + k * 2048, 8192, 1024), idesc_acc,
+                           (acc || k > 0) ? 1u : 0u);
+#pragma unroll
+                for (int k = 0; k < kStep / 16; ++k)
+                    mma_ts(tb + 192, tb + 64 + k * 8, make_smem_desc_sw128(st + k * 2048, 8192, 1024),
+                           idesc_acc, (acc || k > 0) ? 1u : 0u);
+                if constexpr (kSplit) {
+#pragma unroll
+                    for (int k = 0; k < kStep / 16; ++k)
+                        mma_ts(tb + 128, tb + 32 + k * 8,
+                               make_smem_desc_sw128(st + kSmallTile + k * 2048, 8192, 1024), idesc_acc, 1u);
+#pragma unroll
+                    for (int k = 0; k < kStep / 16; ++k)
+                        mma_ts(tb + 192, tb + 96 + k * 8, make_smem_desc_sw128(st + k * 2048, 8192, 1024),
+                               idesc_acc, 1u);
+                }
+            };
+            bool ok = mbar_wait(bar_kv_full(), 0, wc, 0x80);
+            if (ok && j_first < n_q) {
+                ok = mbar_wait(bar_ring_full(slot_of(j_first)), phase_of(j_first), wc, 0x81);
+                if (ok) {
+                    tc_fence_after_sync();
+                    for (int t = 0; t < 2; ++t)
+                        if (active[t] && j_begin[t] == j_first) { issue_sdp(t, slot_of(j_first)); mma_commit(bar_sdp_full(t)); }
+                }
+            }
+            for (int j = j_first; j < n_q && ok; ++j) {
+                const bool have_next = (j + 1 < n_q);
+                if (have_next) ok = mbar_wait(bar_ring_full(slot_of(j + 1)), phase_of(j + 1), wc, 0x82);
+                if (!ok) break;
+                for (int t = 0; t < 2; ++t) {
+                    if (!active[t]) continue;
+                    if (j >= j_begin[t]) {
+                        ok = ok && mbar_wait(bar_pds_full(t), (uint32_t)((j - j_begin[t]) & 1), wc, 0x83 + t);
+                        if (!ok) break;
+                        tc_fence_after_sync();
+                        issue_acc(t, slot_of(j), j > j_begin[t]);
+                        mma_commit(bar_acc_done(t));
+                    }
+                    if (have_next && j + 1 >= j_begin[t]) {
+                        issue_sdp(t, slot_of(j + 1));
+                        mma_commit(bar_sdp_full(t));
+                    }
+                }
+                if (!ok) break;
+                mma_commit(bar_ring_empty(slot_of(j)));
+            }
+            for (int t = 0; t < 2 && ok; ++t)
+                if (active[t])
+                    ok = mbar_wait(bar_acc_done(t), (uint32_t)((n_q - 1 - j_begin[t]) & 1), wc, 0x88 + t);
+        }
+    } else if (warp < 8) {
+        const int t = warp >> 2, wq = warp & 3;
+        const int row = wq * 32 + lane;
+        const int k0 = n_block * 2 * kTile + t * kTile;
+        const int kj = k0 + row;                                   // this thread's key
+        const uint32_t lane_base = (uint32_t)(wq * 32) << 16;
+        const uint32_t tS = tmem_base + lane_base + t * 256;
+        const uint32_t tDP = tS + 64, tDV = tS + 128, tDK = tS + 192;
+        const float c2 = a.scale_log2;
+        const bool general = (a.keep_mask != nullptr) || (a.use_clamp != 0);
+        const bool key_live = kj < kvlen;
+
+        bool ok = true;
+        if (active[t]) {
+            for (int j = j_begin[t]; j < n_q; ++j) {
+                const int it = j - j_begin[t];
+                ok = __all_sync(0xffffffffu, mbar_wait(bar_sdp_full(t), (uint32_t)(it & 1), wc, 0x90 + t));
+                if (!ok) break;
+                tc_fence_after_sync();
+                uint32_t s[64], dp[64];
+                tmem_ld32(tS, reinterpret_cast<uint32_t(&)[32]>(s[0]));
+                tmem_ld32(tS + 32, reinterpret_cast<uint32_t(&)[32]>(s[32]));
+                tmem_ld32(tDP, reinterpret_cast<uint32_t(&)[32]>(dp[0]));
+                tmem_ld32(tDP + 32, reinterpret_cast<uint32_t(&)[32]>(dp[32]));
+                tmem_wait_ld();
+                const float4* st4 = reinterpret_cast<const float4*>(
+                    smem_gen + L::kRingOff + slot_of(j) * L::kStageBytes + 2 * kSmallTile);
+                const int q0 = j * kStep;
+                // a query column c is hidden from this key when q0 + c + off < kj
+                const bool edge = !key_live || (k0 + kTile > kvlen) ||
+                                  (a.causal && (q0 + a.causal_off < k0 + kTile - 1));
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    uint32_t pt[16], dst[16], ptl[16], dstl[16];
+#pragma unroll
+                    for (int c4 = 0; c4 < 8; ++c4) {
+                        const float4 l4 = st4[half * 8 + c4];        // lse2 of 4 query columns (broadcast read)
+                        const float4 d4 = st4[16 + half * 8 + c4];   // delta of the same columns
+                        const float ls[4] = {l4.x, l4.y, l4.z, l4.w};
+                        const float dl[4] = {d4.x, d4.y, d4.z, d4.w};
+                        float p[4], d[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const int c = half * 32 + 4 * c4 + e;
+                            const float sv = __uint_as_float(s[c]);
+                            p[e] = fast_exp2(fmaf(sv, c2, -ls[e]));
+                            d[e] = p[e] * (__uint_as_float(dp[c]) - dl[e]);
+                            if (edge || general) {
+                                bool vis = key_live && (!a.causal || (kj <= q0 + c + a.causal_off));
+                                if (vis && a.keep_mask && (q0 + c) < a.Sq)
+                                    vis = a.keep_mask[((int64_t)b * a.Sq + q0 + c) * a.Sk + kj] != 0.0f;
+                                if (a.use_clamp && sv >= a.clamp_raw) {
+                                    p[e] = fast_exp2(a.clamp_log2 - ls[e]);
+                                    d[e] = 0.f;
+                                }
+                                if (!vis) { p[e] = 0.f; d[e] = 0.f; }
+                            }
+                        }
+#pragma unroll
+                        for (int e = 0; e < 2; ++e) {
+                            const uint32_t ph = pack_bf16x2(p[2 * e], p[2 * e + 1]);
+                            const uint32_t dh = pack_bf16x2(d[2 * e], d[2 * e + 1]);
+                            pt[2 * c4 + e] = ph;
+                            dst[2 * c4 + e] = dh;
+                            if constexpr (kSplit) {
+                                ptl[2 * c4 + e] = pack_bf16x2(p[2 * e] - __uint_as_float(ph << 16),
+                                                              p[2 * e + 1] - __uint_as_float(ph & 0xffff0000u));
+                                dstl[2 * c4 + e] = pack_bf16x2(d[2 * e] - __uint_as_float(dh << 16),
+                                                               d[2 * e + 1] - __uint_as_float(dh & 0xffff0000u));
+                            }
+                        }
+                    }
+                    tmem_st16(tS + half * 16, pt);
+                    tmem_st16(tDP + half * 16, dst);
+                    if constexpr (kSplit) {
+                        tmem_st16(tS + 32 + half * 16, ptl);
+                        tmem_st16(tDP + 32 + half * 16, dstl);
+                    }
+                }
+                tmem_wait_st();
+                tc_fence_before_sync();
+                mbar_arrive(bar_pds_full(t));
+            }
+        }
+        // epilogue: dV and scale * dK (zeros for tiles that no query can see)
+        if (ok && k0 < a.Sk) {
+            if (active[t]) {
+                ok = __all_sync(0xffffffffu,
+                                mbar_wait(bar_acc_done(t), (uint32_t)((n_q - 1 - j_begin[t]) & 1), wc, 0x92 + t));
+                tc_fence_after_sync();
+            }
+            OutT* dkrow = reinterpret_cast<OutT*>(a.dk) + b * a.dks.batch + h * a.dks.head + (int64_t)kj * a.dks.seq;
+            OutT* dvrow = reinterpret_cast<OutT*>(a.dv) + b * a.dvs.batch + h * a.dvs.head + (int64_t)kj * a.dvs.seq;
+#pragma unroll
+            for (int c0 = 0; c0 < kD; c0 += 32) {
+                uint32_t o[32];
+                if (active[t] && ok) { tmem_ld32(tDV + c0, o); tmem_wait_ld(); }
+                else {
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) o[c] = 0u;
+                }
+                if (kj < a.Sk) store_row32<OutT>(dvrow + c0, o, 1.0f);
+                if (active[t] && ok) { tmem_ld32(tDK + c0, o); tmem_wait_ld(); }
+                if (kj < a.Sk) store_row32<OutT>(dkrow + c0, o, a.scale);
+            }
+        }
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == kMmaWarp) {
+        __syncwarp();
+        if (misc[1]) __nanosleep(200000);
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+size_t stats_bytes(const ltca_attn_params* p) {
+    const size_t sq_pad = align_up((size_t)p->Sq, 256);
+    return align_up((size_t)p->B * p->H * sq_pad * sizeof(float), 256);
+}
+
+template <typename OutT>
+int launch_main(ltca_ctx* ctx, const ltca_attn_params* p, const void* q, const void* k, const void* v,
+                const void* dout, const ltca_strides& qs, const ltca_strides& ks, const ltca_strides& vs,
+                const ltca_strides& dos, const float* lse2, const float* delta) {
+    CUtensorMap tq128, tdo128, tk64, tv64, tq64, tdo64, tk128, tv128;
+    int rc;
+    if ((rc = make_tmap_bhsd(ctx, &tq128, q, 2, p->B, p->H, p->Sq, kD, qs, 64, kTile))) return rc;
+    if ((rc = make_tmap_bhsd(ctx, &tdo128, dout, 2, p->B, p->H, p->Sq, kD, dos, 64, kTile))) return rc;
+    if ((rc = make_tmap_bhsd(ctx, &tk64, k, 2, p->B, p->H, p->Sk, kD, ks, 64, kStep))) return rc;
+    if ((rc = make_tmap_bhsd(ctx, &tv64, v, 2, p->B, p->H, p->Sk, kD, vs, 64, kStep))) return rc;
+    if ((rc = make_tmap_bhsd(ctx, &tq64, q, 2, p->B, p->H, p->Sq, kD, qs, 64, kStep))) return rc;
+    if ((rc = make_tmap_bhsd(ctx, &tdo64, dout, 2, p->B, p->H, p->Sq, kD, dos, 64, kStep))) return rc;
+    if ((rc = make_tmap_bhsd(ctx, &tk128, k, 2, p->B, p->H, p->Sk, kD, ks, 64, kTile))) return rc;
+    if ((rc = make_tmap_bhsd(ctx, &tv128, v, 2, p->B, p->H, p->Sk, kD, vs, 64, kTile))) return rc;
+
+    BwdArgs a;
+    memset(&a, 0, sizeof(a));
+    a.B = p->B; a.H = p->H; a.Sq = p->Sq; a.Sk = p->Sk;
+    a.Sq_pad = (int)align_up((size_t)p->Sq, 256);
+    a.causal = p->causal ? 1 : 0;
+    a.causal_off = p->Sk - p->Sq;
+    a.scale = p->scale;
+    a.scale_log2 = p->scale * 1.4426950408889634f;
+    a.use_clamp = p->score_clamp > 0.f ? 1 : 0;
+    a.clamp_raw = a.use_clamp ? p->score_clamp / p->scale : __builtin_inff();
+    a.clamp_log2 = p->score_clamp * 1.4426950408889634f;
+    a.lse2 = lse2; a.delta = delta;
+    a.dq = p->dq; a.dk = p->dk; a.dv = p->dv;
+    a.dqs = p->dq_strides; a.dks = p->dk_strides; a.dvs = p->dv_strides;
+    a.keep_mask = p->keep_mask;
+    a.kv_len = p->kv_len;
+    a.status = ctx->d_status;
+
+    auto kdq = attn_bwd_dq_sm100_kernel<OutT, sizeof(OutT) == 4>;
+    auto kdkv = attn_bwd_dkv_sm100_kernel<OutT, sizeof(OutT) == 4>;
+    static bool attr_done = false;
+    if (!attr_done) {
+        LTCA_CUDA_OK(ctx, cudaFuncSetAttribute(kdq, cudaFuncAttributeMaxDynamicSharedMemorySize, DqSmem::kDynBytes));
+        LTCA_CUDA_OK(ctx, cudaFuncSetAttribute(kdkv, cudaFuncAttributeMaxDynamicSharedMemorySize, DkvSmem::kDynBytes));
+        attr_done = true;
+    }
+    dim3 gq((p->Sq + 2 * kTile - 1) / (2 * kTile), p->H, p->B);
+    kdq<<<gq, kThreads, DqSmem::kDynBytes, ctx->stream>>>(tq128, tdo128, tk64, tv64, a);
+    LTCA_LAUNCH_OK(ctx, "attn_bwd_dq_sm100_kernel");
+    dim3 gk((p->Sk + 2 * kTile - 1) / (2 * kTile), p->H, p->B);
+    kdkv<<<gk, kThreads, DkvSmem::kDynBytes, ctx->stream>>>(tq64, tdo64, tk128, tv128, a);
+    LTCA_LAUNCH_OK(ctx, "attn_bwd_dkv_sm100_kernel");
+    return LTCA_OK;
+}
+
+// Strided fp32 [B,H,S,64] -> contiguous bf16 (same kernel shape as the forward's pack step).
+__global__ void pack_bf16_rows_kernel(const float* __restrict__ src, ltca_strides st,
+                                      __nv_bfloat16* __restrict__ dst, int H, int S, size_t n8) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += stride) {
+        const int dd = (int)(i % 8);
+        size_t r = i / 8;
+        const int s = (int)(r % S); r /= S;
+        const int h = (int)(r % H);
+        const int64_t b = (int64_t)(r / H);
+        const float* sp = src + b * st.batch + h * st.head + (int64_t)s * st.seq + 8 * dd;
+        const float4 x = *reinterpret_cast<const float4*>(sp);
+        const float4 y = *reinterpret_cast<const float4*>(sp + 4);
+        uint4 u;
+        u.x = pack_bf16x2(x.x, x.y); u.y = pack_bf16x2(x.z, x.w);
+        u.z = pack_bf16x2(y.x, y.y); u.w = pack_bf16x2(y.z, y.w);
+        reinterpret_cast<uint4*>(dst)[i] = u;
+    }
+}
+
+}  // namespace
+
+bool attn_bwd_sm100_supported(const ltca_attn_params* p) {
+    if (p->D != 64) return false;
+    if (p->Sq < 1 || p->Sk < 1 || !(p->scale > 0.f)) return false;
+    if (p->H > 65535 || p->B > 65535) return false;
+    return true;
+}
+
+size_t attn_bwd_sm100_workspace(const ltca_attn_params* p) { return 2 * stats_bytes(p); }
+
+int launch_attn_bwd_sm100(ltca_ctx* ctx, const ltca_attn_params* p) {
+    size_t need = attn_bwd_sm100_workspace(p);
+    const size_t pq = align_up((size_t)p->B * p->H * p->Sq * kD * 2, 256);
+    const size_t pk = align_up((size_t)p->B * p->H * p->Sk * kD * 2, 256);
+    if (p->dtype == LTCA_F32) need += 2 * pq + 2 * pk;
+    if (!p->workspace || p->workspace_bytes < need)
+        return fail(ctx, LTCA_ERR_WORKSPACE, "tensor-pipe backward needs %zu bytes of workspace", need);
+    const int es = elem_size(p->dtype);
+    auto bad16 = [&](const void* ptr, const ltca_strides& s) {
+        return (reinterpret_cast<uintptr_t>(ptr) & 15) || ((s.seq * es) & 15) || ((s.head * es) & 15) ||
+               ((s.batch * es) & 15);
+    };
+    if (bad16(p->o, p->o_strides) || bad16(p->dout, p->do_strides) || bad16(p->dq, p->dq_strides) ||
+        bad16(p->dk, p->dk_strides) || bad16(p->dv, p->dv_strides))
+        return fail(ctx, LTCA_ERR_INVALID, "o, dout, dq, dk, dv need 16-byte aligned bases and strides");
+
+    char* w = reinterpret_cast<char*>(p->workspace);
+    float* lse2 = reinterpret_cast<float*>(w);  w += stats_bytes(p);
+    float* delta = reinterpret_cast<float*>(w); w += stats_bytes(p);
+
+    StatsArgs s;
+    s.B = p->B; s.H = p->H; s.Sq = p->Sq; s.Sq_pad = (int)align_up((size_t)p->Sq, 256);
+    s.o = p->o; s.dout = p->dout; s.os = p->o_strides; s.dos = p->do_strides;
+    s.lse = p->lse; s.lse2 = lse2; s.delta = delta;
+    const int64_t rows = (int64_t)p->B * p->H * s.Sq_pad;
+    const unsigned blocks = (unsigned)((rows + 31) / 32);
+    if (p->dtype == LTCA_BF16) attn_bwd_stats_kernel<__nv_bfloat16><<<blocks, 256, 0, ctx->stream>>>(s);
+    else attn_bwd_stats_kernel<float><<<blocks, 256, 0, ctx->stream>>>(s);
+    LTCA_LAUNCH_OK(ctx, "attn_bwd_stats_kernel");
+
+    if (p->dtype == LTCA_BF16)
+        return launch_main<__nv_bfloat16>(ctx, p, p->q, p->k, p->v, p->dout, p->q_strides, p->k_strides,
+                                          p->v_strides, p->do_strides, lse2, delta);
+
+    // fp32 storage: bf16 copies of the four operands, fp32 gradients out
+    void* qb = w;  w += pq;
+    void* kb = w;  w += pk;
+    void* vb = w;  w += pk;
+    void* gb = w;
+    auto pack = [&](const void* src, const ltca_strides& st, void* dst, int S) -> int {
+        if ((reinterpret_cast<uintptr_t>(src) & 15) || (st.seq % 4) || (st.head % 4) || (st.batch % 4))
+            return fail(ctx, LTCA_ERR_INVALID, "fp32 tensors need 16-byte aligned rows for the bf16 mode");
+        const size_t n8 = (size_t)p->B * p->H * S * kD / 8;
+        size_t nb = (n8 + 255) / 256;
+        if (nb > 148 * 16) nb = 148 * 16;
+        pack_bf16_rows_kernel<<<(unsigned)nb, 256, 0, ctx->stream>>>(
+            reinterpret_cast<const float*>(src), st, reinterpret_cast<__nv_bfloat16*>(dst), p->H, S, n8);
+        LTCA_LAUNCH_OK(ctx, "pack_bf16_rows_kernel");
+        return LTCA_OK;
+    };
+    int rc;
+    if ((rc = pack(p->q, p->q_strides, qb, p->Sq))) return rc;
+    if ((rc = pack(p->k, p->k_strides, kb, p->Sk))) return rc;
+    if ((rc = pack(p->v, p->v_strides, vb, p->Sk))) return rc;
+    if ((rc = pack(p->dout, p->do_strides, gb, p->Sq))) return rc;
+    ltca_strides cq{(int64_t)p->H * p->Sq * kD, (int64_t)p->Sq * kD, kD};
+    ltca_strides ck{(int64_t)p->H * p->Sk * kD, (int64_t)p->Sk * kD, kD};
+    return launch_main<float>(ctx, p, qb, kb, vb, gb, cq, ck, ck, cq, lse2, delta);
 }
 
 }  // namespace ltca

@@ -223,3 +223,53 @@ def test_argument_errors(ctx):
     big = torch.zeros((1, 1, 4, 256), device="cuda")
     with pytest.raises(LtcaError):
         ctx.attn_fwd(big, big, big, mode=_lib.MODE_FP32)
+
+
+TC_BWD_CASES = [
+    # B, H, Sq, Sk, causal, kvlen, mask, clamp      (head_dim 64)
+    (1, 1, 128, 128, False, False, False, 0.0),
+    (1, 2, 256, 256, True, False, False, 0.0),
+    (2, 2, 384, 384, True, False, False, 0.0),
+    (2, 3, 257, 257, True, False, False, 0.0),
+    (1, 2, 1000, 1000, False, True, False, 0.0),
+    (2, 2, 130, 515, True, True, False, 0.0),
+    (1, 2, 200, 200, True, False, True, 5.0),
+    (1, 2, 515, 130, True, False, False, 0.0),      # early queries see no key at all
+    (32, 8, 256, 256, True, False, False, 0.0),     # config 2 core
+]
+
+
+@pytest.mark.parametrize("storage", ["bf16", "f32"])
+@pytest.mark.parametrize("case", TC_BWD_CASES)
+def test_tensor_pipe_backward(ctx, case, storage):
+    B, H, Sq, Sk, causal, use_len, use_mask, clamp = case
+    D = 64
+    q, k, v, do = make_case(B, H, Sq, Sk, D, 600, 0.5 if storage == "bf16" else 1.0)
+    qr, kr, vr, dor = bf16_round(q), bf16_round(k), bf16_round(v), bf16_round(do)
+    L = np.random.default_rng(8).integers(1, Sk + 1, size=B).astype(np.int32) if use_len else None
+    m = keep_mask(B, Sq, Sk, 9, 0.8, dead_rows=((0, 3),)) if use_mask else None
+    sc = 1.0 / math.sqrt(D)
+    ref = oracle.attn_bwd(qr, kr, vr, dor, sc, causal, m, L, clamp)
+    dt = torch.bfloat16 if storage == "bf16" else torch.float32
+    tq, tk, tv, tdo = dev(q, dt), dev(k, dt), dev(v, dt), dev(do, dt)
+    dL = torch.from_numpy(L).cuda() if L is not None else None
+    dm = dev(m) if m is not None else None
+    kw = dict(scale=sc, causal=causal, kv_len=dL, keep_mask=dm, score_clamp=clamp, mode=_lib.MODE_BF16)
+    assert ctx.uses_tensor_pipe(tq, tk, tv, causal=causal, mode=_lib.MODE_BF16, backward=True)
+    o, lse = ctx.attn_fwd(tq, tk, tv, **kw)
+    got = ctx.attn_bwd(tq, tk, tv, o, lse, tdo, **kw)
+    again = ctx.attn_bwd(tq, tk, tv, o, lse, tdo, **kw)
+    torch.cuda.synchronize()
+    assert ctx.device_status() == 0
+    for name, g, g2, r in zip(("dq", "dk", "dv"), got, again, ref):
+        assert torch.equal(g, g2), f"{name}: two runs differ"          # no atomics anywhere
+        gh = g.float().cpu().numpy().astype(np.float64)
+        mag = max(1.0, float(np.abs(r).max()))
+        err = np.abs(gh - r)
+        if storage == "bf16":
+            allowed = TC_MAX_ABS * mag + np.abs(r) * 2.0 ** -8
+            assert (err <= allowed).all(), f"{name}: max excess {(err - allowed).max()}"
+            assert rel_l2(gh, r) < 2 * (TC_REL_L2 + 2.0 ** -9), name
+        else:
+            assert err.max() < TC_MAX_ABS * mag, f"{name}: max-abs {err.max()}"
+            assert rel_l2(gh, r) < 2 * TC_REL_L2, f"{name}: rel-L2 {rel_l2(gh, r)}"
