@@ -36,6 +36,8 @@ constexpr int kThreads = 384;
 constexpr int kMmaWarp = 8;
 constexpr int kTmaWarp = 9;
 constexpr uint32_t kTmemCols = 512;
+constexpr int kCtrlRegs = 64;       // registers per thread kept by the TMA / MMA-issue warps
+constexpr int kMathRegs = 216;      // registers per thread of the elementwise warps
 constexpr int kBigTile = kTile * kD * 2;      // 16 KB
 constexpr int kSmallTile = kStep * kD * 2;    // 8 KB
 
@@ -224,7 +226,7 @@ attn_bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
         for (int s = 0; s < L::kStages; ++s) { mbar_init(bar_ring_full(s), 1); mbar_init(bar_ring_empty(s), 1); }
         for (int t = 0; t < 2; ++t) {
             mbar_init(bar_sdp_full(t), 1);
-            mbar_init(bar_ds_full(t), kTile);
+            mbar_init(bar_ds_full(t), 4);          // one arrival per elementwise warp of the tile
             mbar_init(bar_dq_done(t), 1);
         }
         misc[1] = 0u;
@@ -239,7 +241,9 @@ attn_bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
     auto slot_of = [&](int item) { return item % L::kStages; };
     auto phase_of = [&](int item) { return (uint32_t)((item / L::kStages) & 1); };
 
-    if (warp == kTmaWarp) {
+    if (warp >= 8) {
+      reg_dealloc<kCtrlRegs>();
+      if (warp == kTmaWarp) {
         if (lane == 0 && n_max > 0) {
             mbar_arrive_expect_tx(bar_qdo_full(), 4u * kBigTile);
             for (int t = 0; t < 2; ++t) {
@@ -260,7 +264,7 @@ attn_bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 }
             }
         }
-    } else if (warp == kMmaWarp) {
+      } else if (warp == kMmaWarp) {
         if (lane == 0 && n_max > 0) {
             constexpr uint32_t idesc_s = make_idesc_bf16(kTile, kStep, 0, 0);
             constexpr uint32_t idesc_dq = make_idesc_bf16(kTile, kD, 0, 1);
@@ -330,7 +334,9 @@ attn_bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 if (n_steps[t] > 0)
                     ok = mbar_wait(bar_dq_done(t), (uint32_t)((n_steps[t] - 1) & 1), wc, 0x58 + t);
         }
-    } else if (warp < 8) {
+      }
+    } else {
+        reg_alloc<kMathRegs>();
         const int t = warp >> 2, wq = warp & 3;
         const int row = wq * 32 + lane;
         const int q0 = m_block * 2 * kTile + t * kTile;
@@ -358,43 +364,50 @@ attn_bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
             tmem_wait_ld();
             const int k0 = j * kStep;
             const bool edge = (k0 + kStep > kvlen) || (a.causal && (k0 + kStep - 1 > q0 + a.causal_off));
-            int lim = kvlen;
-            if (a.causal) lim = min(lim, qi + a.causal_off + 1);
-            lim -= k0;
-            const float* mrow = nullptr;
-            if (a.keep_mask && qi < a.Sq) mrow = a.keep_mask + ((int64_t)b * a.Sq + qi) * a.Sk + k0;
+            // dS = P o (dP - delta), left in dp[]; the masked variant only runs on edge steps
+            if (edge || general) {
+                int lim = kvlen;
+                if (a.causal) lim = min(lim, qi + a.causal_off + 1);
+                lim -= k0;
+                const float* mrow = nullptr;
+                if (a.keep_mask && qi < a.Sq) mrow = a.keep_mask + ((int64_t)b * a.Sq + qi) * a.Sk + k0;
+#pragma unroll
+                for (int c = 0; c < kStep; ++c) {
+                    const float sv = __uint_as_float(s[c]);
+                    const float p = fast_exp2(fmaf(sv, c2, -lse2));
+                    float d = p * (__uint_as_float(dp[c]) - dlt);
+                    bool vis = c < lim;
+                    if (mrow && vis) vis = (__ldg(mrow + c) != 0.0f);
+                    if (a.use_clamp && sv >= a.clamp_raw) d = 0.f;
+                    dp[c] = __float_as_uint(vis ? d : 0.f);
+                }
+            } else {
+#pragma unroll
+                for (int c = 0; c < kStep; ++c) {
+                    const float p = fast_exp2(fmaf(__uint_as_float(s[c]), c2, -lse2));
+                    dp[c] = __float_as_uint(p * (__uint_as_float(dp[c]) - dlt));
+                }
+            }
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
                 uint32_t hi[16], lo[16];
 #pragma unroll
                 for (int cc = 0; cc < 32; cc += 2) {
-                    float v[2];
-#pragma unroll
-                    for (int e = 0; e < 2; ++e) {
-                        const int c = half * 32 + cc + e;
-                        const float sv = __uint_as_float(s[c]);
-                        const float p = fast_exp2(fmaf(sv, c2, -lse2));
-                        float d = p * (__uint_as_float(dp[c]) - dlt);
-                        if (edge || general) {
-                            bool vis = c < lim;
-                            if (mrow && vis) vis = (__ldg(mrow + c) != 0.0f);
-                            if (a.use_clamp && sv >= a.clamp_raw) d = 0.f;
-                            if (!vis) d = 0.f;
-                        }
-                        v[e] = d;
-                    }
-                    const uint32_t h01 = pack_bf16x2(v[0], v[1]);
+                    const float v0 = __uint_as_float(dp[half * 32 + cc]);
+                    const float v1 = __uint_as_float(dp[half * 32 + cc + 1]);
+                    const uint32_t h01 = pack_bf16x2(v0, v1);
                     hi[cc / 2] = h01;
                     if constexpr (kSplit)
-                        lo[cc / 2] = pack_bf16x2(v[0] - __uint_as_float(h01 << 16),
-                                                 v[1] - __uint_as_float(h01 & 0xffff0000u));
+                        lo[cc / 2] = pack_bf16x2(v0 - __uint_as_float(h01 << 16),
+                                                 v1 - __uint_as_float(h01 & 0xffff0000u));
                 }
                 tmem_st16(tS + half * 16, hi);
                 if constexpr (kSplit) tmem_st16(tS + 32 + half * 16, lo);
             }
             tmem_wait_st();
             tc_fence_before_sync();
-            mbar_arrive(bar_ds_full(t));
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_ds_full(t));
         }
         if (ok && q0 < a.Sq) {
             if (n_t > 0) {
@@ -477,7 +490,7 @@ attn_bwd_dkv_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
         for (int s = 0; s < L::kStages; ++s) { mbar_init(bar_ring_full(s), 1); mbar_init(bar_ring_empty(s), 1); }
         for (int t = 0; t < 2; ++t) {
             mbar_init(bar_sdp_full(t), 1);
-            mbar_init(bar_pds_full(t), kTile);
+            mbar_init(bar_pds_full(t), 4);         // one arrival per elementwise warp of the tile
             mbar_init(bar_acc_done(t), 1);
         }
         misc[1] = 0u;
@@ -493,7 +506,9 @@ attn_bwd_dkv_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
     auto slot_of = [&](int j) { return (j - j_first) % L::kStages; };
     auto phase_of = [&](int j) { return (uint32_t)(((j - j_first) / L::kStages) & 1); };
 
-    if (warp == kTmaWarp) {
+    if (warp >= 8) {
+      reg_dealloc<kCtrlRegs>();
+      if (warp == kTmaWarp) {
         if (lane == 0 && any_active) {
             mbar_arrive_expect_tx(bar_kv_full(), 4u * kBigTile);
             for (int t = 0; t < 2; ++t) {
@@ -521,7 +536,7 @@ attn_bwd_dkv_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
                       "r"(bar_ring_full(slot_of(j))) : "memory");
             }
         }
-    } else if (warp == kMmaWarp) {
+      } else if (warp == kMmaWarp) {
         if (lane == 0 && any_active) {
             constexpr uint32_t idesc_s = make_idesc_bf16(kTile, kStep, 0, 0);
             constexpr uint32_t idesc_acc = make_idesc_bf16(kTile, kD, 0, 1);
@@ -596,7 +611,9 @@ attn_bwd_dkv_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 if (active[t])
                     ok = mbar_wait(bar_acc_done(t), (uint32_t)((n_q - 1 - j_begin[t]) & 1), wc, 0x88 + t);
         }
-    } else if (warp < 8) {
+      }
+    } else {
+        reg_alloc<kMathRegs>();
         const int t = warp >> 2, wq = warp & 3;
         const int row = wq * 32 + lane;
         const int k0 = n_block * 2 * kTile + t * kTile;
@@ -627,45 +644,65 @@ attn_bwd_dkv_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 // a query column c is hidden from this key when q0 + c + off < kj
                 const bool edge = !key_live || (k0 + kTile > kvlen) ||
                                   (a.causal && (q0 + a.causal_off < k0 + kTile - 1));
+                // P^T into s[], dS^T = P^T o (dP^T - delta) into dp[]; lse2 and delta of the 64 query
+                // columns are broadcast reads from the stage (every thread reads the same address)
+                if (edge || general) {
+#pragma unroll
+                    for (int c4 = 0; c4 < kStep / 4; ++c4) {
+                        const float4 l4 = st4[c4];
+                        const float4 d4 = st4[16 + c4];
+                        const float ls[4] = {l4.x, l4.y, l4.z, l4.w};
+                        const float dl[4] = {d4.x, d4.y, d4.z, d4.w};
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const int c = 4 * c4 + e;
+                            const float sv = __uint_as_float(s[c]);
+                            float p = fast_exp2(fmaf(sv, c2, -ls[e]));
+                            float d = p * (__uint_as_float(dp[c]) - dl[e]);
+                            bool vis = key_live && (!a.causal || (kj <= q0 + c + a.causal_off));
+                            if (vis && a.keep_mask && (q0 + c) < a.Sq)
+                                vis = a.keep_mask[((int64_t)b * a.Sq + q0 + c) * a.Sk + kj] != 0.0f;
+                            if (a.use_clamp && sv >= a.clamp_raw) {
+                                p = fast_exp2(a.clamp_log2 - ls[e]);
+                                d = 0.f;
+                            }
+                            s[c] = __float_as_uint(vis ? p : 0.f);
+                            dp[c] = __float_as_uint(vis ? d : 0.f);
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int c4 = 0; c4 < kStep / 4; ++c4) {
+                        const float4 l4 = st4[c4];
+                        const float4 d4 = st4[16 + c4];
+                        const float ls[4] = {l4.x, l4.y, l4.z, l4.w};
+                        const float dl[4] = {d4.x, d4.y, d4.z, d4.w};
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const int c = 4 * c4 + e;
+                            const float p = fast_exp2(fmaf(__uint_as_float(s[c]), c2, -ls[e]));
+                            s[c] = __float_as_uint(p);
+                            dp[c] = __float_as_uint(p * (__uint_as_float(dp[c]) - dl[e]));
+                        }
+                    }
+                }
 #pragma unroll
                 for (int half = 0; half < 2; ++half) {
                     uint32_t pt[16], dst[16], ptl[16], dstl[16];
 #pragma unroll
-                    for (int c4 = 0; c4 < 8; ++c4) {
-                        const float4 l4 = st4[half * 8 + c4];        // lse2 of 4 query columns (broadcast read)
-                        const float4 d4 = st4[16 + half * 8 + c4];   // delta of the same columns
-                        const float ls[4] = {l4.x, l4.y, l4.z, l4.w};
-                        const float dl[4] = {d4.x, d4.y, d4.z, d4.w};
-                        float p[4], d[4];
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const int c = half * 32 + 4 * c4 + e;
-                            const float sv = __uint_as_float(s[c]);
-                            p[e] = fast_exp2(fmaf(sv, c2, -ls[e]));
-                            d[e] = p[e] * (__uint_as_float(dp[c]) - dl[e]);
-                            if (edge || general) {
-                                bool vis = key_live && (!a.causal || (kj <= q0 + c + a.causal_off));
-                                if (vis && a.keep_mask && (q0 + c) < a.Sq)
-                                    vis = a.keep_mask[((int64_t)b * a.Sq + q0 + c) * a.Sk + kj] != 0.0f;
-                                if (a.use_clamp && sv >= a.clamp_raw) {
-                                    p[e] = fast_exp2(a.clamp_log2 - ls[e]);
-                                    d[e] = 0.f;
-                                }
-                                if (!vis) { p[e] = 0.f; d[e] = 0.f; }
-                            }
-                        }
-#pragma unroll
-                        for (int e = 0; e < 2; ++e) {
-                            const uint32_t ph = pack_bf16x2(p[2 * e], p[2 * e + 1]);
-                            const uint32_t dh = pack_bf16x2(d[2 * e], d[2 * e + 1]);
-                            pt[2 * c4 + e] = ph;
-                            dst[2 * c4 + e] = dh;
-                            if constexpr (kSplit) {
-                                ptl[2 * c4 + e] = pack_bf16x2(p[2 * e] - __uint_as_float(ph << 16),
-                                                              p[2 * e + 1] - __uint_as_float(ph & 0xffff0000u));
-                                dstl[2 * c4 + e] = pack_bf16x2(d[2 * e] - __uint_as_float(dh << 16),
-                                                               d[2 * e + 1] - __uint_as_float(dh & 0xffff0000u));
-                            }
+                    for (int cc = 0; cc < 32; cc += 2) {
+                        const int c = half * 32 + cc;
+                        const float p0 = __uint_as_float(s[c]), p1 = __uint_as_float(s[c + 1]);
+                        const float d0 = __uint_as_float(dp[c]), d1 = __uint_as_float(dp[c + 1]);
+                        const uint32_t ph = pack_bf16x2(p0, p1);
+                        const uint32_t dh = pack_bf16x2(d0, d1);
+                        pt[cc / 2] = ph;
+                        dst[cc / 2] = dh;
+                        if constexpr (kSplit) {
+                            ptl[cc / 2] = pack_bf16x2(p0 - __uint_as_float(ph << 16),
+                                                      p1 - __uint_as_float(ph & 0xffff0000u));
+                            dstl[cc / 2] = pack_bf16x2(d0 - __uint_as_float(dh << 16),
+                                                       d1 - __uint_as_float(dh & 0xffff0000u));
                         }
                     }
                     tmem_st16(tS + half * 16, pt);
@@ -677,7 +714,8 @@ attn_bwd_dkv_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 }
                 tmem_wait_st();
                 tc_fence_before_sync();
-                mbar_arrive(bar_pds_full(t));
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_pds_full(t));
             }
         }
         // epilogue: dV and scale * dK (zeros for tiles that no query can see)

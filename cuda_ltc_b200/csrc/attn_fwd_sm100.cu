@@ -11,19 +11,20 @@
 //     that TMA brings in, which halves the L2 -> shared traffic per FLOP;
 //   - warps 0-3 / 4-7: softmax of query tile 0 / 1 (one query row per thread, so row maxima
 //     and sums need no shuffles), also rescale O when the running maximum moved and write the
-//     final O and lse;  warp 8: issues every tcgen05.mma;  warp 9: TMA producer;
-//   - S = Q K^T accumulates in tensor memory (128 fp32 columns per tile), the softmax warps read
-//     it with tcgen05.ld, write P back as packed bf16 (tcgen05.st, aliasing S) and the second
-//     contraction O += P V takes P straight from tensor memory; O (D fp32 columns per tile)
-//     never leaves tensor memory until the epilogue;
+//     final O and lse;  warp 8: issues every tcgen05.mma;  warp 9: TMA producer.  The softmax
+//     warps take the registers the other warps give up (setmaxnreg), so a whole score row
+//     stays in registers;
+//   - S = Q K^T accumulates in tensor memory; the softmax warps read it with tcgen05.ld and
+//     release it at once, so the next step's S is computed while this step's exponentials
+//     run; P goes back to its OWN tensor-memory columns as packed bf16 (tcgen05.st) and the
+//     second contraction O += P V takes it from there; O never leaves tensor memory until the
+//     epilogue;
 //   - K and V tiles travel through one ring of shared-memory slots in the order
-//     K0 V0 K1 V1 ..., each slot guarded by a full/empty mbarrier pair;
-//   - the MMA warp interleaves the two tiles (PV0, QK0', PV1, QK1') so that one tile's
-//     softmax overlaps the other tile's contractions.
+//     K0 V0 K1 V1 ..., each slot guarded by a full/empty mbarrier pair.
 //
-// Tensor-memory map (512 columns): S0 [0,128) S1 [128,256) O0 [256,256+D) O1 [256+D,256+2D);
-// P_t occupies the upper 64 columns of S_t (128 bf16 packed two per column); in the split-P
-// variant its low-order term occupies the lower 64 columns.
+// Keys per step (kBN): 128 for head_dim 64 with a bf16 result, else 64 (head_dim 128, or the
+// split-P variant below), chosen so that everything fits the 512 tensor-memory columns:
+//   S0 S1 (kBN each) | O0 O1 (D each) | P0 P1 (kBN/2 each) | split-P only: Plo0 Plo1 (kBN/2 each)
 #include "host_common.h"
 #include "sm100_ptx.cuh"
 
@@ -32,7 +33,6 @@ namespace ltca {
 namespace {
 
 constexpr int kBlockM = 128;        // query rows per tile
-constexpr int kBlockN = 128;        // keys per step
 constexpr int kFwdThreads = 384;
 constexpr int kMmaWarp = 8;
 constexpr int kTmaWarp = 9;
@@ -53,19 +53,28 @@ struct FwdArgs {
     uint32_t* status;
 };
 
-template <int D>
-struct FwdSmem {
-    static constexpr int kDimBlocks = D / 64;                  // 64-element (128 B) column blocks
-    static constexpr int kTileBytes = kBlockN * D * 2;         // one Q/K/V tile
-    static constexpr int kStages = (D == 64) ? 8 : 4;          // ring slots
+template <int D, bool kSplitP>
+struct FwdCfg {
+    static constexpr int kBN = (D == 64 && !kSplitP) ? 128 : 64;   // keys per step
+    static constexpr int kDimBlocks = D / 64;                      // 64-element (128 B) column blocks
+    static constexpr int kQTileBytes = kBlockM * D * 2;
+    static constexpr int kKvTileBytes = kBN * D * 2;
+    static constexpr int kStages = 8;                              // ring slots
+    // tensor-memory columns
+    static constexpr int kColS = 0;
+    static constexpr int kColO = 2 * kBN;
+    static constexpr int kColP = kColO + 2 * D;
+    static constexpr int kColPlo = kColP + kBN;
+    static_assert(kColPlo + (kSplitP ? kBN : 0) <= 512, "tensor memory overflow");
+    // shared memory
     static constexpr int kQOff = 0;
-    static constexpr int kRingOff = 2 * kTileBytes;
-    static constexpr int kBarOff = kRingOff + kStages * kTileBytes;
-    // barriers: q_full, kv_full[kStages], kv_empty[kStages], s_full[2], p_full[2], o_done[2]
-    static constexpr int kNumBars = 1 + 2 * kStages + 6;
-    static constexpr int kMiscOff = kBarOff + kNumBars * 8;    // tmem base, abort flag
+    static constexpr int kRingOff = 2 * kQTileBytes;
+    static constexpr int kBarOff = kRingOff + kStages * kKvTileBytes;
+    // barriers: q_full, kv_full[kStages], kv_empty[kStages], s_full[2], s_free[2], p_full[2], o_done[2]
+    static constexpr int kNumBars = 1 + 2 * kStages + 8;
+    static constexpr int kMiscOff = kBarOff + kNumBars * 8;        // tmem base, abort flag
     static constexpr int kBytes = kMiscOff + 16;
-    static constexpr int kDynBytes = kBytes + 1024;            // room to align to 1024 B
+    static constexpr int kDynBytes = kBytes + 1024;                // room to align to 1024 B
 };
 
 __device__ __forceinline__ float neg_inf() { return __int_as_float(0xff800000); }
@@ -78,7 +87,8 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
 attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
                       const __grid_constant__ CUtensorMap tmap_k,
                       const __grid_constant__ CUtensorMap tmap_v, const FwdArgs a) {
-    using L = FwdSmem<D>;
+    using L = FwdCfg<D, kSplitP>;
+    constexpr int kBN = L::kBN;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -90,8 +100,9 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
     auto bar_kv_full = [&](int s) { return bar_base + 8u * (1 + s); };
     auto bar_kv_empty = [&](int s) { return bar_base + 8u * (1 + L::kStages + s); };
     auto bar_s_full = [&](int t) { return bar_base + 8u * (1 + 2 * L::kStages + t); };
-    auto bar_p_full = [&](int t) { return bar_base + 8u * (3 + 2 * L::kStages + t); };
-    auto bar_o_done = [&](int t) { return bar_base + 8u * (5 + 2 * L::kStages + t); };
+    auto bar_s_free = [&](int t) { return bar_base + 8u * (3 + 2 * L::kStages + t); };
+    auto bar_p_full = [&](int t) { return bar_base + 8u * (5 + 2 * L::kStages + t); };
+    auto bar_o_done = [&](int t) { return bar_base + 8u * (7 + 2 * L::kStages + t); };
     volatile uint32_t* misc = reinterpret_cast<volatile uint32_t*>(smem_gen + L::kMiscOff);
     // misc[0] = tensor-memory base address, misc[1] = abort flag
 
@@ -112,7 +123,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
             lim = kvlen;
             if (a.causal) lim = min(lim, min(q0 + kBlockM - 1, a.Sq - 1) + a.causal_off + 1);
         }
-        n_tiles[t] = lim > 0 ? (lim + kBlockN - 1) / kBlockN : 0;
+        n_tiles[t] = lim > 0 ? (lim + kBN - 1) / kBN : 0;
     }
     const int n_max = max(n_tiles[0], n_tiles[1]);
 
@@ -124,7 +135,8 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
         }
         for (int t = 0; t < 2; ++t) {
             mbar_init(bar_s_full(t), 1);
-            mbar_init(bar_p_full(t), kBlockM);
+            mbar_init(bar_s_free(t), 4);       // one arrival per softmax warp of the tile
+            mbar_init(bar_p_full(t), 4);
             mbar_init(bar_o_done(t), 1);
         }
         misc[1] = 0u;
@@ -140,109 +152,120 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
     const uint32_t tmem_base = misc[0];
     const WaitCtx wc{&misc[1], a.status};
 
-    if (warp == kTmaWarp) {
-        // ------------------------------ TMA producer ------------------------------------------
-        if (lane == 0 && n_max > 0) {
-            tma_prefetch_desc(&tmap_q);
-            tma_prefetch_desc(&tmap_k);
-            tma_prefetch_desc(&tmap_v);
-            mbar_arrive_expect_tx(bar_q_full(), 2u * L::kTileBytes);
-            for (int t = 0; t < 2; ++t)
-                for (int kb = 0; kb < L::kDimBlocks; ++kb)
-                    tma_load_4d(q_smem + t * L::kTileBytes + kb * (kBlockM * 128), &tmap_q,
-                                bar_q_full(), kb * 64, m_block * 2 * kBlockM + t * kBlockM, h, b);
-            bool ok = true;
-            for (int j = 0; j < n_max && ok; ++j) {
-#pragma unroll
-                for (int which = 0; which < 2; ++which) {     // 0: K_j, 1: V_j
-                    const int item = 2 * j + which;
-                    const int slot = item % L::kStages;
-                    const uint32_t phase = (item / L::kStages) & 1;
-                    ok = ok && mbar_wait(bar_kv_empty(slot), phase ^ 1u, wc, 0x10 + which);
-                    if (!ok) break;
-                    mbar_arrive_expect_tx(bar_kv_full(slot), (uint32_t)L::kTileBytes);
-                    for (int kb = 0; kb < L::kDimBlocks; ++kb)
-                        tma_load_4d(ring_smem + slot * L::kTileBytes + kb * (kBlockN * 128),
-                                    which == 0 ? &tmap_k : &tmap_v, bar_kv_full(slot), kb * 64,
-                                    j * kBlockN, h, b);
-                }
-            }
-        }
-    } else if (warp == kMmaWarp) {
-        // ------------------------------ MMA issuer --------------------------------------------
-        if (lane == 0 && n_max > 0) {
-            constexpr uint32_t idesc_qk = make_idesc_bf16(kBlockM, kBlockN, 0, 0);
-            constexpr uint32_t idesc_pv = make_idesc_bf16(kBlockM, D, 0, 1);
-            auto issue_qk = [&](int t, int slot) {
-                const uint32_t qa = q_smem + t * L::kTileBytes;
-                const uint32_t ka = ring_smem + slot * L::kTileBytes;
-#pragma unroll
-                for (int k = 0; k < D / 16; ++k) {
-                    const uint32_t off = (k / 4) * (kBlockM * 128) + (k % 4) * 32;
-                    mma_ss(tmem_base + t * kBlockN, make_smem_desc_sw128(qa + off, 16, 1024),
-                           make_smem_desc_sw128(ka + off, 16, 1024), idesc_qk, k > 0 ? 1u : 0u);
-                }
-            };
-            auto issue_pv = [&](int t, int slot, bool acc) {
-                const uint32_t va = ring_smem + slot * L::kTileBytes;
-#pragma unroll
-                for (int k = 0; k < kBlockN / 16; ++k) {
-                    mma_ts(tmem_base + 2 * kBlockN + t * D, tmem_base + t * kBlockN + 64 + k * 8,
-                           make_smem_desc_sw128(va + k * 2048, kBlockN * 128, 1024), idesc_pv,
-                           (acc || k > 0) ? 1u : 0u);
-                }
-                if constexpr (kSplitP) {
-#pragma unroll
-                    for (int k = 0; k < kBlockN / 16; ++k)
-                        mma_ts(tmem_base + 2 * kBlockN + t * D, tmem_base + t * kBlockN + k * 8,
-                               make_smem_desc_sw128(va + k * 2048, kBlockN * 128, 1024), idesc_pv, 1u);
-                }
-            };
-            auto slot_of = [&](int item) { return item % L::kStages; };
-            auto phase_of = [&](int item) { return (uint32_t)((item / L::kStages) & 1); };
-
-            bool ok = mbar_wait(bar_q_full(), 0, wc, 0x20);
-            ok = ok && mbar_wait(bar_kv_full(slot_of(0)), phase_of(0), wc, 0x21);
-            if (ok) {
-                tc_fence_after_sync();
+    if (warp >= 8) {
+        reg_dealloc<64>();
+        if (warp == kTmaWarp) {
+            // ------------------------------ TMA producer --------------------------------------
+            if (lane == 0 && n_max > 0) {
+                tma_prefetch_desc(&tmap_q);
+                tma_prefetch_desc(&tmap_k);
+                tma_prefetch_desc(&tmap_v);
+                mbar_arrive_expect_tx(bar_q_full(), 2u * L::kQTileBytes);
                 for (int t = 0; t < 2; ++t)
-                    if (n_tiles[t] > 0) {
-                        issue_qk(t, slot_of(0));
-                        mma_commit(bar_s_full(t));
-                    }
-                mma_commit(bar_kv_empty(slot_of(0)));
-            }
-            for (int j = 0; j < n_max && ok; ++j) {
-                const int item_v = 2 * j + 1, item_k = 2 * j + 2;
-                const bool have_next = (j + 1 < n_max);
-                ok = ok && mbar_wait(bar_kv_full(slot_of(item_v)), phase_of(item_v), wc, 0x22);
-                if (have_next)
-                    ok = ok && mbar_wait(bar_kv_full(slot_of(item_k)), phase_of(item_k), wc, 0x23);
-                if (!ok) break;
-                for (int t = 0; t < 2; ++t) {
-                    if (j < n_tiles[t]) {
-                        ok = ok && mbar_wait(bar_p_full(t), (uint32_t)(j & 1), wc, 0x24 + t);
+                    for (int kb = 0; kb < L::kDimBlocks; ++kb)
+                        tma_load_4d(q_smem + t * L::kQTileBytes + kb * (kBlockM * 128), &tmap_q,
+                                    bar_q_full(), kb * 64, m_block * 2 * kBlockM + t * kBlockM, h, b);
+                bool ok = true;
+                for (int j = 0; j < n_max && ok; ++j) {
+#pragma unroll
+                    for (int which = 0; which < 2; ++which) {     // 0: K_j, 1: V_j
+                        const int item = 2 * j + which;
+                        const int slot = item % L::kStages;
+                        const uint32_t phase = (item / L::kStages) & 1;
+                        ok = ok && mbar_wait(bar_kv_empty(slot), phase ^ 1u, wc, 0x10 + which);
                         if (!ok) break;
-                        tc_fence_after_sync();
-                        issue_pv(t, slot_of(item_v), j > 0);
-                        mma_commit(bar_o_done(t));
-                    }
-                    if (j + 1 < n_tiles[t]) {
-                        issue_qk(t, slot_of(item_k));
-                        mma_commit(bar_s_full(t));
+                        mbar_arrive_expect_tx(bar_kv_full(slot), (uint32_t)L::kKvTileBytes);
+                        for (int kb = 0; kb < L::kDimBlocks; ++kb)
+                            tma_load_4d(ring_smem + slot * L::kKvTileBytes + kb * (kBN * 128),
+                                        which == 0 ? &tmap_k : &tmap_v, bar_kv_full(slot), kb * 64,
+                                        j * kBN, h, b);
                     }
                 }
-                if (!ok) break;
-                mma_commit(bar_kv_empty(slot_of(item_v)));
-                if (have_next) mma_commit(bar_kv_empty(slot_of(item_k)));
             }
-            // everything this thread issued has to be complete before tensor memory is released
-            for (int t = 0; t < 2 && ok; ++t)
-                if (n_tiles[t] > 0)
-                    ok = mbar_wait(bar_o_done(t), (uint32_t)((n_tiles[t] - 1) & 1), wc, 0x28 + t);
+        } else if (warp == kMmaWarp) {
+            // ------------------------------ MMA issuer ----------------------------------------
+            if (lane == 0 && n_max > 0) {
+                constexpr uint32_t idesc_qk = make_idesc_bf16(kBlockM, kBN, 0, 0);
+                constexpr uint32_t idesc_pv = make_idesc_bf16(kBlockM, D, 0, 1);
+                auto issue_qk = [&](int t, int slot) {
+                    const uint32_t qa = q_smem + t * L::kQTileBytes;
+                    const uint32_t ka = ring_smem + slot * L::kKvTileBytes;
+#pragma unroll
+                    for (int k = 0; k < D / 16; ++k) {
+                        const uint32_t qoff = (k / 4) * (kBlockM * 128) + (k % 4) * 32;
+                        const uint32_t koff = (k / 4) * (kBN * 128) + (k % 4) * 32;
+                        mma_ss(tmem_base + L::kColS + t * kBN, make_smem_desc_sw128(qa + qoff, 16, 1024),
+                               make_smem_desc_sw128(ka + koff, 16, 1024), idesc_qk, k > 0 ? 1u : 0u);
+                    }
+                };
+                auto issue_pv = [&](int t, int slot, bool acc) {
+                    const uint32_t va = ring_smem + slot * L::kKvTileBytes;
+#pragma unroll
+                    for (int k = 0; k < kBN / 16; ++k)
+                        mma_ts(tmem_base + L::kColO + t * D, tmem_base + L::kColP + t * (kBN / 2) + k * 8,
+                               make_smem_desc_sw128(va + k * 2048, kBN * 128, 1024), idesc_pv,
+                               (acc || k > 0) ? 1u : 0u);
+                    if constexpr (kSplitP) {
+#pragma unroll
+                        for (int k = 0; k < kBN / 16; ++k)
+                            mma_ts(tmem_base + L::kColO + t * D,
+                                   tmem_base + L::kColPlo + t * (kBN / 2) + k * 8,
+                                   make_smem_desc_sw128(va + k * 2048, kBN * 128, 1024), idesc_pv, 1u);
+                    }
+                };
+                auto slot_of = [&](int item) { return item % L::kStages; };
+                auto phase_of = [&](int item) { return (uint32_t)((item / L::kStages) & 1); };
+
+                bool ok = mbar_wait(bar_q_full(), 0, wc, 0x20);
+                ok = ok && mbar_wait(bar_kv_full(slot_of(0)), phase_of(0), wc, 0x21);
+                if (ok) {
+                    tc_fence_after_sync();
+                    for (int t = 0; t < 2; ++t)
+                        if (n_tiles[t] > 0) {
+                            issue_qk(t, slot_of(0));
+                            mma_commit(bar_s_full(t));
+                        }
+                    mma_commit(bar_kv_empty(slot_of(0)));
+                }
+                for (int j = 0; j < n_max && ok; ++j) {
+                    const int item_v = 2 * j + 1, item_k = 2 * j + 2;
+                    // S of step j+1 as soon as the softmax warps have taken S of step j
+                    if (j + 1 < n_max) {
+                        ok = mbar_wait(bar_kv_full(slot_of(item_k)), phase_of(item_k), wc, 0x23);
+                        for (int t = 0; t < 2 && ok; ++t) {
+                            if (j + 1 < n_tiles[t]) {
+                                ok = mbar_wait(bar_s_free(t), (uint32_t)(j & 1), wc, 0x26 + t);
+                                if (!ok) break;
+                                tc_fence_after_sync();
+                                issue_qk(t, slot_of(item_k));
+                                mma_commit(bar_s_full(t));
+                            }
+                        }
+                        if (!ok) break;
+                        mma_commit(bar_kv_empty(slot_of(item_k)));
+                    }
+                    ok = mbar_wait(bar_kv_full(slot_of(item_v)), phase_of(item_v), wc, 0x22);
+                    for (int t = 0; t < 2 && ok; ++t) {
+                        if (j < n_tiles[t]) {
+                            ok = mbar_wait(bar_p_full(t), (uint32_t)(j & 1), wc, 0x24 + t);
+                            if (!ok) break;
+                            tc_fence_after_sync();
+                            issue_pv(t, slot_of(item_v), j > 0);
+                            mma_commit(bar_o_done(t));
+                        }
+                    }
+                    if (!ok) break;
+                    mma_commit(bar_kv_empty(slot_of(item_v)));
+                }
+                // everything this thread issued has to be complete before tensor memory is released
+                for (int t = 0; t < 2 && ok; ++t)
+                    if (n_tiles[t] > 0)
+                        ok = mbar_wait(bar_o_done(t), (uint32_t)((n_tiles[t] - 1) & 1), wc, 0x28 + t);
+            }
         }
-    } else if (warp < 8) {
+    } else {
         // ------------------------------ softmax / correction / epilogue ------------------------
+        reg_alloc<216>();
         const int t = warp >> 2;
         const int wq = warp & 3;
         const int row = wq * 32 + lane;
@@ -250,9 +273,10 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
         const int qi = q0 + row;
         const int n_t = n_tiles[t];
         const uint32_t lane_base = (uint32_t)(wq * 32) << 16;
-        const uint32_t tS = tmem_base + lane_base + t * kBlockN;
-        const uint32_t tP = tS + 64;
-        const uint32_t tO = tmem_base + lane_base + 2 * kBlockN + t * D;
+        const uint32_t tS = tmem_base + lane_base + L::kColS + t * kBN;
+        const uint32_t tO = tmem_base + lane_base + L::kColO + t * D;
+        const uint32_t tP = tmem_base + lane_base + L::kColP + t * (kBN / 2);
+        const uint32_t tPlo = tmem_base + lane_base + L::kColPlo + t * (kBN / 2);
         const float c2 = a.scale_log2;
         const bool general = (a.keep_mask != nullptr) || (a.use_clamp != 0);
 
@@ -263,16 +287,18 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
             ok = __all_sync(0xffffffffu, mbar_wait(bar_s_full(t), (uint32_t)(j & 1), wc, 0x30 + t));
             if (!ok) break;
             tc_fence_after_sync();
-            uint32_t su[kBlockN];
-            tmem_ld32(tS + 0, reinterpret_cast<uint32_t(&)[32]>(su[0]));
-            tmem_ld32(tS + 32, reinterpret_cast<uint32_t(&)[32]>(su[32]));
-            tmem_ld32(tS + 64, reinterpret_cast<uint32_t(&)[32]>(su[64]));
-            tmem_ld32(tS + 96, reinterpret_cast<uint32_t(&)[32]>(su[96]));
+            uint32_t su[kBN];
+#pragma unroll
+            for (int c0 = 0; c0 < kBN; c0 += 32)
+                tmem_ld32(tS + c0, reinterpret_cast<uint32_t(&)[32]>(su[c0]));
             tmem_wait_ld();
+            // S is in registers: the next step's Q K^T may overwrite it
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_s_free(t));
 #define S_(c) __uint_as_float(su[(c)])
-            const int k0 = j * kBlockN;
-            const bool edge = (k0 + kBlockN > kvlen) ||
-                              (a.causal && (k0 + kBlockN - 1 > q0 + a.causal_off));
+            const int k0 = j * kBN;
+            const bool edge = (k0 + kBN > kvlen) || (a.causal && (k0 + kBN - 1 > q0 + a.causal_off));
             if (edge || general) {
                 int lim = kvlen;
                 if (a.causal) lim = min(lim, qi + a.causal_off + 1);
@@ -281,7 +307,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 if (a.keep_mask && qi < a.Sq)
                     mrow = a.keep_mask + ((int64_t)b * a.Sq + qi) * a.Sk + k0;
 #pragma unroll
-                for (int c = 0; c < kBlockN; ++c) {
+                for (int c = 0; c < kBN; ++c) {
                     float v = S_(c);
                     if (a.use_clamp) v = fminf(v, a.clamp_raw);
                     bool vis = c < lim;
@@ -289,15 +315,13 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
                     su[c] = __float_as_uint(vis ? v : neg_inf());
                 }
             }
-            float mx0 = S_(0), mx1 = S_(1), mx2 = S_(2), mx3 = S_(3);
+            float mx0 = fmaxf(S_(0), S_(1)), mx1 = fmaxf(S_(2), S_(3));
 #pragma unroll
-            for (int c = 4; c < kBlockN; c += 4) {
-                mx0 = fmaxf(mx0, S_(c));
-                mx1 = fmaxf(mx1, S_(c + 1));
-                mx2 = fmaxf(mx2, S_(c + 2));
-                mx3 = fmaxf(mx3, S_(c + 3));
+            for (int c = 4; c < kBN; c += 4) {
+                mx0 = fmax3(mx0, S_(c), S_(c + 1));
+                mx1 = fmax3(mx1, S_(c + 2), S_(c + 3));
             }
-            const float mt = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+            const float mt = fmaxf(mx0, mx1);
 
             // Lazy rescale: keep the stale maximum while the new one exceeds it by less than
             // 2^8 in the exponent; P stays below 256 and fp32 sums keep their accuracy.
@@ -310,10 +334,12 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 m_run = mt;
                 need = true;
             }
+            bool o_waited = (j == 0);
             if (j > 0 && __any_sync(0xffffffffu, need)) {
                 ok = __all_sync(0xffffffffu,
                                 mbar_wait(bar_o_done(t), (uint32_t)((j - 1) & 1), wc, 0x32 + t));
                 if (!ok) break;
+                o_waited = true;
                 tc_fence_after_sync();
 #pragma unroll
                 for (int c0 = 0; c0 < D; c0 += 32) {
@@ -330,11 +356,11 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
             const float mneg = -m_safe * c2;
             float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
 #pragma unroll
-            for (int half = 0; half < 2; ++half) {
-                uint32_t hi[32], lo[32];
+            for (int ch = 0; ch < kBN / 32; ++ch) {
+                uint32_t hi[16], lo[16];
 #pragma unroll
-                for (int cc = 0; cc < 64; cc += 4) {
-                    const int c = half * 64 + cc;
+                for (int cc = 0; cc < 32; cc += 4) {
+                    const int c = ch * 32 + cc;
                     const float p0 = fast_exp2(fmaf(S_(c), c2, mneg));
                     const float p1 = fast_exp2(fmaf(S_(c + 1), c2, mneg));
                     const float p2 = fast_exp2(fmaf(S_(c + 2), c2, mneg));
@@ -350,13 +376,21 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
                                                      p3 - __uint_as_float(h23 & 0xffff0000u));
                     }
                 }
-                tmem_st32(tP + half * 32, hi);
-                if constexpr (kSplitP) tmem_st32(tS + half * 32, lo);
+                if (ch == 0 && !o_waited) {
+                    // P of the previous step must have been consumed before it is overwritten
+                    ok = __all_sync(0xffffffffu,
+                                    mbar_wait(bar_o_done(t), (uint32_t)((j - 1) & 1), wc, 0x36 + t));
+                    if (!ok) break;
+                }
+                tmem_st16(tP + ch * 16, hi);
+                if constexpr (kSplitP) tmem_st16(tPlo + ch * 16, lo);
             }
+            if (!ok) break;
             l_run += (sum0 + sum1) + (sum2 + sum3);
             tmem_wait_st();
             tc_fence_before_sync();
-            mbar_arrive(bar_p_full(t));
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_p_full(t));
 #undef S_
         }
 
@@ -426,12 +460,13 @@ template <int D, typename OutT>
 int launch_fwd(ltca_ctx* ctx, const ltca_attn_params* p, const void* q, const void* k,
                const void* v, const ltca_strides& qs, const ltca_strides& ks,
                const ltca_strides& vs) {
-    using L = FwdSmem<D>;
+    constexpr bool kSplitP = sizeof(OutT) == 4;
+    using L = FwdCfg<D, kSplitP>;
     CUtensorMap tq, tk, tv;
     int rc;
     if ((rc = make_tmap_bhsd(ctx, &tq, q, 2, p->B, p->H, p->Sq, D, qs, 64, kBlockM))) return rc;
-    if ((rc = make_tmap_bhsd(ctx, &tk, k, 2, p->B, p->H, p->Sk, D, ks, 64, kBlockN))) return rc;
-    if ((rc = make_tmap_bhsd(ctx, &tv, v, 2, p->B, p->H, p->Sk, D, vs, 64, kBlockN))) return rc;
+    if ((rc = make_tmap_bhsd(ctx, &tk, k, 2, p->B, p->H, p->Sk, D, ks, 64, L::kBN))) return rc;
+    if ((rc = make_tmap_bhsd(ctx, &tv, v, 2, p->B, p->H, p->Sk, D, vs, 64, L::kBN))) return rc;
 
     FwdArgs a;
     a.B = p->B; a.H = p->H; a.Sq = p->Sq; a.Sk = p->Sk;
@@ -448,7 +483,7 @@ int launch_fwd(ltca_ctx* ctx, const ltca_attn_params* p, const void* q, const vo
     a.kv_len = p->kv_len;
     a.status = ctx->d_status;
 
-    auto kern = attn_fwd_sm100_kernel<D, OutT, sizeof(OutT) == 4>;
+    auto kern = attn_fwd_sm100_kernel<D, OutT, kSplitP>;
     static bool attr_done = false;
     if (!attr_done) {
         LTCA_CUDA_OK(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,

@@ -270,7 +270,24 @@ __device__ __forceinline__ void mma_commit(uint32_t bar) {
         ::"r"(bar) : "memory");
 }
 
+// ---- register reallocation between warpgroups ---------------------------------------------------
+// Every warp of a warpgroup (4 consecutive warps) must execute the same call.  The data-movement
+// and MMA-issue warps give registers up so that the elementwise warps can hold whole score rows.
+template <int N>
+__device__ __forceinline__ void reg_alloc() {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N>
+__device__ __forceinline__ void reg_dealloc() {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+
 // ---- small math helpers -----------------------------------------------------------------------
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
