@@ -24,6 +24,11 @@
 // elementwise work overlaps the other's contractions.  Every wait is bounded.
 #include "host_common.h"
 #include "sm100_ptx.cuh"
+#include "trace.cuh"
+
+#ifndef LTCA_BWD_STAGGER
+#define LTCA_BWD_STAGGER 1
+#endif
 
 namespace ltca {
 
@@ -32,12 +37,15 @@ namespace {
 constexpr int kTile = 128;          // rows of a resident tile (queries in dQ, keys in dKV)
 constexpr int kStep = 64;           // streamed rows per step
 constexpr int kD = 64;
-constexpr int kThreads = 384;
-constexpr int kMmaWarp = 8;
-constexpr int kTmaWarp = 9;
+constexpr int kThreads = 640;        // 16 elementwise warps + one warpgroup of control warps
+constexpr int kMmaWarp0 = 16;        // issues the contractions of tile 0 (tile 1: the next warp)
+constexpr int kTmaWarp = 18;
 constexpr uint32_t kTmemCols = 512;
-constexpr int kCtrlRegs = 64;       // registers per thread kept by the TMA / MMA-issue warps
-constexpr int kMathRegs = 216;      // registers per thread of the elementwise warps
+constexpr int kLaunchRegs = 96;      // registers per thread at launch (65536 / 640 rounded down to 8)
+constexpr int kCtrlRegs = 56;        // kept by the TMA / MMA-issue warps
+constexpr int kMathRegs = 104;       // taken by the elementwise warps
+// setmaxnreg can only redistribute what the CTA was launched with; asking for more never returns
+static_assert(512 * kMathRegs + 128 * kCtrlRegs <= kThreads * kLaunchRegs, "register budget");
 constexpr int kBigTile = kTile * kD * 2;      // 16 KB
 constexpr int kSmallTile = kStep * kD * 2;    // 8 KB
 
@@ -134,8 +142,8 @@ struct DqSmem {
     static constexpr int kDoOff = 2 * kBigTile;               // dO0, dO1
     static constexpr int kRingOff = 4 * kBigTile;
     static constexpr int kBarOff = kRingOff + kStages * kSmallTile;
-    // bars: qdo_full, ring_full[S], ring_empty[S], sdp_full[2], ds_full[2], dq_done[2]
-    static constexpr int kNumBars = 1 + 2 * kStages + 6;
+    // bars: qdo_full, ring_full[S], ring_empty[S], sdp_full[2], sdp_free[2], ds_full[2], dq_done[2], stagger
+    static constexpr int kNumBars = 1 + 2 * kStages + 9;
     static constexpr int kMiscOff = kBarOff + kNumBars * 8;
     static constexpr int kDynBytes = kMiscOff + 16 + 1024;
 };
@@ -147,8 +155,8 @@ struct DkvSmem {
     static constexpr int kVOff = 2 * kBigTile;                // V0, V1
     static constexpr int kRingOff = 4 * kBigTile;
     static constexpr int kBarOff = kRingOff + kStages * kStageBytes;
-    // bars: kv_full, ring_full[S], ring_empty[S], sdp_full[2], pds_full[2], acc_done[2]
-    static constexpr int kNumBars = 1 + 2 * kStages + 6;
+    // bars: kv_full, ring_full[S], ring_empty[S], sdp_full[2], pds_full[2], acc_done[2], stagger
+    static constexpr int kNumBars = 1 + 2 * kStages + 7;
     static constexpr int kMiscOff = kBarOff + kNumBars * 8;
     static constexpr int kDynBytes = kMiscOff + 16 + 1024;
 };
@@ -175,13 +183,28 @@ __device__ __forceinline__ void store_row32(OutT* dst, const uint32_t (&o)[32], 
     }
 }
 
+// Packs 32 fp32 values into 16 bf16 pairs (and, for the split variants, the rounding residue).
+template <bool kSplit>
+__device__ __forceinline__ void pack32(const uint32_t (&v)[32], uint32_t (&hi)[16], uint32_t (&lo)[16]) {
+#pragma unroll
+    for (int cc = 0; cc < 32; cc += 2) {
+        const float v0 = __uint_as_float(v[cc]), v1 = __uint_as_float(v[cc + 1]);
+        const uint32_t h01 = pack_bf16x2(v0, v1);
+        hi[cc / 2] = h01;
+        if constexpr (kSplit)
+            lo[cc / 2] = pack_bf16x2(v0 - __uint_as_float(h01 << 16), v1 - __uint_as_float(h01 & 0xffff0000u));
+    }
+}
+
 // ---------------------------------------------------------------------------------------------
 // 2. dQ
-// tensor memory per tile t (base t*192): S [0,64)  dP [64,128)  dQ [128,192); dS (bf16) over S [0,32)
+// tensor memory: tile t at t*192: S [0,64)  dP [64,128)  dQ [128,192);
+// dS (bf16) of tile t at 384 + t*32, its low-order term (kSplit) at 448 + t*32.
+// A query row belongs to two threads (warps w and w + 8), each owning 32 of the step's 64 keys.
 // ---------------------------------------------------------------------------------------------
-// kSplit (fp32 gradients out): dS is written as two bf16 terms (hi over S [0,32), lo over S [32,64))
-// and the dQ contraction runs once per term, so that the 2^-9 rounding of a single bf16 dS does
-// not dominate the error of an fp32 result.
+// kSplit (fp32 gradients out): dS is written as two bf16 terms and the dQ contraction runs once
+// per term, so that the 2^-9 rounding of a single bf16 dS does not dominate the error of an fp32
+// result.
 template <typename OutT, bool kSplit>
 __global__ void __launch_bounds__(kThreads, 1)
 attn_bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
@@ -198,8 +221,10 @@ attn_bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
     auto bar_ring_full = [&](int s) { return bar_base + 8u * (1 + s); };
     auto bar_ring_empty = [&](int s) { return bar_base + 8u * (1 + L::kStages + s); };
     auto bar_sdp_full = [&](int t) { return bar_base + 8u * (1 + 2 * L::kStages + t); };
-    auto bar_ds_full = [&](int t) { return bar_base + 8u * (3 + 2 * L::kStages + t); };
-    auto bar_dq_done = [&](int t) { return bar_base + 8u * (5 + 2 * L::kStages + t); };
+    auto bar_sdp_free = [&](int t) { return bar_base + 8u * (3 + 2 * L::kStages + t); };
+    auto bar_ds_full = [&](int t) { return bar_base + 8u * (5 + 2 * L::kStages + t); };
+    auto bar_dq_done = [&](int t) { return bar_base + 8u * (7 + 2 * L::kStages + t); };
+    auto bar_stagger = [&]() { return bar_base + 8u * (9 + 2 * L::kStages); };
     volatile uint32_t* misc = reinterpret_cast<volatile uint32_t*>(smem_gen + L::kMiscOff);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -223,16 +248,18 @@ attn_bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
 
     if (threadIdx.x == 0) {
         mbar_init(bar_qdo_full(), 1);
-        for (int s = 0; s < L::kStages; ++s) { mbar_init(bar_ring_full(s), 1); mbar_init(bar_ring_empty(s), 1); }
+        for (int s = 0; s < L::kStages; ++s) { mbar_init(bar_ring_full(s), 1); mbar_init(bar_ring_empty(s), 2); }
         for (int t = 0; t < 2; ++t) {
             mbar_init(bar_sdp_full(t), 1);
-            mbar_init(bar_ds_full(t), 4);          // one arrival per elementwise warp of the tile
+            mbar_init(bar_sdp_free(t), 8);         // one arrival per elementwise warp of the tile
+            mbar_init(bar_ds_full(t), 8);
             mbar_init(bar_dq_done(t), 1);
         }
+        mbar_init(bar_stagger(), 8);
         misc[1] = 0u;
         mbar_fence_init();
     }
-    if (warp == kMmaWarp) { tmem_alloc(smem_u32(const_cast<uint32_t*>(&misc[0])), kTmemCols); tmem_relinquish(); }
+    if (warp == kMmaWarp0) { tmem_alloc(smem_u32(const_cast<uint32_t*>(&misc[0])), kTmemCols); tmem_relinquish(); }
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
@@ -240,8 +267,10 @@ attn_bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
     const WaitCtx wc{&misc[1], a.status};
     auto slot_of = [&](int item) { return item % L::kStages; };
     auto phase_of = [&](int item) { return (uint32_t)((item / L::kStages) & 1); };
+    LTCA_TRACE_DECL(LTCA_TRACE_KERNEL == 1 && blockIdx.x == 0 && blockIdx.y == 5 && blockIdx.z == 0);
+    LTCA_TRACE_EVT(0x01);
 
-    if (warp >= 8) {
+    if (warp >= 16) {
       reg_dealloc<kCtrlRegs>();
       if (warp == kTmaWarp) {
         if (lane == 0 && n_max > 0) {
@@ -264,36 +293,37 @@ attn_bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 }
             }
         }
-      } else if (warp == kMmaWarp) {
+      } else if (warp == kMmaWarp0 || warp == kMmaWarp0 + 1) {
+        const int t = warp - kMmaWarp0;            // this thread issues the contractions of tile t
         if (lane == 0 && n_max > 0) {
+            const int n_t = n_steps[t];
             constexpr uint32_t idesc_s = make_idesc_bf16(kTile, kStep, 0, 0);
             constexpr uint32_t idesc_dq = make_idesc_bf16(kTile, kD, 0, 1);
+            const uint64_t q_desc = make_smem_desc_sw128(q_smem + t * kBigTile, 16, 1024);
+            const uint64_t do_desc = make_smem_desc_sw128(do_smem + t * kBigTile, 16, 1024);
+            const uint64_t ring_desc = make_smem_desc_sw128(ring_smem, 16, 1024);
+            const uint64_t ring_desc_mn = make_smem_desc_sw128(ring_smem, 8192, 1024);
+            const uint32_t tb = tmem_base + t * 192;
+            const uint32_t ds_hi = tmem_base + 384 + t * 32, ds_lo = tmem_base + 448 + t * 32;
             // S_t = Q_t K_j^T and dP_t = dO_t V_j^T
-            auto issue_sdp = [&](int t, int slot_k, int slot_v) {
-                const uint32_t tb = tmem_base + t * 192;
+            auto issue_sdp = [&](int slot_k, int slot_v) {
+                const uint64_t kd = ring_desc + (uint64_t)((slot_k * kSmallTile) >> 4);
+                const uint64_t vd = ring_desc + (uint64_t)((slot_v * kSmallTile) >> 4);
 #pragma unroll
-                for (int k = 0; k < kD / 16; ++k)
-                    mma_ss(tb, make_smem_desc_sw128(q_smem + t * kBigTile + k * 32, 16, 1024),
-                           make_smem_desc_sw128(ring_smem + slot_k * kSmallTile + k * 32, 16, 1024), idesc_s, k > 0);
+                for (int k = 0; k < kD / 16; ++k) mma_ss(tb, q_desc + 2 * k, kd + 2 * k, idesc_s, k > 0);
 #pragma unroll
-                for (int k = 0; k < kD / 16; ++k)
-                    mma_ss(tb + 64, make_smem_desc_sw128(do_smem + t * kBigTile + k * 32, 16, 1024),
-                           make_smem_desc_sw128(ring_smem + slot_v * kSmallTile + k * 32, 16, 1024), idesc_s, k > 0);
+                for (int k = 0; k < kD / 16; ++k) mma_ss(tb + 64, do_desc + 2 * k, vd + 2 * k, idesc_s, k > 0);
             };
             // dQ_t += dS_t K_j   (dS from tensor memory, K_j rows as the contraction index)
-            auto issue_dq = [&](int t, int slot_k, bool acc) {
-                const uint32_t tb = tmem_base + t * 192;
+            auto issue_dq = [&](int slot_k, bool acc) {
+                const uint64_t kd = ring_desc_mn + (uint64_t)((slot_k * kSmallTile) >> 4);
 #pragma unroll
                 for (int k = 0; k < kStep / 16; ++k)
-                    mma_ts(tb + 128, tb + k * 8,
-                           make_smem_desc_sw128(ring_smem + slot_k * kSmallTile + k * 2048, 8192, 1024), idesc_dq,
-                           (acc || k > 0) ? 1u : 0u);
+                    mma_ts(tb + 128, ds_hi + k * 8, kd + 128 * k, idesc_dq, (acc || k > 0) ? 1u : 0u);
                 if constexpr (kSplit) {
 #pragma unroll
                     for (int k = 0; k < kStep / 16; ++k)
-                        mma_ts(tb + 128, tb + 32 + k * 8,
-                               make_smem_desc_sw128(ring_smem + slot_k * kSmallTile + k * 2048, 8192, 1024),
-                               idesc_dq, 1u);
+                        mma_ts(tb + 128, ds_lo + k * 8, kd + 128 * k, idesc_dq, 1u);
                 }
             };
             bool ok = mbar_wait(bar_qdo_full(), 0, wc, 0x50);
@@ -301,50 +331,54 @@ attn_bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
             ok = ok && mbar_wait(bar_ring_full(slot_of(1)), phase_of(1), wc, 0x52);
             if (ok) {
                 tc_fence_after_sync();
-                for (int t = 0; t < 2; ++t)
-                    if (n_steps[t] > 0) { issue_sdp(t, slot_of(0), slot_of(1)); mma_commit(bar_sdp_full(t)); }
+                if (n_t > 0) { issue_sdp(slot_of(0), slot_of(1)); mma_commit(bar_sdp_full(t)); }
                 mma_commit(bar_ring_empty(slot_of(1)));            // V_0 is consumed
             }
             for (int j = 0; j < n_max && ok; ++j) {
                 const int item_k = 2 * j, item_k1 = 2 * j + 2, item_v1 = 2 * j + 3;
-                const bool have_next = (j + 1 < n_max);
-                if (have_next) {
-                    ok = ok && mbar_wait(bar_ring_full(slot_of(item_k1)), phase_of(item_k1), wc, 0x53);
+                if (j + 1 < n_max) {
+                    ok = mbar_wait(bar_ring_full(slot_of(item_k1)), phase_of(item_k1), wc, 0x53);
                     ok = ok && mbar_wait(bar_ring_full(slot_of(item_v1)), phase_of(item_v1), wc, 0x54);
-                }
-                if (!ok) break;
-                for (int t = 0; t < 2; ++t) {
-                    if (j < n_steps[t]) {
-                        ok = ok && mbar_wait(bar_ds_full(t), (uint32_t)(j & 1), wc, 0x55 + t);
+                    if (ok && j + 1 < n_t) {
+                        // S and dP of step j are in registers: compute step j + 1 now
+                        ok = mbar_wait(bar_sdp_free(t), (uint32_t)(j & 1), wc, 0x5a + t);
                         if (!ok) break;
                         tc_fence_after_sync();
-                        issue_dq(t, slot_of(item_k), j > 0);
-                        mma_commit(bar_dq_done(t));
-                    }
-                    if (j + 1 < n_steps[t]) {
-                        issue_sdp(t, slot_of(item_k1), slot_of(item_v1));
+                        LTCA_TRACE_EVT(0x20 + (j << 8));
+                        issue_sdp(slot_of(item_k1), slot_of(item_v1));
                         mma_commit(bar_sdp_full(t));
+                        LTCA_TRACE_EVT(0x21 + (j << 8));
                     }
+                    if (!ok) break;
+                    mma_commit(bar_ring_empty(slot_of(item_v1)));
                 }
-                if (!ok) break;
+                if (j < n_t) {
+                    ok = mbar_wait(bar_ds_full(t), (uint32_t)(j & 1), wc, 0x55 + t);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    LTCA_TRACE_EVT(0x22 + (j << 8));
+                    issue_dq(slot_of(item_k), j > 0);
+                    mma_commit(bar_dq_done(t));
+                    LTCA_TRACE_EVT(0x23 + (j << 8));
+                }
                 mma_commit(bar_ring_empty(slot_of(item_k)));
-                if (have_next) mma_commit(bar_ring_empty(slot_of(item_v1)));
             }
-            for (int t = 0; t < 2 && ok; ++t)
-                if (n_steps[t] > 0)
-                    ok = mbar_wait(bar_dq_done(t), (uint32_t)((n_steps[t] - 1) & 1), wc, 0x58 + t);
+            if (ok && n_t > 0) ok = mbar_wait(bar_dq_done(t), (uint32_t)((n_t - 1) & 1), wc, 0x58 + t);
         }
       }
     } else {
         reg_alloc<kMathRegs>();
-        const int t = warp >> 2, wq = warp & 3;
+        const int t = (warp >> 2) & 1, half = warp >> 3, wq = warp & 3;
         const int row = wq * 32 + lane;
         const int q0 = m_block * 2 * kTile + t * kTile;
         const int qi = q0 + row;
         const int n_t = n_steps[t];
         const uint32_t lane_base = (uint32_t)(wq * 32) << 16;
-        const uint32_t tS = tmem_base + lane_base + t * 192;
-        const uint32_t tDP = tS + 64, tDQ = tS + 128;
+        const uint32_t tS = tmem_base + lane_base + t * 192 + half * 32;
+        const uint32_t tDP = tS + 64;
+        const uint32_t tDQ = tmem_base + lane_base + t * 192 + 128 + half * 32;
+        const uint32_t tDS = tmem_base + lane_base + 384 + t * 32 + half * 16;
+        const uint32_t tDSlo = tDS + 64;
         const float c2 = a.scale_log2;
         const bool general = (a.keep_mask != nullptr) || (a.use_clamp != 0);
         const int64_t srow = ((int64_t)b * a.H + h) * a.Sq_pad + qi;      // qi < Sq_pad by construction
@@ -356,23 +390,33 @@ attn_bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
             ok = __all_sync(0xffffffffu, mbar_wait(bar_sdp_full(t), (uint32_t)(j & 1), wc, 0x60 + t));
             if (!ok) break;
             tc_fence_after_sync();
-            uint32_t s[64], dp[64];
-            tmem_ld32(tS, reinterpret_cast<uint32_t(&)[32]>(s[0]));
-            tmem_ld32(tS + 32, reinterpret_cast<uint32_t(&)[32]>(s[32]));
-            tmem_ld32(tDP, reinterpret_cast<uint32_t(&)[32]>(dp[0]));
-            tmem_ld32(tDP + 32, reinterpret_cast<uint32_t(&)[32]>(dp[32]));
+            LTCA_TRACE_EVT(0x10 + (j << 8));
+            uint32_t s[32], dp[32];
+            tmem_ld32(tS, s);
+            tmem_ld32(tDP, dp);
             tmem_wait_ld();
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_sdp_free(t));
+            LTCA_TRACE_EVT(0x11 + (j << 8));
+            // One-time delay of tile 1: from then on one tile's exponentials overlap the other
+            // tile's loads, stores and barrier traffic instead of all warps stalling together.
+            if (LTCA_BWD_STAGGER && t == 1 && j == 0 && n_steps[0] > 0) {
+                ok = __all_sync(0xffffffffu, mbar_wait(bar_stagger(), 0, wc, 0x66));
+                if (!ok) break;
+            }
             const int k0 = j * kStep;
             const bool edge = (k0 + kStep > kvlen) || (a.causal && (k0 + kStep - 1 > q0 + a.causal_off));
             // dS = P o (dP - delta), left in dp[]; the masked variant only runs on edge steps
             if (edge || general) {
                 int lim = kvlen;
                 if (a.causal) lim = min(lim, qi + a.causal_off + 1);
-                lim -= k0;
+                lim -= k0 + half * 32;
                 const float* mrow = nullptr;
-                if (a.keep_mask && qi < a.Sq) mrow = a.keep_mask + ((int64_t)b * a.Sq + qi) * a.Sk + k0;
+                if (a.keep_mask && qi < a.Sq)
+                    mrow = a.keep_mask + ((int64_t)b * a.Sq + qi) * a.Sk + k0 + half * 32;
 #pragma unroll
-                for (int c = 0; c < kStep; ++c) {
+                for (int c = 0; c < 32; ++c) {
                     const float sv = __uint_as_float(s[c]);
                     const float p = fast_exp2(fmaf(sv, c2, -lse2));
                     float d = p * (__uint_as_float(dp[c]) - dlt);
@@ -383,54 +427,51 @@ attn_bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 }
             } else {
 #pragma unroll
-                for (int c = 0; c < kStep; ++c) {
+                for (int c = 0; c < 32; ++c) {
                     const float p = fast_exp2(fmaf(__uint_as_float(s[c]), c2, -lse2));
                     dp[c] = __float_as_uint(p * (__uint_as_float(dp[c]) - dlt));
                 }
             }
-#pragma unroll
-            for (int half = 0; half < 2; ++half) {
-                uint32_t hi[16], lo[16];
-#pragma unroll
-                for (int cc = 0; cc < 32; cc += 2) {
-                    const float v0 = __uint_as_float(dp[half * 32 + cc]);
-                    const float v1 = __uint_as_float(dp[half * 32 + cc + 1]);
-                    const uint32_t h01 = pack_bf16x2(v0, v1);
-                    hi[cc / 2] = h01;
-                    if constexpr (kSplit)
-                        lo[cc / 2] = pack_bf16x2(v0 - __uint_as_float(h01 << 16),
-                                                 v1 - __uint_as_float(h01 & 0xffff0000u));
-                }
-                tmem_st16(tS + half * 16, hi);
-                if constexpr (kSplit) tmem_st16(tS + 32 + half * 16, lo);
+            uint32_t hi[16], lo[16];
+            pack32<kSplit>(dp, hi, lo);
+            if (LTCA_BWD_STAGGER && t == 0 && j == 0) {
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_stagger());
             }
+            LTCA_TRACE_EVT(0x12 + (j << 8));
+            if (j > 0) {
+                // the previous dS must have been consumed before it is overwritten
+                ok = __all_sync(0xffffffffu, mbar_wait(bar_dq_done(t), (uint32_t)((j - 1) & 1), wc, 0x64 + t));
+                if (!ok) break;
+            }
+            tmem_st16(tDS, hi);
+            if constexpr (kSplit) tmem_st16(tDSlo, lo);
             tmem_wait_st();
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_ds_full(t));
+            LTCA_TRACE_EVT(0x13 + (j << 8));
         }
         if (ok && q0 < a.Sq) {
             if (n_t > 0) {
                 ok = __all_sync(0xffffffffu, mbar_wait(bar_dq_done(t), (uint32_t)((n_t - 1) & 1), wc, 0x62 + t));
                 tc_fence_after_sync();
             }
-            OutT* drow = reinterpret_cast<OutT*>(a.dq) + b * a.dqs.batch + h * a.dqs.head + (int64_t)qi * a.dqs.seq;
+            OutT* drow = reinterpret_cast<OutT*>(a.dq) + b * a.dqs.batch + h * a.dqs.head +
+                         (int64_t)qi * a.dqs.seq + half * 32;
+            uint32_t o[32];
+            if (n_t > 0 && ok) { tmem_ld32(tDQ, o); tmem_wait_ld(); }
+            else {
 #pragma unroll
-            for (int c0 = 0; c0 < kD; c0 += 32) {
-                uint32_t o[32];
-                if (n_t > 0 && ok) { tmem_ld32(tDQ + c0, o); tmem_wait_ld(); }
-                else {
-#pragma unroll
-                    for (int c = 0; c < 32; ++c) o[c] = 0u;
-                }
-                if (qi < a.Sq) store_row32<OutT>(drow + c0, o, a.scale);
+                for (int c = 0; c < 32; ++c) o[c] = 0u;
             }
+            if (qi < a.Sq) store_row32<OutT>(drow, o, a.scale);
         }
     }
 
     tc_fence_before_sync();
     __syncthreads();
-    if (warp == kMmaWarp) {
+    if (warp == kMmaWarp0) {
         __syncwarp();
         if (misc[1]) __nanosleep(200000);
         tc_fence_after_sync();
@@ -440,10 +481,12 @@ attn_bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
 
 // ---------------------------------------------------------------------------------------------
 // 3. dK, dV (transposed problem: one KEY per tensor-memory lane)
-// tensor memory per tile t (base t*256): S^T [0,64) dP^T [64,128) dV [128,192) dK [192,256);
-// P^T (bf16) over S^T [0,32), dS^T (bf16) over dP^T [64,96)
+// tensor memory per tile t (base t*256): S^T [0,64) dP^T [64,128) dV [128,192) dK [192,256).
+// A key row belongs to two threads (warps w and w + 8); thread `half` owns query columns
+// [32*half, 32*half + 32) of S^T and dP^T and writes its P^T / dS^T back INSIDE those columns
+// (bf16 pairs in the first 16, the kSplit low-order term in the next 16), so neither thread
+// ever overwrites scores the other has not read yet.
 // ---------------------------------------------------------------------------------------------
-// kSplit as above: P^T hi/lo over S^T [0,32)/[32,64), dS^T hi/lo over dP^T [64,96)/[96,128).
 template <typename OutT, bool kSplit>
 __global__ void __launch_bounds__(kThreads, 1)
 attn_bwd_dkv_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
@@ -462,6 +505,7 @@ attn_bwd_dkv_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
     auto bar_sdp_full = [&](int t) { return bar_base + 8u * (1 + 2 * L::kStages + t); };
     auto bar_pds_full = [&](int t) { return bar_base + 8u * (3 + 2 * L::kStages + t); };
     auto bar_acc_done = [&](int t) { return bar_base + 8u * (5 + 2 * L::kStages + t); };
+    auto bar_stagger = [&]() { return bar_base + 8u * (7 + 2 * L::kStages); };
     volatile uint32_t* misc = reinterpret_cast<volatile uint32_t*>(smem_gen + L::kMiscOff);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -487,16 +531,17 @@ attn_bwd_dkv_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
 
     if (threadIdx.x == 0) {
         mbar_init(bar_kv_full(), 1);
-        for (int s = 0; s < L::kStages; ++s) { mbar_init(bar_ring_full(s), 1); mbar_init(bar_ring_empty(s), 1); }
+        for (int s = 0; s < L::kStages; ++s) { mbar_init(bar_ring_full(s), 1); mbar_init(bar_ring_empty(s), 2); }
         for (int t = 0; t < 2; ++t) {
             mbar_init(bar_sdp_full(t), 1);
-            mbar_init(bar_pds_full(t), 4);         // one arrival per elementwise warp of the tile
+            mbar_init(bar_pds_full(t), 8);         // one arrival per elementwise warp of the tile
             mbar_init(bar_acc_done(t), 1);
         }
+        mbar_init(bar_stagger(), 8);
         misc[1] = 0u;
         mbar_fence_init();
     }
-    if (warp == kMmaWarp) { tmem_alloc(smem_u32(const_cast<uint32_t*>(&misc[0])), kTmemCols); tmem_relinquish(); }
+    if (warp == kMmaWarp0) { tmem_alloc(smem_u32(const_cast<uint32_t*>(&misc[0])), kTmemCols); tmem_relinquish(); }
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
@@ -505,8 +550,10 @@ attn_bwd_dkv_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
     // ring items are numbered from the first streamed step of this CTA
     auto slot_of = [&](int j) { return (j - j_first) % L::kStages; };
     auto phase_of = [&](int j) { return (uint32_t)(((j - j_first) / L::kStages) & 1); };
+    LTCA_TRACE_DECL(LTCA_TRACE_KERNEL == 2 && blockIdx.x == 0 && blockIdx.y == 5 && blockIdx.z == 0);
+    LTCA_TRACE_EVT(0x01);
 
-    if (warp >= 8) {
+    if (warp >= 16) {
       reg_dealloc<kCtrlRegs>();
       if (warp == kTmaWarp) {
         if (lane == 0 && any_active) {
@@ -536,91 +583,94 @@ attn_bwd_dkv_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
                       "r"(bar_ring_full(slot_of(j))) : "memory");
             }
         }
-      } else if (warp == kMmaWarp) {
+      } else if (warp == kMmaWarp0 || warp == kMmaWarp0 + 1) {
+        const int t = warp - kMmaWarp0;            // this thread issues the contractions of tile t
         if (lane == 0 && any_active) {
             constexpr uint32_t idesc_s = make_idesc_bf16(kTile, kStep, 0, 0);
             constexpr uint32_t idesc_acc = make_idesc_bf16(kTile, kD, 0, 1);
+            const uint64_t k_desc = make_smem_desc_sw128(k_smem + t * kBigTile, 16, 1024);
+            const uint64_t v_desc = make_smem_desc_sw128(v_smem + t * kBigTile, 16, 1024);
+            const uint64_t ring_desc = make_smem_desc_sw128(ring_smem, 16, 1024);
+            const uint64_t ring_desc_mn = make_smem_desc_sw128(ring_smem, 8192, 1024);
+            const uint32_t tb = tmem_base + t * 256;
+            const bool act = active[t];
+            const int jb = j_begin[t];
             // S^T_t = K_t Q_j^T and dP^T_t = V_t dO_j^T
-            auto issue_sdp = [&](int t, int slot) {
-                const uint32_t tb = tmem_base + t * 256;
-                const uint32_t st = ring_smem + slot * L::kStageBytes;
+            auto issue_sdp = [&](int slot) {
+                const uint64_t qd = ring_desc + (uint64_t)((slot * L::kStageBytes) >> 4);
+                const uint64_t gd = qd + (uint64_t)(kSmallTile >> 4);
 #pragma unroll
-                for (int k = 0; k < kD / 16; ++k)
-                    mma_ss(tb, make_smem_desc_sw128(k_smem + t * kBigTile + k * 32, 16, 1024),
-                           make_smem_desc_sw128(st + k * 32, 16, 1024), idesc_s, k > 0);
+                for (int k = 0; k < kD / 16; ++k) mma_ss(tb, k_desc + 2 * k, qd + 2 * k, idesc_s, k > 0);
 #pragma unroll
-                for (int k = 0; k < kD / 16; ++k)
-                    mma_ss(tb + 64, make_smem_desc_sw128(v_smem + t * kBigTile + k * 32, 16, 1024),
-                           make_smem_desc_sw128(st + kSmallTile + k * 32, 16, 1024), idesc_s, k > 0);
+                for (int k = 0; k < kD / 16; ++k) mma_ss(tb + 64, v_desc + 2 * k, gd + 2 * k, idesc_s, k > 0);
             };
-            // dV_t += P^T_t dO_j and dK_t += dS^T_t Q_j   (query rows are the contraction index)
-            auto issue_acc = [&](int t, int slot, bool acc) {
-                const uint32_t tb = tmem_base + t * 256;
-                const uint32_t st = ring_smem + slot * L::kStageBytes;
+            // dV_t += P^T_t dO_j and dK_t += dS^T_t Q_j   (query rows are the contraction index);
+            // queries [0,32) sit in columns [0,16) of their region, queries [32,64) in [32,48)
+            auto issue_acc = [&](int slot, bool acc) {
+                const uint64_t qd = ring_desc_mn + (uint64_t)((slot * L::kStageBytes) >> 4);
+                const uint64_t gd = qd + (uint64_t)(kSmallTile >> 4);
 #pragma unroll
                 for (int k = 0; k < kStep / 16; ++k)
-                    mma_ts(tb + 128, tb + k * 8,
-                           make_smem_desc_sw128(st + kSmallTile + k * 2048, 8192, 1024), idesc_acc,
+                    mma_ts(tb + 128, tb + (k / 2) * 32 + (k % 2) * 8, gd + 128 * k, idesc_acc,
                            (acc || k > 0) ? 1u : 0u);
 #pragma unroll
                 for (int k = 0; k < kStep / 16; ++k)
-                    mma_ts(tb + 192, tb + 64 + k * 8, make_smem_desc_sw128(st + k * 2048, 8192, 1024),
-                           idesc_acc, (acc || k > 0) ? 1u : 0u);
+                    mma_ts(tb + 192, tb + 64 + (k / 2) * 32 + (k % 2) * 8, qd + 128 * k, idesc_acc,
+                           (acc || k > 0) ? 1u : 0u);
                 if constexpr (kSplit) {
 #pragma unroll
                     for (int k = 0; k < kStep / 16; ++k)
-                        mma_ts(tb + 128, tb + 32 + k * 8,
-                               make_smem_desc_sw128(st + kSmallTile + k * 2048, 8192, 1024), idesc_acc, 1u);
+                        mma_ts(tb + 128, tb + 16 + (k / 2) * 32 + (k % 2) * 8, gd + 128 * k, idesc_acc, 1u);
 #pragma unroll
                     for (int k = 0; k < kStep / 16; ++k)
-                        mma_ts(tb + 192, tb + 96 + k * 8, make_smem_desc_sw128(st + k * 2048, 8192, 1024),
-                               idesc_acc, 1u);
+                        mma_ts(tb + 192, tb + 80 + (k / 2) * 32 + (k % 2) * 8, qd + 128 * k, idesc_acc, 1u);
                 }
             };
             bool ok = mbar_wait(bar_kv_full(), 0, wc, 0x80);
             if (ok && j_first < n_q) {
                 ok = mbar_wait(bar_ring_full(slot_of(j_first)), phase_of(j_first), wc, 0x81);
-                if (ok) {
+                if (ok && act && jb == j_first) {
                     tc_fence_after_sync();
-                    for (int t = 0; t < 2; ++t)
-                        if (active[t] && j_begin[t] == j_first) { issue_sdp(t, slot_of(j_first)); mma_commit(bar_sdp_full(t)); }
+                    issue_sdp(slot_of(j_first));
+                    mma_commit(bar_sdp_full(t));
                 }
             }
             for (int j = j_first; j < n_q && ok; ++j) {
                 const bool have_next = (j + 1 < n_q);
                 if (have_next) ok = mbar_wait(bar_ring_full(slot_of(j + 1)), phase_of(j + 1), wc, 0x82);
                 if (!ok) break;
-                for (int t = 0; t < 2; ++t) {
-                    if (!active[t]) continue;
-                    if (j >= j_begin[t]) {
-                        ok = ok && mbar_wait(bar_pds_full(t), (uint32_t)((j - j_begin[t]) & 1), wc, 0x83 + t);
+                if (act) {
+                    if (j >= jb) {
+                        ok = mbar_wait(bar_pds_full(t), (uint32_t)((j - jb) & 1), wc, 0x83 + t);
                         if (!ok) break;
                         tc_fence_after_sync();
-                        issue_acc(t, slot_of(j), j > j_begin[t]);
+                        LTCA_TRACE_EVT(0x22 + (j << 8));
+                        issue_acc(slot_of(j), j > jb);
                         mma_commit(bar_acc_done(t));
+                        LTCA_TRACE_EVT(0x23 + (j << 8));
                     }
-                    if (have_next && j + 1 >= j_begin[t]) {
-                        issue_sdp(t, slot_of(j + 1));
+                    if (have_next && j + 1 >= jb) {
+                        issue_sdp(slot_of(j + 1));
                         mma_commit(bar_sdp_full(t));
+                        LTCA_TRACE_EVT(0x21 + (j << 8));
                     }
                 }
-                if (!ok) break;
                 mma_commit(bar_ring_empty(slot_of(j)));
             }
-            for (int t = 0; t < 2 && ok; ++t)
-                if (active[t])
-                    ok = mbar_wait(bar_acc_done(t), (uint32_t)((n_q - 1 - j_begin[t]) & 1), wc, 0x88 + t);
+            if (ok && act) ok = mbar_wait(bar_acc_done(t), (uint32_t)((n_q - 1 - jb) & 1), wc, 0x88 + t);
         }
       }
     } else {
         reg_alloc<kMathRegs>();
-        const int t = warp >> 2, wq = warp & 3;
+        const int t = (warp >> 2) & 1, half = warp >> 3, wq = warp & 3;
         const int row = wq * 32 + lane;
         const int k0 = n_block * 2 * kTile + t * kTile;
         const int kj = k0 + row;                                   // this thread's key
         const uint32_t lane_base = (uint32_t)(wq * 32) << 16;
-        const uint32_t tS = tmem_base + lane_base + t * 256;
-        const uint32_t tDP = tS + 64, tDV = tS + 128, tDK = tS + 192;
+        const uint32_t tS = tmem_base + lane_base + t * 256 + half * 32;
+        const uint32_t tDP = tS + 64;
+        const uint32_t tDV = tmem_base + lane_base + t * 256 + 128 + half * 32;
+        const uint32_t tDK = tDV + 64;
         const float c2 = a.scale_log2;
         const bool general = (a.keep_mask != nullptr) || (a.use_clamp != 0);
         const bool key_live = kj < kvlen;
@@ -632,23 +682,28 @@ attn_bwd_dkv_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 ok = __all_sync(0xffffffffu, mbar_wait(bar_sdp_full(t), (uint32_t)(it & 1), wc, 0x90 + t));
                 if (!ok) break;
                 tc_fence_after_sync();
-                uint32_t s[64], dp[64];
-                tmem_ld32(tS, reinterpret_cast<uint32_t(&)[32]>(s[0]));
-                tmem_ld32(tS + 32, reinterpret_cast<uint32_t(&)[32]>(s[32]));
-                tmem_ld32(tDP, reinterpret_cast<uint32_t(&)[32]>(dp[0]));
-                tmem_ld32(tDP + 32, reinterpret_cast<uint32_t(&)[32]>(dp[32]));
+                LTCA_TRACE_EVT(0x10 + (j << 8));
+                uint32_t s[32], dp[32];
+                tmem_ld32(tS, s);
+                tmem_ld32(tDP, dp);
                 tmem_wait_ld();
+                LTCA_TRACE_EVT(0x11 + (j << 8));
+                if (LTCA_BWD_STAGGER && t == 1 && it == 0 && active[0] && j_begin[0] <= j_begin[1]) {
+                    ok = __all_sync(0xffffffffu, mbar_wait(bar_stagger(), 0, wc, 0x96));
+                    if (!ok) break;
+                }
+                // lse2 and delta of this thread's 32 query columns (broadcast reads: every lane
+                // of the warp reads the same address)
                 const float4* st4 = reinterpret_cast<const float4*>(
-                    smem_gen + L::kRingOff + slot_of(j) * L::kStageBytes + 2 * kSmallTile);
-                const int q0 = j * kStep;
+                    smem_gen + L::kRingOff + slot_of(j) * L::kStageBytes + 2 * kSmallTile) + half * 8;
+                const int q0 = j * kStep + half * 32;
                 // a query column c is hidden from this key when q0 + c + off < kj
                 const bool edge = !key_live || (k0 + kTile > kvlen) ||
-                                  (a.causal && (q0 + a.causal_off < k0 + kTile - 1));
-                // P^T into s[], dS^T = P^T o (dP^T - delta) into dp[]; lse2 and delta of the 64 query
-                // columns are broadcast reads from the stage (every thread reads the same address)
+                                  (a.causal && (j * kStep + a.causal_off < k0 + kTile - 1));
+                // P^T into s[], dS^T = P^T o (dP^T - delta) into dp[]
                 if (edge || general) {
 #pragma unroll
-                    for (int c4 = 0; c4 < kStep / 4; ++c4) {
+                    for (int c4 = 0; c4 < 8; ++c4) {
                         const float4 l4 = st4[c4];
                         const float4 d4 = st4[16 + c4];
                         const float ls[4] = {l4.x, l4.y, l4.z, l4.w};
@@ -672,7 +727,7 @@ attn_bwd_dkv_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
                     }
                 } else {
 #pragma unroll
-                    for (int c4 = 0; c4 < kStep / 4; ++c4) {
+                    for (int c4 = 0; c4 < 8; ++c4) {
                         const float4 l4 = st4[c4];
                         const float4 d4 = st4[16 + c4];
                         const float ls[4] = {l4.x, l4.y, l4.z, l4.w};
@@ -686,36 +741,25 @@ attn_bwd_dkv_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
                         }
                     }
                 }
-#pragma unroll
-                for (int half = 0; half < 2; ++half) {
-                    uint32_t pt[16], dst[16], ptl[16], dstl[16];
-#pragma unroll
-                    for (int cc = 0; cc < 32; cc += 2) {
-                        const int c = half * 32 + cc;
-                        const float p0 = __uint_as_float(s[c]), p1 = __uint_as_float(s[c + 1]);
-                        const float d0 = __uint_as_float(dp[c]), d1 = __uint_as_float(dp[c + 1]);
-                        const uint32_t ph = pack_bf16x2(p0, p1);
-                        const uint32_t dh = pack_bf16x2(d0, d1);
-                        pt[cc / 2] = ph;
-                        dst[cc / 2] = dh;
-                        if constexpr (kSplit) {
-                            ptl[cc / 2] = pack_bf16x2(p0 - __uint_as_float(ph << 16),
-                                                      p1 - __uint_as_float(ph & 0xffff0000u));
-                            dstl[cc / 2] = pack_bf16x2(d0 - __uint_as_float(dh << 16),
-                                                       d1 - __uint_as_float(dh & 0xffff0000u));
-                        }
-                    }
-                    tmem_st16(tS + half * 16, pt);
-                    tmem_st16(tDP + half * 16, dst);
-                    if constexpr (kSplit) {
-                        tmem_st16(tS + 32 + half * 16, ptl);
-                        tmem_st16(tDP + 32 + half * 16, dstl);
-                    }
+                uint32_t pt[16], ptl[16], dst[16], dstl[16];
+                pack32<kSplit>(s, pt, ptl);
+                pack32<kSplit>(dp, dst, dstl);
+                if (LTCA_BWD_STAGGER && t == 0 && it == 0) {
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar_stagger());
+                }
+                LTCA_TRACE_EVT(0x12 + (j << 8));
+                tmem_st16(tS, pt);
+                tmem_st16(tDP, dst);
+                if constexpr (kSplit) {
+                    tmem_st16(tS + 16, ptl);
+                    tmem_st16(tDP + 16, dstl);
                 }
                 tmem_wait_st();
                 tc_fence_before_sync();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar_pds_full(t));
+                LTCA_TRACE_EVT(0x13 + (j << 8));
             }
         }
         // epilogue: dV and scale * dK (zeros for tiles that no query can see)
@@ -725,32 +769,43 @@ attn_bwd_dkv_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
                                 mbar_wait(bar_acc_done(t), (uint32_t)((n_q - 1 - j_begin[t]) & 1), wc, 0x92 + t));
                 tc_fence_after_sync();
             }
-            OutT* dkrow = reinterpret_cast<OutT*>(a.dk) + b * a.dks.batch + h * a.dks.head + (int64_t)kj * a.dks.seq;
-            OutT* dvrow = reinterpret_cast<OutT*>(a.dv) + b * a.dvs.batch + h * a.dvs.head + (int64_t)kj * a.dvs.seq;
+            OutT* dkrow = reinterpret_cast<OutT*>(a.dk) + b * a.dks.batch + h * a.dks.head +
+                          (int64_t)kj * a.dks.seq + half * 32;
+            OutT* dvrow = reinterpret_cast<OutT*>(a.dv) + b * a.dvs.batch + h * a.dvs.head +
+                          (int64_t)kj * a.dvs.seq + half * 32;
+            uint32_t o[32];
+            if (active[t] && ok) { tmem_ld32(tDV, o); tmem_wait_ld(); }
+            else {
 #pragma unroll
-            for (int c0 = 0; c0 < kD; c0 += 32) {
-                uint32_t o[32];
-                if (active[t] && ok) { tmem_ld32(tDV + c0, o); tmem_wait_ld(); }
-                else {
-#pragma unroll
-                    for (int c = 0; c < 32; ++c) o[c] = 0u;
-                }
-                if (kj < a.Sk) store_row32<OutT>(dvrow + c0, o, 1.0f);
-                if (active[t] && ok) { tmem_ld32(tDK + c0, o); tmem_wait_ld(); }
-                if (kj < a.Sk) store_row32<OutT>(dkrow + c0, o, a.scale);
+                for (int c = 0; c < 32; ++c) o[c] = 0u;
             }
+            if (kj < a.Sk) store_row32<OutT>(dvrow, o, 1.0f);
+            if (active[t] && ok) { tmem_ld32(tDK, o); tmem_wait_ld(); }
+            if (kj < a.Sk) store_row32<OutT>(dkrow, o, a.scale);
         }
     }
 
     tc_fence_before_sync();
     __syncthreads();
-    if (warp == kMmaWarp) {
+    if (warp == kMmaWarp0) {
         __syncwarp();
         if (misc[1]) __nanosleep(200000);
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, kTmemCols);
     }
 }
+
+}  // namespace
+
+#ifdef LTCA_TRACE
+extern "C" int ltca_trace_read_bwd(unsigned long long* events, unsigned int* counts) {
+    if (cudaMemcpyFromSymbol(events, g_trace, sizeof(g_trace)) != cudaSuccess) return -1;
+    if (cudaMemcpyFromSymbol(counts, g_trace_count, sizeof(g_trace_count)) != cudaSuccess) return -1;
+    return 0;
+}
+#endif
+
+namespace {
 
 size_t stats_bytes(const ltca_attn_params* p) {
     const size_t sq_pad = align_up((size_t)p->Sq, 256);

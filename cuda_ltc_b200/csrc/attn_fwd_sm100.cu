@@ -9,11 +9,13 @@
 // Shape of the kernel
 //   - one CTA per (256 query rows, head, batch): two 128-row query tiles share every K/V tile
 //     that TMA brings in, which halves the L2 -> shared traffic per FLOP;
-//   - warps 0-3 / 4-7: softmax of query tile 0 / 1 (one query row per thread, so row maxima
-//     and sums need no shuffles), also rescale O when the running maximum moved and write the
-//     final O and lse;  warp 8: issues every tcgen05.mma;  warp 9: TMA producer.  The softmax
-//     warps take the registers the other warps give up (setmaxnreg), so a whole score row
-//     stays in registers;
+//   - 16 softmax warps: a query row belongs to TWO threads, each owning half of the step's key
+//     columns (warps w and w + 8 read the same 32 tensor-memory lanes), so that every scheduler
+//     holds four softmax warps and the special-function unit stays busy while other warps load,
+//     reduce or wait.  The two threads of a row agree on the row maximum through shared memory;
+//     row sums stay private until the epilogue.  Warps 0-3 / 8-11: tile 0, 4-7 / 12-15: tile 1;
+//   - warps 16 / 17 issue the tcgen05.mma of tile 0 / 1 (one thread each), warp 18 is the TMA
+//     producer.  The control warps give registers up for the softmax warps (setmaxnreg);
 //   - S = Q K^T accumulates in tensor memory; the softmax warps read it with tcgen05.ld and
 //     release it at once, so the next step's S is computed while this step's exponentials
 //     run; P goes back to its OWN tensor-memory columns as packed bf16 (tcgen05.st) and the
@@ -27,15 +29,43 @@
 //   S0 S1 (kBN each) | O0 O1 (D each) | P0 P1 (kBN/2 each) | split-P only: Plo0 Plo1 (kBN/2 each)
 #include "host_common.h"
 #include "sm100_ptx.cuh"
+#include "trace.cuh"
+
+#ifndef LTCA_FWD4
+#define LTCA_FWD4 1
+#endif
+#ifndef LTCA_PAIR_NAMED_BAR
+#define LTCA_PAIR_NAMED_BAR 0
+#endif
+#ifndef LTCA_FWD_ROWSPLIT
+#define LTCA_FWD_ROWSPLIT 2
+#endif
+// 0: tiles run freely, 1: the tiles take strict turns at the exponentials, 2: tile 1 is delayed once
+#ifndef LTCA_FWD_PINGPONG
+#define LTCA_FWD_PINGPONG 2
+#endif
+#ifndef LTCA_FWD_EARLY_TURN
+#define LTCA_FWD_EARLY_TURN 0
+#endif
 
 namespace ltca {
 
 namespace {
 
 constexpr int kBlockM = 128;        // query rows per tile
-constexpr int kFwdThreads = 384;
-constexpr int kMmaWarp = 8;
-constexpr int kTmaWarp = 9;
+// kRowSplit threads share one query row (each owns 1/kRowSplit of the step's key columns):
+//   1: 8 softmax warps, whole rows in registers, no exchange between threads;
+//   2: 16 softmax warps, four per scheduler, row maxima exchanged through shared memory.
+constexpr int kRowSplit = LTCA_FWD_ROWSPLIT;
+constexpr int kMathWarps = 8 * kRowSplit;
+constexpr int kFwdThreads = 32 * (kMathWarps + 4);   // + one warpgroup of control warps
+constexpr int kMmaWarp0 = kMathWarps;                // issues the contractions of tile 0 (tile 1: the next warp)
+constexpr int kTmaWarp = kMathWarps + 2;
+constexpr int kLaunchRegs = kRowSplit == 1 ? 168 : 96;   // registers per thread at launch (65536 / threads, rounded down to 8)
+constexpr int kCtrlRegs = kRowSplit == 1 ? 72 : 32;
+constexpr int kMathRegs = kRowSplit == 1 ? 216 : 112;
+// setmaxnreg can only redistribute what the CTA was launched with; asking for more never returns
+static_assert(32 * kMathWarps * kMathRegs + 128 * kCtrlRegs <= kFwdThreads * kLaunchRegs, "register budget");
 constexpr uint32_t kTmemCols = 512;
 
 struct FwdArgs {
@@ -69,9 +99,11 @@ struct FwdCfg {
     // shared memory
     static constexpr int kQOff = 0;
     static constexpr int kRingOff = 2 * kQTileBytes;
-    static constexpr int kBarOff = kRingOff + kStages * kKvTileBytes;
-    // barriers: q_full, kv_full[kStages], kv_empty[kStages], s_full[2], s_free[2], p_full[2], o_done[2]
-    static constexpr int kNumBars = 1 + 2 * kStages + 8;
+    static constexpr int kXchgOff = kRingOff + kStages * kKvTileBytes;   // float [3][2 tiles][2 halves][128]
+    static constexpr int kBarOff = kXchgOff + 3 * 2 * 2 * kBlockM * 4;
+    // barriers: q_full, kv_full[kStages], kv_empty[kStages], s_full[2], s_free[2], p_full[2], o_done[2],
+    // pair[8] (one per pair of warps that share rows), turn[2]
+    static constexpr int kNumBars = 1 + 2 * kStages + 8 + 8 + 2;
     static constexpr int kMiscOff = kBarOff + kNumBars * 8;        // tmem base, abort flag
     static constexpr int kBytes = kMiscOff + 16;
     static constexpr int kDynBytes = kBytes + 1024;                // room to align to 1024 B
@@ -89,6 +121,8 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
                       const __grid_constant__ CUtensorMap tmap_v, const FwdArgs a) {
     using L = FwdCfg<D, kSplitP>;
     constexpr int kBN = L::kBN;
+    constexpr int kH = kBN / kRowSplit;  // key columns per thread and step
+    constexpr int kDH = D / kRowSplit;   // output columns per thread
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -103,6 +137,9 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
     auto bar_s_free = [&](int t) { return bar_base + 8u * (3 + 2 * L::kStages + t); };
     auto bar_p_full = [&](int t) { return bar_base + 8u * (5 + 2 * L::kStages + t); };
     auto bar_o_done = [&](int t) { return bar_base + 8u * (7 + 2 * L::kStages + t); };
+    auto bar_pair = [&](int t, int wq) { return bar_base + 8u * (9 + 2 * L::kStages + t * 4 + wq); };
+    auto bar_turn = [&](int t) { return bar_base + 8u * (17 + 2 * L::kStages + t); };
+    float* xchg = reinterpret_cast<float*>(smem_gen + L::kXchgOff);
     volatile uint32_t* misc = reinterpret_cast<volatile uint32_t*>(smem_gen + L::kMiscOff);
     // misc[0] = tensor-memory base address, misc[1] = abort flag
 
@@ -131,18 +168,20 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
         mbar_init(bar_q_full(), 1);
         for (int s = 0; s < L::kStages; ++s) {
             mbar_init(bar_kv_full(s), 1);
-            mbar_init(bar_kv_empty(s), 1);
+            mbar_init(bar_kv_empty(s), 2);     // both MMA issuers release a slot
         }
         for (int t = 0; t < 2; ++t) {
             mbar_init(bar_s_full(t), 1);
-            mbar_init(bar_s_free(t), 4);       // one arrival per softmax warp of the tile
-            mbar_init(bar_p_full(t), 4);
+            mbar_init(bar_s_free(t), 4 * kRowSplit);   // one arrival per softmax warp of the tile
+            mbar_init(bar_p_full(t), 4 * kRowSplit);
             mbar_init(bar_o_done(t), 1);
+            for (int wq = 0; wq < 4; ++wq) mbar_init(bar_pair(t, wq), 2);
+            mbar_init(bar_turn(t), 4 * kRowSplit);
         }
         misc[1] = 0u;
         mbar_fence_init();
     }
-    if (warp == kMmaWarp) {
+    if (warp == kMmaWarp0) {
         tmem_alloc(smem_u32(const_cast<uint32_t*>(&misc[0])), kTmemCols);
         tmem_relinquish();
     }
@@ -151,9 +190,13 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
     tc_fence_after_sync();
     const uint32_t tmem_base = misc[0];
     const WaitCtx wc{&misc[1], a.status};
+    LTCA_TRACE_DECL(blockIdx.x == 0 && blockIdx.y == 5 && blockIdx.z == 0);
+    LTCA_TRACE_EVT(0x01);
 
-    if (warp >= 8) {
-        reg_dealloc<64>();
+    if (warp >= kMathWarps) {
+        reg_dealloc<kCtrlRegs>();
+        auto slot_of = [&](int item) { return item % L::kStages; };
+        auto phase_of = [&](int item) { return (uint32_t)((item / L::kStages) & 1); };
         if (warp == kTmaWarp) {
             // ------------------------------ TMA producer --------------------------------------
             if (lane == 0 && n_max > 0) {
@@ -170,9 +213,8 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
 #pragma unroll
                     for (int which = 0; which < 2; ++which) {     // 0: K_j, 1: V_j
                         const int item = 2 * j + which;
-                        const int slot = item % L::kStages;
-                        const uint32_t phase = (item / L::kStages) & 1;
-                        ok = ok && mbar_wait(bar_kv_empty(slot), phase ^ 1u, wc, 0x10 + which);
+                        const int slot = slot_of(item);
+                        ok = ok && mbar_wait(bar_kv_empty(slot), phase_of(item) ^ 1u, wc, 0x10 + which);
                         if (!ok) break;
                         mbar_arrive_expect_tx(bar_kv_full(slot), (uint32_t)L::kKvTileBytes);
                         for (int kb = 0; kb < L::kDimBlocks; ++kb)
@@ -182,49 +224,51 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
                     }
                 }
             }
-        } else if (warp == kMmaWarp) {
-            // ------------------------------ MMA issuer ----------------------------------------
+        } else if (warp == kMmaWarp0 || warp == kMmaWarp0 + 1) {
+            // ------------------------------ MMA issuer of tile t ------------------------------
+            const int t = warp - kMmaWarp0;
             if (lane == 0 && n_max > 0) {
+                const int n_t = n_tiles[t];
                 constexpr uint32_t idesc_qk = make_idesc_bf16(kBlockM, kBN, 0, 0);
                 constexpr uint32_t idesc_pv = make_idesc_bf16(kBlockM, D, 0, 1);
-                auto issue_qk = [&](int t, int slot) {
-                    const uint32_t qa = q_smem + t * L::kQTileBytes;
-                    const uint32_t ka = ring_smem + slot * L::kKvTileBytes;
+                // descriptors are built once; a byte offset inside shared memory adds offset >> 4
+                const uint64_t q_desc = make_smem_desc_sw128(q_smem + t * L::kQTileBytes, 16, 1024);
+                const uint64_t k_desc = make_smem_desc_sw128(ring_smem, 16, 1024);
+                const uint64_t v_desc = make_smem_desc_sw128(ring_smem, kBN * 128, 1024);
+                const uint32_t s_tmem = tmem_base + L::kColS + t * kBN;
+                const uint32_t o_tmem = tmem_base + L::kColO + t * D;
+                const uint32_t p_tmem = tmem_base + L::kColP + t * (kBN / 2);
+                const uint32_t plo_tmem = tmem_base + L::kColPlo + t * (kBN / 2);
+                auto issue_qk = [&](int slot) {
+                    const uint64_t kd = k_desc + (uint64_t)((slot * L::kKvTileBytes) >> 4);
 #pragma unroll
                     for (int k = 0; k < D / 16; ++k) {
                         const uint32_t qoff = (k / 4) * (kBlockM * 128) + (k % 4) * 32;
                         const uint32_t koff = (k / 4) * (kBN * 128) + (k % 4) * 32;
-                        mma_ss(tmem_base + L::kColS + t * kBN, make_smem_desc_sw128(qa + qoff, 16, 1024),
-                               make_smem_desc_sw128(ka + koff, 16, 1024), idesc_qk, k > 0 ? 1u : 0u);
+                        mma_ss(s_tmem, q_desc + (qoff >> 4), kd + (koff >> 4), idesc_qk, k > 0 ? 1u : 0u);
                     }
                 };
-                auto issue_pv = [&](int t, int slot, bool acc) {
-                    const uint32_t va = ring_smem + slot * L::kKvTileBytes;
+                auto issue_pv = [&](int slot, bool acc) {
+                    const uint64_t vd = v_desc + (uint64_t)((slot * L::kKvTileBytes) >> 4);
 #pragma unroll
                     for (int k = 0; k < kBN / 16; ++k)
-                        mma_ts(tmem_base + L::kColO + t * D, tmem_base + L::kColP + t * (kBN / 2) + k * 8,
-                               make_smem_desc_sw128(va + k * 2048, kBN * 128, 1024), idesc_pv,
+                        mma_ts(o_tmem, p_tmem + k * 8, vd + ((k * 2048) >> 4), idesc_pv,
                                (acc || k > 0) ? 1u : 0u);
                     if constexpr (kSplitP) {
 #pragma unroll
                         for (int k = 0; k < kBN / 16; ++k)
-                            mma_ts(tmem_base + L::kColO + t * D,
-                                   tmem_base + L::kColPlo + t * (kBN / 2) + k * 8,
-                                   make_smem_desc_sw128(va + k * 2048, kBN * 128, 1024), idesc_pv, 1u);
+                            mma_ts(o_tmem, plo_tmem + k * 8, vd + ((k * 2048) >> 4), idesc_pv, 1u);
                     }
                 };
-                auto slot_of = [&](int item) { return item % L::kStages; };
-                auto phase_of = [&](int item) { return (uint32_t)((item / L::kStages) & 1); };
 
                 bool ok = mbar_wait(bar_q_full(), 0, wc, 0x20);
                 ok = ok && mbar_wait(bar_kv_full(slot_of(0)), phase_of(0), wc, 0x21);
                 if (ok) {
                     tc_fence_after_sync();
-                    for (int t = 0; t < 2; ++t)
-                        if (n_tiles[t] > 0) {
-                            issue_qk(t, slot_of(0));
-                            mma_commit(bar_s_full(t));
-                        }
+                    if (n_t > 0) {
+                        issue_qk(slot_of(0));
+                        mma_commit(bar_s_full(t));
+                    }
                     mma_commit(bar_kv_empty(slot_of(0)));
                 }
                 for (int j = 0; j < n_max && ok; ++j) {
@@ -232,53 +276,55 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
                     // S of step j+1 as soon as the softmax warps have taken S of step j
                     if (j + 1 < n_max) {
                         ok = mbar_wait(bar_kv_full(slot_of(item_k)), phase_of(item_k), wc, 0x23);
-                        for (int t = 0; t < 2 && ok; ++t) {
-                            if (j + 1 < n_tiles[t]) {
-                                ok = mbar_wait(bar_s_free(t), (uint32_t)(j & 1), wc, 0x26 + t);
-                                if (!ok) break;
-                                tc_fence_after_sync();
-                                issue_qk(t, slot_of(item_k));
-                                mma_commit(bar_s_full(t));
-                            }
+                        if (ok && j + 1 < n_t) {
+                            ok = mbar_wait(bar_s_free(t), (uint32_t)(j & 1), wc, 0x26 + t);
+                            if (!ok) break;
+                            tc_fence_after_sync();
+                            LTCA_TRACE_EVT(0x20 + (j << 8));
+                            issue_qk(slot_of(item_k));
+                            mma_commit(bar_s_full(t));
+                            LTCA_TRACE_EVT(0x22 + (j << 8));
                         }
                         if (!ok) break;
                         mma_commit(bar_kv_empty(slot_of(item_k)));
                     }
                     ok = mbar_wait(bar_kv_full(slot_of(item_v)), phase_of(item_v), wc, 0x22);
-                    for (int t = 0; t < 2 && ok; ++t) {
-                        if (j < n_tiles[t]) {
-                            ok = mbar_wait(bar_p_full(t), (uint32_t)(j & 1), wc, 0x24 + t);
-                            if (!ok) break;
-                            tc_fence_after_sync();
-                            issue_pv(t, slot_of(item_v), j > 0);
-                            mma_commit(bar_o_done(t));
-                        }
+                    if (ok && j < n_t) {
+                        ok = mbar_wait(bar_p_full(t), (uint32_t)(j & 1), wc, 0x24 + t);
+                        if (!ok) break;
+                        tc_fence_after_sync();
+                        LTCA_TRACE_EVT(0x24 + (j << 8));
+                        issue_pv(slot_of(item_v), j > 0);
+                        mma_commit(bar_o_done(t));
+                        LTCA_TRACE_EVT(0x26 + (j << 8));
                     }
                     if (!ok) break;
                     mma_commit(bar_kv_empty(slot_of(item_v)));
                 }
                 // everything this thread issued has to be complete before tensor memory is released
-                for (int t = 0; t < 2 && ok; ++t)
-                    if (n_tiles[t] > 0)
-                        ok = mbar_wait(bar_o_done(t), (uint32_t)((n_tiles[t] - 1) & 1), wc, 0x28 + t);
+                if (ok && n_t > 0) ok = mbar_wait(bar_o_done(t), (uint32_t)((n_t - 1) & 1), wc, 0x28 + t);
             }
         }
     } else {
         // ------------------------------ softmax / correction / epilogue ------------------------
-        reg_alloc<216>();
-        const int t = warp >> 2;
+        reg_alloc<kMathRegs>();
+        const int t = (warp >> 2) & 1;
+        const int half = warp >> 3;          // which part of the key columns (and of the output columns)
         const int wq = warp & 3;
         const int row = wq * 32 + lane;
         const int q0 = m_block * 2 * kBlockM + t * kBlockM;
         const int qi = q0 + row;
         const int n_t = n_tiles[t];
         const uint32_t lane_base = (uint32_t)(wq * 32) << 16;
-        const uint32_t tS = tmem_base + lane_base + L::kColS + t * kBN;
-        const uint32_t tO = tmem_base + lane_base + L::kColO + t * D;
-        const uint32_t tP = tmem_base + lane_base + L::kColP + t * (kBN / 2);
-        const uint32_t tPlo = tmem_base + lane_base + L::kColPlo + t * (kBN / 2);
+        const uint32_t tS = tmem_base + lane_base + L::kColS + t * kBN + half * kH;
+        const uint32_t tO = tmem_base + lane_base + L::kColO + t * D + half * kDH;
+        const uint32_t tP = tmem_base + lane_base + L::kColP + t * (kBN / 2) + half * (kH / 2);
+        const uint32_t tPlo = tmem_base + lane_base + L::kColPlo + t * (kBN / 2) + half * (kH / 2);
         const float c2 = a.scale_log2;
         const bool general = (a.keep_mask != nullptr) || (a.use_clamp != 0);
+        // exchange slots: [buffer][tile][half][row]
+        auto xslot = [&](int buf, int hf) { return xchg + ((buf * 2 + t) * 2 + hf) * kBlockM + row; };
+        uint32_t pair_phase = 0;
 
         float m_run = neg_inf();
         float l_run = 0.f;
@@ -287,27 +333,29 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
             ok = __all_sync(0xffffffffu, mbar_wait(bar_s_full(t), (uint32_t)(j & 1), wc, 0x30 + t));
             if (!ok) break;
             tc_fence_after_sync();
-            uint32_t su[kBN];
+            LTCA_TRACE_EVT(0x10 + (j << 8));
+            uint32_t su[kH];
 #pragma unroll
-            for (int c0 = 0; c0 < kBN; c0 += 32)
+            for (int c0 = 0; c0 < kH; c0 += 32)
                 tmem_ld32(tS + c0, reinterpret_cast<uint32_t(&)[32]>(su[c0]));
             tmem_wait_ld();
             // S is in registers: the next step's Q K^T may overwrite it
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_s_free(t));
+            LTCA_TRACE_EVT(0x11 + (j << 8));
 #define S_(c) __uint_as_float(su[(c)])
             const int k0 = j * kBN;
             const bool edge = (k0 + kBN > kvlen) || (a.causal && (k0 + kBN - 1 > q0 + a.causal_off));
             if (edge || general) {
                 int lim = kvlen;
                 if (a.causal) lim = min(lim, qi + a.causal_off + 1);
-                lim -= k0;                              // columns c < lim are visible
+                lim -= k0 + half * kH;                  // own columns c < lim are visible
                 const float* mrow = nullptr;
                 if (a.keep_mask && qi < a.Sq)
-                    mrow = a.keep_mask + ((int64_t)b * a.Sq + qi) * a.Sk + k0;
+                    mrow = a.keep_mask + ((int64_t)b * a.Sq + qi) * a.Sk + k0 + half * kH;
 #pragma unroll
-                for (int c = 0; c < kBN; ++c) {
+                for (int c = 0; c < kH; ++c) {
                     float v = S_(c);
                     if (a.use_clamp) v = fminf(v, a.clamp_raw);
                     bool vis = c < lim;
@@ -315,13 +363,29 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
                     su[c] = __float_as_uint(vis ? v : neg_inf());
                 }
             }
-            float mx0 = fmaxf(S_(0), S_(1)), mx1 = fmaxf(S_(2), S_(3));
+            float mx[4];
 #pragma unroll
-            for (int c = 4; c < kBN; c += 4) {
-                mx0 = fmax3(mx0, S_(c), S_(c + 1));
-                mx1 = fmax3(mx1, S_(c + 2), S_(c + 3));
+            for (int i = 0; i < 4; ++i) mx[i] = fmaxf(S_(2 * i), S_(2 * i + 1));
+#pragma unroll
+            for (int c = 8; c < kH; c += 8)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) mx[i] = fmax3(mx[i], S_(c + 2 * i), S_(c + 2 * i + 1));
+            float mt = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+            if constexpr (kRowSplit == 2) {
+                // the row's other half: both threads publish, meet, and read each other's maximum
+                *xslot(j & 1, half) = mt;
+#if LTCA_PAIR_NAMED_BAR
+                asm volatile("bar.sync %0, 64;" ::"r"(1 + t * 4 + wq) : "memory");
+#else
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_pair(t, wq));
+                ok = __all_sync(0xffffffffu, mbar_wait(bar_pair(t, wq), pair_phase, wc, 0x3a));
+                pair_phase ^= 1u;
+                if (!ok) break;
+#endif
+                mt = fmaxf(mt, *xslot(j & 1, half ^ 1));
             }
-            const float mt = fmaxf(mx0, mx1);
+            LTCA_TRACE_EVT(0x12 + (j << 8));
 
             // Lazy rescale: keep the stale maximum while the new one exceeds it by less than
             // 2^8 in the exponent; P stays below 256 and fp32 sums keep their accuracy.
@@ -342,7 +406,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 o_waited = true;
                 tc_fence_after_sync();
 #pragma unroll
-                for (int c0 = 0; c0 < D; c0 += 32) {
+                for (int c0 = 0; c0 < kDH; c0 += 32) {
                     uint32_t o[32];
                     tmem_ld32(tO + c0, o);
                     tmem_wait_ld();
@@ -352,11 +416,27 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 }
                 l_run *= factor;
             }
+            // The two tiles take turns on the special-function units: tile 0 runs the exponentials
+            // of step j, then tile 1 those of its step j, then tile 0 step j + 1 ...  While one
+            // tile exponentiates, the other loads its scores, finds its maxima and talks to the
+            // barriers, so those latencies stay off the critical path.
+            if (LTCA_FWD_PINGPONG == 2) {
+                // one-time delay: tile 1 starts its first exponentials when tile 0 has finished its own
+                if (t == 1 && j == 0 && n_tiles[0] > 0) {
+                    ok = __all_sync(0xffffffffu, mbar_wait(bar_turn(0), 0, wc, 0x3e));
+                    if (!ok) break;
+                }
+            } else if (LTCA_FWD_PINGPONG == 1 && (t == 0 ? (j > 0 && j - 1 < n_tiles[1]) : (j < n_tiles[0]))) {
+                const uint32_t par = (uint32_t)((t == 0 ? j - 1 : j) & 1);
+                ok = __all_sync(0xffffffffu, mbar_wait(bar_turn(t ^ 1), par, wc, 0x3c + t));
+                if (!ok) break;
+            }
+            LTCA_TRACE_EVT(0x15 + (j << 8));
             const float m_safe = (m_run == neg_inf()) ? 0.f : m_run;
             const float mneg = -m_safe * c2;
             float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
 #pragma unroll
-            for (int ch = 0; ch < kBN / 32; ++ch) {
+            for (int ch = 0; ch < kH / 32; ++ch) {
                 uint32_t hi[16], lo[16];
 #pragma unroll
                 for (int cc = 0; cc < 32; cc += 4) {
@@ -376,6 +456,11 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
                                                      p3 - __uint_as_float(h23 & 0xffff0000u));
                     }
                 }
+                if (LTCA_FWD_PINGPONG == 1 && LTCA_FWD_EARLY_TURN && ch == kH / 32 - 1) {
+                    // the last quarter of this tile's exponentials overlaps the other tile's start
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar_turn(t));
+                }
                 if (ch == 0 && !o_waited) {
                     // P of the previous step must have been consumed before it is overwritten
                     ok = __all_sync(0xffffffffu,
@@ -386,30 +471,48 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 if constexpr (kSplitP) tmem_st16(tPlo + ch * 16, lo);
             }
             if (!ok) break;
+            if (LTCA_FWD_PINGPONG == 1 ? !LTCA_FWD_EARLY_TURN : (LTCA_FWD_PINGPONG == 2 && t == 0 && j == 0)) {
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_turn(t));
+            }
             l_run += (sum0 + sum1) + (sum2 + sum3);
+            LTCA_TRACE_EVT(0x13 + (j << 8));
             tmem_wait_st();
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_p_full(t));
+            LTCA_TRACE_EVT(0x14 + (j << 8));
 #undef S_
         }
 
-        // epilogue: O / l and lse
+        // epilogue: O / l and lse; the row sum is the total of the two halves
         if (ok && q0 < a.Sq) {
             float inv = 0.f;
             float lse = neg_inf();
             if (n_t > 0) {
-                ok = __all_sync(0xffffffffu,
-                                mbar_wait(bar_o_done(t), (uint32_t)((n_t - 1) & 1), wc, 0x34 + t));
+                if constexpr (kRowSplit == 2) {
+                    *xslot(2, half) = l_run;
+#if LTCA_PAIR_NAMED_BAR
+                    asm volatile("bar.sync %0, 64;" ::"r"(1 + t * 4 + wq) : "memory");
+#else
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar_pair(t, wq));
+                    ok = __all_sync(0xffffffffu, mbar_wait(bar_pair(t, wq), pair_phase, wc, 0x3b));
+#endif
+                    if (ok) l_run += *xslot(2, half ^ 1);
+                }
+                ok = ok && __all_sync(0xffffffffu,
+                                      mbar_wait(bar_o_done(t), (uint32_t)((n_t - 1) & 1), wc, 0x34 + t));
                 tc_fence_after_sync();
                 if (l_run > 0.f) {
                     inv = 1.0f / l_run;
                     lse = m_run * a.scale + __logf(l_run);
                 }
             }
-            OutT* orow = reinterpret_cast<OutT*>(a.o) + b * a.o_sb + h * a.o_sh + (int64_t)qi * a.o_ss;
+            OutT* orow = reinterpret_cast<OutT*>(a.o) + b * a.o_sb + h * a.o_sh + (int64_t)qi * a.o_ss +
+                         half * kDH;
 #pragma unroll
-            for (int c0 = 0; c0 < D; c0 += 32) {
+            for (int c0 = 0; c0 < kDH; c0 += 32) {
                 uint32_t o[32];
                 if (n_t > 0 && ok) {
                     tmem_ld32(tO + c0, o);
@@ -441,6 +544,352 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
                     }
                 }
             }
+            if (half == 0 && a.lse && qi < a.Sq) a.lse[((int64_t)b * a.H + h) * a.Sq + qi] = lse;
+        }
+    }
+
+    // ------------------------------ tear-down -------------------------------------------------
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == kMmaWarp0) {
+        __syncwarp();
+        if (misc[1]) __nanosleep(200000);    // aborted: give copies and MMAs in flight time to land
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Four-tile variant (head_dim 64, bf16 result): one CTA per (512 query rows, head, batch).
+//
+// Every scheduler of the SM holds four softmax warps that belong to four DIFFERENT query tiles;
+// a tile's warps only ever wait for that tile's own barriers, so while one tile sits in a
+// barrier round trip, a tensor-memory load or the tensor pipe's queue, the other three keep the
+// special-function unit busy (measured on B200: four independent warps per scheduler hide every
+// one of those latencies, two dependent ones hide almost none).
+//   - steps of 64 keys; tile t: S_t = Q_t K_j^T in columns [64 t, 64 t + 64), O_t in
+//     [256 + 64 t, 256 + 64 t + 64); P_t (bf16) overwrites the first 32 columns of S_t, so the
+//     issuer queues O_t += P_t V_j and S_t = Q_t K_{j+1}^T back to back (the tensor pipe runs one
+//     thread's MMAs in order) and one commit tells the tile both "S ready" and "O up to date";
+//   - warps 0-15: softmax, one query row per thread (tile = warp / 4); warp 16 issues the
+//     contractions of tiles 0 and 1, warp 17 those of tiles 2 and 3; warp 18: TMA producer.
+// ---------------------------------------------------------------------------------------------
+constexpr int kF4Tiles = 4;
+constexpr int kF4BN = 64;
+constexpr int kF4Threads = 640;
+constexpr int kF4LaunchRegs = 96;
+constexpr int kF4CtrlRegs = 56;
+constexpr int kF4MathRegs = 104;
+static_assert(512 * kF4MathRegs + 128 * kF4CtrlRegs <= kF4Threads * kF4LaunchRegs, "register budget");
+
+struct F4Cfg {
+    static constexpr int kQTileBytes = kBlockM * 64 * 2;       // 16 KB
+    static constexpr int kKvTileBytes = kF4BN * 64 * 2;        // 8 KB
+    static constexpr int kStages = 8;
+    static constexpr int kQOff = 0;
+    static constexpr int kRingOff = kF4Tiles * kQTileBytes;
+    static constexpr int kBarOff = kRingOff + kStages * kKvTileBytes;
+    // barriers: q_full, kv_full[kStages], kv_empty[kStages], s_full[4], p_full[4]
+    static constexpr int kNumBars = 1 + 2 * kStages + 2 * kF4Tiles;
+    static constexpr int kMiscOff = kBarOff + kNumBars * 8;
+    static constexpr int kDynBytes = kMiscOff + 16 + 1024;
+};
+
+__global__ void __launch_bounds__(kF4Threads, 1)
+attn_fwd4_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
+                       const __grid_constant__ CUtensorMap tmap_k,
+                       const __grid_constant__ CUtensorMap tmap_v, const FwdArgs a) {
+    using L = F4Cfg;
+    constexpr int D = 64;
+    constexpr int kBN = kF4BN;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    const uint32_t q_smem = smem_base + L::kQOff;
+    const uint32_t ring_smem = smem_base + L::kRingOff;
+    const uint32_t bar_base = smem_base + L::kBarOff;
+    auto bar_q_full = [&]() { return bar_base; };
+    auto bar_kv_full = [&](int s) { return bar_base + 8u * (1 + s); };
+    auto bar_kv_empty = [&](int s) { return bar_base + 8u * (1 + L::kStages + s); };
+    auto bar_s_full = [&](int t) { return bar_base + 8u * (1 + 2 * L::kStages + t); };
+    auto bar_p_full = [&](int t) { return bar_base + 8u * (1 + 2 * L::kStages + kF4Tiles + t); };
+    volatile uint32_t* misc = reinterpret_cast<volatile uint32_t*>(smem_gen + L::kMiscOff);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int m_block = gridDim.x - 1 - blockIdx.x;     // heavy (late) causal blocks first
+    const int h = blockIdx.y;
+    const int b = blockIdx.z;
+
+    int kvlen = a.Sk;
+    if (a.kv_len) kvlen = min(max(a.kv_len[b], 0), a.Sk);
+    int n_tiles[kF4Tiles];
+    int n_max = 0;
+#pragma unroll
+    for (int t = 0; t < kF4Tiles; ++t) {
+        const int q0 = (m_block * kF4Tiles + t) * kBlockM;
+        int lim = 0;
+        if (q0 < a.Sq) {
+            lim = kvlen;
+            if (a.causal) lim = min(lim, min(q0 + kBlockM - 1, a.Sq - 1) + a.causal_off + 1);
+        }
+        n_tiles[t] = lim > 0 ? (lim + kBN - 1) / kBN : 0;
+        n_max = max(n_max, n_tiles[t]);
+    }
+
+    if (threadIdx.x == 0) {
+        mbar_init(bar_q_full(), 1);
+        for (int s = 0; s < L::kStages; ++s) {
+            mbar_init(bar_kv_full(s), 1);
+            mbar_init(bar_kv_empty(s), 2);     // both MMA issuers release a slot
+        }
+        for (int t = 0; t < kF4Tiles; ++t) {
+            mbar_init(bar_s_full(t), 1);
+            mbar_init(bar_p_full(t), 4);       // one arrival per softmax warp of the tile
+        }
+        misc[1] = 0u;
+        mbar_fence_init();
+    }
+    if (warp == 16) {
+        tmem_alloc(smem_u32(const_cast<uint32_t*>(&misc[0])), kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = misc[0];
+    const WaitCtx wc{&misc[1], a.status};
+
+    if (warp >= 16) {
+        reg_dealloc<kF4CtrlRegs>();
+        auto slot_of = [&](int item) { return item % L::kStages; };
+        auto phase_of = [&](int item) { return (uint32_t)((item / L::kStages) & 1); };
+        if (warp == 18) {
+            // ------------------------------ TMA producer --------------------------------------
+            if (lane == 0 && n_max > 0) {
+                tma_prefetch_desc(&tmap_q);
+                tma_prefetch_desc(&tmap_k);
+                tma_prefetch_desc(&tmap_v);
+                mbar_arrive_expect_tx(bar_q_full(), (uint32_t)(kF4Tiles * L::kQTileBytes));
+                for (int t = 0; t < kF4Tiles; ++t)
+                    tma_load_4d(q_smem + t * L::kQTileBytes, &tmap_q, bar_q_full(), 0,
+                                (m_block * kF4Tiles + t) * kBlockM, h, b);
+                bool ok = true;
+                for (int j = 0; j < n_max && ok; ++j) {
+#pragma unroll
+                    for (int which = 0; which < 2; ++which) {     // 0: K_j, 1: V_j
+                        const int item = 2 * j + which;
+                        const int slot = slot_of(item);
+                        ok = ok && mbar_wait(bar_kv_empty(slot), phase_of(item) ^ 1u, wc, 0x10 + which);
+                        if (!ok) break;
+                        mbar_arrive_expect_tx(bar_kv_full(slot), (uint32_t)L::kKvTileBytes);
+                        tma_load_4d(ring_smem + slot * L::kKvTileBytes, which == 0 ? &tmap_k : &tmap_v,
+                                    bar_kv_full(slot), 0, j * kBN, h, b);
+                    }
+                }
+            }
+        } else if (warp == 16 || warp == 17) {
+            // ------------------------------ MMA issuer of tiles 2i, 2i+1 ----------------------
+            const int t0 = 2 * (warp - 16);
+            if (lane == 0 && n_max > 0) {
+                constexpr uint32_t idesc_qk = make_idesc_bf16(kBlockM, kBN, 0, 0);
+                constexpr uint32_t idesc_pv = make_idesc_bf16(kBlockM, D, 0, 1);
+                const uint64_t q_desc = make_smem_desc_sw128(q_smem, 16, 1024);
+                const uint64_t k_desc = make_smem_desc_sw128(ring_smem, 16, 1024);
+                const uint64_t v_desc = make_smem_desc_sw128(ring_smem, kBN * 128, 1024);
+                auto issue_qk = [&](int t, int slot) {
+                    const uint64_t qd = q_desc + (uint64_t)((t * L::kQTileBytes) >> 4);
+                    const uint64_t kd = k_desc + (uint64_t)((slot * L::kKvTileBytes) >> 4);
+#pragma unroll
+                    for (int k = 0; k < D / 16; ++k)
+                        mma_ss(tmem_base + t * kBN, qd + 2 * k, kd + 2 * k, idesc_qk, k > 0 ? 1u : 0u);
+                };
+                auto issue_pv = [&](int t, int slot, bool acc) {
+                    const uint64_t vd = v_desc + (uint64_t)((slot * L::kKvTileBytes) >> 4);
+#pragma unroll
+                    for (int k = 0; k < kBN / 16; ++k)
+                        mma_ts(tmem_base + 256 + t * D, tmem_base + t * kBN + k * 8, vd + 128 * k, idesc_pv,
+                               (acc || k > 0) ? 1u : 0u);
+                };
+                bool ok = mbar_wait(bar_q_full(), 0, wc, 0x20);
+                ok = ok && mbar_wait(bar_kv_full(slot_of(0)), phase_of(0), wc, 0x21);
+                if (ok) {
+                    tc_fence_after_sync();
+                    for (int i = 0; i < 2; ++i)
+                        if (n_tiles[t0 + i] > 0) {
+                            issue_qk(t0 + i, slot_of(0));
+                            mma_commit(bar_s_full(t0 + i));
+                        }
+                    mma_commit(bar_kv_empty(slot_of(0)));
+                }
+                for (int j = 0; j < n_max && ok; ++j) {
+                    const int item_v = 2 * j + 1, item_k = 2 * j + 2;
+                    const bool have_next = (j + 1 < n_max);
+                    ok = mbar_wait(bar_kv_full(slot_of(item_v)), phase_of(item_v), wc, 0x22);
+                    if (have_next) ok = ok && mbar_wait(bar_kv_full(slot_of(item_k)), phase_of(item_k), wc, 0x23);
+                    for (int i = 0; i < 2 && ok; ++i) {
+                        const int t = t0 + i;
+                        if (j < n_tiles[t]) {
+                            ok = mbar_wait(bar_p_full(t), (uint32_t)(j & 1), wc, 0x24 + t);
+                            if (!ok) break;
+                            tc_fence_after_sync();
+                            issue_pv(t, slot_of(item_v), j > 0);
+                            if (j + 1 < n_tiles[t]) issue_qk(t, slot_of(item_k));
+                            mma_commit(bar_s_full(t));     // S of step j+1 ready, O holds steps 0..j
+                        }
+                    }
+                    if (!ok) break;
+                    mma_commit(bar_kv_empty(slot_of(item_v)));
+                    if (have_next) mma_commit(bar_kv_empty(slot_of(item_k)));
+                }
+                // everything this thread issued has to be complete before tensor memory is released
+                for (int i = 0; i < 2 && ok; ++i)
+                    if (n_tiles[t0 + i] > 0)
+                        ok = mbar_wait(bar_s_full(t0 + i), (uint32_t)(n_tiles[t0 + i] & 1), wc, 0x28 + t0 + i);
+            }
+        }
+    } else {
+        // ------------------------------ softmax / correction / epilogue ------------------------
+        reg_alloc<kF4MathRegs>();
+        const int t = warp >> 2;
+        const int wq = warp & 3;
+        const int row = wq * 32 + lane;
+        const int q0 = (m_block * kF4Tiles + t) * kBlockM;
+        const int qi = q0 + row;
+        const int n_t = n_tiles[t];
+        const uint32_t lane_base = (uint32_t)(wq * 32) << 16;
+        const uint32_t tS = tmem_base + lane_base + t * kBN;
+        const uint32_t tO = tmem_base + lane_base + 256 + t * D;
+        const float c2 = a.scale_log2;
+        const bool general = (a.keep_mask != nullptr) || (a.use_clamp != 0);
+
+        float m_run = neg_inf();
+        float l_run = 0.f;
+        bool ok = true;
+        for (int j = 0; j < n_t; ++j) {
+            ok = __all_sync(0xffffffffu, mbar_wait(bar_s_full(t), (uint32_t)(j & 1), wc, 0x30 + t));
+            if (!ok) break;
+            tc_fence_after_sync();
+            uint32_t su[kBN];
+            tmem_ld32(tS, reinterpret_cast<uint32_t(&)[32]>(su[0]));
+            tmem_ld32(tS + 32, reinterpret_cast<uint32_t(&)[32]>(su[32]));
+            tmem_wait_ld();
+#define S_(c) __uint_as_float(su[(c)])
+            const int k0 = j * kBN;
+            const bool edge = (k0 + kBN > kvlen) || (a.causal && (k0 + kBN - 1 > q0 + a.causal_off));
+            if (edge || general) {
+                int lim = kvlen;
+                if (a.causal) lim = min(lim, qi + a.causal_off + 1);
+                lim -= k0;                              // columns c < lim are visible
+                const float* mrow = nullptr;
+                if (a.keep_mask && qi < a.Sq)
+                    mrow = a.keep_mask + ((int64_t)b * a.Sq + qi) * a.Sk + k0;
+#pragma unroll
+                for (int c = 0; c < kBN; ++c) {
+                    float v = S_(c);
+                    if (a.use_clamp) v = fminf(v, a.clamp_raw);
+                    bool vis = c < lim;
+                    if (mrow && vis) vis = (__ldg(mrow + c) != 0.0f);
+                    su[c] = __float_as_uint(vis ? v : neg_inf());
+                }
+            }
+            float mx[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) mx[i] = fmaxf(S_(2 * i), S_(2 * i + 1));
+#pragma unroll
+            for (int c = 8; c < kBN; c += 8)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) mx[i] = fmax3(mx[i], S_(c + 2 * i), S_(c + 2 * i + 1));
+            const float mt = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+
+            // Lazy rescale: keep the stale maximum while the new one exceeds it by less than
+            // 2^8 in the exponent; P stays below 256 and fp32 sums keep their accuracy.
+            float factor = 1.0f;
+            bool need = false;
+            if (j == 0) {
+                m_run = mt;
+            } else if ((mt - m_run) * c2 > 8.0f) {
+                factor = fast_exp2((m_run - mt) * c2);
+                m_run = mt;
+                need = true;
+            }
+            if (j > 0 && __any_sync(0xffffffffu, need)) {
+                // O already holds every earlier step: the commit behind s_full covered it
+#pragma unroll
+                for (int c0 = 0; c0 < D; c0 += 16) {
+                    uint32_t o[16];
+                    tmem_ld16(tO + c0, o);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int c = 0; c < 16; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * factor);
+                    tmem_st16(tO + c0, o);
+                }
+                l_run *= factor;
+            }
+            const float m_safe = (m_run == neg_inf()) ? 0.f : m_run;
+            const float mneg = -m_safe * c2;
+            float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
+#pragma unroll
+            for (int ch = 0; ch < kBN / 32; ++ch) {
+                uint32_t hi[16];
+#pragma unroll
+                for (int cc = 0; cc < 32; cc += 4) {
+                    const int c = ch * 32 + cc;
+                    const float p0 = fast_exp2(fmaf(S_(c), c2, mneg));
+                    const float p1 = fast_exp2(fmaf(S_(c + 1), c2, mneg));
+                    const float p2 = fast_exp2(fmaf(S_(c + 2), c2, mneg));
+                    const float p3 = fast_exp2(fmaf(S_(c + 3), c2, mneg));
+                    sum0 += p0; sum1 += p1; sum2 += p2; sum3 += p3;
+                    hi[cc / 2] = pack_bf16x2(p0, p1);
+                    hi[cc / 2 + 1] = pack_bf16x2(p2, p3);
+                }
+                tmem_st16(tS + ch * 16, hi);      // P over the first columns of S (all of S is in registers)
+            }
+            l_run += (sum0 + sum1) + (sum2 + sum3);
+            tmem_wait_st();
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_p_full(t));
+#undef S_
+        }
+
+        // epilogue: O / l and lse
+        if (ok && q0 < a.Sq) {
+            float inv = 0.f;
+            float lse = neg_inf();
+            if (n_t > 0) {
+                ok = __all_sync(0xffffffffu, mbar_wait(bar_s_full(t), (uint32_t)(n_t & 1), wc, 0x34 + t));
+                tc_fence_after_sync();
+                if (l_run > 0.f) {
+                    inv = 1.0f / l_run;
+                    lse = m_run * a.scale + __logf(l_run);
+                }
+            }
+            __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(a.o) + b * a.o_sb + h * a.o_sh +
+                                  (int64_t)qi * a.o_ss;
+#pragma unroll
+            for (int c0 = 0; c0 < D; c0 += 32) {
+                uint32_t o[32];
+                if (n_t > 0 && ok) {
+                    tmem_ld32(tO + c0, o);
+                    tmem_wait_ld();
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) o[c] = 0u;
+                }
+                if (qi < a.Sq) {
+                    uint4* dst = reinterpret_cast<uint4*>(orow + c0);
+#pragma unroll
+                    for (int v = 0; v < 4; ++v) {
+                        uint4 w;
+                        w.x = pack_bf16x2(__uint_as_float(o[8 * v + 0]) * inv, __uint_as_float(o[8 * v + 1]) * inv);
+                        w.y = pack_bf16x2(__uint_as_float(o[8 * v + 2]) * inv, __uint_as_float(o[8 * v + 3]) * inv);
+                        w.z = pack_bf16x2(__uint_as_float(o[8 * v + 4]) * inv, __uint_as_float(o[8 * v + 5]) * inv);
+                        w.w = pack_bf16x2(__uint_as_float(o[8 * v + 6]) * inv, __uint_as_float(o[8 * v + 7]) * inv);
+                        dst[v] = w;
+                    }
+                }
+            }
             if (a.lse && qi < a.Sq) a.lse[((int64_t)b * a.H + h) * a.Sq + qi] = lse;
         }
     }
@@ -448,12 +897,32 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
     // ------------------------------ tear-down -------------------------------------------------
     tc_fence_before_sync();
     __syncthreads();
-    if (warp == kMmaWarp) {
+    if (warp == 16) {
         __syncwarp();
         if (misc[1]) __nanosleep(200000);    // aborted: give copies and MMAs in flight time to land
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, kTmemCols);
     }
+}
+
+int launch_fwd4(ltca_ctx* ctx, const ltca_attn_params* p, const void* q, const void* k, const void* v,
+                const ltca_strides& qs, const ltca_strides& ks, const ltca_strides& vs, const FwdArgs& a) {
+    using L = F4Cfg;
+    CUtensorMap tq, tk, tv;
+    int rc;
+    if ((rc = make_tmap_bhsd(ctx, &tq, q, 2, p->B, p->H, p->Sq, 64, qs, 64, kBlockM))) return rc;
+    if ((rc = make_tmap_bhsd(ctx, &tk, k, 2, p->B, p->H, p->Sk, 64, ks, 64, kF4BN))) return rc;
+    if ((rc = make_tmap_bhsd(ctx, &tv, v, 2, p->B, p->H, p->Sk, 64, vs, 64, kF4BN))) return rc;
+    static bool attr_done = false;
+    if (!attr_done) {
+        LTCA_CUDA_OK(ctx, cudaFuncSetAttribute(attn_fwd4_sm100_kernel,
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynBytes));
+        attr_done = true;
+    }
+    dim3 grid((p->Sq + kF4Tiles * kBlockM - 1) / (kF4Tiles * kBlockM), p->H, p->B);
+    attn_fwd4_sm100_kernel<<<grid, kF4Threads, L::kDynBytes, ctx->stream>>>(tq, tk, tv, a);
+    LTCA_LAUNCH_OK(ctx, "attn_fwd4_sm100_kernel");
+    return LTCA_OK;
 }
 
 template <int D, typename OutT>
@@ -483,6 +952,11 @@ int launch_fwd(ltca_ctx* ctx, const ltca_attn_params* p, const void* q, const vo
     a.kv_len = p->kv_len;
     a.status = ctx->d_status;
 
+    if constexpr (D == 64 && sizeof(OutT) == 2) {
+        // long query ranges: four independent tiles per CTA (see attn_fwd4_sm100_kernel)
+        if (LTCA_FWD4 && p->Sq > 2 * kBlockM) return launch_fwd4(ctx, p, q, k, v, qs, ks, vs, a);
+    }
+
     auto kern = attn_fwd_sm100_kernel<D, OutT, kSplitP>;
     static bool attr_done = false;
     if (!attr_done) {
@@ -497,6 +971,14 @@ int launch_fwd(ltca_ctx* ctx, const ltca_attn_params* p, const void* q, const vo
 }
 
 }  // namespace
+
+#ifdef LTCA_TRACE
+extern "C" int ltca_trace_read_fwd(unsigned long long* events, unsigned int* counts) {
+    if (cudaMemcpyFromSymbol(events, g_trace, sizeof(g_trace)) != cudaSuccess) return -1;
+    if (cudaMemcpyFromSymbol(counts, g_trace_count, sizeof(g_trace_count)) != cudaSuccess) return -1;
+    return 0;
+}
+#endif
 
 bool attn_fwd_sm100_supported(const ltca_attn_params* p) {
     if (p->D != 64 && p->D != 128) return false;

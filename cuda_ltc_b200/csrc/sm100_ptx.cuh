@@ -22,7 +22,12 @@ enum : uint32_t {
     kStatusWhereShift    = 8          // bits [8,24): which barrier gave up (role-specific code)
 };
 
+#ifndef LTCA_WAIT_SLEEP_NS
+#define LTCA_WAIT_SLEEP_NS 0
+#endif
 static constexpr unsigned long long kWaitLimitNs = 2000000000ull;   // 2 s
+// (No suspend-time hint on mbarrier.try_wait: measured on B200, a hint more than doubles the
+// latency between an arrival and the waiter's wake-up.)
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -83,6 +88,9 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const W
     if (mbar_try_wait(bar, parity)) return true;
     unsigned long long t0 = 0;
     for (uint32_t it = 1;; ++it) {
+#if LTCA_WAIT_SLEEP_NS > 0
+        __nanosleep(LTCA_WAIT_SLEEP_NS);      // a polling warp takes issue slots from the working ones
+#endif
         if (mbar_try_wait(bar, parity)) return true;
         if ((it & 0xffu) == 0) {
             if (*w.abort_flag) return false;
@@ -203,6 +211,16 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
 }
 
 // 16-column variants (smaller register footprint per call).
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+          "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
 __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
