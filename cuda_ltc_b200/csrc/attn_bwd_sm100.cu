@@ -26,6 +26,12 @@
 #include "sm100_ptx.cuh"
 #include "trace.cuh"
 
+#ifndef LTCA_BWD_DQ4
+#define LTCA_BWD_DQ4 1
+#endif
+#ifndef LTCA_BWD_DKV4
+#define LTCA_BWD_DKV4 1
+#endif
 #ifndef LTCA_BWD_STAGGER
 #define LTCA_BWD_STAGGER 1
 #endif
@@ -795,6 +801,542 @@ attn_bwd_dkv_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// 4. dK, dV, single-tile variant (bf16 operands and results): one CTA per 128 keys, query steps
+// of 128.  Nothing in tensor memory is aliased, so the next step's S^T and dP^T are computed
+// while this step's P^T and dS^T are being formed, and the contractions have N = 128 or K = 128:
+//   S^T [0,128)  dP^T [128,256)  P^T bf16 [256,320)  dS^T bf16 [320,384)  dV [384,448)  dK [448,512)
+// 16 elementwise warps: warp w owns key rows 32 (w % 4) .. +31 and query columns 32 (w / 4) .. +31
+// of the step.  Two MMA threads share the issue work: warp 16 issues S^T and dV, warp 17 dP^T
+// and dK (each accumulator has one issuing thread, so the summation order is fixed).
+// ---------------------------------------------------------------------------------------------
+struct Dkv4Smem {
+    static constexpr int kStages = 4;                         // ring of (Q_j, dO_j, lse2_j, delta_j)
+    static constexpr int kStageBytes = 2 * kBigTile + 1024;
+    static constexpr int kKOff = 0;
+    static constexpr int kVOff = kBigTile;
+    static constexpr int kRingOff = 2 * kBigTile;
+    static constexpr int kBarOff = kRingOff + kStages * kStageBytes;
+    // bars: kv_full, ring_full[S], ring_empty[S], sdp_full, sdp_free, pds_full, acc_done
+    static constexpr int kNumBars = 1 + 2 * kStages + 4;
+    static constexpr int kMiscOff = kBarOff + kNumBars * 8;
+    static constexpr int kDynBytes = kMiscOff + 16 + 1024;
+};
+
+__device__ __forceinline__ void store_row16_bf16(__nv_bfloat16* dst, const uint32_t (&o)[16], float mul) {
+    uint4* d = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+    for (int v = 0; v < 2; ++v) {
+        uint4 w;
+        w.x = pack_bf16x2(__uint_as_float(o[8 * v + 0]) * mul, __uint_as_float(o[8 * v + 1]) * mul);
+        w.y = pack_bf16x2(__uint_as_float(o[8 * v + 2]) * mul, __uint_as_float(o[8 * v + 3]) * mul);
+        w.z = pack_bf16x2(__uint_as_float(o[8 * v + 4]) * mul, __uint_as_float(o[8 * v + 5]) * mul);
+        w.w = pack_bf16x2(__uint_as_float(o[8 * v + 6]) * mul, __uint_as_float(o[8 * v + 7]) * mul);
+        d[v] = w;
+    }
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+attn_bwd_dkv4_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
+                           const __grid_constant__ CUtensorMap tmap_do,
+                           const __grid_constant__ CUtensorMap tmap_k,
+                           const __grid_constant__ CUtensorMap tmap_v, const BwdArgs a) {
+    using L = Dkv4Smem;
+    constexpr int kQStep = 128;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    const uint32_t k_smem = smem_base + L::kKOff, v_smem = smem_base + L::kVOff;
+    const uint32_t ring_smem = smem_base + L::kRingOff, bar_base = smem_base + L::kBarOff;
+    auto bar_kv_full = [&]() { return bar_base; };
+    auto bar_ring_full = [&](int s) { return bar_base + 8u * (1 + s); };
+    auto bar_ring_empty = [&](int s) { return bar_base + 8u * (1 + L::kStages + s); };
+    const uint32_t bar_sdp_full = bar_base + 8u * (1 + 2 * L::kStages);
+    const uint32_t bar_sdp_free = bar_sdp_full + 8u;
+    const uint32_t bar_pds_full = bar_sdp_full + 16u;
+    const uint32_t bar_acc_done = bar_sdp_full + 24u;
+    volatile uint32_t* misc = reinterpret_cast<volatile uint32_t*>(smem_gen + L::kMiscOff);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n_block = blockIdx.x;                 // early key blocks carry the most causal work
+    const int h = blockIdx.y, b = blockIdx.z;
+    const int k0 = n_block * kTile;
+
+    int kvlen = a.Sk;
+    if (a.kv_len) kvlen = min(max(a.kv_len[b], 0), a.Sk);
+    const int n_q = (a.Sq + kQStep - 1) / kQStep;   // query steps in total
+    int j_begin = 0;                                // first query step that can see the tile's keys
+    if (a.causal) j_begin = max(0, k0 - a.causal_off) / kQStep;
+    const bool active = (k0 < kvlen) && (j_begin < n_q);
+    const int n_it = active ? n_q - j_begin : 0;
+
+    if (threadIdx.x == 0) {
+        mbar_init(bar_kv_full(), 1);
+        for (int s = 0; s < L::kStages; ++s) { mbar_init(bar_ring_full(s), 1); mbar_init(bar_ring_empty(s), 2); }
+        mbar_init(bar_sdp_full, 2);                // one commit per MMA thread
+        mbar_init(bar_sdp_free, 16);               // one arrival per elementwise warp
+        mbar_init(bar_pds_full, 16);
+        mbar_init(bar_acc_done, 2);
+        misc[1] = 0u;
+        mbar_fence_init();
+    }
+    if (warp == kMmaWarp0) { tmem_alloc(smem_u32(const_cast<uint32_t*>(&misc[0])), kTmemCols); tmem_relinquish(); }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = misc[0];
+    const WaitCtx wc{&misc[1], a.status};
+    auto slot_of = [&](int it) { return it % L::kStages; };
+    auto phase_of = [&](int it) { return (uint32_t)((it / L::kStages) & 1); };
+
+    if (warp >= 16) {
+      reg_dealloc<kCtrlRegs>();
+      if (warp == kTmaWarp) {
+        if (lane == 0 && active) {
+            mbar_arrive_expect_tx(bar_kv_full(), 2u * kBigTile);
+            tma_load_4d(k_smem, &tmap_k, bar_kv_full(), 0, k0, h, b);
+            tma_load_4d(v_smem, &tmap_v, bar_kv_full(), 0, k0, h, b);
+            const float* lse2_row = a.lse2 + ((int64_t)b * a.H + h) * a.Sq_pad;
+            const float* dlt_row = a.delta + ((int64_t)b * a.H + h) * a.Sq_pad;
+            bool ok = true;
+            for (int it = 0; it < n_it && ok; ++it) {
+                const int j = j_begin + it;
+                ok = mbar_wait(bar_ring_empty(slot_of(it)), phase_of(it) ^ 1u, wc, 0xa0);
+                if (!ok) break;
+                const uint32_t st = ring_smem + slot_of(it) * L::kStageBytes;
+                const uint32_t bar = bar_ring_full(slot_of(it));
+                mbar_arrive_expect_tx(bar, 2u * kBigTile + 1024u);
+                tma_load_4d(st, &tmap_q, bar, 0, j * kQStep, h, b);
+                tma_load_4d(st + kBigTile, &tmap_do, bar, 0, j * kQStep, h, b);
+                asm volatile(
+                    "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], 512, [%2];"
+                    ::"r"(st + 2 * kBigTile), "l"(reinterpret_cast<uint64_t>(lse2_row + j * kQStep)), "r"(bar)
+                    : "memory");
+                asm volatile(
+                    "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], 512, [%2];"
+                    ::"r"(st + 2 * kBigTile + 512), "l"(reinterpret_cast<uint64_t>(dlt_row + j * kQStep)), "r"(bar)
+                    : "memory");
+            }
+        }
+      } else if (warp == kMmaWarp0 || warp == kMmaWarp0 + 1) {
+        // which == 0: S^T = K Q_j^T and dV += P^T dO_j;  which == 1: dP^T = V dO_j^T and dK += dS^T Q_j
+        const int which = warp - kMmaWarp0;
+        if (lane == 0 && active) {
+            constexpr uint32_t idesc_s = make_idesc_bf16(kTile, kQStep, 0, 0);
+            constexpr uint32_t idesc_acc = make_idesc_bf16(kTile, kD, 0, 1);
+            const uint64_t a_desc = make_smem_desc_sw128(which == 0 ? k_smem : v_smem, 16, 1024);
+            // the streamed operand of the first contraction (Q for S^T, dO for dP^T), K-major
+            const uint64_t b1_desc = make_smem_desc_sw128(ring_smem + (which == 0 ? 0 : kBigTile), 16, 1024);
+            // the streamed operand of the accumulation (dO for dV, Q for dK), rows as the contraction index
+            const uint64_t b2_desc = make_smem_desc_sw128(ring_smem + (which == 0 ? kBigTile : 0), 8192, 1024);
+            const uint32_t d1 = tmem_base + (which == 0 ? 0 : 128);
+            const uint32_t a2 = tmem_base + (which == 0 ? 256 : 320);
+            const uint32_t d2 = tmem_base + (which == 0 ? 384 : 448);
+            auto issue_first = [&](int slot) {
+                const uint64_t bd = b1_desc + (uint64_t)((slot * L::kStageBytes) >> 4);
+#pragma unroll
+                for (int k = 0; k < kD / 16; ++k) mma_ss(d1, a_desc + 2 * k, bd + 2 * k, idesc_s, k > 0);
+            };
+            auto issue_acc = [&](int slot, bool acc) {
+                const uint64_t bd = b2_desc + (uint64_t)((slot * L::kStageBytes) >> 4);
+#pragma unroll
+                for (int k = 0; k < kQStep / 16; ++k)
+                    mma_ts(d2, a2 + k * 8, bd + 128 * k, idesc_acc, (acc || k > 0) ? 1u : 0u);
+            };
+            bool ok = mbar_wait(bar_kv_full(), 0, wc, 0xb0);
+            ok = ok && mbar_wait(bar_ring_full(slot_of(0)), phase_of(0), wc, 0xb1);
+            if (ok) {
+                tc_fence_after_sync();
+                issue_first(slot_of(0));
+                mma_commit(bar_sdp_full);
+            }
+            for (int it = 0; it < n_it && ok; ++it) {
+                if (it + 1 < n_it) {
+                    ok = mbar_wait(bar_ring_full(slot_of(it + 1)), phase_of(it + 1), wc, 0xb2);
+                    ok = ok && mbar_wait(bar_sdp_free, (uint32_t)(it & 1), wc, 0xb3);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    issue_first(slot_of(it + 1));
+                    mma_commit(bar_sdp_full);
+                }
+                ok = mbar_wait(bar_pds_full, (uint32_t)(it & 1), wc, 0xb4);
+                if (!ok) break;
+                tc_fence_after_sync();
+                issue_acc(slot_of(it), it > 0);
+                mma_commit(bar_acc_done);
+                mma_commit(bar_ring_empty(slot_of(it)));
+            }
+            if (ok && n_it > 0) ok = mbar_wait(bar_acc_done, (uint32_t)((n_it - 1) & 1), wc, 0xb5);
+        }
+      }
+    } else {
+        reg_alloc<kMathRegs>();
+        const int wq = warp & 3, cq = warp >> 2;
+        const int row = wq * 32 + lane;
+        const int kj = k0 + row;                                   // this thread's key
+        const uint32_t lane_base = (uint32_t)(wq * 32) << 16;
+        const uint32_t tS = tmem_base + lane_base + 32 * cq;
+        const uint32_t tDP = tS + 128;
+        const uint32_t tP = tmem_base + lane_base + 256 + 16 * cq;
+        const uint32_t tDS = tP + 64;
+        const uint32_t tDV = tmem_base + lane_base + 384 + 16 * cq;
+        const uint32_t tDK = tDV + 64;
+        const float c2 = a.scale_log2;
+        const bool general = (a.keep_mask != nullptr) || (a.use_clamp != 0);
+        const bool key_live = kj < kvlen;
+
+        bool ok = true;
+        for (int it = 0; it < n_it; ++it) {
+            const int j = j_begin + it;
+            ok = __all_sync(0xffffffffu, mbar_wait(bar_sdp_full, (uint32_t)(it & 1), wc, 0xc0));
+            if (!ok) break;
+            tc_fence_after_sync();
+            uint32_t s[32], dp[32];
+            tmem_ld32(tS, s);
+            tmem_ld32(tDP, dp);
+            tmem_wait_ld();
+            // S^T and dP^T of this step are in registers: the next step's may be computed
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_sdp_free);
+            // lse2 and delta of this thread's 32 query columns (every lane reads the same address)
+            const float4* st4 = reinterpret_cast<const float4*>(
+                smem_gen + L::kRingOff + slot_of(it) * L::kStageBytes + 2 * kBigTile) + cq * 8;
+            const int q0 = j * kQStep + cq * 32;
+            // a query column c is hidden from this key when q0 + c + off < kj
+            const bool edge = !key_live || (k0 + kTile > kvlen) ||
+                              (a.causal && (j * kQStep + a.causal_off < k0 + kTile - 1));
+            if (edge || general) {
+#pragma unroll
+                for (int c4 = 0; c4 < 8; ++c4) {
+                    const float4 l4 = st4[c4];
+                    const float4 d4 = st4[32 + c4];
+                    const float ls[4] = {l4.x, l4.y, l4.z, l4.w};
+                    const float dl[4] = {d4.x, d4.y, d4.z, d4.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int c = 4 * c4 + e;
+                        const float sv = __uint_as_float(s[c]);
+                        float p = fast_exp2(fmaf(sv, c2, -ls[e]));
+                        float d = p * (__uint_as_float(dp[c]) - dl[e]);
+                        bool vis = key_live && (!a.causal || (kj <= q0 + c + a.causal_off));
+                        if (vis && a.keep_mask && (q0 + c) < a.Sq)
+                            vis = a.keep_mask[((int64_t)b * a.Sq + q0 + c) * a.Sk + kj] != 0.0f;
+                        if (a.use_clamp && sv >= a.clamp_raw) {
+                            p = fast_exp2(a.clamp_log2 - ls[e]);
+                            d = 0.f;
+                        }
+                        s[c] = __float_as_uint(vis ? p : 0.f);
+                        dp[c] = __float_as_uint(vis ? d : 0.f);
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int c4 = 0; c4 < 8; ++c4) {
+                    const float4 l4 = st4[c4];
+                    const float4 d4 = st4[32 + c4];
+                    const float ls[4] = {l4.x, l4.y, l4.z, l4.w};
+                    const float dl[4] = {d4.x, d4.y, d4.z, d4.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int c = 4 * c4 + e;
+                        const float p = fast_exp2(fmaf(__uint_as_float(s[c]), c2, -ls[e]));
+                        s[c] = __float_as_uint(p);
+                        dp[c] = __float_as_uint(p * (__uint_as_float(dp[c]) - dl[e]));
+                    }
+                }
+            }
+            uint32_t pt[16], dst[16], unused[16];
+            pack32<false>(s, pt, unused);
+            pack32<false>(dp, dst, unused);
+            if (it > 0) {
+                // the accumulations of the previous step must have read P^T and dS^T
+                ok = __all_sync(0xffffffffu, mbar_wait(bar_acc_done, (uint32_t)((it - 1) & 1), wc, 0xc1));
+                if (!ok) break;
+            }
+            tmem_st16(tP, pt);
+            tmem_st16(tDS, dst);
+            tmem_wait_st();
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_pds_full);
+        }
+        // epilogue: dV and scale * dK (zeros for tiles that no query can see)
+        if (ok && k0 < a.Sk) {
+            if (n_it > 0) {
+                ok = __all_sync(0xffffffffu, mbar_wait(bar_acc_done, (uint32_t)((n_it - 1) & 1), wc, 0xc2));
+                tc_fence_after_sync();
+            }
+            __nv_bfloat16* dkrow = reinterpret_cast<__nv_bfloat16*>(a.dk) + b * a.dks.batch + h * a.dks.head +
+                                   (int64_t)kj * a.dks.seq + cq * 16;
+            __nv_bfloat16* dvrow = reinterpret_cast<__nv_bfloat16*>(a.dv) + b * a.dvs.batch + h * a.dvs.head +
+                                   (int64_t)kj * a.dvs.seq + cq * 16;
+            uint32_t o[16];
+            if (n_it > 0 && ok) { tmem_ld16(tDV, o); tmem_wait_ld(); }
+            else {
+#pragma unroll
+                for (int c = 0; c < 16; ++c) o[c] = 0u;
+            }
+            if (kj < a.Sk) store_row16_bf16(dvrow, o, 1.0f);
+            if (n_it > 0 && ok) { tmem_ld16(tDK, o); tmem_wait_ld(); }
+            if (kj < a.Sk) store_row16_bf16(dkrow, o, a.scale);
+        }
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == kMmaWarp0) {
+        __syncwarp();
+        if (misc[1]) __nanosleep(200000);
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// 5. dQ, single-tile variant (bf16 operands and results): one CTA per 128 queries, key steps of
+// 128, nothing aliased:  S [0,128)  dP [128,256)  dS bf16 [256,320)  dQ [320,384).
+// Elementwise warp w owns query rows 32 (w % 4) .. +31 and key columns 32 (w / 4) .. +31 of the
+// step.  Warp 16 issues S and dP of the next step as soon as this step's are in registers,
+// warp 17 issues dQ += dS K_j.
+// ---------------------------------------------------------------------------------------------
+struct Dq4Smem {
+    static constexpr int kStages = 4;                         // ring of (K_j, V_j)
+    static constexpr int kStageBytes = 2 * kBigTile;
+    static constexpr int kQOff = 0;
+    static constexpr int kDoOff = kBigTile;
+    static constexpr int kRingOff = 2 * kBigTile;
+    static constexpr int kBarOff = kRingOff + kStages * kStageBytes;
+    // bars: qdo_full, ring_full[S], ring_empty[S], sdp_full, sdp_free, ds_full, dq_done
+    static constexpr int kNumBars = 1 + 2 * kStages + 4;
+    static constexpr int kMiscOff = kBarOff + kNumBars * 8;
+    static constexpr int kDynBytes = kMiscOff + 16 + 1024;
+};
+
+__global__ void __launch_bounds__(kThreads, 1)
+attn_bwd_dq4_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
+                          const __grid_constant__ CUtensorMap tmap_do,
+                          const __grid_constant__ CUtensorMap tmap_k,
+                          const __grid_constant__ CUtensorMap tmap_v, const BwdArgs a) {
+    using L = Dq4Smem;
+    constexpr int kKStep = 128;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    const uint32_t q_smem = smem_base + L::kQOff, do_smem = smem_base + L::kDoOff;
+    const uint32_t ring_smem = smem_base + L::kRingOff, bar_base = smem_base + L::kBarOff;
+    auto bar_qdo_full = [&]() { return bar_base; };
+    auto bar_ring_full = [&](int s) { return bar_base + 8u * (1 + s); };
+    auto bar_ring_empty = [&](int s) { return bar_base + 8u * (1 + L::kStages + s); };
+    const uint32_t bar_sdp_full = bar_base + 8u * (1 + 2 * L::kStages);
+    const uint32_t bar_sdp_free = bar_sdp_full + 8u;
+    const uint32_t bar_ds_full = bar_sdp_full + 16u;
+    const uint32_t bar_dq_done = bar_sdp_full + 24u;
+    volatile uint32_t* misc = reinterpret_cast<volatile uint32_t*>(smem_gen + L::kMiscOff);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m_block = gridDim.x - 1 - blockIdx.x;     // heavy (late) causal blocks first
+    const int h = blockIdx.y, b = blockIdx.z;
+    const int q0 = m_block * kTile;
+
+    int kvlen = a.Sk;
+    if (a.kv_len) kvlen = min(max(a.kv_len[b], 0), a.Sk);
+    int lim = 0;
+    if (q0 < a.Sq) {
+        lim = kvlen;
+        if (a.causal) lim = min(lim, min(q0 + kTile - 1, a.Sq - 1) + a.causal_off + 1);
+    }
+    const int n_it = lim > 0 ? (lim + kKStep - 1) / kKStep : 0;
+
+    if (threadIdx.x == 0) {
+        mbar_init(bar_qdo_full(), 1);
+        for (int s = 0; s < L::kStages; ++s) { mbar_init(bar_ring_full(s), 1); mbar_init(bar_ring_empty(s), 2); }
+        mbar_init(bar_sdp_full, 1);
+        mbar_init(bar_sdp_free, 16);               // one arrival per elementwise warp
+        mbar_init(bar_ds_full, 16);
+        mbar_init(bar_dq_done, 1);
+        misc[1] = 0u;
+        mbar_fence_init();
+    }
+    if (warp == kMmaWarp0) { tmem_alloc(smem_u32(const_cast<uint32_t*>(&misc[0])), kTmemCols); tmem_relinquish(); }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = misc[0];
+    const WaitCtx wc{&misc[1], a.status};
+    auto slot_of = [&](int it) { return it % L::kStages; };
+    auto phase_of = [&](int it) { return (uint32_t)((it / L::kStages) & 1); };
+
+    if (warp >= 16) {
+      reg_dealloc<kCtrlRegs>();
+      if (warp == kTmaWarp) {
+        if (lane == 0 && n_it > 0) {
+            mbar_arrive_expect_tx(bar_qdo_full(), 2u * kBigTile);
+            tma_load_4d(q_smem, &tmap_q, bar_qdo_full(), 0, q0, h, b);
+            tma_load_4d(do_smem, &tmap_do, bar_qdo_full(), 0, q0, h, b);
+            bool ok = true;
+            for (int it = 0; it < n_it && ok; ++it) {
+                ok = mbar_wait(bar_ring_empty(slot_of(it)), phase_of(it) ^ 1u, wc, 0xd0);
+                if (!ok) break;
+                const uint32_t st = ring_smem + slot_of(it) * L::kStageBytes;
+                const uint32_t bar = bar_ring_full(slot_of(it));
+                mbar_arrive_expect_tx(bar, 2u * kBigTile);
+                tma_load_4d(st, &tmap_k, bar, 0, it * kKStep, h, b);
+                tma_load_4d(st + kBigTile, &tmap_v, bar, 0, it * kKStep, h, b);
+            }
+        }
+      } else if (warp == kMmaWarp0) {
+        // S = Q K_j^T and dP = dO V_j^T, one step ahead of the elementwise warps
+        if (lane == 0 && n_it > 0) {
+            constexpr uint32_t idesc_s = make_idesc_bf16(kTile, kKStep, 0, 0);
+            const uint64_t q_desc = make_smem_desc_sw128(q_smem, 16, 1024);
+            const uint64_t do_desc = make_smem_desc_sw128(do_smem, 16, 1024);
+            const uint64_t ring_desc = make_smem_desc_sw128(ring_smem, 16, 1024);
+            auto issue_sdp = [&](int slot) {
+                const uint64_t kd = ring_desc + (uint64_t)((slot * L::kStageBytes) >> 4);
+                const uint64_t vd = kd + (uint64_t)(kBigTile >> 4);
+#pragma unroll
+                for (int k = 0; k < kD / 16; ++k) mma_ss(tmem_base, q_desc + 2 * k, kd + 2 * k, idesc_s, k > 0);
+#pragma unroll
+                for (int k = 0; k < kD / 16; ++k) mma_ss(tmem_base + 128, do_desc + 2 * k, vd + 2 * k, idesc_s, k > 0);
+            };
+            bool ok = mbar_wait(bar_qdo_full(), 0, wc, 0xe0);
+            ok = ok && mbar_wait(bar_ring_full(slot_of(0)), phase_of(0), wc, 0xe1);
+            if (ok) {
+                tc_fence_after_sync();
+                issue_sdp(slot_of(0));
+                mma_commit(bar_sdp_full);
+                mma_commit(bar_ring_empty(slot_of(0)));
+            }
+            for (int it = 0; it + 1 < n_it && ok; ++it) {
+                ok = mbar_wait(bar_ring_full(slot_of(it + 1)), phase_of(it + 1), wc, 0xe2);
+                ok = ok && mbar_wait(bar_sdp_free, (uint32_t)(it & 1), wc, 0xe3);
+                if (!ok) break;
+                tc_fence_after_sync();
+                issue_sdp(slot_of(it + 1));
+                mma_commit(bar_sdp_full);
+                mma_commit(bar_ring_empty(slot_of(it + 1)));
+            }
+            // all of this thread's contractions are complete once the last S / dP has been consumed
+            if (ok) ok = mbar_wait(bar_sdp_full, (uint32_t)((n_it - 1) & 1), wc, 0xe4);
+        }
+      } else if (warp == kMmaWarp0 + 1) {
+        // dQ += dS K_j   (dS from tensor memory, K_j rows as the contraction index)
+        if (lane == 0 && n_it > 0) {
+            constexpr uint32_t idesc_dq = make_idesc_bf16(kTile, kD, 0, 1);
+            const uint64_t ring_desc_mn = make_smem_desc_sw128(ring_smem, 8192, 1024);
+            bool ok = true;
+            for (int it = 0; it < n_it && ok; ++it) {
+                ok = mbar_wait(bar_ring_full(slot_of(it)), phase_of(it), wc, 0xe8);
+                ok = ok && mbar_wait(bar_ds_full, (uint32_t)(it & 1), wc, 0xe9);
+                if (!ok) break;
+                tc_fence_after_sync();
+                const uint64_t kd = ring_desc_mn + (uint64_t)((slot_of(it) * L::kStageBytes) >> 4);
+#pragma unroll
+                for (int k = 0; k < kKStep / 16; ++k)
+                    mma_ts(tmem_base + 320, tmem_base + 256 + k * 8, kd + 128 * k, idesc_dq,
+                           (it > 0 || k > 0) ? 1u : 0u);
+                mma_commit(bar_dq_done);
+                mma_commit(bar_ring_empty(slot_of(it)));
+            }
+            if (ok) ok = mbar_wait(bar_dq_done, (uint32_t)((n_it - 1) & 1), wc, 0xea);
+        }
+      }
+    } else {
+        reg_alloc<kMathRegs>();
+        const int wq = warp & 3, cq = warp >> 2;
+        const int row = wq * 32 + lane;
+        const int qi = q0 + row;
+        const uint32_t lane_base = (uint32_t)(wq * 32) << 16;
+        const uint32_t tS = tmem_base + lane_base + 32 * cq;
+        const uint32_t tDP = tS + 128;
+        const uint32_t tDS = tmem_base + lane_base + 256 + 16 * cq;
+        const uint32_t tDQ = tmem_base + lane_base + 320 + 16 * cq;
+        const float c2 = a.scale_log2;
+        const bool general = (a.keep_mask != nullptr) || (a.use_clamp != 0);
+        const int64_t srow = ((int64_t)b * a.H + h) * a.Sq_pad + qi;      // qi < Sq_pad by construction
+        const float lse2 = a.lse2[srow];
+        const float dlt = a.delta[srow];
+
+        bool ok = true;
+        for (int it = 0; it < n_it; ++it) {
+            ok = __all_sync(0xffffffffu, mbar_wait(bar_sdp_full, (uint32_t)(it & 1), wc, 0xf0));
+            if (!ok) break;
+            tc_fence_after_sync();
+            uint32_t s[32], dp[32];
+            tmem_ld32(tS, s);
+            tmem_ld32(tDP, dp);
+            tmem_wait_ld();
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_sdp_free);
+            const int k0 = it * kKStep;
+            const bool edge = (k0 + kKStep > kvlen) || (a.causal && (k0 + kKStep - 1 > q0 + a.causal_off));
+            // dS = P o (dP - delta), left in dp[]; the masked variant only runs on edge steps
+            if (edge || general) {
+                int vis_lim = kvlen;
+                if (a.causal) vis_lim = min(vis_lim, qi + a.causal_off + 1);
+                vis_lim -= k0 + cq * 32;
+                const float* mrow = nullptr;
+                if (a.keep_mask && qi < a.Sq)
+                    mrow = a.keep_mask + ((int64_t)b * a.Sq + qi) * a.Sk + k0 + cq * 32;
+#pragma unroll
+                for (int c = 0; c < 32; ++c) {
+                    const float sv = __uint_as_float(s[c]);
+                    const float p = fast_exp2(fmaf(sv, c2, -lse2));
+                    float d = p * (__uint_as_float(dp[c]) - dlt);
+                    bool vis = c < vis_lim;
+                    if (mrow && vis) vis = (__ldg(mrow + c) != 0.0f);
+                    if (a.use_clamp && sv >= a.clamp_raw) d = 0.f;
+                    dp[c] = __float_as_uint(vis ? d : 0.f);
+                }
+            } else {
+#pragma unroll
+                for (int c = 0; c < 32; ++c) {
+                    const float p = fast_exp2(fmaf(__uint_as_float(s[c]), c2, -lse2));
+                    dp[c] = __float_as_uint(p * (__uint_as_float(dp[c]) - dlt));
+                }
+            }
+            uint32_t hi[16], unused[16];
+            pack32<false>(dp, hi, unused);
+            if (it > 0) {
+                // the previous dS must have been consumed before it is overwritten
+                ok = __all_sync(0xffffffffu, mbar_wait(bar_dq_done, (uint32_t)((it - 1) & 1), wc, 0xf1));
+                if (!ok) break;
+            }
+            tmem_st16(tDS, hi);
+            tmem_wait_st();
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_ds_full);
+        }
+        if (ok && q0 < a.Sq) {
+            if (n_it > 0) {
+                ok = __all_sync(0xffffffffu, mbar_wait(bar_dq_done, (uint32_t)((n_it - 1) & 1), wc, 0xf2));
+                tc_fence_after_sync();
+            }
+            __nv_bfloat16* drow = reinterpret_cast<__nv_bfloat16*>(a.dq) + b * a.dqs.batch + h * a.dqs.head +
+                                  (int64_t)qi * a.dqs.seq + cq * 16;
+            uint32_t o[16];
+            if (n_it > 0 && ok) { tmem_ld16(tDQ, o); tmem_wait_ld(); }
+            else {
+#pragma unroll
+                for (int c = 0; c < 16; ++c) o[c] = 0u;
+            }
+            if (qi < a.Sq) store_row16_bf16(drow, o, a.scale);
+        }
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == kMmaWarp0) {
+        __syncwarp();
+        if (misc[1]) __nanosleep(200000);
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
 }  // namespace
 
 #ifdef LTCA_TRACE
@@ -853,9 +1395,44 @@ int launch_main(ltca_ctx* ctx, const ltca_attn_params* p, const void* q, const v
         LTCA_CUDA_OK(ctx, cudaFuncSetAttribute(kdkv, cudaFuncAttributeMaxDynamicSharedMemorySize, DkvSmem::kDynBytes));
         attr_done = true;
     }
-    dim3 gq((p->Sq + 2 * kTile - 1) / (2 * kTile), p->H, p->B);
-    kdq<<<gq, kThreads, DqSmem::kDynBytes, ctx->stream>>>(tq128, tdo128, tk64, tv64, a);
-    LTCA_LAUNCH_OK(ctx, "attn_bwd_dq_sm100_kernel");
+    bool dq_launched = false;
+    if constexpr (sizeof(OutT) == 2) {
+        if (LTCA_BWD_DQ4) {
+            static bool attr4q_done = false;
+            if (!attr4q_done) {
+                LTCA_CUDA_OK(ctx, cudaFuncSetAttribute(attn_bwd_dq4_sm100_kernel,
+                                                       cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                       Dq4Smem::kDynBytes));
+                attr4q_done = true;
+            }
+            dim3 g4((p->Sq + kTile - 1) / kTile, p->H, p->B);
+            attn_bwd_dq4_sm100_kernel<<<g4, kThreads, Dq4Smem::kDynBytes, ctx->stream>>>(tq128, tdo128, tk128,
+                                                                                         tv128, a);
+            LTCA_LAUNCH_OK(ctx, "attn_bwd_dq4_sm100_kernel");
+            dq_launched = true;
+        }
+    }
+    if (!dq_launched) {
+        dim3 gq((p->Sq + 2 * kTile - 1) / (2 * kTile), p->H, p->B);
+        kdq<<<gq, kThreads, DqSmem::kDynBytes, ctx->stream>>>(tq128, tdo128, tk64, tv64, a);
+        LTCA_LAUNCH_OK(ctx, "attn_bwd_dq_sm100_kernel");
+    }
+    if constexpr (sizeof(OutT) == 2) {
+        if (LTCA_BWD_DKV4) {
+            static bool attr4_done = false;
+            if (!attr4_done) {
+                LTCA_CUDA_OK(ctx, cudaFuncSetAttribute(attn_bwd_dkv4_sm100_kernel,
+                                                       cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                       Dkv4Smem::kDynBytes));
+                attr4_done = true;
+            }
+            dim3 g4((p->Sk + kTile - 1) / kTile, p->H, p->B);
+            attn_bwd_dkv4_sm100_kernel<<<g4, kThreads, Dkv4Smem::kDynBytes, ctx->stream>>>(tq128, tdo128, tk128,
+                                                                                           tv128, a);
+            LTCA_LAUNCH_OK(ctx, "attn_bwd_dkv4_sm100_kernel");
+            return LTCA_OK;
+        }
+    }
     dim3 gk((p->Sk + 2 * kTile - 1) / (2 * kTile), p->H, p->B);
     kdkv<<<gk, kThreads, DkvSmem::kDynBytes, ctx->stream>>>(tq64, tdo64, tk128, tv128, a);
     LTCA_LAUNCH_OK(ctx, "attn_bwd_dkv_sm100_kernel");
