@@ -26,6 +26,12 @@
 #include "sm100_ptx.cuh"
 #include "trace.cuh"
 
+#ifndef LTCA_BWD_TURNS
+#define LTCA_BWD_TURNS 0
+#endif
+#ifndef LTCA_EXP_PAIRS
+#define LTCA_EXP_PAIRS 0
+#endif
 #ifndef LTCA_BWD_DQ4
 #define LTCA_BWD_DQ4 1
 #endif
@@ -393,7 +399,7 @@ attn_bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
 
         bool ok = true;
         for (int j = 0; j < n_t; ++j) {
-            ok = __all_sync(0xffffffffu, mbar_wait(bar_sdp_full(t), (uint32_t)(j & 1), wc, 0x60 + t));
+            ok = mbar_wait_warp(bar_sdp_full(t), (uint32_t)(j & 1), wc, 0x60 + t);
             if (!ok) break;
             tc_fence_after_sync();
             LTCA_TRACE_EVT(0x10 + (j << 8));
@@ -408,7 +414,7 @@ attn_bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
             // One-time delay of tile 1: from then on one tile's exponentials overlap the other
             // tile's loads, stores and barrier traffic instead of all warps stalling together.
             if (LTCA_BWD_STAGGER && t == 1 && j == 0 && n_steps[0] > 0) {
-                ok = __all_sync(0xffffffffu, mbar_wait(bar_stagger(), 0, wc, 0x66));
+                ok = mbar_wait_warp(bar_stagger(), 0, wc, 0x66);
                 if (!ok) break;
             }
             const int k0 = j * kStep;
@@ -447,7 +453,7 @@ attn_bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
             LTCA_TRACE_EVT(0x12 + (j << 8));
             if (j > 0) {
                 // the previous dS must have been consumed before it is overwritten
-                ok = __all_sync(0xffffffffu, mbar_wait(bar_dq_done(t), (uint32_t)((j - 1) & 1), wc, 0x64 + t));
+                ok = mbar_wait_warp(bar_dq_done(t), (uint32_t)((j - 1) & 1), wc, 0x64 + t);
                 if (!ok) break;
             }
             tmem_st16(tDS, hi);
@@ -460,7 +466,7 @@ attn_bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
         }
         if (ok && q0 < a.Sq) {
             if (n_t > 0) {
-                ok = __all_sync(0xffffffffu, mbar_wait(bar_dq_done(t), (uint32_t)((n_t - 1) & 1), wc, 0x62 + t));
+                ok = mbar_wait_warp(bar_dq_done(t), (uint32_t)((n_t - 1) & 1), wc, 0x62 + t);
                 tc_fence_after_sync();
             }
             OutT* drow = reinterpret_cast<OutT*>(a.dq) + b * a.dqs.batch + h * a.dqs.head +
@@ -685,7 +691,7 @@ attn_bwd_dkv_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
         if (active[t]) {
             for (int j = j_begin[t]; j < n_q; ++j) {
                 const int it = j - j_begin[t];
-                ok = __all_sync(0xffffffffu, mbar_wait(bar_sdp_full(t), (uint32_t)(it & 1), wc, 0x90 + t));
+                ok = mbar_wait_warp(bar_sdp_full(t), (uint32_t)(it & 1), wc, 0x90 + t);
                 if (!ok) break;
                 tc_fence_after_sync();
                 LTCA_TRACE_EVT(0x10 + (j << 8));
@@ -695,7 +701,7 @@ attn_bwd_dkv_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 tmem_wait_ld();
                 LTCA_TRACE_EVT(0x11 + (j << 8));
                 if (LTCA_BWD_STAGGER && t == 1 && it == 0 && active[0] && j_begin[0] <= j_begin[1]) {
-                    ok = __all_sync(0xffffffffu, mbar_wait(bar_stagger(), 0, wc, 0x96));
+                    ok = mbar_wait_warp(bar_stagger(), 0, wc, 0x96);
                     if (!ok) break;
                 }
                 // lse2 and delta of this thread's 32 query columns (broadcast reads: every lane
@@ -771,8 +777,7 @@ attn_bwd_dkv_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
         // epilogue: dV and scale * dK (zeros for tiles that no query can see)
         if (ok && k0 < a.Sk) {
             if (active[t]) {
-                ok = __all_sync(0xffffffffu,
-                                mbar_wait(bar_acc_done(t), (uint32_t)((n_q - 1 - j_begin[t]) & 1), wc, 0x92 + t));
+                ok = mbar_wait_warp(bar_acc_done(t), (uint32_t)((n_q - 1 - j_begin[t]) & 1), wc, 0x92 + t);
                 tc_fence_after_sync();
             }
             OutT* dkrow = reinterpret_cast<OutT*>(a.dk) + b * a.dks.batch + h * a.dks.head +
@@ -817,8 +822,8 @@ struct Dkv4Smem {
     static constexpr int kVOff = kBigTile;
     static constexpr int kRingOff = 2 * kBigTile;
     static constexpr int kBarOff = kRingOff + kStages * kStageBytes;
-    // bars: kv_full, ring_full[S], ring_empty[S], sdp_full, sdp_free, pds_full, acc_done
-    static constexpr int kNumBars = 1 + 2 * kStages + 4;
+    // bars: kv_full, ring_full[S], ring_empty[S], sdp_full, sdp_free, pds_full, acc_done, turn
+    static constexpr int kNumBars = 1 + 2 * kStages + 5;
     static constexpr int kMiscOff = kBarOff + kNumBars * 8;
     static constexpr int kDynBytes = kMiscOff + 16 + 1024;
 };
@@ -855,11 +860,12 @@ attn_bwd_dkv4_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
     const uint32_t bar_sdp_free = bar_sdp_full + 8u;
     const uint32_t bar_pds_full = bar_sdp_full + 16u;
     const uint32_t bar_acc_done = bar_sdp_full + 24u;
+    const uint32_t bar_turn = bar_sdp_full + 32u;
     volatile uint32_t* misc = reinterpret_cast<volatile uint32_t*>(smem_gen + L::kMiscOff);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n_block = blockIdx.x;                 // early key blocks carry the most causal work
-    const int h = blockIdx.y, b = blockIdx.z;
+    int n_block, h, b;
+    sched_block(n_block, h, b);                     // early key blocks carry the most causal work
     const int k0 = n_block * kTile;
 
     int kvlen = a.Sk;
@@ -877,6 +883,7 @@ attn_bwd_dkv4_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
         mbar_init(bar_sdp_free, 16);               // one arrival per elementwise warp
         mbar_init(bar_pds_full, 16);
         mbar_init(bar_acc_done, 2);
+        mbar_init(bar_turn, 8);
         misc[1] = 0u;
         mbar_fence_init();
     }
@@ -988,7 +995,7 @@ attn_bwd_dkv4_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
         bool ok = true;
         for (int it = 0; it < n_it; ++it) {
             const int j = j_begin + it;
-            ok = __all_sync(0xffffffffu, mbar_wait(bar_sdp_full, (uint32_t)(it & 1), wc, 0xc0));
+            ok = mbar_wait_warp(bar_sdp_full, (uint32_t)(it & 1), wc, 0xc0);
             if (!ok) break;
             tc_fence_after_sync();
             uint32_t s[32], dp[32];
@@ -999,6 +1006,11 @@ attn_bwd_dkv4_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_sdp_free);
+            // the warps of query columns 64..127 take their turn after those of columns 0..63
+            if (LTCA_BWD_TURNS && cq >= 2) {
+                ok = mbar_wait_warp(bar_turn, (uint32_t)(it & 1), wc, 0xc3);
+                if (!ok) break;
+            }
             // lse2 and delta of this thread's 32 query columns (every lane reads the same address)
             const float4* st4 = reinterpret_cast<const float4*>(
                 smem_gen + L::kRingOff + slot_of(it) * L::kStageBytes + 2 * kBigTile) + cq * 8;
@@ -1049,9 +1061,13 @@ attn_bwd_dkv4_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
             uint32_t pt[16], dst[16], unused[16];
             pack32<false>(s, pt, unused);
             pack32<false>(dp, dst, unused);
+            if (LTCA_BWD_TURNS && cq < 2) {
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_turn);
+            }
             if (it > 0) {
                 // the accumulations of the previous step must have read P^T and dS^T
-                ok = __all_sync(0xffffffffu, mbar_wait(bar_acc_done, (uint32_t)((it - 1) & 1), wc, 0xc1));
+                ok = mbar_wait_warp(bar_acc_done, (uint32_t)((it - 1) & 1), wc, 0xc1);
                 if (!ok) break;
             }
             tmem_st16(tP, pt);
@@ -1064,7 +1080,7 @@ attn_bwd_dkv4_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
         // epilogue: dV and scale * dK (zeros for tiles that no query can see)
         if (ok && k0 < a.Sk) {
             if (n_it > 0) {
-                ok = __all_sync(0xffffffffu, mbar_wait(bar_acc_done, (uint32_t)((n_it - 1) & 1), wc, 0xc2));
+                ok = mbar_wait_warp(bar_acc_done, (uint32_t)((n_it - 1) & 1), wc, 0xc2);
                 tc_fence_after_sync();
             }
             __nv_bfloat16* dkrow = reinterpret_cast<__nv_bfloat16*>(a.dk) + b * a.dks.batch + h * a.dks.head +
@@ -1107,8 +1123,8 @@ struct Dq4Smem {
     static constexpr int kDoOff = kBigTile;
     static constexpr int kRingOff = 2 * kBigTile;
     static constexpr int kBarOff = kRingOff + kStages * kStageBytes;
-    // bars: qdo_full, ring_full[S], ring_empty[S], sdp_full, sdp_free, ds_full, dq_done
-    static constexpr int kNumBars = 1 + 2 * kStages + 4;
+    // bars: qdo_full, ring_full[S], ring_empty[S], sdp_full, sdp_free, ds_full, dq_done, turn
+    static constexpr int kNumBars = 1 + 2 * kStages + 5;
     static constexpr int kMiscOff = kBarOff + kNumBars * 8;
     static constexpr int kDynBytes = kMiscOff + 16 + 1024;
 };
@@ -1132,11 +1148,13 @@ attn_bwd_dq4_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
     const uint32_t bar_sdp_free = bar_sdp_full + 8u;
     const uint32_t bar_ds_full = bar_sdp_full + 16u;
     const uint32_t bar_dq_done = bar_sdp_full + 24u;
+    const uint32_t bar_turn = bar_sdp_full + 32u;
     volatile uint32_t* misc = reinterpret_cast<volatile uint32_t*>(smem_gen + L::kMiscOff);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m_block = gridDim.x - 1 - blockIdx.x;     // heavy (late) causal blocks first
-    const int h = blockIdx.y, b = blockIdx.z;
+    int rank, h, b;
+    sched_block(rank, h, b);
+    const int m_block = gridDim.x - 1 - rank;           // heavy (late) causal blocks first
     const int q0 = m_block * kTile;
 
     int kvlen = a.Sk;
@@ -1155,6 +1173,7 @@ attn_bwd_dq4_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
         mbar_init(bar_sdp_free, 16);               // one arrival per elementwise warp
         mbar_init(bar_ds_full, 16);
         mbar_init(bar_dq_done, 1);
+        mbar_init(bar_turn, 8);
         misc[1] = 0u;
         mbar_fence_init();
     }
@@ -1166,6 +1185,8 @@ attn_bwd_dq4_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
     const WaitCtx wc{&misc[1], a.status};
     auto slot_of = [&](int it) { return it % L::kStages; };
     auto phase_of = [&](int it) { return (uint32_t)((it / L::kStages) & 1); };
+    LTCA_TRACE_DECL(LTCA_TRACE_KERNEL == 3 && blockIdx.x == 0 && blockIdx.y == 5 && blockIdx.z == 0);
+    LTCA_TRACE_EVT(0x01);
 
     if (warp >= 16) {
       reg_dealloc<kCtrlRegs>();
@@ -1213,9 +1234,11 @@ attn_bwd_dq4_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 ok = ok && mbar_wait(bar_sdp_free, (uint32_t)(it & 1), wc, 0xe3);
                 if (!ok) break;
                 tc_fence_after_sync();
+                LTCA_TRACE_EVT(0x20 + (it << 8));
                 issue_sdp(slot_of(it + 1));
                 mma_commit(bar_sdp_full);
                 mma_commit(bar_ring_empty(slot_of(it + 1)));
+                LTCA_TRACE_EVT(0x21 + (it << 8));
             }
             // all of this thread's contractions are complete once the last S / dP has been consumed
             if (ok) ok = mbar_wait(bar_sdp_full, (uint32_t)((n_it - 1) & 1), wc, 0xe4);
@@ -1231,6 +1254,7 @@ attn_bwd_dq4_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 ok = ok && mbar_wait(bar_ds_full, (uint32_t)(it & 1), wc, 0xe9);
                 if (!ok) break;
                 tc_fence_after_sync();
+                LTCA_TRACE_EVT(0x22 + (it << 8));
                 const uint64_t kd = ring_desc_mn + (uint64_t)((slot_of(it) * L::kStageBytes) >> 4);
 #pragma unroll
                 for (int k = 0; k < kKStep / 16; ++k)
@@ -1238,6 +1262,7 @@ attn_bwd_dq4_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
                            (it > 0 || k > 0) ? 1u : 0u);
                 mma_commit(bar_dq_done);
                 mma_commit(bar_ring_empty(slot_of(it)));
+                LTCA_TRACE_EVT(0x23 + (it << 8));
             }
             if (ok) ok = mbar_wait(bar_dq_done, (uint32_t)((n_it - 1) & 1), wc, 0xea);
         }
@@ -1260,9 +1285,10 @@ attn_bwd_dq4_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
 
         bool ok = true;
         for (int it = 0; it < n_it; ++it) {
-            ok = __all_sync(0xffffffffu, mbar_wait(bar_sdp_full, (uint32_t)(it & 1), wc, 0xf0));
+            ok = mbar_wait_warp(bar_sdp_full, (uint32_t)(it & 1), wc, 0xf0);
             if (!ok) break;
             tc_fence_after_sync();
+            LTCA_TRACE_EVT(0x10 + (it << 8));
             uint32_t s[32], dp[32];
             tmem_ld32(tS, s);
             tmem_ld32(tDP, dp);
@@ -1270,6 +1296,14 @@ attn_bwd_dq4_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_sdp_free);
+            LTCA_TRACE_EVT(0x11 + (it << 8));
+            // The warps of key columns 64..127 take their turn at the exponentials after those of
+            // columns 0..63, so that each half's loads, stores and barrier traffic overlap the
+            // other half's arithmetic instead of all sixteen warps stalling together.
+            if (LTCA_BWD_TURNS && cq >= 2) {
+                ok = mbar_wait_warp(bar_turn, (uint32_t)(it & 1), wc, 0xf3);
+                if (!ok) break;
+            }
             const int k0 = it * kKStep;
             const bool edge = (k0 + kKStep > kvlen) || (a.causal && (k0 + kKStep - 1 > q0 + a.causal_off));
             // dS = P o (dP - delta), left in dp[]; the masked variant only runs on edge steps
@@ -1291,28 +1325,46 @@ attn_bwd_dq4_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
                     dp[c] = __float_as_uint(vis ? d : 0.f);
                 }
             } else {
+#if LTCA_EXP_PAIRS
+#pragma unroll
+                for (int c = 0; c < 32; c += 2) {
+                    float p0, p1;
+                    exp2_pair(fmaf(__uint_as_float(s[c]), c2, -lse2), fmaf(__uint_as_float(s[c + 1]), c2, -lse2),
+                              p0, p1);
+                    dp[c] = __float_as_uint(p0 * (__uint_as_float(dp[c]) - dlt));
+                    dp[c + 1] = __float_as_uint(p1 * (__uint_as_float(dp[c + 1]) - dlt));
+                }
+#else
 #pragma unroll
                 for (int c = 0; c < 32; ++c) {
                     const float p = fast_exp2(fmaf(__uint_as_float(s[c]), c2, -lse2));
                     dp[c] = __float_as_uint(p * (__uint_as_float(dp[c]) - dlt));
                 }
+#endif
             }
             uint32_t hi[16], unused[16];
             pack32<false>(dp, hi, unused);
+            if (LTCA_BWD_TURNS && cq < 2) {
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_turn);
+            }
+            LTCA_TRACE_EVT(0x12 + (it << 8));
             if (it > 0) {
                 // the previous dS must have been consumed before it is overwritten
-                ok = __all_sync(0xffffffffu, mbar_wait(bar_dq_done, (uint32_t)((it - 1) & 1), wc, 0xf1));
+                ok = mbar_wait_warp(bar_dq_done, (uint32_t)((it - 1) & 1), wc, 0xf1);
                 if (!ok) break;
             }
+            LTCA_TRACE_EVT(0x14 + (it << 8));
             tmem_st16(tDS, hi);
             tmem_wait_st();
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_ds_full);
+            LTCA_TRACE_EVT(0x13 + (it << 8));
         }
         if (ok && q0 < a.Sq) {
             if (n_it > 0) {
-                ok = __all_sync(0xffffffffu, mbar_wait(bar_dq_done, (uint32_t)((n_it - 1) & 1), wc, 0xf2));
+                ok = mbar_wait_warp(bar_dq_done, (uint32_t)((n_it - 1) & 1), wc, 0xf2);
                 tc_fence_after_sync();
             }
             __nv_bfloat16* drow = reinterpret_cast<__nv_bfloat16*>(a.dq) + b * a.dqs.batch + h * a.dqs.head +

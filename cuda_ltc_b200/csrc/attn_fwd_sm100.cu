@@ -330,7 +330,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
         float l_run = 0.f;
         bool ok = true;
         for (int j = 0; j < n_t; ++j) {
-            ok = __all_sync(0xffffffffu, mbar_wait(bar_s_full(t), (uint32_t)(j & 1), wc, 0x30 + t));
+            ok = mbar_wait_warp(bar_s_full(t), (uint32_t)(j & 1), wc, 0x30 + t);
             if (!ok) break;
             tc_fence_after_sync();
             LTCA_TRACE_EVT(0x10 + (j << 8));
@@ -379,7 +379,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
 #else
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar_pair(t, wq));
-                ok = __all_sync(0xffffffffu, mbar_wait(bar_pair(t, wq), pair_phase, wc, 0x3a));
+                ok = mbar_wait_warp(bar_pair(t, wq), pair_phase, wc, 0x3a);
                 pair_phase ^= 1u;
                 if (!ok) break;
 #endif
@@ -400,8 +400,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
             }
             bool o_waited = (j == 0);
             if (j > 0 && __any_sync(0xffffffffu, need)) {
-                ok = __all_sync(0xffffffffu,
-                                mbar_wait(bar_o_done(t), (uint32_t)((j - 1) & 1), wc, 0x32 + t));
+                ok = mbar_wait_warp(bar_o_done(t), (uint32_t)((j - 1) & 1), wc, 0x32 + t);
                 if (!ok) break;
                 o_waited = true;
                 tc_fence_after_sync();
@@ -423,12 +422,12 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
             if (LTCA_FWD_PINGPONG == 2) {
                 // one-time delay: tile 1 starts its first exponentials when tile 0 has finished its own
                 if (t == 1 && j == 0 && n_tiles[0] > 0) {
-                    ok = __all_sync(0xffffffffu, mbar_wait(bar_turn(0), 0, wc, 0x3e));
+                    ok = mbar_wait_warp(bar_turn(0), 0, wc, 0x3e);
                     if (!ok) break;
                 }
             } else if (LTCA_FWD_PINGPONG == 1 && (t == 0 ? (j > 0 && j - 1 < n_tiles[1]) : (j < n_tiles[0]))) {
                 const uint32_t par = (uint32_t)((t == 0 ? j - 1 : j) & 1);
-                ok = __all_sync(0xffffffffu, mbar_wait(bar_turn(t ^ 1), par, wc, 0x3c + t));
+                ok = mbar_wait_warp(bar_turn(t ^ 1), par, wc, 0x3c + t);
                 if (!ok) break;
             }
             LTCA_TRACE_EVT(0x15 + (j << 8));
@@ -463,8 +462,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 }
                 if (ch == 0 && !o_waited) {
                     // P of the previous step must have been consumed before it is overwritten
-                    ok = __all_sync(0xffffffffu,
-                                    mbar_wait(bar_o_done(t), (uint32_t)((j - 1) & 1), wc, 0x36 + t));
+                    ok = mbar_wait_warp(bar_o_done(t), (uint32_t)((j - 1) & 1), wc, 0x36 + t);
                     if (!ok) break;
                 }
                 tmem_st16(tP + ch * 16, hi);
@@ -497,12 +495,11 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
 #else
                     __syncwarp();
                     if (lane == 0) mbar_arrive(bar_pair(t, wq));
-                    ok = __all_sync(0xffffffffu, mbar_wait(bar_pair(t, wq), pair_phase, wc, 0x3b));
+                    ok = mbar_wait_warp(bar_pair(t, wq), pair_phase, wc, 0x3b);
 #endif
                     if (ok) l_run += *xslot(2, half ^ 1);
                 }
-                ok = ok && __all_sync(0xffffffffu,
-                                      mbar_wait(bar_o_done(t), (uint32_t)((n_t - 1) & 1), wc, 0x34 + t));
+                ok = ok && mbar_wait_warp(bar_o_done(t), (uint32_t)((n_t - 1) & 1), wc, 0x34 + t);
                 tc_fence_after_sync();
                 if (l_run > 0.f) {
                     inv = 1.0f / l_run;
@@ -617,9 +614,9 @@ attn_fwd4_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int m_block = gridDim.x - 1 - blockIdx.x;     // heavy (late) causal blocks first
-    const int h = blockIdx.y;
-    const int b = blockIdx.z;
+    int rank, h, b;
+    sched_block(rank, h, b);
+    const int m_block = gridDim.x - 1 - rank;           // heavy (late) causal blocks first
 
     int kvlen = a.Sk;
     if (a.kv_len) kvlen = min(max(a.kv_len[b], 0), a.Sk);
@@ -767,7 +764,7 @@ attn_fwd4_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
         float l_run = 0.f;
         bool ok = true;
         for (int j = 0; j < n_t; ++j) {
-            ok = __all_sync(0xffffffffu, mbar_wait(bar_s_full(t), (uint32_t)(j & 1), wc, 0x30 + t));
+            ok = mbar_wait_warp(bar_s_full(t), (uint32_t)(j & 1), wc, 0x30 + t);
             if (!ok) break;
             tc_fence_after_sync();
             uint32_t su[kBN];
@@ -858,7 +855,7 @@ attn_fwd4_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
             float inv = 0.f;
             float lse = neg_inf();
             if (n_t > 0) {
-                ok = __all_sync(0xffffffffu, mbar_wait(bar_s_full(t), (uint32_t)(n_t & 1), wc, 0x34 + t));
+                ok = mbar_wait_warp(bar_s_full(t), (uint32_t)(n_t & 1), wc, 0x34 + t);
                 tc_fence_after_sync();
                 if (l_run > 0.f) {
                     inv = 1.0f / l_run;

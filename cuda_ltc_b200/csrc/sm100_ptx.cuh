@@ -105,6 +105,13 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const W
     }
 }
 
+// Whole-warp wait: every lane polls (measured on B200: electing one lane to poll and
+// broadcasting the outcome is slower than letting the 32 lanes poll together).
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, const WaitCtx& w,
+                                               uint32_t where) {
+    return __all_sync(0xffffffffu, mbar_wait(bar, parity, w, where));
+}
+
 // ---- TMA ------------------------------------------------------------------------------------
 __device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tmap)) : "memory");
@@ -300,6 +307,24 @@ __device__ __forceinline__ void reg_dealloc() {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
 }
 
+// ---- CTA order for causal work ----------------------------------------------------------------
+// Thread blocks start in the order of their linear index.  The (batch, head) pairs are taken in
+// groups of kSchedGroup; inside a group every pair's heaviest block starts first, then every
+// pair's second heaviest, and so on, so the long blocks of a launch never start last (short
+// tail), while one group's K / V / Q / dO (a few tens of MB) stay resident in L2.
+constexpr int kSchedGroup = 16;
+__device__ __forceinline__ void sched_block(int& rank, int& h, int& b) {
+    const int nblk = gridDim.x, H = gridDim.y, BH = gridDim.y * gridDim.z;
+    const int linear = blockIdx.x + nblk * (blockIdx.y + H * blockIdx.z);
+    const int g = linear / (kSchedGroup * nblk);
+    const int n_in = min(kSchedGroup, BH - g * kSchedGroup);
+    const int local = linear - g * kSchedGroup * nblk;
+    rank = local / n_in;
+    const int bh = g * kSchedGroup + local % n_in;
+    h = bh % H;
+    b = bh / H;
+}
+
 // ---- small math helpers -----------------------------------------------------------------------
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
     float d;
@@ -310,6 +335,26 @@ __device__ __forceinline__ float fast_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
+}
+// Two exponentials per special-function instruction: the arguments travel as an f16 pair.
+// With |x| < 16 the argument's rounding error is below 2^-7, i.e. below the rounding error of
+// the bf16 value the result is stored as, wherever the result is large enough to matter.
+__device__ __forceinline__ void exp2_pair(float x0, float x1, float& p0, float& p1) {
+    uint32_t h;
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(h) : "f"(x1), "f"(x0));
+    asm("ex2.approx.f16x2 %0, %1;" : "=r"(h) : "r"(h));
+    asm("{\n\t.reg .b16 lo, hi;\n\t"
+        "mov.b32 {lo, hi}, %2;\n\t"
+        "cvt.f32.f16 %0, lo;\n\t"
+        "cvt.f32.f16 %1, hi;\n\t}\n"
+        : "=f"(p0), "=f"(p1) : "r"(h));
+}
+// Same, result left as the f16 pair (element 0 in the low half).
+__device__ __forceinline__ uint32_t exp2_pair_f16(float x0, float x1) {
+    uint32_t h;
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(h) : "f"(x1), "f"(x0));
+    asm("ex2.approx.f16x2 %0, %1;" : "=r"(h) : "r"(h));
+    return h;
 }
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     uint32_t r;
