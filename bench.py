@@ -240,6 +240,22 @@ def main():
     bwd_ms = sum(e[1].elapsed_time(e[2]) for e in ev) / K
     status = ctx.device_status()
 
+    # ---- per-kernel durations of the backward (events recorded inside the library on the same stream) --
+    kern_ms = None
+    if bwd_tensor:
+        ctx.enable_kernel_timing(True)
+        acc = [0.0, 0.0, 0.0]
+        Kk = max(3, min(K, 10))
+        with torch.cuda.stream(stream):
+            for _ in range(Kk):
+                ctx.attn_fwd(q, k, v, causal=True, mode=_lib.MODE_BF16, out=o, lse=lse)
+                ctx.attn_bwd(q, k, v, o, lse, do, causal=True, mode=_lib.MODE_AUTO, dq=dq, dk=dk, dv=dv)
+                for i, x in enumerate(ctx.last_bwd_kernel_ms()):
+                    acc[i] += x
+        ctx.enable_kernel_timing(False)
+        kern_ms = [x / Kk for x in acc]
+        barrier()
+
     # ---- end to end: host buffers in, results back, through the same public call ---------------
     e2e = None
     if not args.no_e2e:
@@ -269,11 +285,11 @@ def main():
         e2e = (e2e_ms, 4 * nbytes, 4 * nbytes)
 
     # ---- max over ranks --------------------------------------------------------------------------
-    vals = torch.tensor([total_ms, fwd_ms, bwd_ms, e2e[0] if e2e else 0.0, float(status)],
-                        dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(vals, op=dist.ReduceOp.MAX)
-    total_ms, fwd_ms, bwd_ms, e2e_ms, status = vals.tolist()
+    from cuda_ltc_b200.shard import reduce_max
+    red = reduce_max([total_ms, fwd_ms, bwd_ms, e2e[0] if e2e else 0.0, float(status)] + (kern_ms or []))
+    total_ms, fwd_ms, bwd_ms, e2e_ms, status = red[:5]
+    if kern_ms:
+        kern_ms = red[5:8]
 
     if rank == 0:
         f_fwd = flops_fwd(B, H, S, D)
@@ -282,10 +298,23 @@ def main():
         value = world * f_step / (ms_per_step * 1e-3) / 1e12
         peaks, peak_kind = measured_peaks()
         peak = peaks.get("bf16_tflops_sustained") or peaks.get("bf16_tflops")
-        dom_bwd = bwd_ms >= fwd_ms
-        dom_ms = bwd_ms if dom_bwd else fwd_ms
-        dom_fl = 2.5 * f_fwd if dom_bwd else f_fwd
-        achieved = dom_fl / (dom_ms * 1e-3) / 1e12
+        # Algorithmic FLOPs per launch: one contraction over the causal half is f_fwd / 2.  Forward =
+        # 2 contractions; the dK/dV kernel is charged S^T, dP^T, dV, dK (4), the dQ kernel only dQ (1; its
+        # own S and dP are recomputation): together the 2.5 x forward of the backward pass.
+        kernels = {"attn_fwd4_sm100_kernel": {"ms": fwd_ms, "flops": f_fwd}}
+        if kern_ms:
+            kernels["attn_bwd_stats_kernel"] = {"ms": kern_ms[0], "flops": 0.0}
+            kernels["attn_bwd_dq4_sm100_kernel"] = {"ms": kern_ms[1], "flops": 0.5 * f_fwd}
+            kernels["attn_bwd_dkv4_sm100_kernel"] = {"ms": kern_ms[2], "flops": 2.0 * f_fwd}
+        else:
+            kernels["attention backward (fp32 path)"] = {"ms": bwd_ms, "flops": 2.5 * f_fwd}
+        dom = max(kernels, key=lambda n: kernels[n]["ms"])
+        achieved = kernels[dom]["flops"] / (kernels[dom]["ms"] * 1e-3) / 1e12
+        # DRAM bytes per launch of that kernel: ncu capture at B=2 (profiles/attention_core_b2_s4096_ncu_full.md),
+        # which grows in proportion to batch x heads; None for a kernel that was not captured
+        dram_per_bh = {"attn_fwd4_sm100_kernel": 1.654e6, "attn_bwd_dq4_sm100_kernel": 2.264e6,
+                       "attn_bwd_dkv4_sm100_kernel": 2.352e6}
+        traffic = dram_per_bh[dom] * B * H if dom in dram_per_bh else None
         line = {
             "metric": "attention fwd+bwd TFLOP/s", "value": value, "unit": "TFLOP/s",
             "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms_per_step,
@@ -294,9 +323,12 @@ def main():
             "fwd": {"ms": fwd_ms, "tflops_per_gpu": f_fwd / (fwd_ms * 1e-3) / 1e12},
             "bwd": {"ms": bwd_ms, "tflops_per_gpu": 2.5 * f_fwd / (bwd_ms * 1e-3) / 1e12,
                     "tensor_pipe": bool(bwd_tensor)},
-            "roofline": {"bound": "tensor", "kernel": "attention backward" if dom_bwd else "attention forward",
-                         "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                         "peak_source": f"{peak_kind} bf16_tflops_sustained", "traffic": None},
+            "kernels_ms": {n: round(kernels[n]["ms"], 4) for n in kernels},
+            "roofline": {"bound": "tensor", "kernel": dom, "achieved": achieved, "peak": peak,
+                         "unit": "TFLOP/s", "frac": achieved / peak,
+                         "peak_source": f"{peak_kind} bf16_tflops_sustained", "traffic": traffic,
+                         "traffic_unit": "DRAM bytes per launch (ncu, scaled from B=2)",
+                         "whole_step_frac": value / world / peak},
             "gpu_launches": kernels_per_step * K,
             "clocks": clocks, "device_status": int(status),
         }

@@ -66,6 +66,8 @@ EXPORTS = {
     "ltca_version": (C.c_int, []),
     "ltca_ctx_create": (C.c_int, [C.c_int, C.c_void_p, C.POINTER(C.c_void_p)]),
     "ltca_ctx_set_stream": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "ltca_ctx_enable_kernel_timing": (C.c_int, [C.c_void_p, C.c_int]),
+    "ltca_ctx_last_bwd_kernel_ms": (C.c_int, [C.c_void_p, C.POINTER(C.c_float)]),
     "ltca_ctx_destroy": (None, [C.c_void_p]),
     "ltca_last_error": (C.c_char_p, [C.c_void_p]),
     "ltca_device_status": (C.c_int, [C.c_void_p, C.POINTER(C.c_uint32)]),

@@ -68,6 +68,16 @@ class Context:
     def set_stream(self, stream: torch.cuda.Stream):
         self.lib.ltca_ctx_set_stream(self.handle, C.c_void_p(stream.cuda_stream))
 
+    def enable_kernel_timing(self, enable: bool = True):
+        """Per-kernel CUDA-event timing of the tensor-pipe backward (benchmark aid)."""
+        self.check(self.lib.ltca_ctx_enable_kernel_timing(self.handle, int(enable)))
+
+    def last_bwd_kernel_ms(self):
+        """(statistics, dQ kernel, dK/dV kernel) durations in ms of the last timed backward."""
+        ms = (C.c_float * 3)()
+        self.check(self.lib.ltca_ctx_last_bwd_kernel_ms(self.handle, ms))
+        return tuple(float(x) for x in ms)
+
     def check(self, rc: int):
         if rc != 0:
             raise LtcaError(rc, self.lib.ltca_last_error(self.handle).decode())

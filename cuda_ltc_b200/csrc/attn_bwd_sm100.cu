@@ -1469,6 +1469,7 @@ int launch_main(ltca_ctx* ctx, const ltca_attn_params* p, const void* q, const v
         kdq<<<gq, kThreads, DqSmem::kDynBytes, ctx->stream>>>(tq128, tdo128, tk64, tv64, a);
         LTCA_LAUNCH_OK(ctx, "attn_bwd_dq_sm100_kernel");
     }
+    kernel_timing_mark(ctx, 2);
     if constexpr (sizeof(OutT) == 2) {
         if (LTCA_BWD_DKV4) {
             static bool attr4_done = false;
@@ -1482,12 +1483,14 @@ int launch_main(ltca_ctx* ctx, const ltca_attn_params* p, const void* q, const v
             attn_bwd_dkv4_sm100_kernel<<<g4, kThreads, Dkv4Smem::kDynBytes, ctx->stream>>>(tq128, tdo128, tk128,
                                                                                            tv128, a);
             LTCA_LAUNCH_OK(ctx, "attn_bwd_dkv4_sm100_kernel");
+            kernel_timing_mark(ctx, 3);
             return LTCA_OK;
         }
     }
     dim3 gk((p->Sk + 2 * kTile - 1) / (2 * kTile), p->H, p->B);
     kdkv<<<gk, kThreads, DkvSmem::kDynBytes, ctx->stream>>>(tq64, tdo64, tk128, tv128, a);
     LTCA_LAUNCH_OK(ctx, "attn_bwd_dkv_sm100_kernel");
+    kernel_timing_mark(ctx, 3);
     return LTCA_OK;
 }
 
@@ -1548,9 +1551,11 @@ int launch_attn_bwd_sm100(ltca_ctx* ctx, const ltca_attn_params* p) {
     s.lse = p->lse; s.lse2 = lse2; s.delta = delta;
     const int64_t rows = (int64_t)p->B * p->H * s.Sq_pad;
     const unsigned blocks = (unsigned)((rows + 31) / 32);
+    kernel_timing_mark(ctx, 0);
     if (p->dtype == LTCA_BF16) attn_bwd_stats_kernel<__nv_bfloat16><<<blocks, 256, 0, ctx->stream>>>(s);
     else attn_bwd_stats_kernel<float><<<blocks, 256, 0, ctx->stream>>>(s);
     LTCA_LAUNCH_OK(ctx, "attn_bwd_stats_kernel");
+    if (p->dtype == LTCA_BF16) kernel_timing_mark(ctx, 1);
 
     if (p->dtype == LTCA_BF16)
         return launch_main<__nv_bfloat16>(ctx, p, p->q, p->k, p->v, p->dout, p->q_strides, p->k_strides,
@@ -1577,6 +1582,7 @@ int launch_attn_bwd_sm100(ltca_ctx* ctx, const ltca_attn_params* p) {
     if ((rc = pack(p->k, p->k_strides, kb, p->Sk))) return rc;
     if ((rc = pack(p->v, p->v_strides, vb, p->Sk))) return rc;
     if ((rc = pack(p->dout, p->do_strides, gb, p->Sq))) return rc;
+    kernel_timing_mark(ctx, 1);
     ltca_strides cq{(int64_t)p->H * p->Sq * kD, (int64_t)p->Sq * kD, kD};
     ltca_strides ck{(int64_t)p->H * p->Sk * kD, (int64_t)p->Sk * kD, kD};
     return launch_main<float>(ctx, p, qb, kb, vb, gb, cq, ck, ck, cq, lse2, delta);

@@ -193,6 +193,25 @@ int ltca_ctx_create(int device, void* stream, ltca_ctx** out) {
     return LTCA_OK;
 }
 
+int ltca_ctx_enable_kernel_timing(ltca_ctx* ctx, int enable) {
+    if (!ctx) return LTCA_ERR_INVALID;
+    LTCA_CUDA_OK(ctx, cudaSetDevice(ctx->device));
+    if (enable && !ctx->kev[0])
+        for (int i = 0; i < 4; ++i) LTCA_CUDA_OK(ctx, cudaEventCreate(&ctx->kev[i]));
+    ctx->time_kernels = enable != 0;
+    ctx->kev_recorded = 0;
+    return LTCA_OK;
+}
+
+int ltca_ctx_last_bwd_kernel_ms(ltca_ctx* ctx, float* ms_out) {
+    if (!ctx || !ms_out) return LTCA_ERR_INVALID;
+    if (!ctx->time_kernels || ctx->kev_recorded < 4)
+        return fail(ctx, LTCA_ERR_INVALID, "no timed tensor-pipe backward has run on this context");
+    LTCA_CUDA_OK(ctx, cudaEventSynchronize(ctx->kev[3]));
+    for (int i = 0; i < 3; ++i) LTCA_CUDA_OK(ctx, cudaEventElapsedTime(&ms_out[i], ctx->kev[i], ctx->kev[i + 1]));
+    return LTCA_OK;
+}
+
 int ltca_ctx_set_stream(ltca_ctx* ctx, void* stream) {
     if (!ctx) return LTCA_ERR_INVALID;
     ctx->stream = reinterpret_cast<cudaStream_t>(stream);
@@ -201,6 +220,8 @@ int ltca_ctx_set_stream(ltca_ctx* ctx, void* stream) {
 
 void ltca_ctx_destroy(ltca_ctx* ctx) {
     if (!ctx) return;
+    for (int i = 0; i < 4; ++i)
+        if (ctx->kev[i]) cudaEventDestroy(ctx->kev[i]);
     if (ctx->d_status) cudaFree(ctx->d_status);
     delete ctx;
 }

@@ -19,7 +19,21 @@ struct ltca_ctx {
     int cc_major = 0, cc_minor = 0;
     uint32_t* d_status = nullptr;     // device status word (allocated once at context creation)
     char err[512] = {0};
+    // optional per-kernel timing of the backward pass (ltca_ctx_enable_kernel_timing)
+    bool time_kernels = false;
+    cudaEvent_t kev[4] = {nullptr, nullptr, nullptr, nullptr};
+    int kev_recorded = 0;
 };
+
+namespace ltca {
+// Marks a boundary between two kernels of the backward pass on the context's stream.
+inline void kernel_timing_mark(ltca_ctx* ctx, int i) {
+    if (ctx->time_kernels && i < 4 && ctx->kev[i]) {
+        cudaEventRecord(ctx->kev[i], ctx->stream);
+        ctx->kev_recorded = i + 1;
+    }
+}
+}  // namespace ltca
 
 namespace ltca {
 

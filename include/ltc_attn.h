@@ -107,6 +107,16 @@ void ltca_ctx_destroy(ltca_ctx* ctx);
 const char* ltca_last_error(const ltca_ctx* ctx);
 int ltca_version(void);
 
+/* Optional timing of the kernels of the tensor-pipe backward (for benchmarks): when enabled,
+ * ltca_attn_bwd records CUDA events on the context's stream around its three stages, and
+ * ltca_ctx_last_bwd_kernel_ms waits for the last one and returns the durations in
+ * milliseconds: ms_out[0] row statistics (delta, lse; plus the bf16 packing for fp32 storage),
+ * ms_out[1] the dQ kernel, ms_out[2] the dK/dV kernel.  (No counterpart in the reference, whose
+ * only timing is the per-stage event pair of ml::InferencePipeline::executeStage,
+ * src/ml/ml_inference_pipeline.cu:42-80.) */
+int ltca_ctx_enable_kernel_timing(ltca_ctx* ctx, int enable);
+int ltca_ctx_last_bwd_kernel_ms(ltca_ctx* ctx, float* ms_out);
+
 /* Reads and clears the device status word that kernels set when a bounded wait ran out or an
  * internal check failed.  Synchronises the context's stream.  0 = clean. */
 int ltca_device_status(ltca_ctx* ctx, uint32_t* status_out);

@@ -1,0 +1,322 @@
+// ltc_attn_shim.hpp -- header-only C++ binding of libltc_attn.so for the CUDA_LTC code base.
+//
+// Include it AFTER the reference's own headers "cuda_resources.h" and "time_self_attention.h"
+// (it uses cudatrader::CudaMemory<float> and derives from cudatrader::TimeSelfAttention exactly
+// as they are declared there, include/cuda_resources.h:531-770 and
+// include/time_self_attention.h:19-165 of the reference).  It adds
+//
+//   cudatrader::B200TimeSelfAttention      a TimeSelfAttention whose forward / backward /
+//                                          backwardWeights run on the sm_100a kernels,
+//   cudatrader::createB200TimeSelfAttention the factory to call from TimeSelfAttention::create
+//                                          (src/ml/time_self_attention.cu:41-56),
+//   cudatrader::b200::flashAttention       the body of FlashAttention::flashAttention
+//                                          (src/ml/flash_attention.cu:961-1046) on un-permuted
+//                                          projection outputs, plus its backward.
+//
+// Error behaviour follows the reference: constructor argument errors are std::invalid_argument
+// (src/ml/time_self_attention.cu:12-36), failures of the library are std::runtime_error (the type
+// CHECK_CUDNN_ERROR throws, include/cuDNN_ops.h:42-49).  Nothing is swallowed.
+#ifndef LTC_ATTN_SHIM_HPP_
+#define LTC_ATTN_SHIM_HPP_
+
+#include <cmath>
+#include <cstdint>
+#include <cstdio>
+#include <fstream>
+#include <memory>
+#include <random>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+#include "ltc_attn.h"
+
+namespace cudatrader {
+
+namespace b200 {
+
+inline void check(ltca_ctx* ctx, int rc, const char* what) {
+    if (rc != LTCA_OK)
+        throw std::runtime_error(std::string(what) + ": " + (ctx ? ltca_last_error(ctx) : "no context"));
+}
+
+// One library context per (device, stream) user; the stream is rebound on every call because
+// the reference passes it per call.
+class Context {
+public:
+    explicit Context(int device = 0) {
+        const int rc = ltca_ctx_create(device, nullptr, &ctx_);
+        if (rc != LTCA_OK) throw std::runtime_error("ltca_ctx_create failed: no sm_100 device or CUDA error");
+    }
+    ~Context() { ltca_ctx_destroy(ctx_); }
+    Context(const Context&) = delete;
+    Context& operator=(const Context&) = delete;
+    ltca_ctx* get(cudaStream_t stream) const {
+        ltca_ctx_set_stream(ctx_, reinterpret_cast<void*>(stream));
+        return ctx_;
+    }
+private:
+    ltca_ctx* ctx_ = nullptr;
+};
+
+// Scaled-dot-product attention on projection outputs laid out [batch*seq, heads*head_dim]
+// (batch-major rows), the layout FlashAttention::forward produces before its reshape kernels
+// (src/ml/flash_attention.cu:866-958).  mask: optional dense [B,S,S] keep-mask, 0 hides
+// (:161-164).  Returns [batch*seq, heads*head_dim]; `lse_out` (optional, [B,H,S]) receives the
+// log-sum-exp needed by flashAttentionBackward.
+inline CudaMemory<float> flashAttention(const Context& c, const CudaMemory<float>& query,
+                                        const CudaMemory<float>& key, const CudaMemory<float>& value,
+                                        int batch_size, int seq_len, int num_heads, int head_dim,
+                                        const CudaMemory<float>* mask = nullptr, cudaStream_t stream = nullptr,
+                                        CudaMemory<float>* lse_out = nullptr, float score_clamp = 10.0f) {
+    const size_t n = (size_t)batch_size * seq_len * num_heads * head_dim;
+    CudaMemory<float> out(n, stream);
+    CudaMemory<float> ws;
+    ltca_attn_params p = {};
+    p.B = batch_size; p.H = num_heads; p.Sq = seq_len; p.Sk = seq_len; p.D = head_dim;
+    p.dtype = LTCA_F32; p.mode = LTCA_MODE_AUTO; p.causal = 0;
+    p.scale = 1.0f / std::sqrt((float)head_dim);                    // flash_attention.cu:998
+    p.score_clamp = score_clamp;                                     // flash_attention.cu:167
+    const ltca_strides st = {(int64_t)seq_len * num_heads * head_dim, (int64_t)head_dim,
+                             (int64_t)num_heads * head_dim};
+    p.q = query.get(); p.k = key.get(); p.v = value.get(); p.o = out.get();
+    p.q_strides = p.k_strides = p.v_strides = p.o_strides = st;
+    p.lse = lse_out ? lse_out->get() : nullptr;
+    p.keep_mask = mask ? mask->get() : nullptr;
+    size_t need = 0;
+    ltca_attn_workspace_bytes(&p, 0, &need);
+    if (need) { ws = CudaMemory<float>((need + 3) / 4, stream); p.workspace = ws.get(); p.workspace_bytes = need; }
+    ltca_ctx* ctx = c.get(stream);
+    check(ctx, ltca_attn_fwd(ctx, &p), "ltca_attn_fwd");
+    return out;
+}
+
+// Gradients of flashAttention with respect to query, key and value (the reference's
+// FlashAttention has no backward; this is the extension the attention path needs for training).
+inline void flashAttentionBackward(const Context& c, const CudaMemory<float>& query,
+                                   const CudaMemory<float>& key, const CudaMemory<float>& value,
+                                   const CudaMemory<float>& out, const CudaMemory<float>& lse,
+                                   const CudaMemory<float>& grad_out, CudaMemory<float>& grad_query,
+                                   CudaMemory<float>& grad_key, CudaMemory<float>& grad_value,
+                                   int batch_size, int seq_len, int num_heads, int head_dim,
+                                   const CudaMemory<float>* mask = nullptr, cudaStream_t stream = nullptr,
+                                   float score_clamp = 10.0f) {
+    CudaMemory<float> ws;
+    ltca_attn_params p = {};
+    p.B = batch_size; p.H = num_heads; p.Sq = seq_len; p.Sk = seq_len; p.D = head_dim;
+    p.dtype = LTCA_F32; p.mode = LTCA_MODE_AUTO; p.causal = 0;
+    p.scale = 1.0f / std::sqrt((float)head_dim);
+    p.score_clamp = score_clamp;
+    const ltca_strides st = {(int64_t)seq_len * num_heads * head_dim, (int64_t)head_dim,
+                             (int64_t)num_heads * head_dim};
+    p.q = query.get(); p.k = key.get(); p.v = value.get(); p.o = out.get(); p.lse = lse.get();
+    p.dout = grad_out.get(); p.dq = grad_query.get(); p.dk = grad_key.get(); p.dv = grad_value.get();
+    p.q_strides = p.k_strides = p.v_strides = p.o_strides = st;
+    p.do_strides = p.dq_strides = p.dk_strides = p.dv_strides = st;
+    p.keep_mask = mask ? mask->get() : nullptr;
+    size_t need = 0;
+    ltca_attn_workspace_bytes(&p, 1, &need);
+    if (need) { ws = CudaMemory<float>((need + 3) / 4, stream); p.workspace = ws.get(); p.workspace_bytes = need; }
+    ltca_ctx* ctx = c.get(stream);
+    check(ctx, ltca_attn_bwd(ctx, &p), "ltca_attn_bwd");
+}
+
+}  // namespace b200
+
+// TimeSelfAttention on the sm_100a kernels.  `head_width` selects the arithmetic: input_dim
+// reproduces the reference's cuDNN configuration (per-head projection width = input_dim, scale
+// 1.0, no mask use, include/cuDNN_ops.h:152-178); input_dim / num_heads gives the compact form
+// (scale 1/sqrt(head_dim)).  Rows are time-major, as the reference hands them to cuDNN
+// (include/cuDNN_ops.h:322-328).
+class B200TimeSelfAttention : public TimeSelfAttention {
+public:
+    B200TimeSelfAttention(int input_dim, int num_heads, bool use_layer_norm = true, bool use_residual = true,
+                          float dropout_rate = 0.0f, unsigned long long seed = 42, bool compact_heads = false,
+                          bool causal = false, int device = 0)
+        : TimeSelfAttention(input_dim, num_heads, use_layer_norm, use_residual, dropout_rate, seed),
+          ctx_(device),
+          head_width_(compact_heads ? input_dim / num_heads : input_dim),
+          scale_(compact_heads ? 1.0f / std::sqrt((float)(input_dim / num_heads)) : 1.0f),
+          causal_(causal) {
+        const size_t e = (size_t)input_dim_, hw = (size_t)num_heads_ * head_width_;
+        wq_ = CudaMemory<float>(e * hw); wk_ = CudaMemory<float>(e * hw); wv_ = CudaMemory<float>(e * hw);
+        wo_ = CudaMemory<float>(hw * e);
+        ln_gamma_ = CudaMemory<float>(e); ln_beta_ = CudaMemory<float>(e);
+        // Xavier-uniform in the reference's order Q, K, V, O from one mt19937(seed)
+        // (src/ml/cuDNN_ops.cu:34-96): limit = sqrt(6 / (fan_in + fan_out)) of each matrix
+        std::mt19937 gen((unsigned)seed_);
+        auto fill = [&](CudaMemory<float>& w, size_t fan_in, size_t fan_out) {
+            const float limit = std::sqrt(6.0f / (float)(fan_in + fan_out));
+            std::uniform_real_distribution<float> dist(-limit, limit);
+            std::vector<float> host(w.size());
+            for (float& x : host) x = dist(gen);
+            w.copyFromHost(host.data());
+            cudaDeviceSynchronize();                  // `host` goes out of scope
+        };
+        fill(wq_, e, (size_t)head_width_); fill(wk_, e, (size_t)head_width_);
+        fill(wv_, e, (size_t)head_width_); fill(wo_, (size_t)head_width_, e);
+        std::vector<float> ones(e, 1.0f), zeros(e, 0.0f);
+        ln_gamma_.copyFromHost(ones.data());
+        ln_beta_.copyFromHost(zeros.data());
+        cudaDeviceSynchronize();                      // the host vectors go out of scope
+    }
+
+    CudaMemory<float> forward(const CudaMemory<float>& x_seq, int batch_size, int seq_len,
+                              const CudaMemory<float>* mask = nullptr, cudaStream_t stream = nullptr) override {
+        CudaMemory<float> out((size_t)batch_size * seq_len * input_dim_, stream);
+        ltca_tsa_params p = params(x_seq, batch_size, seq_len, mask);
+        p.out = out.get();
+        run(p, 0, stream, ltca_tsa_fwd, "ltca_tsa_fwd");
+        return out;
+    }
+
+    CudaMemory<float> backward(const CudaMemory<float>& grad_output, const CudaMemory<float>& x_seq,
+                               int batch_size, int seq_len, const CudaMemory<float>* mask = nullptr,
+                               cudaStream_t stream = nullptr) override {
+        CudaMemory<float> dx((size_t)batch_size * seq_len * input_dim_, stream);
+        ltca_tsa_params p = params(x_seq, batch_size, seq_len, mask);
+        p.dy = grad_output.get();
+        p.dx = dx.get();
+        run(p, 1, stream, ltca_tsa_bwd_data, "ltca_tsa_bwd_data");
+        return dx;
+    }
+
+    void backwardWeights(const CudaMemory<float>& grad_output, const CudaMemory<float>& x_seq,
+                         int batch_size, int seq_len, const CudaMemory<float>* mask = nullptr,
+                         cudaStream_t stream = nullptr) override {
+        ensure_gradients(stream);
+        ltca_tsa_params p = params(x_seq, batch_size, seq_len, mask);
+        p.dy = grad_output.get();
+        p.dwq = dwq_.get(); p.dwk = dwk_.get(); p.dwv = dwv_.get(); p.dwo = dwo_.get();
+        run(p, 2, stream, ltca_tsa_bwd_weights, "ltca_tsa_bwd_weights");
+    }
+
+    // LayerNorm scale and shift are the parameters the reference exposes
+    // (src/ml/cudnn_time_self_attention.cu:436-450); the projection matrices follow them here so
+    // that an optimizer can finally update them.
+    std::vector<CudaMemory<float>*> getParameters() override {
+        return {&ln_gamma_, &ln_beta_, &wq_, &wk_, &wv_, &wo_};
+    }
+    void initializeGradientStorage(cudaStream_t stream = nullptr) override {
+        ensure_gradients(stream);
+        dgamma_.memset(0, stream); dbeta_.memset(0, stream);
+        dwq_.memset(0, stream); dwk_.memset(0, stream); dwv_.memset(0, stream); dwo_.memset(0, stream);
+    }
+    // gamma / beta gradients are zero placeholders, as in the reference
+    // (src/ml/cudnn_time_self_attention.cu:357-364): LayerNorm is not differentiated there.
+    std::vector<CudaMemory<float>*> getComputedGradients() override {
+        ensure_gradients(nullptr);
+        return {&dgamma_, &dbeta_, &dwq_, &dwk_, &dwv_, &dwo_};
+    }
+
+    // File layout: the reference's blob header (u32 0x43444E4E, u32 version, size_t byte count,
+    // src/ml/cuDNN_ops.cu:391-420) followed by Wq, Wk, Wv, Wo as fp32 row-major matrices, and
+    // `<path>.layernorm` with gamma then beta (src/ml/cudnn_time_self_attention.cu:382-398).
+    void saveWeights(const std::string& filepath) override {
+        std::ofstream f(filepath, std::ios::binary);
+        if (!f.is_open()) throw std::runtime_error("Failed to open file for writing: " + filepath);
+        const uint32_t magic = 0x43444E4E, version = 1;
+        const size_t nbytes = (wq_.size() + wk_.size() + wv_.size() + wo_.size()) * sizeof(float);
+        f.write(reinterpret_cast<const char*>(&magic), sizeof(magic));
+        f.write(reinterpret_cast<const char*>(&version), sizeof(version));
+        f.write(reinterpret_cast<const char*>(&nbytes), sizeof(nbytes));
+        for (const CudaMemory<float>* w : {&wq_, &wk_, &wv_, &wo_}) write_tensor(f, *w);
+        if (f.fail()) throw std::runtime_error("Failed to write weights to file: " + filepath);
+        std::ofstream g(filepath + ".layernorm", std::ios::binary);
+        if (!g.is_open()) throw std::runtime_error("Failed to open file for writing: " + filepath + ".layernorm");
+        write_tensor(g, ln_gamma_);
+        write_tensor(g, ln_beta_);
+    }
+    void loadWeights(const std::string& filepath) override {
+        std::ifstream f(filepath, std::ios::binary);
+        if (!f.is_open()) throw std::runtime_error("Failed to open file for reading: " + filepath);
+        uint32_t magic = 0, version = 0;
+        size_t nbytes = 0;
+        f.read(reinterpret_cast<char*>(&magic), sizeof(magic));
+        f.read(reinterpret_cast<char*>(&version), sizeof(version));
+        f.read(reinterpret_cast<char*>(&nbytes), sizeof(nbytes));
+        const size_t want = (wq_.size() + wk_.size() + wv_.size() + wo_.size()) * sizeof(float);
+        if (magic != 0x43444E4E || version != 1 || nbytes != want)
+            throw std::runtime_error("Weight file does not match this module: " + filepath);
+        for (CudaMemory<float>* w : {&wq_, &wk_, &wv_, &wo_}) read_tensor(f, *w);
+        if (f.fail()) throw std::runtime_error("Failed to read weights from file: " + filepath);
+        std::ifstream g(filepath + ".layernorm", std::ios::binary);
+        if (g.is_open()) { read_tensor(g, ln_gamma_); read_tensor(g, ln_beta_); }
+    }
+
+    int getHeadWidth() const { return head_width_; }
+
+private:
+    ltca_tsa_params params(const CudaMemory<float>& x, int B, int S, const CudaMemory<float>* mask) const {
+        ltca_tsa_params p = {};
+        p.B = B; p.S = S; p.E = input_dim_; p.H = num_heads_; p.head_width = head_width_;
+        p.causal = causal_ ? 1 : 0;
+        p.time_major = 1;
+        p.use_residual = use_residual_ ? 1 : 0;
+        p.use_layer_norm = use_layer_norm_ ? 1 : 0;
+        p.mode = LTCA_MODE_AUTO;
+        p.scale = scale_;
+        p.x = x.get();
+        p.wq = wq_.get(); p.wk = wk_.get(); p.wv = wv_.get(); p.wo = wo_.get();
+        p.ln_gamma = ln_gamma_.get(); p.ln_beta = ln_beta_.get();
+        p.keep_mask = mask ? mask->get() : nullptr;
+        return p;
+    }
+    template <typename Fn>
+    void run(ltca_tsa_params& p, int which, cudaStream_t stream, Fn fn, const char* what) {
+        size_t need = 0;
+        ltca_tsa_workspace_bytes(&p, which, &need);
+        if (need > workspace_.bytes()) workspace_ = CudaMemory<float>((need + 3) / 4, stream);
+        p.workspace = workspace_.get();
+        p.workspace_bytes = workspace_.bytes();
+        ltca_ctx* ctx = ctx_.get(stream);
+        b200::check(ctx, fn(ctx, &p), what);
+    }
+    void ensure_gradients(cudaStream_t stream) {
+        if (dwq_.size() == wq_.size() && dwq_.size() != 0) return;
+        dwq_ = CudaMemory<float>(wq_.size(), stream); dwk_ = CudaMemory<float>(wk_.size(), stream);
+        dwv_ = CudaMemory<float>(wv_.size(), stream); dwo_ = CudaMemory<float>(wo_.size(), stream);
+        dgamma_ = CudaMemory<float>(ln_gamma_.size(), stream); dbeta_ = CudaMemory<float>(ln_beta_.size(), stream);
+    }
+    static void write_tensor(std::ofstream& f, const CudaMemory<float>& t) {
+        std::vector<float> host(t.size());
+        t.copyToHost(host.data());
+        cudaDeviceSynchronize();
+        f.write(reinterpret_cast<const char*>(host.data()), (std::streamsize)(host.size() * sizeof(float)));
+    }
+    static void read_tensor(std::ifstream& f, CudaMemory<float>& t) {
+        std::vector<float> host(t.size());
+        f.read(reinterpret_cast<char*>(host.data()), (std::streamsize)(host.size() * sizeof(float)));
+        t.copyFromHost(host.data());
+        cudaDeviceSynchronize();
+    }
+
+    b200::Context ctx_;
+    int head_width_;
+    float scale_;
+    bool causal_;
+    CudaMemory<float> wq_, wk_, wv_, wo_, ln_gamma_, ln_beta_;
+    CudaMemory<float> dwq_, dwk_, dwv_, dwo_, dgamma_, dbeta_;
+    CudaMemory<float> workspace_;
+};
+
+// Returns nullptr when the machine has no sm_100 device, so that TimeSelfAttention::create can
+// fall through to its existing branches.
+inline std::unique_ptr<TimeSelfAttention> createB200TimeSelfAttention(int input_dim, int num_heads,
+                                                                      bool use_layer_norm = true,
+                                                                      bool use_residual = true,
+                                                                      float dropout_rate = 0.0f,
+                                                                      unsigned long long seed = 42) {
+    try {
+        return std::unique_ptr<TimeSelfAttention>(
+            new B200TimeSelfAttention(input_dim, num_heads, use_layer_norm, use_residual, dropout_rate, seed));
+    } catch (const std::invalid_argument&) {
+        throw;                         // argument errors surface exactly as in the reference
+    } catch (const std::runtime_error&) {
+        return nullptr;
+    }
+}
+
+}  // namespace cudatrader
+
+#endif  // LTC_ATTN_SHIM_HPP_
