@@ -1111,7 +1111,8 @@ attn_bwd_dkv4_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
 
 // ---------------------------------------------------------------------------------------------
 // 5. dQ, single-tile variant (bf16 operands and results): one CTA per 128 queries, key steps of
-// 128, nothing aliased:  S [0,128)  dP [128,256)  dS bf16 [256,320)  dQ [320,384).
+// 128, nothing aliased:  S [0,128)  dP [128,256)  dQ [320,384)  and three dS (bf16) buffers used in
+// turn, [256,320) [384,448) [448,512).
 // Elementwise warp w owns query rows 32 (w % 4) .. +31 and key columns 32 (w / 4) .. +31 of the
 // step.  Warp 16 issues S and dP of the next step as soon as this step's are in registers,
 // warp 17 issues dQ += dS K_j.
@@ -1123,8 +1124,8 @@ struct Dq4Smem {
     static constexpr int kDoOff = kBigTile;
     static constexpr int kRingOff = 2 * kBigTile;
     static constexpr int kBarOff = kRingOff + kStages * kStageBytes;
-    // bars: qdo_full, ring_full[S], ring_empty[S], sdp_full, sdp_free, ds_full, dq_done, turn
-    static constexpr int kNumBars = 1 + 2 * kStages + 5;
+    // bars: qdo_full, ring_full[S], ring_empty[S], sdp_full, sdp_free, ds_full[3], ds_free[3]
+    static constexpr int kNumBars = 1 + 2 * kStages + 8;
     static constexpr int kMiscOff = kBarOff + kNumBars * 8;
     static constexpr int kDynBytes = kMiscOff + 16 + 1024;
 };
@@ -1146,9 +1147,13 @@ attn_bwd_dq4_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
     auto bar_ring_empty = [&](int s) { return bar_base + 8u * (1 + L::kStages + s); };
     const uint32_t bar_sdp_full = bar_base + 8u * (1 + 2 * L::kStages);
     const uint32_t bar_sdp_free = bar_sdp_full + 8u;
-    const uint32_t bar_ds_full = bar_sdp_full + 16u;
-    const uint32_t bar_dq_done = bar_sdp_full + 24u;
-    const uint32_t bar_turn = bar_sdp_full + 32u;
+    // One pair of barriers per dS buffer.  A barrier that is reused every step could complete
+    // twice before a late waiter looks at it, and a parity wait cannot tell "not yet" from
+    // "two phases ago"; with one barrier per buffer the next completion always depends on the
+    // waiter itself.
+    auto bar_ds_full = [&](int it) { return bar_sdp_full + 16u + 8u * (it % 3); };     // dS of step `it` stored
+    auto bar_ds_free = [&](int it) { return bar_sdp_full + 40u + 8u * (it % 3); };     // dQ of step `it` done
+    auto ds_parity = [&](int it) { return (uint32_t)((it / 3) & 1); };
     volatile uint32_t* misc = reinterpret_cast<volatile uint32_t*>(smem_gen + L::kMiscOff);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -1171,9 +1176,7 @@ attn_bwd_dq4_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
         for (int s = 0; s < L::kStages; ++s) { mbar_init(bar_ring_full(s), 1); mbar_init(bar_ring_empty(s), 2); }
         mbar_init(bar_sdp_full, 1);
         mbar_init(bar_sdp_free, 16);               // one arrival per elementwise warp
-        mbar_init(bar_ds_full, 16);
-        mbar_init(bar_dq_done, 1);
-        mbar_init(bar_turn, 8);
+        for (int r = 0; r < 3; ++r) { mbar_init(bar_ds_full(r), 16); mbar_init(bar_ds_free(r), 1); }
         misc[1] = 0u;
         mbar_fence_init();
     }
@@ -1185,6 +1188,8 @@ attn_bwd_dq4_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
     const WaitCtx wc{&misc[1], a.status};
     auto slot_of = [&](int it) { return it % L::kStages; };
     auto phase_of = [&](int it) { return (uint32_t)((it / L::kStages) & 1); };
+    // tensor-memory column of the dS buffer of step `it`: 256, 384, 448 in turn
+    auto ds_col = [&](int it) { const int r = it % 3; return (uint32_t)(r == 0 ? 256 : (r == 1 ? 384 : 448)); };
     LTCA_TRACE_DECL(LTCA_TRACE_KERNEL == 3 && blockIdx.x == 0 && blockIdx.y == 5 && blockIdx.z == 0);
     LTCA_TRACE_EVT(0x01);
 
@@ -1232,6 +1237,9 @@ attn_bwd_dq4_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
             for (int it = 0; it + 1 < n_it && ok; ++it) {
                 ok = mbar_wait(bar_ring_full(slot_of(it + 1)), phase_of(it + 1), wc, 0xe2);
                 ok = ok && mbar_wait(bar_sdp_free, (uint32_t)(it & 1), wc, 0xe3);
+                // dS lives in three buffers; step it+1 reuses the one dQ(it-2) read.  Waiting for
+                // that contraction here keeps the check off the elementwise warps' path.
+                if (it >= 2) ok = ok && mbar_wait(bar_ds_free(it - 2), ds_parity(it - 2), wc, 0xe5);
                 if (!ok) break;
                 tc_fence_after_sync();
                 LTCA_TRACE_EVT(0x20 + (it << 8));
@@ -1251,20 +1259,20 @@ attn_bwd_dq4_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
             bool ok = true;
             for (int it = 0; it < n_it && ok; ++it) {
                 ok = mbar_wait(bar_ring_full(slot_of(it)), phase_of(it), wc, 0xe8);
-                ok = ok && mbar_wait(bar_ds_full, (uint32_t)(it & 1), wc, 0xe9);
+                ok = ok && mbar_wait(bar_ds_full(it), ds_parity(it), wc, 0xe9);
                 if (!ok) break;
                 tc_fence_after_sync();
                 LTCA_TRACE_EVT(0x22 + (it << 8));
                 const uint64_t kd = ring_desc_mn + (uint64_t)((slot_of(it) * L::kStageBytes) >> 4);
 #pragma unroll
                 for (int k = 0; k < kKStep / 16; ++k)
-                    mma_ts(tmem_base + 320, tmem_base + 256 + k * 8, kd + 128 * k, idesc_dq,
+                    mma_ts(tmem_base + 320, tmem_base + ds_col(it) + k * 8, kd + 128 * k, idesc_dq,
                            (it > 0 || k > 0) ? 1u : 0u);
-                mma_commit(bar_dq_done);
+                mma_commit(bar_ds_free(it));
                 mma_commit(bar_ring_empty(slot_of(it)));
                 LTCA_TRACE_EVT(0x23 + (it << 8));
             }
-            if (ok) ok = mbar_wait(bar_dq_done, (uint32_t)((n_it - 1) & 1), wc, 0xea);
+            if (ok) ok = mbar_wait(bar_ds_free(n_it - 1), ds_parity(n_it - 1), wc, 0xea);
         }
       }
     } else {
@@ -1275,7 +1283,6 @@ attn_bwd_dq4_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
         const uint32_t lane_base = (uint32_t)(wq * 32) << 16;
         const uint32_t tS = tmem_base + lane_base + 32 * cq;
         const uint32_t tDP = tS + 128;
-        const uint32_t tDS = tmem_base + lane_base + 256 + 16 * cq;
         const uint32_t tDQ = tmem_base + lane_base + 320 + 16 * cq;
         const float c2 = a.scale_log2;
         const bool general = (a.keep_mask != nullptr) || (a.use_clamp != 0);
@@ -1284,26 +1291,21 @@ attn_bwd_dq4_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
         const float dlt = a.delta[srow];
 
         bool ok = true;
-        for (int it = 0; it < n_it; ++it) {
-            ok = mbar_wait_warp(bar_sdp_full, (uint32_t)(it & 1), wc, 0xf0);
-            if (!ok) break;
-            tc_fence_after_sync();
-            LTCA_TRACE_EVT(0x10 + (it << 8));
-            uint32_t s[32], dp[32];
-            tmem_ld32(tS, s);
-            tmem_ld32(tDP, dp);
-            tmem_wait_ld();
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar_sdp_free);
-            LTCA_TRACE_EVT(0x11 + (it << 8));
-            // The warps of key columns 64..127 take their turn at the exponentials after those of
-            // columns 0..63, so that each half's loads, stores and barrier traffic overlap the
-            // other half's arithmetic instead of all sixteen warps stalling together.
-            if (LTCA_BWD_TURNS && cq >= 2) {
-                ok = mbar_wait_warp(bar_turn, (uint32_t)(it & 1), wc, 0xf3);
-                if (!ok) break;
+        uint32_t s[32], dp[32];
+        if (n_it > 0) {
+            ok = mbar_wait_warp(bar_sdp_full, 0, wc, 0xf0);
+            if (ok) {
+                tc_fence_after_sync();
+                tmem_ld32(tS, s);
+                tmem_ld32(tDP, dp);
+                tmem_wait_ld();
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_sdp_free);
             }
+        }
+        for (int it = 0; it < n_it && ok; ++it) {
+            LTCA_TRACE_EVT(0x11 + (it << 8));
             const int k0 = it * kKStep;
             const bool edge = (k0 + kKStep > kvlen) || (a.causal && (k0 + kKStep - 1 > q0 + a.causal_off));
             // dS = P o (dP - delta), left in dp[]; the masked variant only runs on edge steps
@@ -1325,46 +1327,43 @@ attn_bwd_dq4_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
                     dp[c] = __float_as_uint(vis ? d : 0.f);
                 }
             } else {
-#if LTCA_EXP_PAIRS
-#pragma unroll
-                for (int c = 0; c < 32; c += 2) {
-                    float p0, p1;
-                    exp2_pair(fmaf(__uint_as_float(s[c]), c2, -lse2), fmaf(__uint_as_float(s[c + 1]), c2, -lse2),
-                              p0, p1);
-                    dp[c] = __float_as_uint(p0 * (__uint_as_float(dp[c]) - dlt));
-                    dp[c + 1] = __float_as_uint(p1 * (__uint_as_float(dp[c + 1]) - dlt));
-                }
-#else
 #pragma unroll
                 for (int c = 0; c < 32; ++c) {
                     const float p = fast_exp2(fmaf(__uint_as_float(s[c]), c2, -lse2));
                     dp[c] = __float_as_uint(p * (__uint_as_float(dp[c]) - dlt));
                 }
-#endif
             }
             uint32_t hi[16], unused[16];
             pack32<false>(dp, hi, unused);
-            if (LTCA_BWD_TURNS && cq < 2) {
-                __syncwarp();
-                if (lane == 0) mbar_arrive(bar_turn);
-            }
             LTCA_TRACE_EVT(0x12 + (it << 8));
-            if (it > 0) {
-                // the previous dS must have been consumed before it is overwritten
-                ok = mbar_wait_warp(bar_dq_done, (uint32_t)((it - 1) & 1), wc, 0xf1);
+            // The next step's S and dP are requested now, so that their tensor-memory load runs
+            // while this step's dS is stored and announced.  (No wait for dQ here: the dS buffer
+            // written below was released before S and dP of this step were even issued.)
+            const bool more = it + 1 < n_it;
+            if (more) {
+                ok = mbar_wait_warp(bar_sdp_full, (uint32_t)((it + 1) & 1), wc, 0xf0);
                 if (!ok) break;
+                tc_fence_after_sync();
+                tmem_ld32(tS, s);
+                tmem_ld32(tDP, dp);
             }
             LTCA_TRACE_EVT(0x14 + (it << 8));
-            tmem_st16(tDS, hi);
+            tmem_st16(tmem_base + lane_base + ds_col(it) + 16 * cq, hi);
             tmem_wait_st();
             tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar_ds_full);
+            if (lane == 0) mbar_arrive(bar_ds_full(it));
+            if (more) {
+                tmem_wait_ld();
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_sdp_free);
+            }
             LTCA_TRACE_EVT(0x13 + (it << 8));
         }
         if (ok && q0 < a.Sq) {
             if (n_it > 0) {
-                ok = mbar_wait_warp(bar_dq_done, (uint32_t)((n_it - 1) & 1), wc, 0xf2);
+                ok = mbar_wait_warp(bar_ds_free(n_it - 1), ds_parity(n_it - 1), wc, 0xf2);
                 tc_fence_after_sync();
             }
             __nv_bfloat16* drow = reinterpret_cast<__nv_bfloat16*>(a.dq) + b * a.dqs.batch + h * a.dqs.head +
