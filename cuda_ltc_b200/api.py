@@ -176,6 +176,61 @@ class Context:
         del ws
         return o, lse
 
+    # ---- TimeSelfAttention module --------------------------------------------------------
+    def _tsa_params(self, x, wq, wk, wv, wo, B, S, H, head_width, scale, causal, time_major,
+                    use_residual, use_layer_norm, gamma, beta, keep_mask, mode):
+        from ._lib import TsaParams
+        E = x.shape[1]
+        assert x.shape == (B * S, E) and x.dtype == torch.float32 and x.is_contiguous()
+        HW = H * head_width
+        assert wq.shape == (E, HW) and wk.shape == (E, HW) and wv.shape == (E, HW) and wo.shape == (HW, E)
+        p = TsaParams()
+        p.B, p.S, p.E, p.H, p.head_width = B, S, E, H, head_width
+        p.causal, p.time_major = int(bool(causal)), int(bool(time_major))
+        p.use_residual, p.use_layer_norm, p.mode = int(bool(use_residual)), int(bool(use_layer_norm)), int(mode)
+        p.scale, p.score_clamp = float(scale), 0.0
+        p.x = x.data_ptr()
+        p.wq, p.wk, p.wv, p.wo = (w.data_ptr() for w in (wq, wk, wv, wo))
+        if gamma is not None:
+            p.ln_gamma, p.ln_beta = gamma.data_ptr(), beta.data_ptr()
+        if keep_mask is not None:
+            p.keep_mask = keep_mask.data_ptr()
+        return p
+
+    def _tsa_workspace(self, p, which):
+        need = C.c_size_t(0)
+        self.check(self.lib.ltca_tsa_workspace_bytes(C.byref(p), which, C.byref(need)))
+        ws = self.workspace(need.value)
+        p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel()
+        return ws
+
+    def tsa_fwd(self, x, wq, wk, wv, wo, B, S, H, head_width, scale=1.0, causal=False, time_major=True,
+                use_residual=True, use_layer_norm=True, gamma=None, beta=None, keep_mask=None,
+                mode=_lib.MODE_AUTO):
+        """out = LayerNorm(x + MHA(x)); x [B*S, E] fp32, weights as in ``ltca_tsa_params``."""
+        p = self._tsa_params(x, wq, wk, wv, wo, B, S, H, head_width, scale, causal, time_major,
+                             use_residual, use_layer_norm, gamma, beta, keep_mask, mode)
+        out = torch.empty_like(x)
+        p.out = out.data_ptr()
+        ws = self._tsa_workspace(p, 0)
+        self.check(self.lib.ltca_tsa_fwd(self.handle, C.byref(p)))
+        del ws
+        return out
+
+    def tsa_bwd(self, x, wq, wk, wv, wo, dy, B, S, H, head_width, scale=1.0, causal=False, time_major=True,
+                keep_mask=None, mode=_lib.MODE_AUTO):
+        """(dx, dwq, dwk, dwv, dwo) of the module; LayerNorm and residual pass dy through."""
+        p = self._tsa_params(x, wq, wk, wv, wo, B, S, H, head_width, scale, causal, time_major,
+                             False, False, None, None, keep_mask, mode)
+        dx = torch.empty_like(x)
+        dws = [torch.empty_like(w) for w in (wq, wk, wv, wo)]
+        p.dy, p.dx = dy.data_ptr(), dx.data_ptr()
+        p.dwq, p.dwk, p.dwv, p.dwo = (w.data_ptr() for w in dws)
+        ws = self._tsa_workspace(p, 3)
+        self.check(self.lib.ltca_tsa_bwd(self.handle, C.byref(p)))
+        del ws
+        return (dx, *dws)
+
     def uses_tensor_pipe(self, q, k, v, causal=False, mode=_lib.MODE_AUTO, backward=False) -> bool:
         o = q
         p = self._params(q, k, v, o, None, 1.0, causal, None, None, 0.0, mode)

@@ -1,0 +1,91 @@
+"""TimeSelfAttention module against the reference's own cuDNN implementation.
+
+tests/golden/ref_tsa_case*.npz were produced on a B200 by the reference's CuDNNTimeSelfAttention
+(compiled from the reference sources, oracle/ref_tsa_driver.cu): input, output, input gradient
+and the four projection matrices as the reference reads them out of cuDNN's weight buffer.  The
+fp64 oracle is checked against them on CPU (this pins its layout, scale and ordering choices: rows
+time-major, per-head projection width = input_dim, scale 1.0, no mask); the CUDA module is checked
+against them through the C ABI on the GPU.  cuDNN's default math for fp32 data uses TF32 tensor
+cores, so agreement is at the 1e-3 level, not fp32 round-off.
+"""
+import glob
+import os
+
+import numpy as np
+import pytest
+
+import oracle
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+CASES = sorted(glob.glob(os.path.join(HERE, "golden", "ref_tsa_case*.npz")))
+TOL = 5e-3          # relative to the tensor's largest magnitude
+
+
+def load(path):
+    d = np.load(path)
+    E, H, B, S = (int(d[k]) for k in ("E", "H", "B", "S"))
+    # cuDNN hands out [heads, projected, input] views for Q/K/V and [heads, output, projected] for O;
+    # the ABI wants y = x w with w [E, H*W] and ctx wo with wo [H*W, E]  (W = E here)
+    qkv = [np.ascontiguousarray(np.transpose(d[n], (2, 0, 1)).reshape(E, H * E)) for n in ("wq", "wk", "wv")]
+    wo = np.ascontiguousarray(np.transpose(d["wo"], (0, 2, 1)).reshape(H * E, E))
+    return d, E, H, B, S, qkv, wo
+
+
+def test_golden_files_exist():
+    assert len(CASES) >= 4
+
+
+@pytest.mark.parametrize("path", CASES)
+def test_oracle_matches_reference_cudnn_module(path):
+    d, E, H, B, S, (wq, wk, wv), wo = load(path)
+    gamma, beta = np.ones(E, np.float32), np.zeros(E, np.float32)
+    out, _ = oracle.tsa_fwd(d["x"], wq, wk, wv, wo, B, S, H, E, 1.0, False, True, bool(d["res"]), bool(d["ln"]),
+                            gamma, beta)
+    assert np.abs(out - d["y"]).max() < TOL * max(1.0, np.abs(d["y"]).max())
+    if "dx" in d.files:
+        dx = oracle.tsa_bwd(d["x"], wq, wk, wv, wo, d["dy"], B, S, H, E, 1.0, False, True)[0]
+        assert np.abs(dx - d["dx"]).max() < TOL * max(1.0, np.abs(d["dx"]).max())
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("path", CASES)
+def test_cuda_module_matches_reference_cudnn_module(ctx, path):
+    import torch
+    from cuda_ltc_b200 import _lib
+    d, E, H, B, S, (wq, wk, wv), wo = load(path)
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).cuda()
+    x, dy, twq, twk, twv, two = (dev(a) for a in (d["x"], d["dy"], wq, wk, wv, wo))
+    gamma, beta = torch.ones(E, device="cuda"), torch.zeros(E, device="cuda")
+    out = ctx.tsa_fwd(x, twq, twk, twv, two, B, S, H, E, scale=1.0, time_major=True,
+                      use_residual=bool(d["res"]), use_layer_norm=bool(d["ln"]), gamma=gamma, beta=beta,
+                      mode=_lib.MODE_FP32)
+    assert np.abs(out.cpu().numpy() - d["y"]).max() < TOL * max(1.0, np.abs(d["y"]).max())
+    got = ctx.tsa_bwd(x, twq, twk, twv, two, dy, B, S, H, E, scale=1.0, time_major=True, mode=_lib.MODE_FP32)
+    if "dx" in d.files:
+        assert np.abs(got[0].cpu().numpy() - d["dx"]).max() < TOL * max(1.0, np.abs(d["dx"]).max())
+    # and, tighter, against the fp64 oracle (same arithmetic, no TF32 in between)
+    ref = oracle.tsa_bwd(d["x"], wq, wk, wv, wo, d["dy"], B, S, H, E, 1.0, False, True)
+    for g, r in zip(got, ref):
+        assert np.abs(g.cpu().numpy() - r).max() < 2e-4 * max(1.0, np.abs(r).max())
+
+
+@pytest.mark.gpu
+def test_cuda_module_compact_heads_causal(ctx):
+    """The benchmark's form of the module (head width E/H, scale 1/sqrt(width), causal) on the
+    tensor pipe, against the oracle."""
+    import math
+    import torch
+    from cuda_ltc_b200 import _lib
+    B, S, E, H = 2, 128, 256, 4
+    W = E // H
+    rng = np.random.default_rng(3)
+    x = rng.standard_normal((B * S, E)).astype(np.float32)
+    lim = math.sqrt(6.0 / (2 * E))
+    wq, wk, wv = (rng.uniform(-lim, lim, (E, H * W)).astype(np.float32) for _ in range(3))
+    wo = rng.uniform(-lim, lim, (H * W, E)).astype(np.float32)
+    gamma, beta = np.ones(E, np.float32), np.zeros(E, np.float32)
+    ref, _ = oracle.tsa_fwd(x, wq, wk, wv, wo, B, S, H, W, 1 / math.sqrt(W), True, False, True, True, gamma, beta)
+    dev = lambda a: torch.from_numpy(a).cuda()
+    out = ctx.tsa_fwd(dev(x), dev(wq), dev(wk), dev(wv), dev(wo), B, S, H, W, scale=1 / math.sqrt(W),
+                      causal=True, time_major=False, gamma=dev(gamma), beta=dev(beta), mode=_lib.MODE_BF16)
+    assert np.abs(out.cpu().numpy() - ref).max() < 2e-2        # bf16 operands in the core, then LayerNorm
