@@ -21,7 +21,9 @@
  *
  * Parity pin: the reference ships no golden vectors and no CPU path.  The oracle is pinned
  * against outputs of the reference's own flashAttentionKernel, built unmodified from the
- * reference sources and run on a GPU (see ref_driver.cu and tests/golden/).
+ * reference sources and run on a GPU (see ref_driver.cu and tests/golden/ref_flash_case*), and
+ * the module functions against the reference's own cuDNN TimeSelfAttention, linked from the
+ * reference sources (see ref_tsa_driver.cu and tests/golden/ref_tsa_case*).
  *
  * Extensions beyond the reference (needed by the benchmark configurations): a causal flag,
  * per-sequence key lengths, a backward for the attention core, log-sum-exp output.
