@@ -184,11 +184,13 @@ int ltca_ctx_create(int device, void* stream, ltca_ctx** out) {
         delete ctx;
         return LTCA_ERR_NO_DEVICE;       // the kernels are built for sm_100a only
     }
-    if (cudaMalloc(&ctx->d_status, sizeof(uint32_t)) != cudaSuccess ||
-        cudaMemset(ctx->d_status, 0, sizeof(uint32_t)) != cudaSuccess) {
+    // one small allocation: the status word, then the work-item counters of the persistent kernels
+    if (cudaMalloc(&ctx->d_status, 16 * sizeof(uint32_t)) != cudaSuccess ||
+        cudaMemset(ctx->d_status, 0, 16 * sizeof(uint32_t)) != cudaSuccess) {
         delete ctx;
         return LTCA_ERR_CUDA;
     }
+    ctx->d_sched = reinterpret_cast<int*>(ctx->d_status + 4);
     *out = ctx;
     return LTCA_OK;
 }
@@ -233,7 +235,8 @@ int ltca_device_status(ltca_ctx* ctx, uint32_t* status_out) {
     uint32_t v = 0;
     LTCA_CUDA_OK(ctx, cudaMemcpyAsync(&v, ctx->d_status, sizeof(v), cudaMemcpyDeviceToHost, ctx->stream));
     LTCA_CUDA_OK(ctx, cudaStreamSynchronize(ctx->stream));
-    if (v) LTCA_CUDA_OK(ctx, cudaMemsetAsync(ctx->d_status, 0, sizeof(v), ctx->stream));
+    // a kernel that gave up may have left its work-item counters mid-count: clear everything
+    if (v) LTCA_CUDA_OK(ctx, cudaMemsetAsync(ctx->d_status, 0, 16 * sizeof(uint32_t), ctx->stream));
     *status_out = v;
     if (v) return fail(ctx, LTCA_ERR_DEVICE, "device status word 0x%08x", v);
     return LTCA_OK;

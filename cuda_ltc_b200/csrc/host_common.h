@@ -18,6 +18,8 @@ struct ltca_ctx {
     int sm_count = 0;
     int cc_major = 0, cc_minor = 0;
     uint32_t* d_status = nullptr;     // device status word (allocated once at context creation)
+    int* d_sched = nullptr;           // work-item counters of the persistent kernels (same allocation:
+                                      // d_status + 4 .. ; two ints per kernel kind, kept at zero between launches)
     char err[512] = {0};
     // optional per-kernel timing of the backward pass (ltca_ctx_enable_kernel_timing)
     bool time_kernels = false;

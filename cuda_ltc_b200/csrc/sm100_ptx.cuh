@@ -325,6 +325,55 @@ __device__ __forceinline__ void sched_block(int& rank, int& h, int& b) {
     b = bh / H;
 }
 
+// ---- work items of a persistent kernel ----------------------------------------------------------
+// One CTA per SM takes work items from a global counter (list order = grouped heavy-first order,
+// so greedy hand-out balances the SMs to within one light item).  The producer thread fetches the
+// next item while the current one is still in flight and publishes it through a small shared-
+// memory queue; every consumer (MMA threads: one arrival each, elementwise warps: one arrival per
+// warp) reads the same sequence.  Item -1 ends the sequence.  The last CTA to finish puts the two
+// counters back to zero, so the next launch needs no memset.
+constexpr int kItemSlots = 4;
+struct ItemQueue {
+    uint32_t bar_full0, bar_empty0;      // kItemSlots barriers each, consecutive
+    volatile int* slots;                 // shared memory, kItemSlots ints
+    __device__ __forceinline__ uint32_t full(int nq) const { return bar_full0 + 8u * (nq % kItemSlots); }
+    __device__ __forceinline__ uint32_t empty(int nq) const { return bar_empty0 + 8u * (nq % kItemSlots); }
+    __device__ __forceinline__ uint32_t parity(int nq) const { return (uint32_t)((nq / kItemSlots) & 1); }
+    // producer thread: returns the item (or -1), -2 if a wait gave up
+    __device__ __forceinline__ int produce(int nq, int* counter, int n_items, const WaitCtx& w) const {
+        if (!mbar_wait(empty(nq), parity(nq) ^ 1u, w, 0xfa)) return -2;
+        int item = atomicAdd(counter, 1);
+        if (item >= n_items) item = -1;
+        slots[nq % kItemSlots] = item;
+        mbar_arrive(full(nq));           // release: the slot is written before the arrival is seen
+        return item;
+    }
+    // single consumer thread
+    __device__ __forceinline__ int consume(int nq, const WaitCtx& w) const {
+        if (!mbar_wait(full(nq), parity(nq), w, 0xfb)) return -2;
+        const int item = slots[nq % kItemSlots];
+        mbar_arrive(empty(nq));
+        return item;
+    }
+    // whole consumer warp (one arrival)
+    __device__ __forceinline__ int consume_warp(int nq, const WaitCtx& w) const {
+        if (!mbar_wait_warp(full(nq), parity(nq), w, 0xfc)) return -2;
+        const int item = slots[nq % kItemSlots];
+        __syncwarp();
+        if ((threadIdx.x & 31) == 0) mbar_arrive(empty(nq));
+        return item;
+    }
+};
+// Called by one thread per CTA at the very end: counters[0] = item counter, counters[1] = CTAs done.
+__device__ __forceinline__ void item_counters_release(int* counters) {
+    __threadfence();
+    if (atomicAdd(counters + 1, 1) == (int)gridDim.x - 1) {
+        counters[0] = 0;
+        counters[1] = 0;
+        __threadfence();
+    }
+}
+
 // ---- small math helpers -----------------------------------------------------------------------
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
     float d;
