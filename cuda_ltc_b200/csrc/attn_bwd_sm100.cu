@@ -807,25 +807,42 @@ attn_bwd_dkv_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
 }
 
 // ---------------------------------------------------------------------------------------------
-// 4. dK, dV, single-tile variant (bf16 operands and results): one CTA per 128 keys, query steps
-// of 128.  Nothing in tensor memory is aliased, so the next step's S^T and dP^T are computed
-// while this step's P^T and dS^T are being formed, and the contractions have N = 128 or K = 128:
+// 4. dK, dV, single-tile persistent variant (bf16 operands and results).
+// Work item = 128 keys of one (batch, head); query steps of 128.  Nothing in tensor memory is
+// aliased, so the next step's S^T and dP^T are computed while this step's P^T and dS^T are being
+// formed, and the contractions have N = 128 or K = 128:
 //   S^T [0,128)  dP^T [128,256)  P^T bf16 [256,320)  dS^T bf16 [320,384)  dV [384,448)  dK [448,512)
+// One CTA per SM takes items from the global counter (see ItemQueue); K and V are double-buffered
+// so the next item's tiles and first query steps load while the current item drains, and the MMA
+// threads issue the next item's first S^T / dP^T before the current item's last accumulation.
 // 16 elementwise warps: warp w owns key rows 32 (w % 4) .. +31 and query columns 32 (w / 4) .. +31
 // of the step.  Two MMA threads share the issue work: warp 16 issues S^T and dV, warp 17 dP^T
 // and dK (each accumulator has one issuing thread, so the summation order is fixed).
 // ---------------------------------------------------------------------------------------------
+struct ItemGrid { int nblk, H, BH, n_items; int* counters; };
+
+// Entry `linear` of the grouped heavy-first order (see sched_block): rank 0 is the heaviest block.
+__device__ __forceinline__ void sched_item(const ItemGrid& g, int linear, int& rank, int& h, int& b) {
+    const int grp = linear / (kSchedGroup * g.nblk);
+    const int n_in = min(kSchedGroup, g.BH - grp * kSchedGroup);
+    const int local = linear - grp * kSchedGroup * g.nblk;
+    rank = local / n_in;
+    const int bh = grp * kSchedGroup + local % n_in;
+    h = bh % g.H;
+    b = bh / g.H;
+}
+
 struct Dkv4Smem {
     static constexpr int kStages = 4;                         // ring of (Q_j, dO_j, lse2_j, delta_j)
     static constexpr int kStageBytes = 2 * kBigTile + 1024;
-    static constexpr int kKOff = 0;
-    static constexpr int kVOff = kBigTile;
-    static constexpr int kRingOff = 2 * kBigTile;
+    static constexpr int kResOff = 0;                         // two (K, V) buffers
+    static constexpr int kRingOff = 4 * kBigTile;
     static constexpr int kBarOff = kRingOff + kStages * kStageBytes;
-    // bars: kv_full, ring_full[S], ring_empty[S], sdp_full, sdp_free, pds_full, acc_done, turn
-    static constexpr int kNumBars = 1 + 2 * kStages + 5;
-    static constexpr int kMiscOff = kBarOff + kNumBars * 8;
-    static constexpr int kDynBytes = kMiscOff + 16 + 1024;
+    // bars: res_full[2], res_empty[2], ring_full[S], ring_empty[S], sdp_full, sdp_free, pds_full, acc_done,
+    // acc_free, item_full[kItemSlots], item_empty[kItemSlots]
+    static constexpr int kNumBars = 4 + 2 * kStages + 5 + 2 * kItemSlots;
+    static constexpr int kMiscOff = kBarOff + kNumBars * 8;   // tmem base, abort flag, item slots
+    static constexpr int kDynBytes = kMiscOff + 16 + 4 * kItemSlots + 1024;
 };
 
 __device__ __forceinline__ void store_row16_bf16(__nv_bfloat16* dst, const uint32_t (&o)[16], float mul) {
@@ -845,45 +862,39 @@ __global__ void __launch_bounds__(kThreads, 1)
 attn_bwd_dkv4_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
                            const __grid_constant__ CUtensorMap tmap_do,
                            const __grid_constant__ CUtensorMap tmap_k,
-                           const __grid_constant__ CUtensorMap tmap_v, const BwdArgs a) {
+                           const __grid_constant__ CUtensorMap tmap_v, const BwdArgs a, const ItemGrid grid) {
     using L = Dkv4Smem;
     constexpr int kQStep = 128;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-    const uint32_t k_smem = smem_base + L::kKOff, v_smem = smem_base + L::kVOff;
+    const uint32_t res_smem = smem_base + L::kResOff;
     const uint32_t ring_smem = smem_base + L::kRingOff, bar_base = smem_base + L::kBarOff;
-    auto bar_kv_full = [&]() { return bar_base; };
-    auto bar_ring_full = [&](int s) { return bar_base + 8u * (1 + s); };
-    auto bar_ring_empty = [&](int s) { return bar_base + 8u * (1 + L::kStages + s); };
-    const uint32_t bar_sdp_full = bar_base + 8u * (1 + 2 * L::kStages);
+    auto bar_res_full = [&](int r) { return bar_base + 8u * r; };
+    auto bar_res_empty = [&](int r) { return bar_base + 8u * (2 + r); };
+    auto bar_ring_full = [&](int s) { return bar_base + 8u * (4 + s); };
+    auto bar_ring_empty = [&](int s) { return bar_base + 8u * (4 + L::kStages + s); };
+    const uint32_t bar_sdp_full = bar_base + 8u * (4 + 2 * L::kStages);
     const uint32_t bar_sdp_free = bar_sdp_full + 8u;
     const uint32_t bar_pds_full = bar_sdp_full + 16u;
     const uint32_t bar_acc_done = bar_sdp_full + 24u;
-    const uint32_t bar_turn = bar_sdp_full + 32u;
+    const uint32_t bar_acc_free = bar_sdp_full + 32u;
     volatile uint32_t* misc = reinterpret_cast<volatile uint32_t*>(smem_gen + L::kMiscOff);
+    const ItemQueue iq{bar_sdp_full + 40u, bar_sdp_full + 40u + 8u * kItemSlots,
+                       reinterpret_cast<volatile int*>(smem_gen + L::kMiscOff + 16)};
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    int n_block, h, b;
-    sched_block(n_block, h, b);                     // early key blocks carry the most causal work
-    const int k0 = n_block * kTile;
-
-    int kvlen = a.Sk;
-    if (a.kv_len) kvlen = min(max(a.kv_len[b], 0), a.Sk);
     const int n_q = (a.Sq + kQStep - 1) / kQStep;   // query steps in total
-    int j_begin = 0;                                // first query step that can see the tile's keys
-    if (a.causal) j_begin = max(0, k0 - a.causal_off) / kQStep;
-    const bool active = (k0 < kvlen) && (j_begin < n_q);
-    const int n_it = active ? n_q - j_begin : 0;
 
     if (threadIdx.x == 0) {
-        mbar_init(bar_kv_full(), 1);
+        for (int r = 0; r < 2; ++r) { mbar_init(bar_res_full(r), 1); mbar_init(bar_res_empty(r), 2); }
         for (int s = 0; s < L::kStages; ++s) { mbar_init(bar_ring_full(s), 1); mbar_init(bar_ring_empty(s), 2); }
         mbar_init(bar_sdp_full, 2);                // one commit per MMA thread
         mbar_init(bar_sdp_free, 16);               // one arrival per elementwise warp
         mbar_init(bar_pds_full, 16);
         mbar_init(bar_acc_done, 2);
-        mbar_init(bar_turn, 8);
+        mbar_init(bar_acc_free, 16);
+        for (int i = 0; i < kItemSlots; ++i) { mbar_init(iq.full(i), 1); mbar_init(iq.empty(i), 18); }
         misc[1] = 0u;
         mbar_fence_init();
     }
@@ -893,45 +904,70 @@ attn_bwd_dkv4_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
     tc_fence_after_sync();
     const uint32_t tmem_base = misc[0];
     const WaitCtx wc{&misc[1], a.status};
-    auto slot_of = [&](int it) { return it % L::kStages; };
-    auto phase_of = [&](int it) { return (uint32_t)((it / L::kStages) & 1); };
+    auto slot_of = [&](int g) { return g % L::kStages; };
+    auto phase_of = [&](int g) { return (uint32_t)((g / L::kStages) & 1); };
+    // the item's key tile, first query step that can see it and number of query steps (0: none)
+    auto item_steps = [&](int linear, int& k0, int& h, int& b, int& kvlen, int& j_begin) {
+        int rank;
+        sched_item(grid, linear, rank, h, b);
+        k0 = rank * kTile;                          // early key blocks carry the most causal work
+        kvlen = a.Sk;
+        if (a.kv_len) kvlen = min(max(a.kv_len[b], 0), a.Sk);
+        j_begin = 0;
+        if (a.causal) j_begin = max(0, k0 - a.causal_off) / kQStep;
+        const bool active = (k0 < kvlen) && (j_begin < n_q);
+        return active ? n_q - j_begin : 0;
+    };
 
     if (warp >= 16) {
       reg_dealloc<kCtrlRegs>();
       if (warp == kTmaWarp) {
-        if (lane == 0 && active) {
-            mbar_arrive_expect_tx(bar_kv_full(), 2u * kBigTile);
-            tma_load_4d(k_smem, &tmap_k, bar_kv_full(), 0, k0, h, b);
-            tma_load_4d(v_smem, &tmap_v, bar_kv_full(), 0, k0, h, b);
-            const float* lse2_row = a.lse2 + ((int64_t)b * a.H + h) * a.Sq_pad;
-            const float* dlt_row = a.delta + ((int64_t)b * a.H + h) * a.Sq_pad;
+        if (lane == 0) {
+            int g = 0, na = 0;
             bool ok = true;
-            for (int it = 0; it < n_it && ok; ++it) {
-                const int j = j_begin + it;
-                ok = mbar_wait(bar_ring_empty(slot_of(it)), phase_of(it) ^ 1u, wc, 0xa0);
+            for (int nq = 0; ok; ++nq) {
+                const int linear = iq.produce(nq, grid.counters, grid.n_items, wc);
+                if (linear < 0) break;
+                int k0, h, b, kvlen, j_begin;
+                const int n_it = item_steps(linear, k0, h, b, kvlen, j_begin);
+                if (n_it == 0) continue;
+                const int r = na & 1;
+                ok = mbar_wait(bar_res_empty(r), (uint32_t)(((na >> 1) & 1) ^ 1), wc, 0xa1);
                 if (!ok) break;
-                const uint32_t st = ring_smem + slot_of(it) * L::kStageBytes;
-                const uint32_t bar = bar_ring_full(slot_of(it));
-                mbar_arrive_expect_tx(bar, 2u * kBigTile + 1024u);
-                tma_load_4d(st, &tmap_q, bar, 0, j * kQStep, h, b);
-                tma_load_4d(st + kBigTile, &tmap_do, bar, 0, j * kQStep, h, b);
-                asm volatile(
-                    "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], 512, [%2];"
-                    ::"r"(st + 2 * kBigTile), "l"(reinterpret_cast<uint64_t>(lse2_row + j * kQStep)), "r"(bar)
-                    : "memory");
-                asm volatile(
-                    "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], 512, [%2];"
-                    ::"r"(st + 2 * kBigTile + 512), "l"(reinterpret_cast<uint64_t>(dlt_row + j * kQStep)), "r"(bar)
-                    : "memory");
+                mbar_arrive_expect_tx(bar_res_full(r), 2u * kBigTile);
+                tma_load_4d(res_smem + r * 2 * kBigTile, &tmap_k, bar_res_full(r), 0, k0, h, b);
+                tma_load_4d(res_smem + r * 2 * kBigTile + kBigTile, &tmap_v, bar_res_full(r), 0, k0, h, b);
+                const float* lse2_row = a.lse2 + ((int64_t)b * a.H + h) * a.Sq_pad;
+                const float* dlt_row = a.delta + ((int64_t)b * a.H + h) * a.Sq_pad;
+                for (int it = 0; it < n_it && ok; ++it, ++g) {
+                    const int j = j_begin + it;
+                    ok = mbar_wait(bar_ring_empty(slot_of(g)), phase_of(g) ^ 1u, wc, 0xa0);
+                    if (!ok) break;
+                    const uint32_t st = ring_smem + slot_of(g) * L::kStageBytes;
+                    const uint32_t bar = bar_ring_full(slot_of(g));
+                    mbar_arrive_expect_tx(bar, 2u * kBigTile + 1024u);
+                    tma_load_4d(st, &tmap_q, bar, 0, j * kQStep, h, b);
+                    tma_load_4d(st + kBigTile, &tmap_do, bar, 0, j * kQStep, h, b);
+                    asm volatile(
+                        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], 512, [%2];"
+                        ::"r"(st + 2 * kBigTile), "l"(reinterpret_cast<uint64_t>(lse2_row + j * kQStep)), "r"(bar)
+                        : "memory");
+                    asm volatile(
+                        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], 512, [%2];"
+                        ::"r"(st + 2 * kBigTile + 512), "l"(reinterpret_cast<uint64_t>(dlt_row + j * kQStep)),
+                          "r"(bar)
+                        : "memory");
+                }
+                ++na;
             }
         }
       } else if (warp == kMmaWarp0 || warp == kMmaWarp0 + 1) {
         // which == 0: S^T = K Q_j^T and dV += P^T dO_j;  which == 1: dP^T = V dO_j^T and dK += dS^T Q_j
         const int which = warp - kMmaWarp0;
-        if (lane == 0 && active) {
+        if (lane == 0) {
             constexpr uint32_t idesc_s = make_idesc_bf16(kTile, kQStep, 0, 0);
             constexpr uint32_t idesc_acc = make_idesc_bf16(kTile, kD, 0, 1);
-            const uint64_t a_desc = make_smem_desc_sw128(which == 0 ? k_smem : v_smem, 16, 1024);
+            const uint64_t res_desc = make_smem_desc_sw128(res_smem + (which == 0 ? 0 : kBigTile), 16, 1024);
             // the streamed operand of the first contraction (Q for S^T, dO for dP^T), K-major
             const uint64_t b1_desc = make_smem_desc_sw128(ring_smem + (which == 0 ? 0 : kBigTile), 16, 1024);
             // the streamed operand of the accumulation (dO for dV, Q for dK), rows as the contraction index
@@ -939,48 +975,60 @@ attn_bwd_dkv4_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
             const uint32_t d1 = tmem_base + (which == 0 ? 0 : 128);
             const uint32_t a2 = tmem_base + (which == 0 ? 256 : 320);
             const uint32_t d2 = tmem_base + (which == 0 ? 384 : 448);
-            auto issue_first = [&](int slot) {
-                const uint64_t bd = b1_desc + (uint64_t)((slot * L::kStageBytes) >> 4);
-#pragma unroll
-                for (int k = 0; k < kD / 16; ++k) mma_ss(d1, a_desc + 2 * k, bd + 2 * k, idesc_s, k > 0);
-            };
-            auto issue_acc = [&](int slot, bool acc) {
-                const uint64_t bd = b2_desc + (uint64_t)((slot * L::kStageBytes) >> 4);
+            // the accumulation that is still to be issued (one step behind the first contraction)
+            bool pending = false;
+            int p_g = 0, p_na = 0;
+            bool p_acc = false, p_first = false;
+            bool ok = true;
+            auto do_acc = [&]() {
+                ok = mbar_wait(bar_pds_full, (uint32_t)(p_g & 1), wc, 0xb4);
+                // the previous item's dV / dK must have left tensor memory before they are overwritten
+                if (ok && p_first && p_na > 0) ok = mbar_wait(bar_acc_free, (uint32_t)((p_na - 1) & 1), wc, 0xb6);
+                if (!ok) return;
+                tc_fence_after_sync();
+                const uint64_t bd = b2_desc + (uint64_t)((slot_of(p_g) * L::kStageBytes) >> 4);
 #pragma unroll
                 for (int k = 0; k < kQStep / 16; ++k)
-                    mma_ts(d2, a2 + k * 8, bd + 128 * k, idesc_acc, (acc || k > 0) ? 1u : 0u);
+                    mma_ts(d2, a2 + k * 8, bd + 128 * k, idesc_acc, (p_acc || k > 0) ? 1u : 0u);
+                mma_commit(bar_acc_done);
+                mma_commit(bar_ring_empty(slot_of(p_g)));
+                pending = false;
             };
-            bool ok = mbar_wait(bar_kv_full(), 0, wc, 0xb0);
-            ok = ok && mbar_wait(bar_ring_full(slot_of(0)), phase_of(0), wc, 0xb1);
-            if (ok) {
-                tc_fence_after_sync();
-                issue_first(slot_of(0));
-                mma_commit(bar_sdp_full);
-            }
-            for (int it = 0; it < n_it && ok; ++it) {
-                if (it + 1 < n_it) {
-                    ok = mbar_wait(bar_ring_full(slot_of(it + 1)), phase_of(it + 1), wc, 0xb2);
-                    ok = ok && mbar_wait(bar_sdp_free, (uint32_t)(it & 1), wc, 0xb3);
+            int g = 0, na = 0;
+            for (int nq = 0; ok; ++nq) {
+                const int linear = iq.consume(nq, wc);
+                if (linear < 0) break;
+                int k0, h, b, kvlen, j_begin;
+                const int n_it = item_steps(linear, k0, h, b, kvlen, j_begin);
+                if (n_it == 0) continue;
+                const int r = na & 1;
+                ok = mbar_wait(bar_res_full(r), (uint32_t)((na >> 1) & 1), wc, 0xb0);
+                const uint64_t a_desc = res_desc + (uint64_t)((r * 2 * kBigTile) >> 4);
+                for (int it = 0; it < n_it && ok; ++it, ++g) {
+                    ok = mbar_wait(bar_ring_full(slot_of(g)), phase_of(g), wc, 0xb2);
+                    if (g >= 1) ok = ok && mbar_wait(bar_sdp_free, (uint32_t)((g - 1) & 1), wc, 0xb3);
                     if (!ok) break;
                     tc_fence_after_sync();
-                    issue_first(slot_of(it + 1));
+                    const uint64_t bd = b1_desc + (uint64_t)((slot_of(g) * L::kStageBytes) >> 4);
+#pragma unroll
+                    for (int k = 0; k < kD / 16; ++k) mma_ss(d1, a_desc + 2 * k, bd + 2 * k, idesc_s, k > 0);
                     mma_commit(bar_sdp_full);
+                    if (it == n_it - 1) mma_commit(bar_res_empty(r));   // K (or V) of this item is no longer read
+                    if (pending) do_acc();
+                    if (!ok) break;
+                    p_g = g; p_na = na; p_acc = it > 0; p_first = it == 0;
+                    pending = true;
                 }
-                ok = mbar_wait(bar_pds_full, (uint32_t)(it & 1), wc, 0xb4);
-                if (!ok) break;
-                tc_fence_after_sync();
-                issue_acc(slot_of(it), it > 0);
-                mma_commit(bar_acc_done);
-                mma_commit(bar_ring_empty(slot_of(it)));
+                ++na;
             }
-            if (ok && n_it > 0) ok = mbar_wait(bar_acc_done, (uint32_t)((n_it - 1) & 1), wc, 0xb5);
+            if (ok && pending) do_acc();
+            if (ok && g > 0) ok = mbar_wait(bar_acc_done, (uint32_t)((g - 1) & 1), wc, 0xb5);
         }
       }
     } else {
         reg_alloc<kMathRegs>();
         const int wq = warp & 3, cq = warp >> 2;
         const int row = wq * 32 + lane;
-        const int kj = k0 + row;                                   // this thread's key
         const uint32_t lane_base = (uint32_t)(wq * 32) << 16;
         const uint32_t tS = tmem_base + lane_base + 32 * cq;
         const uint32_t tDP = tS + 128;
@@ -990,15 +1038,34 @@ attn_bwd_dkv4_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
         const uint32_t tDK = tDV + 64;
         const float c2 = a.scale_log2;
         const bool general = (a.keep_mask != nullptr) || (a.use_clamp != 0);
-        const bool key_live = kj < kvlen;
 
+        int g = 0;
         bool ok = true;
-        for (int it = 0; it < n_it; ++it) {
-            const int j = j_begin + it;
-            ok = mbar_wait_warp(bar_sdp_full, (uint32_t)(it & 1), wc, 0xc0);
+        for (int nq = 0; ok; ++nq) {
+            const int linear = iq.consume_warp(nq, wc);
+            if (linear < 0) break;
+            int k0, h, b, kvlen, j_begin;
+            const int n_it = item_steps(linear, k0, h, b, kvlen, j_begin);
+            const int kj = k0 + row;                                   // this thread's key
+            const bool key_live = kj < kvlen;
+            __nv_bfloat16* dkrow = reinterpret_cast<__nv_bfloat16*>(a.dk) + b * a.dks.batch + h * a.dks.head +
+                                   (int64_t)kj * a.dks.seq + cq * 16;
+            __nv_bfloat16* dvrow = reinterpret_cast<__nv_bfloat16*>(a.dv) + b * a.dvs.batch + h * a.dvs.head +
+                                   (int64_t)kj * a.dvs.seq + cq * 16;
+            if (n_it == 0) {
+                if (kj < a.Sk) {                       // no query sees these keys: the gradients are zero
+                    uint32_t z[16];
+#pragma unroll
+                    for (int c = 0; c < 16; ++c) z[c] = 0u;
+                    store_row16_bf16(dvrow, z, 0.f);
+                    store_row16_bf16(dkrow, z, 0.f);
+                }
+                continue;
+            }
+            uint32_t s[32], dp[32];
+            ok = mbar_wait_warp(bar_sdp_full, (uint32_t)(g & 1), wc, 0xc0);
             if (!ok) break;
             tc_fence_after_sync();
-            uint32_t s[32], dp[32];
             tmem_ld32(tS, s);
             tmem_ld32(tDP, dp);
             tmem_wait_ld();
@@ -1006,101 +1073,106 @@ attn_bwd_dkv4_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_sdp_free);
-            // the warps of query columns 64..127 take their turn after those of columns 0..63
-            if (LTCA_BWD_TURNS && cq >= 2) {
-                ok = mbar_wait_warp(bar_turn, (uint32_t)(it & 1), wc, 0xc3);
-                if (!ok) break;
-            }
-            // lse2 and delta of this thread's 32 query columns (every lane reads the same address)
-            const float4* st4 = reinterpret_cast<const float4*>(
-                smem_gen + L::kRingOff + slot_of(it) * L::kStageBytes + 2 * kBigTile) + cq * 8;
-            const int q0 = j * kQStep + cq * 32;
-            // a query column c is hidden from this key when q0 + c + off < kj
-            const bool edge = !key_live || (k0 + kTile > kvlen) ||
-                              (a.causal && (j * kQStep + a.causal_off < k0 + kTile - 1));
-            if (edge || general) {
+
+            for (int it = 0; it < n_it && ok; ++it, ++g) {
+                const int j = j_begin + it;
+                // lse2 and delta of this thread's 32 query columns (every lane reads the same address)
+                const float4* st4 = reinterpret_cast<const float4*>(
+                    smem_gen + L::kRingOff + slot_of(g) * L::kStageBytes + 2 * kBigTile) + cq * 8;
+                const int q0 = j * kQStep + cq * 32;
+                // a query column c is hidden from this key when q0 + c + off < kj
+                const bool edge = !key_live || (k0 + kTile > kvlen) ||
+                                  (a.causal && (j * kQStep + a.causal_off < k0 + kTile - 1));
+                if (edge || general) {
 #pragma unroll
-                for (int c4 = 0; c4 < 8; ++c4) {
-                    const float4 l4 = st4[c4];
-                    const float4 d4 = st4[32 + c4];
-                    const float ls[4] = {l4.x, l4.y, l4.z, l4.w};
-                    const float dl[4] = {d4.x, d4.y, d4.z, d4.w};
+                    for (int c4 = 0; c4 < 8; ++c4) {
+                        const float4 l4 = st4[c4];
+                        const float4 d4 = st4[32 + c4];
+                        const float ls[4] = {l4.x, l4.y, l4.z, l4.w};
+                        const float dl[4] = {d4.x, d4.y, d4.z, d4.w};
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const int c = 4 * c4 + e;
-                        const float sv = __uint_as_float(s[c]);
-                        float p = fast_exp2(fmaf(sv, c2, -ls[e]));
-                        float d = p * (__uint_as_float(dp[c]) - dl[e]);
-                        bool vis = key_live && (!a.causal || (kj <= q0 + c + a.causal_off));
-                        if (vis && a.keep_mask && (q0 + c) < a.Sq)
-                            vis = a.keep_mask[((int64_t)b * a.Sq + q0 + c) * a.Sk + kj] != 0.0f;
-                        if (a.use_clamp && sv >= a.clamp_raw) {
-                            p = fast_exp2(a.clamp_log2 - ls[e]);
-                            d = 0.f;
+                        for (int e = 0; e < 4; ++e) {
+                            const int c = 4 * c4 + e;
+                            const float sv = __uint_as_float(s[c]);
+                            float p = fast_exp2(fmaf(sv, c2, -ls[e]));
+                            float d = p * (__uint_as_float(dp[c]) - dl[e]);
+                            bool vis = key_live && (!a.causal || (kj <= q0 + c + a.causal_off));
+                            if (vis && a.keep_mask && (q0 + c) < a.Sq)
+                                vis = a.keep_mask[((int64_t)b * a.Sq + q0 + c) * a.Sk + kj] != 0.0f;
+                            if (a.use_clamp && sv >= a.clamp_raw) {
+                                p = fast_exp2(a.clamp_log2 - ls[e]);
+                                d = 0.f;
+                            }
+                            s[c] = __float_as_uint(vis ? p : 0.f);
+                            dp[c] = __float_as_uint(vis ? d : 0.f);
                         }
-                        s[c] = __float_as_uint(vis ? p : 0.f);
-                        dp[c] = __float_as_uint(vis ? d : 0.f);
+                    }
+                } else {
+#pragma unroll
+                    for (int c4 = 0; c4 < 8; ++c4) {
+                        const float4 l4 = st4[c4];
+                        const float4 d4 = st4[32 + c4];
+                        const float ls[4] = {l4.x, l4.y, l4.z, l4.w};
+                        const float dl[4] = {d4.x, d4.y, d4.z, d4.w};
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const int c = 4 * c4 + e;
+                            const float p = fast_exp2(fmaf(__uint_as_float(s[c]), c2, -ls[e]));
+                            s[c] = __float_as_uint(p);
+                            dp[c] = __float_as_uint(p * (__uint_as_float(dp[c]) - dl[e]));
+                        }
                     }
                 }
-            } else {
-#pragma unroll
-                for (int c4 = 0; c4 < 8; ++c4) {
-                    const float4 l4 = st4[c4];
-                    const float4 d4 = st4[32 + c4];
-                    const float ls[4] = {l4.x, l4.y, l4.z, l4.w};
-                    const float dl[4] = {d4.x, d4.y, d4.z, d4.w};
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const int c = 4 * c4 + e;
-                        const float p = fast_exp2(fmaf(__uint_as_float(s[c]), c2, -ls[e]));
-                        s[c] = __float_as_uint(p);
-                        dp[c] = __float_as_uint(p * (__uint_as_float(dp[c]) - dl[e]));
-                    }
+                uint32_t pt[16], dst[16], unused[16];
+                pack32<false>(s, pt, unused);
+                pack32<false>(dp, dst, unused);
+                if (g > 0) {
+                    // the accumulations of the previous step must have read P^T and dS^T
+                    ok = mbar_wait_warp(bar_acc_done, (uint32_t)((g - 1) & 1), wc, 0xc1);
+                    if (!ok) break;
                 }
-            }
-            uint32_t pt[16], dst[16], unused[16];
-            pack32<false>(s, pt, unused);
-            pack32<false>(dp, dst, unused);
-            if (LTCA_BWD_TURNS && cq < 2) {
+                tmem_st16(tP, pt);
+                tmem_st16(tDS, dst);
+                tmem_wait_st();
+                tc_fence_before_sync();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(bar_turn);
+                if (lane == 0) mbar_arrive(bar_pds_full);
+                // (P^T and dS^T are announced before the next S^T / dP^T are awaited: the tensor pipe is
+                // the busier unit in this kernel and must get this step's accumulations as early as possible)
+                if (it + 1 < n_it) {
+                    ok = mbar_wait_warp(bar_sdp_full, (uint32_t)((g + 1) & 1), wc, 0xc0);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    tmem_ld32(tS, s);
+                    tmem_ld32(tDP, dp);
+                    tmem_wait_ld();
+                    tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar_sdp_free);
+                }
             }
-            if (it > 0) {
-                // the accumulations of the previous step must have read P^T and dS^T
-                ok = mbar_wait_warp(bar_acc_done, (uint32_t)((it - 1) & 1), wc, 0xc1);
-                if (!ok) break;
-            }
-            tmem_st16(tP, pt);
-            tmem_st16(tDS, dst);
-            tmem_wait_st();
+            if (!ok) break;
+            // item epilogue: dV and scale * dK out of tensor memory, which is then free for the next item
+            ok = mbar_wait_warp(bar_acc_done, (uint32_t)((g - 1) & 1), wc, 0xc2);
+            if (!ok) break;
+            tc_fence_after_sync();
+            uint32_t ov[16], ok_[16];
+            tmem_ld16(tDV, ov);
+            tmem_ld16(tDK, ok_);
+            tmem_wait_ld();
             tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar_pds_full);
-        }
-        // epilogue: dV and scale * dK (zeros for tiles that no query can see)
-        if (ok && k0 < a.Sk) {
-            if (n_it > 0) {
-                ok = mbar_wait_warp(bar_acc_done, (uint32_t)((n_it - 1) & 1), wc, 0xc2);
-                tc_fence_after_sync();
+            if (lane == 0) mbar_arrive(bar_acc_free);
+            if (kj < a.Sk) {
+                store_row16_bf16(dvrow, ov, 1.0f);
+                store_row16_bf16(dkrow, ok_, a.scale);
             }
-            __nv_bfloat16* dkrow = reinterpret_cast<__nv_bfloat16*>(a.dk) + b * a.dks.batch + h * a.dks.head +
-                                   (int64_t)kj * a.dks.seq + cq * 16;
-            __nv_bfloat16* dvrow = reinterpret_cast<__nv_bfloat16*>(a.dv) + b * a.dvs.batch + h * a.dvs.head +
-                                   (int64_t)kj * a.dvs.seq + cq * 16;
-            uint32_t o[16];
-            if (n_it > 0 && ok) { tmem_ld16(tDV, o); tmem_wait_ld(); }
-            else {
-#pragma unroll
-                for (int c = 0; c < 16; ++c) o[c] = 0u;
-            }
-            if (kj < a.Sk) store_row16_bf16(dvrow, o, 1.0f);
-            if (n_it > 0 && ok) { tmem_ld16(tDK, o); tmem_wait_ld(); }
-            if (kj < a.Sk) store_row16_bf16(dkrow, o, a.scale);
         }
     }
 
     tc_fence_before_sync();
     __syncthreads();
+    if (threadIdx.x == 0) item_counters_release(grid.counters);
     if (warp == kMmaWarp0) {
         __syncwarp();
         if (misc[1]) __nanosleep(200000);
@@ -1135,19 +1207,6 @@ struct Dq4Smem {
     static constexpr int kMiscOff = kBarOff + kNumBars * 8;        // tmem base, abort flag, item slots
     static constexpr int kDynBytes = kMiscOff + 16 + 4 * kItemSlots + 1024;
 };
-
-struct ItemGrid { int nblk, H, BH, n_items; int* counters; };
-
-// Entry `linear` of the grouped heavy-first order (see sched_block): rank 0 is the heaviest block.
-__device__ __forceinline__ void sched_item(const ItemGrid& g, int linear, int& rank, int& h, int& b) {
-    const int grp = linear / (kSchedGroup * g.nblk);
-    const int n_in = min(kSchedGroup, g.BH - grp * kSchedGroup);
-    const int local = linear - grp * kSchedGroup * g.nblk;
-    rank = local / n_in;
-    const int bh = grp * kSchedGroup + local % n_in;
-    h = bh % g.H;
-    b = bh / g.H;
-}
 
 __global__ void __launch_bounds__(kThreads, 1)
 attn_bwd_dq4_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
@@ -1564,9 +1623,15 @@ int launch_main(ltca_ctx* ctx, const ltca_attn_params* p, const void* q, const v
                                                        Dkv4Smem::kDynBytes));
                 attr4_done = true;
             }
-            dim3 g4((p->Sk + kTile - 1) / kTile, p->H, p->B);
-            attn_bwd_dkv4_sm100_kernel<<<g4, kThreads, Dkv4Smem::kDynBytes, ctx->stream>>>(tq128, tdo128, tk128,
-                                                                                           tv128, a);
+            ItemGrid ig;
+            ig.nblk = (p->Sk + kTile - 1) / kTile;
+            ig.H = p->H;
+            ig.BH = p->H * p->B;
+            ig.n_items = ig.nblk * ig.BH;
+            ig.counters = ctx->d_sched + 4;             // ints 4,5: the dK/dV kernel's item counters
+            const int n_cta = ig.n_items < ctx->sm_count ? ig.n_items : ctx->sm_count;
+            attn_bwd_dkv4_sm100_kernel<<<n_cta, kThreads, Dkv4Smem::kDynBytes, ctx->stream>>>(tq128, tdo128, tk128,
+                                                                                             tv128, a, ig);
             LTCA_LAUNCH_OK(ctx, "attn_bwd_dkv4_sm100_kernel");
             kernel_timing_mark(ctx, 3);
             return LTCA_OK;
