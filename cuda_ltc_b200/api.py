@@ -178,7 +178,7 @@ class Context:
 
     # ---- TimeSelfAttention module --------------------------------------------------------
     def _tsa_params(self, x, wq, wk, wv, wo, B, S, H, head_width, scale, causal, time_major,
-                    use_residual, use_layer_norm, gamma, beta, keep_mask, mode):
+                    use_residual, use_layer_norm, gamma, beta, keep_mask, mode, biases=(None, None, None, None)):
         from ._lib import TsaParams
         E = x.shape[1]
         assert x.shape == (B * S, E) and x.dtype == torch.float32 and x.is_contiguous()
@@ -195,6 +195,10 @@ class Context:
             p.ln_gamma, p.ln_beta = gamma.data_ptr(), beta.data_ptr()
         if keep_mask is not None:
             p.keep_mask = keep_mask.data_ptr()
+        for name, b in zip(("bq", "bk", "bv", "bo"), biases):
+            if b is not None:
+                assert b.dtype == torch.float32 and b.is_contiguous()
+                setattr(p, name, b.data_ptr())
         return p
 
     def _tsa_workspace(self, p, which):
@@ -206,10 +210,10 @@ class Context:
 
     def tsa_fwd(self, x, wq, wk, wv, wo, B, S, H, head_width, scale=1.0, causal=False, time_major=True,
                 use_residual=True, use_layer_norm=True, gamma=None, beta=None, keep_mask=None,
-                mode=_lib.MODE_AUTO):
+                mode=_lib.MODE_AUTO, bq=None, bk=None, bv=None, bo=None):
         """out = LayerNorm(x + MHA(x)); x [B*S, E] fp32, weights as in ``ltca_tsa_params``."""
         p = self._tsa_params(x, wq, wk, wv, wo, B, S, H, head_width, scale, causal, time_major,
-                             use_residual, use_layer_norm, gamma, beta, keep_mask, mode)
+                             use_residual, use_layer_norm, gamma, beta, keep_mask, mode, (bq, bk, bv, bo))
         out = torch.empty_like(x)
         p.out = out.data_ptr()
         ws = self._tsa_workspace(p, 0)
@@ -218,10 +222,10 @@ class Context:
         return out
 
     def tsa_bwd(self, x, wq, wk, wv, wo, dy, B, S, H, head_width, scale=1.0, causal=False, time_major=True,
-                keep_mask=None, mode=_lib.MODE_AUTO):
+                keep_mask=None, mode=_lib.MODE_AUTO, bq=None, bk=None, bv=None):
         """(dx, dwq, dwk, dwv, dwo) of the module; LayerNorm and residual pass dy through."""
         p = self._tsa_params(x, wq, wk, wv, wo, B, S, H, head_width, scale, causal, time_major,
-                             False, False, None, None, keep_mask, mode)
+                             False, False, None, None, keep_mask, mode, (bq, bk, bv, None))
         dx = torch.empty_like(x)
         dws = [torch.empty_like(w) for w in (wq, wk, wv, wo)]
         p.dy, p.dx = dy.data_ptr(), dx.data_ptr()

@@ -1,0 +1,367 @@
+// Projection GEMMs of the TimeSelfAttention module on the tcgen05 tensor pipe.
+//
+//   C[M,N] = sum over pairs p of op(A_p) op(B_p)  (+ bias[N]),   bf16 operands, fp32 accumulation
+//
+// replaces the reference's cublasSgemm + addBiasKernel calls
+// (reference src/ml/flash_attention.cu:866-958, 1075-1104) and the projections that cuDNN performs
+// inside cudnnMultiHeadAttnForward / BackwardData / BackwardWeights (src/ml/cuDNN_ops.cu:203, 301, 366).
+//
+// Operand forms (all row-major in HBM):
+//   A "K-major":  stored [M, K]  (activations x, ctx, dy, dq ...)      -> one 128 x 64 TMA box
+//   A "M-major":  stored [K, M]  (x^T, ctx^T of the weight gradients)  -> two 64 x 64 boxes
+//   B "K-major":  stored [N, K]  (a weight matrix used transposed)     -> one 128 x 64 box
+//   B "N-major":  stored [K, N]  (a weight matrix used as stored; dq of the weight gradients)
+// so no operand is ever transposed in memory: the instruction descriptor's major bits select the
+// form and the shared-memory descriptors follow the layout the TMA boxes produce.
+//
+// One CTA computes one 128 x 128 tile of C: warp 0 is the TMA producer (ring of kStages
+// (A, B) stage pairs, 32 KB each), warp 1 issues the MMAs and owns the 128 tensor-memory columns,
+// warps 2-5 are the epilogue (one accumulator row per thread: tcgen05.ld, bias, convert, store).
+// grid.z runs independent problems (Q, K and V projections share one launch) and/or splits K
+// (weight gradients: K = batch x time is long and M x N is small, so the K range is cut into
+// slices whose partial tiles go to scratch and are summed in a fixed order by a second kernel).
+// `n_sum` > 1 accumulates several operand pairs into one tile (dx = dq Wq^T + dk Wk^T + dv Wv^T).
+#include "host_common.h"
+#include "gemm_sm100.h"
+#include "sm100_ptx.cuh"
+
+namespace ltca {
+
+namespace {
+
+constexpr int kBM = 128, kBN = 128, kBK = 64;
+constexpr int kStages = 6;
+constexpr int kTileBytes = 128 * kBK * 2;          // 16 KB per operand per stage
+constexpr int kGemmThreads = 192;
+constexpr int kBarOff = kStages * 2 * kTileBytes;
+constexpr int kNumBars = 2 * kStages + 1;
+constexpr int kMiscOff = kBarOff + kNumBars * 8;
+constexpr int kDynBytes = kMiscOff + 16 + 1024;
+
+struct GemmKArgs {
+    int M, N, K;
+    int n_sum, ksplit;
+    int64_t ldc;
+    int out_bf16;
+    void* C[3];
+    const float* bias[3];
+    float* partial;          // [problem][slice][M][N] when ksplit > 1
+    uint32_t* status;
+};
+
+template <bool kAMn, bool kBMn>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap ta0, const __grid_constant__ CUtensorMap ta1,
+                       const __grid_constant__ CUtensorMap ta2, const __grid_constant__ CUtensorMap tb0,
+                       const __grid_constant__ CUtensorMap tb1, const __grid_constant__ CUtensorMap tb2,
+                       const GemmKArgs g) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    const uint32_t bar_base = smem_base + kBarOff;
+    auto a_smem = [&](int s) { return smem_base + (uint32_t)(s * 2 * kTileBytes); };
+    auto b_smem = [&](int s) { return smem_base + (uint32_t)(s * 2 * kTileBytes + kTileBytes); };
+    auto bar_full = [&](int s) { return bar_base + 8u * s; };
+    auto bar_empty = [&](int s) { return bar_base + 8u * (kStages + s); };
+    const uint32_t bar_acc = bar_base + 8u * (2 * kStages);
+    volatile uint32_t* misc = reinterpret_cast<volatile uint32_t*>(smem_gen + kMiscOff);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = blockIdx.x * kBN, m0 = blockIdx.y * kBM;
+    const int problem = blockIdx.z / g.ksplit, slice = blockIdx.z % g.ksplit;
+    // this CTA's range of 64-wide K blocks
+    const int nkb = (g.K + kBK - 1) / kBK;
+    const int per = (nkb + g.ksplit - 1) / g.ksplit;
+    const int kb_begin = min(slice * per, nkb), kb_end = min(kb_begin + per, nkb);
+    const int pair_begin = g.n_sum > 1 ? 0 : problem;
+    const int n_pairs = g.n_sum > 1 ? g.n_sum : 1;
+    const int n_iters = n_pairs * (kb_end - kb_begin);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_empty(s), 1); }
+        mbar_init(bar_acc, 1);
+        misc[1] = 0u;
+        mbar_fence_init();
+    }
+    if (warp == 1) { tmem_alloc(smem_u32(const_cast<uint32_t*>(&misc[0])), 128); tmem_relinquish(); }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = misc[0];
+    const WaitCtx wc{&misc[1], g.status};
+
+    if (warp == 0) {
+        if (lane == 0) {
+            bool ok = true;
+            int it = 0;
+            for (int p = 0; p < n_pairs && ok; ++p) {
+                const int pair = pair_begin + p;
+                const CUtensorMap* ta = pair == 0 ? &ta0 : (pair == 1 ? &ta1 : &ta2);
+                const CUtensorMap* tb = pair == 0 ? &tb0 : (pair == 1 ? &tb1 : &tb2);
+                if (it == 0) { tma_prefetch_desc(ta); tma_prefetch_desc(tb); }
+                for (int kb = kb_begin; kb < kb_end; ++kb, ++it) {
+                    const int s = it % kStages;
+                    ok = mbar_wait(bar_empty(s), (uint32_t)(((it / kStages) & 1) ^ 1), wc, 0xd0);
+                    if (!ok) break;
+                    mbar_arrive_expect_tx(bar_full(s), 2u * kTileBytes);
+                    const int k0 = kb * kBK;
+                    if (kAMn) {
+                        tma_load_4d(a_smem(s), ta, bar_full(s), m0, k0, 0, 0);
+                        tma_load_4d(a_smem(s) + kTileBytes / 2, ta, bar_full(s), m0 + 64, k0, 0, 0);
+                    } else {
+                        tma_load_4d(a_smem(s), ta, bar_full(s), k0, m0, 0, 0);
+                    }
+                    if (kBMn) {
+                        tma_load_4d(b_smem(s), tb, bar_full(s), n0, k0, 0, 0);
+                        tma_load_4d(b_smem(s) + kTileBytes / 2, tb, bar_full(s), n0 + 64, k0, 0, 0);
+                    } else {
+                        tma_load_4d(b_smem(s), tb, bar_full(s), k0, n0, 0, 0);
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc_bf16(kBM, kBN, kAMn ? 1 : 0, kBMn ? 1 : 0);
+            // K-major tile: 128 rows of 128 bytes, 8-row groups 1024 bytes apart, 32 bytes per K step.
+            // MN-major tile: two blocks of 64 columns, 8192 bytes apart, each 64 K rows of 128 bytes;
+            // a K step of 16 rows advances 2048 bytes.
+            const uint64_t a_desc0 = kAMn ? make_smem_desc_sw128(a_smem(0), kTileBytes / 2, 1024)
+                                          : make_smem_desc_sw128(a_smem(0), 16, 1024);
+            const uint64_t b_desc0 = kBMn ? make_smem_desc_sw128(b_smem(0), kTileBytes / 2, 1024)
+                                          : make_smem_desc_sw128(b_smem(0), 16, 1024);
+            constexpr uint64_t a_step = kAMn ? 128 : 2, b_step = kBMn ? 128 : 2;
+            bool ok = true;
+            for (int it = 0; it < n_iters && ok; ++it) {
+                const int s = it % kStages;
+                ok = mbar_wait(bar_full(s), (uint32_t)((it / kStages) & 1), wc, 0xd1);
+                if (!ok) break;
+                tc_fence_after_sync();
+                const uint64_t ad = a_desc0 + (uint64_t)((s * 2 * kTileBytes) >> 4);
+                const uint64_t bd = b_desc0 + (uint64_t)((s * 2 * kTileBytes) >> 4);
+#pragma unroll
+                for (int k = 0; k < kBK / 16; ++k)
+                    mma_ss(tmem_base, ad + a_step * k, bd + b_step * k, idesc, (it > 0 || k > 0) ? 1u : 0u);
+                mma_commit(bar_empty(s));
+            }
+            if (ok && n_iters > 0) mma_commit(bar_acc);
+        }
+    } else {
+        // epilogue: warp w reads the 32 accumulator rows of its lane quarter (w % 4)
+        const int qd = warp & 3;
+        const int row = qd * 32 + lane;
+        const int gm = m0 + row;
+        bool ok = true;
+        if (n_iters > 0) {
+            ok = mbar_wait_warp(bar_acc, 0u, wc, 0xd2);
+            tc_fence_after_sync();
+        }
+        const uint32_t tacc = tmem_base + ((uint32_t)(qd * 32) << 16);
+        const float* bias = (g.ksplit == 1) ? g.bias[problem] : nullptr;
+#pragma unroll 1
+        for (int c0 = 0; c0 < kBN && ok; c0 += 32) {
+            uint32_t v[32];
+            __syncwarp();
+            if (n_iters > 0) {
+                tmem_ld32(tacc + c0, v);
+                tmem_wait_ld();
+            } else {
+#pragma unroll
+                for (int c = 0; c < 32; ++c) v[c] = 0u;
+            }
+            const int gn0 = n0 + c0;
+            if (gm >= g.M || gn0 >= g.N) continue;
+            if (bias) {
+#pragma unroll
+                for (int c = 0; c < 32; ++c)
+                    if (gn0 + c < g.N) v[c] = __float_as_uint(__uint_as_float(v[c]) + __ldg(bias + gn0 + c));
+            }
+            const bool full = gn0 + 32 <= g.N;
+            if (g.ksplit > 1) {
+                float* dst = g.partial + (((int64_t)problem * g.ksplit + slice) * g.M + gm) * g.N + gn0;
+                if (full && (g.N & 3) == 0) {
+#pragma unroll
+                    for (int c = 0; c < 32; c += 4)
+                        *reinterpret_cast<uint4*>(dst + c) = make_uint4(v[c], v[c + 1], v[c + 2], v[c + 3]);
+                } else {
+                    {
+#pragma unroll
+                    for (int c = 0; c < 32; ++c)
+                        if (gn0 + c < g.N) dst[c] = __uint_as_float(v[c]);
+                }
+                }
+            } else if (g.out_bf16) {
+                __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(g.C[problem]) + (int64_t)gm * g.ldc + gn0;
+                if (full && (g.ldc & 7) == 0 && (reinterpret_cast<uintptr_t>(g.C[problem]) & 15) == 0) {
+#pragma unroll
+                    for (int c = 0; c < 32; c += 8) {
+                        uint4 w;
+                        w.x = pack_bf16x2(__uint_as_float(v[c]), __uint_as_float(v[c + 1]));
+                        w.y = pack_bf16x2(__uint_as_float(v[c + 2]), __uint_as_float(v[c + 3]));
+                        w.z = pack_bf16x2(__uint_as_float(v[c + 4]), __uint_as_float(v[c + 5]));
+                        w.w = pack_bf16x2(__uint_as_float(v[c + 6]), __uint_as_float(v[c + 7]));
+                        *reinterpret_cast<uint4*>(dst + c) = w;
+                    }
+                } else {
+                    {
+#pragma unroll
+                    for (int c = 0; c < 32; ++c)
+                        if (gn0 + c < g.N) dst[c] = __float2bfloat16_rn(__uint_as_float(v[c]));
+                }
+                }
+            } else {
+                float* dst = reinterpret_cast<float*>(g.C[problem]) + (int64_t)gm * g.ldc + gn0;
+                if (full && (g.ldc & 3) == 0 && (reinterpret_cast<uintptr_t>(g.C[problem]) & 15) == 0) {
+#pragma unroll
+                    for (int c = 0; c < 32; c += 4)
+                        *reinterpret_cast<uint4*>(dst + c) = make_uint4(v[c], v[c + 1], v[c + 2], v[c + 3]);
+                } else {
+                    {
+#pragma unroll
+                    for (int c = 0; c < 32; ++c)
+                        if (gn0 + c < g.N) dst[c] = __uint_as_float(v[c]);
+                }
+                }
+            }
+        }
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        if (misc[1]) __nanosleep(200000);    // aborted: give copies and MMAs in flight time to land
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, 128);
+    }
+}
+
+// C[problem][i] = sum over slices of partial[problem][slice][i], in slice order.
+__global__ void gemm_splitk_reduce_kernel(const float* __restrict__ partial, float* c0, float* c1, float* c2,
+                                          int64_t mn, int ksplit) {
+    const int problem = blockIdx.y;
+    float* c = problem == 0 ? c0 : (problem == 1 ? c1 : c2);
+    const float* p = partial + (int64_t)problem * ksplit * mn;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < mn; i += (int64_t)gridDim.x * blockDim.x) {
+        float acc = 0.f;
+        for (int s = 0; s < ksplit; ++s) acc += p[(int64_t)s * mn + i];
+        c[i] = acc;
+    }
+}
+
+__global__ void cvt_rows_bf16_kernel(const float* __restrict__ src, int64_t ld_src, __nv_bfloat16* __restrict__ dst,
+                                     int64_t ld_dst, int64_t rows, int cols) {
+    const int64_t n = rows * cols;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / cols;
+        const int c = (int)(i - r * cols);
+        dst[r * ld_dst + c] = __float2bfloat16_rn(src[r * ld_src + c]);
+    }
+}
+
+__global__ void cvt_rows_bf16_vec_kernel(const float4* __restrict__ src, uint2* __restrict__ dst, int64_t n4) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (int64_t)gridDim.x * blockDim.x) {
+        const float4 v = __ldg(src + i);
+        dst[i] = make_uint2(pack_bf16x2(v.x, v.y), pack_bf16x2(v.z, v.w));
+    }
+}
+
+int make_operand_map(ltca_ctx* ctx, CUtensorMap* map, const GemmOperand& o, int mn_extent, int k_extent) {
+    ltca_strides st;
+    st.batch = 0; st.head = 0; st.seq = o.ld;
+    if (o.mn_major)   // stored [K, MN]: rows are K, 64 x 64 boxes
+        return make_tmap_bhsd(ctx, map, o.ptr, 2, 1, 1, k_extent, mn_extent, st, 64, 64);
+    return make_tmap_bhsd(ctx, map, o.ptr, 2, 1, 1, mn_extent, k_extent, st, 64, 128);
+}
+
+}  // namespace
+
+size_t gemm_sm100_partial_bytes(int M, int N, int n_problems, int ksplit) {
+    if (ksplit <= 1) return 0;
+    return align_up((size_t)n_problems * ksplit * M * N * sizeof(float), 256);
+}
+
+int gemm_sm100_pick_ksplit(int M, int N, int K, int n_problems, int sm_count) {
+    const int tiles = ((M + kBM - 1) / kBM) * ((N + kBN - 1) / kBN) * n_problems;
+    const int nkb = (K + kBK - 1) / kBK;
+    if (sm_count <= 0) sm_count = 148;
+    int ks = 1;
+    // split while the tiles alone leave most SMs idle and every slice keeps at least 8 K blocks
+    while (tiles * ks * 2 <= sm_count && nkb / (ks * 2) >= 8 && ks < 16) ks *= 2;
+    return ks;
+}
+
+int gemm_sm100(ltca_ctx* ctx, const GemmProblem& gp) {
+    if (gp.n_problems < 1 || gp.n_problems > 3 || gp.n_sum < 1 || gp.n_sum > 3 ||
+        (gp.n_sum > 1 && gp.n_problems != 1))
+        return fail(ctx, LTCA_ERR_INVALID, "gemm: between 1 and 3 problems, or one problem of up to 3 summed pairs");
+    if (gp.M < 1 || gp.N < 1 || gp.K < 1) return fail(ctx, LTCA_ERR_INVALID, "gemm: empty problem");
+    const int n_pairs = gp.n_sum > 1 ? gp.n_sum : gp.n_problems;
+    CUtensorMap ta[3], tb[3];
+    int rc;
+    for (int i = 0; i < 3; ++i) {
+        const int j = i < n_pairs ? i : 0;
+        if (gp.a[j].mn_major != gp.a[0].mn_major || gp.b[j].mn_major != gp.b[0].mn_major)
+            return fail(ctx, LTCA_ERR_INVALID, "gemm: all pairs of one launch share the operand forms");
+        if ((rc = make_operand_map(ctx, &ta[i], gp.a[j], gp.M, gp.K))) return rc;
+        if ((rc = make_operand_map(ctx, &tb[i], gp.b[j], gp.N, gp.K))) return rc;
+    }
+    GemmKArgs g;
+    g.M = gp.M; g.N = gp.N; g.K = gp.K;
+    g.n_sum = gp.n_sum;
+    g.ksplit = gp.ksplit > 1 ? gp.ksplit : 1;
+    g.ldc = gp.ldc;
+    g.out_bf16 = gp.out_bf16;
+    for (int i = 0; i < 3; ++i) { g.C[i] = gp.c[i < gp.n_problems ? i : 0]; g.bias[i] = i < gp.n_problems ? gp.bias[i] : nullptr; }
+    g.partial = gp.partial;
+    g.status = ctx->d_status;
+    if (g.ksplit > 1) {
+        if (!gp.partial) return fail(ctx, LTCA_ERR_WORKSPACE, "gemm: split K needs scratch");
+        if (gp.out_bf16) return fail(ctx, LTCA_ERR_INVALID, "gemm: split K writes fp32 results");
+        for (int i = 0; i < gp.n_problems; ++i)
+            if (gp.bias[i]) return fail(ctx, LTCA_ERR_INVALID, "gemm: split K takes no bias");
+    }
+    dim3 grid((gp.N + kBN - 1) / kBN, (gp.M + kBM - 1) / kBM, gp.n_problems * g.ksplit);
+    const bool amn = gp.a[0].mn_major != 0, bmn = gp.b[0].mn_major != 0;
+    auto launch = [&](auto kern) -> int {
+        LTCA_CUDA_OK(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kDynBytes));
+        kern<<<grid, kGemmThreads, kDynBytes, ctx->stream>>>(ta[0], ta[1], ta[2], tb[0], tb[1], tb[2], g);
+        LTCA_LAUNCH_OK(ctx, "gemm_bf16_sm100_kernel");
+        return LTCA_OK;
+    };
+    if (!amn && !bmn) rc = launch(gemm_bf16_sm100_kernel<false, false>);
+    else if (!amn && bmn) rc = launch(gemm_bf16_sm100_kernel<false, true>);
+    else if (amn && bmn) rc = launch(gemm_bf16_sm100_kernel<true, true>);
+    else return fail(ctx, LTCA_ERR_UNSUPPORTED, "gemm: A stored [K, M] with B stored [N, K] is not built");
+    if (rc) return rc;
+    if (g.ksplit > 1) {
+        const int64_t mn = (int64_t)gp.M * gp.N;
+        dim3 rg((unsigned)((mn + 255) / 256 < 1184 ? (mn + 255) / 256 : 1184), gp.n_problems);
+        gemm_splitk_reduce_kernel<<<rg, 256, 0, ctx->stream>>>(
+            gp.partial, reinterpret_cast<float*>(gp.c[0]), reinterpret_cast<float*>(gp.c[gp.n_problems > 1 ? 1 : 0]),
+            reinterpret_cast<float*>(gp.c[gp.n_problems > 2 ? 2 : 0]), mn, g.ksplit);
+        LTCA_LAUNCH_OK(ctx, "gemm_splitk_reduce_kernel");
+    }
+    return LTCA_OK;
+}
+
+int convert_rows_bf16(ltca_ctx* ctx, const float* src, int64_t ld_src, void* dst, int64_t ld_dst, int64_t rows,
+                      int cols) {
+    if (rows < 1 || cols < 1) return LTCA_OK;
+    const int64_t n = rows * cols;
+    if (ld_src == cols && ld_dst == cols && (n & 3) == 0 && (reinterpret_cast<uintptr_t>(src) & 15) == 0 &&
+        (reinterpret_cast<uintptr_t>(dst) & 7) == 0) {
+        const int64_t n4 = n / 4;
+        const unsigned blocks = (unsigned)((n4 + 255) / 256 < 2368 ? (n4 + 255) / 256 : 2368);
+        cvt_rows_bf16_vec_kernel<<<blocks, 256, 0, ctx->stream>>>(reinterpret_cast<const float4*>(src),
+                                                                  reinterpret_cast<uint2*>(dst), n4);
+    } else {
+        const unsigned blocks = (unsigned)((n + 255) / 256 < 2368 ? (n + 255) / 256 : 2368);
+        cvt_rows_bf16_kernel<<<blocks, 256, 0, ctx->stream>>>(src, ld_src, reinterpret_cast<__nv_bfloat16*>(dst),
+                                                              ld_dst, rows, cols);
+    }
+    LTCA_LAUNCH_OK(ctx, "cvt_rows_bf16_kernel");
+    return LTCA_OK;
+}
+
+}  // namespace ltca

@@ -9,9 +9,18 @@
 // row-major projection buffers, so the reference's reshape kernels
 // (src/ml/flash_attention.cu:402-455) have no counterpart here.
 //
-// The projections run on an fp32 FMA GEMM (exact mode).  Backward follows the reference:
+// Two pipelines:
+//   - exact (LTCA_MODE_FP32, or shapes the tensor-pipe attention kernels do not cover): fp32 FMA GEMMs,
+//     fp32 buffers between the kernels;
+//   - tensor pipe (other modes): x, dy and the weights are rounded to bf16 once, every projection is
+//     a tcgen05 GEMM (gemm_sm100.cu), q / k / v / ctx and their gradients stay in bf16 between the
+//     kernels (the attention kernels read them through strides, nothing is packed or permuted), Q, K
+//     and V share one launch, dx is one GEMM over the three (dq, W^T) pairs, the weight gradients
+//     split their long contraction (batch x time) across CTAs and are summed in a fixed order.
+// Backward follows the reference:
 // the incoming gradient passes through LayerNorm and the residual unchanged
 // (src/ml/cudnn_time_self_attention.cu:291-299), dx = dQ Wq^T + dK Wk^T + dV Wv^T.
+#include "gemm_sm100.h"
 #include "host_common.h"
 
 namespace ltca {
@@ -219,6 +228,227 @@ int forward_core(ltca_ctx* ctx, const ltca_tsa_params* t, const Plan& pl, char* 
     return rc;
 }
 
+// ---- tensor-pipe pipeline ---------------------------------------------------------------------
+
+void fill_attn_bf16(const ltca_tsa_params* t, ltca_attn_params* a) {
+    fill_attn(t, a);
+    a->dtype = LTCA_BF16;
+    a->mode = LTCA_MODE_BF16;
+}
+
+// Whether the module runs on the tensor pipe: the caller allows it, the attention kernels cover
+// the head width, and the bf16 rows keep the 16-byte pitch TMA needs.
+bool use_tensor(const ltca_tsa_params* t, bool backward) {
+    if (t->mode == LTCA_MODE_FP32) return false;
+    if ((t->H * t->head_width) % 8) return false;
+    ltca_attn_params a;
+    fill_attn_bf16(t, &a);
+    if (!attn_fwd_sm100_supported(&a)) return false;
+    if (backward && !attn_bwd_sm100_supported(&a)) return false;
+    return true;
+}
+
+struct TPlan {
+    int64_t rows;
+    int HW, Ep;
+    size_t xb, w_in, w_out, act, lse, y;
+    size_t attn_fwd, attn_bwd, partial;
+    int ks_in, ks_out;
+};
+
+int make_tplan(const ltca_tsa_params* t, TPlan* pl) {
+    pl->rows = (int64_t)t->B * t->S;
+    pl->HW = t->H * t->head_width;
+    pl->Ep = (t->E + 7) / 8 * 8;
+    pl->xb = align_up((size_t)pl->rows * pl->Ep * 2, 256);
+    pl->w_in = align_up((size_t)t->E * pl->HW * 2, 256);
+    pl->w_out = align_up((size_t)pl->HW * pl->Ep * 2, 256);
+    pl->act = align_up((size_t)pl->rows * pl->HW * 2, 256);
+    pl->lse = align_up((size_t)t->B * t->H * t->S * sizeof(float), 256);
+    pl->y = align_up((size_t)pl->rows * t->E * sizeof(float), 256);
+    ltca_attn_params a;
+    fill_attn_bf16(t, &a);
+    int rc = ltca_attn_workspace_bytes(&a, 0, &pl->attn_fwd);
+    if (rc) return rc;
+    if ((rc = ltca_attn_workspace_bytes(&a, 1, &pl->attn_bwd))) return rc;
+    const int rows = (int)pl->rows;
+    pl->ks_in = gemm_sm100_pick_ksplit(t->E, pl->HW, rows, 3, 148);
+    pl->ks_out = gemm_sm100_pick_ksplit(pl->HW, t->E, rows, 1, 148);
+    const size_t p_in = gemm_sm100_partial_bytes(t->E, pl->HW, 3, pl->ks_in);
+    const size_t p_out = gemm_sm100_partial_bytes(pl->HW, t->E, 1, pl->ks_out);
+    pl->partial = p_in > p_out ? p_in : p_out;
+    return LTCA_OK;
+}
+
+size_t tensor_workspace(const TPlan& pl, int which) {
+    // x, the four weight matrices, q, k, v, ctx, lse
+    size_t n = pl.xb + 3 * pl.w_in + pl.w_out + 4 * pl.act + pl.lse;
+    if (which == 0) return n + pl.y + pl.attn_fwd;
+    n += pl.xb + 4 * pl.act;                       // dy, dctx, dq, dk, dv
+    n += pl.attn_fwd > pl.attn_bwd ? pl.attn_fwd : pl.attn_bwd;
+    return n + pl.partial;
+}
+
+struct TBufs {
+    void *xb, *wq, *wk, *wv, *wo, *q, *k, *v, *ctx;
+    float* lse;
+    char* rest;
+};
+
+// bf16 copies, fused Q/K/V projection, attention forward.
+int tensor_forward_core(ltca_ctx* ctx, const ltca_tsa_params* t, const TPlan& pl, char* w, TBufs* tb) {
+    tb->xb = w;  w += pl.xb;
+    tb->wq = w;  w += pl.w_in;
+    tb->wk = w;  w += pl.w_in;
+    tb->wv = w;  w += pl.w_in;
+    tb->wo = w;  w += pl.w_out;
+    tb->q = w;   w += pl.act;
+    tb->k = w;   w += pl.act;
+    tb->v = w;   w += pl.act;
+    tb->ctx = w; w += pl.act;
+    tb->lse = reinterpret_cast<float*>(w); w += pl.lse;
+    tb->rest = w;
+    const int E = t->E, HW = pl.HW, Ep = pl.Ep;
+    int rc;
+    if ((rc = convert_rows_bf16(ctx, t->x, E, tb->xb, Ep, pl.rows, E))) return rc;
+    if ((rc = convert_rows_bf16(ctx, t->wq, HW, tb->wq, HW, E, HW))) return rc;
+    if ((rc = convert_rows_bf16(ctx, t->wk, HW, tb->wk, HW, E, HW))) return rc;
+    if ((rc = convert_rows_bf16(ctx, t->wv, HW, tb->wv, HW, E, HW))) return rc;
+    if ((rc = convert_rows_bf16(ctx, t->wo, E, tb->wo, Ep, HW, E))) return rc;
+    GemmProblem gp;
+    gp.M = (int)pl.rows; gp.N = HW; gp.K = E;
+    gp.n_problems = 3;
+    const void* wsrc[3] = {tb->wq, tb->wk, tb->wv};
+    void* dst[3] = {tb->q, tb->k, tb->v};
+    const float* bias[3] = {t->bq, t->bk, t->bv};
+    for (int i = 0; i < 3; ++i) {
+        gp.a[i] = GemmOperand{tb->xb, Ep, 0};
+        gp.b[i] = GemmOperand{wsrc[i], HW, 1};           // stored [E, HW] = [K, N]
+        gp.c[i] = dst[i];
+        gp.bias[i] = bias[i];
+    }
+    gp.ldc = HW;
+    gp.out_bf16 = 1;
+    if ((rc = gemm_sm100(ctx, gp))) return rc;
+    ltca_attn_params a;
+    fill_attn_bf16(t, &a);
+    a.q = tb->q; a.k = tb->k; a.v = tb->v; a.o = tb->ctx; a.lse = tb->lse;
+    a.workspace = pl.attn_fwd ? tb->rest : nullptr;
+    a.workspace_bytes = pl.attn_fwd;
+    return ltca_attn_fwd(ctx, &a);
+}
+
+int tensor_forward(ltca_ctx* ctx, const ltca_tsa_params* t) {
+    TPlan pl;
+    int rc;
+    if ((rc = make_tplan(t, &pl))) return rc;
+    const size_t need = tensor_workspace(pl, 0);
+    if (!t->workspace || t->workspace_bytes < need)
+        return fail(ctx, LTCA_ERR_WORKSPACE, "forward needs %zu bytes of workspace", need);
+    char* w = reinterpret_cast<char*>(t->workspace);
+    float* y = reinterpret_cast<float*>(w);
+    w += pl.y;
+    TBufs tb;
+    if ((rc = tensor_forward_core(ctx, t, pl, w, &tb))) return rc;
+    GemmProblem gp;
+    gp.M = (int)pl.rows; gp.N = t->E; gp.K = pl.HW;
+    gp.a[0] = GemmOperand{tb.ctx, pl.HW, 0};
+    gp.b[0] = GemmOperand{tb.wo, pl.Ep, 1};              // stored [HW, E] = [K, N]
+    gp.c[0] = y;
+    gp.bias[0] = t->bo;
+    gp.ldc = t->E;
+    if ((rc = gemm_sm100(ctx, gp))) return rc;
+    const int wpb = 8;
+    residual_layer_norm_kernel<<<(unsigned)((pl.rows + wpb - 1) / wpb), wpb * 32, 0, ctx->stream>>>(
+        y, t->x, t->ln_gamma, t->ln_beta, t->out, pl.rows, t->E, t->use_residual, t->use_layer_norm,
+        1e-5f);
+    LTCA_LAUNCH_OK(ctx, "residual_layer_norm_kernel");
+    return LTCA_OK;
+}
+
+int tensor_backward(ltca_ctx* ctx, const ltca_tsa_params* t, bool want_dx, bool want_dw) {
+    TPlan pl;
+    int rc;
+    if ((rc = make_tplan(t, &pl))) return rc;
+    const size_t need = tensor_workspace(pl, 1);
+    if (!t->workspace || t->workspace_bytes < need)
+        return fail(ctx, LTCA_ERR_WORKSPACE, "backward needs %zu bytes of workspace", need);
+    char* w = reinterpret_cast<char*>(t->workspace);
+    void* dyb = w;   w += pl.xb;
+    void* dctx = w;  w += pl.act;
+    void* dq = w;    w += pl.act;
+    void* dk = w;    w += pl.act;
+    void* dv = w;    w += pl.act;
+    float* partial = reinterpret_cast<float*>(w); w += pl.partial;
+    TBufs tb;
+    // the forward is recomputed, as the reference's caller does before each backward
+    // (src/ml/ml_liquid_net.cu:715-721)
+    if ((rc = tensor_forward_core(ctx, t, pl, w, &tb))) return rc;
+    const int rows = (int)pl.rows, E = t->E, HW = pl.HW, Ep = pl.Ep;
+    if ((rc = convert_rows_bf16(ctx, t->dy, E, dyb, Ep, pl.rows, E))) return rc;
+    {   // dctx = dy Wo^T : Wo is stored [HW, E] = [N, K]
+        GemmProblem gp;
+        gp.M = rows; gp.N = HW; gp.K = E;
+        gp.a[0] = GemmOperand{dyb, Ep, 0};
+        gp.b[0] = GemmOperand{tb.wo, Ep, 0};
+        gp.c[0] = dctx;
+        gp.ldc = HW;
+        gp.out_bf16 = 1;
+        if ((rc = gemm_sm100(ctx, gp))) return rc;
+    }
+    ltca_attn_params a;
+    fill_attn_bf16(t, &a);
+    a.q = tb.q; a.k = tb.k; a.v = tb.v; a.o = tb.ctx; a.lse = tb.lse;
+    a.dout = dctx; a.dq = dq; a.dk = dk; a.dv = dv;
+    a.workspace = pl.attn_bwd ? tb.rest : nullptr;
+    a.workspace_bytes = pl.attn_bwd;
+    if ((rc = ltca_attn_bwd(ctx, &a))) return rc;
+    const void* grads[3] = {dq, dk, dv};
+    if (want_dx) {
+        // dx = dq Wq^T + dk Wk^T + dv Wv^T : each W is stored [E, HW] = [N, K]; one accumulator tile
+        GemmProblem gp;
+        gp.M = rows; gp.N = E; gp.K = HW;
+        gp.n_sum = 3;
+        const void* wsrc[3] = {tb.wq, tb.wk, tb.wv};
+        for (int i = 0; i < 3; ++i) {
+            gp.a[i] = GemmOperand{grads[i], HW, 0};
+            gp.b[i] = GemmOperand{wsrc[i], HW, 0};
+        }
+        gp.c[0] = t->dx;
+        gp.ldc = E;
+        if ((rc = gemm_sm100(ctx, gp))) return rc;
+    }
+    if (want_dw) {
+        {   // dW = x^T dq : x is stored [rows, E] = [K, M], dq [rows, HW] = [K, N]
+            GemmProblem gp;
+            gp.M = E; gp.N = HW; gp.K = rows;
+            gp.n_problems = 3;
+            gp.ksplit = pl.ks_in;
+            void* dst[3] = {t->dwq, t->dwk, t->dwv};
+            for (int i = 0; i < 3; ++i) {
+                gp.a[i] = GemmOperand{tb.xb, Ep, 1};
+                gp.b[i] = GemmOperand{grads[i], HW, 1};
+                gp.c[i] = dst[i];
+            }
+            gp.ldc = HW;
+            gp.partial = partial;
+            if ((rc = gemm_sm100(ctx, gp))) return rc;
+        }
+        {   // dWo = ctx^T dy
+            GemmProblem gp;
+            gp.M = HW; gp.N = E; gp.K = rows;
+            gp.ksplit = pl.ks_out;
+            gp.a[0] = GemmOperand{tb.ctx, HW, 1};
+            gp.b[0] = GemmOperand{dyb, Ep, 1};
+            gp.c[0] = t->dwo;
+            gp.ldc = E;
+            gp.partial = partial;
+            if ((rc = gemm_sm100(ctx, gp))) return rc;
+        }
+    }
+    return LTCA_OK;
+}
+
 }  // namespace
 }  // namespace ltca
 
@@ -228,6 +458,13 @@ extern "C" {
 
 int ltca_tsa_workspace_bytes(const ltca_tsa_params* t, int which, size_t* bytes_out) {
     if (!t || !bytes_out || which < 0 || which > 3) return LTCA_ERR_INVALID;
+    if (use_tensor(t, which != 0)) {
+        TPlan tp;
+        int trc = make_tplan(t, &tp);
+        if (trc) return trc;
+        *bytes_out = tensor_workspace(tp, which);
+        return LTCA_OK;
+    }
     Plan pl;
     int rc = make_plan(t, &pl);
     if (rc) return rc;
@@ -249,6 +486,7 @@ int ltca_tsa_fwd(ltca_ctx* ctx, const ltca_tsa_params* t) {
     if (!t->out) return fail(ctx, LTCA_ERR_INVALID, "out must be non-null");
     if (t->use_layer_norm && (!t->ln_gamma || !t->ln_beta))
         return fail(ctx, LTCA_ERR_INVALID, "LayerNorm needs gamma and beta");
+    if (use_tensor(t, false)) return tensor_forward(ctx, t);
     Plan pl;
     if ((rc = make_plan(t, &pl))) return rc;
     size_t need = 0;
@@ -278,6 +516,7 @@ static int tsa_backward(ltca_ctx* ctx, const ltca_tsa_params* t, bool want_dx, b
     if (want_dx && !t->dx) return fail(ctx, LTCA_ERR_INVALID, "dx must be non-null");
     if (want_dw && (!t->dwq || !t->dwk || !t->dwv || !t->dwo))
         return fail(ctx, LTCA_ERR_INVALID, "dwq, dwk, dwv, dwo must be non-null");
+    if (use_tensor(t, true)) return tensor_backward(ctx, t, want_dx, want_dw);
     Plan pl;
     if ((rc = make_plan(t, &pl))) return rc;
     size_t need = 0;

@@ -89,3 +89,55 @@ def test_cuda_module_compact_heads_causal(ctx):
     out = ctx.tsa_fwd(dev(x), dev(wq), dev(wk), dev(wv), dev(wo), B, S, H, W, scale=1 / math.sqrt(W),
                       causal=True, time_major=False, gamma=dev(gamma), beta=dev(beta), mode=_lib.MODE_BF16)
     assert np.abs(out.cpu().numpy() - ref).max() < 2e-2        # bf16 operands in the core, then LayerNorm
+
+
+TENSOR_MODULE_CASES = [
+    # B, S, E, H, causal, time_major, biases
+    (2, 128, 256, 4, True, False, False),
+    (3, 100, 100, 2, False, True, True),      # E not a multiple of 8: padded bf16 rows; ragged tiles
+    (8, 128, 256, 4, True, False, False),     # 1024 rows: the weight gradients split their contraction
+]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("case", TENSOR_MODULE_CASES)
+def test_cuda_module_tensor_pipe_forward_backward(ctx, case):
+    """Every projection of the module on the tcgen05 GEMM (bf16 operands, fp32 accumulation), head
+    width 64: forward output, input gradient and the four weight gradients against the oracle."""
+    import math
+    import torch
+    from cuda_ltc_b200 import _lib
+    B, S, E, H, causal, time_major, biases = case
+    W = 64
+    HW = H * W
+    rng = np.random.default_rng(17)
+    x = rng.standard_normal((B * S, E)).astype(np.float32)
+    dy = rng.standard_normal((B * S, E)).astype(np.float32)
+    lim = math.sqrt(6.0 / (E + HW))
+    wq, wk, wv = (rng.uniform(-lim, lim, (E, HW)).astype(np.float32) for _ in range(3))
+    wo = rng.uniform(-lim, lim, (HW, E)).astype(np.float32)
+    bq, bk, bv = ((0.1 * rng.standard_normal(HW)).astype(np.float32) if biases else None for _ in range(3))
+    bo = (0.1 * rng.standard_normal(E)).astype(np.float32) if biases else None
+    gamma = (1.0 + 0.1 * rng.standard_normal(E)).astype(np.float32)
+    beta = (0.1 * rng.standard_normal(E)).astype(np.float32)
+    sc = 1 / math.sqrt(W)
+    ref, _ = oracle.tsa_fwd(x, wq, wk, wv, wo, B, S, H, W, sc, causal, time_major, True, True, gamma, beta,
+                            bq, bk, bv, bo)
+    gref = oracle.tsa_bwd(x, wq, wk, wv, wo, dy, B, S, H, W, sc, causal, time_major, bq, bk, bv)
+    dev = lambda a: None if a is None else torch.from_numpy(a).cuda()
+    kw = dict(scale=sc, causal=causal, time_major=time_major, mode=_lib.MODE_BF16)
+    out = ctx.tsa_fwd(dev(x), dev(wq), dev(wk), dev(wv), dev(wo), B, S, H, W, gamma=dev(gamma), beta=dev(beta),
+                      bq=dev(bq), bk=dev(bk), bv=dev(bv), bo=dev(bo), **kw)
+    got = ctx.tsa_bwd(dev(x), dev(wq), dev(wk), dev(wv), dev(wo), dev(dy), B, S, H, W,
+                      bq=dev(bq), bk=dev(bk), bv=dev(bv), **kw)
+    again = ctx.tsa_bwd(dev(x), dev(wq), dev(wk), dev(wv), dev(wo), dev(dy), B, S, H, W,
+                        bq=dev(bq), bk=dev(bk), bv=dev(bv), **kw)
+    torch.cuda.synchronize()
+    assert ctx.device_status() == 0
+    assert np.abs(out.cpu().numpy() - ref).max() < 2e-2
+    for name, g, g2, r in zip(("dx", "dwq", "dwk", "dwv", "dwo"), got, again, gref):
+        assert torch.equal(g, g2), f"{name}: two runs differ"
+        gh = g.cpu().numpy().astype(np.float64)
+        scale = max(1.0, float(np.abs(r).max()))
+        assert np.abs(gh - r).max() < 2e-2 * scale, f"{name}: {np.abs(gh - r).max()} vs magnitude {scale}"
+        assert np.linalg.norm(gh - r) < 1e-2 * np.linalg.norm(r), name
