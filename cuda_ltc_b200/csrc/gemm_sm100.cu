@@ -15,7 +15,7 @@
 // form and the shared-memory descriptors follow the layout the TMA boxes produce.
 //
 // One CTA computes one 128 x 128 tile of C: warp 0 is the TMA producer (ring of kStages
-// (A, B) stage pairs, 32 KB each), warp 1 issues the MMAs and owns the 128 tensor-memory columns,
+// (A, B) stage pairs, 32 KB each; two CTAs per SM), warp 1 issues the MMAs and owns the 128 tensor-memory columns,
 // warps 2-5 are the epilogue (one accumulator row per thread: tcgen05.ld, bias, convert, store).
 // grid.z runs independent problems (Q, K and V projections share one launch) and/or splits K
 // (weight gradients: K = batch x time is long and M x N is small, so the K range is cut into
@@ -30,7 +30,8 @@ namespace ltca {
 namespace {
 
 constexpr int kBM = 128, kBN = 128, kBK = 64;
-constexpr int kStages = 6;
+constexpr int kStages = 3;                         // 96 KB of operand ring: two CTAs share an SM, so one
+                                                   // CTA's prologue and epilogue overlap the other's MMAs
 constexpr int kTileBytes = 128 * kBK * 2;          // 16 KB per operand per stage
 constexpr int kGemmThreads = 192;
 constexpr int kBarOff = kStages * 2 * kTileBytes;
@@ -50,7 +51,7 @@ struct GemmKArgs {
 };
 
 template <bool kAMn, bool kBMn>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __launch_bounds__(kGemmThreads, 2)
 gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap ta0, const __grid_constant__ CUtensorMap ta1,
                        const __grid_constant__ CUtensorMap ta2, const __grid_constant__ CUtensorMap tb0,
                        const __grid_constant__ CUtensorMap tb1, const __grid_constant__ CUtensorMap tb2,
@@ -266,6 +267,24 @@ __global__ void cvt_rows_bf16_vec_kernel(const float4* __restrict__ src, uint2* 
     }
 }
 
+struct CvtBatch {
+    const float* src[4];
+    __nv_bfloat16* dst[4];
+    int64_t ld_src[4], ld_dst[4], rows[4];
+    int cols[4];
+};
+// Up to four small matrices (the module's weights) in one launch: blockIdx.y selects the matrix.
+__global__ void cvt_batch_bf16_kernel(const CvtBatch b) {
+    const int m = blockIdx.y;
+    const int64_t n = b.rows[m] * b.cols[m];
+    const int cols = b.cols[m];
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / cols;
+        const int c = (int)(i - r * cols);
+        b.dst[m][r * b.ld_dst[m] + c] = __float2bfloat16_rn(__ldg(b.src[m] + r * b.ld_src[m] + c));
+    }
+}
+
 int make_operand_map(ltca_ctx* ctx, CUtensorMap* map, const GemmOperand& o, int mn_extent, int k_extent) {
     ltca_strides st;
     st.batch = 0; st.head = 0; st.seq = o.ld;
@@ -361,6 +380,25 @@ int convert_rows_bf16(ltca_ctx* ctx, const float* src, int64_t ld_src, void* dst
                                                               ld_dst, rows, cols);
     }
     LTCA_LAUNCH_OK(ctx, "cvt_rows_bf16_kernel");
+    return LTCA_OK;
+}
+
+
+int convert_batch_bf16(ltca_ctx* ctx, int n, const float* const* src, const int64_t* ld_src, void* const* dst,
+                       const int64_t* ld_dst, const int64_t* rows, const int* cols) {
+    if (n < 1 || n > 4) return fail(ctx, LTCA_ERR_INVALID, "convert_batch_bf16 takes 1 to 4 matrices");
+    CvtBatch b;
+    int64_t most = 0;
+    for (int i = 0; i < 4; ++i) {
+        const int j = i < n ? i : 0;
+        b.src[i] = src[j]; b.dst[i] = reinterpret_cast<__nv_bfloat16*>(dst[j]);
+        b.ld_src[i] = ld_src[j]; b.ld_dst[i] = ld_dst[j]; b.rows[i] = rows[j]; b.cols[i] = cols[j];
+        if (rows[j] * cols[j] > most) most = rows[j] * cols[j];
+    }
+    if (most < 1) return LTCA_OK;
+    dim3 grid((unsigned)((most + 1023) / 1024 < 592 ? (most + 1023) / 1024 : 592), n);
+    cvt_batch_bf16_kernel<<<grid, 256, 0, ctx->stream>>>(b);
+    LTCA_LAUNCH_OK(ctx, "cvt_batch_bf16_kernel");
     return LTCA_OK;
 }
 

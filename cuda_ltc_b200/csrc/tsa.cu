@@ -122,6 +122,55 @@ __global__ void residual_layer_norm_kernel(const float* __restrict__ y, const fl
     const float* yr = y + row * E;
     const float* xr = x + row * E;
     float* outr = out + row * E;
+    const uintptr_t align_bits = reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(x) |
+                                 reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(gamma) |
+                                 reinterpret_cast<uintptr_t>(beta);
+    if (use_ln && (E & 127) == 0 && E <= 1024 && (align_bits & 15) == 0) {
+        // the row stays in registers: one read of y and x, one write of the result
+        float4 v[8];
+        const int n4 = E >> 7;                        // float4 per lane
+        float sum4 = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            if (i < n4) {
+                v[i] = __ldg(reinterpret_cast<const float4*>(yr) + lane + 32 * i);
+                if (use_res) {
+                    const float4 r = __ldg(reinterpret_cast<const float4*>(xr) + lane + 32 * i);
+                    v[i].x += r.x; v[i].y += r.y; v[i].z += r.z; v[i].w += r.w;
+                }
+                sum4 += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sum4 += __shfl_xor_sync(0xffffffffu, sum4, o);
+        const float mean4 = sum4 / E;
+        float var4 = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            if (i < n4) {
+                const float a = v[i].x - mean4, b = v[i].y - mean4, c = v[i].z - mean4, d = v[i].w - mean4;
+                var4 = fmaf(a, a, var4); var4 = fmaf(b, b, var4); var4 = fmaf(c, c, var4); var4 = fmaf(d, d, var4);
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) var4 += __shfl_xor_sync(0xffffffffu, var4, o);
+        const float inv4 = rsqrtf(var4 / E + eps);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            if (i < n4) {
+                float4 gm = make_float4(1.f, 1.f, 1.f, 1.f), bt = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (gamma) gm = __ldg(reinterpret_cast<const float4*>(gamma) + lane + 32 * i);
+                if (beta) bt = __ldg(reinterpret_cast<const float4*>(beta) + lane + 32 * i);
+                float4 o4;
+                o4.x = (v[i].x - mean4) * inv4 * gm.x + bt.x;
+                o4.y = (v[i].y - mean4) * inv4 * gm.y + bt.y;
+                o4.z = (v[i].z - mean4) * inv4 * gm.z + bt.z;
+                o4.w = (v[i].w - mean4) * inv4 * gm.w + bt.w;
+                reinterpret_cast<float4*>(outr)[lane + 32 * i] = o4;
+            }
+        }
+        return;
+    }
     float sum = 0.f;
     for (int i = lane; i < E; i += 32) {
         const float v = yr[i] + (use_res ? xr[i] : 0.f);
@@ -311,10 +360,13 @@ int tensor_forward_core(ltca_ctx* ctx, const ltca_tsa_params* t, const TPlan& pl
     const int E = t->E, HW = pl.HW, Ep = pl.Ep;
     int rc;
     if ((rc = convert_rows_bf16(ctx, t->x, E, tb->xb, Ep, pl.rows, E))) return rc;
-    if ((rc = convert_rows_bf16(ctx, t->wq, HW, tb->wq, HW, E, HW))) return rc;
-    if ((rc = convert_rows_bf16(ctx, t->wk, HW, tb->wk, HW, E, HW))) return rc;
-    if ((rc = convert_rows_bf16(ctx, t->wv, HW, tb->wv, HW, E, HW))) return rc;
-    if ((rc = convert_rows_bf16(ctx, t->wo, E, tb->wo, Ep, HW, E))) return rc;
+    {
+        const float* src[4] = {t->wq, t->wk, t->wv, t->wo};
+        void* dst[4] = {tb->wq, tb->wk, tb->wv, tb->wo};
+        const int64_t ld_src[4] = {HW, HW, HW, E}, ld_dst[4] = {HW, HW, HW, Ep}, nrows[4] = {E, E, E, HW};
+        const int ncols[4] = {HW, HW, HW, E};
+        if ((rc = convert_batch_bf16(ctx, 4, src, ld_src, dst, ld_dst, nrows, ncols))) return rc;
+    }
     GemmProblem gp;
     gp.M = (int)pl.rows; gp.N = HW; gp.K = E;
     gp.n_problems = 3;
