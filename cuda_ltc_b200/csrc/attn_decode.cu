@@ -8,9 +8,15 @@
 //     per CTA through shared memory;
 //   - when batch x heads cannot fill the GPU the key range is split across CTAs, partial
 //     (max, sum, output) triples go to a caller-provided scratch buffer and a second small
-//     kernel merges them.
+//     kernel merges them;
+//   - when batch x heads does fill the GPU but the sequences have different lengths, each
+//     (batch, head) pair is a thread-block cluster of two or four CTAs that take alternate
+//     32-key blocks of ITS keys and merge through distributed shared memory (no scratch, no
+//     second kernel): the work per CTA is less uneven, which shortens the tail in which only
+//     the CTAs of the longest sequences are still streaming.
 // The reference has no counterpart: its cuDNN call always passes currIdx = -1
 // (reference src/ml/cuDNN_ops.cu:206).
+#include <cooperative_groups.h>
 #include <math.h>
 
 #include "host_common.h"
@@ -33,7 +39,7 @@ struct DecodeArgs {
     const float* keep_mask;     // [B, 1, Sk]
     const int32_t* kv_len;
     int nsplit;
-    float* partial;             // [B*H][nsplit][D + 2]
+    float* partial;             // [B*H][nsplit][D + 2]; null when the splits are one cluster
 };
 
 __device__ __forceinline__ float4 ld4(const float* p) { return __ldg(reinterpret_cast<const float4*>(p)); }
@@ -46,13 +52,15 @@ __device__ __forceinline__ float4 ld4(const __nv_bfloat16* p) {
 __device__ __forceinline__ void st1(float* p, float v) { *p = v; }
 __device__ __forceinline__ void st1(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
 
-template <typename T, int LPK>
+// kCluster: the nsplit CTAs of one (batch, head) pair form a thread-block cluster (1, nsplit, 1).
+template <typename T, int LPK, bool kCluster>
 __global__ void __launch_bounds__(kDecThreads) attn_decode_kernel(const DecodeArgs a) {
     constexpr int D = 4 * LPK;
     constexpr int G = 32 / LPK;                         // key groups per warp
     constexpr int NG = (kDecThreads / 32) * G;          // key groups per CTA
     __shared__ float sm_o[NG][D];
     __shared__ float sm_m[NG], sm_l[NG];
+    __shared__ float sm_part[D + 2];                    // this CTA's (max, sum, output) for the cluster merge
 
     const int bh = blockIdx.x;
     const int b = bh / a.H, h = bh % a.H;
@@ -63,8 +71,9 @@ __global__ void __launch_bounds__(kDecThreads) attn_decode_kernel(const DecodeAr
 
     int kvlen = a.Sk;
     if (a.kv_len) kvlen = min(max(a.kv_len[b], 0), a.Sk);
-    const int per = (kvlen + a.nsplit - 1) / a.nsplit;
-    const int ks = min(split * per, kvlen), ke = min(ks + per, kvlen);
+    // the CTA's splits interleave at the granularity of one iteration (NG * kUnroll keys), so only
+    // the sequence's last iteration is ragged, whatever the split count
+    const int ks = 0, ke = kvlen;
 
     const T* qp = reinterpret_cast<const T*>(a.q) + b * a.qs.batch + h * a.qs.head + 4 * sub;
     const T* kp = reinterpret_cast<const T*>(a.k) + b * a.ks.batch + h * a.ks.head + 4 * sub;
@@ -76,7 +85,7 @@ __global__ void __launch_bounds__(kDecThreads) attn_decode_kernel(const DecodeAr
     float m = -INFINITY, l = 0.f;
     float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
     const int iters = (ke - ks + NG * kUnroll - 1) / (NG * kUnroll);
-    for (int it = 0; it < iters; ++it) {
+    for (int it = split; it < iters; it += a.nsplit) {
         float4 kk[kUnroll], vv[kUnroll];
         float s[kUnroll];
         bool live[kUnroll];
@@ -133,7 +142,10 @@ __global__ void __launch_bounds__(kDecThreads) attn_decode_kernel(const DecodeAr
             L = fmaf(sm_l[i], w, L);
             acc = fmaf(sm_o[i][d], w, acc);
         }
-        if (a.nsplit == 1) {
+        if (kCluster) {
+            sm_part[2 + d] = acc;
+            if (d == 0) { sm_part[0] = M; sm_part[1] = L; }
+        } else if (a.nsplit == 1) {
             T* op = reinterpret_cast<T*>(a.o) + b * a.os.batch + h * a.os.head;
             st1(op + d, L > 0.f ? acc / L : 0.f);
             if (d == 0 && a.lse) a.lse[bh] = L > 0.f ? M + logf(L) : -INFINITY;
@@ -142,6 +154,29 @@ __global__ void __launch_bounds__(kDecThreads) attn_decode_kernel(const DecodeAr
             part[2 + d] = acc;
             if (d == 0) { part[0] = M; part[1] = L; }
         }
+    }
+    if (kCluster) {
+        namespace cg = cooperative_groups;
+        cg::cluster_group cluster = cg::this_cluster();
+        cluster.sync();                                  // every CTA's partial is in its shared memory
+        if (cluster.block_rank() == 0 && threadIdx.x < D) {
+            const int d = threadIdx.x;
+            const int n = (int)cluster.num_blocks();
+            float M = -INFINITY;
+            for (int r = 0; r < n; ++r) M = fmaxf(M, cluster.map_shared_rank(sm_part, r)[0]);
+            const float Ms = (M == -INFINITY) ? 0.f : M;
+            float L = 0.f, acc = 0.f;
+            for (int r = 0; r < n; ++r) {
+                const float* ps = cluster.map_shared_rank(sm_part, r);
+                const float w = (ps[0] == -INFINITY) ? 0.f : expf(ps[0] - Ms);
+                L = fmaf(ps[1], w, L);
+                acc = fmaf(ps[2 + d], w, acc);
+            }
+            T* op = reinterpret_cast<T*>(a.o) + b * a.os.batch + h * a.os.head;
+            st1(op + d, L > 0.f ? acc / L : 0.f);
+            if (d == 0 && a.lse) a.lse[bh] = L > 0.f ? M + logf(L) : -INFINITY;
+        }
+        cluster.sync();                                  // nobody leaves while its partial may still be read
     }
 }
 
@@ -179,10 +214,38 @@ int pick_splits(const ltca_attn_params* p, int sm_count) {
     return (int)n;
 }
 
+// Splits of one (batch, head) pair that run as one cluster (0: none).  Used when batch x heads
+// already fills the GPU (so the scratch path would not split) but the lengths differ.
+int pick_cluster(const ltca_attn_params* p, int sm_count) {
+#ifdef LTCA_DECODE_NO_CLUSTER
+    return 0;
+#endif
+    if (pick_splits(p, sm_count) != 1) return 0;
+    if (!p->kv_len || p->Sk < 512) return 0;
+    // measured at B=256 H=8 lengths U{1..1024}: 2 CTAs 6112 GB/s, 4: 6011, 8: 4869 (1: 4820)
+    return p->Sk < 2048 ? 2 : 4;
+}
+
 template <typename T, int LPK>
 int run_decode(ltca_ctx* ctx, const DecodeArgs& a) {
     dim3 grid(a.B * a.H, a.nsplit);
-    attn_decode_kernel<T, LPK><<<grid, kDecThreads, 0, ctx->stream>>>(a);
+    if (a.nsplit > 1 && !a.partial) {
+        cudaLaunchConfig_t cfg;
+        memset(&cfg, 0, sizeof(cfg));
+        cfg.gridDim = grid;
+        cfg.blockDim = dim3(kDecThreads);
+        cfg.stream = ctx->stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 1;
+        attr[0].val.clusterDim.y = (unsigned)a.nsplit;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        LTCA_CUDA_OK(ctx, cudaLaunchKernelEx(&cfg, attn_decode_kernel<T, LPK, true>, a));
+        return LTCA_OK;
+    }
+    attn_decode_kernel<T, LPK, false><<<grid, kDecThreads, 0, ctx->stream>>>(a);
     LTCA_LAUNCH_OK(ctx, "attn_decode_kernel");
     if (a.nsplit > 1) {
         attn_decode_merge_kernel<T><<<a.B * a.H, 128, 0, ctx->stream>>>(a);
@@ -235,7 +298,9 @@ int launch_attn_decode(ltca_ctx* ctx, const ltca_attn_params* p) {
     a.keep_mask = p->keep_mask;
     a.kv_len = p->kv_len;
     a.nsplit = pick_splits(p, 148);
-    if (a.nsplit > 1) {
+    if (pick_cluster(p, 148) > 1) {
+        a.nsplit = pick_cluster(p, 148);       // merged inside the cluster: a.partial stays null
+    } else if (a.nsplit > 1) {
         const size_t need = attn_decode_workspace(p);
         if (!p->workspace || p->workspace_bytes < need)
             return fail(ctx, LTCA_ERR_WORKSPACE, "decode needs %zu bytes of workspace", need);
