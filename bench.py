@@ -301,7 +301,7 @@ def main():
         # Algorithmic FLOPs per launch: one contraction over the causal half is f_fwd / 2.  Forward =
         # 2 contractions; the dK/dV kernel is charged S^T, dP^T, dV, dK (4), the dQ kernel only dQ (1; its
         # own S and dP are recomputation): together the 2.5 x forward of the backward pass.
-        kernels = {"attn_fwd4_sm100_kernel": {"ms": fwd_ms, "flops": f_fwd}}
+        kernels = {"attn_fwd4p_sm100_kernel": {"ms": fwd_ms, "flops": f_fwd}}
         if kern_ms:
             kernels["attn_bwd_stats_kernel"] = {"ms": kern_ms[0], "flops": 0.0}
             kernels["attn_bwd_dq4_sm100_kernel"] = {"ms": kern_ms[1], "flops": 0.5 * f_fwd}
@@ -312,7 +312,7 @@ def main():
         achieved = kernels[dom]["flops"] / (kernels[dom]["ms"] * 1e-3) / 1e12
         # DRAM bytes per launch of that kernel: ncu capture at B=2 (profiles/attention_core_b2_s4096_ncu_full.md),
         # which grows in proportion to batch x heads; None for a kernel that was not captured
-        dram_per_bh = {"attn_fwd4_sm100_kernel": 1.628e6, "attn_bwd_dq4_sm100_kernel": 2.294e6,
+        dram_per_bh = {"attn_fwd4p_sm100_kernel": 1.628e6, "attn_bwd_dq4_sm100_kernel": 2.294e6,
                        "attn_bwd_dkv4_sm100_kernel": 2.357e6}
         traffic = dram_per_bh[dom] * B * H if dom in dram_per_bh else None
         line = {

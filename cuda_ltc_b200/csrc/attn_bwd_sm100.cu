@@ -420,7 +420,7 @@ attn_bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
             const int k0 = j * kStep;
             const bool edge = (k0 + kStep > kvlen) || (a.causal && (k0 + kStep - 1 > q0 + a.causal_off));
             // dS = P o (dP - delta), left in dp[]; the masked variant only runs on edge steps
-            if (edge || general) {
+            if (general) {
                 int lim = kvlen;
                 if (a.causal) lim = min(lim, qi + a.causal_off + 1);
                 lim -= k0 + half * 32;
@@ -436,6 +436,16 @@ attn_bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
                     if (mrow && vis) vis = (__ldg(mrow + c) != 0.0f);
                     if (a.use_clamp && sv >= a.clamp_raw) d = 0.f;
                     dp[c] = __float_as_uint(vis ? d : 0.f);
+                }
+            } else if (edge) {
+                // causal diagonal or end of the keys, no dense mask: selects only, no branches
+                int lim = kvlen;
+                if (a.causal) lim = min(lim, qi + a.causal_off + 1);
+                lim -= k0 + half * 32;
+#pragma unroll
+                for (int c = 0; c < 32; ++c) {
+                    const float p = fast_exp2(fmaf(__uint_as_float(s[c]), c2, -lse2));
+                    dp[c] = __float_as_uint((c < lim) ? p * (__uint_as_float(dp[c]) - dlt) : 0.f);
                 }
             } else {
 #pragma unroll
@@ -713,7 +723,7 @@ attn_bwd_dkv_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 const bool edge = !key_live || (k0 + kTile > kvlen) ||
                                   (a.causal && (j * kStep + a.causal_off < k0 + kTile - 1));
                 // P^T into s[], dS^T = P^T o (dP^T - delta) into dp[]
-                if (edge || general) {
+                if (general) {
 #pragma unroll
                     for (int c4 = 0; c4 < 8; ++c4) {
                         const float4 l4 = st4[c4];
@@ -735,6 +745,25 @@ attn_bwd_dkv_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
                             }
                             s[c] = __float_as_uint(vis ? p : 0.f);
                             dp[c] = __float_as_uint(vis ? d : 0.f);
+                        }
+                    }
+                } else if (edge) {
+                    // causal diagonal or end of the keys, no dense mask: selects only, no branches.
+                    // Query column c is visible to this key when c >= cmin.
+                    const int cmin = !key_live ? 0x7fffffff : (a.causal ? kj - a.causal_off - q0 : -0x7fffffff);
+#pragma unroll
+                    for (int c4 = 0; c4 < 8; ++c4) {
+                        const float4 l4 = st4[c4];
+                        const float4 d4 = st4[16 + c4];
+                        const float ls[4] = {l4.x, l4.y, l4.z, l4.w};
+                        const float dl[4] = {d4.x, d4.y, d4.z, d4.w};
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const int c = 4 * c4 + e;
+                            const float p = fast_exp2(fmaf(__uint_as_float(s[c]), c2, -ls[e]));
+                            const bool vis = c >= cmin;
+                            s[c] = __float_as_uint(vis ? p : 0.f);
+                            dp[c] = __float_as_uint(vis ? p * (__uint_as_float(dp[c]) - dl[e]) : 0.f);
                         }
                     }
                 } else {
@@ -819,19 +848,6 @@ attn_bwd_dkv_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
 // of the step.  Two MMA threads share the issue work: warp 16 issues S^T and dV, warp 17 dP^T
 // and dK (each accumulator has one issuing thread, so the summation order is fixed).
 // ---------------------------------------------------------------------------------------------
-struct ItemGrid { int nblk, H, BH, n_items; int* counters; };
-
-// Entry `linear` of the grouped heavy-first order (see sched_block): rank 0 is the heaviest block.
-__device__ __forceinline__ void sched_item(const ItemGrid& g, int linear, int& rank, int& h, int& b) {
-    const int grp = linear / (kSchedGroup * g.nblk);
-    const int n_in = min(kSchedGroup, g.BH - grp * kSchedGroup);
-    const int local = linear - grp * kSchedGroup * g.nblk;
-    rank = local / n_in;
-    const int bh = grp * kSchedGroup + local % n_in;
-    h = bh % g.H;
-    b = bh / g.H;
-}
-
 struct Dkv4Smem {
     static constexpr int kStages = 4;                         // ring of (Q_j, dO_j, lse2_j, delta_j)
     static constexpr int kStageBytes = 2 * kBigTile + 1024;
@@ -1083,7 +1099,7 @@ attn_bwd_dkv4_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 // a query column c is hidden from this key when q0 + c + off < kj
                 const bool edge = !key_live || (k0 + kTile > kvlen) ||
                                   (a.causal && (j * kQStep + a.causal_off < k0 + kTile - 1));
-                if (edge || general) {
+                if (general) {
 #pragma unroll
                     for (int c4 = 0; c4 < 8; ++c4) {
                         const float4 l4 = st4[c4];
@@ -1105,6 +1121,25 @@ attn_bwd_dkv4_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
                             }
                             s[c] = __float_as_uint(vis ? p : 0.f);
                             dp[c] = __float_as_uint(vis ? d : 0.f);
+                        }
+                    }
+                } else if (edge) {
+                    // causal diagonal or end of the keys, no dense mask: selects only, no branches.
+                    // Query column c is visible to this key when c >= cmin.
+                    const int cmin = !key_live ? 0x7fffffff : (a.causal ? kj - a.causal_off - q0 : -0x7fffffff);
+#pragma unroll
+                    for (int c4 = 0; c4 < 8; ++c4) {
+                        const float4 l4 = st4[c4];
+                        const float4 d4 = st4[32 + c4];
+                        const float ls[4] = {l4.x, l4.y, l4.z, l4.w};
+                        const float dl[4] = {d4.x, d4.y, d4.z, d4.w};
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const int c = 4 * c4 + e;
+                            const float p = fast_exp2(fmaf(__uint_as_float(s[c]), c2, -ls[e]));
+                            const bool vis = c >= cmin;
+                            s[c] = __float_as_uint(vis ? p : 0.f);
+                            dp[c] = __float_as_uint(vis ? p * (__uint_as_float(dp[c]) - dl[e]) : 0.f);
                         }
                     }
                 } else {
@@ -1438,7 +1473,7 @@ attn_bwd_dq4_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 const int k0 = it * kKStep;
                 const bool edge = (k0 + kKStep > kvlen) || (a.causal && (k0 + kKStep - 1 > q0 + a.causal_off));
                 // dS = P o (dP - delta), left in dp[]; the masked variant only runs on edge steps
-                if (edge || general) {
+                if (general) {
                     int vis_lim = kvlen;
                     if (a.causal) vis_lim = min(vis_lim, qi + a.causal_off + 1);
                     vis_lim -= k0 + cq * 32;
@@ -1454,6 +1489,16 @@ attn_bwd_dq4_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
                         if (mrow && vis) vis = (__ldg(mrow + c) != 0.0f);
                         if (a.use_clamp && sv >= a.clamp_raw) d = 0.f;
                         dp[c] = __float_as_uint(vis ? d : 0.f);
+                    }
+                } else if (edge) {
+                    // causal diagonal or end of the keys, no dense mask: selects only, no branches
+                    int vis_lim = kvlen;
+                    if (a.causal) vis_lim = min(vis_lim, qi + a.causal_off + 1);
+                    vis_lim -= k0 + cq * 32;
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) {
+                        const float p = fast_exp2(fmaf(__uint_as_float(s[c]), c2, -lse2));
+                        dp[c] = __float_as_uint((c < vis_lim) ? p * (__uint_as_float(dp[c]) - dlt) : 0.f);
                     }
                 } else {
 #if LTCA_EXP_PAIRS

@@ -25,6 +25,12 @@ enum : uint32_t {
 #ifndef LTCA_WAIT_SLEEP_NS
 #define LTCA_WAIT_SLEEP_NS 0
 #endif
+#ifndef LTCA_WAIT_BACKOFF_AFTER
+#define LTCA_WAIT_BACKOFF_AFTER 0
+#endif
+#ifndef LTCA_WAIT_BACKOFF_NS
+#define LTCA_WAIT_BACKOFF_NS 200
+#endif
 static constexpr unsigned long long kWaitLimitNs = 2000000000ull;   // 2 s
 // (No suspend-time hint on mbarrier.try_wait: measured on B200, a hint more than doubles the
 // latency between an arrival and the waiter's wake-up.)
@@ -90,6 +96,11 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const W
     for (uint32_t it = 1;; ++it) {
 #if LTCA_WAIT_SLEEP_NS > 0
         __nanosleep(LTCA_WAIT_SLEEP_NS);      // a polling warp takes issue slots from the working ones
+#endif
+#if LTCA_WAIT_BACKOFF_AFTER > 0
+        // a wait that has already lasted this many polls is not on a per-step critical path (a tile
+        // that is done with its item, a CTA that ran out of items): poll rarely from here on
+        if (it > LTCA_WAIT_BACKOFF_AFTER) __nanosleep(LTCA_WAIT_BACKOFF_NS);
 #endif
         if (mbar_try_wait(bar, parity)) return true;
         if ((it & 0xffu) == 0) {
@@ -372,6 +383,20 @@ __device__ __forceinline__ void item_counters_release(int* counters) {
         counters[1] = 0;
         __threadfence();
     }
+}
+
+// The item list of a persistent kernel: nblk row blocks for each of BH (batch, head) pairs.
+struct ItemGrid { int nblk, H, BH, n_items; int* counters; };
+
+// Entry `linear` of the grouped heavy-first order (see sched_block): rank 0 is the heaviest block.
+__device__ __forceinline__ void sched_item(const ItemGrid& g, int linear, int& rank, int& h, int& b) {
+    const int grp = linear / (kSchedGroup * g.nblk);
+    const int n_in = min(kSchedGroup, g.BH - grp * kSchedGroup);
+    const int local = linear - grp * kSchedGroup * g.nblk;
+    rank = local / n_in;
+    const int bh = grp * kSchedGroup + local % n_in;
+    h = bh % g.H;
+    b = bh / g.H;
 }
 
 // ---- small math helpers -----------------------------------------------------------------------
