@@ -855,8 +855,8 @@ struct Dkv4Smem {
     static constexpr int kRingOff = 4 * kBigTile;
     static constexpr int kBarOff = kRingOff + kStages * kStageBytes;
     // bars: res_full[2], res_empty[2], ring_full[S], ring_empty[S], sdp_full, sdp_free, pds_full, acc_done,
-    // acc_free, item_full[kItemSlots], item_empty[kItemSlots]
-    static constexpr int kNumBars = 4 + 2 * kStages + 5 + 2 * kItemSlots;
+    // acc_free, item_full[kItemSlots], item_empty[kItemSlots], staged[2]
+    static constexpr int kNumBars = 4 + 2 * kStages + 5 + 2 * kItemSlots + 2;
     static constexpr int kMiscOff = kBarOff + kNumBars * 8;   // tmem base, abort flag, item slots
     static constexpr int kDynBytes = kMiscOff + 16 + 4 * kItemSlots + 1024;
 };
@@ -878,7 +878,9 @@ __global__ void __launch_bounds__(kThreads, 1)
 attn_bwd_dkv4_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
                            const __grid_constant__ CUtensorMap tmap_do,
                            const __grid_constant__ CUtensorMap tmap_k,
-                           const __grid_constant__ CUtensorMap tmap_v, const BwdArgs a, const ItemGrid grid) {
+                           const __grid_constant__ CUtensorMap tmap_v,
+                           const __grid_constant__ CUtensorMap tmap_dk,
+                           const __grid_constant__ CUtensorMap tmap_dv, const BwdArgs a, const ItemGrid grid) {
     using L = Dkv4Smem;
     constexpr int kQStep = 128;
     extern __shared__ uint8_t smem_raw[];
@@ -898,19 +900,29 @@ attn_bwd_dkv4_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
     volatile uint32_t* misc = reinterpret_cast<volatile uint32_t*>(smem_gen + L::kMiscOff);
     const ItemQueue iq{bar_sdp_full + 40u, bar_sdp_full + 40u + 8u * kItemSlots,
                        reinterpret_cast<volatile int*>(smem_gen + L::kMiscOff + 16)};
+    // dK and dV of an item staged in the item's own K / V buffer (one barrier per buffer)
+    auto bar_staged = [&](int r) { return bar_sdp_full + 40u + 16u * kItemSlots + 8u * r; };
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n_q = (a.Sq + kQStep - 1) / kQStep;   // query steps in total
+    LTCA_TRACE_DECL(LTCA_TRACE_KERNEL == 4 && blockIdx.x == 5);
+    LTCA_TRACE_EVT(0x01);
 
     if (threadIdx.x == 0) {
-        for (int r = 0; r < 2; ++r) { mbar_init(bar_res_full(r), 1); mbar_init(bar_res_empty(r), 2); }
+        // a K / V buffer is free again when both MMA threads are done with it and the item's dK / dV,
+        // which are staged in it, have been read by their TMA stores
+        for (int r = 0; r < 2; ++r) {
+            mbar_init(bar_res_full(r), 1);
+            mbar_init(bar_res_empty(r), 3);
+            mbar_init(bar_staged(r), 16);
+        }
         for (int s = 0; s < L::kStages; ++s) { mbar_init(bar_ring_full(s), 1); mbar_init(bar_ring_empty(s), 2); }
         mbar_init(bar_sdp_full, 2);                // one commit per MMA thread
         mbar_init(bar_sdp_free, 16);               // one arrival per elementwise warp
         mbar_init(bar_pds_full, 16);
         mbar_init(bar_acc_done, 2);
         mbar_init(bar_acc_free, 16);
-        for (int i = 0; i < kItemSlots; ++i) { mbar_init(iq.full(i), 1); mbar_init(iq.empty(i), 18); }
+        for (int i = 0; i < kItemSlots; ++i) { mbar_init(iq.full(i), 1); mbar_init(iq.empty(i), 19); }
         misc[1] = 0u;
         mbar_fence_init();
     }
@@ -1008,6 +1020,7 @@ attn_bwd_dkv4_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
                     mma_ts(d2, a2 + k * 8, bd + 128 * k, idesc_acc, (p_acc || k > 0) ? 1u : 0u);
                 mma_commit(bar_acc_done);
                 mma_commit(bar_ring_empty(slot_of(p_g)));
+                LTCA_TRACE_EVT(0x22 + (p_g << 8));
                 pending = false;
             };
             int g = 0, na = 0;
@@ -1029,6 +1042,7 @@ attn_bwd_dkv4_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
 #pragma unroll
                     for (int k = 0; k < kD / 16; ++k) mma_ss(d1, a_desc + 2 * k, bd + 2 * k, idesc_s, k > 0);
                     mma_commit(bar_sdp_full);
+                    LTCA_TRACE_EVT(0x20 + (g << 8));
                     if (it == n_it - 1) mma_commit(bar_res_empty(r));   // K (or V) of this item is no longer read
                     if (pending) do_acc();
                     if (!ok) break;
@@ -1039,6 +1053,31 @@ attn_bwd_dkv4_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
             }
             if (ok && pending) do_acc();
             if (ok && g > 0) ok = mbar_wait(bar_acc_done, (uint32_t)((g - 1) & 1), wc, 0xb5);
+        }
+      } else {
+        // warp 19: stores each item's dK and dV tiles (staged by the elementwise warps in the item's
+        // K / V buffer, 128-byte swizzle) with TMA and hands the buffer back to the producer.  Rows
+        // past the end of the keys are clipped by the tensor maps.
+        if (lane == 0) {
+            int na = 0;
+            bool ok = true;
+            for (int nq = 0; ok; ++nq) {
+                const int linear = iq.consume(nq, wc);
+                if (linear < 0) break;
+                int k0, h, b, kvlen, j_begin;
+                const int n_it = item_steps(linear, k0, h, b, kvlen, j_begin);
+                if (n_it == 0) continue;
+                const int r = na & 1;
+                ok = mbar_wait(bar_staged(r), (uint32_t)((na >> 1) & 1), wc, 0xd8);
+                if (ok) {
+                    tma_store_4d(&tmap_dk, res_smem + r * 2 * kBigTile, 0, k0, h, b);
+                    tma_store_4d(&tmap_dv, res_smem + r * 2 * kBigTile + kBigTile, 0, k0, h, b);
+                    tma_store_commit();
+                    tma_store_wait_read<0>();
+                }
+                mbar_arrive(bar_res_empty(r));
+                ++na;
+            }
         }
       }
     } else {
@@ -1055,7 +1094,7 @@ attn_bwd_dkv4_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
         const float c2 = a.scale_log2;
         const bool general = (a.keep_mask != nullptr) || (a.use_clamp != 0);
 
-        int g = 0;
+        int g = 0, na = 0;
         bool ok = true;
         for (int nq = 0; ok; ++nq) {
             const int linear = iq.consume_warp(nq, wc);
@@ -1092,6 +1131,7 @@ attn_bwd_dkv4_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
 
             for (int it = 0; it < n_it && ok; ++it, ++g) {
                 const int j = j_begin + it;
+                LTCA_TRACE_EVT(0x11 + (g << 8));
                 // lse2 and delta of this thread's 32 query columns (every lane reads the same address)
                 const float4* st4 = reinterpret_cast<const float4*>(
                     smem_gen + L::kRingOff + slot_of(g) * L::kStageBytes + 2 * kBigTile) + cq * 8;
@@ -1161,17 +1201,20 @@ attn_bwd_dkv4_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 uint32_t pt[16], dst[16], unused[16];
                 pack32<false>(s, pt, unused);
                 pack32<false>(dp, dst, unused);
+                LTCA_TRACE_EVT(0x12 + (g << 8));
                 if (g > 0) {
                     // the accumulations of the previous step must have read P^T and dS^T
                     ok = mbar_wait_warp(bar_acc_done, (uint32_t)((g - 1) & 1), wc, 0xc1);
                     if (!ok) break;
                 }
+                LTCA_TRACE_EVT(0x15 + (g << 8));
                 tmem_st16(tP, pt);
                 tmem_st16(tDS, dst);
                 tmem_wait_st();
                 tc_fence_before_sync();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar_pds_full);
+                LTCA_TRACE_EVT(0x13 + (g << 8));
                 // (P^T and dS^T are announced before the next S^T / dP^T are awaited: the tensor pipe is
                 // the busier unit in this kernel and must get this step's accumulations as early as possible)
                 if (it + 1 < n_it) {
@@ -1190,6 +1233,7 @@ attn_bwd_dkv4_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
             // item epilogue: dV and scale * dK out of tensor memory, which is then free for the next item
             ok = mbar_wait_warp(bar_acc_done, (uint32_t)((g - 1) & 1), wc, 0xc2);
             if (!ok) break;
+            LTCA_TRACE_EVT(0x18);
             tc_fence_after_sync();
             uint32_t ov[16], ok_[16];
             tmem_ld16(tDV, ov);
@@ -1198,10 +1242,36 @@ attn_bwd_dkv4_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_acc_free);
-            if (kj < a.Sk) {
-                store_row16_bf16(dvrow, ov, 1.0f);
-                store_row16_bf16(dkrow, ok_, a.scale);
+            {
+                // this thread's 16 columns of dK (scaled) and dV, bf16, into the item's K and V buffers in
+                // the layout of a 128-byte-swizzled TMA box; warp 19 stores the two tiles.  (Storing
+                // 16-byte pieces of 128-byte rows straight from registers costs 32 L1 wavefronts per
+                // instruction: measured, one item's 2048 wavefronts held up every shared-memory
+                // operation of the SM for about 5000 cycles.)
+                const int r = na & 1;
+                ++na;
+                uint8_t* st_k = smem_gen + L::kResOff + r * 2 * kBigTile + row * 128;
+                uint8_t* st_v = st_k + kBigTile;
+#pragma unroll
+                for (int v = 0; v < 2; ++v) {
+                    uint4 wk, wv;
+                    wk.x = pack_bf16x2(__uint_as_float(ok_[8 * v + 0]) * a.scale, __uint_as_float(ok_[8 * v + 1]) * a.scale);
+                    wk.y = pack_bf16x2(__uint_as_float(ok_[8 * v + 2]) * a.scale, __uint_as_float(ok_[8 * v + 3]) * a.scale);
+                    wk.z = pack_bf16x2(__uint_as_float(ok_[8 * v + 4]) * a.scale, __uint_as_float(ok_[8 * v + 5]) * a.scale);
+                    wk.w = pack_bf16x2(__uint_as_float(ok_[8 * v + 6]) * a.scale, __uint_as_float(ok_[8 * v + 7]) * a.scale);
+                    wv.x = pack_bf16x2(__uint_as_float(ov[8 * v + 0]), __uint_as_float(ov[8 * v + 1]));
+                    wv.y = pack_bf16x2(__uint_as_float(ov[8 * v + 2]), __uint_as_float(ov[8 * v + 3]));
+                    wv.z = pack_bf16x2(__uint_as_float(ov[8 * v + 4]), __uint_as_float(ov[8 * v + 5]));
+                    wv.w = pack_bf16x2(__uint_as_float(ov[8 * v + 6]), __uint_as_float(ov[8 * v + 7]));
+                    const int pos = ((2 * cq + v) ^ (row & 7)) << 4;
+                    *reinterpret_cast<uint4*>(st_k + pos) = wk;
+                    *reinterpret_cast<uint4*>(st_v + pos) = wv;
+                }
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_staged(r));
             }
+            LTCA_TRACE_EVT(0x19);
         }
     }
 
@@ -1237,8 +1307,8 @@ struct Dq4Smem {
     static constexpr int kRingOff = 4 * kBigTile;
     static constexpr int kBarOff = kRingOff + kStages * kStageBytes;
     // bars: res_full[2], res_empty[2], ring_full[S], ring_empty[S], sdp_full, sdp_free, ds_full[3],
-    // ds_free[3], acc_free, item_full[kItemSlots], item_empty[kItemSlots]
-    static constexpr int kNumBars = 4 + 2 * kStages + 9 + 2 * kItemSlots;
+    // ds_free[3], acc_free, item_full[kItemSlots], item_empty[kItemSlots], staged[2]
+    static constexpr int kNumBars = 4 + 2 * kStages + 9 + 2 * kItemSlots + 2;
     static constexpr int kMiscOff = kBarOff + kNumBars * 8;        // tmem base, abort flag, item slots
     static constexpr int kDynBytes = kMiscOff + 16 + 4 * kItemSlots + 1024;
 };
@@ -1247,7 +1317,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 attn_bwd_dq4_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
                           const __grid_constant__ CUtensorMap tmap_do,
                           const __grid_constant__ CUtensorMap tmap_k,
-                          const __grid_constant__ CUtensorMap tmap_v, const BwdArgs a, const ItemGrid grid) {
+                          const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_dq, const BwdArgs a, const ItemGrid grid) {
     using L = Dq4Smem;
     constexpr int kKStep = 128;
     extern __shared__ uint8_t smem_raw[];
@@ -1272,17 +1342,25 @@ attn_bwd_dq4_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
     volatile uint32_t* misc = reinterpret_cast<volatile uint32_t*>(smem_gen + L::kMiscOff);
     const ItemQueue iq{bar_sdp_full + 72u, bar_sdp_full + 72u + 8u * kItemSlots,
                        reinterpret_cast<volatile int*>(smem_gen + L::kMiscOff + 16)};
+    // dQ of an item staged in the item's own Q buffer (one barrier per buffer)
+    auto bar_staged = [&](int r) { return bar_sdp_full + 72u + 16u * kItemSlots + 8u * r; };
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0) {
-        for (int r = 0; r < 2; ++r) { mbar_init(bar_res_full(r), 1); mbar_init(bar_res_empty(r), 1); }
+        // a Q / dO buffer is free again when the MMA thread is done with it and the item's dQ, which is
+        // staged in its Q half, has been read by its TMA store
+        for (int r = 0; r < 2; ++r) {
+            mbar_init(bar_res_full(r), 1);
+            mbar_init(bar_res_empty(r), 2);
+            mbar_init(bar_staged(r), 16);
+        }
         for (int s = 0; s < L::kStages; ++s) { mbar_init(bar_ring_full(s), 1); mbar_init(bar_ring_empty(s), 2); }
         mbar_init(bar_sdp_full, 1);
         mbar_init(bar_sdp_free, 16);               // one arrival per elementwise warp
         for (int r = 0; r < 3; ++r) { mbar_init(bar_ds_full(r), 16); mbar_init(bar_ds_free(r), 1); }
         mbar_init(bar_acc_free, 16);
-        for (int i = 0; i < kItemSlots; ++i) { mbar_init(iq.full(i), 1); mbar_init(iq.empty(i), 18); }
+        for (int i = 0; i < kItemSlots; ++i) { mbar_init(iq.full(i), 1); mbar_init(iq.empty(i), 19); }
         misc[1] = 0u;
         mbar_fence_init();
     }
@@ -1422,6 +1500,30 @@ attn_bwd_dq4_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
             }
             if (ok && g > 0) ok = mbar_wait(bar_ds_free(g - 1), ds_parity(g - 1), wc, 0xea);
         }
+      } else {
+        // warp 19: stores each item's dQ tile (staged by the elementwise warps in the item's Q buffer,
+        // 128-byte swizzle) with TMA and hands the buffer back to the producer.  Rows past the end of
+        // the queries are clipped by the tensor map.
+        if (lane == 0) {
+            int na = 0;
+            bool ok = true;
+            for (int nq = 0; ok; ++nq) {
+                const int linear = iq.consume(nq, wc);
+                if (linear < 0) break;
+                int q0, h, b, kvlen;
+                const int n_it = item_steps(linear, q0, h, b, kvlen);
+                if (n_it == 0) continue;
+                const int r = na & 1;
+                ok = mbar_wait(bar_staged(r), (uint32_t)((na >> 1) & 1), wc, 0xd9);
+                if (ok) {
+                    tma_store_4d(&tmap_dq, res_smem + r * 2 * kBigTile, 0, q0, h, b);
+                    tma_store_commit();
+                    tma_store_wait_read<0>();
+                }
+                mbar_arrive(bar_res_empty(r));
+                ++na;
+            }
+        }
       }
     } else {
         reg_alloc<kMathRegs>();
@@ -1434,7 +1536,7 @@ attn_bwd_dq4_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
         const float c2 = a.scale_log2;
         const bool general = (a.keep_mask != nullptr) || (a.use_clamp != 0);
 
-        int g = 0;
+        int g = 0, na = 0;
         bool ok = true;
         for (int nq = 0; ok; ++nq) {
             const int linear = iq.consume_warp(nq, wc);
@@ -1557,7 +1659,25 @@ attn_bwd_dq4_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_acc_free);
-            if (qi < a.Sq) store_row16_bf16(drow, o, a.scale);
+            {
+                // this thread's 16 columns of dQ (scaled), bf16, into the item's Q buffer in the layout of a
+                // 128-byte-swizzled TMA box; warp 19 stores the tile
+                const int r = na & 1;
+                ++na;
+                uint8_t* st_q = smem_gen + L::kResOff + r * 2 * kBigTile + row * 128;
+#pragma unroll
+                for (int v = 0; v < 2; ++v) {
+                    uint4 w;
+                    w.x = pack_bf16x2(__uint_as_float(o[8 * v + 0]) * a.scale, __uint_as_float(o[8 * v + 1]) * a.scale);
+                    w.y = pack_bf16x2(__uint_as_float(o[8 * v + 2]) * a.scale, __uint_as_float(o[8 * v + 3]) * a.scale);
+                    w.z = pack_bf16x2(__uint_as_float(o[8 * v + 4]) * a.scale, __uint_as_float(o[8 * v + 5]) * a.scale);
+                    w.w = pack_bf16x2(__uint_as_float(o[8 * v + 6]) * a.scale, __uint_as_float(o[8 * v + 7]) * a.scale);
+                    *reinterpret_cast<uint4*>(st_q + (((2 * cq + v) ^ (row & 7)) << 4)) = w;
+                }
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_staged(r));
+            }
         }
     }
 
@@ -1647,8 +1767,10 @@ int launch_main(ltca_ctx* ctx, const ltca_attn_params* p, const void* q, const v
             ig.n_items = ig.nblk * ig.BH;
             ig.counters = ctx->d_sched + 2;             // ints 2,3: the dQ kernel's item counters
             const int n_cta = ig.n_items < ctx->sm_count ? ig.n_items : ctx->sm_count;
+            CUtensorMap tdq;
+            if ((rc = make_tmap_bhsd(ctx, &tdq, p->dq, 2, p->B, p->H, p->Sq, kD, p->dq_strides, 64, kTile))) return rc;
             attn_bwd_dq4_sm100_kernel<<<n_cta, kThreads, Dq4Smem::kDynBytes, ctx->stream>>>(tq128, tdo128, tk128,
-                                                                                            tv128, a, ig);
+                                                                                            tv128, tdq, a, ig);
             LTCA_LAUNCH_OK(ctx, "attn_bwd_dq4_sm100_kernel");
             dq_launched = true;
         }
@@ -1675,8 +1797,11 @@ int launch_main(ltca_ctx* ctx, const ltca_attn_params* p, const void* q, const v
             ig.n_items = ig.nblk * ig.BH;
             ig.counters = ctx->d_sched + 4;             // ints 4,5: the dK/dV kernel's item counters
             const int n_cta = ig.n_items < ctx->sm_count ? ig.n_items : ctx->sm_count;
+            CUtensorMap tdk, tdv;
+            if ((rc = make_tmap_bhsd(ctx, &tdk, p->dk, 2, p->B, p->H, p->Sk, kD, p->dk_strides, 64, kTile))) return rc;
+            if ((rc = make_tmap_bhsd(ctx, &tdv, p->dv, 2, p->B, p->H, p->Sk, kD, p->dv_strides, 64, kTile))) return rc;
             attn_bwd_dkv4_sm100_kernel<<<n_cta, kThreads, Dkv4Smem::kDynBytes, ctx->stream>>>(tq128, tdo128, tk128,
-                                                                                             tv128, a, ig);
+                                                                                             tv128, tdk, tdv, a, ig);
             LTCA_LAUNCH_OK(ctx, "attn_bwd_dkv4_sm100_kernel");
             kernel_timing_mark(ctx, 3);
             return LTCA_OK;

@@ -1216,10 +1216,21 @@ attn_fwd4p_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
             const int lin = iq.consume_warp(nq, wc);
             if (lin < 0) break;
             decode(lin, it);
-            const int b = it.b, h = it.h, kvlen = it.kvlen;
-            const int q0 = (it.m_block * kF4Tiles + t) * kBlockM;
-            const int qi = q0 + row;
             const int n_t = steps_of(it, t);
+            const int n_max = it.n_max;
+            const int b_mask = it.b;
+            // per row: number of visible keys; per tile: the first step that needs masking at all
+            int lim_row, je = n_t;
+            {
+                const int q0 = (it.m_block * kF4Tiles + t) * kBlockM;
+                lim_row = it.kvlen;
+                if (a.causal) lim_row = min(lim_row, q0 + row + a.causal_off + 1);
+                if (it.kvlen % kBN) je = min(je, it.kvlen / kBN);
+                if (a.causal) {
+                    const int v = q0 + a.causal_off - (kBN - 1);      // step j is cut by the diagonal when j * kBN > v
+                    je = min(je, v < 0 ? 0 : v / kBN + 1);
+                }
+            }
 
             float m_run = neg_inf();
             float l_run = 0.f;
@@ -1228,7 +1239,7 @@ attn_fwd4p_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
             // pair's contractions are in flight.  Every warp takes it.n_max turns per item, idle ones
             // included, so the two turn barriers see eight arrivals per step.
             const int grp = t >> 1;
-            for (int j = 0; j < it.n_max; ++j) {
+            for (int j = 0; j < n_max; ++j) {
                 if (j < n_t) {
                     ok = mbar_wait_warp(bar_s_full(t), (uint32_t)(scnt & 1), wc, 0x30 + t);
                     if (!ok) break;
@@ -1256,15 +1267,13 @@ attn_fwd4p_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 tmem_wait_ld();
                 LTCA_TRACE_EVT(0x11 + (j << 8));
 #define S_(c) __uint_as_float(su[(c)])
-                const int k0 = j * kBN;
-                const bool edge = (k0 + kBN > kvlen) || (a.causal && (k0 + kBN - 1 > q0 + a.causal_off));
                 if (general) {
-                    int lim = kvlen;
-                    if (a.causal) lim = min(lim, qi + a.causal_off + 1);
-                    lim -= k0;                              // columns c < lim are visible
+                    const int k0 = j * kBN;
+                    const int lim = lim_row - k0;           // columns c < lim are visible
+                    const int qi = (it.m_block * kF4Tiles + t) * kBlockM + row;
                     const float* mrow = nullptr;
                     if (a.keep_mask && qi < a.Sq)
-                        mrow = a.keep_mask + ((int64_t)b * a.Sq + qi) * a.Sk + k0;
+                        mrow = a.keep_mask + ((int64_t)b_mask * a.Sq + qi) * a.Sk + k0;
 #pragma unroll
                     for (int c = 0; c < kBN; ++c) {
                         float v = S_(c);
@@ -1273,11 +1282,9 @@ attn_fwd4p_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
                         if (mrow && vis) vis = (__ldg(mrow + c) != 0.0f);
                         su[c] = __float_as_uint(vis ? v : neg_inf());
                     }
-                } else if (edge) {
+                } else if (j >= je) {
                     // causal diagonal or end of the keys, no dense mask: a select per column, no branches
-                    int lim = kvlen;
-                    if (a.causal) lim = min(lim, qi + a.causal_off + 1);
-                    lim -= k0;
+                    const int lim = lim_row - j * kBN;
 #pragma unroll
                     for (int c = 0; c < kBN; ++c) su[c] = (c < lim) ? su[c] : 0xff800000u;
                 }
@@ -1347,6 +1354,10 @@ attn_fwd4p_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
             if (!ok) break;
 
             // epilogue: O / l and lse; the tile's tensor memory is handed back before the stores
+            decode(lin, it);                    // (re-derived here rather than kept in registers across the key loop)
+            const int b = it.b, h = it.h;
+            const int q0 = (it.m_block * kF4Tiles + t) * kBlockM;
+            const int qi = q0 + row;
             if (it.n_max > 0) {
                 const int r = na & 1;
                 ++na;
