@@ -31,6 +31,9 @@
 #include "sm100_ptx.cuh"
 #include "trace.cuh"
 
+#ifndef LTCA_FWD4_MIN_SQ
+#define LTCA_FWD4_MIN_SQ 256      // queries above which the four-tile persistent kernel is used
+#endif
 #ifndef LTCA_FWD4_TURNS
 #define LTCA_FWD4_TURNS 0
 #endif
@@ -1517,7 +1520,7 @@ int launch_fwd(ltca_ctx* ctx, const ltca_attn_params* p, const void* q, const vo
 
     if constexpr (D == 64 && sizeof(OutT) == 2) {
         // long query ranges: four independent tiles per CTA (see attn_fwd4_sm100_kernel)
-        if (LTCA_FWD4 && p->Sq > 2 * kBlockM) return launch_fwd4(ctx, p, q, k, v, qs, ks, vs, a);
+        if (LTCA_FWD4 && p->Sq > LTCA_FWD4_MIN_SQ) return launch_fwd4(ctx, p, q, k, v, qs, ks, vs, a);
     }
 
     auto kern = attn_fwd_sm100_kernel<D, OutT, kSplitP>;
