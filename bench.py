@@ -312,8 +312,8 @@ def main():
         achieved = kernels[dom]["flops"] / (kernels[dom]["ms"] * 1e-3) / 1e12
         # DRAM bytes per launch of that kernel: ncu capture at B=2 (profiles/attention_core_b2_s4096_ncu_full.md),
         # which grows in proportion to batch x heads; None for a kernel that was not captured
-        dram_per_bh = {"attn_fwd4p_sm100_kernel": 1.628e6, "attn_bwd_dq4_sm100_kernel": 2.294e6,
-                       "attn_bwd_dkv4_sm100_kernel": 2.357e6}
+        dram_per_bh = {"attn_fwd4p_sm100_kernel": 1.649e6, "attn_bwd_dq4_sm100_kernel": 2.258e6,
+                       "attn_bwd_dkv4_sm100_kernel": 2.358e6}
         traffic = dram_per_bh[dom] * B * H if dom in dram_per_bh else None
         line = {
             "metric": "attention fwd+bwd TFLOP/s", "value": value, "unit": "TFLOP/s",
