@@ -1,5 +1,5 @@
 // fp32 attention: the exact arithmetic mode (fp32 FMA, accurate expf) and the path for every
-// shape the tensor-pipe kernels do not take (any head_dim up to 128, dense keep-masks, tiny
+// shape the tensor-pipe kernels do not take (any head_dim up to 512, dense keep-masks, tiny
 // sequences).  Forward, backward (two passes, no atomics, bit-reproducible) and the
 // row-statistics helper shared with the tensor-pipe backward.
 //
@@ -532,8 +532,204 @@ int run_bwd(ltca_ctx* ctx, const CoreArgs& a) {
     return LTCA_OK;
 }
 
+
+// ----------------------------------------------------------------------------------------------
+// Wide heads (128 < head_dim <= 512): the reference-compatible TimeSelfAttention gives every head
+// the full model width (include/cuDNN_ops.h:166-169 of the reference), so a 512-wide model has
+// 512-wide heads.  A tile of such rows no longer fits in shared memory next to its keys, so these
+// kernels give one warp to one query row (or one key row in the dK/dV pass): the lanes split the
+// feature dimension, a score is a warp reduction, and the row's accumulator lives in registers.
+// Same arithmetic and the same masks as the tiled kernels above; no atomics.
+// ----------------------------------------------------------------------------------------------
+constexpr int kWideMaxD = 512;
+constexpr int kWC = kWideMaxD / 32;        // feature columns per lane
+constexpr int kWideWarps = 4;
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+template <typename T>
+__device__ __forceinline__ void load_row(float (&r)[kWC], const T* p, int D, int lane, float mul) {
+#pragma unroll
+    for (int c = 0; c < kWC; ++c) {
+        const int d = lane + 32 * c;
+        r[c] = d < D ? ld_elem(p + d) * mul : 0.f;
+    }
+}
+__device__ __forceinline__ float dot_row(const float (&x)[kWC], const float (&y)[kWC]) {
+    float s = 0.f;
+#pragma unroll
+    for (int c = 0; c < kWC; ++c) s = fmaf(x[c], y[c], s);
+    return warp_sum(s);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kWideWarps * 32) attn_fwd_wide_kernel(const CoreArgs a) {
+    const int lane = threadIdx.x & 31;
+    const int64_t row = (int64_t)blockIdx.x * kWideWarps + (threadIdx.x >> 5);
+    if (row >= (int64_t)a.B * a.H * a.Sq) return;
+    const int qi = (int)(row % a.Sq);
+    const int64_t bh = row / a.Sq;
+    const int h = (int)(bh % a.H), b = (int)(bh / a.H);
+    int kvlen = a.Sk;
+    if (a.kv_len) kvlen = min(max(a.kv_len[b], 0), a.Sk);
+    const T* kb = reinterpret_cast<const T*>(a.k) + b * a.ks.batch + h * a.ks.head;
+    const T* vb = reinterpret_cast<const T*>(a.v) + b * a.vs.batch + h * a.vs.head;
+    float q[kWC], acc[kWC];
+    load_row(q, reinterpret_cast<const T*>(a.q) + b * a.qs.batch + h * a.qs.head + (int64_t)qi * a.qs.seq, a.D,
+             lane, a.scale);
+#pragma unroll
+    for (int c = 0; c < kWC; ++c) acc[c] = 0.f;
+    float m = -INFINITY, l = 0.f;
+    int k_end = kvlen;
+    if (a.causal) k_end = min(k_end, qi + a.causal_off + 1);
+    for (int j = 0; j < k_end; ++j) {
+        if (!key_visible(a, b, qi, j, kvlen)) continue;          // the same answer in every lane
+        float kr[kWC];
+        load_row(kr, kb + (int64_t)j * a.ks.seq, a.D, lane, 1.f);
+        float v = dot_row(q, kr);
+        if (a.use_clamp) v = fminf(v, a.clamp);
+        const float m_new = fmaxf(m, v);
+        const float corr = (m == -INFINITY) ? 0.f : expf(m - m_new);
+        const float p = expf(v - m_new);
+        l = l * corr + p;
+        m = m_new;
+        load_row(kr, vb + (int64_t)j * a.vs.seq, a.D, lane, 1.f);
+#pragma unroll
+        for (int c = 0; c < kWC; ++c) acc[c] = fmaf(p, kr[c], acc[c] * corr);
+    }
+    T* op = reinterpret_cast<T*>(a.o) + b * a.os.batch + h * a.os.head + (int64_t)qi * a.os.seq;
+    const float inv = l > 0.f ? 1.f / l : 0.f;
+#pragma unroll
+    for (int c = 0; c < kWC; ++c) {
+        const int d = lane + 32 * c;
+        if (d < a.D) st_elem(op + d, acc[c] * inv);
+    }
+    if (a.lse && lane == 0) a.lse[row] = l > 0.f ? m + logf(l) : -INFINITY;
+}
+
+// dQ: one warp per query row.
+template <typename T>
+__global__ void __launch_bounds__(kWideWarps * 32) attn_bwd_dq_wide_kernel(const CoreArgs a) {
+    const int lane = threadIdx.x & 31;
+    const int64_t row = (int64_t)blockIdx.x * kWideWarps + (threadIdx.x >> 5);
+    if (row >= (int64_t)a.B * a.H * a.Sq) return;
+    const int qi = (int)(row % a.Sq);
+    const int64_t bh = row / a.Sq;
+    const int h = (int)(bh % a.H), b = (int)(bh / a.H);
+    int kvlen = a.Sk;
+    if (a.kv_len) kvlen = min(max(a.kv_len[b], 0), a.Sk);
+    const T* kb = reinterpret_cast<const T*>(a.k) + b * a.ks.batch + h * a.ks.head;
+    const T* vb = reinterpret_cast<const T*>(a.v) + b * a.vs.batch + h * a.vs.head;
+    float q[kWC], g[kWC], acc[kWC];
+    load_row(q, reinterpret_cast<const T*>(a.q) + b * a.qs.batch + h * a.qs.head + (int64_t)qi * a.qs.seq, a.D,
+             lane, a.scale);
+    load_row(g, reinterpret_cast<const T*>(a.dout) + b * a.dos.batch + h * a.dos.head + (int64_t)qi * a.dos.seq,
+             a.D, lane, 1.f);
+#pragma unroll
+    for (int c = 0; c < kWC; ++c) acc[c] = 0.f;
+    const float lse = a.lse_in[row], dlt = a.delta[row];
+    int k_end = kvlen;
+    if (a.causal) k_end = min(k_end, qi + a.causal_off + 1);
+    if (lse == -INFINITY) k_end = 0;
+    for (int j = 0; j < k_end; ++j) {
+        if (!key_visible(a, b, qi, j, kvlen)) continue;
+        float kr[kWC], vr[kWC];
+        load_row(kr, kb + (int64_t)j * a.ks.seq, a.D, lane, 1.f);
+        load_row(vr, vb + (int64_t)j * a.vs.seq, a.D, lane, 1.f);
+        float v = dot_row(q, kr);
+        const float dp = dot_row(g, vr);
+        bool clamped = false;
+        if (a.use_clamp && v >= a.clamp) { v = a.clamp; clamped = true; }
+        const float ds = clamped ? 0.f : expf(v - lse) * (dp - dlt) * a.scale;
+#pragma unroll
+        for (int c = 0; c < kWC; ++c) acc[c] = fmaf(ds, kr[c], acc[c]);
+    }
+    T* dqp = reinterpret_cast<T*>(a.dq) + b * a.dqs.batch + h * a.dqs.head + (int64_t)qi * a.dqs.seq;
+#pragma unroll
+    for (int c = 0; c < kWC; ++c) {
+        const int d = lane + 32 * c;
+        if (d < a.D) st_elem(dqp + d, acc[c]);
+    }
+}
+
+// dK and dV: one warp per key row, looping over the queries that see the key.
+template <typename T>
+__global__ void __launch_bounds__(kWideWarps * 32) attn_bwd_dkv_wide_kernel(const CoreArgs a) {
+    const int lane = threadIdx.x & 31;
+    const int64_t row = (int64_t)blockIdx.x * kWideWarps + (threadIdx.x >> 5);
+    if (row >= (int64_t)a.B * a.H * a.Sk) return;
+    const int kj = (int)(row % a.Sk);
+    const int64_t bh = row / a.Sk;
+    const int h = (int)(bh % a.H), b = (int)(bh / a.H);
+    int kvlen = a.Sk;
+    if (a.kv_len) kvlen = min(max(a.kv_len[b], 0), a.Sk);
+    const T* qb = reinterpret_cast<const T*>(a.q) + b * a.qs.batch + h * a.qs.head;
+    const T* gb = reinterpret_cast<const T*>(a.dout) + b * a.dos.batch + h * a.dos.head;
+    float kr[kWC], vr[kWC], dk[kWC], dv[kWC];
+    load_row(kr, reinterpret_cast<const T*>(a.k) + b * a.ks.batch + h * a.ks.head + (int64_t)kj * a.ks.seq, a.D,
+             lane, a.scale);
+    load_row(vr, reinterpret_cast<const T*>(a.v) + b * a.vs.batch + h * a.vs.head + (int64_t)kj * a.vs.seq, a.D,
+             lane, 1.f);
+#pragma unroll
+    for (int c = 0; c < kWC; ++c) { dk[c] = 0.f; dv[c] = 0.f; }
+    int q_begin = 0;
+    if (a.causal) q_begin = max(0, kj - a.causal_off);
+    const int q_end = kj < kvlen ? a.Sq : 0;
+    const int64_t stat0 = bh * a.Sq;
+    for (int qi = q_begin; qi < q_end; ++qi) {
+        if (!key_visible(a, b, qi, kj, kvlen)) continue;
+        const float lse = a.lse_in[stat0 + qi];
+        if (lse == -INFINITY) continue;
+        float qr[kWC], gr[kWC];
+        load_row(qr, qb + (int64_t)qi * a.qs.seq, a.D, lane, 1.f);
+        load_row(gr, gb + (int64_t)qi * a.dos.seq, a.D, lane, 1.f);
+        float v = dot_row(qr, kr);                     // kr carries the scale
+        const float dp = dot_row(gr, vr);
+        bool clamped = false;
+        if (a.use_clamp && v >= a.clamp) { v = a.clamp; clamped = true; }
+        const float p = expf(v - lse);
+        const float ds = clamped ? 0.f : p * (dp - a.delta[stat0 + qi]) * a.scale;
+#pragma unroll
+        for (int c = 0; c < kWC; ++c) {
+            dv[c] = fmaf(p, gr[c], dv[c]);
+            dk[c] = fmaf(ds, qr[c], dk[c]);
+        }
+    }
+    T* dkp = reinterpret_cast<T*>(a.dk) + b * a.dks.batch + h * a.dks.head + (int64_t)kj * a.dks.seq;
+    T* dvp = reinterpret_cast<T*>(a.dv) + b * a.dvs.batch + h * a.dvs.head + (int64_t)kj * a.dvs.seq;
+#pragma unroll
+    for (int c = 0; c < kWC; ++c) {
+        const int d = lane + 32 * c;
+        if (d < a.D) { st_elem(dkp + d, dk[c]); st_elem(dvp + d, dv[c]); }
+    }
+}
+
+template <typename T>
+int run_wide(ltca_ctx* ctx, const CoreArgs& a, bool bwd) {
+    const int64_t qrows = (int64_t)a.B * a.H * a.Sq, krows = (int64_t)a.B * a.H * a.Sk;
+    const unsigned qblocks = (unsigned)((qrows + kWideWarps - 1) / kWideWarps);
+    if (!bwd) {
+        attn_fwd_wide_kernel<T><<<qblocks, kWideWarps * 32, 0, ctx->stream>>>(a);
+        LTCA_LAUNCH_OK(ctx, "attn_fwd_wide_kernel");
+        return LTCA_OK;
+    }
+    attn_bwd_delta_kernel<T><<<(unsigned)((qrows + 7) / 8), 256, 0, ctx->stream>>>(a);
+    LTCA_LAUNCH_OK(ctx, "attn_bwd_delta_kernel");
+    attn_bwd_dq_wide_kernel<T><<<qblocks, kWideWarps * 32, 0, ctx->stream>>>(a);
+    LTCA_LAUNCH_OK(ctx, "attn_bwd_dq_wide_kernel");
+    attn_bwd_dkv_wide_kernel<T><<<(unsigned)((krows + kWideWarps - 1) / kWideWarps), kWideWarps * 32, 0,
+                                  ctx->stream>>>(a);
+    LTCA_LAUNCH_OK(ctx, "attn_bwd_dkv_wide_kernel");
+    return LTCA_OK;
+}
+
 template <typename T>
 int dispatch(ltca_ctx* ctx, const CoreArgs& a, bool bwd) {
+    if (a.D > 128) return run_wide<T>(ctx, a, bwd);
     const int dc = (a.D + 15) / 16;
 #define LTCA_CASE(N) return bwd ? run_bwd<T, N>(ctx, a) : run_fwd<T, N>(ctx, a)
     if (dc <= 1) LTCA_CASE(1);
@@ -550,15 +746,15 @@ size_t attn_bwd_fp32_workspace(const ltca_attn_params* p) {
 }
 
 int launch_attn_fwd_fp32(ltca_ctx* ctx, const ltca_attn_params* p) {
-    if (p->D < 1 || p->D > 128)
-        return fail(ctx, LTCA_ERR_UNSUPPORTED, "fp32 attention supports head_dim 1..128, got %d", p->D);
+    if (p->D < 1 || p->D > kWideMaxD)
+        return fail(ctx, LTCA_ERR_UNSUPPORTED, "fp32 attention supports head_dim 1..%d, got %d", kWideMaxD, p->D);
     CoreArgs a = make_args(p);
     return p->dtype == LTCA_BF16 ? dispatch<__nv_bfloat16>(ctx, a, false) : dispatch<float>(ctx, a, false);
 }
 
 int launch_attn_bwd_fp32(ltca_ctx* ctx, const ltca_attn_params* p) {
-    if (p->D < 1 || p->D > 128)
-        return fail(ctx, LTCA_ERR_UNSUPPORTED, "fp32 attention supports head_dim 1..128, got %d", p->D);
+    if (p->D < 1 || p->D > kWideMaxD)
+        return fail(ctx, LTCA_ERR_UNSUPPORTED, "fp32 attention supports head_dim 1..%d, got %d", kWideMaxD, p->D);
     if (p->workspace_bytes < attn_bwd_fp32_workspace(p) || !p->workspace)
         return fail(ctx, LTCA_ERR_WORKSPACE, "backward needs %zu bytes of workspace",
                     attn_bwd_fp32_workspace(p));

@@ -44,6 +44,9 @@ FP32_CASES = [
     (2, 2, 33, 70, 24, False, True, True, 0.7),
     (1, 1, 70, 33, 8, True, False, False, 0.0),        # more queries than keys: early rows see nothing
     (2, 8, 256, 256, 64, True, False, False, 0.0),     # per-head shape of config 2
+    (2, 2, 32, 32, 512, False, False, False, 0.0),     # wide heads: the reference module's head width = model width
+    (1, 3, 50, 77, 200, True, True, True, 2.0),        # wide, every mask kind, ragged width
+    (2, 1, 40, 24, 256, True, False, False, 0.0),      # wide, more queries than keys
 ]
 
 

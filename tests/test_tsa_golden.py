@@ -141,3 +141,30 @@ def test_cuda_module_tensor_pipe_forward_backward(ctx, case):
         scale = max(1.0, float(np.abs(r).max()))
         assert np.abs(gh - r).max() < 2e-2 * scale, f"{name}: {np.abs(gh - r).max()} vs magnitude {scale}"
         assert np.linalg.norm(gh - r) < 1e-2 * np.linalg.norm(r), name
+
+
+@pytest.mark.gpu
+def test_cuda_module_reference_form_wide_heads(ctx):
+    """The reference's largest configuration, (input_dim, heads) = (512, 8): every head is 512 wide
+    (include/cuDNN_ops.h:166-169 of the reference), scale 1.0, no mask, time-major rows.  Forward and backward
+    of the module against the oracle."""
+    import torch
+    from cuda_ltc_b200 import _lib
+    B, S, E, H = 2, 12, 512, 8
+    W = E
+    rng = np.random.default_rng(23)
+    x = (0.5 * rng.standard_normal((B * S, E))).astype(np.float32)
+    dy = rng.standard_normal((B * S, E)).astype(np.float32)
+    lim = np.sqrt(6.0 / (E + W))
+    wq, wk, wv = (rng.uniform(-lim, lim, (E, H * W)).astype(np.float32) * 0.2 for _ in range(3))
+    wo = rng.uniform(-lim, lim, (H * W, E)).astype(np.float32)
+    gamma, beta = np.ones(E, np.float32), np.zeros(E, np.float32)
+    ref, _ = oracle.tsa_fwd(x, wq, wk, wv, wo, B, S, H, W, 1.0, False, True, True, True, gamma, beta)
+    gref = oracle.tsa_bwd(x, wq, wk, wv, wo, dy, B, S, H, W, 1.0, False, True)
+    dev = lambda a: torch.from_numpy(a).cuda()
+    kw = dict(scale=1.0, causal=False, time_major=True, mode=_lib.MODE_AUTO)
+    out = ctx.tsa_fwd(dev(x), dev(wq), dev(wk), dev(wv), dev(wo), B, S, H, W, gamma=dev(gamma), beta=dev(beta), **kw)
+    got = ctx.tsa_bwd(dev(x), dev(wq), dev(wk), dev(wv), dev(wo), dev(dy), B, S, H, W, **kw)
+    assert np.abs(out.cpu().numpy() - ref).max() < 1e-3
+    for name, g, r in zip(("dx", "dwq", "dwk", "dwv", "dwo"), got, gref):
+        assert np.abs(g.cpu().numpy() - r).max() < 1e-3 * max(1.0, np.abs(r).max()), name
