@@ -6,6 +6,7 @@
 from . import _lib  # noqa: F401
 from .api import (  # noqa: F401
     Context,
+    HostStepPipeline,
     LtcaError,
     attention_backward,
     attention_decode,

@@ -244,6 +244,62 @@ class Context:
 _default: dict = {}
 
 
+class HostStepPipeline:
+    """Attention forward + backward steps whose operands live in pinned HOST memory and whose results
+    return to pinned host memory, the way a caller that keeps its tensors on the host (the reference
+    allocates and fills them there before every call) uses the library.
+
+    Three streams - copy in, compute (the context's stream), copy out - and two sets of device buffers:
+    while step i computes, the operands of step i+1 arrive and the results of step i-1 leave, so in
+    steady state a step costs the slowest of the three stages instead of their sum (host-to-device and
+    device-to-host traffic use the two directions of the link at the same time).
+    """
+
+    def __init__(self, ctx: "Context", compute_stream: torch.cuda.Stream, like_q: torch.Tensor,
+                 like_k: torch.Tensor, causal: bool = True):
+        self.ctx, self.causal = ctx, causal
+        self.s_comp = compute_stream
+        self.s_in, self.s_out = torch.cuda.Stream(like_q.device), torch.cuda.Stream(like_q.device)
+        B, H, Sq, _ = like_q.shape
+        mk = torch.empty_like
+        self.bufs = []
+        for _ in range(2):
+            self.bufs.append(dict(q=mk(like_q), k=mk(like_k), v=mk(like_k), do=mk(like_q), o=mk(like_q),
+                                  lse=torch.empty((B, H, Sq), dtype=torch.float32, device=like_q.device),
+                                  dq=mk(like_q), dk=mk(like_k), dv=mk(like_k)))
+        ev = lambda: [torch.cuda.Event() for _ in range(2)]
+        self.ev_in, self.ev_comp, self.ev_out = ev(), ev(), ev()
+
+    def run(self, host_in, host_out, steps: int):
+        """`steps` forward+backward passes over host_in = (q, k, v, dout), results into
+        host_out = (o, dq, dk, dv); all pinned host tensors.  Returns nothing; the caller synchronises."""
+        hq, hk, hv, hdo = host_in
+        ho, hdq, hdk, hdv = host_out
+        for i in range(steps):
+            j = i & 1
+            b = self.bufs[j]
+            with torch.cuda.stream(self.s_in):
+                if i >= 2:
+                    self.s_in.wait_event(self.ev_comp[j])        # step i-2 has read these operand buffers
+                b["q"].copy_(hq, non_blocking=True); b["k"].copy_(hk, non_blocking=True)
+                b["v"].copy_(hv, non_blocking=True); b["do"].copy_(hdo, non_blocking=True)
+                self.ev_in[j].record(self.s_in)
+            with torch.cuda.stream(self.s_comp):
+                self.s_comp.wait_event(self.ev_in[j])
+                if i >= 2:
+                    self.s_comp.wait_event(self.ev_out[j])       # the results of step i-2 have left
+                self.ctx.attn_fwd(b["q"], b["k"], b["v"], causal=self.causal, mode=_lib.MODE_BF16,
+                                  out=b["o"], lse=b["lse"])
+                self.ctx.attn_bwd(b["q"], b["k"], b["v"], b["o"], b["lse"], b["do"], causal=self.causal,
+                                  mode=_lib.MODE_AUTO, dq=b["dq"], dk=b["dk"], dv=b["dv"])
+                self.ev_comp[j].record(self.s_comp)
+            with torch.cuda.stream(self.s_out):
+                self.s_out.wait_event(self.ev_comp[j])
+                ho.copy_(b["o"], non_blocking=True); hdq.copy_(b["dq"], non_blocking=True)
+                hdk.copy_(b["dk"], non_blocking=True); hdv.copy_(b["dv"], non_blocking=True)
+                self.ev_out[j].record(self.s_out)
+
+
 def _ctx_for(t: torch.Tensor) -> Context:
     dev = t.device.index if t.device.index is not None else torch.cuda.current_device()
     if dev not in _default:
