@@ -223,7 +223,7 @@ def test_argument_errors(ctx):
     with pytest.raises(LtcaError) as e:
         ctx.attn_fwd(q, q, q, scale=-1.0)
     assert e.value.code == -1
-    big = torch.zeros((1, 1, 4, 256), device="cuda")
+    big = torch.zeros((1, 1, 4, 1024), device="cuda")        # wider than the widest head the exact kernels take (512)
     with pytest.raises(LtcaError):
         ctx.attn_fwd(big, big, big, mode=_lib.MODE_FP32)
 
