@@ -27,8 +27,9 @@ namespace ltca {
 
 namespace {
 
-constexpr int kGT = 64;     // GEMM tile (M and N)
+constexpr int kGT = 128;    // GEMM tile (M and N)
 constexpr int kGK = 16;     // GEMM K step
+constexpr int kGP = 4;      // row padding of the shared tiles (floats)
 
 // C[M,N] (+)= op(A) op(B) (+ bias[N]); row-major storage.
 //   ta == 0: A is [M,K] (lda = K-extent stride), ta == 1: A is stored [K,M].
@@ -41,58 +42,109 @@ struct GemmArgs {
     int ta, tb, accumulate;
 };
 
+// Exact-mode projection GEMM (fp32 FMA, the arithmetic of the reference's cublasSgemm with tensor cores
+// off, src/ml/flash_attention.cu:531-536): 128 x 128 tile per CTA, 16 x 16 threads with 8 x 8 outputs each
+// (two 4-wide groups 64 apart per dimension, so shared-memory reads are conflict-free float4 loads), the
+// next K slab is fetched from global memory into registers while the current one is multiplied.
 __global__ void __launch_bounds__(256) gemm_fp32_kernel(const GemmArgs g) {
-    __shared__ float As[kGK][kGT + 1];
-    __shared__ float Bs[kGK][kGT + 1];
+    __shared__ __align__(16) float As[kGK][kGT + kGP];
+    __shared__ __align__(16) float Bs[kGK][kGT + kGP];
     const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
     const int m0 = blockIdx.y * kGT, n0 = blockIdx.x * kGT;
-    float acc[4][4];
+    float acc[8][8];
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
+    for (int i = 0; i < 8; ++i)
 #pragma unroll
-        for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+        for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
 
+    // Each thread moves 8 elements of the A slab and 8 of the B slab.  With the contraction index
+    // contiguous in memory (ta == 0 / tb == 1) a thread takes elements (r, k..k+7) of one row half; with the
+    // M / N index contiguous (ta == 1 / tb == 0) it takes (k, c..c+7) of one K row.
+    float ra[8], rb[8];
+    auto fetch = [&](int k0) {
+        if (!g.ta) {
+            const int r = threadIdx.x >> 1, kk = (threadIdx.x & 1) * 8;
+            const int gm = m0 + r;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const int gk = k0 + kk + e;
+                ra[e] = (gm < g.M && gk < g.K) ? __ldg(g.A + (int64_t)gm * g.lda + gk) : 0.f;
+            }
+        } else {
+            const int kk = threadIdx.x >> 4, c = (threadIdx.x & 15) * 8;
+            const int gk = k0 + kk;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const int gm = m0 + c + e;
+                ra[e] = (gm < g.M && gk < g.K) ? __ldg(g.A + (int64_t)gk * g.lda + gm) : 0.f;
+            }
+        }
+        if (g.tb) {
+            const int r = threadIdx.x >> 1, kk = (threadIdx.x & 1) * 8;
+            const int gn = n0 + r;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const int gk = k0 + kk + e;
+                rb[e] = (gn < g.N && gk < g.K) ? __ldg(g.B + (int64_t)gn * g.ldb + gk) : 0.f;
+            }
+        } else {
+            const int kk = threadIdx.x >> 4, c = (threadIdx.x & 15) * 8;
+            const int gk = k0 + kk;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const int gn = n0 + c + e;
+                rb[e] = (gn < g.N && gk < g.K) ? __ldg(g.B + (int64_t)gk * g.ldb + gn) : 0.f;
+            }
+        }
+    };
+    auto stash = [&]() {
+        if (!g.ta) {
+            const int r = threadIdx.x >> 1, kk = (threadIdx.x & 1) * 8;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) As[kk + e][r] = ra[e];
+        } else {
+            const int kk = threadIdx.x >> 4, c = (threadIdx.x & 15) * 8;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) As[kk][c + e] = ra[e];
+        }
+        if (g.tb) {
+            const int r = threadIdx.x >> 1, kk = (threadIdx.x & 1) * 8;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) Bs[kk + e][r] = rb[e];
+        } else {
+            const int kk = threadIdx.x >> 4, c = (threadIdx.x & 15) * 8;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) Bs[kk][c + e] = rb[e];
+        }
+    };
+
+    fetch(0);
     for (int k0 = 0; k0 < g.K; k0 += kGK) {
-        for (int idx = threadIdx.x; idx < kGT * kGK; idx += 256) {
-            int m, k;
-            if (g.ta) { m = idx % kGT; k = idx / kGT; } else { k = idx % kGK; m = idx / kGK; }
-            const int gm = m0 + m, gk = k0 + k;
-            float v = 0.f;
-            if (gm < g.M && gk < g.K)
-                v = g.ta ? g.A[(int64_t)gk * g.lda + gm] : g.A[(int64_t)gm * g.lda + gk];
-            As[k][m] = v;
-        }
-        for (int idx = threadIdx.x; idx < kGT * kGK; idx += 256) {
-            int n, k;
-            if (g.tb) { k = idx % kGK; n = idx / kGK; } else { n = idx % kGT; k = idx / kGT; }
-            const int gn = n0 + n, gk = k0 + k;
-            float v = 0.f;
-            if (gn < g.N && gk < g.K)
-                v = g.tb ? g.B[(int64_t)gn * g.ldb + gk] : g.B[(int64_t)gk * g.ldb + gn];
-            Bs[k][n] = v;
-        }
+        stash();
         __syncthreads();
+        if (k0 + kGK < g.K) fetch(k0 + kGK);
 #pragma unroll
         for (int k = 0; k < kGK; ++k) {
-            float a[4], b[4];
+            const float4 a0 = *reinterpret_cast<const float4*>(&As[k][4 * ty]);
+            const float4 a1 = *reinterpret_cast<const float4*>(&As[k][64 + 4 * ty]);
+            const float4 b0 = *reinterpret_cast<const float4*>(&Bs[k][4 * tx]);
+            const float4 b1 = *reinterpret_cast<const float4*>(&Bs[k][64 + 4 * tx]);
+            const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+            const float b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
 #pragma unroll
-            for (int i = 0; i < 4; ++i) a[i] = As[k][ty + 16 * i];
+            for (int i = 0; i < 8; ++i)
 #pragma unroll
-            for (int j = 0; j < 4; ++j) b[j] = Bs[k][tx + 16 * j];
-#pragma unroll
-            for (int i = 0; i < 4; ++i)
-#pragma unroll
-                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+                for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
         }
         __syncthreads();
     }
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const int gm = m0 + ty + 16 * i;
+    for (int i = 0; i < 8; ++i) {
+        const int gm = m0 + (i < 4 ? 4 * ty + i : 64 + 4 * ty + i - 4);
         if (gm >= g.M) continue;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const int gn = n0 + tx + 16 * j;
+        for (int j = 0; j < 8; ++j) {
+            const int gn = n0 + (j < 4 ? 4 * tx + j : 64 + 4 * tx + j - 4);
             if (gn >= g.N) continue;
             float v = acc[i][j];
             if (g.bias) v += g.bias[gn];
