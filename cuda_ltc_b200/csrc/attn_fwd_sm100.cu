@@ -34,12 +34,6 @@
 #ifndef LTCA_FWD4_MIN_SQ
 #define LTCA_FWD4_MIN_SQ 256      // queries above which the four-tile persistent kernel is used
 #endif
-#ifndef LTCA_FWD4_TURNS
-#define LTCA_FWD4_TURNS 0
-#endif
-#ifndef LTCA_FWD4_PERSIST
-#define LTCA_FWD4_PERSIST 1
-#endif
 #ifndef LTCA_FWD4
 #define LTCA_FWD4 1
 #endif
@@ -573,7 +567,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
 }
 
 // ---------------------------------------------------------------------------------------------
-// Four-tile variant (head_dim 64, bf16 result): one CTA per (512 query rows, head, batch).
+// Four-tile persistent kernel (head_dim 64, bf16 result): the kernel used for long query ranges.
 //
 // Every scheduler of the SM holds four softmax warps that belong to four DIFFERENT query tiles;
 // a tile's warps only ever wait for that tile's own barriers, so while one tile sits in a
@@ -586,6 +580,20 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
 //     thread's MMAs in order) and one commit tells the tile both "S ready" and "O up to date";
 //   - warps 0-15: softmax, one query row per thread (tile = warp / 4); warp 16 issues the
 //     contractions of tiles 0 and 1, warp 17 those of tiles 2 and 3; warp 18: TMA producer.
+//
+// Persistent: one CTA per SM takes (512 query rows, head, batch)
+// items from a global counter (ItemQueue; grouped heavy-first order).  Barriers, tensor memory
+// and tensor maps are set up once per CTA; the Q tiles are double-buffered and the K/V ring runs
+// straight from one item's last keys into the next item's first, so the pipeline never drains:
+// a tile that has finished its rows of item i (the early tiles of a causal block have fewer key
+// steps) writes its output and starts on item i+1 while the later tiles still work on item i.
+// (A one-CTA-per-block version of this kernel spent 8.6 us per 512-row block on set-up, pipeline fill and drain.)
+// Barrier phases run on per-role counters; every completion of a reused barrier depends on the
+// waiter of the previous one, so a parity wait cannot alias:
+//   s_full(t)    one commit per key step + one at the start and one at the end of an item
+//   p_full(t)    one arrival per softmax warp per step
+//   tile_free(t) the tile's warps have read O of the previous item out of tensor memory
+//   q_full/q_empty[2], kv_full/kv_empty[8] as usual (both MMA threads release a slot).
 // ---------------------------------------------------------------------------------------------
 constexpr int kF4Tiles = 4;
 constexpr int kF4BN = 64;
@@ -595,351 +603,6 @@ constexpr int kF4CtrlRegs = 56;
 constexpr int kF4MathRegs = 104;
 static_assert(512 * kF4MathRegs + 128 * kF4CtrlRegs <= kF4Threads * kF4LaunchRegs, "register budget");
 
-struct F4Cfg {
-    static constexpr int kQTileBytes = kBlockM * 64 * 2;       // 16 KB
-    static constexpr int kKvTileBytes = kF4BN * 64 * 2;        // 8 KB
-    static constexpr int kStages = 8;
-    static constexpr int kQOff = 0;
-    static constexpr int kRingOff = kF4Tiles * kQTileBytes;
-    static constexpr int kBarOff = kRingOff + kStages * kKvTileBytes;
-    // barriers: q_full, kv_full[kStages], kv_empty[kStages], s_full[4], p_full[4]
-    static constexpr int kNumBars = 1 + 2 * kStages + 2 * kF4Tiles;
-    static constexpr int kMiscOff = kBarOff + kNumBars * 8;
-    static constexpr int kDynBytes = kMiscOff + 16 + 1024;
-};
-
-__global__ void __launch_bounds__(kF4Threads, 1)
-attn_fwd4_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
-                       const __grid_constant__ CUtensorMap tmap_k,
-                       const __grid_constant__ CUtensorMap tmap_v, const FwdArgs a) {
-    using L = F4Cfg;
-    constexpr int D = 64;
-    constexpr int kBN = kF4BN;
-    extern __shared__ uint8_t smem_raw[];
-    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-    const uint32_t q_smem = smem_base + L::kQOff;
-    const uint32_t ring_smem = smem_base + L::kRingOff;
-    const uint32_t bar_base = smem_base + L::kBarOff;
-    auto bar_q_full = [&]() { return bar_base; };
-    auto bar_kv_full = [&](int s) { return bar_base + 8u * (1 + s); };
-    auto bar_kv_empty = [&](int s) { return bar_base + 8u * (1 + L::kStages + s); };
-    auto bar_s_full = [&](int t) { return bar_base + 8u * (1 + 2 * L::kStages + t); };
-    auto bar_p_full = [&](int t) { return bar_base + 8u * (1 + 2 * L::kStages + kF4Tiles + t); };
-    volatile uint32_t* misc = reinterpret_cast<volatile uint32_t*>(smem_gen + L::kMiscOff);
-
-    const int warp = threadIdx.x >> 5;
-    const int lane = threadIdx.x & 31;
-    int rank, h, b;
-    sched_block(rank, h, b);
-    const int m_block = gridDim.x - 1 - rank;           // heavy (late) causal blocks first
-
-    int kvlen = a.Sk;
-    if (a.kv_len) kvlen = min(max(a.kv_len[b], 0), a.Sk);
-    int n_tiles[kF4Tiles];
-    int n_max = 0;
-#pragma unroll
-    for (int t = 0; t < kF4Tiles; ++t) {
-        const int q0 = (m_block * kF4Tiles + t) * kBlockM;
-        int lim = 0;
-        if (q0 < a.Sq) {
-            lim = kvlen;
-            if (a.causal) lim = min(lim, min(q0 + kBlockM - 1, a.Sq - 1) + a.causal_off + 1);
-        }
-        n_tiles[t] = lim > 0 ? (lim + kBN - 1) / kBN : 0;
-        n_max = max(n_max, n_tiles[t]);
-    }
-
-    if (threadIdx.x == 0) {
-        mbar_init(bar_q_full(), 1);
-        for (int s = 0; s < L::kStages; ++s) {
-            mbar_init(bar_kv_full(s), 1);
-            mbar_init(bar_kv_empty(s), 2);     // both MMA issuers release a slot
-        }
-        for (int t = 0; t < kF4Tiles; ++t) {
-            mbar_init(bar_s_full(t), 1);
-            mbar_init(bar_p_full(t), 4);       // one arrival per softmax warp of the tile
-        }
-        misc[1] = 0u;
-        mbar_fence_init();
-    }
-    if (warp == 16) {
-        tmem_alloc(smem_u32(const_cast<uint32_t*>(&misc[0])), kTmemCols);
-        tmem_relinquish();
-    }
-    tc_fence_before_sync();
-    __syncthreads();
-    tc_fence_after_sync();
-    const uint32_t tmem_base = misc[0];
-    const WaitCtx wc{&misc[1], a.status};
-
-    if (warp >= 16) {
-        reg_dealloc<kF4CtrlRegs>();
-        auto slot_of = [&](int item) { return item % L::kStages; };
-        auto phase_of = [&](int item) { return (uint32_t)((item / L::kStages) & 1); };
-        if (warp == 18) {
-            // ------------------------------ TMA producer --------------------------------------
-            if (lane == 0 && n_max > 0) {
-                tma_prefetch_desc(&tmap_q);
-                tma_prefetch_desc(&tmap_k);
-                tma_prefetch_desc(&tmap_v);
-                mbar_arrive_expect_tx(bar_q_full(), (uint32_t)(kF4Tiles * L::kQTileBytes));
-                for (int t = 0; t < kF4Tiles; ++t)
-                    tma_load_4d(q_smem + t * L::kQTileBytes, &tmap_q, bar_q_full(), 0,
-                                (m_block * kF4Tiles + t) * kBlockM, h, b);
-                bool ok = true;
-                for (int j = 0; j < n_max && ok; ++j) {
-#pragma unroll
-                    for (int which = 0; which < 2; ++which) {     // 0: K_j, 1: V_j
-                        const int item = 2 * j + which;
-                        const int slot = slot_of(item);
-                        ok = ok && mbar_wait(bar_kv_empty(slot), phase_of(item) ^ 1u, wc, 0x10 + which);
-                        if (!ok) break;
-                        mbar_arrive_expect_tx(bar_kv_full(slot), (uint32_t)L::kKvTileBytes);
-                        tma_load_4d(ring_smem + slot * L::kKvTileBytes, which == 0 ? &tmap_k : &tmap_v,
-                                    bar_kv_full(slot), 0, j * kBN, h, b);
-                    }
-                }
-            }
-        } else if (warp == 16 || warp == 17) {
-            // ------------------------------ MMA issuer of tiles 2i, 2i+1 ----------------------
-            const int t0 = 2 * (warp - 16);
-            if (lane == 0 && n_max > 0) {
-                constexpr uint32_t idesc_qk = make_idesc_bf16(kBlockM, kBN, 0, 0);
-                constexpr uint32_t idesc_pv = make_idesc_bf16(kBlockM, D, 0, 1);
-                const uint64_t q_desc = make_smem_desc_sw128(q_smem, 16, 1024);
-                const uint64_t k_desc = make_smem_desc_sw128(ring_smem, 16, 1024);
-                const uint64_t v_desc = make_smem_desc_sw128(ring_smem, kBN * 128, 1024);
-                auto issue_qk = [&](int t, int slot) {
-                    const uint64_t qd = q_desc + (uint64_t)((t * L::kQTileBytes) >> 4);
-                    const uint64_t kd = k_desc + (uint64_t)((slot * L::kKvTileBytes) >> 4);
-#pragma unroll
-                    for (int k = 0; k < D / 16; ++k)
-                        mma_ss(tmem_base + t * kBN, qd + 2 * k, kd + 2 * k, idesc_qk, k > 0 ? 1u : 0u);
-                };
-                auto issue_pv = [&](int t, int slot, bool acc) {
-                    const uint64_t vd = v_desc + (uint64_t)((slot * L::kKvTileBytes) >> 4);
-#pragma unroll
-                    for (int k = 0; k < kBN / 16; ++k)
-                        mma_ts(tmem_base + 256 + t * D, tmem_base + t * kBN + k * 8, vd + 128 * k, idesc_pv,
-                               (acc || k > 0) ? 1u : 0u);
-                };
-                bool ok = mbar_wait(bar_q_full(), 0, wc, 0x20);
-                ok = ok && mbar_wait(bar_kv_full(slot_of(0)), phase_of(0), wc, 0x21);
-                if (ok) {
-                    tc_fence_after_sync();
-                    for (int i = 0; i < 2; ++i)
-                        if (n_tiles[t0 + i] > 0) {
-                            issue_qk(t0 + i, slot_of(0));
-                            mma_commit(bar_s_full(t0 + i));
-                        }
-                    mma_commit(bar_kv_empty(slot_of(0)));
-                }
-                for (int j = 0; j < n_max && ok; ++j) {
-                    const int item_v = 2 * j + 1, item_k = 2 * j + 2;
-                    const bool have_next = (j + 1 < n_max);
-                    ok = mbar_wait(bar_kv_full(slot_of(item_v)), phase_of(item_v), wc, 0x22);
-                    if (have_next) ok = ok && mbar_wait(bar_kv_full(slot_of(item_k)), phase_of(item_k), wc, 0x23);
-                    for (int i = 0; i < 2 && ok; ++i) {
-                        const int t = t0 + i;
-                        if (j < n_tiles[t]) {
-                            ok = mbar_wait(bar_p_full(t), (uint32_t)(j & 1), wc, 0x24 + t);
-                            if (!ok) break;
-                            tc_fence_after_sync();
-                            issue_pv(t, slot_of(item_v), j > 0);
-                            if (j + 1 < n_tiles[t]) issue_qk(t, slot_of(item_k));
-                            mma_commit(bar_s_full(t));     // S of step j+1 ready, O holds steps 0..j
-                        }
-                    }
-                    if (!ok) break;
-                    mma_commit(bar_kv_empty(slot_of(item_v)));
-                    if (have_next) mma_commit(bar_kv_empty(slot_of(item_k)));
-                }
-                // everything this thread issued has to be complete before tensor memory is released
-                for (int i = 0; i < 2 && ok; ++i)
-                    if (n_tiles[t0 + i] > 0)
-                        ok = mbar_wait(bar_s_full(t0 + i), (uint32_t)(n_tiles[t0 + i] & 1), wc, 0x28 + t0 + i);
-            }
-        }
-    } else {
-        // ------------------------------ softmax / correction / epilogue ------------------------
-        reg_alloc<kF4MathRegs>();
-        const int t = warp >> 2;
-        const int wq = warp & 3;
-        const int row = wq * 32 + lane;
-        const int q0 = (m_block * kF4Tiles + t) * kBlockM;
-        const int qi = q0 + row;
-        const int n_t = n_tiles[t];
-        const uint32_t lane_base = (uint32_t)(wq * 32) << 16;
-        const uint32_t tS = tmem_base + lane_base + t * kBN;
-        const uint32_t tO = tmem_base + lane_base + 256 + t * D;
-        const float c2 = a.scale_log2;
-        const bool general = (a.keep_mask != nullptr) || (a.use_clamp != 0);
-
-        float m_run = neg_inf();
-        float l_run = 0.f;
-        bool ok = true;
-        for (int j = 0; j < n_t; ++j) {
-            ok = mbar_wait_warp(bar_s_full(t), (uint32_t)(j & 1), wc, 0x30 + t);
-            if (!ok) break;
-            tc_fence_after_sync();
-            uint32_t su[kBN];
-            tmem_ld32(tS, reinterpret_cast<uint32_t(&)[32]>(su[0]));
-            tmem_ld32(tS + 32, reinterpret_cast<uint32_t(&)[32]>(su[32]));
-            tmem_wait_ld();
-#define S_(c) __uint_as_float(su[(c)])
-            const int k0 = j * kBN;
-            const bool edge = (k0 + kBN > kvlen) || (a.causal && (k0 + kBN - 1 > q0 + a.causal_off));
-            if (general) {
-                int lim = kvlen;
-                if (a.causal) lim = min(lim, qi + a.causal_off + 1);
-                lim -= k0;                              // columns c < lim are visible
-                const float* mrow = nullptr;
-                if (a.keep_mask && qi < a.Sq)
-                    mrow = a.keep_mask + ((int64_t)b * a.Sq + qi) * a.Sk + k0;
-#pragma unroll
-                for (int c = 0; c < kBN; ++c) {
-                    float v = S_(c);
-                    if (a.use_clamp) v = fminf(v, a.clamp_raw);
-                    bool vis = c < lim;
-                    if (mrow && vis) vis = (__ldg(mrow + c) != 0.0f);
-                    su[c] = __float_as_uint(vis ? v : neg_inf());
-                }
-            } else if (edge) {
-                // causal diagonal or end of the keys, no dense mask: a select per column, no branches
-                int lim = kvlen;
-                if (a.causal) lim = min(lim, qi + a.causal_off + 1);
-                lim -= k0;
-#pragma unroll
-                for (int c = 0; c < kBN; ++c) su[c] = (c < lim) ? su[c] : 0xff800000u;
-            }
-            float mx[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) mx[i] = fmaxf(S_(2 * i), S_(2 * i + 1));
-#pragma unroll
-            for (int c = 8; c < kBN; c += 8)
-#pragma unroll
-                for (int i = 0; i < 4; ++i) mx[i] = fmax3(mx[i], S_(c + 2 * i), S_(c + 2 * i + 1));
-            const float mt = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-
-            // Lazy rescale: keep the stale maximum while the new one exceeds it by less than
-            // 2^8 in the exponent; P stays below 256 and fp32 sums keep their accuracy.
-            float factor = 1.0f;
-            bool need = false;
-            if (j == 0) {
-                m_run = mt;
-            } else if ((mt - m_run) * c2 > 8.0f) {
-                factor = fast_exp2((m_run - mt) * c2);
-                m_run = mt;
-                need = true;
-            }
-            if (j > 0 && __any_sync(0xffffffffu, need)) {
-                // O already holds every earlier step: the commit behind s_full covered it
-#pragma unroll
-                for (int c0 = 0; c0 < D; c0 += 16) {
-                    uint32_t o[16];
-                    tmem_ld16(tO + c0, o);
-                    tmem_wait_ld();
-#pragma unroll
-                    for (int c = 0; c < 16; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * factor);
-                    tmem_st16(tO + c0, o);
-                }
-                l_run *= factor;
-            }
-            const float m_safe = (m_run == neg_inf()) ? 0.f : m_run;
-            const float mneg = -m_safe * c2;
-            float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
-#pragma unroll
-            for (int ch = 0; ch < kBN / 32; ++ch) {
-                uint32_t hi[16];
-#pragma unroll
-                for (int cc = 0; cc < 32; cc += 4) {
-                    const int c = ch * 32 + cc;
-                    const float p0 = fast_exp2(fmaf(S_(c), c2, mneg));
-                    const float p1 = fast_exp2(fmaf(S_(c + 1), c2, mneg));
-                    const float p2 = fast_exp2(fmaf(S_(c + 2), c2, mneg));
-                    const float p3 = fast_exp2(fmaf(S_(c + 3), c2, mneg));
-                    sum0 += p0; sum1 += p1; sum2 += p2; sum3 += p3;
-                    hi[cc / 2] = pack_bf16x2(p0, p1);
-                    hi[cc / 2 + 1] = pack_bf16x2(p2, p3);
-                }
-                tmem_st16(tS + ch * 16, hi);      // P over the first columns of S (all of S is in registers)
-            }
-            l_run += (sum0 + sum1) + (sum2 + sum3);
-            tmem_wait_st();
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar_p_full(t));
-#undef S_
-        }
-
-        // epilogue: O / l and lse
-        if (ok && q0 < a.Sq) {
-            float inv = 0.f;
-            float lse = neg_inf();
-            if (n_t > 0) {
-                ok = mbar_wait_warp(bar_s_full(t), (uint32_t)(n_t & 1), wc, 0x34 + t);
-                tc_fence_after_sync();
-                if (l_run > 0.f) {
-                    inv = 1.0f / l_run;
-                    lse = m_run * a.scale + __logf(l_run);
-                }
-            }
-            __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(a.o) + b * a.o_sb + h * a.o_sh +
-                                  (int64_t)qi * a.o_ss;
-#pragma unroll
-            for (int c0 = 0; c0 < D; c0 += 32) {
-                uint32_t o[32];
-                if (n_t > 0 && ok) {
-                    tmem_ld32(tO + c0, o);
-                    tmem_wait_ld();
-                } else {
-#pragma unroll
-                    for (int c = 0; c < 32; ++c) o[c] = 0u;
-                }
-                if (qi < a.Sq) {
-                    uint4* dst = reinterpret_cast<uint4*>(orow + c0);
-#pragma unroll
-                    for (int v = 0; v < 4; ++v) {
-                        uint4 w;
-                        w.x = pack_bf16x2(__uint_as_float(o[8 * v + 0]) * inv, __uint_as_float(o[8 * v + 1]) * inv);
-                        w.y = pack_bf16x2(__uint_as_float(o[8 * v + 2]) * inv, __uint_as_float(o[8 * v + 3]) * inv);
-                        w.z = pack_bf16x2(__uint_as_float(o[8 * v + 4]) * inv, __uint_as_float(o[8 * v + 5]) * inv);
-                        w.w = pack_bf16x2(__uint_as_float(o[8 * v + 6]) * inv, __uint_as_float(o[8 * v + 7]) * inv);
-                        dst[v] = w;
-                    }
-                }
-            }
-            if (a.lse && qi < a.Sq) a.lse[((int64_t)b * a.H + h) * a.Sq + qi] = lse;
-        }
-    }
-
-    // ------------------------------ tear-down -------------------------------------------------
-    tc_fence_before_sync();
-    __syncthreads();
-    if (warp == 16) {
-        __syncwarp();
-        if (misc[1]) __nanosleep(200000);    // aborted: give copies and MMAs in flight time to land
-        tc_fence_after_sync();
-        tmem_dealloc(tmem_base, kTmemCols);
-    }
-}
-
-// ---------------------------------------------------------------------------------------------
-// Persistent form of the four-tile kernel: one CTA per SM takes (512 query rows, head, batch)
-// items from a global counter (ItemQueue; grouped heavy-first order).  Barriers, tensor memory
-// and tensor maps are set up once per CTA; the Q tiles are double-buffered and the K/V ring runs
-// straight from one item's last keys into the next item's first, so the pipeline never drains:
-// a tile that has finished its rows of item i (the early tiles of a causal block have fewer key
-// steps) writes its output and starts on item i+1 while the later tiles still work on item i.
-// Measured before this change: 8.6 us of set-up, pipeline fill and drain per 512-row block.
-// Barrier phases run on per-role counters; every completion of a reused barrier depends on the
-// waiter of the previous one, so a parity wait cannot alias:
-//   s_full(t)    one commit per key step + one at the start and one at the end of an item
-//   p_full(t)    one arrival per softmax warp per step
-//   tile_free(t) the tile's warps have read O of the previous item out of tensor memory
-//   q_full/q_empty[2], kv_full/kv_empty[8] as usual (both MMA threads release a slot).
-// ---------------------------------------------------------------------------------------------
 struct F4PCfg {
     static constexpr int kQTileBytes = kBlockM * 64 * 2;       // 16 KB
     static constexpr int kKvTileBytes = kF4BN * 64 * 2;        // 8 KB
@@ -948,7 +611,7 @@ struct F4PCfg {
     static constexpr int kRingOff = 2 * kQBufBytes;
     static constexpr int kBarOff = kRingOff + kStages * kKvTileBytes;
     // q_full[2], q_empty[2], kv_full[S], kv_empty[S], s_full[4], p_full[4], tile_free[4], staged[4], item full/empty
-    static constexpr int kNumBars = 4 + 2 * kStages + 4 * kF4Tiles + 2 * kItemSlots + 2;   // + turn[2]
+    static constexpr int kNumBars = 4 + 2 * kStages + 4 * kF4Tiles + 2 * kItemSlots;
     static constexpr int kMiscOff = kBarOff + kNumBars * 8;
     static constexpr int kDynBytes = kMiscOff + 16 + 4 * kItemSlots + 1024;
 };
@@ -976,7 +639,6 @@ attn_fwd4p_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
     auto bar_tile_free = [&](int t) { return bar_base + 8u * (4 + 2 * L::kStages + 2 * kF4Tiles + t); };
     auto bar_staged = [&](int t) { return bar_base + 8u * (4 + 2 * L::kStages + 3 * kF4Tiles + t); };
     const uint32_t bar_item0 = bar_base + 8u * (4 + 2 * L::kStages + 4 * kF4Tiles);
-    auto bar_turn = [&](int g) { return bar_base + 8u * (4 + 2 * L::kStages + 4 * kF4Tiles + 2 * kItemSlots + g); };
     volatile uint32_t* misc = reinterpret_cast<volatile uint32_t*>(smem_gen + L::kMiscOff);
     const ItemQueue iq{bar_item0, bar_item0 + 8u * kItemSlots,
                        reinterpret_cast<volatile int*>(smem_gen + L::kMiscOff + 16)};
@@ -998,8 +660,6 @@ attn_fwd4p_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
             mbar_init(bar_staged(t), 4);
         }
         for (int i = 0; i < kItemSlots; ++i) { mbar_init(iq.full(i), 1); mbar_init(iq.empty(i), 18); }
-        mbar_init(bar_turn(0), 8);
-        mbar_init(bar_turn(1), 8);
         misc[1] = 0u;
         mbar_fence_init();
     }
@@ -1210,9 +870,6 @@ attn_fwd4p_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
         int scnt = 0;                       // s_full phases consumed
         int na = 0;                         // items with keys so far (selects the Q buffer)
         int ecnt = 0;                       // outputs this tile has staged
-#if LTCA_FWD4_TURNS
-        int tcnt = 0;                       // turns taken
-#endif
         bool ok = true;
         Item it;
         for (int nq = 0; ok; ++nq) {
@@ -1237,31 +894,10 @@ attn_fwd4p_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
 
             float m_run = neg_inf();
             float l_run = 0.f;
-#if LTCA_FWD4_TURNS
-            // The tile pairs (0,1) and (2,3) take turns: one pair's exponentials run while the other
-            // pair's contractions are in flight.  Every warp takes it.n_max turns per item, idle ones
-            // included, so the two turn barriers see eight arrivals per step.
-            const int grp = t >> 1;
-            for (int j = 0; j < n_max; ++j) {
-                if (j < n_t) {
-                    ok = mbar_wait_warp(bar_s_full(t), (uint32_t)(scnt & 1), wc, 0x30 + t);
-                    if (!ok) break;
-                    ++scnt;
-                }
-                ok = mbar_wait_warp(bar_turn(grp), (uint32_t)((tcnt & 1) ^ (grp == 0 ? 1 : 0)), wc, 0x3c + grp);
-                if (!ok) break;
-                ++tcnt;
-                if (j >= n_t) {
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(bar_turn(grp ^ 1));
-                    continue;
-                }
-#else
             for (int j = 0; j < n_t; ++j) {
                 ok = mbar_wait_warp(bar_s_full(t), (uint32_t)(scnt & 1), wc, 0x30 + t);
                 if (!ok) break;
                 ++scnt;
-#endif
                 LTCA_TRACE_EVT(0x10 + (j << 8));
                 tc_fence_after_sync();
                 uint32_t su[kBN];
@@ -1348,9 +984,6 @@ attn_fwd4p_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 tc_fence_before_sync();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar_p_full(t));
-#if LTCA_FWD4_TURNS
-                if (lane == 0) mbar_arrive(bar_turn(grp ^ 1));
-#endif
                 LTCA_TRACE_EVT(0x12 + (j << 8));
 #undef S_
             }
@@ -1448,46 +1081,28 @@ attn_fwd4p_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
 
 int launch_fwd4(ltca_ctx* ctx, const ltca_attn_params* p, const void* q, const void* k, const void* v,
                 const ltca_strides& qs, const ltca_strides& ks, const ltca_strides& vs, const FwdArgs& a) {
-    using L = F4Cfg;
-    CUtensorMap tq, tk, tv;
+    using P = F4PCfg;
+    CUtensorMap tq, tk, tv, to;
     int rc;
     if ((rc = make_tmap_bhsd(ctx, &tq, q, 2, p->B, p->H, p->Sq, 64, qs, 64, kBlockM))) return rc;
     if ((rc = make_tmap_bhsd(ctx, &tk, k, 2, p->B, p->H, p->Sk, 64, ks, 64, kF4BN))) return rc;
     if ((rc = make_tmap_bhsd(ctx, &tv, v, 2, p->B, p->H, p->Sk, 64, vs, 64, kF4BN))) return rc;
+    if ((rc = make_tmap_bhsd(ctx, &to, p->o, 2, p->B, p->H, p->Sq, 64, p->o_strides, 64, kBlockM))) return rc;
     static bool attr_done = false;
     if (!attr_done) {
-        LTCA_CUDA_OK(ctx, cudaFuncSetAttribute(attn_fwd4_sm100_kernel,
-                                               cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynBytes));
+        LTCA_CUDA_OK(ctx, cudaFuncSetAttribute(attn_fwd4p_sm100_kernel,
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize, P::kDynBytes));
         attr_done = true;
     }
-#if LTCA_FWD4_PERSIST
-    {
-        using P = F4PCfg;
-        static bool attr_p_done = false;
-        if (!attr_p_done) {
-            LTCA_CUDA_OK(ctx, cudaFuncSetAttribute(attn_fwd4p_sm100_kernel,
-                                                   cudaFuncAttributeMaxDynamicSharedMemorySize, P::kDynBytes));
-            attr_p_done = true;
-        }
-        ItemGrid ig;
-        ig.nblk = (p->Sq + kF4Tiles * kBlockM - 1) / (kF4Tiles * kBlockM);
-        ig.H = p->H;
-        ig.BH = p->B * p->H;
-        ig.n_items = ig.nblk * ig.BH;
-        ig.counters = ctx->d_sched + 6;             // ints 6,7: the forward kernel's item counters
-        const int n_cta = ig.n_items < ctx->sm_count ? ig.n_items : ctx->sm_count;
-        CUtensorMap to;
-        ltca_strides os;
-        os.batch = p->o_strides.batch; os.head = p->o_strides.head; os.seq = p->o_strides.seq;
-        if ((rc = make_tmap_bhsd(ctx, &to, p->o, 2, p->B, p->H, p->Sq, 64, os, 64, kBlockM))) return rc;
-        attn_fwd4p_sm100_kernel<<<n_cta, kF4Threads, P::kDynBytes, ctx->stream>>>(tq, tk, tv, to, a, ig);
-        LTCA_LAUNCH_OK(ctx, "attn_fwd4p_sm100_kernel");
-        return LTCA_OK;
-    }
-#endif
-    dim3 grid((p->Sq + kF4Tiles * kBlockM - 1) / (kF4Tiles * kBlockM), p->H, p->B);
-    attn_fwd4_sm100_kernel<<<grid, kF4Threads, L::kDynBytes, ctx->stream>>>(tq, tk, tv, a);
-    LTCA_LAUNCH_OK(ctx, "attn_fwd4_sm100_kernel");
+    ItemGrid ig;
+    ig.nblk = (p->Sq + kF4Tiles * kBlockM - 1) / (kF4Tiles * kBlockM);
+    ig.H = p->H;
+    ig.BH = p->B * p->H;
+    ig.n_items = ig.nblk * ig.BH;
+    ig.counters = ctx->d_sched + 6;             // ints 6,7: the forward kernel's item counters
+    const int n_cta = ig.n_items < ctx->sm_count ? ig.n_items : ctx->sm_count;
+    attn_fwd4p_sm100_kernel<<<n_cta, kF4Threads, P::kDynBytes, ctx->stream>>>(tq, tk, tv, to, a, ig);
+    LTCA_LAUNCH_OK(ctx, "attn_fwd4p_sm100_kernel");
     return LTCA_OK;
 }
 
@@ -1519,7 +1134,7 @@ int launch_fwd(ltca_ctx* ctx, const ltca_attn_params* p, const void* q, const vo
     a.status = ctx->d_status;
 
     if constexpr (D == 64 && sizeof(OutT) == 2) {
-        // long query ranges: four independent tiles per CTA (see attn_fwd4_sm100_kernel)
+        // long query ranges: four independent tiles per CTA (see attn_fwd4p_sm100_kernel)
         if (LTCA_FWD4 && p->Sq > LTCA_FWD4_MIN_SQ) return launch_fwd4(ctx, p, q, k, v, qs, ks, vs, a);
     }
 

@@ -25,12 +25,6 @@ enum : uint32_t {
 #ifndef LTCA_WAIT_SLEEP_NS
 #define LTCA_WAIT_SLEEP_NS 0
 #endif
-#ifndef LTCA_WAIT_BACKOFF_AFTER
-#define LTCA_WAIT_BACKOFF_AFTER 0
-#endif
-#ifndef LTCA_WAIT_BACKOFF_NS
-#define LTCA_WAIT_BACKOFF_NS 200
-#endif
 static constexpr unsigned long long kWaitLimitNs = 2000000000ull;   // 2 s
 // (No suspend-time hint on mbarrier.try_wait: measured on B200, a hint more than doubles the
 // latency between an arrival and the waiter's wake-up.)
@@ -96,11 +90,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const W
     for (uint32_t it = 1;; ++it) {
 #if LTCA_WAIT_SLEEP_NS > 0
         __nanosleep(LTCA_WAIT_SLEEP_NS);      // a polling warp takes issue slots from the working ones
-#endif
-#if LTCA_WAIT_BACKOFF_AFTER > 0
-        // a wait that has already lasted this many polls is not on a per-step critical path (a tile
-        // that is done with its item, a CTA that ran out of items): poll rarely from here on
-        if (it > LTCA_WAIT_BACKOFF_AFTER) __nanosleep(LTCA_WAIT_BACKOFF_NS);
 #endif
         if (mbar_try_wait(bar, parity)) return true;
         if ((it & 0xffu) == 0) {
