@@ -158,6 +158,52 @@ def workload_config(n_gpus):
             "l2": f"inputs ({32 * CFG['B']} MB per step) exceed the 126 MB L2; no explicit flush"}
 
 
+def module_measurement(args):
+    """TimeSelfAttention forward and backward (with the recomputed forward) at B=32 S=256 E=512 H=8, head
+    width 64, causal: back-to-back calls between CUDA events, an L2 flush is not needed for a figure that is
+    dominated by eleven GEMMs over 16 MB activations.  Prints one JSON line."""
+    import math
+    import torch
+    import cuda_ltc_b200 as ltc
+    from cuda_ltc_b200 import _lib
+    torch.cuda.set_device(0)
+    ctx = ltc.Context(0)
+    B, S, E, H, W = 32, 256, 512, 8, 64
+    g = torch.Generator(device="cuda").manual_seed(SEED)
+    x = torch.randn((B * S, E), generator=g, device="cuda")
+    dy = torch.randn((B * S, E), generator=g, device="cuda")
+    lim = math.sqrt(6.0 / (2 * E))
+    ws = [(torch.rand((E, H * W), generator=g, device="cuda") * 2 - 1) * lim for _ in range(3)]
+    wo = (torch.rand((H * W, E), generator=g, device="cuda") * 2 - 1) * lim
+    gamma, beta = torch.ones(E, device="cuda"), torch.zeros(E, device="cuda")
+    kw = dict(scale=1 / math.sqrt(W), causal=True, time_major=False, mode=_lib.MODE_BF16)
+    fwd = lambda: ctx.tsa_fwd(x, *ws, wo, B, S, H, W, gamma=gamma, beta=beta, **kw)
+    bwd = lambda: ctx.tsa_bwd(x, *ws, wo, dy, B, S, H, W, **kw)
+    n, w = (1, 1) if args.profile else (max(5, args.steps), max(3, args.warmup))
+
+    def timed(f):
+        for _ in range(w):
+            f()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            f()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n
+
+    f_ms, b_ms = timed(fwd), timed(bwd)
+    rows = B * S
+    gemm = 2.0 * rows * E * H * W                       # one projection
+    core = 4.0 * B * H * S * S * W / 2
+    print(json.dumps({"workload": "TimeSelfAttention module, B=32 S=256 E=512 H=8 W=64 causal, tensor-pipe mode",
+                      "fwd_us": f_ms * 1e3, "bwd_incl_recompute_us": b_ms * 1e3,
+                      "fwd_tflops": (4 * gemm + core) / f_ms / 1e9,
+                      "bwd_tflops": (11 * gemm + 3.5 * core) / b_ms / 1e9,
+                      "device_status": ctx.device_status()}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -170,7 +216,13 @@ def main():
                     help="sequences per GPU; anything but the default is a reduced case for profiler captures")
     ap.add_argument("--profile", action="store_true",
                     help="profiler capture mode: 1 warm-up, 1 step, no end-to-end or CPU legs (not a bench value)")
+    ap.add_argument("--module", action="store_true",
+                    help="side measurement, not the bench line: the TimeSelfAttention module (projections + "
+                         "attention + residual + LayerNorm) at BASELINE configs[1], one GPU, tensor-pipe mode")
     args = ap.parse_args()
+    if args.module:
+        module_measurement(args)
+        return
     if args.profile:
         args.steps, args.warmup, args.no_e2e, args.no_cpu_baseline = 1, 1, True, True
     CFG["B"] = args.batch

@@ -26,12 +26,6 @@
 #include "sm100_ptx.cuh"
 #include "trace.cuh"
 
-#ifndef LTCA_BWD_TURNS
-#define LTCA_BWD_TURNS 0
-#endif
-#ifndef LTCA_EXP_PAIRS
-#define LTCA_EXP_PAIRS 0
-#endif
 #ifndef LTCA_BWD_DQ4
 #define LTCA_BWD_DQ4 1
 #endif
@@ -1603,22 +1597,11 @@ attn_bwd_dq4_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
                         dp[c] = __float_as_uint((c < vis_lim) ? p * (__uint_as_float(dp[c]) - dlt) : 0.f);
                     }
                 } else {
-#if LTCA_EXP_PAIRS
-#pragma unroll
-                    for (int c = 0; c < 32; c += 2) {
-                        float p0, p1;
-                        exp2_pair(fmaf(__uint_as_float(s[c]), c2, -lse2), fmaf(__uint_as_float(s[c + 1]), c2, -lse2),
-                                  p0, p1);
-                        dp[c] = __float_as_uint(p0 * (__uint_as_float(dp[c]) - dlt));
-                        dp[c + 1] = __float_as_uint(p1 * (__uint_as_float(dp[c + 1]) - dlt));
-                    }
-#else
 #pragma unroll
                     for (int c = 0; c < 32; ++c) {
                         const float p = fast_exp2(fmaf(__uint_as_float(s[c]), c2, -lse2));
                         dp[c] = __float_as_uint(p * (__uint_as_float(dp[c]) - dlt));
                     }
-#endif
                 }
                 uint32_t hi[16], unused[16];
                 pack32<false>(dp, hi, unused);

@@ -399,26 +399,6 @@ __device__ __forceinline__ float fast_exp2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
-// Two exponentials per special-function instruction: the arguments travel as an f16 pair.
-// With |x| < 16 the argument's rounding error is below 2^-7, i.e. below the rounding error of
-// the bf16 value the result is stored as, wherever the result is large enough to matter.
-__device__ __forceinline__ void exp2_pair(float x0, float x1, float& p0, float& p1) {
-    uint32_t h;
-    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(h) : "f"(x1), "f"(x0));
-    asm("ex2.approx.f16x2 %0, %1;" : "=r"(h) : "r"(h));
-    asm("{\n\t.reg .b16 lo, hi;\n\t"
-        "mov.b32 {lo, hi}, %2;\n\t"
-        "cvt.f32.f16 %0, lo;\n\t"
-        "cvt.f32.f16 %1, hi;\n\t}\n"
-        : "=f"(p0), "=f"(p1) : "r"(h));
-}
-// Same, result left as the f16 pair (element 0 in the low half).
-__device__ __forceinline__ uint32_t exp2_pair_f16(float x0, float x1) {
-    uint32_t h;
-    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(h) : "f"(x1), "f"(x0));
-    asm("ex2.approx.f16x2 %0, %1;" : "=r"(h) : "r"(h));
-    return h;
-}
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     uint32_t r;
     asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
