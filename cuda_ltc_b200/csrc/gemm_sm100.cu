@@ -44,6 +44,7 @@ struct GemmKArgs {
     int n_sum, ksplit;
     int64_t ldc;
     int out_bf16;
+    int tma_store;           // results leave through shared memory and a TMA store (needs 16-byte aligned rows)
     void* C[3];
     const float* bias[3];
     float* partial;          // [problem][slice][M][N] when ksplit > 1
@@ -55,7 +56,8 @@ __global__ void __launch_bounds__(kGemmThreads, 2)
 gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap ta0, const __grid_constant__ CUtensorMap ta1,
                        const __grid_constant__ CUtensorMap ta2, const __grid_constant__ CUtensorMap tb0,
                        const __grid_constant__ CUtensorMap tb1, const __grid_constant__ CUtensorMap tb2,
-                       const GemmKArgs g) {
+                       const __grid_constant__ CUtensorMap tc0, const __grid_constant__ CUtensorMap tc1,
+                       const __grid_constant__ CUtensorMap tc2, const GemmKArgs g) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -159,6 +161,62 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap ta0, const __grid_con
         }
         const uint32_t tacc = tmem_base + ((uint32_t)(qd * 32) << 16);
         const float* bias = (g.ksplit == 1) ? g.bias[problem] : nullptr;
+        if (g.tma_store && g.ksplit == 1) {
+            // The tile goes to shared memory (the operand ring is idle by now) in the layout of 128-byte
+            // swizzled TMA boxes - 64 bf16 or 32 fp32 columns wide, 128 rows - and one thread stores the boxes;
+            // the tensor map clips rows and columns past the end of C.  (Storing a row's 16-byte pieces
+            // straight from registers costs 32 L1 wavefronts per instruction, about as many cycles per tile
+            // as its MMAs.)
+            uint8_t* stage = smem_gen;
+            const int box_cols = g.out_bf16 ? 64 : 32;
+#pragma unroll 1
+            for (int c0 = 0; c0 < kBN; c0 += 32) {
+                uint32_t v[32];
+                __syncwarp();
+                if (n_iters > 0 && ok) {
+                    tmem_ld32(tacc + c0, v);
+                    tmem_wait_ld();
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) v[c] = 0u;
+                }
+                if (bias) {
+#pragma unroll
+                    for (int c = 0; c < 32; ++c)
+                        if (n0 + c0 + c < g.N) v[c] = __float_as_uint(__uint_as_float(v[c]) + __ldg(bias + n0 + c0 + c));
+                }
+                if (g.out_bf16) {
+                    uint8_t* box = stage + (c0 / 64) * (kBM * 128) + row * 128;
+                    const int ch0 = (c0 % 64) / 8;
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        uint4 w;
+                        w.x = pack_bf16x2(__uint_as_float(v[8 * c + 0]), __uint_as_float(v[8 * c + 1]));
+                        w.y = pack_bf16x2(__uint_as_float(v[8 * c + 2]), __uint_as_float(v[8 * c + 3]));
+                        w.z = pack_bf16x2(__uint_as_float(v[8 * c + 4]), __uint_as_float(v[8 * c + 5]));
+                        w.w = pack_bf16x2(__uint_as_float(v[8 * c + 6]), __uint_as_float(v[8 * c + 7]));
+                        *reinterpret_cast<uint4*>(box + (((ch0 + c) ^ (row & 7)) << 4)) = w;
+                    }
+                } else {
+                    uint8_t* box = stage + (c0 / 32) * (kBM * 128) + row * 128;
+#pragma unroll
+                    for (int c = 0; c < 8; ++c)
+                        *reinterpret_cast<uint4*>(box + ((c ^ (row & 7)) << 4)) =
+                            make_uint4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+                }
+            }
+            fence_proxy_async_smem();
+            asm volatile("bar.sync 1, 128;" ::: "memory");        // the four epilogue warps
+            if (warp == 2 && lane == 0) {
+                const CUtensorMap* tc = problem == 0 ? &tc0 : (problem == 1 ? &tc1 : &tc2);
+                const int n_boxes = kBN / box_cols;
+                for (int bx = 0; bx < n_boxes; ++bx)
+                    if (n0 + bx * box_cols < g.N)
+                        tma_store_4d(tc, smem_base + bx * (kBM * 128), n0 + bx * box_cols, m0, 0, 0);
+                tma_store_commit();
+                tma_store_wait_read<0>();
+            }
+        } else
 #pragma unroll 1
         for (int c0 = 0; c0 < kBN && ok; c0 += 32) {
             uint32_t v[32];
@@ -334,6 +392,20 @@ int gemm_sm100(ltca_ctx* ctx, const GemmProblem& gp) {
     for (int i = 0; i < 3; ++i) { g.C[i] = gp.c[i < gp.n_problems ? i : 0]; g.bias[i] = i < gp.n_problems ? gp.bias[i] : nullptr; }
     g.partial = gp.partial;
     g.status = ctx->d_status;
+    const int ces = gp.out_bf16 ? 2 : 4;
+    g.tma_store = (g.ksplit == 1 && ((gp.ldc * ces) % 16) == 0) ? 1 : 0;
+    for (int i = 0; i < gp.n_problems && g.tma_store; ++i)
+        if (reinterpret_cast<uintptr_t>(gp.c[i]) & 15) g.tma_store = 0;
+    CUtensorMap tc[3];
+    memset(tc, 0, sizeof(tc));
+    if (g.tma_store) {
+        ltca_strides cs;
+        cs.batch = 0; cs.head = 0; cs.seq = gp.ldc;
+        for (int i = 0; i < 3; ++i) {
+            const int j = i < gp.n_problems ? i : 0;
+            if ((rc = make_tmap_bhsd(ctx, &tc[i], gp.c[j], ces, 1, 1, gp.M, gp.N, cs, gp.out_bf16 ? 64 : 32, kBM))) return rc;
+        }
+    }
     if (g.ksplit > 1) {
         if (!gp.partial) return fail(ctx, LTCA_ERR_WORKSPACE, "gemm: split K needs scratch");
         if (gp.out_bf16) return fail(ctx, LTCA_ERR_INVALID, "gemm: split K writes fp32 results");
@@ -344,7 +416,7 @@ int gemm_sm100(ltca_ctx* ctx, const GemmProblem& gp) {
     const bool amn = gp.a[0].mn_major != 0, bmn = gp.b[0].mn_major != 0;
     auto launch = [&](auto kern) -> int {
         LTCA_CUDA_OK(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kDynBytes));
-        kern<<<grid, kGemmThreads, kDynBytes, ctx->stream>>>(ta[0], ta[1], ta[2], tb[0], tb[1], tb[2], g);
+        kern<<<grid, kGemmThreads, kDynBytes, ctx->stream>>>(ta[0], ta[1], ta[2], tb[0], tb[1], tb[2], tc[0], tc[1], tc[2], g);
         LTCA_LAUNCH_OK(ctx, "gemm_bf16_sm100_kernel");
         return LTCA_OK;
     };
