@@ -58,6 +58,9 @@ class TsaParams(C.Structure):
         ("dy", C.c_void_p), ("dx", C.c_void_p),
         ("dwq", C.c_void_p), ("dwk", C.c_void_p), ("dwv", C.c_void_p), ("dwo", C.c_void_p),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+        ("pre_norm", C.c_int32), ("dropout_prob", C.c_float), ("dropout_seed", C.c_uint64),
+        ("dbq", C.c_void_p), ("dbk", C.c_void_p), ("dbv", C.c_void_p), ("dbo", C.c_void_p),
+        ("dgamma", C.c_void_p), ("dbeta", C.c_void_p),
     ]
 
 

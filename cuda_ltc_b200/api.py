@@ -235,6 +235,46 @@ class Context:
         del ws
         return (dx, *dws)
 
+    def fa_fwd(self, x, wq, wk, wv, wo, B, S, H, head_dim, biases=(None, None, None, None), gamma=None, beta=None,
+               use_layer_norm=True, use_residual=True, keep_mask=None, dropout_prob=0.0, dropout_seed=0,
+               score_clamp=10.0, mode=_lib.MODE_AUTO):
+        """The reference's FlashAttention module: out = dropout(x + Wo MHA(LayerNorm(x)) + bo); x [B*S, E]
+        batch-major rows, scale 1/sqrt(head_dim), score clamp 10."""
+        p = self._tsa_params(x, wq, wk, wv, wo, B, S, H, head_dim, 1.0 / math.sqrt(head_dim), False, False,
+                             use_residual, use_layer_norm, gamma, beta, keep_mask, mode, biases)
+        p.pre_norm, p.score_clamp = 1, float(score_clamp)
+        p.dropout_prob, p.dropout_seed = float(dropout_prob), int(dropout_seed)
+        out = torch.empty_like(x)
+        p.out = out.data_ptr()
+        ws = self._tsa_workspace(p, 0)
+        self.check(self.lib.ltca_tsa_fwd(self.handle, C.byref(p)))
+        del ws
+        return out
+
+    def fa_bwd(self, x, wq, wk, wv, wo, dy, B, S, H, head_dim, biases=(None, None, None, None), gamma=None,
+               beta=None, use_layer_norm=True, use_residual=True, keep_mask=None, dropout_prob=0.0,
+               dropout_seed=0, score_clamp=10.0, mode=_lib.MODE_AUTO):
+        """Backward of fa_fwd (an extension: the reference class has none).  Returns a dict with dx, dwq, dwk,
+        dwv, dwo, dbq, dbk, dbv, dbo and, with LayerNorm, dgamma and dbeta."""
+        p = self._tsa_params(x, wq, wk, wv, wo, B, S, H, head_dim, 1.0 / math.sqrt(head_dim), False, False,
+                             use_residual, use_layer_norm, gamma, beta, keep_mask, mode, biases)
+        p.pre_norm, p.score_clamp = 1, float(score_clamp)
+        p.dropout_prob, p.dropout_seed = float(dropout_prob), int(dropout_seed)
+        E, HW = x.shape[1], H * head_dim
+        f32 = dict(dtype=torch.float32, device=x.device)
+        g = dict(dx=torch.empty_like(x), dwq=torch.empty_like(wq), dwk=torch.empty_like(wk),
+                 dwv=torch.empty_like(wv), dwo=torch.empty_like(wo), dbq=torch.empty(HW, **f32),
+                 dbk=torch.empty(HW, **f32), dbv=torch.empty(HW, **f32), dbo=torch.empty(E, **f32))
+        if use_layer_norm:
+            g["dgamma"], g["dbeta"] = torch.empty(E, **f32), torch.empty(E, **f32)
+        p.dy = dy.data_ptr()
+        for name, t in g.items():
+            setattr(p, name, t.data_ptr())
+        ws = self._tsa_workspace(p, 3)
+        self.check(self.lib.ltca_tsa_bwd(self.handle, C.byref(p)))
+        del ws
+        return g
+
     def uses_tensor_pipe(self, q, k, v, causal=False, mode=_lib.MODE_AUTO, backward=False) -> bool:
         o = q
         p = self._params(q, k, v, o, None, 1.0, causal, None, None, 0.0, mode)

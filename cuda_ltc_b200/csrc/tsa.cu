@@ -245,6 +245,110 @@ __global__ void residual_layer_norm_kernel(const float* __restrict__ y, const fl
         outr[i] = (outr[i] - mean) * inv_std * (gamma ? gamma[i] : 1.f) + (beta ? beta[i] : 0.f);
 }
 
+
+// ---- pieces of the FlashAttention form: dropout, LayerNorm backward, column sums -----------------
+
+// u in [0,1) from (seed, element index): splitmix64 finaliser, top 24 bits.  The same function runs on the host
+// in the oracle, so masks can be compared element by element.
+__host__ __device__ inline float dropout_uniform(uint64_t seed, uint64_t idx) {
+    uint64_t z = seed + (idx + 1) * 0x9E3779B97F4A7C15ull;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    z ^= z >> 31;
+    return (float)(z >> 40) * (1.0f / 16777216.0f);
+}
+
+// dst[i] = keep(i) ? src[i] / (1 - p) : 0   (inverted dropout, reference src/ml/flash_attention.cu:380-399;
+// the reference draws from curand with a time-dependent offset, so only the distribution can match)
+__global__ void dropout_kernel(const float* __restrict__ src, float* __restrict__ dst, int64_t n, float p,
+                               uint64_t seed) {
+    const float scale = 1.0f / (1.0f - p);
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+        dst[i] = dropout_uniform(seed, (uint64_t)i) >= p ? src[i] * scale : 0.f;
+}
+
+// LayerNorm backward, one warp per row.  g = gradient at the LayerNorm output, x = its input.
+//   dx = inv_std * (g*gamma - mean(g*gamma) - xhat * mean(g*gamma*xhat))  (+ res[row] when res != null)
+// prod (optional) receives g * xhat, whose column sums are dgamma.
+__global__ void layer_norm_bwd_kernel(const float* __restrict__ g, const float* __restrict__ x,
+                                      const float* __restrict__ gamma, const float* __restrict__ res,
+                                      float* __restrict__ dx, float* __restrict__ prod, int64_t rows, int E,
+                                      float eps) {
+    const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const int lane = threadIdx.x & 31;
+    const float* xr = x + row * E;
+    const float* gr = g + row * E;
+    float sum = 0.f;
+    for (int i = lane; i < E; i += 32) sum += xr[i];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    const float mean = sum / E;
+    float var = 0.f;
+    for (int i = lane; i < E; i += 32) { const float d = xr[i] - mean; var = fmaf(d, d, var); }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) var += __shfl_xor_sync(0xffffffffu, var, o);
+    const float inv_std = rsqrtf(var / E + eps);
+    float m1 = 0.f, m2 = 0.f;
+    for (int i = lane; i < E; i += 32) {
+        const float xh = (xr[i] - mean) * inv_std;
+        const float gg = gr[i] * gamma[i];
+        m1 += gg;
+        m2 = fmaf(gg, xh, m2);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        m1 += __shfl_xor_sync(0xffffffffu, m1, o);
+        m2 += __shfl_xor_sync(0xffffffffu, m2, o);
+    }
+    m1 /= E; m2 /= E;
+    for (int i = lane; i < E; i += 32) {
+        const float xh = (xr[i] - mean) * inv_std;
+        const float gi = gr[i];
+        float v = inv_std * (gi * gamma[i] - m1 - xh * m2);
+        if (res) v += res[row * E + i];
+        if (prod) prod[row * E + i] = gi * xh;          // may alias g: each element is read before it is written
+        dx[row * E + i] = v;
+    }
+}
+
+// Column sums of a [rows, cols] matrix in two fixed-order stages (no atomics): kColChunks row chunks, then
+// the chunks.
+constexpr int kColChunks = 64;
+__device__ __forceinline__ float ld_f(const float* p) { return *p; }
+__device__ __forceinline__ float ld_f(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+template <typename T>
+__global__ void column_sum_partial_kernel(const T* __restrict__ src, int64_t ld, int64_t rows, int cols,
+                                          float* __restrict__ partial) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= cols) return;
+    const int64_t per = (rows + kColChunks - 1) / kColChunks;
+    const int64_t r0 = blockIdx.y * per, r1 = r0 + per < rows ? r0 + per : rows;
+    float acc = 0.f;
+    for (int64_t r = r0; r < r1; ++r) acc += ld_f(src + r * ld + c);
+    partial[(int64_t)blockIdx.y * cols + c] = acc;
+}
+__global__ void column_sum_final_kernel(const float* __restrict__ partial, int cols, float* __restrict__ dst) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= cols) return;
+    float acc = 0.f;
+    for (int k = 0; k < kColChunks; ++k) acc += partial[(int64_t)k * cols + c];
+    dst[c] = acc;
+}
+template <typename T>
+int column_sum(ltca_ctx* ctx, const T* src, int64_t ld, int64_t rows, int cols, float* dst, float* scratch) {
+    dim3 grid((cols + 127) / 128, kColChunks);
+    column_sum_partial_kernel<T><<<grid, 128, 0, ctx->stream>>>(src, ld, rows, cols, scratch);
+    LTCA_LAUNCH_OK(ctx, "column_sum_partial_kernel");
+    column_sum_final_kernel<<<(cols + 127) / 128, 128, 0, ctx->stream>>>(scratch, cols, dst);
+    LTCA_LAUNCH_OK(ctx, "column_sum_final_kernel");
+    return LTCA_OK;
+}
+size_t colsum_scratch_bytes(const ltca_tsa_params* t) {
+    const int hw = t->H * t->head_width;
+    return align_up((size_t)kColChunks * (hw > t->E ? hw : t->E) * sizeof(float), 256);
+}
+
 struct Plan {
     int64_t rows;
     int HW;
@@ -470,7 +574,7 @@ int tensor_forward(ltca_ctx* ctx, const ltca_tsa_params* t) {
     return LTCA_OK;
 }
 
-int tensor_backward(ltca_ctx* ctx, const ltca_tsa_params* t, bool want_dx, bool want_dw) {
+int tensor_backward(ltca_ctx* ctx, const ltca_tsa_params* t, bool want_dx, bool want_dw, float* colsum_scratch) {
     TPlan pl;
     int rc;
     if ((rc = make_tplan(t, &pl))) return rc;
@@ -508,6 +612,14 @@ int tensor_backward(ltca_ctx* ctx, const ltca_tsa_params* t, bool want_dx, bool 
     a.workspace_bytes = pl.attn_bwd;
     if ((rc = ltca_attn_bwd(ctx, &a))) return rc;
     const void* grads[3] = {dq, dk, dv};
+    if (want_dw) {
+        // bias gradients (FlashAttention form): column sums of the projection outputs' gradients
+        float* db[3] = {t->dbq, t->dbk, t->dbv};
+        for (int i = 0; i < 3; ++i)
+            if (db[i] && (rc = column_sum(ctx, reinterpret_cast<const __nv_bfloat16*>(grads[i]), HW, pl.rows, HW, db[i],
+                                          colsum_scratch))) return rc;
+        if (t->dbo && (rc = column_sum(ctx, t->dy, E, pl.rows, E, t->dbo, colsum_scratch))) return rc;
+    }
     if (want_dx) {
         // dx = dq Wq^T + dk Wk^T + dv Wv^T : each W is stored [E, HW] = [N, K]; one accumulator tile
         GemmProblem gp;
@@ -560,8 +672,8 @@ using namespace ltca;
 
 extern "C" {
 
-int ltca_tsa_workspace_bytes(const ltca_tsa_params* t, int which, size_t* bytes_out) {
-    if (!t || !bytes_out || which < 0 || which > 3) return LTCA_ERR_INVALID;
+// Workspace of the TimeSelfAttention form (no input LayerNorm, no dropout), without the column-sum scratch.
+static int inner_workspace(const ltca_tsa_params* t, int which, size_t* bytes_out) {
     if (use_tensor(t, which != 0)) {
         TPlan tp;
         int trc = make_tplan(t, &tp);
@@ -584,12 +696,139 @@ int ltca_tsa_workspace_bytes(const ltca_tsa_params* t, int which, size_t* bytes_
     return LTCA_OK;
 }
 
+// The module without the FlashAttention-form steps: what the pre_norm wrappers run in the middle.
+static ltca_tsa_params core_form(const ltca_tsa_params* t) {
+    ltca_tsa_params c = *t;
+    c.pre_norm = 0;
+    c.use_residual = 0;
+    c.use_layer_norm = 0;
+    c.dropout_prob = 0.f;
+    c.dgamma = nullptr;
+    c.dbeta = nullptr;
+    return c;
+}
+static size_t act_bytes(const ltca_tsa_params* t) {
+    return align_up((size_t)t->B * t->S * t->E * sizeof(float), 256);
+}
+
+int ltca_tsa_workspace_bytes(const ltca_tsa_params* t, int which, size_t* bytes_out) {
+    if (!t || !bytes_out || which < 0 || which > 3) return LTCA_ERR_INVALID;
+    size_t n = 0;
+    int rc;
+    if (t->pre_norm) {
+        const ltca_tsa_params c = core_form(t);
+        if ((rc = inner_workspace(&c, which, &n))) return rc;
+        n += (which == 0 ? 1 : 3) * act_bytes(t);         // LayerNorm(x); backward: + masked dy, gradient at LayerNorm(x)
+    } else if ((rc = inner_workspace(t, which, &n))) {
+        return rc;
+    }
+    if (which != 0) n += colsum_scratch_bytes(t);
+    *bytes_out = n;
+    return LTCA_OK;
+}
+
+static int tsa_backward(ltca_ctx* ctx, const ltca_tsa_params* t, bool want_dx, bool want_dw);
+
+// FlashAttention form, forward: LayerNorm on the input, the core module, residual with the raw input, dropout.
+static int prenorm_forward(ltca_ctx* ctx, const ltca_tsa_params* t) {
+    size_t need = 0;
+    int rc = ltca_tsa_workspace_bytes(t, 0, &need);
+    if (rc) return rc;
+    if (!t->workspace || t->workspace_bytes < need)
+        return fail(ctx, LTCA_ERR_WORKSPACE, "forward needs %zu bytes of workspace", need);
+    const int64_t rows = (int64_t)t->B * t->S;
+    const int64_t n = rows * t->E;
+    char* w = reinterpret_cast<char*>(t->workspace);
+    float* xin = reinterpret_cast<float*>(w);
+    w += act_bytes(t);
+    ltca_tsa_params c = core_form(t);
+    if (t->use_layer_norm) {
+        const int wpb = 8;
+        residual_layer_norm_kernel<<<(unsigned)((rows + wpb - 1) / wpb), wpb * 32, 0, ctx->stream>>>(
+            t->x, t->x, t->ln_gamma, t->ln_beta, xin, rows, t->E, 0, 1, 1e-5f);
+        LTCA_LAUNCH_OK(ctx, "residual_layer_norm_kernel");
+        c.x = xin;
+    }
+    c.workspace = w;
+    c.workspace_bytes = t->workspace_bytes - act_bytes(t);
+    if ((rc = ltca_tsa_fwd(ctx, &c))) return rc;
+    if (t->use_residual && (rc = ltca_add_tensors(ctx, t->out, t->x, t->out, (size_t)n))) return rc;
+    if (t->dropout_prob > 0.f) {
+        const unsigned blocks = (unsigned)((n + 255) / 256 < 2368 ? (n + 255) / 256 : 2368);
+        dropout_kernel<<<blocks, 256, 0, ctx->stream>>>(t->out, t->out, n, t->dropout_prob, t->dropout_seed);
+        LTCA_LAUNCH_OK(ctx, "dropout_kernel");
+    }
+    return LTCA_OK;
+}
+
+// FlashAttention form, backward (an extension: the reference class has no backward pass).
+static int prenorm_backward(ltca_ctx* ctx, const ltca_tsa_params* t, bool want_dx, bool want_dw) {
+    size_t need = 0;
+    int rc = ltca_tsa_workspace_bytes(t, 1, &need);
+    if (rc) return rc;
+    if (!t->workspace || t->workspace_bytes < need)
+        return fail(ctx, LTCA_ERR_WORKSPACE, "backward needs %zu bytes of workspace", need);
+    if (t->use_layer_norm && !t->ln_gamma) return fail(ctx, LTCA_ERR_INVALID, "LayerNorm needs gamma");
+    const int64_t rows = (int64_t)t->B * t->S;
+    const int64_t n = rows * t->E;
+    const size_t act = act_bytes(t);
+    char* w = reinterpret_cast<char*>(t->workspace);
+    float* xin = reinterpret_cast<float*>(w);   w += act;
+    float* gbuf = reinterpret_cast<float*>(w);  w += act;
+    float* dxin = reinterpret_cast<float*>(w);  w += act;
+    float* colsum_scratch = reinterpret_cast<float*>(reinterpret_cast<char*>(t->workspace) + need - colsum_scratch_bytes(t));
+    const int wpb = 8;
+    const unsigned row_blocks = (unsigned)((rows + wpb - 1) / wpb);
+    ltca_tsa_params c = core_form(t);
+    if (t->use_layer_norm) {
+        residual_layer_norm_kernel<<<row_blocks, wpb * 32, 0, ctx->stream>>>(
+            t->x, t->x, t->ln_gamma, t->ln_beta, xin, rows, t->E, 0, 1, 1e-5f);
+        LTCA_LAUNCH_OK(ctx, "residual_layer_norm_kernel");
+        c.x = xin;
+    }
+    const float* g = t->dy;                      // gradient behind the dropout
+    if (t->dropout_prob > 0.f) {
+        const unsigned blocks = (unsigned)((n + 255) / 256 < 2368 ? (n + 255) / 256 : 2368);
+        dropout_kernel<<<blocks, 256, 0, ctx->stream>>>(t->dy, gbuf, n, t->dropout_prob, t->dropout_seed);
+        LTCA_LAUNCH_OK(ctx, "dropout_kernel");
+        g = gbuf;
+    }
+    const bool want_ln_params = want_dw && t->use_layer_norm && (t->dgamma || t->dbeta);
+    const bool need_dxin = want_dx || want_ln_params;
+    c.dy = g;
+    c.dx = dxin;
+    c.workspace = w;
+    c.workspace_bytes = t->workspace_bytes - 3 * act;
+    if ((rc = tsa_backward(ctx, &c, need_dxin, want_dw))) return rc;
+    if (!need_dxin) return LTCA_OK;
+    if (!t->use_layer_norm) {
+        if (want_dx) {
+            if (t->use_residual) return ltca_add_tensors(ctx, dxin, g, t->dx, (size_t)n);
+            LTCA_CUDA_OK(ctx, cudaMemcpyAsync(t->dx, dxin, (size_t)n * sizeof(float), cudaMemcpyDeviceToDevice, ctx->stream));
+        }
+        return LTCA_OK;
+    }
+    if (want_ln_params && t->dbeta && (rc = column_sum(ctx, dxin, t->E, rows, t->E, t->dbeta, colsum_scratch))) return rc;
+    // dx (or, when only parameter gradients are wanted, a dump into the no longer needed LayerNorm(x) buffer);
+    // dxin is overwritten by dxin * xhat, whose column sums are dgamma
+    float* dx_out = want_dx ? t->dx : xin;
+    layer_norm_bwd_kernel<<<row_blocks, wpb * 32, 0, ctx->stream>>>(
+        dxin, t->x, t->ln_gamma, (want_dx && t->use_residual) ? g : nullptr, dx_out,
+        (want_ln_params && t->dgamma) ? dxin : nullptr, rows, t->E, 1e-5f);
+    LTCA_LAUNCH_OK(ctx, "layer_norm_bwd_kernel");
+    if (want_ln_params && t->dgamma && (rc = column_sum(ctx, dxin, t->E, rows, t->E, t->dgamma, colsum_scratch))) return rc;
+    return LTCA_OK;
+}
+
 int ltca_tsa_fwd(ltca_ctx* ctx, const ltca_tsa_params* t) {
     int rc = check(ctx, t);
     if (rc) return rc;
     if (!t->out) return fail(ctx, LTCA_ERR_INVALID, "out must be non-null");
     if (t->use_layer_norm && (!t->ln_gamma || !t->ln_beta))
         return fail(ctx, LTCA_ERR_INVALID, "LayerNorm needs gamma and beta");
+    if (t->dropout_prob < 0.f || t->dropout_prob >= 1.f)
+        return fail(ctx, LTCA_ERR_INVALID, "dropout_prob must be in [0, 1)");
+    if (t->pre_norm) return prenorm_forward(ctx, t);
     if (use_tensor(t, false)) return tensor_forward(ctx, t);
     Plan pl;
     if ((rc = make_plan(t, &pl))) return rc;
@@ -620,11 +859,18 @@ static int tsa_backward(ltca_ctx* ctx, const ltca_tsa_params* t, bool want_dx, b
     if (want_dx && !t->dx) return fail(ctx, LTCA_ERR_INVALID, "dx must be non-null");
     if (want_dw && (!t->dwq || !t->dwk || !t->dwv || !t->dwo))
         return fail(ctx, LTCA_ERR_INVALID, "dwq, dwk, dwv, dwo must be non-null");
-    if (use_tensor(t, true)) return tensor_backward(ctx, t, want_dx, want_dw);
-    Plan pl;
-    if ((rc = make_plan(t, &pl))) return rc;
+    if (t->dropout_prob < 0.f || t->dropout_prob >= 1.f)
+        return fail(ctx, LTCA_ERR_INVALID, "dropout_prob must be in [0, 1)");
+    if (t->pre_norm) return prenorm_backward(ctx, t, want_dx, want_dw);
     size_t need = 0;
     ltca_tsa_workspace_bytes(t, 1, &need);
+    if (!t->workspace || t->workspace_bytes < need)
+        return fail(ctx, LTCA_ERR_WORKSPACE, "backward needs %zu bytes of workspace", need);
+    float* colsum_scratch =
+        reinterpret_cast<float*>(reinterpret_cast<char*>(t->workspace) + need - colsum_scratch_bytes(t));
+    if (use_tensor(t, true)) return tensor_backward(ctx, t, want_dx, want_dw, colsum_scratch);
+    Plan pl;
+    if ((rc = make_plan(t, &pl))) return rc;
     if (!t->workspace || t->workspace_bytes < need)
         return fail(ctx, LTCA_ERR_WORKSPACE, "backward needs %zu bytes of workspace", need);
     char* w = reinterpret_cast<char*>(t->workspace);
@@ -646,6 +892,13 @@ static int tsa_backward(ltca_ctx* ctx, const ltca_tsa_params* t, bool want_dx, b
     a.workspace = pl.attn_bwd ? fb.rest : nullptr;
     a.workspace_bytes = pl.attn_bwd;
     if ((rc = ltca_attn_bwd(ctx, &a))) return rc;
+    if (want_dw) {
+        // bias gradients (FlashAttention form): column sums of the projection outputs' gradients
+        if (t->dbq && (rc = column_sum(ctx, dq, HW, pl.rows, HW, t->dbq, colsum_scratch))) return rc;
+        if (t->dbk && (rc = column_sum(ctx, dk, HW, pl.rows, HW, t->dbk, colsum_scratch))) return rc;
+        if (t->dbv && (rc = column_sum(ctx, dv, HW, pl.rows, HW, t->dbv, colsum_scratch))) return rc;
+        if (t->dbo && (rc = column_sum(ctx, t->dy, E, pl.rows, E, t->dbo, colsum_scratch))) return rc;
+    }
     if (want_dx) {
         if ((rc = gemm(ctx, dq, t->wq, nullptr, t->dx, rows, E, HW, HW, HW, E, 0, 1, 0))) return rc;
         if ((rc = gemm(ctx, dk, t->wk, nullptr, t->dx, rows, E, HW, HW, HW, E, 0, 1, 1))) return rc;

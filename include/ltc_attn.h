@@ -210,6 +210,18 @@ typedef struct {
                                                   (CUDNN_WGRAD_MODE_SET, cuDNN_ops.cu:366-385) */
     void*  workspace;
     size_t workspace_bytes;
+    /* FlashAttention form of the module (src/ml/flash_attention.cu:808-1150 of the reference):
+     *   out = dropout( x + Wo·MHA(LayerNorm(x)) + bo )
+     * i.e. LayerNorm on the INPUT (:822-834), residual with the raw input (:1107-1113), inverted dropout last
+     * (:1117-1131).  Set pre_norm; use_layer_norm / use_residual then select those two steps, head_width is the
+     * reference's head_dim, scale its 1/sqrt(head_dim) (:998), score_clamp its 10 (:167).  Zero keeps the
+     * TimeSelfAttention form described above. */
+    int32_t  pre_norm;
+    float    dropout_prob;          /* 0 = none.  The keep decision of element i is a hash of (dropout_seed, i), */
+    uint64_t dropout_seed;          /* so the backward pass regenerates the forward pass's mask. */
+    /* optional outputs of the backward passes (the reference's FlashAttention has no backward; these complete it) */
+    float *dbq, *dbk, *dbv, *dbo;   /* bias gradients [H*W], [H*W], [H*W], [E] */
+    float *dgamma, *dbeta;          /* LayerNorm parameter gradients [E], pre_norm only */
 } ltca_tsa_params;
 
 /* which: 0 forward, 1 backward-data, 2 backward-weights, 3 both backward passes. */

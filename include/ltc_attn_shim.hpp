@@ -9,6 +9,8 @@
 //                                          backwardWeights run on the sm_100a kernels,
 //   cudatrader::createB200TimeSelfAttention the factory to call from TimeSelfAttention::create
 //                                          (src/ml/time_self_attention.cu:41-56),
+//   cudatrader::B200FlashAttention         the reference's FlashAttention module (same constructor, forward,
+//                                          weight-file and getter signatures) plus a backward pass,
 //   cudatrader::b200::flashAttention       the body of FlashAttention::flashAttention
 //                                          (src/ml/flash_attention.cu:961-1046) on un-permuted
 //                                          projection outputs, plus its backward.
@@ -297,6 +299,207 @@ private:
     bool causal_;
     CudaMemory<float> wq_, wk_, wv_, wo_, ln_gamma_, ln_beta_;
     CudaMemory<float> dwq_, dwk_, dwv_, dwo_, dgamma_, dbeta_;
+    CudaMemory<float> workspace_;
+};
+
+// The reference's FlashAttention module (include/flash_attention.h:19-260, src/ml/flash_attention.cu:485-1150)
+// on the sm_100a kernels, with the constructor, forward, weight-file and getter signatures of that class:
+//   out = dropout( x + Wo MHA(LayerNorm(x)) + bo ),  scale 1/sqrt(head_dim), scores clamped at 10,
+//   optional dense keep-mask [B,S,S]; x is [batch*seq, input_dim] with batch-major rows.
+// backward / backwardWeights are extensions with the signatures of TimeSelfAttention's
+// (include/time_self_attention.h:84-106): the reference class is forward-only.
+// Not reproduced: the reference swallows exceptions in forward and returns zeros
+// (src/ml/flash_attention.cu:1058-1061, 1144-1147); failures here are std::runtime_error.  Dropout draws
+// its mask from a hash of (seed, call counter, element index) instead of curand seeded with the wall clock
+// (:1117-1131); backward(…) regenerates the mask of the latest forward call.
+class B200FlashAttention {
+public:
+    B200FlashAttention(int input_dim, int head_dim, int num_heads, float dropout_prob = 0.0f,
+                       bool use_layer_norm = true, bool use_residual = true, bool use_mixed_precision = false,
+                       unsigned long long seed = 12345ULL, int device = 0)
+        : ctx_(device), input_dim_(input_dim), head_dim_(head_dim), num_heads_(num_heads),
+          model_dim_(head_dim * num_heads), dropout_prob_(dropout_prob), use_layer_norm_(use_layer_norm),
+          use_residual_(use_residual), use_mixed_precision_(use_mixed_precision), seed_(seed) {
+        if (input_dim <= 0 || head_dim <= 0 || num_heads <= 0)
+            throw std::invalid_argument("FlashAttention: input_dim, head_dim and num_heads must be positive");
+        if (dropout_prob < 0.0f || dropout_prob >= 1.0f)
+            throw std::invalid_argument("FlashAttention: dropout_prob must be in [0, 1)");
+        const size_t e = (size_t)input_dim_, m = (size_t)model_dim_;
+        wq_ = CudaMemory<float>(e * m); wk_ = CudaMemory<float>(e * m); wv_ = CudaMemory<float>(e * m);
+        wo_ = CudaMemory<float>(m * e);
+        bq_ = CudaMemory<float>(m); bk_ = CudaMemory<float>(m); bv_ = CudaMemory<float>(m); bo_ = CudaMemory<float>(e);
+        ln_gamma_ = CudaMemory<float>(e); ln_beta_ = CudaMemory<float>(e);
+        initializeWeights(seed);
+    }
+
+    CudaMemory<float> forward(const CudaMemory<float>& x_seq, int batch_size, int seq_len,
+                              const CudaMemory<float>* mask = nullptr, cudaStream_t stream = nullptr) {
+        CudaMemory<float> out((size_t)batch_size * seq_len * input_dim_, stream);
+        ++calls_;
+        ltca_tsa_params p = params(x_seq, batch_size, seq_len, mask);
+        p.out = out.get();
+        run(p, 0, stream, ltca_tsa_fwd, "ltca_tsa_fwd");
+        return out;
+    }
+
+    // Gradient with respect to x_seq of the latest forward call (same dropout mask).
+    CudaMemory<float> backward(const CudaMemory<float>& grad_output, const CudaMemory<float>& x_seq,
+                               int batch_size, int seq_len, const CudaMemory<float>* mask = nullptr,
+                               cudaStream_t stream = nullptr) {
+        CudaMemory<float> dx((size_t)batch_size * seq_len * input_dim_, stream);
+        ltca_tsa_params p = params(x_seq, batch_size, seq_len, mask);
+        p.dy = grad_output.get();
+        p.dx = dx.get();
+        run(p, 1, stream, ltca_tsa_bwd_data, "ltca_tsa_bwd_data");
+        return dx;
+    }
+
+    // Gradients of every parameter, kept inside the object (getComputedGradients).
+    void backwardWeights(const CudaMemory<float>& grad_output, const CudaMemory<float>& x_seq, int batch_size,
+                         int seq_len, const CudaMemory<float>* mask = nullptr, cudaStream_t stream = nullptr) {
+        ensure_gradients(stream);
+        ltca_tsa_params p = params(x_seq, batch_size, seq_len, mask);
+        p.dy = grad_output.get();
+        p.dwq = dwq_.get(); p.dwk = dwk_.get(); p.dwv = dwv_.get(); p.dwo = dwo_.get();
+        p.dbq = dbq_.get(); p.dbk = dbk_.get(); p.dbv = dbv_.get(); p.dbo = dbo_.get();
+        if (use_layer_norm_) { p.dgamma = dgamma_.get(); p.dbeta = dbeta_.get(); }
+        run(p, 2, stream, ltca_tsa_bwd_weights, "ltca_tsa_bwd_weights");
+    }
+    // Order: Wq, Wk, Wv, Wo, bq, bk, bv, bo, gamma, beta (the order of the weight file).
+    std::vector<CudaMemory<float>*> getParameters() {
+        return {&wq_, &wk_, &wv_, &wo_, &bq_, &bk_, &bv_, &bo_, &ln_gamma_, &ln_beta_};
+    }
+    std::vector<CudaMemory<float>*> getComputedGradients() {
+        ensure_gradients(nullptr);
+        return {&dwq_, &dwk_, &dwv_, &dwo_, &dbq_, &dbk_, &dbv_, &dbo_, &dgamma_, &dbeta_};
+    }
+
+    bool isTensorCoreOptimized() const {                       // src/ml/flash_attention.cu:613-615
+        return (input_dim_ % 8 == 0) && (head_dim_ % 8 == 0) && (model_dim_ % 8 == 0);
+    }
+
+    // Xavier-uniform with one limit sqrt(6 / (input_dim + model_dim)), drawn from one mt19937(seed) in the
+    // reference's order: (Wq[i], Wk[i], Wv[i]) interleaved, then Wo; biases zero, gamma one, beta zero
+    // (src/ml/flash_attention.cu:548-611).
+    void initializeWeights(unsigned long long seed = 12345ULL) {
+        std::mt19937 gen((unsigned)seed);
+        const size_t e = (size_t)input_dim_, m = (size_t)model_dim_;
+        const float limit = std::sqrt(6.0f / (float)(input_dim_ + model_dim_));
+        std::uniform_real_distribution<float> dist(-limit, limit);
+        std::vector<float> q(e * m), k(e * m), v(e * m), o(m * e);
+        for (size_t i = 0; i < e * m; ++i) { q[i] = dist(gen); k[i] = dist(gen); v[i] = dist(gen); }
+        for (size_t i = 0; i < m * e; ++i) o[i] = dist(gen);
+        std::vector<float> zm(m, 0.0f), ze(e, 0.0f), ones(e, 1.0f);
+        wq_.copyFromHost(q.data()); wk_.copyFromHost(k.data()); wv_.copyFromHost(v.data()); wo_.copyFromHost(o.data());
+        bq_.copyFromHost(zm.data()); bk_.copyFromHost(zm.data()); bv_.copyFromHost(zm.data()); bo_.copyFromHost(ze.data());
+        ln_gamma_.copyFromHost(ones.data()); ln_beta_.copyFromHost(ze.data());
+        cudaDeviceSynchronize();                      // the host vectors go out of scope
+    }
+
+    // The reference's file: input_dim, head_dim, num_heads, model_dim (int), dropout_prob (float),
+    // use_layer_norm, use_residual (bool), then Wq, Wk, Wv, Wo, bq, bk, bv, bo and, with LayerNorm, gamma and
+    // beta as fp32 (src/ml/flash_attention.cu:619-779).  Both return false on failure, as there.
+    bool saveWeights(const std::string& path) const {
+        std::ofstream f(path, std::ios::binary);
+        if (!f.is_open()) return false;
+        f.write(reinterpret_cast<const char*>(&input_dim_), sizeof(input_dim_));
+        f.write(reinterpret_cast<const char*>(&head_dim_), sizeof(head_dim_));
+        f.write(reinterpret_cast<const char*>(&num_heads_), sizeof(num_heads_));
+        f.write(reinterpret_cast<const char*>(&model_dim_), sizeof(model_dim_));
+        f.write(reinterpret_cast<const char*>(&dropout_prob_), sizeof(dropout_prob_));
+        f.write(reinterpret_cast<const char*>(&use_layer_norm_), sizeof(use_layer_norm_));
+        f.write(reinterpret_cast<const char*>(&use_residual_), sizeof(use_residual_));
+        for (const CudaMemory<float>* w : {&wq_, &wk_, &wv_, &wo_, &bq_, &bk_, &bv_, &bo_}) write_tensor(f, *w);
+        if (use_layer_norm_) { write_tensor(f, ln_gamma_); write_tensor(f, ln_beta_); }
+        return !f.fail();
+    }
+    bool loadWeights(const std::string& path) {
+        std::ifstream f(path, std::ios::binary);
+        if (!f.is_open()) return false;
+        int in = 0, hd = 0, nh = 0, md = 0;
+        float dp = 0.0f;
+        bool ln = false, res = false;
+        f.read(reinterpret_cast<char*>(&in), sizeof(in));
+        f.read(reinterpret_cast<char*>(&hd), sizeof(hd));
+        f.read(reinterpret_cast<char*>(&nh), sizeof(nh));
+        f.read(reinterpret_cast<char*>(&md), sizeof(md));
+        f.read(reinterpret_cast<char*>(&dp), sizeof(dp));
+        f.read(reinterpret_cast<char*>(&ln), sizeof(ln));
+        f.read(reinterpret_cast<char*>(&res), sizeof(res));
+        if (f.fail() || in != input_dim_ || hd != head_dim_ || nh != num_heads_ || md != model_dim_) return false;
+        for (CudaMemory<float>* w : {&wq_, &wk_, &wv_, &wo_, &bq_, &bk_, &bv_, &bo_}) read_tensor(f, *w);
+        if (use_layer_norm_ && ln) { read_tensor(f, ln_gamma_); read_tensor(f, ln_beta_); }
+        return !f.fail();
+    }
+
+    int getNumHeads() const { return num_heads_; }
+    int getHeadDim() const { return head_dim_; }
+    bool getUseLayerNorm() const { return use_layer_norm_; }
+    bool getUseResidual() const { return use_residual_; }
+    int getInputDim() const { return input_dim_; }
+    float getDropoutProb() const { return dropout_prob_; }
+    int getModelDim() const { return model_dim_; }
+
+private:
+    ltca_tsa_params params(const CudaMemory<float>& x, int B, int S, const CudaMemory<float>* mask) const {
+        ltca_tsa_params p = {};
+        p.B = B; p.S = S; p.E = input_dim_; p.H = num_heads_; p.head_width = head_dim_;
+        p.causal = 0;
+        p.time_major = 0;                                          // rows are (batch, time), flash_attention.h:52
+        p.pre_norm = 1;
+        p.use_residual = use_residual_ ? 1 : 0;
+        p.use_layer_norm = use_layer_norm_ ? 1 : 0;
+        p.mode = LTCA_MODE_AUTO;
+        p.scale = 1.0f / std::sqrt((float)head_dim_);              // flash_attention.cu:998
+        p.score_clamp = 10.0f;                                     // flash_attention.cu:167
+        p.dropout_prob = dropout_prob_;
+        p.dropout_seed = (uint64_t)seed_ * 0x100000001B3ull + calls_;
+        p.x = x.get();
+        p.wq = wq_.get(); p.wk = wk_.get(); p.wv = wv_.get(); p.wo = wo_.get();
+        p.bq = bq_.get(); p.bk = bk_.get(); p.bv = bv_.get(); p.bo = bo_.get();
+        p.ln_gamma = ln_gamma_.get(); p.ln_beta = ln_beta_.get();
+        p.keep_mask = mask ? mask->get() : nullptr;
+        return p;
+    }
+    template <typename Fn>
+    void run(ltca_tsa_params& p, int which, cudaStream_t stream, Fn fn, const char* what) {
+        size_t need = 0;
+        ltca_tsa_workspace_bytes(&p, which, &need);
+        if (need > workspace_.bytes()) workspace_ = CudaMemory<float>((need + 3) / 4, stream);
+        p.workspace = workspace_.get();
+        p.workspace_bytes = workspace_.bytes();
+        ltca_ctx* ctx = ctx_.get(stream);
+        b200::check(ctx, fn(ctx, &p), what);
+    }
+    void ensure_gradients(cudaStream_t stream) {
+        if (dwq_.size() == wq_.size() && dwq_.size() != 0) return;
+        dwq_ = CudaMemory<float>(wq_.size(), stream); dwk_ = CudaMemory<float>(wk_.size(), stream);
+        dwv_ = CudaMemory<float>(wv_.size(), stream); dwo_ = CudaMemory<float>(wo_.size(), stream);
+        dbq_ = CudaMemory<float>(bq_.size(), stream); dbk_ = CudaMemory<float>(bk_.size(), stream);
+        dbv_ = CudaMemory<float>(bv_.size(), stream); dbo_ = CudaMemory<float>(bo_.size(), stream);
+        dgamma_ = CudaMemory<float>(ln_gamma_.size(), stream); dbeta_ = CudaMemory<float>(ln_beta_.size(), stream);
+    }
+    static void write_tensor(std::ofstream& f, const CudaMemory<float>& t) {
+        std::vector<float> host(t.size());
+        t.copyToHost(host.data());
+        cudaDeviceSynchronize();
+        f.write(reinterpret_cast<const char*>(host.data()), (std::streamsize)(host.size() * sizeof(float)));
+    }
+    static void read_tensor(std::ifstream& f, CudaMemory<float>& t) {
+        std::vector<float> host(t.size());
+        f.read(reinterpret_cast<char*>(host.data()), (std::streamsize)(host.size() * sizeof(float)));
+        t.copyFromHost(host.data());
+        cudaDeviceSynchronize();
+    }
+
+    b200::Context ctx_;
+    int input_dim_, head_dim_, num_heads_, model_dim_;
+    float dropout_prob_;
+    bool use_layer_norm_, use_residual_, use_mixed_precision_;
+    unsigned long long seed_;
+    uint64_t calls_ = 0;
+    CudaMemory<float> wq_, wk_, wv_, wo_, bq_, bk_, bv_, bo_, ln_gamma_, ln_beta_;
+    CudaMemory<float> dwq_, dwk_, dwv_, dwo_, dbq_, dbk_, dbv_, dbo_, dgamma_, dbeta_;
     CudaMemory<float> workspace_;
 };
 

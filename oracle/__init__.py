@@ -256,3 +256,89 @@ def attn_bwd_numpy(q, k, v, dout, scale, causal=False, keep_mask=None, kv_len=No
     dq = np.einsum("bhij,bhjd->bhid", ds, k)
     dk = np.einsum("bhij,bhid->bhjd", ds, q)
     return dq, dk, dv
+
+
+# ----------------------------------------------------------------------------------------------
+# FlashAttention form of the module (reference src/ml/flash_attention.cu:808-1150):
+#   out = dropout( x + Wo MHA(LayerNorm(x)) + bo )
+# LayerNorm on the input (:822-834, kernel :275-377, eps 1e-5, biased variance), projections with
+# biases (:866-958), scores scaled by 1/sqrt(head_dim) (:998) and clamped at 10 (:167), keep-mask
+# (:161-164), output projection with bias (:1075-1104), residual with the raw input (:1107-1113),
+# inverted dropout last (:1117-1131).  The backward is the derivative of exactly that.
+# ----------------------------------------------------------------------------------------------
+def dropout_keep(seed: int, n: int, p: float) -> np.ndarray:
+    """Keep decisions of n elements: the hash of (seed, index) the CUDA kernel uses (splitmix64 finaliser,
+    top 24 bits as a uniform in [0, 1), keep iff u >= p)."""
+    with np.errstate(over="ignore"):
+        z = np.uint64(seed) + (np.arange(n, dtype=np.uint64) + np.uint64(1)) * np.uint64(0x9E3779B97F4A7C15)
+        z = (z ^ (z >> np.uint64(30))) * np.uint64(0xBF58476D1CE4E5B9)
+        z = (z ^ (z >> np.uint64(27))) * np.uint64(0x94D049BB133111EB)
+        z = z ^ (z >> np.uint64(31))
+    u = (z >> np.uint64(40)).astype(np.float32) * np.float32(1.0 / 16777216.0)
+    return u >= np.float32(p)
+
+
+def layer_norm_fwd(x, gamma, beta, eps=1e-5):
+    x = np.asarray(x, dtype=np.float64)
+    mean = x.mean(axis=1, keepdims=True)
+    inv_std = 1.0 / np.sqrt(((x - mean) ** 2).mean(axis=1, keepdims=True) + eps)
+    xhat = (x - mean) * inv_std
+    return xhat * np.asarray(gamma, np.float64) + np.asarray(beta, np.float64), xhat, inv_std
+
+
+def layer_norm_bwd(g, xhat, inv_std, gamma):
+    """(dx, dgamma, dbeta) for y = xhat * gamma + beta."""
+    g = np.asarray(g, dtype=np.float64)
+    gg = g * np.asarray(gamma, np.float64)
+    dx = inv_std * (gg - gg.mean(axis=1, keepdims=True) - xhat * (gg * xhat).mean(axis=1, keepdims=True))
+    return dx, (g * xhat).sum(axis=0), g.sum(axis=0)
+
+
+def fa_fwd(x, wq, wk, wv, wo, B, S, H, D, biases=(None, None, None, None), gamma=None, beta=None,
+           use_layer_norm=True, use_residual=True, keep_mask=None, dropout_prob=0.0, dropout_seed=0,
+           score_clamp=10.0):
+    x = np.asarray(x, dtype=np.float64)
+    xin = layer_norm_fwd(x, gamma, beta)[0] if use_layer_norm else x
+    bq, bk, bv, bo = biases
+    _, y = tsa_fwd(xin.astype(np.float32), wq, wk, wv, wo, B, S, H, D, 1.0 / np.sqrt(D), False, False, False, False,
+                   None, None, bq, bk, bv, bo, keep_mask, None, score_clamp)
+    out = y + x if use_residual else y
+    if dropout_prob > 0.0:
+        keep = dropout_keep(dropout_seed, out.size, dropout_prob).reshape(out.shape)
+        out = np.where(keep, out / (1.0 - dropout_prob), 0.0)
+    return out
+
+
+def fa_bwd(x, wq, wk, wv, wo, dy, B, S, H, D, biases=(None, None, None, None), gamma=None, beta=None,
+           use_layer_norm=True, use_residual=True, keep_mask=None, dropout_prob=0.0, dropout_seed=0,
+           score_clamp=10.0):
+    """Gradients of fa_fwd.  Bias gradients come out of the weight-gradient code by giving the input a column
+    of ones whose weight row is the bias."""
+    x = np.asarray(x, dtype=np.float64)
+    g = np.asarray(dy, dtype=np.float64)
+    if dropout_prob > 0.0:
+        keep = dropout_keep(dropout_seed, g.size, dropout_prob).reshape(g.shape)
+        g = np.where(keep, g / (1.0 - dropout_prob), 0.0)
+    E, HW = x.shape[1], H * D
+    if use_layer_norm:
+        xin, xhat, inv_std = layer_norm_fwd(x, gamma, beta)
+    else:
+        xin = x
+    bq, bk, bv, _ = biases
+    zeros = np.zeros(HW, np.float32)
+    aug = lambda w, b: np.concatenate([np.asarray(w, np.float32), (zeros if b is None else np.asarray(b, np.float32))[None]], 0)
+    x1 = np.concatenate([xin.astype(np.float32), np.ones((x.shape[0], 1), np.float32)], 1)
+    wo1 = np.concatenate([np.asarray(wo, np.float32), np.zeros((HW, 1), np.float32)], 1)
+    g1 = np.concatenate([g.astype(np.float32), np.zeros((x.shape[0], 1), np.float32)], 1)
+    dx1, dwq1, dwk1, dwv1, dwo1 = tsa_bwd(x1, aug(wq, bq), aug(wk, bk), aug(wv, bv), wo1, g1, B, S, H, D,
+                                          1.0 / np.sqrt(D), False, False, None, None, None, keep_mask, None,
+                                          score_clamp)
+    out = dict(dwq=dwq1[:E], dwk=dwk1[:E], dwv=dwv1[:E], dwo=dwo1[:, :E], dbq=dwq1[E], dbk=dwk1[E], dbv=dwv1[E],
+               dbo=g.sum(axis=0))
+    dxin = dx1[:, :E]
+    if use_layer_norm:
+        dx, out["dgamma"], out["dbeta"] = layer_norm_bwd(dxin, xhat, inv_std, gamma)
+    else:
+        dx = dxin
+    out["dx"] = dx + g if use_residual else dx
+    return out

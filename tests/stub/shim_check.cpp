@@ -24,3 +24,17 @@ CudaMemory<float> core(const b200::Context& c, const CudaMemory<float>& q, const
                        const CudaMemory<float>& v, CudaMemory<float>& lse) {
     return b200::flashAttention(c, q, k, v, 2, 8, 2, 16, nullptr, nullptr, &lse);
 }
+
+CudaMemory<float> flash_module(const CudaMemory<float>& x, const CudaMemory<float>& dy, const CudaMemory<float>& mask) {
+    B200FlashAttention fa(32, 16, 2, 0.1f, true, true, false, 12345ULL);
+    CudaMemory<float> y = fa.forward(x, 2, 8, &mask);
+    fa.backwardWeights(dy, x, 2, 8, &mask);
+    CudaMemory<float> dx = fa.backward(dy, x, 2, 8, &mask);
+    (void)fa.getParameters();
+    (void)fa.getComputedGradients();
+    (void)fa.isTensorCoreOptimized();
+    if (!fa.saveWeights("fa.bin") || !fa.loadWeights("fa.bin")) return y;
+    (void)(fa.getNumHeads() + fa.getHeadDim() + fa.getInputDim() + fa.getModelDim());
+    (void)(fa.getUseLayerNorm() && fa.getUseResidual() && fa.getDropoutProb() > 0.f);
+    return dx;
+}
