@@ -14,10 +14,14 @@
 // so no operand is ever transposed in memory: the instruction descriptor's major bits select the
 // form and the shared-memory descriptors follow the layout the TMA boxes produce.
 //
-// One CTA computes one 128 x 128 tile of C: warp 0 is the TMA producer (ring of kStages
-// (A, B) stage pairs, 32 KB each; two CTAs per SM), warp 1 issues the MMAs and owns the 128 tensor-memory columns,
-// warps 2-5 are the epilogue (one accumulator row per thread: tcgen05.ld, bias, convert, store).
-// grid.z runs independent problems (Q, K and V projections share one launch) and/or splits K
+// Persistent CTAs (one per SM) walk a list of 128 x 256 tiles of C: warp 0 is the TMA producer (ring of three
+// 48 KB (A, B) stages), warp 1 issues the MMAs (M128 N256 K16) into one of two 256-column accumulators in tensor
+// memory, warps 2-5 are the epilogue (one accumulator row per thread: tcgen05.ld, bias, convert; the tile is
+// staged in shared memory as 128-byte-swizzled boxes and stored with TMA), which works on tile i while the MMAs
+// of tile i+1 run.  Measured at the module's sizes the kernel is bound by operand traffic from L2 (6.3 TB/s at
+// 27 % tensor-pipe activity for the fused Q/K/V projection: every 128-row block of A is re-read once per N tile
+// and every weight matrix once per M tile), which is why the tile is 256 wide.
+// The tile list runs over independent problems (Q, K and V projections share one launch) and/or splits of K
 // (weight gradients: K = batch x time is long and M x N is small, so the K range is cut into
 // slices whose partial tiles go to scratch and are summed in a fixed order by a second kernel).
 // `n_sum` > 1 accumulates several operand pairs into one tile (dx = dq Wq^T + dk Wk^T + dv Wv^T).
@@ -29,19 +33,24 @@ namespace ltca {
 
 namespace {
 
-constexpr int kBM = 128, kBN = 128, kBK = 64;
-constexpr int kStages = 3;                         // 96 KB of operand ring: two CTAs share an SM, so one
-                                                   // CTA's prologue and epilogue overlap the other's MMAs
-constexpr int kTileBytes = 128 * kBK * 2;          // 16 KB per operand per stage
+constexpr int kBM = 128, kBN = 256, kBK = 64;
+constexpr int kStages = 3;                         // operand ring: 3 x (16 KB of A + 32 KB of B)
+constexpr int kATileBytes = kBM * kBK * 2;         // 16 KB
+constexpr int kBTileBytes = kBN * kBK * 2;         // 32 KB
+constexpr int kStageBytes = kATileBytes + kBTileBytes;
+constexpr int kStageOutBytes = kBM * 128 * 4;      // 64 KB: the result tile leaves in pieces of 128 fp32 / 256 bf16 columns
 constexpr int kGemmThreads = 192;
-constexpr int kBarOff = kStages * 2 * kTileBytes;
-constexpr int kNumBars = 2 * kStages + 1;
+constexpr int kOutOff = kStages * kStageBytes;
+constexpr int kBarOff = kOutOff + kStageOutBytes;
+constexpr int kNumBars = 2 * kStages + 4;          // full[S], empty[S], acc_full[2], acc_empty[2]
 constexpr int kMiscOff = kBarOff + kNumBars * 8;
 constexpr int kDynBytes = kMiscOff + 16 + 1024;
+constexpr uint32_t kAccCols = 2 * kBN;             // two accumulators
 
 struct GemmKArgs {
     int M, N, K;
     int n_sum, ksplit;
+    int tiles_x, tiles_y, tiles_z;   // N tiles, M tiles, problems x K slices
     int64_t ldc;
     int out_bf16;
     int tma_store;           // results leave through shared memory and a TMA store (needs 16-byte aligned rows)
@@ -51,8 +60,35 @@ struct GemmKArgs {
     uint32_t* status;
 };
 
+// One tile of the work list of a CTA.
+struct GemmTile {
+    int m0, n0, problem, slice, kb_begin, kb_end, pair_begin, n_pairs, n_iters;
+};
+__device__ __forceinline__ GemmTile gemm_tile(const GemmKArgs& g, int linear) {
+    GemmTile t;
+    const int x = linear % g.tiles_x;
+    const int yz = linear / g.tiles_x;
+    const int y = yz % g.tiles_y, z = yz / g.tiles_y;
+    t.n0 = x * kBN;
+    t.m0 = y * kBM;
+    t.problem = z / g.ksplit;
+    t.slice = z % g.ksplit;
+    const int nkb = (g.K + kBK - 1) / kBK;
+    const int per = (nkb + g.ksplit - 1) / g.ksplit;
+    t.kb_begin = min(t.slice * per, nkb);
+    t.kb_end = min(t.kb_begin + per, nkb);
+    t.pair_begin = g.n_sum > 1 ? 0 : t.problem;
+    t.n_pairs = g.n_sum > 1 ? g.n_sum : 1;
+    t.n_iters = t.n_pairs * (t.kb_end - t.kb_begin);
+    return t;
+}
+
+// Persistent: CTA c computes tiles c, c + gridDim.x, ... of the list (N tiles fastest, so neighbouring CTAs
+// share their rows of A in L2).  The two accumulators alternate: while the epilogue warps read tile i out of
+// tensor memory, convert it and hand it to the TMA store, the MMA thread is already accumulating tile i+1 and
+// the producer is loading tile i+2's operands.
 template <bool kAMn, bool kBMn>
-__global__ void __launch_bounds__(kGemmThreads, 2)
+__global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap ta0, const __grid_constant__ CUtensorMap ta1,
                        const __grid_constant__ CUtensorMap ta2, const __grid_constant__ CUtensorMap tb0,
                        const __grid_constant__ CUtensorMap tb1, const __grid_constant__ CUtensorMap tb2,
@@ -62,31 +98,24 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap ta0, const __grid_con
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
     const uint32_t bar_base = smem_base + kBarOff;
-    auto a_smem = [&](int s) { return smem_base + (uint32_t)(s * 2 * kTileBytes); };
-    auto b_smem = [&](int s) { return smem_base + (uint32_t)(s * 2 * kTileBytes + kTileBytes); };
+    auto a_smem = [&](int s) { return smem_base + (uint32_t)(s * kStageBytes); };
+    auto b_smem = [&](int s) { return smem_base + (uint32_t)(s * kStageBytes + kATileBytes); };
     auto bar_full = [&](int s) { return bar_base + 8u * s; };
     auto bar_empty = [&](int s) { return bar_base + 8u * (kStages + s); };
-    const uint32_t bar_acc = bar_base + 8u * (2 * kStages);
+    auto bar_acc_full = [&](int b) { return bar_base + 8u * (2 * kStages + b); };
+    auto bar_acc_empty = [&](int b) { return bar_base + 8u * (2 * kStages + 2 + b); };
     volatile uint32_t* misc = reinterpret_cast<volatile uint32_t*>(smem_gen + kMiscOff);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = blockIdx.x * kBN, m0 = blockIdx.y * kBM;
-    const int problem = blockIdx.z / g.ksplit, slice = blockIdx.z % g.ksplit;
-    // this CTA's range of 64-wide K blocks
-    const int nkb = (g.K + kBK - 1) / kBK;
-    const int per = (nkb + g.ksplit - 1) / g.ksplit;
-    const int kb_begin = min(slice * per, nkb), kb_end = min(kb_begin + per, nkb);
-    const int pair_begin = g.n_sum > 1 ? 0 : problem;
-    const int n_pairs = g.n_sum > 1 ? g.n_sum : 1;
-    const int n_iters = n_pairs * (kb_end - kb_begin);
+    const int n_tiles = g.tiles_x * g.tiles_y * g.tiles_z;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_empty(s), 1); }
-        mbar_init(bar_acc, 1);
+        for (int b = 0; b < 2; ++b) { mbar_init(bar_acc_full(b), 1); mbar_init(bar_acc_empty(b), 4); }
         misc[1] = 0u;
         mbar_fence_init();
     }
-    if (warp == 1) { tmem_alloc(smem_u32(const_cast<uint32_t*>(&misc[0])), 128); tmem_relinquish(); }
+    if (warp == 1) { tmem_alloc(smem_u32(const_cast<uint32_t*>(&misc[0])), kAccCols); tmem_relinquish(); }
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
@@ -95,30 +124,37 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap ta0, const __grid_con
 
     if (warp == 0) {
         if (lane == 0) {
+            tma_prefetch_desc(&ta0);
+            tma_prefetch_desc(&tb0);
             bool ok = true;
             int it = 0;
-            for (int p = 0; p < n_pairs && ok; ++p) {
-                const int pair = pair_begin + p;
-                const CUtensorMap* ta = pair == 0 ? &ta0 : (pair == 1 ? &ta1 : &ta2);
-                const CUtensorMap* tb = pair == 0 ? &tb0 : (pair == 1 ? &tb1 : &tb2);
-                if (it == 0) { tma_prefetch_desc(ta); tma_prefetch_desc(tb); }
-                for (int kb = kb_begin; kb < kb_end; ++kb, ++it) {
-                    const int s = it % kStages;
-                    ok = mbar_wait(bar_empty(s), (uint32_t)(((it / kStages) & 1) ^ 1), wc, 0xd0);
-                    if (!ok) break;
-                    mbar_arrive_expect_tx(bar_full(s), 2u * kTileBytes);
-                    const int k0 = kb * kBK;
-                    if (kAMn) {
-                        tma_load_4d(a_smem(s), ta, bar_full(s), m0, k0, 0, 0);
-                        tma_load_4d(a_smem(s) + kTileBytes / 2, ta, bar_full(s), m0 + 64, k0, 0, 0);
-                    } else {
-                        tma_load_4d(a_smem(s), ta, bar_full(s), k0, m0, 0, 0);
-                    }
-                    if (kBMn) {
-                        tma_load_4d(b_smem(s), tb, bar_full(s), n0, k0, 0, 0);
-                        tma_load_4d(b_smem(s) + kTileBytes / 2, tb, bar_full(s), n0 + 64, k0, 0, 0);
-                    } else {
-                        tma_load_4d(b_smem(s), tb, bar_full(s), k0, n0, 0, 0);
+            for (int lin = blockIdx.x; lin < n_tiles && ok; lin += gridDim.x) {
+                const GemmTile t = gemm_tile(g, lin);
+                for (int p = 0; p < t.n_pairs && ok; ++p) {
+                    const int pair = t.pair_begin + p;
+                    const CUtensorMap* ta = pair == 0 ? &ta0 : (pair == 1 ? &ta1 : &ta2);
+                    const CUtensorMap* tb = pair == 0 ? &tb0 : (pair == 1 ? &tb1 : &tb2);
+                    for (int kb = t.kb_begin; kb < t.kb_end; ++kb, ++it) {
+                        const int s = it % kStages;
+                        ok = mbar_wait(bar_empty(s), (uint32_t)(((it / kStages) & 1) ^ 1), wc, 0xd0);
+                        if (!ok) break;
+                        mbar_arrive_expect_tx(bar_full(s), (uint32_t)kStageBytes);
+                        const int k0 = kb * kBK;
+                        if (kAMn) {
+                            tma_load_4d(a_smem(s), ta, bar_full(s), t.m0, k0, 0, 0);
+                            tma_load_4d(a_smem(s) + 8192, ta, bar_full(s), t.m0 + 64, k0, 0, 0);
+                        } else {
+                            tma_load_4d(a_smem(s), ta, bar_full(s), k0, t.m0, 0, 0);
+                        }
+                        if (kBMn) {
+#pragma unroll
+                            for (int pn = 0; pn < kBN / 64; ++pn)     // 64-column blocks of 64 K rows, 8 KB each
+                                tma_load_4d(b_smem(s) + pn * 8192, tb, bar_full(s), t.n0 + 64 * pn, k0, 0, 0);
+                        } else {
+                            // 256 rows of 128 bytes, as two boxes of 128 rows
+                            tma_load_4d(b_smem(s), tb, bar_full(s), k0, t.n0, 0, 0);
+                            tma_load_4d(b_smem(s) + kBTileBytes / 2, tb, bar_full(s), k0, t.n0 + 128, 0, 0);
+                        }
                     }
                 }
             }
@@ -129,157 +165,153 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap ta0, const __grid_con
             // K-major tile: 128 rows of 128 bytes, 8-row groups 1024 bytes apart, 32 bytes per K step.
             // MN-major tile: two blocks of 64 columns, 8192 bytes apart, each 64 K rows of 128 bytes;
             // a K step of 16 rows advances 2048 bytes.
-            const uint64_t a_desc0 = kAMn ? make_smem_desc_sw128(a_smem(0), kTileBytes / 2, 1024)
+            const uint64_t a_desc0 = kAMn ? make_smem_desc_sw128(a_smem(0), 8192, 1024)
                                           : make_smem_desc_sw128(a_smem(0), 16, 1024);
-            const uint64_t b_desc0 = kBMn ? make_smem_desc_sw128(b_smem(0), kTileBytes / 2, 1024)
+            const uint64_t b_desc0 = kBMn ? make_smem_desc_sw128(b_smem(0), 8192, 1024)
                                           : make_smem_desc_sw128(b_smem(0), 16, 1024);
             constexpr uint64_t a_step = kAMn ? 128 : 2, b_step = kBMn ? 128 : 2;
             bool ok = true;
-            for (int it = 0; it < n_iters && ok; ++it) {
-                const int s = it % kStages;
-                ok = mbar_wait(bar_full(s), (uint32_t)((it / kStages) & 1), wc, 0xd1);
+            int it = 0, na = 0;                         // ring position; tiles that used an accumulator
+            for (int lin = blockIdx.x; lin < n_tiles && ok; lin += gridDim.x) {
+                const GemmTile t = gemm_tile(g, lin);
+                if (t.n_iters == 0) continue;
+                const int buf = na & 1;
+                // the epilogue has read this accumulator's previous tile out
+                ok = mbar_wait(bar_acc_empty(buf), (uint32_t)(((na >> 1) & 1) ^ 1), wc, 0xd3);
                 if (!ok) break;
-                tc_fence_after_sync();
-                const uint64_t ad = a_desc0 + (uint64_t)((s * 2 * kTileBytes) >> 4);
-                const uint64_t bd = b_desc0 + (uint64_t)((s * 2 * kTileBytes) >> 4);
+                const uint32_t acc = tmem_base + (uint32_t)kBN * buf;
+                for (int i = 0; i < t.n_iters && ok; ++i, ++it) {
+                    const int s = it % kStages;
+                    ok = mbar_wait(bar_full(s), (uint32_t)((it / kStages) & 1), wc, 0xd1);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    const uint64_t ad = a_desc0 + (uint64_t)((s * kStageBytes) >> 4);
+                    const uint64_t bd = b_desc0 + (uint64_t)((s * kStageBytes) >> 4);
 #pragma unroll
-                for (int k = 0; k < kBK / 16; ++k)
-                    mma_ss(tmem_base, ad + a_step * k, bd + b_step * k, idesc, (it > 0 || k > 0) ? 1u : 0u);
-                mma_commit(bar_empty(s));
+                    for (int k = 0; k < kBK / 16; ++k)
+                        mma_ss(acc, ad + a_step * k, bd + b_step * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+                    mma_commit(bar_empty(s));
+                }
+                if (ok) mma_commit(bar_acc_full(buf));
+                ++na;
             }
-            if (ok && n_iters > 0) mma_commit(bar_acc);
         }
     } else {
         // epilogue: warp w reads the 32 accumulator rows of its lane quarter (w % 4)
         const int qd = warp & 3;
         const int row = qd * 32 + lane;
-        const int gm = m0 + row;
+        uint8_t* stage = smem_gen + kOutOff;
+        const uint32_t stage_addr = smem_base + kOutOff;
+        const int box_cols = g.out_bf16 ? 64 : 32;
         bool ok = true;
-        if (n_iters > 0) {
-            ok = mbar_wait_warp(bar_acc, 0u, wc, 0xd2);
-            tc_fence_after_sync();
-        }
-        const uint32_t tacc = tmem_base + ((uint32_t)(qd * 32) << 16);
-        const float* bias = (g.ksplit == 1) ? g.bias[problem] : nullptr;
-        if (g.tma_store && g.ksplit == 1) {
-            // The tile goes to shared memory (the operand ring is idle by now) in the layout of 128-byte
-            // swizzled TMA boxes - 64 bf16 or 32 fp32 columns wide, 128 rows - and one thread stores the boxes;
-            // the tensor map clips rows and columns past the end of C.  (Storing a row's 16-byte pieces
-            // straight from registers costs 32 L1 wavefronts per instruction, about as many cycles per tile
-            // as its MMAs.)
-            uint8_t* stage = smem_gen;
-            const int box_cols = g.out_bf16 ? 64 : 32;
+        int na = 0;
+        for (int lin = blockIdx.x; lin < n_tiles; lin += gridDim.x) {
+            const GemmTile t = gemm_tile(g, lin);
+            const int gm = t.m0 + row;
+            const int buf = na & 1;
+            const bool have = t.n_iters > 0;
+            if (have) {
+                if (ok) ok = mbar_wait_warp(bar_acc_full(buf), (uint32_t)((na >> 1) & 1), wc, 0xd2);
+                tc_fence_after_sync();
+                ++na;
+            }
+            const uint32_t tacc = tmem_base + (uint32_t)kBN * buf + ((uint32_t)(qd * 32) << 16);
+            const float* bias = (g.ksplit == 1) ? g.bias[t.problem] : nullptr;
+            const bool staged = g.tma_store && g.ksplit == 1;
+            // The tile leaves in pieces that fit the 64 KB staging area: all 256 bf16 columns at once, or two
+            // pieces of 128 fp32 columns.  A piece goes to shared memory in the layout of 128-byte swizzled TMA
+            // boxes - 64 bf16 or 32 fp32 columns wide, 128 rows - and one thread stores the boxes; the tensor map
+            // clips rows and columns past the end of C.  (Storing a row's 16-byte pieces straight from registers
+            // costs 32 L1 wavefronts per instruction, about as many cycles per tile as its MMAs.)
+            const int piece_cols = (staged && !g.out_bf16) ? 128 : kBN;
+            for (int p0 = 0; p0 < kBN; p0 += piece_cols) {
+                if (staged) {
+                    // the previous piece's boxes have been read: the storing thread waits for that before it comes here
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                }
 #pragma unroll 1
-            for (int c0 = 0; c0 < kBN; c0 += 32) {
-                uint32_t v[32];
-                __syncwarp();
-                if (n_iters > 0 && ok) {
-                    tmem_ld32(tacc + c0, v);
-                    tmem_wait_ld();
-                } else {
+                for (int c0 = p0; c0 < p0 + piece_cols; c0 += 32) {
+                    uint32_t v[32];
+                    __syncwarp();
+                    if (have && ok) {
+                        tmem_ld32(tacc + c0, v);
+                        tmem_wait_ld();
+                    } else {
 #pragma unroll
-                    for (int c = 0; c < 32; ++c) v[c] = 0u;
-                }
-                if (bias) {
-#pragma unroll
-                    for (int c = 0; c < 32; ++c)
-                        if (n0 + c0 + c < g.N) v[c] = __float_as_uint(__uint_as_float(v[c]) + __ldg(bias + n0 + c0 + c));
-                }
-                if (g.out_bf16) {
-                    uint8_t* box = stage + (c0 / 64) * (kBM * 128) + row * 128;
-                    const int ch0 = (c0 % 64) / 8;
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        uint4 w;
-                        w.x = pack_bf16x2(__uint_as_float(v[8 * c + 0]), __uint_as_float(v[8 * c + 1]));
-                        w.y = pack_bf16x2(__uint_as_float(v[8 * c + 2]), __uint_as_float(v[8 * c + 3]));
-                        w.z = pack_bf16x2(__uint_as_float(v[8 * c + 4]), __uint_as_float(v[8 * c + 5]));
-                        w.w = pack_bf16x2(__uint_as_float(v[8 * c + 6]), __uint_as_float(v[8 * c + 7]));
-                        *reinterpret_cast<uint4*>(box + (((ch0 + c) ^ (row & 7)) << 4)) = w;
+                        for (int c = 0; c < 32; ++c) v[c] = 0u;
                     }
-                } else {
-                    uint8_t* box = stage + (c0 / 32) * (kBM * 128) + row * 128;
-#pragma unroll
-                    for (int c = 0; c < 8; ++c)
-                        *reinterpret_cast<uint4*>(box + ((c ^ (row & 7)) << 4)) =
-                            make_uint4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
-                }
-            }
-            fence_proxy_async_smem();
-            asm volatile("bar.sync 1, 128;" ::: "memory");        // the four epilogue warps
-            if (warp == 2 && lane == 0) {
-                const CUtensorMap* tc = problem == 0 ? &tc0 : (problem == 1 ? &tc1 : &tc2);
-                const int n_boxes = kBN / box_cols;
-                for (int bx = 0; bx < n_boxes; ++bx)
-                    if (n0 + bx * box_cols < g.N)
-                        tma_store_4d(tc, smem_base + bx * (kBM * 128), n0 + bx * box_cols, m0, 0, 0);
-                tma_store_commit();
-                tma_store_wait_read<0>();
-            }
-        } else
-#pragma unroll 1
-        for (int c0 = 0; c0 < kBN && ok; c0 += 32) {
-            uint32_t v[32];
-            __syncwarp();
-            if (n_iters > 0) {
-                tmem_ld32(tacc + c0, v);
-                tmem_wait_ld();
-            } else {
-#pragma unroll
-                for (int c = 0; c < 32; ++c) v[c] = 0u;
-            }
-            const int gn0 = n0 + c0;
-            if (gm >= g.M || gn0 >= g.N) continue;
-            if (bias) {
-#pragma unroll
-                for (int c = 0; c < 32; ++c)
-                    if (gn0 + c < g.N) v[c] = __float_as_uint(__uint_as_float(v[c]) + __ldg(bias + gn0 + c));
-            }
-            const bool full = gn0 + 32 <= g.N;
-            if (g.ksplit > 1) {
-                float* dst = g.partial + (((int64_t)problem * g.ksplit + slice) * g.M + gm) * g.N + gn0;
-                if (full && (g.N & 3) == 0) {
-#pragma unroll
-                    for (int c = 0; c < 32; c += 4)
-                        *reinterpret_cast<uint4*>(dst + c) = make_uint4(v[c], v[c + 1], v[c + 2], v[c + 3]);
-                } else {
-                    {
-#pragma unroll
-                    for (int c = 0; c < 32; ++c)
-                        if (gn0 + c < g.N) dst[c] = __uint_as_float(v[c]);
-                }
-                }
-            } else if (g.out_bf16) {
-                __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(g.C[problem]) + (int64_t)gm * g.ldc + gn0;
-                if (full && (g.ldc & 7) == 0 && (reinterpret_cast<uintptr_t>(g.C[problem]) & 15) == 0) {
-#pragma unroll
-                    for (int c = 0; c < 32; c += 8) {
-                        uint4 w;
-                        w.x = pack_bf16x2(__uint_as_float(v[c]), __uint_as_float(v[c + 1]));
-                        w.y = pack_bf16x2(__uint_as_float(v[c + 2]), __uint_as_float(v[c + 3]));
-                        w.z = pack_bf16x2(__uint_as_float(v[c + 4]), __uint_as_float(v[c + 5]));
-                        w.w = pack_bf16x2(__uint_as_float(v[c + 6]), __uint_as_float(v[c + 7]));
-                        *reinterpret_cast<uint4*>(dst + c) = w;
+                    if (have && c0 + 32 == kBN) {
+                        // the accumulator is in registers: the MMA thread may start the tile after next in it
+                        tc_fence_before_sync();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(bar_acc_empty(buf));
                     }
-                } else {
-                    {
+                    const int gn0 = t.n0 + c0;
+                    if (bias) {
 #pragma unroll
-                    for (int c = 0; c < 32; ++c)
-                        if (gn0 + c < g.N) dst[c] = __float2bfloat16_rn(__uint_as_float(v[c]));
-                }
-                }
-            } else {
-                float* dst = reinterpret_cast<float*>(g.C[problem]) + (int64_t)gm * g.ldc + gn0;
-                if (full && (g.ldc & 3) == 0 && (reinterpret_cast<uintptr_t>(g.C[problem]) & 15) == 0) {
+                        for (int c = 0; c < 32; ++c)
+                            if (gn0 + c < g.N) v[c] = __float_as_uint(__uint_as_float(v[c]) + __ldg(bias + gn0 + c));
+                    }
+                    if (staged) {
+                        const int cp = c0 - p0;                 // column inside the piece
+                        if (g.out_bf16) {
+                            uint8_t* box = stage + (cp / 64) * (kBM * 128) + row * 128;
+                            const int ch0 = (cp % 64) / 8;
 #pragma unroll
-                    for (int c = 0; c < 32; c += 4)
-                        *reinterpret_cast<uint4*>(dst + c) = make_uint4(v[c], v[c + 1], v[c + 2], v[c + 3]);
-                } else {
-                    {
+                            for (int c = 0; c < 4; ++c) {
+                                uint4 w;
+                                w.x = pack_bf16x2(__uint_as_float(v[8 * c + 0]), __uint_as_float(v[8 * c + 1]));
+                                w.y = pack_bf16x2(__uint_as_float(v[8 * c + 2]), __uint_as_float(v[8 * c + 3]));
+                                w.z = pack_bf16x2(__uint_as_float(v[8 * c + 4]), __uint_as_float(v[8 * c + 5]));
+                                w.w = pack_bf16x2(__uint_as_float(v[8 * c + 6]), __uint_as_float(v[8 * c + 7]));
+                                *reinterpret_cast<uint4*>(box + (((ch0 + c) ^ (row & 7)) << 4)) = w;
+                            }
+                        } else {
+                            uint8_t* box = stage + (cp / 32) * (kBM * 128) + row * 128;
 #pragma unroll
-                    for (int c = 0; c < 32; ++c)
-                        if (gn0 + c < g.N) dst[c] = __uint_as_float(v[c]);
+                            for (int c = 0; c < 8; ++c)
+                                *reinterpret_cast<uint4*>(box + ((c ^ (row & 7)) << 4)) =
+                                    make_uint4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+                        }
+                        continue;
+                    }
+                    if (gm >= g.M || gn0 >= g.N) continue;
+                    const bool full = gn0 + 32 <= g.N;
+                    if (g.ksplit > 1) {
+                        float* dst = g.partial + (((int64_t)t.problem * g.ksplit + t.slice) * g.M + gm) * g.N + gn0;
+                        if (full && (g.N & 3) == 0) {
+#pragma unroll
+                            for (int c = 0; c < 32; c += 4)
+                                *reinterpret_cast<uint4*>(dst + c) = make_uint4(v[c], v[c + 1], v[c + 2], v[c + 3]);
+                        } else {
+#pragma unroll
+                            for (int c = 0; c < 32; ++c)
+                                if (gn0 + c < g.N) dst[c] = __uint_as_float(v[c]);
+                        }
+                    } else if (g.out_bf16) {
+                        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(g.C[t.problem]) + (int64_t)gm * g.ldc + gn0;
+#pragma unroll
+                        for (int c = 0; c < 32; ++c)
+                            if (gn0 + c < g.N) dst[c] = __float2bfloat16_rn(__uint_as_float(v[c]));
+                    } else {
+                        float* dst = reinterpret_cast<float*>(g.C[t.problem]) + (int64_t)gm * g.ldc + gn0;
+#pragma unroll
+                        for (int c = 0; c < 32; ++c)
+                            if (gn0 + c < g.N) dst[c] = __uint_as_float(v[c]);
+                    }
                 }
+                if (staged) {
+                    fence_proxy_async_smem();
+                    asm volatile("bar.sync 1, 128;" ::: "memory");    // the four epilogue warps have staged their rows
+                    if (warp == 2 && lane == 0) {
+                        const CUtensorMap* tc = t.problem == 0 ? &tc0 : (t.problem == 1 ? &tc1 : &tc2);
+                        const int n_boxes = piece_cols / box_cols;
+                        for (int bx = 0; bx < n_boxes; ++bx)
+                            if (t.n0 + p0 + bx * box_cols < g.N)
+                                tma_store_4d(tc, stage_addr + bx * (kBM * 128), t.n0 + p0 + bx * box_cols, t.m0, 0, 0);
+                        tma_store_commit();
+                        tma_store_wait_read<0>();
+                    }
                 }
             }
         }
@@ -291,7 +323,7 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap ta0, const __grid_con
         __syncwarp();
         if (misc[1]) __nanosleep(200000);    // aborted: give copies and MMAs in flight time to land
         tc_fence_after_sync();
-        tmem_dealloc(tmem_base, 128);
+        tmem_dealloc(tmem_base, kAccCols);
     }
 }
 
@@ -412,7 +444,12 @@ int gemm_sm100(ltca_ctx* ctx, const GemmProblem& gp) {
         for (int i = 0; i < gp.n_problems; ++i)
             if (gp.bias[i]) return fail(ctx, LTCA_ERR_INVALID, "gemm: split K takes no bias");
     }
-    dim3 grid((gp.N + kBN - 1) / kBN, (gp.M + kBM - 1) / kBM, gp.n_problems * g.ksplit);
+    g.tiles_x = (gp.N + kBN - 1) / kBN;
+    g.tiles_y = (gp.M + kBM - 1) / kBM;
+    g.tiles_z = gp.n_problems * g.ksplit;
+    const int64_t n_tiles = (int64_t)g.tiles_x * g.tiles_y * g.tiles_z;
+    const int sms = ctx->sm_count > 0 ? ctx->sm_count : 148;
+    dim3 grid((unsigned)(n_tiles < sms ? n_tiles : sms));
     const bool amn = gp.a[0].mn_major != 0, bmn = gp.b[0].mn_major != 0;
     auto launch = [&](auto kern) -> int {
         LTCA_CUDA_OK(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kDynBytes));
