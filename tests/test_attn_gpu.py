@@ -278,6 +278,39 @@ def test_tensor_pipe_backward(ctx, case, storage):
             assert rel_l2(gh, r) < 2 * TC_REL_L2, f"{name}: rel-L2 {rel_l2(gh, r)}"
 
 
+def test_tensor_pipe_backward_full_size(ctx):
+    """Config 3 (B=8 H=16 S=4096 D=64 causal bf16) at full size, backward: two (batch, head) pairs against the
+    oracle, bit-identical repeat, and two size-independent properties - the gradient of the last key's value row
+    is (its attention weight from the last query) x dO of that query alone, and dO = 0 for one head gives zero
+    gradients for that head only."""
+    B, H, S, D = 8, 16, 4096, 64
+    g = torch.Generator(device="cuda").manual_seed(5)
+    mk = lambda: (torch.randn((B, H, S, D), generator=g, device="cuda") * 0.5).bfloat16()
+    q, k, v, do = mk(), mk(), mk(), mk()
+    do[2, 3] = 0
+    o, lse = ctx.attn_fwd(q, k, v, causal=True, mode=_lib.MODE_BF16)
+    dq, dk, dv = ctx.attn_bwd(q, k, v, o, lse, do, causal=True, mode=_lib.MODE_AUTO)
+    dq2, dk2, dv2 = ctx.attn_bwd(q, k, v, o, lse, do, causal=True, mode=_lib.MODE_AUTO)
+    torch.cuda.synchronize()
+    assert ctx.device_status() == 0
+    assert torch.equal(dq, dq2) and torch.equal(dk, dk2) and torch.equal(dv, dv2)
+    for t in (dq, dk, dv):
+        assert (t[2, 3] == 0).all() and (t[2, 4] != 0).any()
+    # the last key is seen by the last query only: dV[S-1] = P[S-1, S-1] * dO[S-1]
+    s_last = (q[:, :, -1].float() * k[:, :, -1].float()).sum(-1) / 8.0
+    p_last = torch.exp(s_last - lse[:, :, -1])
+    want = p_last[..., None] * do[:, :, -1].float()
+    assert (dv[:, :, -1].float() - want).abs().max().item() < 2e-3
+    for (b, h) in ((0, 0), (7, 15)):
+        qs, ks, vs, gs = (t[b:b + 1, h:h + 1].float().cpu().numpy() for t in (q, k, v, do))
+        ref = oracle.attn_bwd(qs, ks, vs, gs, 0.125, True)
+        for name, got, r in zip(("dq", "dk", "dv"), (dq, dk, dv), ref):
+            gh = got[b, h].float().cpu().numpy()[None, None].astype(np.float64)
+            mag = max(1.0, float(np.abs(r).max()))
+            assert (np.abs(gh - r) <= TC_MAX_ABS * mag + np.abs(r) * 2.0 ** -8).all(), name
+            assert rel_l2(gh, r) < 2 * (TC_REL_L2 + 2.0 ** -9), name
+
+
 def test_host_step_pipeline_matches_direct_calls(ctx):
     """Operands in pinned host memory, results back to pinned host memory, three overlapping steps:
     the same bits as the direct device-buffer calls."""
