@@ -40,6 +40,8 @@ struct GemmArgs {
     int M, N, K;
     int lda, ldb, ldc;
     int ta, tb, accumulate;
+    int kper;          // contraction extent one CTA covers (blockIdx.z selects the slice)
+    float* partial;    // [gridDim.z][M][N] slice results when the contraction is split, else null
 };
 
 // Exact-mode projection GEMM (fp32 FMA, the arithmetic of the reference's cublasSgemm with tensor cores
@@ -51,6 +53,8 @@ __global__ void __launch_bounds__(256) gemm_fp32_kernel(const GemmArgs g) {
     __shared__ __align__(16) float Bs[kGK][kGT + kGP];
     const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
     const int m0 = blockIdx.y * kGT, n0 = blockIdx.x * kGT;
+    const int kbeg = blockIdx.z * g.kper;
+    const int kend = min(g.K, kbeg + g.kper);
     float acc[8][8];
 #pragma unroll
     for (int i = 0; i < 8; ++i)
@@ -68,7 +72,7 @@ __global__ void __launch_bounds__(256) gemm_fp32_kernel(const GemmArgs g) {
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
                 const int gk = k0 + kk + e;
-                ra[e] = (gm < g.M && gk < g.K) ? __ldg(g.A + (int64_t)gm * g.lda + gk) : 0.f;
+                ra[e] = (gm < g.M && gk < kend) ? __ldg(g.A + (int64_t)gm * g.lda + gk) : 0.f;
             }
         } else {
             const int kk = threadIdx.x >> 4, c = (threadIdx.x & 15) * 8;
@@ -76,7 +80,7 @@ __global__ void __launch_bounds__(256) gemm_fp32_kernel(const GemmArgs g) {
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
                 const int gm = m0 + c + e;
-                ra[e] = (gm < g.M && gk < g.K) ? __ldg(g.A + (int64_t)gk * g.lda + gm) : 0.f;
+                ra[e] = (gm < g.M && gk < kend) ? __ldg(g.A + (int64_t)gk * g.lda + gm) : 0.f;
             }
         }
         if (g.tb) {
@@ -85,7 +89,7 @@ __global__ void __launch_bounds__(256) gemm_fp32_kernel(const GemmArgs g) {
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
                 const int gk = k0 + kk + e;
-                rb[e] = (gn < g.N && gk < g.K) ? __ldg(g.B + (int64_t)gn * g.ldb + gk) : 0.f;
+                rb[e] = (gn < g.N && gk < kend) ? __ldg(g.B + (int64_t)gn * g.ldb + gk) : 0.f;
             }
         } else {
             const int kk = threadIdx.x >> 4, c = (threadIdx.x & 15) * 8;
@@ -93,7 +97,7 @@ __global__ void __launch_bounds__(256) gemm_fp32_kernel(const GemmArgs g) {
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
                 const int gn = n0 + c + e;
-                rb[e] = (gn < g.N && gk < g.K) ? __ldg(g.B + (int64_t)gk * g.ldb + gn) : 0.f;
+                rb[e] = (gn < g.N && gk < kend) ? __ldg(g.B + (int64_t)gk * g.ldb + gn) : 0.f;
             }
         }
     };
@@ -118,11 +122,11 @@ __global__ void __launch_bounds__(256) gemm_fp32_kernel(const GemmArgs g) {
         }
     };
 
-    fetch(0);
-    for (int k0 = 0; k0 < g.K; k0 += kGK) {
+    fetch(kbeg);
+    for (int k0 = kbeg; k0 < kend; k0 += kGK) {
         stash();
         __syncthreads();
-        if (k0 + kGK < g.K) fetch(k0 + kGK);
+        if (k0 + kGK < kend) fetch(k0 + kGK);
 #pragma unroll
         for (int k = 0; k < kGK; ++k) {
             const float4 a0 = *reinterpret_cast<const float4*>(&As[k][4 * ty]);
@@ -147,6 +151,10 @@ __global__ void __launch_bounds__(256) gemm_fp32_kernel(const GemmArgs g) {
             const int gn = n0 + (j < 4 ? 4 * tx + j : 64 + 4 * tx + j - 4);
             if (gn >= g.N) continue;
             float v = acc[i][j];
+            if (g.partial) {
+                g.partial[((int64_t)blockIdx.z * g.M + gm) * g.N + gn] = v;
+                continue;
+            }
             if (g.bias) v += g.bias[gn];
             float* c = g.C + (int64_t)gm * g.ldc + gn;
             *c = g.accumulate ? *c + v : v;
@@ -154,12 +162,47 @@ __global__ void __launch_bounds__(256) gemm_fp32_kernel(const GemmArgs g) {
     }
 }
 
+// C[m][n] = sum over slices, in slice order, of partial[z][m][n]: the second pass of a split contraction.
+__global__ void gemm_fp32_reduce_kernel(const float* __restrict__ partial, float* __restrict__ C, int M,
+                                        int N, int ldc, int slices) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (int64_t)M * N) return;
+    float v = 0.f;
+    for (int z = 0; z < slices; ++z) v += partial[(int64_t)z * M * N + i];
+    C[(i / N) * ldc + (i % N)] = v;
+}
+
 int gemm(ltca_ctx* ctx, const float* A, const float* B, const float* bias, float* C, int M, int N,
          int K, int lda, int ldb, int ldc, int ta, int tb, int accumulate) {
-    GemmArgs g{A, B, bias, C, M, N, K, lda, ldb, ldc, ta, tb, accumulate};
+    GemmArgs g{A, B, bias, C, M, N, K, lda, ldb, ldc, ta, tb, accumulate, K, nullptr};
     dim3 grid((N + kGT - 1) / kGT, (M + kGT - 1) / kGT);
     gemm_fp32_kernel<<<grid, 256, 0, ctx->stream>>>(g);
     LTCA_LAUNCH_OK(ctx, "gemm_fp32_kernel");
+    return LTCA_OK;
+}
+
+// A weight-gradient product (few output tiles, long contraction): the contraction is cut into slices, one
+// CTA per (tile, slice), and the slices are summed in a fixed order, so the result does not depend on
+// the launch.  `scratch` holds the slice results; with too little of it the product runs unsplit.
+int gemm_long_k(ltca_ctx* ctx, const float* A, const float* B, float* C, int M, int N, int K, int lda,
+                int ldb, int ldc, int ta, int tb, float* scratch, size_t scratch_bytes) {
+    const int tiles = ((N + kGT - 1) / kGT) * ((M + kGT - 1) / kGT);
+    int slices = (2 * ctx->sm_count + tiles - 1) / tiles;
+    const size_t one = (size_t)M * N * sizeof(float);
+    if ((size_t)slices * one > scratch_bytes) slices = (int)(scratch_bytes / one);
+    if (slices > K / (4 * kGK)) slices = K / (4 * kGK);
+    if (slices < 2) return gemm(ctx, A, B, nullptr, C, M, N, K, lda, ldb, ldc, ta, tb, 0);
+    int kper = (K + slices - 1) / slices;
+    kper = (kper + kGK - 1) / kGK * kGK;
+    slices = (K + kper - 1) / kper;
+    GemmArgs g{A, B, nullptr, C, M, N, K, lda, ldb, ldc, ta, tb, 0, kper, scratch};
+    dim3 grid((N + kGT - 1) / kGT, (M + kGT - 1) / kGT, slices);
+    gemm_fp32_kernel<<<grid, 256, 0, ctx->stream>>>(g);
+    LTCA_LAUNCH_OK(ctx, "gemm_fp32_kernel");
+    const int64_t n = (int64_t)M * N;
+    gemm_fp32_reduce_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(scratch, C, M, N, ldc,
+                                                                                  slices);
+    LTCA_LAUNCH_OK(ctx, "gemm_fp32_reduce_kernel");
     return LTCA_OK;
 }
 
@@ -906,10 +949,12 @@ static int tsa_backward(ltca_ctx* ctx, const ltca_tsa_params* t, bool want_dx, b
     }
     if (want_dw) {
         // dW = x^T dQ  ([E, rows] x [rows, HW]),  dWo = ctx^T dy  ([HW, rows] x [rows, E])
-        if ((rc = gemm(ctx, t->x, dq, nullptr, t->dwq, E, HW, rows, E, HW, HW, 1, 0, 0))) return rc;
-        if ((rc = gemm(ctx, t->x, dk, nullptr, t->dwk, E, HW, rows, E, HW, HW, 1, 0, 0))) return rc;
-        if ((rc = gemm(ctx, t->x, dv, nullptr, t->dwv, E, HW, rows, E, HW, HW, 1, 0, 0))) return rc;
-        if ((rc = gemm(ctx, fb.ctx, t->dy, nullptr, t->dwo, HW, E, rows, HW, E, E, 1, 0, 0))) return rc;
+        // dctx is dead once the attention backward has run: it holds the contraction slices
+        if ((rc = gemm_long_k(ctx, t->x, dq, t->dwq, E, HW, rows, E, HW, HW, 1, 0, dctx, pl.buf))) return rc;
+        if ((rc = gemm_long_k(ctx, t->x, dk, t->dwk, E, HW, rows, E, HW, HW, 1, 0, dctx, pl.buf))) return rc;
+        if ((rc = gemm_long_k(ctx, t->x, dv, t->dwv, E, HW, rows, E, HW, HW, 1, 0, dctx, pl.buf))) return rc;
+        if ((rc = gemm_long_k(ctx, fb.ctx, t->dy, t->dwo, HW, E, rows, HW, E, E, 1, 0, dctx, pl.buf)))
+            return rc;
     }
     return LTCA_OK;
 }
