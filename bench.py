@@ -159,32 +159,50 @@ def workload_config(n_gpus):
 
 
 def module_measurement(args):
-    """TimeSelfAttention forward and backward (with the recomputed forward) at B=32 S=256 E=512 H=8, head
-    width 64, causal: back-to-back calls between CUDA events, an L2 flush is not needed for a figure that is
-    dominated by eleven GEMMs over 16 MB activations.  Prints one JSON line."""
+    """TimeSelfAttention forward and backward (with the recomputed forward) at B=32 S=256 E=512 H=8 per GPU,
+    head width 64, causal; with several ranks the weight gradients are summed over them after each
+    backward.  Back-to-back calls between CUDA events; an L2 flush is not needed for a figure that is dominated
+    by eleven GEMMs over 16 MB activations.  Rank 0 prints one JSON line (maximum over the ranks' times)."""
     import math
     import torch
+    import torch.distributed as dist
     import cuda_ltc_b200 as ltc
     from cuda_ltc_b200 import _lib
-    torch.cuda.set_device(0)
-    ctx = ltc.Context(0)
-    B, S, E, H, W = 32, 256, 512, 8, 64
-    g = torch.Generator(device="cuda").manual_seed(SEED)
+    from cuda_ltc_b200.shard import reduce_max, sum_weight_grads
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    ctx = ltc.Context(local_rank)
+    B, S, E, H, W = 32, 256, 512, 8, 64                 # per rank: sequences are dealt out, weights replicated
+    g = torch.Generator(device="cuda").manual_seed(SEED + rank)
     x = torch.randn((B * S, E), generator=g, device="cuda")
     dy = torch.randn((B * S, E), generator=g, device="cuda")
+    gw = torch.Generator(device="cuda").manual_seed(SEED)
     lim = math.sqrt(6.0 / (2 * E))
-    ws = [(torch.rand((E, H * W), generator=g, device="cuda") * 2 - 1) * lim for _ in range(3)]
-    wo = (torch.rand((H * W, E), generator=g, device="cuda") * 2 - 1) * lim
+    ws = [(torch.rand((E, H * W), generator=gw, device="cuda") * 2 - 1) * lim for _ in range(3)]
+    wo = (torch.rand((H * W, E), generator=gw, device="cuda") * 2 - 1) * lim
     gamma, beta = torch.ones(E, device="cuda"), torch.zeros(E, device="cuda")
     kw = dict(scale=1 / math.sqrt(W), causal=True, time_major=False, mode=_lib.MODE_BF16)
     fwd = lambda: ctx.tsa_fwd(x, *ws, wo, B, S, H, W, gamma=gamma, beta=beta, **kw)
-    bwd = lambda: ctx.tsa_bwd(x, *ws, wo, dy, B, S, H, W, **kw)
+
+    def bwd():
+        grads = ctx.tsa_bwd(x, *ws, wo, dy, B, S, H, W, **kw)
+        sum_weight_grads(grads[1:])                     # one 4 MiB sum over the ranks; nothing at one rank
+        return grads
+
     n, w = (1, 1) if args.profile else (max(5, args.steps), max(3, args.warmup))
 
     def timed(f):
         for _ in range(w):
             f()
         torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for _ in range(n):
@@ -193,15 +211,23 @@ def module_measurement(args):
         torch.cuda.synchronize()
         return e0.elapsed_time(e1) / n
 
-    f_ms, b_ms = timed(fwd), timed(bwd)
-    rows = B * S
+    f_ms, b_ms = reduce_max([timed(fwd), timed(bwd)])
+    status = ctx.device_status()
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank != 0:
+        return
+    rows = B * S * world
     gemm = 2.0 * rows * E * H * W                       # one projection
-    core = 4.0 * B * H * S * S * W / 2
-    print(json.dumps({"workload": "TimeSelfAttention module, B=32 S=256 E=512 H=8 W=64 causal, tensor-pipe mode",
+    core = 4.0 * B * world * H * S * S * W / 2
+    print(json.dumps({"workload": "TimeSelfAttention module, B=32 per GPU, S=256 E=512 H=8 W=64 causal, "
+                                  "tensor-pipe mode; weight gradients summed over the ranks",
+                      "n_gpus": world,
                       "fwd_us": f_ms * 1e3, "bwd_incl_recompute_us": b_ms * 1e3,
                       "fwd_tflops": (4 * gemm + core) / f_ms / 1e9,
                       "bwd_tflops": (11 * gemm + 3.5 * core) / b_ms / 1e9,
-                      "device_status": ctx.device_status()}))
+                      "device_status": status}))
 
 
 def main():
@@ -218,7 +244,7 @@ def main():
                     help="profiler capture mode: 1 warm-up, 1 step, no end-to-end or CPU legs (not a bench value)")
     ap.add_argument("--module", action="store_true",
                     help="side measurement, not the bench line: the TimeSelfAttention module (projections + "
-                         "attention + residual + LayerNorm) at BASELINE configs[1], one GPU, tensor-pipe mode")
+                         "attention + residual + LayerNorm) at BASELINE configs[1] per GPU, tensor-pipe mode")
     args = ap.parse_args()
     if args.module:
         module_measurement(args)

@@ -5,6 +5,10 @@ ranks in contiguous, balanced ranges and no rank ever needs another rank's data:
 collective on the data path.  The only communication of a multi-GPU run is the reduction of
 the per-rank timings (maximum over ranks) and, for checks, of a few scalars.
 
+The whole module (projections around the core) shards by sequences with replicated weights:
+forward and the input gradient stay local, and only the weight gradients, which are sums over
+rows, need one sum over the ranks (``sum_weight_grads``).
+
 The reference is single-GPU (its only device selection is ``cudaSetDevice(0)`` in a test,
 src/ml/time_self_attention_test.cu:523); this module has no counterpart there.
 """
@@ -55,3 +59,42 @@ def reduce_max(values, group=None):
             t = t.cuda()
         dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
     return t.cpu().tolist()
+
+
+class _Pending:
+    """Handle of a weight-gradient sum in flight: ``wait()`` finishes it and scatters the bucket back."""
+
+    def __init__(self, work, bucket, grads):
+        self._work, self._bucket, self._grads = work, bucket, grads
+
+    def wait(self):
+        if self._work is not None:
+            self._work.wait()
+            self._work = None
+        off = 0
+        for g in self._grads:
+            n = g.numel()
+            g.copy_(self._bucket[off:off + n].view_as(g))
+            off += n
+        return self._grads
+
+
+def sum_weight_grads(grads, group=None, async_op=False):
+    """Sum each rank's partial weight gradients over the ranks, in place, with ONE collective.
+
+    With sequences dealt out over the ranks and the weights replicated, dWq, dWk, dWv, dWo (and the
+    bias / LayerNorm gradients) of a rank cover only its rows; the full gradient is their sum.  The
+    tensors are packed into one bucket (4 MiB for four 512 x 512 fp32 matrices) so the cost is one
+    launch, not one per matrix.  ``async_op=True`` returns a handle whose ``wait()`` completes the sum,
+    so the caller can run the previous layer's backward meanwhile.  Without a process group the
+    gradients are returned unchanged.
+    """
+    import torch
+    import torch.distributed as dist
+    grads = [g for g in grads if g is not None]
+    if not grads or not (dist.is_available() and dist.is_initialized()) or dist.get_world_size(group) == 1:
+        return _Pending(None, None, []) if async_op else grads
+    bucket = torch.cat([g.reshape(-1) for g in grads])
+    work = dist.all_reduce(bucket, op=dist.ReduceOp.SUM, group=group, async_op=True)
+    pending = _Pending(work, bucket, grads)
+    return pending if async_op else pending.wait()

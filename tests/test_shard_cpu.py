@@ -67,3 +67,52 @@ def test_max_over_ranks_with_two_gloo_ranks():
         red, total = out[r]
         assert red == [2.0, 5.0]
         assert total == 10.0
+
+
+def _module_worker(rank, world, port, out):
+    """Each rank differentiates the module on its own sequences; the weight gradients are summed."""
+    import numpy as np
+    import oracle
+    from cuda_ltc_b200.shard import sum_weight_grads
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        B, S, E, H = 4, 8, 16, 2
+        rng = np.random.default_rng(7)
+        x = rng.standard_normal((B, S, E))
+        dy = rng.standard_normal((B, S, E))
+        ws = [rng.standard_normal((E, E)) * 0.2 for _ in range(4)]
+        mine = unit_range(B, world, rank)
+        sl = slice(mine.start, mine.stop)
+        kw = dict(scale=(E // H) ** -0.5, causal=True, time_major=False)
+        part = oracle.tsa_bwd(x[sl].reshape(-1, E), *ws, dy[sl].reshape(-1, E), len(mine), S, H, E // H, **kw)
+        grads = [torch.from_numpy(np.ascontiguousarray(g)) for g in part[1:5]]
+        handle = sum_weight_grads(grads, async_op=True)
+        handle.wait()
+        full = oracle.tsa_bwd(x.reshape(-1, E), *ws, dy.reshape(-1, E), B, S, H, E // H, **kw)
+        err = max(float(np.abs(g.numpy() - f).max()) for g, f in zip(grads, full[1:5]))
+        # the input gradient of the rank's rows needs no exchange at all
+        dx_err = float(np.abs(part[0] - full[0].reshape(B, S, E)[sl].reshape(-1, E)).max())
+        out[rank] = (err, dx_err)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_module_weight_gradients_sum_over_two_gloo_ranks():
+    world = 2
+    port = _free_port()
+    mgr = mp.Manager()
+    out = mgr.dict()
+    mp.spawn(_module_worker, args=(world, port, out), nprocs=world, join=True)
+    for r in range(world):
+        err, dx_err = out[r]
+        assert err < 1e-10 and dx_err < 1e-10
+
+
+def test_weight_gradient_sum_without_a_group_is_the_identity():
+    from cuda_ltc_b200.shard import sum_weight_grads
+    g = [torch.ones(3, 3), None, torch.full((2,), 2.0)]
+    got = sum_weight_grads(g)
+    assert len(got) == 2 and torch.equal(got[0], torch.ones(3, 3)) and torch.equal(got[1], torch.full((2,), 2.0))
+    assert sum_weight_grads(g, async_op=True).wait() == []
