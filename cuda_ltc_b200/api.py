@@ -227,7 +227,13 @@ class Context:
         p = self._tsa_params(x, wq, wk, wv, wo, B, S, H, head_width, scale, causal, time_major,
                              False, False, None, None, keep_mask, mode, (bq, bk, bv, None))
         dx = torch.empty_like(x)
-        dws = [torch.empty_like(w) for w in (wq, wk, wv, wo)]
+        # the four weight gradients are views of one allocation, so a multi-GPU caller sums them over the
+        # ranks with a single collective on that allocation (shard.sum_weight_grads) without packing them
+        flat = torch.empty(sum(w.numel() for w in (wq, wk, wv, wo)), dtype=wq.dtype, device=wq.device)
+        dws, off = [], 0
+        for w in (wq, wk, wv, wo):
+            dws.append(flat[off:off + w.numel()].view(w.shape))
+            off += w.numel()
         p.dy, p.dx = dy.data_ptr(), dx.data_ptr()
         p.dwq, p.dwk, p.dwv, p.dwo = (w.data_ptr() for w in dws)
         ws = self._tsa_workspace(p, 3)

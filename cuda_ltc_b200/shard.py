@@ -64,19 +64,34 @@ def reduce_max(values, group=None):
 class _Pending:
     """Handle of a weight-gradient sum in flight: ``wait()`` finishes it and scatters the bucket back."""
 
-    def __init__(self, work, bucket, grads):
+    def __init__(self, work, bucket, grads, all_grads=None):
         self._work, self._bucket, self._grads = work, bucket, grads
+        self._all = grads if all_grads is None else all_grads
 
     def wait(self):
         if self._work is not None:
             self._work.wait()
             self._work = None
         off = 0
-        for g in self._grads:
+        for g in self._grads:                      # empty when the sum ran in place on the gradients' own memory
             n = g.numel()
             g.copy_(self._bucket[off:off + n].view_as(g))
             off += n
-        return self._grads
+        return self._all
+
+
+def _as_one_allocation(grads):
+    """One flat tensor aliasing all of ``grads`` if they are back-to-back contiguous views of one
+    allocation (as ``Context.tsa_bwd`` returns them), else None."""
+    first = grads[0]
+    off = first.storage_offset()
+    for g in grads:
+        if (not g.is_contiguous() or g.dtype != first.dtype or g.device != first.device
+                or g.untyped_storage().data_ptr() != first.untyped_storage().data_ptr()
+                or g.storage_offset() != off):
+            return None
+        off += g.numel()
+    return first.as_strided((off - first.storage_offset(),), (1,), first.storage_offset())
 
 
 def sum_weight_grads(grads, group=None, async_op=False):
@@ -94,7 +109,8 @@ def sum_weight_grads(grads, group=None, async_op=False):
     grads = [g for g in grads if g is not None]
     if not grads or not (dist.is_available() and dist.is_initialized()) or dist.get_world_size(group) == 1:
         return _Pending(None, None, []) if async_op else grads
-    bucket = torch.cat([g.reshape(-1) for g in grads])
+    packed = _as_one_allocation(grads)
+    bucket = packed if packed is not None else torch.cat([g.reshape(-1) for g in grads])
     work = dist.all_reduce(bucket, op=dist.ReduceOp.SUM, group=group, async_op=True)
-    pending = _Pending(work, bucket, grads)
+    pending = _Pending(work, bucket, [] if packed is not None else grads, grads)
     return pending if async_op else pending.wait()

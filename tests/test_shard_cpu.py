@@ -88,8 +88,17 @@ def _module_worker(rank, world, port, out):
         kw = dict(scale=(E // H) ** -0.5, causal=True, time_major=False)
         part = oracle.tsa_bwd(x[sl].reshape(-1, E), *ws, dy[sl].reshape(-1, E), len(mine), S, H, E // H, **kw)
         grads = [torch.from_numpy(np.ascontiguousarray(g)) for g in part[1:5]]
+        if rank == 0:
+            # back-to-back views of one allocation are summed in place, separate tensors through a bucket
+            flat = torch.cat([g.reshape(-1) for g in grads])
+            views, off = [], 0
+            for g in grads:
+                views.append(flat[off:off + g.numel()].view(g.shape))
+                off += g.numel()
+            grads = views
         handle = sum_weight_grads(grads, async_op=True)
-        handle.wait()
+        done = handle.wait()
+        assert len(done) == 4 and all(a is b for a, b in zip(done, grads))
         full = oracle.tsa_bwd(x.reshape(-1, E), *ws, dy.reshape(-1, E), B, S, H, E // H, **kw)
         err = max(float(np.abs(g.numpy() - f).max()) for g, f in zip(grads, full[1:5]))
         # the input gradient of the rank's rows needs no exchange at all
