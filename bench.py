@@ -230,6 +230,121 @@ def module_measurement(args):
                       "device_status": status}))
 
 
+def model_step_measurement(args):
+    """Attention's share of a model-shaped training step (BASELINE configs[4]: B=64, S=512, fp32).
+
+    Only the attention module is this library's code.  Its neighbours in the reference's model
+    (src/ml/ml_liquid_net.cu:146-170: PreConvBlock -> positional embedding -> projection ->
+    TimeSelfAttention -> LTCBlock -> PolicyHead / ValueNet) are plain torch stand-ins of the same shapes,
+    there to give the step its surrounding cost, not to reproduce those layers: a k=3 convolution 64 -> 512
+    with LayerNorm and GELU, a learned positional table, a 512 x 512 projection, a recurrent cell of 256
+    units stepped over the 512 positions with 6 semi-implicit ODE unfolds per position (the update rule of
+    src/ml/ltc_cell.cu:59-106), and two linear heads (16 actions, 1 value) on the last state.
+    The attention module's forward and backward are bracketed by CUDA events inside the step."""
+    import math
+    import torch
+    import torch.nn.functional as F
+    import cuda_ltc_b200 as ltc
+    from cuda_ltc_b200 import _lib
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    ctx = ltc.Context(0)
+    B, S, Cin, E, H, W, U, UNF, ACT = 64, 512, 64, 512, 8, 64, 256, 6, 16
+    g = torch.Generator(device=dev).manual_seed(SEED)
+
+    def param(*shape, fan):
+        lim = math.sqrt(6.0 / fan)
+        return ((torch.rand(shape, generator=g, device=dev) * 2 - 1) * lim).requires_grad_()
+
+    conv_w, conv_b = param(E, Cin, 3, fan=Cin * 3 + E), torch.zeros(E, device=dev, requires_grad=True)
+    ln_g, ln_b = torch.ones(E, device=dev, requires_grad=True), torch.zeros(E, device=dev, requires_grad=True)
+    pos = (torch.randn((S, E), generator=g, device=dev) * 0.02).requires_grad_()
+    proj_w = param(E, E, fan=2 * E)
+    wq, wk, wv, wo = (param(E, E, fan=2 * E) for _ in range(4))
+    a_gamma, a_beta = torch.ones(E, device=dev), torch.zeros(E, device=dev)
+    w_in, w_rec = param(E, 4 * U, fan=E + U), param(U, 4 * U, fan=2 * U)
+    b_gate = torch.zeros(4 * U, device=dev, requires_grad=True)
+    tau = torch.ones(U, device=dev, requires_grad=True)
+    a_vec = torch.ones(U, device=dev, requires_grad=True)
+    pol_w, val_w = param(U, ACT, fan=U + ACT), param(U, 1, fan=U + 1)
+    params = [conv_w, conv_b, ln_g, ln_b, pos, proj_w, wq, wk, wv, wo, w_in, w_rec, b_gate, tau, a_vec, pol_w,
+              val_w]
+    x_in = torch.randn((B, S, Cin), generator=g, device=dev)
+    kw = dict(scale=1 / math.sqrt(W), causal=True, time_major=False, mode=_lib.MODE_BF16)
+    attn_events = []
+
+    class Attention(torch.autograd.Function):
+        @staticmethod
+        def forward(fctx, x, wq_, wk_, wv_, wo_):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            out = ctx.tsa_fwd(x, wq_, wk_, wv_, wo_, B, S, H, W, gamma=a_gamma, beta=a_beta, **kw)
+            e1.record()
+            attn_events.append((e0, e1))
+            fctx.save_for_backward(x, wq_, wk_, wv_, wo_)
+            return out
+
+        @staticmethod
+        def backward(fctx, dy):
+            x, wq_, wk_, wv_, wo_ = fctx.saved_tensors
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            grads = ctx.tsa_bwd(x, wq_, wk_, wv_, wo_, dy.contiguous(), B, S, H, W, **kw)
+            e1.record()
+            attn_events.append((e0, e1))
+            return grads
+
+    def step(recurrent=True):
+        h = F.conv1d(x_in.transpose(1, 2), conv_w, conv_b, padding=1).transpose(1, 2)
+        h = F.gelu(F.layer_norm(h, (E,), ln_g, ln_b)) + pos
+        h = (h.reshape(B * S, E) @ proj_w).contiguous()
+        h = Attention.apply(h, wq, wk, wv, wo)
+        gates_in = (h @ w_in + b_gate).view(B, S, 4 * U)
+        state = torch.zeros((B, U), device=dev)
+        dt = 1.0 / UNF
+        for t in range(S if recurrent else 1):
+            i_t, f_t, o_t, c_t = (gates_in[:, t] + state @ w_rec).chunk(4, dim=1)
+            i_t, f_t, o_t, c_t = torch.sigmoid(i_t), torch.sigmoid(f_t), torch.sigmoid(o_t), torch.tanh(c_t)
+            f_x = o_t * torch.tanh(f_t * c_t + i_t * torch.tanh(a_vec))
+            for _ in range(UNF):
+                state = (state + dt * f_x * a_vec) / (1.0 + dt * (1.0 / tau.clamp_min(1e-6) + f_x))
+        loss = (state @ pol_w).square().mean() + (state @ val_w).square().mean()
+        loss.backward()
+        for p_ in params:
+            p_.grad = None
+        return loss
+
+    n, w = (1, 1) if args.profile else (max(2, min(args.steps, 5)), 1)
+    for _ in range(w):
+        step()
+    torch.cuda.synchronize()
+    attn_events.clear()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(n):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    step_ms = e0.elapsed_time(e1) / n
+    attn_ms = sum(a.elapsed_time(b) for a, b in attn_events) / n
+    # the same step with the recurrent cell run at one position only: what is left when the cell's
+    # launch-bound loop over the positions is taken out
+    step(False)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(n):
+        step(False)
+    e1.record()
+    torch.cuda.synchronize()
+    flat_ms = e0.elapsed_time(e1) / n
+    print(json.dumps({"workload": "model-shaped step, B=64 S=512 fp32 (BASELINE configs[4]); attention module = this "
+                                  "library (tensor-pipe mode), every other layer a torch stand-in of the same shape",
+                      "step_ms": step_ms, "attention_ms": attn_ms, "attention_share": attn_ms / step_ms,
+                      "step_one_recurrent_position_ms": flat_ms, "attention_share_there": attn_ms / flat_ms,
+                      "steps": n, "recurrent_positions": S, "ode_unfolds": UNF,
+                      "device_status": ctx.device_status()}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -242,12 +357,18 @@ def main():
                     help="sequences per GPU; anything but the default is a reduced case for profiler captures")
     ap.add_argument("--profile", action="store_true",
                     help="profiler capture mode: 1 warm-up, 1 step, no end-to-end or CPU legs (not a bench value)")
+    ap.add_argument("--model-step", action="store_true",
+                    help="side measurement, not the bench line: attention's share of a step shaped like BASELINE "
+                         "configs[4] (the layers around the attention module are torch stand-ins), one GPU")
     ap.add_argument("--module", action="store_true",
                     help="side measurement, not the bench line: the TimeSelfAttention module (projections + "
                          "attention + residual + LayerNorm) at BASELINE configs[1] per GPU, tensor-pipe mode")
     args = ap.parse_args()
     if args.module:
         module_measurement(args)
+        return
+    if args.model_step:
+        model_step_measurement(args)
         return
     if args.profile:
         args.steps, args.warmup, args.no_e2e, args.no_cpu_baseline = 1, 1, True, True
