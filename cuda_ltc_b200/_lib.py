@@ -87,6 +87,10 @@ EXPORTS = {
     "ltca_tsa_bwd_data": (C.c_int, [C.c_void_p, C.POINTER(TsaParams)]),
     "ltca_tsa_bwd_weights": (C.c_int, [C.c_void_p, C.POINTER(TsaParams)]),
     "ltca_add_tensors": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t]),
+    "ltca_attn_merge": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p,
+                                  C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_int32]),
+    "ltca_accumulate_rows": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int64, C.c_int32,
+                                       C.c_int32, C.c_int32, C.c_int32]),
     "ltca_layer_norm": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32]),
     "ltca_validate_finite": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     "ltca_f32_to_bf16": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t]),

@@ -176,6 +176,24 @@ class Context:
         del ws
         return o, lse
 
+    # ---- sequence sharding: fold one key/value shard's result into running accumulators ----
+    def attn_merge(self, o_acc, lse_acc, o_blk, lse_blk, s0=0):
+        """o_acc [B,H,S,D] fp32, lse_acc [B,H,S] fp32 (contiguous) absorb o_blk [B,H,n,D], lse_blk [B,H,n]
+        (contiguous) at rows s0 .. s0+n of every (batch, head)."""
+        B, H, S, D = o_acc.shape
+        n = o_blk.shape[2]
+        assert o_acc.is_contiguous() and lse_acc.is_contiguous() and o_blk.is_contiguous() and lse_blk.is_contiguous()
+        assert o_acc.dtype == torch.float32 and lse_acc.dtype == torch.float32 and lse_blk.dtype == torch.float32
+        self.check(self.lib.ltca_attn_merge(self.handle, o_acc.data_ptr(), lse_acc.data_ptr(), o_blk.data_ptr(),
+                                            _dtype_code(o_blk), lse_blk.data_ptr(), B * H, S, s0, n, D))
+
+    def accumulate_rows(self, acc, part, s0=0):
+        """acc [B,H,S,D] fp32 += part [B,H,n,D] (fp32 or bf16, contiguous) at rows s0 .. s0+n."""
+        B, H, S, D = acc.shape
+        assert acc.is_contiguous() and part.is_contiguous() and acc.dtype == torch.float32
+        self.check(self.lib.ltca_accumulate_rows(self.handle, acc.data_ptr(), part.data_ptr(), _dtype_code(part),
+                                                 B * H, S, s0, part.shape[2], D))
+
     # ---- TimeSelfAttention module --------------------------------------------------------
     def _tsa_params(self, x, wq, wk, wv, wo, B, S, H, head_width, scale, causal, time_major,
                     use_residual, use_layer_norm, gamma, beta, keep_mask, mode, biases=(None, None, None, None)):

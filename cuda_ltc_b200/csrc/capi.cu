@@ -95,6 +95,49 @@ __global__ void pack_bf16_kernel(const float* __restrict__ src, ltca_strides st,
     }
 }
 
+__device__ __forceinline__ float to_f32(float v) { return v; }
+__device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+// One warp per row i of the block (rows s0 .. s0+n of each of the BH accumulator slabs):
+//   lse' = log(exp(lse_acc) + exp(lse_blk)),  o_acc = o_acc * exp(lse_acc - lse') + o_blk * exp(lse_blk - lse').
+// A block row with no visible key carries lse_blk = -inf and leaves the accumulator as it is.
+template <typename T>
+__global__ void attn_merge_kernel(float* __restrict__ o_acc, float* __restrict__ lse_acc,
+                                  const T* __restrict__ o_blk, const float* __restrict__ lse_blk,
+                                  int64_t BH, int S_acc, int s0, int n, int D) {
+    const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= BH * n) return;
+    const int lane = threadIdx.x & 31;
+    const int64_t bh = row / n;
+    const int i = (int)(row % n);
+    const int64_t arow = bh * S_acc + s0 + i;
+    const float la = lse_acc[arow], lb = lse_blk[row];
+    if (lb == -INFINITY) return;
+    const float m = fmaxf(la, lb);
+    const float ea = (la == -INFINITY) ? 0.f : __expf(la - m), eb = __expf(lb - m);
+    const float inv = 1.f / (ea + eb);
+    const float wa = ea * inv, wb = eb * inv;
+    float* oa = o_acc + arow * D;
+    const T* ob = o_blk + row * D;
+    for (int d = lane; d < D; d += 32) oa[d] = oa[d] * wa + to_f32(ob[d]) * wb;
+    __syncwarp();
+    if (lane == 0) lse_acc[arow] = m + __logf(ea + eb);
+}
+
+// acc[bh][s0 + i][d] += part[bh][i][d]
+template <typename T>
+__global__ void accumulate_rows_kernel(float* __restrict__ acc, const T* __restrict__ part, int64_t total,
+                                       int S_acc, int s0, int n, int D) {
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += stride) {
+        const int d = (int)(e % D);
+        const int64_t r = e / D;
+        const int64_t bh = r / n;
+        const int i = (int)(r % n);
+        acc[(bh * S_acc + s0 + i) * D + d] += to_f32(part[e]);
+    }
+}
+
 inline int blocks_for(size_t n, int threads, int sm_count) {
     size_t b = (n + threads - 1) / threads;
     const size_t cap = (size_t)(sm_count > 0 ? sm_count : 148) * 16;
@@ -332,6 +375,46 @@ int ltca_add_tensors(ltca_ctx* ctx, const float* a, const float* b, float* r, si
     else
         add_scalar_kernel<<<blocks_for(n, 256, ctx->sm_count), 256, 0, ctx->stream>>>(a, b, r, n);
     LTCA_LAUNCH_OK(ctx, "add_kernel");
+    return LTCA_OK;
+}
+
+int ltca_attn_merge(ltca_ctx* ctx, float* o_acc, float* lse_acc, const void* o_blk, int32_t blk_dtype,
+                    const float* lse_blk, int64_t BH, int32_t S_acc, int32_t s0, int32_t n, int32_t D) {
+    if (!ctx) return LTCA_ERR_INVALID;
+    if (!o_acc || !lse_acc || !o_blk || !lse_blk) return fail(ctx, LTCA_ERR_INVALID, "null tensor");
+    if (BH < 0 || S_acc < 0 || s0 < 0 || n < 0 || D < 1 || s0 + n > S_acc)
+        return fail(ctx, LTCA_ERR_INVALID, "bad row range %d + %d of %d", s0, n, S_acc);
+    if (blk_dtype != LTCA_F32 && blk_dtype != LTCA_BF16) return fail(ctx, LTCA_ERR_INVALID, "bad dtype");
+    if (BH * n == 0) return LTCA_OK;
+    const int wpb = 8;
+    const unsigned grid = (unsigned)((BH * n + wpb - 1) / wpb);
+    if (blk_dtype == LTCA_F32)
+        attn_merge_kernel<float><<<grid, wpb * 32, 0, ctx->stream>>>(
+            o_acc, lse_acc, static_cast<const float*>(o_blk), lse_blk, BH, S_acc, s0, n, D);
+    else
+        attn_merge_kernel<__nv_bfloat16><<<grid, wpb * 32, 0, ctx->stream>>>(
+            o_acc, lse_acc, static_cast<const __nv_bfloat16*>(o_blk), lse_blk, BH, S_acc, s0, n, D);
+    LTCA_LAUNCH_OK(ctx, "attn_merge_kernel");
+    return LTCA_OK;
+}
+
+int ltca_accumulate_rows(ltca_ctx* ctx, float* acc, const void* part, int32_t part_dtype, int64_t BH,
+                         int32_t S_acc, int32_t s0, int32_t n, int32_t D) {
+    if (!ctx) return LTCA_ERR_INVALID;
+    if (!acc || !part) return fail(ctx, LTCA_ERR_INVALID, "null tensor");
+    if (BH < 0 || S_acc < 0 || s0 < 0 || n < 0 || D < 1 || s0 + n > S_acc)
+        return fail(ctx, LTCA_ERR_INVALID, "bad row range %d + %d of %d", s0, n, S_acc);
+    if (part_dtype != LTCA_F32 && part_dtype != LTCA_BF16) return fail(ctx, LTCA_ERR_INVALID, "bad dtype");
+    const int64_t total = BH * n * D;
+    if (total == 0) return LTCA_OK;
+    const int grid = blocks_for((size_t)total, 256, ctx->sm_count);
+    if (part_dtype == LTCA_F32)
+        accumulate_rows_kernel<float><<<grid, 256, 0, ctx->stream>>>(
+            acc, static_cast<const float*>(part), total, S_acc, s0, n, D);
+    else
+        accumulate_rows_kernel<__nv_bfloat16><<<grid, 256, 0, ctx->stream>>>(
+            acc, static_cast<const __nv_bfloat16*>(part), total, S_acc, s0, n, D);
+    LTCA_LAUNCH_OK(ctx, "accumulate_rows_kernel");
     return LTCA_OK;
 }
 

@@ -241,6 +241,18 @@ int ltca_tsa_bwd(ltca_ctx* ctx, const ltca_tsa_params* p);
 
 /* r = a + b, n fp32 elements.  Replaces cudatrader::addTensors (src/cuda_tensor_utils.cu:25-41). */
 int ltca_add_tensors(ltca_ctx* ctx, const float* a, const float* b, float* r, size_t n);
+/* Sequence sharding with key/value exchange (an extension: the reference is single-GPU and has no such
+ * step).  A rank that holds a slice of the queries attends to one key/value shard at a time; each partial
+ * result (o_blk [BH, n, D] contiguous, fp32 or bf16, with its natural-log sum-exp lse_blk [BH, n]) is
+ * folded into fp32 accumulators o_acc [BH, S_acc, D], lse_acc [BH, S_acc] at rows s0 .. s0+n:
+ *   lse' = log(exp(lse_acc) + exp(lse_blk)),  o_acc = o_acc e^(lse_acc - lse') + o_blk e^(lse_blk - lse').
+ * Start from o_acc = 0, lse_acc = -inf.  Rows whose lse_blk is -inf leave the accumulator unchanged. */
+int ltca_attn_merge(ltca_ctx* ctx, float* o_acc, float* lse_acc, const void* o_blk, int32_t blk_dtype,
+                    const float* lse_blk, int64_t BH, int32_t S_acc, int32_t s0, int32_t n, int32_t D);
+/* acc[bh][s0 + i][d] += part[bh][i][d]: partial dQ / dK / dV of one shard pair into fp32 accumulators
+ * (acc [BH, S_acc, D] fp32, part [BH, n, D] contiguous, fp32 or bf16). */
+int ltca_accumulate_rows(ltca_ctx* ctx, float* acc, const void* part, int32_t part_dtype, int64_t BH,
+                         int32_t S_acc, int32_t s0, int32_t n, int32_t D);
 /* In-place LayerNorm of [rows, E] fp32, biased variance, eps 1e-5.
  * Replaces applyLayerNorm / layerNormKernel (src/ml/cudnn_time_self_attention.cu:9-68, :496-508). */
 int ltca_layer_norm(ltca_ctx* ctx, float* x, const float* gamma, const float* beta,
