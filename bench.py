@@ -345,6 +345,66 @@ def model_step_measurement(args):
                       "device_status": ctx.device_status()}))
 
 
+def ring_measurement(args):
+    """The long-sequence configuration with the SEQUENCE dealt out over the ranks (ring exchange of K/V,
+    zig-zag causal layout) instead of the batch: total work is fixed (B=8 H=16 S=4096 D=64 causal bf16), each
+    rank holds S / N positions.  Launch with one rank per GPU; rank 0 prints one JSON line with the
+    maximum over the ranks' times.  A side measurement, not the bench line: the batch x head partition
+    needs no exchange and is the headline."""
+    import torch
+    import torch.distributed as dist
+    import cuda_ltc_b200 as ltc
+    from cuda_ltc_b200 import ring
+    from cuda_ltc_b200.shard import reduce_max
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    dev = torch.device("cuda", local_rank)
+    ctx = ltc.Context(local_rank)
+    B, H, S, D = CFG["B"], CFG["H"], args.seq_len or CFG["S"], CFG["D"]
+    L = S // world
+    g = torch.Generator(device=dev).manual_seed(SEED + rank)
+    mk = lambda: (torch.randn((B, H, L, D), generator=g, device=dev) * 0.5).bfloat16()
+    q, k, v, do = mk(), mk(), mk(), mk()
+    ops = ring.CudaOps(ctx)
+    cache = {}                                          # scratch and receive buffers live across the steps
+    n, w = max(5, args.steps), max(3, args.warmup)
+
+    def step():
+        o, lse = ring.ring_attention_fwd(ops, q, k, v, rank, world, causal=True, cache=cache)
+        ring.ring_attention_bwd(ops, q, k, v, o, lse, do, rank, world, causal=True, cache=cache)
+
+    for _ in range(w):
+        step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+        torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(n):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = reduce_max([e0.elapsed_time(e1) / n])[0]
+    status = ctx.device_status()
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank != 0:
+        return
+    flops = 3.5 * 4.0 * B * H * S * S * D / 2
+    print(json.dumps({"workload": f"attention fwd+bwd, B={B} H={H} S={S} D={D} causal bf16, sequence dealt out over "
+                                  f"{world} GPU(s) with ring K/V exchange (strong scaling)",
+                      "n_gpus": world, "ms_per_step": ms, "tflops_whole_job": flops / ms / 1e9,
+                      "kv_bytes_per_hop_per_gpu": 2 * B * H * L * D * 2,
+                      "dkv_bytes_per_hop_per_gpu": 2 * B * H * L * D * 4, "device_status": status}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -357,6 +417,11 @@ def main():
                     help="sequences per GPU; anything but the default is a reduced case for profiler captures")
     ap.add_argument("--profile", action="store_true",
                     help="profiler capture mode: 1 warm-up, 1 step, no end-to-end or CPU legs (not a bench value)")
+    ap.add_argument("--seq-len", type=int, default=0, help="sequence length of the --ring measurement (default: the "
+                                                           "bench configuration's)")
+    ap.add_argument("--ring", action="store_true",
+                    help="side measurement, not the bench line: the same problem with the sequence dealt out over "
+                         "the ranks and K/V exchanged round a ring (launch one rank per GPU)")
     ap.add_argument("--model-step", action="store_true",
                     help="side measurement, not the bench line: attention's share of a step shaped like BASELINE "
                          "configs[4] (the layers around the attention module are torch stand-ins), one GPU")
@@ -369,6 +434,10 @@ def main():
         return
     if args.model_step:
         model_step_measurement(args)
+        return
+    if args.ring:
+        CFG["B"] = args.batch
+        ring_measurement(args)
         return
     if args.profile:
         args.steps, args.warmup, args.no_e2e, args.no_cpu_baseline = 1, 1, True, True

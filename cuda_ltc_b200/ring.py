@@ -86,17 +86,32 @@ class CudaOps:
         self.ctx, self.scale = ctx, scale
         self.mode = _lib.MODE_AUTO if mode is None else mode
 
-    def block_fwd(self, q, k, v, causal):
-        return self.ctx.attn_fwd(q, k, v, scale=self.scale, causal=causal, mode=self.mode)
+    def block_fwd(self, q, k, v, causal, out=None, lse=None):
+        return self.ctx.attn_fwd(q, k, v, scale=self.scale, causal=causal, mode=self.mode, out=out, lse=lse)
 
     def merge(self, o_acc, lse_acc, o_blk, lse_blk, s0):
         self.ctx.attn_merge(o_acc, lse_acc, o_blk, lse_blk, s0)
 
-    def block_bwd(self, q, k, v, o, lse, dout, causal):
-        return self.ctx.attn_bwd(q, k, v, o, lse, dout, scale=self.scale, causal=causal, mode=self.mode)
+    def block_bwd(self, q, k, v, o, lse, dout, causal, dq=None, dk=None, dv=None):
+        return self.ctx.attn_bwd(q, k, v, o, lse, dout, scale=self.scale, causal=causal, mode=self.mode,
+                                 dq=dq, dk=dk, dv=dv)
 
     def accumulate(self, acc, part, s0):
         self.ctx.accumulate_rows(acc, part, s0)
+
+
+# ---- buffers -----------------------------------------------------------------------------------------------
+def _buf(cache, name, shape, dtype, device):
+    """A scratch tensor that lives in ``cache`` across calls (steady-state steps then allocate nothing; the
+    allocator would otherwise stall the host on every hop, because tensors handed to the communication stream
+    are not reusable at once).  With ``cache`` None a fresh tensor is returned."""
+    if cache is None:
+        return torch.empty(shape, dtype=dtype, device=device)
+    key = (name, tuple(shape), dtype, str(device))
+    t = cache.get(key)
+    if t is None:
+        t = cache[key] = torch.empty(shape, dtype=dtype, device=device)
+    return t
 
 
 # ---- exchange ----------------------------------------------------------------------------------------------
@@ -114,12 +129,17 @@ class _Transfer:
 class RingExchange:
     """Sends tensors to rank+1 and receives the same shapes from rank-1 (one batched P2P call per hop)."""
 
-    def __init__(self, rank: int, world: int, group=None):
-        self.rank, self.world, self.group = rank, world, group
+    def __init__(self, rank: int, world: int, group=None, cache=None):
+        self.rank, self.world, self.group, self.cache = rank, world, group, cache
+        self._hop = {}
 
-    def start(self, tensors: List[torch.Tensor]) -> _Transfer:
+    def start(self, tensors: List[torch.Tensor], tag: str = "x") -> _Transfer:
+        """``tag`` names the stream of messages (K/V, gradients): its hops alternate between two sets of
+        receive buffers, so a hop never lands in the buffers the next hop is being sent from."""
         import torch.distributed as dist
-        received = [torch.empty_like(t) for t in tensors]
+        hop = self._hop[tag] = self._hop.get(tag, -1) + 1
+        received = [_buf(self.cache, f"recv.{tag}.{hop & 1}.{i}", t.shape, t.dtype, t.device)
+                    for i, t in enumerate(tensors)]
         nxt, prv = (self.rank + 1) % self.world, (self.rank - 1) % self.world
         if self.group is not None:
             nxt, prv = dist.get_global_rank(self.group, nxt), dist.get_global_rank(self.group, prv)
@@ -132,80 +152,112 @@ class RingExchange:
 
 # ---- per-rank state ----------------------------------------------------------------------------------------
 class _Forward:
-    def __init__(self, ops, q, k, v, rank, world, causal):
-        self.ops, self.q, self.rank, self.world, self.causal = ops, q, rank, world, causal
+    def __init__(self, ops, q, k, v, rank, world, causal, cache=None):
+        self.ops, self.q, self.rank, self.world, self.causal, self.cache = ops, q, rank, world, causal, cache
+        self.kv = [k, v]                                       # the slice currently held (two messages per hop)
         B, H, L, D = q.shape
-        self.kv = torch.stack([k, v]).contiguous()             # [2, B, H, L, D]: one message per hop
-        self.o_acc = torch.zeros((B, H, L, D), dtype=torch.float32, device=q.device)
-        self.lse_acc = torch.full((B, H, L), float("-inf"), dtype=torch.float32, device=q.device)
+        self.o_acc = _buf(cache, "o_acc", (B, H, L, D), torch.float32, q.device)
+        self.lse_acc = _buf(cache, "lse_acc", (B, H, L), torch.float32, q.device)
 
     def compute(self, step):
+        q = self.q
+        B, H, L, D = q.shape
         src = (self.rank - step) % self.world
-        (qs, qn), (ks, kn), cz = block_plan(self.rank, src, self.q.shape[2], self.causal)
-        o_blk, lse_blk = self.ops.block_fwd(self.q[:, :, qs:qs + qn], self.kv[0][:, :, ks:ks + kn],
-                                            self.kv[1][:, :, ks:ks + kn], cz)
+        (qs, qn), (ks, kn), cz = block_plan(self.rank, src, L, self.causal)
+        o_blk = _buf(self.cache, "o_blk", (B, H, qn, D), q.dtype, q.device)
+        if step == 0:
+            # the rank's own slice covers every local row: its result starts the accumulators
+            self.ops.block_fwd(q, self.kv[0], self.kv[1], cz, out=o_blk, lse=self.lse_acc)
+            self.o_acc.copy_(o_blk)
+            return
+        lse_blk = _buf(self.cache, "lse_blk", (B, H, qn), torch.float32, q.device)
+        self.ops.block_fwd(q[:, :, qs:qs + qn], self.kv[0][:, :, ks:ks + kn], self.kv[1][:, :, ks:ks + kn], cz,
+                           out=o_blk, lse=lse_blk)
         self.ops.merge(self.o_acc, self.lse_acc, o_blk, lse_blk, qs)
 
     def result(self):
-        return self.o_acc.to(self.q.dtype), self.lse_acc
+        return self.o_acc.to(self.q.dtype, copy=True), self.lse_acc.clone()
 
 
 class _Backward:
-    def __init__(self, ops, q, k, v, o, lse, dout, rank, world, causal):
+    def __init__(self, ops, q, k, v, o, lse, dout, rank, world, causal, cache=None):
         self.ops, self.q, self.o, self.lse, self.dout = ops, q, o, lse, dout
-        self.rank, self.world, self.causal = rank, world, causal
-        self.kv = torch.stack([k, v]).contiguous()
-        self.dkv = torch.zeros(self.kv.shape, dtype=torch.float32, device=q.device)   # travels with kv
-        self.dq_acc = torch.zeros(q.shape, dtype=torch.float32, device=q.device)
+        self.rank, self.world, self.causal, self.cache = rank, world, causal, cache
+        self.kv = [k, v]
+        f32 = torch.float32
+        # fp32 [dK, dV] of the slice currently held; they travel with it
+        self.dkv = [_buf(cache, "dk_acc", k.shape, f32, q.device), _buf(cache, "dv_acc", v.shape, f32, q.device)]
+        self.dq_acc = _buf(cache, "dq_acc", q.shape, f32, q.device)
         c = q.shape[2] // 2
-        self._lse_hi = lse[:, :, c:].contiguous() if causal else None
+        self._lse_hi = lse[:, :, c:].contiguous() if causal and world > 1 else None
 
-    def compute(self, step):
+    def kernels(self, step):
+        """The step's partial gradients (dq, dk, dv) and the rows they belong to."""
+        q = self.q
+        B, H, L, D = q.shape
         src = (self.rank - step) % self.world
-        L = self.q.shape[2]
         (qs, qn), (ks, kn), cz = block_plan(self.rank, src, L, self.causal)
         lse = self.lse if qn == L else self._lse_hi
         rows = slice(qs, qs + qn)
-        dq, dk, dv = self.ops.block_bwd(self.q[:, :, rows], self.kv[0][:, :, ks:ks + kn],
-                                        self.kv[1][:, :, ks:ks + kn], self.o[:, :, rows], lse,
-                                        self.dout[:, :, rows], cz)
+        outs = dict(dq=_buf(self.cache, "dq_blk", (B, H, qn, D), q.dtype, q.device),
+                    dk=_buf(self.cache, "dk_blk", (B, H, kn, D), q.dtype, q.device),
+                    dv=_buf(self.cache, "dv_blk", (B, H, kn, D), q.dtype, q.device))
+        parts = self.ops.block_bwd(q[:, :, rows], self.kv[0][:, :, ks:ks + kn], self.kv[1][:, :, ks:ks + kn],
+                                   self.o[:, :, rows], lse, self.dout[:, :, rows], cz, **outs)
+        return parts, qs, ks
+
+    def absorb(self, step, parts, qs, ks):
+        dq, dk, dv = parts
+        if step == 0:                                          # own slice: full rows on both sides
+            self.dq_acc.copy_(dq)
+            self.dkv[0].copy_(dk)
+            self.dkv[1].copy_(dv)
+            return
         self.ops.accumulate(self.dq_acc, dq, qs)
         self.ops.accumulate(self.dkv[0], dk, ks)
         self.ops.accumulate(self.dkv[1], dv, ks)
 
     def result(self):
         dt = self.q.dtype
-        return self.dq_acc.to(dt), self.dkv[0].to(dt), self.dkv[1].to(dt)
+        return tuple(t.to(dt, copy=True) for t in (self.dq_acc, self.dkv[0], self.dkv[1]))
 
 
 # ---- drivers -----------------------------------------------------------------------------------------------
-def ring_attention_fwd(ops, q, k, v, rank, world, causal=False, exchange=None):
+def ring_attention_fwd(ops, q, k, v, rank, world, causal=False, exchange=None, cache=None):
     """Forward of the rank's query slice against the whole sequence.  q, k, v: the rank's slices
-    [B, H, L, D] (``shard_sequence``).  Returns (o [B, H, L, D] in q's dtype, lse [B, H, L] fp32)."""
-    exchange = exchange or RingExchange(rank, world)
-    st = _Forward(ops, q, k, v, rank, world, causal)
+    [B, H, L, D] (``shard_sequence``), contiguous.  Returns (o [B, H, L, D] in q's dtype, lse [B, H, L] fp32).
+    ``cache``: a dict the caller keeps between calls; all scratch and receive buffers then live in it."""
+    if world == 1:
+        return ops.block_fwd(q, k, v, causal)
+    exchange = exchange or RingExchange(rank, world, cache=cache)
+    st = _Forward(ops, q, k, v, rank, world, causal, cache)
     for step in range(world):
-        moving = exchange.start([st.kv]) if step + 1 < world else None   # next slice arrives during this step
+        moving = exchange.start(st.kv, "kv") if step + 1 < world else None   # arrives during this step
         st.compute(step)
         if moving is not None:
-            st.kv = moving.wait()[0]
+            st.kv = moving.wait()
     return st.result()
 
 
-def ring_attention_bwd(ops, q, k, v, o, lse, dout, rank, world, causal=False, exchange=None):
+def ring_attention_bwd(ops, q, k, v, o, lse, dout, rank, world, causal=False, exchange=None, cache=None):
     """Backward of ``ring_attention_fwd``: (dq, dk, dv) of the rank's slices."""
-    exchange = exchange or RingExchange(rank, world)
-    st = _Backward(ops, q, k, v, o, lse, dout, rank, world, causal)
+    if world == 1:
+        return ops.block_bwd(q, k, v, o, lse, dout, causal)
+    exchange = exchange or RingExchange(rank, world, cache=cache)
+    st = _Backward(ops, q, k, v, o, lse, dout, rank, world, causal, cache)
+    arriving = None
     for step in range(world):
-        moving = exchange.start([st.kv]) if step + 1 < world else None
-        st.compute(step)
+        moving = exchange.start(st.kv, "kv") if step + 1 < world else None
+        parts = st.kernels(step)                 # runs while the previous hop of the gradients is in flight
+        if arriving is not None:
+            st.dkv = arriving.wait()
+        st.absorb(step, *parts)
         # the gradient accumulators follow their slice once this rank has added its share; after the last
         # step they belong to rank+1, so the same hop brings every slice's gradients home
-        grads = exchange.start([st.dkv]) if world > 1 else None
+        arriving = exchange.start(st.dkv, "dkv")
         if moving is not None:
-            st.kv = moving.wait()[0]
-        if grads is not None:
-            st.dkv = grads.wait()[0]
+            st.kv = moving.wait()
+    st.dkv = arriving.wait()
     return st.result()
 
 
@@ -234,7 +286,7 @@ def ring_attention_bwd_emulated(ops, qs, ks, vs, os_, lses, douts, causal=False)
               for r in range(world)]
     for step in range(world):
         for s in states:
-            s.compute(step)
+            s.absorb(step, *s.kernels(step))
         if step + 1 < world:
             _rotate(states, "kv")
         if world > 1:

@@ -32,13 +32,18 @@ class NumpyOps:
             s = np.where(j <= i, s, -np.inf)
         return s
 
-    def block_fwd(self, q, k, v, causal):
+    def block_fwd(self, q, k, v, causal, out=None, lse=None):
         s = self._scores(q, k, causal)
         m = s.max(-1, keepdims=True)
         p = np.exp(s - m)
         l = p.sum(-1, keepdims=True)
         o = np.einsum("bhij,bhjd->bhid", p / l, v.numpy().astype(np.float64))
-        return torch.from_numpy(o), torch.from_numpy((m + np.log(l))[..., 0]).float()
+        o, l = torch.from_numpy(o), torch.from_numpy((m + np.log(l))[..., 0]).float()
+        if out is not None:
+            out.copy_(o)
+            lse.copy_(l)
+            return out, lse
+        return o, l
 
     def merge(self, o_acc, lse_acc, o_blk, lse_blk, s0):
         n = o_blk.shape[2]
@@ -48,7 +53,8 @@ class NumpyOps:
                                   + o_blk.double() * torch.exp(lb - new)[..., None]).float()
         lse_acc[:, :, s0:s0 + n] = new.float()
 
-    def block_bwd(self, q, k, v, o, lse, dout, causal):
+    def block_bwd(self, q, k, v, o, lse, dout, causal, dq=None, dk=None, dv=None):
+        outs = (dq, dk, dv)
         s = self._scores(q, k, causal)
         p = np.exp(s - lse.numpy().astype(np.float64)[..., None])
         do = dout.numpy().astype(np.float64)
@@ -58,7 +64,9 @@ class NumpyOps:
         ds = p * (dp - delta) * self.scale
         dq = np.einsum("bhij,bhjd->bhid", ds, k.numpy().astype(np.float64))
         dk = np.einsum("bhij,bhid->bhjd", ds, q.numpy().astype(np.float64))
-        return tuple(torch.from_numpy(a) for a in (dq, dk, dv))
+        for dst, a in zip(outs, (dq, dk, dv)):
+            dst.copy_(torch.from_numpy(a))
+        return outs
 
     def accumulate(self, acc, part, s0):
         acc[:, :, s0:s0 + part.shape[2]] += part.float()
