@@ -272,13 +272,16 @@ def model_step_measurement(args):
     x_in = torch.randn((B, S, Cin), generator=g, device=dev)
     kw = dict(scale=1 / math.sqrt(W), causal=True, time_major=False, mode=_lib.MODE_BF16)
     attn_events = []
+    # the forward keeps its intermediates for the backward (no recomputation inside the step)
+    saved = ctx.tsa_saved_buffer(torch.empty((B * S, E), device=dev), wq, wk, wv, wo, B, S, H, W,
+                                 mode=_lib.MODE_BF16, causal=True)
 
     class Attention(torch.autograd.Function):
         @staticmethod
         def forward(fctx, x, wq_, wk_, wv_, wo_):
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
-            out = ctx.tsa_fwd(x, wq_, wk_, wv_, wo_, B, S, H, W, gamma=a_gamma, beta=a_beta, **kw)
+            out = ctx.tsa_fwd(x, wq_, wk_, wv_, wo_, B, S, H, W, gamma=a_gamma, beta=a_beta, saved=saved, **kw)
             e1.record()
             attn_events.append((e0, e1))
             fctx.save_for_backward(x, wq_, wk_, wv_, wo_)
@@ -289,7 +292,8 @@ def model_step_measurement(args):
             x, wq_, wk_, wv_, wo_ = fctx.saved_tensors
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
-            grads = ctx.tsa_bwd(x, wq_, wk_, wv_, wo_, dy.contiguous(), B, S, H, W, **kw)
+            grads = ctx.tsa_bwd(x, wq_, wk_, wv_, wo_, dy.contiguous(), B, S, H, W, saved=saved,
+                                reuse_forward=True, **kw)
             e1.record()
             attn_events.append((e0, e1))
             return grads

@@ -226,12 +226,23 @@ class Context:
         p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel()
         return ws
 
+    def tsa_saved_buffer(self, x, wq, wk, wv, wo, B, S, H, head_width, mode=_lib.MODE_AUTO, causal=False):
+        """A buffer for the forward's intermediates: give it to ``tsa_fwd(saved=...)`` and then to
+        ``tsa_bwd(saved=..., reuse_forward=True)`` to skip the backward's recomputation of the forward."""
+        p = self._tsa_params(x, wq, wk, wv, wo, B, S, H, head_width, 1.0, causal, False, False, False, None, None,
+                             None, mode, (None, None, None, None))
+        need = C.c_size_t(0)
+        self.check(self.lib.ltca_tsa_saved_bytes(C.byref(p), C.byref(need)))
+        return torch.empty(need.value, dtype=torch.uint8, device=x.device)
+
     def tsa_fwd(self, x, wq, wk, wv, wo, B, S, H, head_width, scale=1.0, causal=False, time_major=True,
                 use_residual=True, use_layer_norm=True, gamma=None, beta=None, keep_mask=None,
-                mode=_lib.MODE_AUTO, bq=None, bk=None, bv=None, bo=None):
+                mode=_lib.MODE_AUTO, bq=None, bk=None, bv=None, bo=None, saved=None):
         """out = LayerNorm(x + MHA(x)); x [B*S, E] fp32, weights as in ``ltca_tsa_params``."""
         p = self._tsa_params(x, wq, wk, wv, wo, B, S, H, head_width, scale, causal, time_major,
                              use_residual, use_layer_norm, gamma, beta, keep_mask, mode, (bq, bk, bv, bo))
+        if saved is not None:
+            p.saved, p.saved_bytes = saved.data_ptr(), saved.numel()
         out = torch.empty_like(x)
         p.out = out.data_ptr()
         ws = self._tsa_workspace(p, 0)
@@ -240,10 +251,12 @@ class Context:
         return out
 
     def tsa_bwd(self, x, wq, wk, wv, wo, dy, B, S, H, head_width, scale=1.0, causal=False, time_major=True,
-                keep_mask=None, mode=_lib.MODE_AUTO, bq=None, bk=None, bv=None):
+                keep_mask=None, mode=_lib.MODE_AUTO, bq=None, bk=None, bv=None, saved=None, reuse_forward=False):
         """(dx, dwq, dwk, dwv, dwo) of the module; LayerNorm and residual pass dy through."""
         p = self._tsa_params(x, wq, wk, wv, wo, B, S, H, head_width, scale, causal, time_major,
                              False, False, None, None, keep_mask, mode, (bq, bk, bv, None))
+        if saved is not None:
+            p.saved, p.saved_bytes, p.reuse_forward = saved.data_ptr(), saved.numel(), int(reuse_forward)
         dx = torch.empty_like(x)
         # the four weight gradients are views of one allocation, so a multi-GPU caller sums them over the
         # ranks with a single collective on that allocation (shard.sum_weight_grads) without packing them

@@ -448,20 +448,38 @@ int check(ltca_ctx* ctx, const ltca_tsa_params* t) {
     if (!(t->scale > 0.f)) return fail(ctx, LTCA_ERR_INVALID, "scale must be positive");
     if (reinterpret_cast<uintptr_t>(t->workspace) & 255)
         return fail(ctx, LTCA_ERR_INVALID, "workspace must be 256-byte aligned");
+    if (t->reuse_forward && !t->saved)
+        return fail(ctx, LTCA_ERR_INVALID, "reuse_forward needs the saved block of the forward call");
+    if (t->saved) {
+        if (t->pre_norm)
+            return fail(ctx, LTCA_ERR_UNSUPPORTED, "the saved block is not available in the pre_norm form");
+        if (reinterpret_cast<uintptr_t>(t->saved) & 255)
+            return fail(ctx, LTCA_ERR_INVALID, "saved must be 256-byte aligned");
+        size_t need = 0;
+        int rc = ltca_tsa_saved_bytes(t, &need);
+        if (rc) return fail(ctx, rc, "bad shape for the saved block");
+        if (t->saved_bytes < need)
+            return fail(ctx, LTCA_ERR_WORKSPACE, "the saved block needs %zu bytes", need);
+    }
     return LTCA_OK;
 }
 
 // Projections + attention forward into workspace; returns pointers into it.
 struct FwdBufs { float *q, *k, *v, *ctx, *lse; char* rest; };
 
+// With a caller-kept `saved` block (ltca_tsa_params.saved) q, k, v, ctx and lse live there and the
+// workspace only holds the attention scratch; with reuse_forward they are taken as they are.
 int forward_core(ltca_ctx* ctx, const ltca_tsa_params* t, const Plan& pl, char* w, FwdBufs* fb,
                  size_t attn_ws_bytes) {
+    char* rest = w;
+    if (t->saved) w = reinterpret_cast<char*>(t->saved);
     fb->q = reinterpret_cast<float*>(w);   w += pl.buf;
     fb->k = reinterpret_cast<float*>(w);   w += pl.buf;
     fb->v = reinterpret_cast<float*>(w);   w += pl.buf;
     fb->ctx = reinterpret_cast<float*>(w); w += pl.buf;
     fb->lse = reinterpret_cast<float*>(w); w += pl.lse;
-    fb->rest = w;
+    fb->rest = t->saved ? rest : w;
+    if (t->saved && t->reuse_forward) return LTCA_OK;
     const int rows = (int)pl.rows, E = t->E, HW = pl.HW;
     int rc;
     if ((rc = gemm(ctx, t->x, t->wq, t->bq, fb->q, rows, HW, E, E, HW, HW, 0, 0, 0))) return rc;
@@ -537,6 +555,8 @@ size_t tensor_workspace(const TPlan& pl, int which) {
     return n + pl.partial;
 }
 
+size_t tensor_saved_bytes(const TPlan& pl) { return pl.xb + 3 * pl.w_in + pl.w_out + 4 * pl.act + pl.lse; }
+
 struct TBufs {
     void *xb, *wq, *wk, *wv, *wo, *q, *k, *v, *ctx;
     float* lse;
@@ -545,6 +565,8 @@ struct TBufs {
 
 // bf16 copies, fused Q/K/V projection, attention forward.
 int tensor_forward_core(ltca_ctx* ctx, const ltca_tsa_params* t, const TPlan& pl, char* w, TBufs* tb) {
+    char* rest = w;
+    if (t->saved) w = reinterpret_cast<char*>(t->saved);
     tb->xb = w;  w += pl.xb;
     tb->wq = w;  w += pl.w_in;
     tb->wk = w;  w += pl.w_in;
@@ -555,7 +577,8 @@ int tensor_forward_core(ltca_ctx* ctx, const ltca_tsa_params* t, const TPlan& pl
     tb->v = w;   w += pl.act;
     tb->ctx = w; w += pl.act;
     tb->lse = reinterpret_cast<float*>(w); w += pl.lse;
-    tb->rest = w;
+    tb->rest = t->saved ? rest : w;
+    if (t->saved && t->reuse_forward) return LTCA_OK;
     const int E = t->E, HW = pl.HW, Ep = pl.Ep;
     int rc;
     if ((rc = convert_rows_bf16(ctx, t->x, E, tb->xb, Ep, pl.rows, E))) return rc;
@@ -717,7 +740,7 @@ extern "C" {
 
 // Workspace of the TimeSelfAttention form (no input LayerNorm, no dropout), without the column-sum scratch.
 static int inner_workspace(const ltca_tsa_params* t, int which, size_t* bytes_out) {
-    if (use_tensor(t, which != 0)) {
+    if (use_tensor(t, which != 0 || t->saved != nullptr)) {
         TPlan tp;
         int trc = make_tplan(t, &tp);
         if (trc) return trc;
@@ -752,6 +775,25 @@ static ltca_tsa_params core_form(const ltca_tsa_params* t) {
 }
 static size_t act_bytes(const ltca_tsa_params* t) {
     return align_up((size_t)t->B * t->S * t->E * sizeof(float), 256);
+}
+
+int ltca_tsa_saved_bytes(const ltca_tsa_params* t, size_t* bytes_out) {
+    if (!t || !bytes_out) return LTCA_ERR_INVALID;
+    if (t->pre_norm) return LTCA_ERR_UNSUPPORTED;
+    ltca_tsa_params probe = *t;
+    probe.saved = nullptr;
+    if (use_tensor(&probe, true)) {
+        TPlan tp;
+        int rc = make_tplan(&probe, &tp);
+        if (rc) return rc;
+        *bytes_out = tensor_saved_bytes(tp);
+        return LTCA_OK;
+    }
+    Plan pl;
+    int rc = make_plan(&probe, &pl);
+    if (rc) return rc;
+    *bytes_out = 4 * pl.buf + pl.lse;
+    return LTCA_OK;
 }
 
 int ltca_tsa_workspace_bytes(const ltca_tsa_params* t, int which, size_t* bytes_out) {
@@ -872,7 +914,7 @@ int ltca_tsa_fwd(ltca_ctx* ctx, const ltca_tsa_params* t) {
     if (t->dropout_prob < 0.f || t->dropout_prob >= 1.f)
         return fail(ctx, LTCA_ERR_INVALID, "dropout_prob must be in [0, 1)");
     if (t->pre_norm) return prenorm_forward(ctx, t);
-    if (use_tensor(t, false)) return tensor_forward(ctx, t);
+    if (use_tensor(t, t->saved != nullptr)) return tensor_forward(ctx, t);
     Plan pl;
     if ((rc = make_plan(t, &pl))) return rc;
     size_t need = 0;

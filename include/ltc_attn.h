@@ -222,7 +222,20 @@ typedef struct {
     /* optional outputs of the backward passes (the reference's FlashAttention has no backward; these complete it) */
     float *dbq, *dbk, *dbv, *dbo;   /* bias gradients [H*W], [H*W], [H*W], [E] */
     float *dgamma, *dbeta;          /* LayerNorm parameter gradients [E], pre_norm only */
+    /* Optional: keep the forward's intermediates for the backward.  The reference's API carries nothing from
+     * forward() to backward(), so its caller runs forward() again before every backward()
+     * (src/ml/ml_liquid_net.cu:715-721) and the backward entry points here recompute it once more by default.
+     * A caller that gives the SAME `saved` block (ltca_tsa_saved_bytes, 256-byte aligned) to ltca_tsa_fwd and
+     * then, with x, the weights, the shape and the mode unchanged, to a backward call with reuse_forward = 1
+     * skips that recomputation.  Not available with pre_norm.  With `saved` set the forward takes the pipeline
+     * the backward will take. */
+    void*   saved;
+    size_t  saved_bytes;
+    int32_t reuse_forward;
 } ltca_tsa_params;
+
+/* Size of the `saved` block for this shape and mode. */
+int ltca_tsa_saved_bytes(const ltca_tsa_params* p, size_t* bytes_out);
 
 /* which: 0 forward, 1 backward-data, 2 backward-weights, 3 both backward passes. */
 int ltca_tsa_workspace_bytes(const ltca_tsa_params* p, int which, size_t* bytes_out);

@@ -168,9 +168,24 @@ public:
         CudaMemory<float> out((size_t)batch_size * seq_len * input_dim_, stream);
         ltca_tsa_params p = params(x_seq, batch_size, seq_len, mask);
         p.out = out.get();
+        if (reuse_forward_) {
+            size_t need = 0;
+            b200::check(ctx_.get(stream), ltca_tsa_saved_bytes(&p, &need), "ltca_tsa_saved_bytes");
+            if (need > saved_.bytes()) saved_ = CudaMemory<float>((need + 3) / 4, stream);
+            p.saved = saved_.get();
+            p.saved_bytes = saved_.bytes();
+            saved_x_ = x_seq.get(); saved_mask_ = p.keep_mask; saved_b_ = batch_size; saved_s_ = seq_len;
+        }
         run(p, 0, stream, ltca_tsa_fwd, "ltca_tsa_fwd");
         return out;
     }
+
+    // Extension.  The reference's interface carries nothing from forward() to backward(), so its caller runs
+    // forward() again right before backward() (src/ml/ml_liquid_net.cu:715-721) and backward() here recomputes
+    // it once more.  With this switch on, forward() keeps its intermediates, and a backward() /
+    // backwardWeights() call for the same x_seq buffer, mask and shape uses them instead.  The caller promises
+    // that the contents of x_seq and the weights have not changed in between; any other call recomputes.
+    void setReuseForward(bool on) { reuse_forward_ = on; if (!on) saved_x_ = nullptr; }
 
     CudaMemory<float> backward(const CudaMemory<float>& grad_output, const CudaMemory<float>& x_seq,
                                int batch_size, int seq_len, const CudaMemory<float>* mask = nullptr,
@@ -179,6 +194,7 @@ public:
         ltca_tsa_params p = params(x_seq, batch_size, seq_len, mask);
         p.dy = grad_output.get();
         p.dx = dx.get();
+        attach_saved(p, x_seq, batch_size, seq_len);
         run(p, 1, stream, ltca_tsa_bwd_data, "ltca_tsa_bwd_data");
         return dx;
     }
@@ -190,6 +206,7 @@ public:
         ltca_tsa_params p = params(x_seq, batch_size, seq_len, mask);
         p.dy = grad_output.get();
         p.dwq = dwq_.get(); p.dwk = dwk_.get(); p.dwv = dwv_.get(); p.dwo = dwo_.get();
+        attach_saved(p, x_seq, batch_size, seq_len);
         run(p, 2, stream, ltca_tsa_bwd_weights, "ltca_tsa_bwd_weights");
     }
 
@@ -264,6 +281,13 @@ private:
         p.keep_mask = mask ? mask->get() : nullptr;
         return p;
     }
+    void attach_saved(ltca_tsa_params& p, const CudaMemory<float>& x, int B, int S) const {
+        if (!reuse_forward_ || saved_x_ != x.get() || saved_mask_ != p.keep_mask || saved_b_ != B || saved_s_ != S)
+            return;
+        p.saved = saved_.get();
+        p.saved_bytes = saved_.bytes();
+        p.reuse_forward = 1;
+    }
     template <typename Fn>
     void run(ltca_tsa_params& p, int which, cudaStream_t stream, Fn fn, const char* what) {
         size_t need = 0;
@@ -300,6 +324,11 @@ private:
     CudaMemory<float> wq_, wk_, wv_, wo_, ln_gamma_, ln_beta_;
     CudaMemory<float> dwq_, dwk_, dwv_, dwo_, dgamma_, dbeta_;
     CudaMemory<float> workspace_;
+    bool reuse_forward_ = false;
+    CudaMemory<float> saved_;
+    const float* saved_x_ = nullptr;
+    const float* saved_mask_ = nullptr;
+    int saved_b_ = 0, saved_s_ = 0;
 };
 
 // The reference's FlashAttention module (include/flash_attention.h:19-260, src/ml/flash_attention.cu:485-1150)

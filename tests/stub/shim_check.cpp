@@ -8,6 +8,14 @@ using namespace cudatrader;
 
 std::unique_ptr<TimeSelfAttention> make(int e, int h) { return createB200TimeSelfAttention(e, h); }
 
+CudaMemory<float> step_without_recomputation(B200TimeSelfAttention& tsa, const CudaMemory<float>& x,
+                                             const CudaMemory<float>& dy, int B, int S) {
+    tsa.setReuseForward(true);
+    CudaMemory<float> y = tsa.forward(x, B, S);
+    tsa.backwardWeights(dy, x, B, S);
+    return tsa.backward(dy, x, B, S);
+}
+
 CudaMemory<float> step(TimeSelfAttention& tsa, const CudaMemory<float>& x, const CudaMemory<float>& dy, int B, int S) {
     CudaMemory<float> y = tsa.forward(x, B, S);
     tsa.backwardWeights(dy, x, B, S);

@@ -144,6 +144,40 @@ def test_cuda_module_tensor_pipe_forward_backward(ctx, case):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("mode_name", ["tensor", "exact"])
+def test_backward_from_saved_forward_equals_backward_with_recomputation(ctx, mode_name):
+    """A forward call that keeps its intermediates in a caller-held block, then a backward that reuses them:
+    same bits as the default backward, which recomputes the forward; the forward output is unchanged too."""
+    import math
+    import torch
+    from cuda_ltc_b200 import _lib
+    from cuda_ltc_b200.api import LtcaError
+    B, S, E, H, W = 4, 128, 256, 4, 64
+    mode = _lib.MODE_BF16 if mode_name == "tensor" else _lib.MODE_FP32
+    g = torch.Generator(device="cuda").manual_seed(5)
+    x = torch.randn((B * S, E), generator=g, device="cuda")
+    dy = torch.randn((B * S, E), generator=g, device="cuda")
+    lim = math.sqrt(6.0 / (2 * E))
+    ws = [(torch.rand((E, H * W), generator=g, device="cuda") * 2 - 1) * lim for _ in range(3)]
+    wo = (torch.rand((H * W, E), generator=g, device="cuda") * 2 - 1) * lim
+    gamma, beta = torch.ones(E, device="cuda"), torch.zeros(E, device="cuda")
+    kw = dict(scale=1 / math.sqrt(W), causal=True, time_major=False, mode=mode)
+    plain_out = ctx.tsa_fwd(x, *ws, wo, B, S, H, W, gamma=gamma, beta=beta, **kw)
+    plain = ctx.tsa_bwd(x, *ws, wo, dy, B, S, H, W, **kw)
+    saved = ctx.tsa_saved_buffer(x, *ws, wo, B, S, H, W, mode=mode, causal=True)
+    assert saved.numel() > 0
+    out = ctx.tsa_fwd(x, *ws, wo, B, S, H, W, gamma=gamma, beta=beta, saved=saved, **kw)
+    got = ctx.tsa_bwd(x, *ws, wo, dy, B, S, H, W, saved=saved, reuse_forward=True, **kw)
+    torch.cuda.synchronize()
+    assert ctx.device_status() == 0
+    assert torch.equal(out, plain_out)
+    for a, b in zip(got, plain):
+        assert torch.equal(a, b)
+    with pytest.raises(LtcaError):                       # a block that is too small is refused
+        ctx.tsa_fwd(x, *ws, wo, B, S, H, W, gamma=gamma, beta=beta, saved=saved[:1024], **kw)
+
+
+@pytest.mark.gpu
 def test_cuda_module_reference_form_wide_heads(ctx):
     """The reference's largest configuration, (input_dim, heads) = (512, 8): every head is 512 wide
     (include/cuDNN_ops.h:166-169 of the reference), scale 1.0, no mask, time-major rows.  Forward and backward
