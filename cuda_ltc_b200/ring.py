@@ -246,19 +246,28 @@ def ring_attention_bwd(ops, q, k, v, o, lse, dout, rank, world, causal=False, ex
     exchange = exchange or RingExchange(rank, world, cache=cache)
     st = _Backward(ops, q, k, v, o, lse, dout, rank, world, causal, cache)
     arriving = None
+    dt = q.dtype
     for step in range(world):
-        moving = exchange.start(st.kv, "kv") if step + 1 < world else None
+        last = step + 1 == world
+        moving = exchange.start(st.kv, "kv") if not last else None
         parts = st.kernels(step)                 # runs while the previous hop of the gradients is in flight
         if arriving is not None:
             st.dkv = arriving.wait()
         st.absorb(step, *parts)
         # the gradient accumulators follow their slice once this rank has added its share; after the last
-        # step they belong to rank+1, so the same hop brings every slice's gradients home
-        arriving = exchange.start(st.dkv, "dkv")
+        # step they belong to rank+1, so the same hop brings every slice's gradients home.  Nothing is added
+        # after that hop, so it carries the gradients already rounded to the output type (half the bytes).
+        if last and dt != torch.float32:
+            home = [_buf(cache, f"home.{i}", t.shape, dt, t.device) for i, t in enumerate(st.dkv)]
+            for h, t in zip(home, st.dkv):
+                h.copy_(t)
+            arriving = exchange.start(home, "home")
+        else:
+            arriving = exchange.start(st.dkv, "dkv")
         if moving is not None:
             st.kv = moving.wait()
-    st.dkv = arriving.wait()
-    return st.result()
+    dk, dv = arriving.wait()
+    return st.dq_acc.to(dt, copy=True), dk.to(dt, copy=True), dv.to(dt, copy=True)
 
 
 def _rotate(states, name):
