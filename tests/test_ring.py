@@ -193,3 +193,44 @@ def test_cuda_kernels_under_the_emulated_schedule(world, causal, S, dtype):
         else:
             assert np.abs(g_ - r).max() < tol
     assert ctx.device_status() == 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_merge_and_accumulate_kernels(dtype):
+    """ltca_attn_merge / ltca_accumulate_rows on a row range, rows without a visible key, and argument errors."""
+    from cuda_ltc_b200 import Context
+    from cuda_ltc_b200.api import LtcaError
+    ctx = Context()
+    B, H, S, D, s0, n = 2, 3, 40, 64, 8, 24
+    g = torch.Generator(device="cuda").manual_seed(2)
+    o_acc = torch.randn((B, H, S, D), generator=g, device="cuda")
+    lse_acc = torch.randn((B, H, S), generator=g, device="cuda")
+    lse_acc[0, 0, s0 + 1] = float("-inf")                    # nothing accumulated yet on this row
+    o_blk = torch.randn((B, H, n, D), generator=g, device="cuda").to(dtype)
+    lse_blk = torch.randn((B, H, n), generator=g, device="cuda")
+    lse_blk[1, 2, 3] = float("-inf")                         # this row saw no key in the block
+    want_o, want_l = o_acc.double().clone(), lse_acc.double().clone()
+    la, lb = want_l[:, :, s0:s0 + n], lse_blk.double()
+    new = torch.logaddexp(la, lb)
+    wa = torch.where(torch.isinf(la) & (la < 0), torch.zeros_like(la), torch.exp(la - new))
+    wb = torch.where(torch.isinf(lb) & (lb < 0), torch.zeros_like(lb), torch.exp(lb - new))
+    want_o[:, :, s0:s0 + n] = want_o[:, :, s0:s0 + n] * wa[..., None] + o_blk.double() * wb[..., None]
+    want_l[:, :, s0:s0 + n] = new
+    ctx.attn_merge(o_acc, lse_acc, o_blk, lse_blk, s0)
+    assert torch.allclose(o_acc.double(), want_o, atol=2e-5, rtol=1e-5)
+    assert torch.allclose(lse_acc.double(), want_l, atol=1e-5)
+    assert torch.equal(o_acc[1, 2, s0 + 3].double(), want_o[1, 2, s0 + 3])     # untouched row: same bits
+
+    acc = torch.randn((B, H, S, D), generator=g, device="cuda")
+    part = torch.randn((B, H, n, D), generator=g, device="cuda").to(dtype)
+    want = acc.clone()
+    want[:, :, s0:s0 + n] += part.float()
+    ctx.accumulate_rows(acc, part, s0)
+    assert torch.equal(acc, want)
+
+    with pytest.raises(LtcaError):
+        ctx.accumulate_rows(acc, part, S - n + 1)            # the range runs past the accumulator
+    with pytest.raises(LtcaError):
+        ctx.attn_merge(o_acc, lse_acc, o_blk, lse_blk, S)
+    assert ctx.device_status() == 0
