@@ -98,43 +98,77 @@ __global__ void pack_bf16_kernel(const float* __restrict__ src, ltca_strides st,
 __device__ __forceinline__ float to_f32(float v) { return v; }
 __device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
 
-// One warp per row i of the block (rows s0 .. s0+n of each of the BH accumulator slabs):
+__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4(const __nv_bfloat16* p) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    return make_float4(lo.x, lo.y, hi.x, hi.y);
+}
+
+// Half a warp per row i of the block (rows s0 .. s0+n of each of the BH accumulator slabs), four
+// elements per lane and pass:
 //   lse' = log(exp(lse_acc) + exp(lse_blk)),  o_acc = o_acc * exp(lse_acc - lse') + o_blk * exp(lse_blk - lse').
 // A block row with no visible key carries lse_blk = -inf and leaves the accumulator as it is.
+// D is a multiple of 4 and both tensors are 16-byte aligned (checked by the caller).
 template <typename T>
 __global__ void attn_merge_kernel(float* __restrict__ o_acc, float* __restrict__ lse_acc,
                                   const T* __restrict__ o_blk, const float* __restrict__ lse_blk,
                                   int64_t BH, int S_acc, int s0, int n, int D) {
-    const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (row >= BH * n) return;
-    const int lane = threadIdx.x & 31;
-    const int64_t bh = row / n;
-    const int i = (int)(row % n);
-    const int64_t arow = bh * S_acc + s0 + i;
-    const float la = lse_acc[arow], lb = lse_blk[row];
-    if (lb == -INFINITY) return;
-    const float m = fmaxf(la, lb);
-    const float ea = (la == -INFINITY) ? 0.f : __expf(la - m), eb = __expf(lb - m);
-    const float inv = 1.f / (ea + eb);
-    const float wa = ea * inv, wb = eb * inv;
-    float* oa = o_acc + arow * D;
-    const T* ob = o_blk + row * D;
-    for (int d = lane; d < D; d += 32) oa[d] = oa[d] * wa + to_f32(ob[d]) * wb;
-    __syncwarp();
-    if (lane == 0) lse_acc[arow] = m + __logf(ea + eb);
+    const int64_t row = ((int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * 2 + ((threadIdx.x >> 4) & 1);
+    const bool live = row < BH * n;
+    const int sub = threadIdx.x & 15;
+    int64_t arow = 0;
+    float wa = 1.f, wb = 0.f, lnew = 0.f;
+    bool touch = false;
+    if (live) {
+        const int64_t bh = row / n;
+        const int i = (int)(row % n);
+        arow = bh * S_acc + s0 + i;
+        const float la = lse_acc[arow], lb = lse_blk[row];
+        if (lb != -INFINITY) {
+            const float m = fmaxf(la, lb);
+            const float ea = (la == -INFINITY) ? 0.f : __expf(la - m), eb = __expf(lb - m);
+            const float inv = 1.f / (ea + eb);
+            wa = ea * inv;
+            wb = eb * inv;
+            lnew = m + __logf(ea + eb);
+            touch = true;
+        }
+    }
+    if (touch) {
+        float* oa = o_acc + arow * D;
+        const T* ob = o_blk + row * D;
+        for (int d = 4 * sub; d < D; d += 64) {
+            float4 a = *reinterpret_cast<float4*>(oa + d);
+            const float4 b = load4(ob + d);
+            a.x = a.x * wa + b.x * wb;
+            a.y = a.y * wa + b.y * wb;
+            a.z = a.z * wa + b.z * wb;
+            a.w = a.w * wa + b.w * wb;
+            *reinterpret_cast<float4*>(oa + d) = a;
+        }
+    }
+    __syncwarp();                        // every lane has read the old lse before it is replaced
+    if (touch && sub == 0) lse_acc[arow] = lnew;
 }
 
-// acc[bh][s0 + i][d] += part[bh][i][d]
+// acc[bh][s0 + i][d] += part[bh][i][d], four elements per thread (D is a multiple of 4)
 template <typename T>
-__global__ void accumulate_rows_kernel(float* __restrict__ acc, const T* __restrict__ part, int64_t total,
+__global__ void accumulate_rows_kernel(float* __restrict__ acc, const T* __restrict__ part, int64_t total4,
                                        int S_acc, int s0, int n, int D) {
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-    for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += stride) {
-        const int d = (int)(e % D);
-        const int64_t r = e / D;
+    const int D4 = D >> 2;
+    for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < total4; e += stride) {
+        const int d = (int)(e % D4) * 4;
+        const int64_t r = e / D4;
         const int64_t bh = r / n;
         const int i = (int)(r % n);
-        acc[(bh * S_acc + s0 + i) * D + d] += to_f32(part[e]);
+        float* dst = acc + (bh * S_acc + s0 + i) * D + d;
+        float4 a = *reinterpret_cast<float4*>(dst);
+        const float4 b = load4(part + e * 4);
+        a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+        *reinterpret_cast<float4*>(dst) = a;
     }
 }
 
@@ -386,8 +420,10 @@ int ltca_attn_merge(ltca_ctx* ctx, float* o_acc, float* lse_acc, const void* o_b
         return fail(ctx, LTCA_ERR_INVALID, "bad row range %d + %d of %d", s0, n, S_acc);
     if (blk_dtype != LTCA_F32 && blk_dtype != LTCA_BF16) return fail(ctx, LTCA_ERR_INVALID, "bad dtype");
     if (BH * n == 0) return LTCA_OK;
-    const int wpb = 8;
-    const unsigned grid = (unsigned)((BH * n + wpb - 1) / wpb);
+    if ((D & 3) || ((reinterpret_cast<uintptr_t>(o_acc) | reinterpret_cast<uintptr_t>(o_blk)) & 15))
+        return fail(ctx, LTCA_ERR_INVALID, "head_dim must be a multiple of 4 and the tensors 16-byte aligned");
+    const int wpb = 8;                                         // two rows per warp
+    const unsigned grid = (unsigned)((BH * n + 2 * wpb - 1) / (2 * wpb));
     if (blk_dtype == LTCA_F32)
         attn_merge_kernel<float><<<grid, wpb * 32, 0, ctx->stream>>>(
             o_acc, lse_acc, static_cast<const float*>(o_blk), lse_blk, BH, S_acc, s0, n, D);
@@ -405,7 +441,9 @@ int ltca_accumulate_rows(ltca_ctx* ctx, float* acc, const void* part, int32_t pa
     if (BH < 0 || S_acc < 0 || s0 < 0 || n < 0 || D < 1 || s0 + n > S_acc)
         return fail(ctx, LTCA_ERR_INVALID, "bad row range %d + %d of %d", s0, n, S_acc);
     if (part_dtype != LTCA_F32 && part_dtype != LTCA_BF16) return fail(ctx, LTCA_ERR_INVALID, "bad dtype");
-    const int64_t total = BH * n * D;
+    if ((D & 3) || ((reinterpret_cast<uintptr_t>(acc) | reinterpret_cast<uintptr_t>(part)) & 15))
+        return fail(ctx, LTCA_ERR_INVALID, "head_dim must be a multiple of 4 and the tensors 16-byte aligned");
+    const int64_t total = BH * n * (D >> 2);
     if (total == 0) return LTCA_OK;
     const int grid = blocks_for((size_t)total, 256, ctx->sm_count);
     if (part_dtype == LTCA_F32)
