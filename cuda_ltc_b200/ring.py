@@ -266,8 +266,9 @@ def ring_attention_bwd(ops, q, k, v, o, lse, dout, rank, world, causal=False, ex
             arriving = exchange.start(st.dkv, "dkv")
         if moving is not None:
             st.kv = moving.wait()
+    dq = st.dq_acc.to(dt, copy=True)             # while the hop home is in flight
     dk, dv = arriving.wait()
-    return st.dq_acc.to(dt, copy=True), dk.to(dt, copy=True), dv.to(dt, copy=True)
+    return dq, dk.to(dt, copy=True), dv.to(dt, copy=True)
 
 
 def _rotate(states, name):
