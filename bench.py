@@ -374,7 +374,7 @@ def ring_measurement(args):
     g = torch.Generator(device=dev).manual_seed(SEED + rank)
     mk = lambda: (torch.randn((B, H, L, D), generator=g, device=dev) * 0.5).bfloat16()
     q, k, v, do = mk(), mk(), mk(), mk()
-    ops = ring.CudaOps(ctx)
+    ops = ring.CudaOps(ctx, comm_sms=args.comm_sms)
     cache = {}                                          # scratch and receive buffers live across the steps
     n, w = max(5, args.steps), max(3, args.warmup)
 
@@ -405,6 +405,7 @@ def ring_measurement(args):
     print(json.dumps({"workload": f"attention fwd+bwd, B={B} H={H} S={S} D={D} causal bf16, sequence dealt out over "
                                   f"{world} GPU(s) with ring K/V exchange (strong scaling)",
                       "n_gpus": world, "ms_per_step": ms, "tflops_whole_job": flops / ms / 1e9,
+                      "comm_sms": args.comm_sms if world > 1 else 0,
                       "kv_bytes_per_hop_per_gpu": 2 * B * H * L * D * 2,
                       "dkv_bytes_per_hop_per_gpu": 2 * B * H * L * D * 4, "device_status": status}))
 
@@ -423,6 +424,8 @@ def main():
                     help="profiler capture mode: 1 warm-up, 1 step, no end-to-end or CPU legs (not a bench value)")
     ap.add_argument("--seq-len", type=int, default=0, help="sequence length of the --ring measurement (default: the "
                                                            "bench configuration's)")
+    ap.add_argument("--comm-sms", type=int, default=16,
+                    help="--ring: SMs the attention kernels leave free for the exchange's copy kernels")
     ap.add_argument("--ring", action="store_true",
                     help="side measurement, not the bench line: the same problem with the sequence dealt out over "
                          "the ranks and K/V exchanged round a ring (launch one rank per GPU)")

@@ -74,6 +74,7 @@ EXPORTS = {
     "ltca_ctx_last_bwd_kernel_ms": (C.c_int, [C.c_void_p, C.POINTER(C.c_float)]),
     "ltca_ctx_destroy": (None, [C.c_void_p]),
     "ltca_last_error": (C.c_char_p, [C.c_void_p]),
+    "ltca_ctx_set_sm_limit": (C.c_int, [C.c_void_p, C.c_int32]),
     "ltca_device_status": (C.c_int, [C.c_void_p, C.POINTER(C.c_uint32)]),
     "ltca_attn_workspace_bytes": (C.c_int, [C.POINTER(AttnParams), C.c_int, C.POINTER(C.c_size_t)]),
     "ltca_attn_uses_tensor_pipe": (C.c_int, [C.POINTER(AttnParams), C.c_int]),

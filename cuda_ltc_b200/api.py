@@ -82,6 +82,14 @@ class Context:
         if rc != 0:
             raise LtcaError(rc, self.lib.ltca_last_error(self.handle).decode())
 
+    def set_sm_limit(self, n_sms: int = 0):
+        """Cap the SMs the persistent kernels spread over (0 = all): leaves room for a communication
+        library's kernels to run beside them."""
+        self.check(self.lib.ltca_ctx_set_sm_limit(self.handle, int(n_sms)))
+
+    def sm_count(self) -> int:
+        return torch.cuda.get_device_properties(self.device).multi_processor_count
+
     def device_status(self) -> int:
         v = C.c_uint32(0)
         self.lib.ltca_device_status(self.handle, C.byref(v))

@@ -254,7 +254,7 @@ int ltca_ctx_create(int device, void* stream, ltca_ctx** out) {
         delete ctx;
         return LTCA_ERR_CUDA;
     }
-    ctx->sm_count = prop.multiProcessorCount;
+    ctx->sm_count = ctx->sm_device = prop.multiProcessorCount;
     ctx->cc_major = prop.major;
     ctx->cc_minor = prop.minor;
     if (prop.major != 10) {
@@ -395,6 +395,12 @@ int ltca_attn_decode(ltca_ctx* ctx, const ltca_attn_params* p) {
 int ltca_attn_decode_workspace_bytes(const ltca_attn_params* p, size_t* bytes_out) {
     if (!p || !bytes_out) return LTCA_ERR_INVALID;
     *bytes_out = attn_decode_workspace(p);
+    return LTCA_OK;
+}
+
+int ltca_ctx_set_sm_limit(ltca_ctx* ctx, int32_t n_sms) {
+    if (!ctx) return LTCA_ERR_INVALID;
+    ctx->sm_count = (n_sms <= 0 || n_sms > ctx->sm_device) ? ctx->sm_device : n_sms;
     return LTCA_OK;
 }
 

@@ -15,7 +15,8 @@
 struct ltca_ctx {
     int device = 0;
     cudaStream_t stream = nullptr;
-    int sm_count = 0;
+    int sm_count = 0;                 // SMs the persistent kernels spread over (ltca_ctx_set_sm_limit)
+    int sm_device = 0;                // SMs of the device
     int cc_major = 0, cc_minor = 0;
     uint32_t* d_status = nullptr;     // device status word (allocated once at context creation)
     int* d_sched = nullptr;           // work-item counters of the persistent kernels (same allocation:

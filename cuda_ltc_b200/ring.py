@@ -81,10 +81,20 @@ def block_plan(rank: int, src: int, local_len: int, causal: bool) -> Tuple[Tuple
 class CudaOps:
     """The steps' arithmetic on this library's kernels (``Context``); raises if the library is missing."""
 
-    def __init__(self, ctx, scale=None, mode=None):
+    def __init__(self, ctx, scale=None, mode=None, comm_sms=16):
+        """``comm_sms``: SMs left free while slices are in flight.  The attention kernels are persistent (one
+        CTA per SM for the whole launch), so without free SMs the communication library's copy kernels would
+        only start when an attention kernel ends and the exchange would not overlap the arithmetic."""
         from . import _lib
-        self.ctx, self.scale = ctx, scale
+        self.ctx, self.scale, self.comm_sms = ctx, scale, comm_sms
         self.mode = _lib.MODE_AUTO if mode is None else mode
+
+    def begin(self):
+        if self.comm_sms > 0:
+            self.ctx.set_sm_limit(max(1, self.ctx.sm_count() - self.comm_sms))
+
+    def end(self):
+        self.ctx.set_sm_limit(0)
 
     def block_fwd(self, q, k, v, causal, out=None, lse=None):
         return self.ctx.attn_fwd(q, k, v, scale=self.scale, causal=causal, mode=self.mode, out=out, lse=lse)
@@ -231,11 +241,15 @@ def ring_attention_fwd(ops, q, k, v, rank, world, causal=False, exchange=None, c
         return ops.block_fwd(q, k, v, causal)
     exchange = exchange or RingExchange(rank, world, cache=cache)
     st = _Forward(ops, q, k, v, rank, world, causal, cache)
-    for step in range(world):
-        moving = exchange.start(st.kv, "kv") if step + 1 < world else None   # arrives during this step
-        st.compute(step)
-        if moving is not None:
-            st.kv = moving.wait()
+    getattr(ops, "begin", lambda: None)()
+    try:
+        for step in range(world):
+            moving = exchange.start(st.kv, "kv") if step + 1 < world else None   # arrives during this step
+            st.compute(step)
+            if moving is not None:
+                st.kv = moving.wait()
+    finally:
+        getattr(ops, "end", lambda: None)()
     return st.result()
 
 
@@ -247,25 +261,29 @@ def ring_attention_bwd(ops, q, k, v, o, lse, dout, rank, world, causal=False, ex
     st = _Backward(ops, q, k, v, o, lse, dout, rank, world, causal, cache)
     arriving = None
     dt = q.dtype
-    for step in range(world):
-        last = step + 1 == world
-        moving = exchange.start(st.kv, "kv") if not last else None
-        parts = st.kernels(step)                 # runs while the previous hop of the gradients is in flight
-        if arriving is not None:
-            st.dkv = arriving.wait()
-        st.absorb(step, *parts)
-        # the gradient accumulators follow their slice once this rank has added its share; after the last
-        # step they belong to rank+1, so the same hop brings every slice's gradients home.  Nothing is added
-        # after that hop, so it carries the gradients already rounded to the output type (half the bytes).
-        if last and dt != torch.float32:
-            home = [_buf(cache, f"home.{i}", t.shape, dt, t.device) for i, t in enumerate(st.dkv)]
-            for h, t in zip(home, st.dkv):
-                h.copy_(t)
-            arriving = exchange.start(home, "home")
-        else:
-            arriving = exchange.start(st.dkv, "dkv")
-        if moving is not None:
-            st.kv = moving.wait()
+    getattr(ops, "begin", lambda: None)()
+    try:
+        for step in range(world):
+            last = step + 1 == world
+            moving = exchange.start(st.kv, "kv") if not last else None
+            parts = st.kernels(step)                 # runs while the previous hop of the gradients is in flight
+            if arriving is not None:
+                st.dkv = arriving.wait()
+            st.absorb(step, *parts)
+            # the gradient accumulators follow their slice once this rank has added its share; after the last
+            # step they belong to rank+1, so the same hop brings every slice's gradients home.  Nothing is added
+            # after that hop, so it carries the gradients already rounded to the output type (half the bytes).
+            if last and dt != torch.float32:
+                home = [_buf(cache, f"home.{i}", t.shape, dt, t.device) for i, t in enumerate(st.dkv)]
+                for h, t in zip(home, st.dkv):
+                    h.copy_(t)
+                arriving = exchange.start(home, "home")
+            else:
+                arriving = exchange.start(st.dkv, "dkv")
+            if moving is not None:
+                st.kv = moving.wait()
+    finally:
+        getattr(ops, "end", lambda: None)()
     dq = st.dq_acc.to(dt, copy=True)             # while the hop home is in flight
     dk, dv = arriving.wait()
     return dq, dk.to(dt, copy=True), dv.to(dt, copy=True)

@@ -120,6 +120,11 @@ int ltca_ctx_last_bwd_kernel_ms(ltca_ctx* ctx, float* ms_out);
 /* Reads and clears the device status word that kernels set when a bounded wait ran out or an
  * internal check failed.  Synchronises the context's stream.  0 = clean. */
 int ltca_device_status(ltca_ctx* ctx, uint32_t* status_out);
+/* The persistent kernels of this context launch one CTA per SM; n_sms caps that number so that other work
+ * on the GPU (a communication library's copy kernels while slices are exchanged between GPUs) finds free SMs
+ * at once instead of waiting for a whole kernel to end.  n_sms <= 0 or above the device's count restores the
+ * default (all SMs).  Takes effect from the next launch. */
+int ltca_ctx_set_sm_limit(ltca_ctx* ctx, int32_t n_sms);
 
 /* ---- attention core --------------------------------------------------------------------- */
 
