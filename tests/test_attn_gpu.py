@@ -330,3 +330,24 @@ def test_host_step_pipeline_matches_direct_calls(ctx):
     assert ctx2.device_status() == 0
     for got, ref in zip(host_out, (o, dq, dk, dv)):
         assert torch.equal(got, ref.cpu())
+
+
+def test_sm_limit_changes_the_launch_width_not_the_results(ctx):
+    """Capping the SMs the persistent kernels spread over (room for a communication library's kernels)
+    must leave forward and backward results bit-identical; 0 restores the default."""
+    import torch
+    g = torch.Generator(device="cuda").manual_seed(4)
+    q, k, v, do = ((torch.randn((2, 4, 1024, 64), generator=g, device="cuda") * 0.5).bfloat16() for _ in range(4))
+    o, lse = ctx.attn_fwd(q, k, v, causal=True)
+    grads = ctx.attn_bwd(q, k, v, o, lse, do, causal=True)
+    try:
+        ctx.set_sm_limit(ctx.sm_count() - 40)
+        o2, lse2 = ctx.attn_fwd(q, k, v, causal=True)
+        grads2 = ctx.attn_bwd(q, k, v, o2, lse2, do, causal=True)
+    finally:
+        ctx.set_sm_limit(0)
+    torch.cuda.synchronize()
+    assert ctx.device_status() == 0
+    assert torch.equal(o, o2) and torch.equal(lse, lse2)
+    for a, b in zip(grads, grads2):
+        assert torch.equal(a, b)
