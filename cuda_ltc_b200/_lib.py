@@ -76,6 +76,7 @@ EXPORTS = {
     "ltca_last_error": (C.c_char_p, [C.c_void_p]),
     "ltca_ctx_set_sm_limit": (C.c_int, [C.c_void_p, C.c_int32]),
     "ltca_device_status": (C.c_int, [C.c_void_p, C.POINTER(C.c_uint32)]),
+    "ltca_selftest_bounded_wait": (C.c_int, [C.c_void_p, C.c_uint32]),
     "ltca_attn_workspace_bytes": (C.c_int, [C.POINTER(AttnParams), C.c_int, C.POINTER(C.c_size_t)]),
     "ltca_attn_uses_tensor_pipe": (C.c_int, [C.POINTER(AttnParams), C.c_int]),
     "ltca_attn_fwd": (C.c_int, [C.c_void_p, C.POINTER(AttnParams)]),

@@ -95,6 +95,46 @@ class Context:
         self.lib.ltca_device_status(self.handle, C.byref(v))
         return int(v.value)
 
+    def selftest_bounded_wait(self, limit_us: int = 20000):
+        """Launches the wait self-test: one warp waits `limit_us` for a barrier that never completes, gives up
+        and sets the time-out bit that :meth:`device_status` then returns."""
+        self.check(self.lib.ltca_selftest_bounded_wait(self.handle, int(limit_us)))
+
+    # ---- small tensor helpers on the path ------------------------------------------------------
+    def add_tensors(self, a, b, out=None):
+        """out = a + b for fp32 tensors of equal size (the reference's addTensors)."""
+        assert a.dtype == b.dtype == torch.float32 and a.numel() == b.numel()
+        out = torch.empty_like(a) if out is None else out
+        self.check(self.lib.ltca_add_tensors(self.handle, a.data_ptr(), b.data_ptr(), out.data_ptr(), a.numel()))
+        return out
+
+    def validate_finite(self, x) -> bool:
+        """True if every element of the fp32 tensor is finite (the reference's validateGradients)."""
+        assert x.dtype == torch.float32
+        flag = torch.zeros(1, dtype=torch.int32, device=x.device)
+        self.check(self.lib.ltca_validate_finite(self.handle, x.data_ptr(), x.numel(), flag.data_ptr()))
+        return int(flag.item()) == 0
+
+    def layer_norm_(self, x, gamma=None, beta=None):
+        """In-place LayerNorm of a contiguous fp32 [rows, E] tensor (biased variance, eps 1e-5)."""
+        assert x.dtype == torch.float32 and x.is_contiguous() and x.dim() == 2
+        self.check(self.lib.ltca_layer_norm(self.handle, x.data_ptr(),
+                                            gamma.data_ptr() if gamma is not None else None,
+                                            beta.data_ptr() if beta is not None else None, x.shape[0], x.shape[1]))
+        return x
+
+    def to_bf16(self, x):
+        assert x.dtype == torch.float32 and x.is_contiguous()
+        out = torch.empty(x.shape, dtype=torch.bfloat16, device=x.device)
+        self.check(self.lib.ltca_f32_to_bf16(self.handle, x.data_ptr(), out.data_ptr(), x.numel()))
+        return out
+
+    def to_f32(self, x):
+        assert x.dtype == torch.bfloat16 and x.is_contiguous()
+        out = torch.empty(x.shape, dtype=torch.float32, device=x.device)
+        self.check(self.lib.ltca_bf16_to_f32(self.handle, x.data_ptr(), out.data_ptr(), x.numel()))
+        return out
+
     def workspace(self, nbytes: int) -> Optional[torch.Tensor]:
         """A cached scratch buffer of at least ``nbytes`` (grown on demand, 256-byte aligned)."""
         if nbytes == 0:

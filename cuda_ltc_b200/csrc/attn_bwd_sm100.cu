@@ -1727,22 +1727,14 @@ int launch_main(ltca_ctx* ctx, const ltca_attn_params* p, const void* q, const v
 
     auto kdq = attn_bwd_dq_sm100_kernel<OutT, sizeof(OutT) == 4>;
     auto kdkv = attn_bwd_dkv_sm100_kernel<OutT, sizeof(OutT) == 4>;
-    static bool attr_done = false;
-    if (!attr_done) {
-        LTCA_CUDA_OK(ctx, cudaFuncSetAttribute(kdq, cudaFuncAttributeMaxDynamicSharedMemorySize, DqSmem::kDynBytes));
-        LTCA_CUDA_OK(ctx, cudaFuncSetAttribute(kdkv, cudaFuncAttributeMaxDynamicSharedMemorySize, DkvSmem::kDynBytes));
-        attr_done = true;
-    }
+    static SmemOptIn opt_dq, opt_dkv;         // one pair per template instantiation
+    LTCA_CUDA_OK(ctx, opt_in_dynamic_smem(opt_dq, ctx->device, kdq, DqSmem::kDynBytes));
+    LTCA_CUDA_OK(ctx, opt_in_dynamic_smem(opt_dkv, ctx->device, kdkv, DkvSmem::kDynBytes));
     bool dq_launched = false;
     if constexpr (sizeof(OutT) == 2) {
         if (LTCA_BWD_DQ4) {
-            static bool attr4q_done = false;
-            if (!attr4q_done) {
-                LTCA_CUDA_OK(ctx, cudaFuncSetAttribute(attn_bwd_dq4_sm100_kernel,
-                                                       cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                       Dq4Smem::kDynBytes));
-                attr4q_done = true;
-            }
+            static SmemOptIn opt_dq4;
+            LTCA_CUDA_OK(ctx, opt_in_dynamic_smem(opt_dq4, ctx->device, attn_bwd_dq4_sm100_kernel, Dq4Smem::kDynBytes));
             ItemGrid ig;
             ig.nblk = (p->Sq + kTile - 1) / kTile;
             ig.H = p->H;
@@ -1766,13 +1758,9 @@ int launch_main(ltca_ctx* ctx, const ltca_attn_params* p, const void* q, const v
     kernel_timing_mark(ctx, 2);
     if constexpr (sizeof(OutT) == 2) {
         if (LTCA_BWD_DKV4) {
-            static bool attr4_done = false;
-            if (!attr4_done) {
-                LTCA_CUDA_OK(ctx, cudaFuncSetAttribute(attn_bwd_dkv4_sm100_kernel,
-                                                       cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                       Dkv4Smem::kDynBytes));
-                attr4_done = true;
-            }
+            static SmemOptIn opt_dkv4;
+            LTCA_CUDA_OK(ctx, opt_in_dynamic_smem(opt_dkv4, ctx->device, attn_bwd_dkv4_sm100_kernel,
+                                                  Dkv4Smem::kDynBytes));
             ItemGrid ig;
             ig.nblk = (p->Sk + kTile - 1) / kTile;
             ig.H = p->H;
@@ -1874,7 +1862,8 @@ int launch_attn_bwd_sm100(ltca_ctx* ctx, const ltca_attn_params* p) {
             return fail(ctx, LTCA_ERR_INVALID, "fp32 tensors need 16-byte aligned rows for the bf16 mode");
         const size_t n8 = (size_t)p->B * p->H * S * kD / 8;
         size_t nb = (n8 + 255) / 256;
-        if (nb > 148 * 16) nb = 148 * 16;
+        const size_t cap = (size_t)ctx->sm_device * 16;
+        if (nb > cap) nb = cap;
         pack_bf16_rows_kernel<<<(unsigned)nb, 256, 0, ctx->stream>>>(
             reinterpret_cast<const float*>(src), st, reinterpret_cast<__nv_bfloat16*>(dst), p->H, S, n8);
         LTCA_LAUNCH_OK(ctx, "pack_bf16_rows_kernel");

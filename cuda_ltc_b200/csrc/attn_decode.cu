@@ -203,8 +203,9 @@ __global__ void attn_decode_merge_kernel(const DecodeArgs a) {
 }
 
 int pick_splits(const ltca_attn_params* p, int sm_count) {
+    if (p->B < 1 || p->H < 1 || p->Sk < 1) return 1;      // nothing to split (and no division by zero below)
     const int64_t bh = (int64_t)p->B * p->H;
-    if (sm_count <= 0) sm_count = 148;
+    if (sm_count <= 0) sm_count = kPlanSms;
     if (bh >= 2 * sm_count) return 1;
     int64_t want = (4 * (int64_t)sm_count + bh - 1) / bh;
     int64_t cap = (p->Sk + 255) / 256;
@@ -268,9 +269,10 @@ int dispatch_decode(ltca_ctx* ctx, const DecodeArgs& a) {
 }  // namespace
 
 // The split count must not depend on the context, so that the size query (which has no
-// context) and the launch agree: it is derived from the B200's 148 SMs.
+// context) and the launch agree.  Non-positive shapes need no scratch (the launch refuses them).
 size_t attn_decode_workspace(const ltca_attn_params* p) {
-    const int ns = pick_splits(p, 148);
+    if (p->B < 1 || p->H < 1 || p->Sk < 1 || p->D < 1) return 0;
+    const int ns = pick_splits(p, kPlanSms);
     if (ns <= 1) return 0;
     return align_up((size_t)p->B * p->H * ns * (p->D + 2) * sizeof(float), 256);
 }
@@ -297,9 +299,9 @@ int launch_attn_decode(ltca_ctx* ctx, const ltca_attn_params* p) {
     a.lse = p->lse;
     a.keep_mask = p->keep_mask;
     a.kv_len = p->kv_len;
-    a.nsplit = pick_splits(p, 148);
-    if (pick_cluster(p, 148) > 1) {
-        a.nsplit = pick_cluster(p, 148);       // merged inside the cluster: a.partial stays null
+    a.nsplit = pick_splits(p, kPlanSms);
+    if (pick_cluster(p, kPlanSms) > 1) {
+        a.nsplit = pick_cluster(p, kPlanSms);       // merged inside the cluster: a.partial stays null
     } else if (a.nsplit > 1) {
         const size_t need = attn_decode_workspace(p);
         if (!p->workspace || p->workspace_bytes < need)
@@ -328,8 +330,10 @@ namespace {
 constexpr size_t kStaticScratchBytes = 256u << 10;   // 256 KiB, resident on every GPU that loads the library
 static __device__ __align__(256) unsigned char g_decode_static_scratch[kStaticScratchBytes];
 
+// Device address of the array on each GPU, looked up on the first call there.  Host threads that make that
+// first call at the same time all store the same value, hence relaxed atomics are enough.
 constexpr int kMaxDevices = 64;
-void* g_static_scratch_ptr[kMaxDevices] = {nullptr};
+std::atomic<void*> g_static_scratch_ptr[kMaxDevices];
 
 void set_err(char* buf, size_t len, const char* msg) {
     if (buf && len) snprintf(buf, len, "%s", msg);
@@ -340,21 +344,15 @@ void set_err(char* buf, size_t len, const char* msg) {
 extern "C" int ltca_attn_decode_static(void* stream, const ltca_attn_params* p, char* err,
                                        size_t err_len) {
     if (!p) { set_err(err, err_len, "null parameter block"); return LTCA_ERR_INVALID; }
-    int dev = -1;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
-        set_err(err, err_len, "no current CUDA device (or device index above 63)");
-        return LTCA_ERR_NO_DEVICE;
+    // Arguments first: nothing below may divide by, or size a buffer from, a shape that is not positive.
+    if (p->B < 1 || p->H < 1 || p->Sk < 1 || p->D < 1 || !p->q || !p->k || !p->v || !p->o ||
+        !(p->scale > 0.f) || (p->dtype != LTCA_F32 && p->dtype != LTCA_BF16)) {
+        set_err(err, err_len, "bad decode arguments (shape, null pointer, scale or dtype)");
+        return LTCA_ERR_INVALID;
     }
-    // One-time set-up per device, with that device current: in host code the array's name is
-    // only a stand-in, the kernel needs the address the symbol has on THIS device.
-    if (!g_static_scratch_ptr[dev]) {
-        void* ptr = nullptr;
-        cudaError_t e = cudaGetSymbolAddress(&ptr, g_decode_static_scratch);
-        if (e != cudaSuccess || !ptr) {
-            set_err(err, err_len, cudaGetErrorString(e));
-            return LTCA_ERR_CUDA;
-        }
-        g_static_scratch_ptr[dev] = ptr;
+    if (p->Sq != 1) {
+        set_err(err, err_len, "decode needs Sq == 1");
+        return LTCA_ERR_INVALID;
     }
     const size_t need = ltca::attn_decode_workspace(p);
     if (need > kStaticScratchBytes) {
@@ -365,17 +363,28 @@ extern "C" int ltca_attn_decode_static(void* stream, const ltca_attn_params* p, 
         set_err(err, err_len, msg);
         return LTCA_ERR_WORKSPACE;
     }
-    if (p->B < 1 || p->H < 1 || p->Sk < 1 || p->D < 1 || !p->q || !p->k || !p->v || !p->o ||
-        !(p->scale > 0.f) || (p->dtype != LTCA_F32 && p->dtype != LTCA_BF16)) {
-        set_err(err, err_len, "bad decode arguments (shape, null pointer, scale or dtype)");
-        return LTCA_ERR_INVALID;
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+        set_err(err, err_len, "no current CUDA device (or device index above 63)");
+        return LTCA_ERR_NO_DEVICE;
+    }
+    // One-time set-up per device, with that device current: in host code the array's name is
+    // only a stand-in, the kernel needs the address the symbol has on THIS device.
+    void* scratch = g_static_scratch_ptr[dev].load(std::memory_order_relaxed);
+    if (!scratch) {
+        cudaError_t e = cudaGetSymbolAddress(&scratch, g_decode_static_scratch);
+        if (e != cudaSuccess || !scratch) {
+            set_err(err, err_len, cudaGetErrorString(e));
+            return LTCA_ERR_CUDA;
+        }
+        g_static_scratch_ptr[dev].store(scratch, std::memory_order_relaxed);
     }
     ltca_ctx tmp;                       // host-only bookkeeping: stream and error text
     tmp.device = dev;
     tmp.stream = reinterpret_cast<cudaStream_t>(stream);
-    tmp.sm_count = 148;
+    tmp.sm_count = tmp.sm_device = ltca::kPlanSms;    // only the split plan uses it, and that is fixed (see kPlanSms)
     ltca_attn_params q = *p;
-    q.workspace = g_static_scratch_ptr[dev];
+    q.workspace = scratch;
     q.workspace_bytes = kStaticScratchBytes;
     const int rc = ltca::launch_attn_decode(&tmp, &q);
     if (rc) set_err(err, err_len, tmp.err);

@@ -1088,12 +1088,8 @@ int launch_fwd4(ltca_ctx* ctx, const ltca_attn_params* p, const void* q, const v
     if ((rc = make_tmap_bhsd(ctx, &tk, k, 2, p->B, p->H, p->Sk, 64, ks, 64, kF4BN))) return rc;
     if ((rc = make_tmap_bhsd(ctx, &tv, v, 2, p->B, p->H, p->Sk, 64, vs, 64, kF4BN))) return rc;
     if ((rc = make_tmap_bhsd(ctx, &to, p->o, 2, p->B, p->H, p->Sq, 64, p->o_strides, 64, kBlockM))) return rc;
-    static bool attr_done = false;
-    if (!attr_done) {
-        LTCA_CUDA_OK(ctx, cudaFuncSetAttribute(attn_fwd4p_sm100_kernel,
-                                               cudaFuncAttributeMaxDynamicSharedMemorySize, P::kDynBytes));
-        attr_done = true;
-    }
+    static SmemOptIn opt_in;
+    LTCA_CUDA_OK(ctx, opt_in_dynamic_smem(opt_in, ctx->device, attn_fwd4p_sm100_kernel, P::kDynBytes));
     ItemGrid ig;
     ig.nblk = (p->Sq + kF4Tiles * kBlockM - 1) / (kF4Tiles * kBlockM);
     ig.H = p->H;
@@ -1139,12 +1135,8 @@ int launch_fwd(ltca_ctx* ctx, const ltca_attn_params* p, const void* q, const vo
     }
 
     auto kern = attn_fwd_sm100_kernel<D, OutT, kSplitP>;
-    static bool attr_done = false;
-    if (!attr_done) {
-        LTCA_CUDA_OK(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                               L::kDynBytes));
-        attr_done = true;
-    }
+    static SmemOptIn opt_in;                  // one per template instantiation
+    LTCA_CUDA_OK(ctx, opt_in_dynamic_smem(opt_in, ctx->device, kern, L::kDynBytes));
     dim3 grid((p->Sq + 2 * kBlockM - 1) / (2 * kBlockM), p->H, p->B);
     kern<<<grid, kFwdThreads, L::kDynBytes, ctx->stream>>>(tq, tk, tv, a);
     LTCA_LAUNCH_OK(ctx, "attn_fwd_sm100_kernel");

@@ -4,6 +4,7 @@
 #include <new>
 
 #include "host_common.h"
+#include "sm100_ptx.cuh"
 
 namespace ltca {
 int launch_attn_fwd_sm100_bf16in(ltca_ctx* ctx, const ltca_attn_params* p, const void* q,
@@ -172,9 +173,24 @@ __global__ void accumulate_rows_kernel(float* __restrict__ acc, const T* __restr
     }
 }
 
+// One warp waits on a barrier that nothing ever arrives at: the path every bounded wait of the tensor-pipe
+// kernels takes when its producer never shows up, with a limit short enough for a test.
+__global__ void bounded_wait_selftest_kernel(uint32_t* status, unsigned long long limit_ns) {
+    __shared__ __align__(8) uint64_t bar;
+    __shared__ uint32_t abort_flag;
+    if (threadIdx.x == 0) {
+        abort_flag = 0u;
+        mbar_init(smem_u32(&bar), 1);
+        mbar_fence_init();
+    }
+    __syncthreads();
+    const WaitCtx wc{&abort_flag, status, limit_ns};
+    mbar_wait_warp(smem_u32(&bar), 0, wc, 0x7f);
+}
+
 inline int blocks_for(size_t n, int threads, int sm_count) {
     size_t b = (n + threads - 1) / threads;
-    const size_t cap = (size_t)(sm_count > 0 ? sm_count : 148) * 16;
+    const size_t cap = (size_t)(sm_count > 0 ? sm_count : kPlanSms) * 16;
     if (b > cap) b = cap;
     if (b < 1) b = 1;
     return (int)b;
@@ -310,12 +326,23 @@ const char* ltca_last_error(const ltca_ctx* ctx) { return ctx ? ctx->err : "null
 int ltca_device_status(ltca_ctx* ctx, uint32_t* status_out) {
     if (!ctx || !status_out) return LTCA_ERR_INVALID;
     uint32_t v = 0;
+    LTCA_CUDA_OK(ctx, cudaSetDevice(ctx->device));
     LTCA_CUDA_OK(ctx, cudaMemcpyAsync(&v, ctx->d_status, sizeof(v), cudaMemcpyDeviceToHost, ctx->stream));
     LTCA_CUDA_OK(ctx, cudaStreamSynchronize(ctx->stream));
     // a kernel that gave up may have left its work-item counters mid-count: clear everything
     if (v) LTCA_CUDA_OK(ctx, cudaMemsetAsync(ctx->d_status, 0, 16 * sizeof(uint32_t), ctx->stream));
     *status_out = v;
     if (v) return fail(ctx, LTCA_ERR_DEVICE, "device status word 0x%08x", v);
+    return LTCA_OK;
+}
+
+int ltca_selftest_bounded_wait(ltca_ctx* ctx, uint32_t limit_us) {
+    if (!ctx) return LTCA_ERR_INVALID;
+    if (limit_us < 1 || limit_us > 1000000)
+        return fail(ctx, LTCA_ERR_INVALID, "limit must be between 1 us and 1 s (got %u us)", limit_us);
+    LTCA_CUDA_OK(ctx, cudaSetDevice(ctx->device));
+    bounded_wait_selftest_kernel<<<1, 32, 0, ctx->stream>>>(ctx->d_status, 1000ull * limit_us);
+    LTCA_LAUNCH_OK(ctx, "bounded_wait_selftest_kernel");
     return LTCA_OK;
 }
 
@@ -408,6 +435,7 @@ int ltca_add_tensors(ltca_ctx* ctx, const float* a, const float* b, float* r, si
     if (!ctx) return LTCA_ERR_INVALID;
     if (!a || !b || !r) return fail(ctx, LTCA_ERR_INVALID, "null tensor");
     if (n == 0) return LTCA_OK;
+    LTCA_CUDA_OK(ctx, cudaSetDevice(ctx->device));
     const bool aligned = !((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) |
                             reinterpret_cast<uintptr_t>(r)) & 15);
     if (aligned)
@@ -426,6 +454,7 @@ int ltca_attn_merge(ltca_ctx* ctx, float* o_acc, float* lse_acc, const void* o_b
         return fail(ctx, LTCA_ERR_INVALID, "bad row range %d + %d of %d", s0, n, S_acc);
     if (blk_dtype != LTCA_F32 && blk_dtype != LTCA_BF16) return fail(ctx, LTCA_ERR_INVALID, "bad dtype");
     if (BH * n == 0) return LTCA_OK;
+    LTCA_CUDA_OK(ctx, cudaSetDevice(ctx->device));
     if ((D & 3) || ((reinterpret_cast<uintptr_t>(o_acc) | reinterpret_cast<uintptr_t>(o_blk)) & 15))
         return fail(ctx, LTCA_ERR_INVALID, "head_dim must be a multiple of 4 and the tensors 16-byte aligned");
     const int wpb = 8;                                         // two rows per warp
@@ -451,6 +480,7 @@ int ltca_accumulate_rows(ltca_ctx* ctx, float* acc, const void* part, int32_t pa
         return fail(ctx, LTCA_ERR_INVALID, "head_dim must be a multiple of 4 and the tensors 16-byte aligned");
     const int64_t total = BH * n * (D >> 2);
     if (total == 0) return LTCA_OK;
+    LTCA_CUDA_OK(ctx, cudaSetDevice(ctx->device));
     const int grid = blocks_for((size_t)total, 256, ctx->sm_count);
     if (part_dtype == LTCA_F32)
         accumulate_rows_kernel<float><<<grid, 256, 0, ctx->stream>>>(
@@ -467,6 +497,7 @@ int ltca_layer_norm(ltca_ctx* ctx, float* x, const float* gamma, const float* be
     if (!ctx) return LTCA_ERR_INVALID;
     if (!x || rows < 0 || E < 1) return fail(ctx, LTCA_ERR_INVALID, "bad LayerNorm arguments");
     if (rows == 0) return LTCA_OK;
+    LTCA_CUDA_OK(ctx, cudaSetDevice(ctx->device));
     const int wpb = 8;
     layer_norm_kernel<<<(unsigned)((rows + wpb - 1) / wpb), wpb * 32, 0, ctx->stream>>>(
         x, gamma, beta, rows, E, 1e-5f);
@@ -477,6 +508,7 @@ int ltca_layer_norm(ltca_ctx* ctx, float* x, const float* gamma, const float* be
 int ltca_validate_finite(ltca_ctx* ctx, const float* x, size_t n, int32_t* flag_out) {
     if (!ctx) return LTCA_ERR_INVALID;
     if (!x || !flag_out) return fail(ctx, LTCA_ERR_INVALID, "null argument");
+    LTCA_CUDA_OK(ctx, cudaSetDevice(ctx->device));
     LTCA_CUDA_OK(ctx, cudaMemsetAsync(flag_out, 0, sizeof(int32_t), ctx->stream));
     if (n == 0) return LTCA_OK;
     validate_finite_kernel<<<blocks_for(n, 256, ctx->sm_count), 256, 0, ctx->stream>>>(x, n, flag_out);
@@ -488,6 +520,7 @@ int ltca_f32_to_bf16(ltca_ctx* ctx, const float* src, void* dst, size_t n) {
     if (!ctx) return LTCA_ERR_INVALID;
     if (!src || !dst) return fail(ctx, LTCA_ERR_INVALID, "null argument");
     if (n == 0) return LTCA_OK;
+    LTCA_CUDA_OK(ctx, cudaSetDevice(ctx->device));
     f32_to_bf16_kernel<<<blocks_for(n, 256, ctx->sm_count), 256, 0, ctx->stream>>>(
         src, reinterpret_cast<__nv_bfloat16*>(dst), n);
     LTCA_LAUNCH_OK(ctx, "f32_to_bf16_kernel");
@@ -498,6 +531,7 @@ int ltca_bf16_to_f32(ltca_ctx* ctx, const void* src, float* dst, size_t n) {
     if (!ctx) return LTCA_ERR_INVALID;
     if (!src || !dst) return fail(ctx, LTCA_ERR_INVALID, "null argument");
     if (n == 0) return LTCA_OK;
+    LTCA_CUDA_OK(ctx, cudaSetDevice(ctx->device));
     bf16_to_f32_kernel<<<blocks_for(n, 256, ctx->sm_count), 256, 0, ctx->stream>>>(
         reinterpret_cast<const __nv_bfloat16*>(src), dst, n);
     LTCA_LAUNCH_OK(ctx, "bf16_to_f32_kernel");

@@ -393,7 +393,7 @@ size_t gemm_sm100_partial_bytes(int M, int N, int n_problems, int ksplit) {
 int gemm_sm100_pick_ksplit(int M, int N, int K, int n_problems, int sm_count) {
     const int tiles = ((M + kBM - 1) / kBM) * ((N + kBN - 1) / kBN) * n_problems;
     const int nkb = (K + kBK - 1) / kBK;
-    if (sm_count <= 0) sm_count = 148;
+    if (sm_count <= 0) sm_count = kPlanSms;
     int ks = 1;
     // split while the tiles alone leave most SMs idle and every slice keeps at least 8 K blocks
     while (tiles * ks * 2 <= sm_count && nkb / (ks * 2) >= 8 && ks < 16) ks *= 2;
@@ -448,7 +448,7 @@ int gemm_sm100(ltca_ctx* ctx, const GemmProblem& gp) {
     g.tiles_y = (gp.M + kBM - 1) / kBM;
     g.tiles_z = gp.n_problems * g.ksplit;
     const int64_t n_tiles = (int64_t)g.tiles_x * g.tiles_y * g.tiles_z;
-    const int sms = ctx->sm_count > 0 ? ctx->sm_count : 148;
+    const int sms = ctx->sm_count > 0 ? ctx->sm_count : kPlanSms;
     dim3 grid((unsigned)(n_tiles < sms ? n_tiles : sms));
     const bool amn = gp.a[0].mn_major != 0, bmn = gp.b[0].mn_major != 0;
     auto launch = [&](auto kern) -> int {

@@ -10,6 +10,8 @@
 #include <stdio.h>
 #include <string.h>
 
+#include <atomic>
+
 #include "../../include/ltc_attn.h"
 
 struct ltca_ctx {
@@ -65,6 +67,24 @@ inline int fail(ltca_ctx* ctx, int code, const char* fmt, ...) {
             return ::ltca::fail((ctx), LTCA_ERR_CUDA, "launch of %s failed: %s", (what),    \
                                 cudaGetErrorString(e__));                                   \
     } while (0)
+
+// The opt-in to more than 48 KB of dynamic shared memory (cudaFuncSetAttribute) is a property of a kernel ON ONE
+// DEVICE, so a process-wide "already done" flag would leave the second GPU of a process without it.  One bit per
+// device and call site; two threads that race only repeat the call.
+struct SmemOptIn { std::atomic<uint64_t> done{0}; };
+template <typename Kernel>
+inline cudaError_t opt_in_dynamic_smem(SmemOptIn& once, int device, Kernel kernel, int bytes) {
+    const uint64_t bit = (device >= 0 && device < 64) ? (1ull << device) : 0ull;
+    if (bit && (once.done.load(std::memory_order_acquire) & bit)) return cudaSuccess;
+    const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e == cudaSuccess && bit) once.done.fetch_or(bit, std::memory_order_release);
+    return e;
+}
+
+// SM count that size queries plan for.  Split counts (decode key ranges, the contraction of the weight-gradient
+// products) fix how much scratch a call needs, and the size queries have no context to ask the device, so the plan
+// is a function of the problem alone, laid out for the B200's 148 SMs.  Launch widths always come from the context.
+constexpr int kPlanSms = 148;
 
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 inline int elem_size(int dtype) { return dtype == LTCA_BF16 ? 2 : 4; }

@@ -538,8 +538,8 @@ int make_tplan(const ltca_tsa_params* t, TPlan* pl) {
     if (rc) return rc;
     if ((rc = ltca_attn_workspace_bytes(&a, 1, &pl->attn_bwd))) return rc;
     const int rows = (int)pl->rows;
-    pl->ks_in = gemm_sm100_pick_ksplit(t->E, pl->HW, rows, 3, 148);
-    pl->ks_out = gemm_sm100_pick_ksplit(pl->HW, t->E, rows, 1, 148);
+    pl->ks_in = gemm_sm100_pick_ksplit(t->E, pl->HW, rows, 3, kPlanSms);
+    pl->ks_out = gemm_sm100_pick_ksplit(pl->HW, t->E, rows, 1, kPlanSms);
     const size_t p_in = gemm_sm100_partial_bytes(t->E, pl->HW, 3, pl->ks_in);
     const size_t p_out = gemm_sm100_partial_bytes(pl->HW, t->E, 1, pl->ks_out);
     pl->partial = p_in > p_out ? p_in : p_out;
@@ -908,6 +908,7 @@ static int prenorm_backward(ltca_ctx* ctx, const ltca_tsa_params* t, bool want_d
 int ltca_tsa_fwd(ltca_ctx* ctx, const ltca_tsa_params* t) {
     int rc = check(ctx, t);
     if (rc) return rc;
+    LTCA_CUDA_OK(ctx, cudaSetDevice(ctx->device));
     if (!t->out) return fail(ctx, LTCA_ERR_INVALID, "out must be non-null");
     if (t->use_layer_norm && (!t->ln_gamma || !t->ln_beta))
         return fail(ctx, LTCA_ERR_INVALID, "LayerNorm needs gamma and beta");
@@ -940,6 +941,7 @@ int ltca_tsa_fwd(ltca_ctx* ctx, const ltca_tsa_params* t) {
 static int tsa_backward(ltca_ctx* ctx, const ltca_tsa_params* t, bool want_dx, bool want_dw) {
     int rc = check(ctx, t);
     if (rc) return rc;
+    LTCA_CUDA_OK(ctx, cudaSetDevice(ctx->device));
     if (!t->dy) return fail(ctx, LTCA_ERR_INVALID, "dy must be non-null");
     if (want_dx && !t->dx) return fail(ctx, LTCA_ERR_INVALID, "dx must be non-null");
     if (want_dw && (!t->dwq || !t->dwk || !t->dwv || !t->dwo))

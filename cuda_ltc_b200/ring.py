@@ -90,6 +90,10 @@ class CudaOps:
         self.mode = _lib.MODE_AUTO if mode is None else mode
 
     def begin(self):
+        # The exchange (torch.distributed P2P) orders itself against torch's CURRENT stream at call time; the
+        # context's kernels must run on that same stream, or they would race with the K/V receives.
+        import torch
+        self.ctx.set_stream(torch.cuda.current_stream(self.ctx.device))
         if self.comm_sms > 0:
             self.ctx.set_sm_limit(max(1, self.ctx.sm_count() - self.comm_sms))
 

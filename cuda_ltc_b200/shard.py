@@ -108,7 +108,7 @@ def sum_weight_grads(grads, group=None, async_op=False):
     import torch.distributed as dist
     grads = [g for g in grads if g is not None]
     if not grads or not (dist.is_available() and dist.is_initialized()) or dist.get_world_size(group) == 1:
-        return _Pending(None, None, []) if async_op else grads
+        return _Pending(None, None, [], grads) if async_op else grads   # wait() hands the gradients back
     packed = _as_one_allocation(grads)
     bucket = packed if packed is not None else torch.cat([g.reshape(-1) for g in grads])
     work = dist.all_reduce(bucket, op=dist.ReduceOp.SUM, group=group, async_op=True)

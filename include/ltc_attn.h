@@ -101,6 +101,10 @@ typedef struct {
  * Replaces the per-object handle set-up of FlashAttention::FlashAttention
  * (src/ml/flash_attention.cu:485-549) and cudnn_ops::CuDNNHandle (include/cuDNN_ops.h:95-115). */
 int ltca_ctx_create(int device, void* stream, ltca_ctx** out);
+/* Rebinds the stream for the calls that follow.  A context is not thread-safe, and it keeps the work-item
+ * counters of its persistent kernels: two launches of one context that overlap on the GPU (issued on two
+ * streams with no ordering between them) would share those counters and corrupt each other.  Work that is
+ * meant to overlap takes one context per stream; one process may hold contexts on several devices. */
 int ltca_ctx_set_stream(ltca_ctx* ctx, void* stream);
 void ltca_ctx_destroy(ltca_ctx* ctx);
 /* Text of the last error on this context (host string, valid until the next call). */
@@ -120,6 +124,12 @@ int ltca_ctx_last_bwd_kernel_ms(ltca_ctx* ctx, float* ms_out);
 /* Reads and clears the device status word that kernels set when a bounded wait ran out or an
  * internal check failed.  Synchronises the context's stream.  0 = clean. */
 int ltca_device_status(ltca_ctx* ctx, uint32_t* status_out);
+/* Self-test of the bounded waits (no counterpart in the reference, whose only time limit,
+ * InferencePipelineConfig::timeoutMs, is never read: include/inference_pipeline.h:28).  Launches one warp that
+ * waits on a barrier nothing arrives at, with `limit_us` (1 .. 1 000 000) in place of the kernels' two seconds.
+ * The kernel returns on its own; ltca_device_status then reports LTCA_ERR_DEVICE with the time-out bit
+ * (status & 1) and barrier code 0x7f in bits 8..23, and the context stays usable. */
+int ltca_selftest_bounded_wait(ltca_ctx* ctx, uint32_t limit_us);
 /* The persistent kernels of this context launch one CTA per SM; n_sms caps that number so that other work
  * on the GPU (a communication library's copy kernels while slices are exchanged between GPUs) finds free SMs
  * at once instead of waiting for a whole kernel to end.  n_sms <= 0 or above the device's count restores the

@@ -130,6 +130,12 @@ inline void flashAttentionBackward(const Context& c, const CudaMemory<float>& qu
 // 1.0, no mask use, include/cuDNN_ops.h:152-178); input_dim / num_heads gives the compact form
 // (scale 1/sqrt(head_dim)).  Rows are time-major, as the reference hands them to cuDNN
 // (include/cuDNN_ops.h:322-328).
+//
+// The `mask` argument of forward / backward / backwardWeights is IGNORED by default, because the reference's
+// module never reads it (src/ml/cudnn_time_self_attention.cu:211-237 passes no mask and a full attention window
+// to cuDNN, src/ml/cuDNN_ops.cu:185-197) and its callers rely on that: its tests hand a 1 = keep / 0 = drop mask
+// to forward and expect the unmasked result to stay finite (src/ml/time_self_attention_test.cu:452-457).
+// setHonourMask(true) is the extension: the mask is then applied as a dense [B,S,S] keep-mask, 0 hides the key.
 class B200TimeSelfAttention : public TimeSelfAttention {
 public:
     B200TimeSelfAttention(int input_dim, int num_heads, bool use_layer_norm = true, bool use_residual = true,
@@ -187,6 +193,9 @@ public:
     // that the contents of x_seq and the weights have not changed in between; any other call recomputes.
     void setReuseForward(bool on) { reuse_forward_ = on; if (!on) saved_x_ = nullptr; }
 
+    // Off (default): the mask argument is ignored, as in the reference.  On: dense keep-mask, 0 hides the key.
+    void setHonourMask(bool on) { honour_mask_ = on; }
+
     CudaMemory<float> backward(const CudaMemory<float>& grad_output, const CudaMemory<float>& x_seq,
                                int batch_size, int seq_len, const CudaMemory<float>* mask = nullptr,
                                cudaStream_t stream = nullptr) override {
@@ -229,8 +238,17 @@ public:
     }
 
     // File layout: the reference's blob header (u32 0x43444E4E, u32 version, size_t byte count,
-    // src/ml/cuDNN_ops.cu:391-420) followed by Wq, Wk, Wv, Wo as fp32 row-major matrices, and
-    // `<path>.layernorm` with gamma then beta (src/ml/cudnn_time_self_attention.cu:382-398).
+    // src/ml/cuDNN_ops.cu:391-420) followed by Wq, Wk, Wv [input_dim, heads * width] and Wo [heads * width,
+    // input_dim] as fp32 row-major matrices, and `<path>.layernorm` with gamma then beta
+    // (src/ml/cudnn_time_self_attention.cu:382-398).  In the reference's form (width = input_dim) this IS the
+    // byte order of cuDNN's weight buffer on cuDNN 9.10: cudnnGetMultiHeadAttnWeights places the kinds Q, K, V, O
+    // back to back and describes Q/K/V as [heads, width, input] with strides (width, 1, heads * width) and O as
+    // [heads, output, width] with strides (output * width, 1, output), i.e. exactly those four row-major
+    // matrices.  Files written by the reference's saveAttentionWeights therefore load here unchanged and files
+    // written here load there, and since the constructor draws the matrices in that same order from one
+    // mt19937(seed) with the reference's limits (src/ml/cuDNN_ops.cu:34-96), equal seeds give byte-identical
+    // files.  A file of the compact form (width = input_dim / heads) has another byte count and is refused by
+    // the other form.
     void saveWeights(const std::string& filepath) override {
         std::ofstream f(filepath, std::ios::binary);
         if (!f.is_open()) throw std::runtime_error("Failed to open file for writing: " + filepath);
@@ -278,7 +296,7 @@ private:
         p.x = x.get();
         p.wq = wq_.get(); p.wk = wk_.get(); p.wv = wv_.get(); p.wo = wo_.get();
         p.ln_gamma = ln_gamma_.get(); p.ln_beta = ln_beta_.get();
-        p.keep_mask = mask ? mask->get() : nullptr;
+        p.keep_mask = (mask && honour_mask_) ? mask->get() : nullptr;
         return p;
     }
     void attach_saved(ltca_tsa_params& p, const CudaMemory<float>& x, int B, int S) const {
@@ -325,6 +343,7 @@ private:
     CudaMemory<float> dwq_, dwk_, dwv_, dwo_, dgamma_, dbeta_;
     CudaMemory<float> workspace_;
     bool reuse_forward_ = false;
+    bool honour_mask_ = false;
     CudaMemory<float> saved_;
     const float* saved_x_ = nullptr;
     const float* saved_mask_ = nullptr;

@@ -10,7 +10,13 @@
 //       projection matrices out of that blob exactly as the reference does
 //       (cudnnGetMultiHeadAttnWeights + cudnnGetTensorNdDescriptor, src/ml/cuDNN_ops.cu:54-70)
 //       and write x, dy, the matrices (with their dims and strides), out and dx as raw float32
-//       plus a manifest.
+//       plus a manifest.  The weight gradients come next: the reference class keeps them in a private byte
+//       buffer that no accessor returns (src/ml/cudnn_time_self_attention.cu:340-356, :474-493), so this
+//       file includes that source file textually (path given by the Makefile, nothing is copied) with its
+//       `private:` sections opened, calls initializeGradientStorage + backwardWeights after backward (the
+//       order cuDNN documents: weight gradients after data gradients) and dumps the buffer, whose layout is
+//       the weight buffer's (same descriptors, src/ml/cuDNN_ops.cu:366-385).  The module's own weight file
+//       is kept too (w<i>.bin): it is what saveWeights of the reference writes.
 #include <cudnn.h>
 
 #include <cstdio>
@@ -21,9 +27,18 @@
 #include <string>
 #include <vector>
 
+#include <iostream>
+#include <memory>
+#include <stdexcept>
+
 #include "cuda_resources.h"
 #include "time_self_attention.h"
 #include "cuDNN_ops.h"
+
+// every standard header the included file uses is already in; only its own class is affected
+#define private public
+#include REF_CUDNN_TSA_CU
+#undef private
 
 using namespace cudatrader;
 
@@ -87,6 +102,27 @@ int main(int argc, char** argv) {
                 fprintf(stderr, "case %d backward: %s\n", idx, e.what());
                 have_dx = false;
             }
+            // weight gradients, after the data gradients as cuDNN asks
+            bool have_dw = false;
+            std::vector<uint8_t> hdw;
+            if (have_dx) {
+                try {
+                    auto* impl = dynamic_cast<CuDNNTimeSelfAttention*>(tsa.get());
+                    if (impl) {
+                        impl->initializeGradientStorage();
+                        cudaDeviceSynchronize();
+                        impl->backwardWeights(dy, x, c.B, c.S);
+                        cudaDeviceSynchronize();
+                        if (impl->gradWeightBuffer_ && impl->gradWeightBuffer_->size() > 0) {
+                            hdw.resize(impl->gradWeightBuffer_->size());
+                            cudaMemcpy(hdw.data(), impl->gradWeightBuffer_->get(), hdw.size(), cudaMemcpyDeviceToHost);
+                            have_dw = true;
+                        }
+                    }
+                } catch (const std::exception& e) {
+                    fprintf(stderr, "case %d backwardWeights: %s\n", idx, e.what());
+                }
+            }
             // weights: through the module's own file, then the reference's own query recipe
             const std::string wpath = out + "/w" + std::to_string(idx) + ".bin";
             tsa->saveWeights(wpath);
@@ -111,8 +147,12 @@ int main(int argc, char** argv) {
             const cudnnMultiHeadAttnWeightKind_t kinds[4] = {CUDNN_MH_ATTN_Q_WEIGHTS, CUDNN_MH_ATTN_K_WEIGHTS,
                                                              CUDNN_MH_ATTN_V_WEIGHTS, CUDNN_MH_ATTN_O_WEIGHTS};
             const char* names[4] = {"wq", "wk", "wv", "wo"};
-            fprintf(mf, "case %d E %d H %d B %d S %d ln %d res %d dx %d blob %zu\n", idx, c.E, c.H, c.B, c.S,
-                    (int)c.ln, (int)c.res, (int)have_dx, nbytes);
+            fprintf(mf, "case %d E %d H %d B %d S %d ln %d res %d dx %d dw %d blob %zu\n", idx, c.E, c.H, c.B, c.S,
+                    (int)c.ln, (int)c.res, (int)have_dx, (int)(have_dw && hdw.size() == nbytes), nbytes);
+            if (have_dw && hdw.size() == nbytes) {
+                FILE* f = fopen((out + "/dw" + std::to_string(idx) + ".bin").c_str(), "wb");
+                if (f) { fwrite(hdw.data(), 1, hdw.size(), f); fclose(f); }
+            }
             for (int k = 0; k < 4; ++k) {
                 cudnnTensorDescriptor_t wd;
                 cudnnCreateTensorDescriptor(&wd);

@@ -6,9 +6,14 @@ run on a B200) into the committed golden vectors tests/golden/ref_tsa_case*.npz.
 
 The projection matrices are stored as the reference reads them (cudnnGetMultiHeadAttnWeights,
 reference src/ml/cuDNN_ops.cu:54-70): a [heads, a, b] view with explicit strides; the arrays
-saved here are dense [heads, a, b] copies of that view.
+saved here are dense [heads, a, b] copies of that view, and `<name>_offset` is the byte offset of
+the view inside the weight buffer.  The weight gradients (dwq ... dwo, where the driver could read
+them) are the same views of the reference's gradient buffer.  For the two smallest cases the
+module's own weight file, exactly as the reference's saveWeights wrote it, is kept beside the
+vectors as ref_tsa_weights_case<i>.bin.
 """
 import os
+import shutil
 import sys
 
 import numpy as np
@@ -38,10 +43,18 @@ def main(src):
             dense = np.lib.stride_tricks.as_strided(raw, shape=dims, strides=[4 * s for s in strides]).copy()
             out[name] = dense
             out[name + "_strides"] = np.array(strides, dtype=np.int64)
+            offset = int(w[w.index("offset") + 1])
+            out[name + "_offset"] = np.int64(offset)
+            if meta.get("dw"):
+                graw = np.fromfile(os.path.join(src, f"dw{idx}.bin"), dtype=np.float32)[offset // 4:]
+                out["d" + name] = np.lib.stride_tricks.as_strided(
+                    graw, shape=dims, strides=[4 * s for s in strides]).copy()
         n = (meta["B"] * meta["S"], meta["E"])
         for name in ("x", "dy", "y") + (("dx",) if meta["dx"] else ()):
             out[name] = np.fromfile(os.path.join(src, f"{name}{idx}.f32"), dtype=np.float32).reshape(n)
         np.savez_compressed(os.path.join(HERE, f"ref_tsa_case{idx}.npz"), **out)
+        if meta["blob"] <= 4096:
+            shutil.copyfile(os.path.join(src, f"w{idx}.bin"), os.path.join(HERE, f"ref_tsa_weights_case{idx}.bin"))
         print("wrote case", idx, {k: v for k, v in meta.items()})
         i += 1
 

@@ -79,3 +79,21 @@ def test_size_queries_run_without_gpu(lib):
     assert lib.ltca_attn_uses_tensor_pipe(C.byref(p), 0) == 1
     p.D = 32
     assert lib.ltca_attn_uses_tensor_pipe(C.byref(p), 0) == 0
+
+
+def test_decode_size_query_and_static_entry_reject_bad_shapes_on_the_host(lib):
+    """Argument checks run before anything touches a device: no GPU is needed to see the status codes (a zero
+    batch x heads used to reach a division in the split planner)."""
+    from cuda_ltc_b200 import _lib
+    n = C.c_size_t(7)
+    err = C.create_string_buffer(200)
+    dummy = (C.c_float * 64)()
+    for B, H, Sk, D in ((0, 8, 128, 64), (4, 0, 128, 64), (4, -2, 128, 64), (4, 8, 0, 64), (4, 8, 128, 0)):
+        p = _lib.AttnParams()
+        p.B, p.H, p.Sq, p.Sk, p.D = B, H, 1, Sk, D
+        p.dtype, p.mode, p.scale = _lib.LTCA_F32, _lib.MODE_FP32, 0.125
+        p.q = p.k = p.v = p.o = C.addressof(dummy)          # never dereferenced: the shape is refused first
+        assert lib.ltca_attn_decode_workspace_bytes(C.byref(p), C.byref(n)) == 0 and n.value == 0
+        assert lib.ltca_attn_decode_static(None, C.byref(p), err, len(err)) == -1
+        assert b"bad decode arguments" in err.value
+    assert lib.ltca_attn_decode_static(None, None, err, len(err)) == -1

@@ -124,4 +124,5 @@ def test_weight_gradient_sum_without_a_group_is_the_identity():
     g = [torch.ones(3, 3), None, torch.full((2,), 2.0)]
     got = sum_weight_grads(g)
     assert len(got) == 2 and torch.equal(got[0], torch.ones(3, 3)) and torch.equal(got[1], torch.full((2,), 2.0))
-    assert sum_weight_grads(g, async_op=True).wait() == []
+    waited = sum_weight_grads(g, async_op=True).wait()       # the handle gives the same gradients back
+    assert len(waited) == 2 and waited[0] is got[0] and waited[1] is got[1]

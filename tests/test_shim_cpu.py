@@ -9,7 +9,8 @@ import pytest
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 CUDA_INC = "/usr/local/cuda/include"
-REF_INC = "/root/reference/include"
+REF_INC = os.path.join(os.environ.get("LTCA_REFERENCE_ROOT") or os.path.join(os.path.dirname(ROOT), "reference"),
+                       "include")
 
 
 def _check(extra_include):

@@ -14,6 +14,7 @@ import numpy as np
 import pytest
 import torch
 
+import oracle
 from cuda_ltc_b200 import _lib
 from util import randn
 
@@ -50,6 +51,11 @@ def test_static_decode_matches_regular_entry_point(ctx):
             assert need.value > 0, "this shape must exercise the scratch path"
         assert np.abs(o.cpu().numpy() - o_ref.cpu().numpy()).max() < 1e-5
         assert np.abs(lse.cpu().numpy() - lse_ref.cpu().numpy()).max() < 1e-5
+        # and against the fp64 oracle, so that the pair of entry points cannot be wrong together
+        o_orc, lse_orc = oracle.attn_fwd(q.cpu().numpy(), k.cpu().numpy(), v.cpu().numpy(), scale, False, None,
+                                         kv_len.cpu().numpy())
+        assert np.abs(o.cpu().numpy() - o_orc).max() < 1e-5
+        assert np.abs(lse.cpu().numpy() - lse_orc).max() < 1e-5
 
 
 def test_static_decode_refuses_oversized_scratch(ctx):
@@ -66,3 +72,22 @@ def test_static_decode_refuses_oversized_scratch(ctx):
     err = C.create_string_buffer(256)
     rc = lib.ltca_attn_decode_static(None, C.byref(p), err, len(err))
     assert rc == -4 and b"262144" in err.value
+
+
+def test_static_decode_argument_errors_come_back_as_status_codes(ctx):
+    """Shapes that are not positive, or a query length other than 1, are refused before any size is computed
+    from them (a zero batch x heads once divided by zero in the split planner)."""
+    lib = _lib.load()
+    q = torch.zeros((2, 2, 1, 64), device="cuda")
+    k = torch.zeros((2, 2, 16, 64), device="cuda")
+    o = torch.empty_like(q)
+    err = C.create_string_buffer(256)
+    need = C.c_size_t(123)
+    for field, value in (("B", 0), ("H", 0), ("H", -3), ("Sk", 0), ("D", 0), ("Sq", 2)):
+        p = ctx._params(q, k, k, o, None, 0.1, False, None, None, 0.0, _lib.MODE_FP32)
+        setattr(p, field, value)
+        assert lib.ltca_attn_decode_workspace_bytes(C.byref(p), C.byref(need)) == 0
+        if field != "Sq":
+            assert need.value == 0
+        assert lib.ltca_attn_decode_static(None, C.byref(p), err, len(err)) == -1, (field, value)
+        assert err.value

@@ -36,3 +36,22 @@ def keep_mask(B, Sq, Sk, seed, p_keep=0.7, dead_rows=((0, 0),)):
         if b < B and i < Sq:
             m[b, i, :] = 0.0
     return m
+
+
+def std_uniform_stream(seed: int, n: int, lo: float, hi: float) -> np.ndarray:
+    """The first `n` draws of ``std::uniform_real_distribution<float>(lo, hi)`` fed by ``std::mt19937(seed)``
+    (libstdc++): one 32-bit output per draw, u = float(raw) * 2^-32 (clamped just below 1), value = u * (hi - lo)
+    + lo in float arithmetic.  ``numpy.random.RandomState(seed)`` seeds MT19937 the way std::mt19937 does."""
+    raw = np.random.RandomState(seed)._bit_generator.random_raw(n).astype(np.float32)
+    u = (raw * np.float32(2.0 ** -32)).astype(np.float32)
+    u = np.where(u >= 1, np.nextafter(np.float32(1), np.float32(0)), u).astype(np.float32)
+    lo32, hi32 = np.float32(lo), np.float32(hi)
+    return (u * (hi32 - lo32) + lo32).astype(np.float32)
+
+
+def reference_tsa_weight_blob(E: int, H: int, seed: int) -> np.ndarray:
+    """Payload of the weight file the reference's cuDNN TimeSelfAttention writes for (input_dim E, H heads, seed):
+    Wq, Wk, Wv, Wo drawn in that order from one generator, each with limit sqrt(6 / (E + E))
+    (reference src/ml/cuDNN_ops.cu:34-96; every head is E wide, include/cuDNN_ops.h:166-169)."""
+    lim = np.sqrt(np.float32(6.0) / np.float32(E + E)).astype(np.float32)
+    return std_uniform_stream(seed, 4 * E * H * E, -lim, lim)
