@@ -395,9 +395,11 @@ class HostStepPipeline:
         ev = lambda: [torch.cuda.Event() for _ in range(2)]
         self.ev_in, self.ev_comp, self.ev_out = ev(), ev(), ev()
 
-    def run(self, host_in, host_out, steps: int):
+    def run(self, host_in, host_out, steps: int, compute: bool = True):
         """`steps` forward+backward passes over host_in = (q, k, v, dout), results into
-        host_out = (o, dq, dk, dv); all pinned host tensors.  Returns nothing; the caller synchronises."""
+        host_out = (o, dq, dk, dv); all pinned host tensors.  Returns nothing; the caller synchronises.
+        ``compute=False`` runs the same copies and the same stream dependencies without the kernels: what the
+        host link alone allows."""
         hq, hk, hv, hdo = host_in
         ho, hdq, hdk, hdv = host_out
         for i in range(steps):
@@ -413,10 +415,11 @@ class HostStepPipeline:
                 self.s_comp.wait_event(self.ev_in[j])
                 if i >= 2:
                     self.s_comp.wait_event(self.ev_out[j])       # the results of step i-2 have left
-                self.ctx.attn_fwd(b["q"], b["k"], b["v"], causal=self.causal, mode=_lib.MODE_BF16,
-                                  out=b["o"], lse=b["lse"])
-                self.ctx.attn_bwd(b["q"], b["k"], b["v"], b["o"], b["lse"], b["do"], causal=self.causal,
-                                  mode=_lib.MODE_AUTO, dq=b["dq"], dk=b["dk"], dv=b["dv"])
+                if compute:
+                    self.ctx.attn_fwd(b["q"], b["k"], b["v"], causal=self.causal, mode=_lib.MODE_BF16,
+                                      out=b["o"], lse=b["lse"])
+                    self.ctx.attn_bwd(b["q"], b["k"], b["v"], b["o"], b["lse"], b["do"], causal=self.causal,
+                                      mode=_lib.MODE_AUTO, dq=b["dq"], dk=b["dk"], dv=b["dv"])
                 self.ev_comp[j].record(self.s_comp)
             with torch.cuda.stream(self.s_out):
                 self.s_out.wait_event(self.ev_comp[j])

@@ -507,10 +507,10 @@ int ltca_layer_norm(ltca_ctx* ctx, float* x, const float* gamma, const float* be
 
 int ltca_validate_finite(ltca_ctx* ctx, const float* x, size_t n, int32_t* flag_out) {
     if (!ctx) return LTCA_ERR_INVALID;
-    if (!x || !flag_out) return fail(ctx, LTCA_ERR_INVALID, "null argument");
+    if (!flag_out || (!x && n > 0)) return fail(ctx, LTCA_ERR_INVALID, "null argument");
     LTCA_CUDA_OK(ctx, cudaSetDevice(ctx->device));
     LTCA_CUDA_OK(ctx, cudaMemsetAsync(flag_out, 0, sizeof(int32_t), ctx->stream));
-    if (n == 0) return LTCA_OK;
+    if (n == 0) return LTCA_OK;                 // nothing to check: clean
     validate_finite_kernel<<<blocks_for(n, 256, ctx->sm_count), 256, 0, ctx->stream>>>(x, n, flag_out);
     LTCA_LAUNCH_OK(ctx, "validate_finite_kernel");
     return LTCA_OK;

@@ -49,7 +49,10 @@ FA_CASES = [
     (2, 16, 64, 4, 16, True, 0.1, True, True, "fp32", 2e-4),
     (3, 40, 48, 3, 8, True, 0.3, False, True, "fp32", 2e-4),
     (2, 24, 32, 2, 16, False, 0.0, True, False, "fp32", 2e-4),
-    (4, 128, 256, 4, 64, False, 0.1, True, True, "tensor", 3e-2),
+    # tensor-pipe mode: every operand of a bf16 tensor-core product is rounded to bf16 (up to 2^-8 relative each);
+    # the oracle is fed the bf16-rounded weights and output gradient, and the result is held to two stacked
+    # worst-case roundings, 2^-7 of the largest magnitude (the derivation is in tests/test_configs_gpu.py)
+    (4, 128, 256, 4, 64, False, 0.1, True, True, "tensor", 2.0 ** -7),
 ]
 
 
@@ -62,8 +65,13 @@ def test_cuda_flash_attention_module(ctx, case):
     x, dy, wq, wk, wv, wo, biases, gamma, beta, m = make(B, S, E, H, D, 5, mask)
     kw = dict(biases=biases, gamma=gamma, beta=beta, use_layer_norm=ln, use_residual=res, keep_mask=m,
               dropout_prob=p, dropout_seed=99)
-    ref = oracle.fa_fwd(x, wq, wk, wv, wo, B, S, H, D, **kw)
-    gref = oracle.fa_bwd(x, wq, wk, wv, wo, dy, B, S, H, D, **kw)
+    if mode == "tensor":
+        from util import bf16_round
+        ref = oracle.fa_fwd(x, *(bf16_round(w) for w in (wq, wk, wv, wo)), B, S, H, D, **kw)
+        gref = oracle.fa_bwd(x, *(bf16_round(w) for w in (wq, wk, wv, wo)), bf16_round(dy), B, S, H, D, **kw)
+    else:
+        ref = oracle.fa_fwd(x, wq, wk, wv, wo, B, S, H, D, **kw)
+        gref = oracle.fa_bwd(x, wq, wk, wv, wo, dy, B, S, H, D, **kw)
     dev = lambda a: None if a is None else torch.from_numpy(a).cuda()
     dkw = dict(biases=tuple(dev(b) for b in biases), gamma=dev(gamma), beta=dev(beta), use_layer_norm=ln,
                use_residual=res, keep_mask=dev(m), dropout_prob=p, dropout_seed=99,
