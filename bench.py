@@ -655,7 +655,7 @@ def main():
     stream = torch.cuda.Stream(device=dev)
     ctx = ltc.Context(local_rank, stream)
     bwd_tensor = ctx.uses_tensor_pipe(q, k, v, causal=True, backward=True)
-    kernels_per_step = 1 + 3        # forward; backward = row statistics + dQ kernel + dK/dV kernel on either path
+    kernels_per_step = 1 + 3        # forward; backward = row statistics + fused kernel + dQ conversion (fp32 path: 3 too)
 
     def step():
         ctx.attn_fwd(q, k, v, causal=True, mode=_lib.MODE_BF16, out=o, lse=lse)
@@ -704,6 +704,20 @@ def main():
         ctx.enable_kernel_timing(False)
         kern_ms = [x / Kk for x in acc]
         barrier()
+
+    # ---- the bit-reproducible backward (two kernels, seven contractions), for comparison --------------------
+    det_bwd_ms = None
+    if bwd_tensor and not args.profile:
+        with torch.cuda.stream(stream):
+            ctx.attn_bwd(q, k, v, o, lse, do, causal=True, mode=_lib.MODE_AUTO, dq=dq, dk=dk, dv=dv, deterministic=True)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(5):
+                ctx.attn_bwd(q, k, v, o, lse, do, causal=True, mode=_lib.MODE_AUTO, dq=dq, dk=dk, dv=dv,
+                             deterministic=True)
+            e1.record(stream)
+        barrier()
+        det_bwd_ms = e0.elapsed_time(e1) / 5
 
     # ---- the same step repeated for about two seconds: the figure under the power cap --------------------
     sustained = None
@@ -799,9 +813,11 @@ def main():
         # own S and dP are recomputation): together the 2.5 x forward of the backward pass.
         kernels = {"attn_fwd4p_sm100_kernel": {"ms": fwd_ms, "flops": f_fwd}}
         if kern_ms:
+            # bf16 storage takes the fused backward: row statistics (which also clear the fp32 dQ accumulator),
+            # one kernel with the five contractions (2.5 x forward), and the conversion of the accumulator
             kernels["attn_bwd_stats_kernel"] = {"ms": kern_ms[0], "flops": 0.0}
-            kernels["attn_bwd_dq4_sm100_kernel"] = {"ms": kern_ms[1], "flops": 0.5 * f_fwd}
-            kernels["attn_bwd_dkv4_sm100_kernel"] = {"ms": kern_ms[2], "flops": 2.0 * f_fwd}
+            kernels["attn_bwd_fused_sm100_kernel"] = {"ms": kern_ms[1], "flops": 2.5 * f_fwd}
+            kernels["attn_bwd_dq_convert_kernel"] = {"ms": kern_ms[2], "flops": 0.0}
         else:
             kernels["attention backward (fp32 path)"] = {"ms": bwd_ms, "flops": 2.5 * f_fwd}
         dom = max(kernels, key=lambda n: kernels[n]["ms"])
@@ -818,7 +834,7 @@ def main():
             "data": "synthetic", "config": workload_config(world),
             "fwd": {"ms": fwd_ms, "tflops_per_gpu": f_fwd / (fwd_ms * 1e-3) / 1e12},
             "bwd": {"ms": bwd_ms, "tflops_per_gpu": 2.5 * f_fwd / (bwd_ms * 1e-3) / 1e12,
-                    "tensor_pipe": bool(bwd_tensor)},
+                    "tensor_pipe": bool(bwd_tensor), "bit_reproducible_variant_ms": det_bwd_ms},
             "kernels_ms": {n: round(kernels[n]["ms"], 4) for n in kernels},
             "roofline": {"bound": "tensor", "kernel": dom, "achieved": achieved, "peak": peak,
                          "unit": "TFLOP/s", "frac": achieved / peak,

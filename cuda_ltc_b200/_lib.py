@@ -40,6 +40,7 @@ class AttnParams(C.Structure):
         ("dk", C.c_void_p), ("dk_strides", Strides),
         ("dv", C.c_void_p), ("dv_strides", Strides),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+        ("bwd_deterministic", C.c_int32),
     ]
 
 

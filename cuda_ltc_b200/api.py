@@ -194,13 +194,17 @@ class Context:
         return o, lse
 
     def attn_bwd(self, q, k, v, o, lse, dout, scale=None, causal=False, keep_mask=None,
-                 kv_len=None, score_clamp=0.0, mode=_lib.MODE_AUTO, dq=None, dk=None, dv=None):
+                 kv_len=None, score_clamp=0.0, mode=_lib.MODE_AUTO, dq=None, dk=None, dv=None,
+                 deterministic=False):
+        """dq, dk, dv.  ``deterministic=True`` asks for bit-identical results from run to run (bf16 storage on the
+        tensor pipe otherwise takes the fused kernel, whose dq can differ between runs by fp32 rounding)."""
         D = q.shape[3]
         scale = 1.0 / math.sqrt(D) if scale is None else scale
         dq = torch.empty(q.shape, dtype=q.dtype, device=q.device) if dq is None else dq
         dk = torch.empty(k.shape, dtype=k.dtype, device=k.device) if dk is None else dk
         dv = torch.empty(v.shape, dtype=v.dtype, device=v.device) if dv is None else dv
         p = self._params(q, k, v, o, lse, scale, causal, keep_mask, kv_len, score_clamp, mode)
+        p.bwd_deterministic = int(bool(deterministic))
         p.dout, p.do_strides = dout.data_ptr(), _strides(dout)
         p.dq, p.dq_strides = dq.data_ptr(), _strides(dq)
         p.dk, p.dk_strides = dk.data_ptr(), _strides(dk)
@@ -381,8 +385,8 @@ class HostStepPipeline:
     """
 
     def __init__(self, ctx: "Context", compute_stream: torch.cuda.Stream, like_q: torch.Tensor,
-                 like_k: torch.Tensor, causal: bool = True):
-        self.ctx, self.causal = ctx, causal
+                 like_k: torch.Tensor, causal: bool = True, deterministic: bool = False):
+        self.ctx, self.causal, self.deterministic = ctx, causal, deterministic
         self.s_comp = compute_stream
         self.s_in, self.s_out = torch.cuda.Stream(like_q.device), torch.cuda.Stream(like_q.device)
         B, H, Sq, _ = like_q.shape
@@ -419,7 +423,8 @@ class HostStepPipeline:
                     self.ctx.attn_fwd(b["q"], b["k"], b["v"], causal=self.causal, mode=_lib.MODE_BF16,
                                       out=b["o"], lse=b["lse"])
                     self.ctx.attn_bwd(b["q"], b["k"], b["v"], b["o"], b["lse"], b["do"], causal=self.causal,
-                                      mode=_lib.MODE_AUTO, dq=b["dq"], dk=b["dk"], dv=b["dv"])
+                                      mode=_lib.MODE_AUTO, dq=b["dq"], dk=b["dk"], dv=b["dv"],
+                                      deterministic=self.deterministic)
                 self.ev_comp[j].record(self.s_comp)
             with torch.cuda.stream(self.s_out):
                 self.s_out.wait_event(self.ev_comp[j])

@@ -22,6 +22,8 @@
 // Both main kernels share the forward's structure: warps 0-3 / 4-7 elementwise for tile 0 / 1,
 // warp 8 issues tcgen05.mma, warp 9 drives TMA; the two tiles are interleaved so one tile's
 // elementwise work overlaps the other's contractions.  Every wait is bounded.
+#include <type_traits>
+
 #include "host_common.h"
 #include "sm100_ptx.cuh"
 #include "trace.cuh"
@@ -82,6 +84,7 @@ struct StatsArgs {
     ltca_strides os, dos;
     const float* lse;
     float *lse2, *delta;
+    float* dq_acc;           // optional: fp32 [B*H, Sq_pad, 64] accumulator of the fused kernel, cleared here
 };
 
 __device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&f)[8]) {
@@ -109,6 +112,11 @@ __global__ void __launch_bounds__(256) attn_bwd_stats_kernel(const StatsArgs a) 
     const int qi = (int)(row % a.Sq_pad);
     const int64_t bh = row / a.Sq_pad;
     const int h = (int)(bh % a.H), b = (int)(bh / a.H);
+    if (a.dq_acc) {
+        float4* z = reinterpret_cast<float4*>(a.dq_acc + row * kD + 8 * sub);
+        z[0] = make_float4(0.f, 0.f, 0.f, 0.f);
+        z[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
     float acc = 0.f;
     if (qi < a.Sq) {
         const T* o = reinterpret_cast<const T*>(a.o) + b * a.os.batch + h * a.os.head + (int64_t)qi * a.os.seq + 8 * sub;
@@ -1281,6 +1289,570 @@ attn_bwd_dkv4_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
 }
 
 // ---------------------------------------------------------------------------------------------
+// 4b. dK, dV and dQ in ONE persistent kernel (bf16 operands and results): five contractions per
+// (128 keys x 128 queries) block instead of the seven of the two-kernel path, and every exponential once.
+// The structure is that of the dK/dV kernel above (work item = 128 keys of one (batch, head), query steps of
+// 128, one key per tensor-memory lane); on top of it every step forms this key block's share of
+//   dQ_j = dS_j K          (M = 128 queries, N = 64, contraction over the 128 keys)
+// and adds it into an fp32 accumulator [B*H, Sq_pad, 64] in global memory with a bulk tensor reduce
+// (cp.reduce.async.bulk.tensor ... add: the addition is performed by the memory system, 4.4 - 5.9 TB/s of
+// payload measured on B200 in this access pattern, no issue slots of the SM).  A conversion kernel then scales
+// the accumulator and writes dQ in the caller's type.  The order in which the key blocks' shares arrive is not
+// fixed, so dQ is reproducible only to fp32 rounding (before its conversion to bf16); dK and dV keep one issuing
+// thread per accumulator and stay bit-reproducible.  Callers that need bit-identical dQ set
+// ltca_attn_params.bwd_deterministic and get the two-kernel path.
+//
+// dS^T has to be an operand from SHARED memory for dQ (its A operand wants queries along M, and tensor memory
+// holds keys along the lanes): the elementwise warps write it there too, in the 128-byte-swizzled layout of two
+// [128 keys x 64 queries] blocks, which dQ_j = dS_j K reads as an M-major A operand.
+// Tensor memory: S^T [0,128)  dP^T [128,256)  P^T bf16 [256,320)  dS^T bf16, then dQ_j [320,384)  dV [384,448)
+// dK [448,512): dK takes dS^T from tensor memory (an operand from shared memory costs 4 KB of shared-memory reads
+// per K step, and the contractions with N = 64 are already bound by that bandwidth), and the thread that issues dK
+// issues dQ_j right behind it into the same columns.
+// Shared memory: K, V (single buffer; released as soon as the item's last contraction has been issued, the
+// elementwise warps are busy with the item's epilogue while the next item's tiles arrive) | ring of three
+// (Q_j, dO_j, lse2_j, delta_j) stages | dS^T (32 KB; also the staging area of the item's dK / dV tiles) |
+// dQ_j staging (fp32, two 128-byte-swizzled boxes of 32 columns).
+// Warp 16 issues S^T and dV, warp 17 dP^T, dK and dQ_j, warp 18 is the TMA producer, warp 19 issues the
+// reduces of dQ_j and the stores of dK / dV.
+// ---------------------------------------------------------------------------------------------
+struct FusedSmem {
+    static constexpr int kStages = 3;                         // ring of (Q_j, dO_j, lse2_j, delta_j)
+    static constexpr int kStageBytes = 2 * kBigTile + 1024;
+    static constexpr int kResOff = 0;                         // K, V
+    static constexpr int kRingOff = 2 * kBigTile;
+    static constexpr int kDsOff = kRingOff + kStages * kStageBytes;
+    static constexpr int kDsBytes = 2 * kBigTile;             // bf16 [2 blocks of 64 queries][128 keys][128 B]
+    static constexpr int kDqOff = kDsOff + kDsBytes;
+    static constexpr int kDqBytes = kTile * kD * 4;           // fp32 [2 boxes of 32 columns][128 queries][128 B]
+    static constexpr int kBarOff = kDqOff + kDqBytes;
+    // bars: res_full, res_empty, ring_full[S], ring_empty[S], sdp_full, sdp_free, pds_full, acc_done, acc_free,
+    // dq_staged, dq_free, kv_staged, dsbuf_free, item_full[kItemSlots], item_empty[kItemSlots]
+    static constexpr int kNumBars = 2 + 2 * kStages + 9 + 2 * kItemSlots;
+    static constexpr int kMiscOff = kBarOff + kNumBars * 8;   // tmem base, abort flag, item slots
+    static constexpr int kDynBytes = kMiscOff + 16 + 4 * kItemSlots + 1024;
+};
+static_assert(FusedSmem::kDynBytes <= 227 * 1024, "shared memory plan of the fused backward kernel");
+constexpr int kFusedCtrlRegs = 64;   // the MMA thread of dP^T / dK / dQ_j holds three more operand descriptors
+static_assert(512 * kMathRegs + 128 * kFusedCtrlRegs <= kThreads * kLaunchRegs, "register budget");
+
+__global__ void __launch_bounds__(kThreads, 1)
+attn_bwd_fused_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
+                            const __grid_constant__ CUtensorMap tmap_do,
+                            const __grid_constant__ CUtensorMap tmap_k,
+                            const __grid_constant__ CUtensorMap tmap_v,
+                            const __grid_constant__ CUtensorMap tmap_dk,
+                            const __grid_constant__ CUtensorMap tmap_dv,
+                            const __grid_constant__ CUtensorMap tmap_dqacc, const BwdArgs a, const ItemGrid grid) {
+    using L = FusedSmem;
+    constexpr int kQStep = 128;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    const uint32_t res_smem = smem_base + L::kResOff;
+    const uint32_t ring_smem = smem_base + L::kRingOff, bar_base = smem_base + L::kBarOff;
+    const uint32_t ds_smem = smem_base + L::kDsOff, dq_smem = smem_base + L::kDqOff;
+    const uint32_t bar_res_full = bar_base, bar_res_empty = bar_base + 8u;
+    auto bar_ring_full = [&](int s) { return bar_base + 8u * (2 + s); };
+    auto bar_ring_empty = [&](int s) { return bar_base + 8u * (2 + L::kStages + s); };
+    const uint32_t bar_sdp_full = bar_base + 8u * (2 + 2 * L::kStages);
+    const uint32_t bar_sdp_free = bar_sdp_full + 8u;
+    const uint32_t bar_pds_full = bar_sdp_full + 16u;
+    const uint32_t bar_acc_done = bar_sdp_full + 24u;
+    const uint32_t bar_acc_free = bar_sdp_full + 32u;
+    const uint32_t bar_dq_staged = bar_sdp_full + 40u;      // the 16 warps have written dQ_j into the staging area
+    const uint32_t bar_dq_free = bar_sdp_full + 48u;        // the reduce has read the staging area
+    const uint32_t bar_kv_staged = bar_sdp_full + 56u;      // the 16 warps have written dK / dV into the dS^T area
+    const uint32_t bar_dsbuf_free = bar_sdp_full + 64u;     // the stores of dK / dV have read the dS^T area
+    volatile uint32_t* misc = reinterpret_cast<volatile uint32_t*>(smem_gen + L::kMiscOff);
+    const ItemQueue iq{bar_sdp_full + 72u, bar_sdp_full + 72u + 8u * kItemSlots,
+                       reinterpret_cast<volatile int*>(smem_gen + L::kMiscOff + 16)};
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n_q = (a.Sq + kQStep - 1) / kQStep;   // query steps in total
+    LTCA_TRACE_DECL(LTCA_TRACE_KERNEL == 5 && blockIdx.x == 5);
+    LTCA_TRACE_EVT(0x01);
+
+    if (threadIdx.x == 0) {
+        mbar_init(bar_res_full, 1);
+        mbar_init(bar_res_empty, 2);               // both MMA threads are done with K and V
+        for (int s = 0; s < L::kStages; ++s) { mbar_init(bar_ring_full(s), 1); mbar_init(bar_ring_empty(s), 2); }
+        mbar_init(bar_sdp_full, 2);                // one commit per MMA thread
+        mbar_init(bar_sdp_free, 16);               // one arrival per elementwise warp
+        mbar_init(bar_pds_full, 16);
+        mbar_init(bar_acc_done, 2);
+        mbar_init(bar_acc_free, 16);
+        mbar_init(bar_dq_staged, 16);
+        mbar_init(bar_dq_free, 1);
+        mbar_init(bar_kv_staged, 16);
+        mbar_init(bar_dsbuf_free, 1);
+        for (int i = 0; i < kItemSlots; ++i) { mbar_init(iq.full(i), 1); mbar_init(iq.empty(i), 19); }
+        misc[1] = 0u;
+        mbar_fence_init();
+    }
+    if (warp == kMmaWarp0) { tmem_alloc(smem_u32(const_cast<uint32_t*>(&misc[0])), kTmemCols); tmem_relinquish(); }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = misc[0];
+    const WaitCtx wc{&misc[1], a.status};
+    auto slot_of = [&](int g) { return g % L::kStages; };
+    auto phase_of = [&](int g) { return (uint32_t)((g / L::kStages) & 1); };
+    // the item's key tile, first query step that can see it and number of query steps (0: none)
+    auto item_steps = [&](int linear, int& k0, int& h, int& b, int& kvlen, int& j_begin) {
+        int rank;
+        sched_item(grid, linear, rank, h, b);
+        k0 = rank * kTile;                          // early key blocks carry the most causal work
+        kvlen = a.Sk;
+        if (a.kv_len) kvlen = min(max(a.kv_len[b], 0), a.Sk);
+        j_begin = 0;
+        if (a.causal) j_begin = max(0, k0 - a.causal_off) / kQStep;
+        const bool active = (k0 < kvlen) && (j_begin < n_q);
+        return active ? n_q - j_begin : 0;
+    };
+
+    if (warp >= 16) {
+      reg_dealloc<kFusedCtrlRegs>();
+      if (warp == kTmaWarp) {
+        if (lane == 0) {
+            int g = 0, na = 0;
+            bool ok = true;
+            for (int nq = 0; ok; ++nq) {
+                const int linear = iq.produce(nq, grid.counters, grid.n_items, wc);
+                if (linear < 0) break;
+                int k0, h, b, kvlen, j_begin;
+                const int n_it = item_steps(linear, k0, h, b, kvlen, j_begin);
+                if (n_it == 0) continue;
+                ok = mbar_wait(bar_res_empty, (uint32_t)((na & 1) ^ 1), wc, 0xe1);
+                if (!ok) break;
+                mbar_arrive_expect_tx(bar_res_full, 2u * kBigTile);
+                tma_load_4d(res_smem, &tmap_k, bar_res_full, 0, k0, h, b);
+                tma_load_4d(res_smem + kBigTile, &tmap_v, bar_res_full, 0, k0, h, b);
+                const float* lse2_row = a.lse2 + ((int64_t)b * a.H + h) * a.Sq_pad;
+                const float* dlt_row = a.delta + ((int64_t)b * a.H + h) * a.Sq_pad;
+                for (int it = 0; it < n_it && ok; ++it, ++g) {
+                    const int j = j_begin + it;
+                    ok = mbar_wait(bar_ring_empty(slot_of(g)), phase_of(g) ^ 1u, wc, 0xe0);
+                    if (!ok) break;
+                    const uint32_t st = ring_smem + slot_of(g) * L::kStageBytes;
+                    const uint32_t bar = bar_ring_full(slot_of(g));
+                    mbar_arrive_expect_tx(bar, 2u * kBigTile + 1024u);
+                    tma_load_4d(st, &tmap_q, bar, 0, j * kQStep, h, b);
+                    tma_load_4d(st + kBigTile, &tmap_do, bar, 0, j * kQStep, h, b);
+                    asm volatile(
+                        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], 512, [%2];"
+                        ::"r"(st + 2 * kBigTile), "l"(reinterpret_cast<uint64_t>(lse2_row + j * kQStep)), "r"(bar)
+                        : "memory");
+                    asm volatile(
+                        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], 512, [%2];"
+                        ::"r"(st + 2 * kBigTile + 512), "l"(reinterpret_cast<uint64_t>(dlt_row + j * kQStep)),
+                          "r"(bar)
+                        : "memory");
+                }
+                ++na;
+            }
+        }
+      } else if (warp == kMmaWarp0 || warp == kMmaWarp0 + 1) {
+        // which == 0: S^T = K Q_j^T and dV += P^T dO_j
+        // which == 1: dP^T = V dO_j^T, dK += dS^T Q_j and dQ_j = dS_j K
+        // one instantiation per role, so that each thread's code only carries its own operand descriptors
+        auto mma_role = [&](auto which_c) {
+            constexpr int which = decltype(which_c)::value;
+            constexpr uint32_t idesc_s = make_idesc_bf16(kTile, kQStep, 0, 0);
+            constexpr uint32_t idesc_acc = make_idesc_bf16(kTile, kD, 0, 1);    // A K-major (or tensor memory), B N-major
+            constexpr uint32_t idesc_dq = make_idesc_bf16(kQStep, kD, 1, 1);    // A M-major (dS^T read as dS), B N-major
+            const uint64_t a_desc = make_smem_desc_sw128(res_smem + (which == 0 ? 0 : kBigTile), 16, 1024);
+            // the streamed operand of the first contraction (Q for S^T, dO for dP^T), K-major
+            const uint64_t b1_desc = make_smem_desc_sw128(ring_smem + (which == 0 ? 0 : kBigTile), 16, 1024);
+            // the streamed operand of the accumulation (dO for dV, Q for dK), rows as the contraction index
+            const uint64_t b2_desc = make_smem_desc_sw128(ring_smem + (which == 0 ? kBigTile : 0), 8192, 1024);
+            // dS^T in shared memory: K-major A of dK (two 64-query blocks 16 KB apart, 32 B per K step inside a
+            // block) and M-major A of dQ_j (blocks of 64 queries 16 KB apart, 16 key rows = 2 KB per K step)
+            const uint64_t ds_m_desc = make_smem_desc_sw128(ds_smem, 2 * kBigTile / 2, 1024);
+            // K as the N-major B operand of dQ_j: 128 key rows of 128 bytes, 16 rows per K step
+            const uint64_t kn_desc = make_smem_desc_sw128(res_smem, 8192, 1024);
+            const uint32_t d1 = tmem_base + (which == 0 ? 0 : 128);
+            const uint32_t a2 = tmem_base + 256;                 // P^T (which == 0 only)
+            const uint32_t d2 = tmem_base + (which == 0 ? 384 : 448);
+            const uint32_t ds_tmem = tmem_base + 320;            // dS^T (bf16) of the step, then dQ_j (which == 1 only)
+            // the accumulation that is still to be issued (one step behind the first contraction)
+            bool pending = false;
+            int p_g = 0, p_na = 0;
+            bool p_acc = false, p_first = false, p_last = false;
+            bool ok = true;
+            auto do_acc = [&]() {
+                ok = mbar_wait(bar_pds_full, (uint32_t)(p_g & 1), wc, 0xf4);
+                LTCA_TRACE_EVT(0x21 + (p_g << 8));
+                // the previous item's dV / dK must have left tensor memory before they are overwritten
+                if (ok && p_first && p_na > 0) ok = mbar_wait(bar_acc_free, (uint32_t)((p_na - 1) & 1), wc, 0xf6);
+                if (!ok) return;
+                tc_fence_after_sync();
+                const uint64_t bd = b2_desc + (uint64_t)((slot_of(p_g) * L::kStageBytes) >> 4);
+                if constexpr (which == 0) {
+#pragma unroll
+                    for (int k = 0; k < kQStep / 16; ++k)
+                        mma_ts(d2, a2 + k * 8, bd + 128 * k, idesc_acc, (p_acc || k > 0) ? 1u : 0u);
+                } else {
+                    // dK takes dS^T from tensor memory; dQ_j then overwrites those very columns: one thread's
+                    // contractions run in order, so dK has read them by then
+#pragma unroll
+                    for (int k = 0; k < kQStep / 16; ++k)
+                        mma_ts(d2, ds_tmem + k * 8, bd + 128 * k, idesc_acc, (p_acc || k > 0) ? 1u : 0u);
+#pragma unroll
+                    for (int k = 0; k < kTile / 16; ++k)
+                        mma_ss(ds_tmem, ds_m_desc + 128 * k, kn_desc + 128 * k, idesc_dq, k > 0 ? 1u : 0u);
+                }
+                mma_commit(bar_acc_done);
+                mma_commit(bar_ring_empty(slot_of(p_g)));
+                if (p_last) mma_commit(bar_res_empty);          // K (or V) of this item is no longer read
+                LTCA_TRACE_EVT(0x22 + (p_g << 8));
+                pending = false;
+            };
+            int g = 0, na = 0;
+            for (int nq = 0; ok; ++nq) {
+                const int linear = iq.consume(nq, wc);
+                if (linear < 0) break;
+                int k0, h, b, kvlen, j_begin;
+                const int n_it = item_steps(linear, k0, h, b, kvlen, j_begin);
+                if (n_it == 0) continue;
+                // the previous item's last accumulation reads K / V of that item: it goes out before the wait
+                // for this item's tiles, which arrive only after that accumulation has released the buffer
+                if (pending) do_acc();
+                if (!ok) break;
+                ok = mbar_wait(bar_res_full, (uint32_t)(na & 1), wc, 0xf0);
+                for (int it = 0; it < n_it && ok; ++it, ++g) {
+                    ok = mbar_wait(bar_ring_full(slot_of(g)), phase_of(g), wc, 0xf2);
+                    if (g >= 1) ok = ok && mbar_wait(bar_sdp_free, (uint32_t)((g - 1) & 1), wc, 0xf3);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    const uint64_t bd = b1_desc + (uint64_t)((slot_of(g) * L::kStageBytes) >> 4);
+#pragma unroll
+                    for (int k = 0; k < kD / 16; ++k) mma_ss(d1, a_desc + 2 * k, bd + 2 * k, idesc_s, k > 0);
+                    mma_commit(bar_sdp_full);
+                    LTCA_TRACE_EVT(0x20 + (g << 8));
+                    if (pending) do_acc();
+                    if (!ok) break;
+                    p_g = g; p_na = na; p_acc = it > 0; p_first = it == 0; p_last = it == n_it - 1;
+                    pending = true;
+                }
+                ++na;
+            }
+            if (ok && pending) do_acc();
+            if (ok && g > 0) ok = mbar_wait(bar_acc_done, (uint32_t)((g - 1) & 1), wc, 0xf5);
+        };
+        if (lane == 0) {
+            if (warp == kMmaWarp0) mma_role(std::integral_constant<int, 0>{});
+            else mma_role(std::integral_constant<int, 1>{});
+        }
+      } else {
+        // warp 19: adds every step's dQ_j tile into the fp32 accumulator (two boxes of 32 columns) and stores each
+        // item's dK and dV tiles (staged by the elementwise warps in the dS^T area).  Rows past the end of the
+        // keys are clipped by the tensor maps; the accumulator's rows are padded to whole steps.
+        if (lane == 0) {
+            int g = 0, na = 0;
+            bool ok = true;
+            for (int nq = 0; ok; ++nq) {
+                const int linear = iq.consume(nq, wc);
+                if (linear < 0) break;
+                int k0, h, b, kvlen, j_begin;
+                const int n_it = item_steps(linear, k0, h, b, kvlen, j_begin);
+                if (n_it == 0) continue;
+                for (int it = 0; it < n_it && ok; ++it, ++g) {
+                    ok = mbar_wait(bar_dq_staged, (uint32_t)(g & 1), wc, 0xe8);
+                    if (!ok) break;
+                    LTCA_TRACE_EVT(0x30 + (g << 8));
+                    const int q0 = (j_begin + it) * kQStep;
+                    tma_reduce_add_4d(&tmap_dqacc, dq_smem, 0, q0, h, b);
+                    tma_reduce_add_4d(&tmap_dqacc, dq_smem + kTile * 128, 32, q0, h, b);
+                    tma_store_commit();
+                    tma_store_wait_read<0>();
+                    LTCA_TRACE_EVT(0x31 + (g << 8));
+                    mbar_arrive(bar_dq_free);
+                }
+                if (!ok) break;
+                ok = mbar_wait(bar_kv_staged, (uint32_t)(na & 1), wc, 0xe9);
+                if (ok) {
+                    tma_store_4d(&tmap_dk, ds_smem, 0, k0, h, b);
+                    tma_store_4d(&tmap_dv, ds_smem + kBigTile, 0, k0, h, b);
+                    tma_store_commit();
+                    tma_store_wait_read<0>();
+                }
+                mbar_arrive(bar_dsbuf_free);
+                ++na;
+            }
+            tma_store_wait_all<0>();                // every reduce and store has landed before the CTA ends
+        }
+      }
+    } else {
+        reg_alloc<kMathRegs>();
+        const int wq = warp & 3, cq = warp >> 2;
+        const int row = wq * 32 + lane;
+        const uint32_t lane_base = (uint32_t)(wq * 32) << 16;
+        const uint32_t tS = tmem_base + lane_base + 32 * cq;
+        const uint32_t tDP = tS + 128;
+        const uint32_t tP = tmem_base + lane_base + 256 + 16 * cq;
+        const uint32_t tDQ = tmem_base + lane_base + 320 + 16 * cq;
+        const uint32_t tDV = tmem_base + lane_base + 384 + 16 * cq;
+        const uint32_t tDK = tDV + 64;
+        const float c2 = a.scale_log2;
+        const bool general = (a.keep_mask != nullptr) || (a.use_clamp != 0);
+        // this thread's 64 bytes of its dS^T row (32 query columns of key `row`): block cq / 2, 16-byte chunks
+        // 4 (cq % 2) .. + 3, swizzled with the row; the dQ_j staging uses the same geometry with fp32 columns
+        // 16 cq .. + 15 of query `row`: box cq / 2, chunks 4 (cq % 2) .. + 3
+        // (both areas have the same size and geometry, so one 32-bit address serves both)
+        static_assert(L::kDqBytes == L::kDsBytes && kTile * 128 == kBigTile, "dS^T and dQ staging share their geometry");
+        const uint32_t ds_row = ds_smem + (uint32_t)((cq >> 1) * kBigTile + row * 128);
+        const uint32_t chunk0 = (uint32_t)((cq & 1) * 4);
+        const uint32_t sw = (uint32_t)(row & 7);
+
+        int g = 0, na = 0;
+        bool ok = true;
+        // dQ_j of step g - 1: out of tensor memory, into the staging area, announced to the reducing thread
+        // (the caller has already waited for the staging area: no loop in here, so that the 16 values are not kept
+        // in registers across a wait)
+        auto stage_dq = [&](const uint32_t (&dqv)[16], int gprev) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                st_shared_v4(ds_row + (uint32_t)L::kDsBytes + (((chunk0 + i) ^ sw) << 4), dqv[4 * i], dqv[4 * i + 1],
+                             dqv[4 * i + 2], dqv[4 * i + 3]);
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_dq_staged);
+            LTCA_TRACE_EVT(0x16 + (gprev << 8));
+        };
+        // the reduce of tile gprev - 1 has read the staging area
+        auto wait_dq_stage = [&](int gprev) {
+            if (gprev > 0) ok = mbar_wait_warp(bar_dq_free, (uint32_t)((gprev - 1) & 1), wc, 0xca);
+        };
+        for (int nq = 0; ok; ++nq) {
+            const int linear = iq.consume_warp(nq, wc);
+            if (linear < 0) break;
+            int k0, h, b, kvlen, j_begin;
+            const int n_it = item_steps(linear, k0, h, b, kvlen, j_begin);
+            const int kj = k0 + row;                                   // this thread's key
+            const bool key_live = kj < kvlen;
+            if (n_it == 0) {
+                if (kj < a.Sk) {                       // no query sees these keys: the gradients are zero
+                    __nv_bfloat16* dkrow = reinterpret_cast<__nv_bfloat16*>(a.dk) + b * a.dks.batch +
+                                           h * a.dks.head + (int64_t)kj * a.dks.seq + cq * 16;
+                    __nv_bfloat16* dvrow = reinterpret_cast<__nv_bfloat16*>(a.dv) + b * a.dvs.batch +
+                                           h * a.dvs.head + (int64_t)kj * a.dvs.seq + cq * 16;
+                    uint32_t z[16];
+#pragma unroll
+                    for (int c = 0; c < 16; ++c) z[c] = 0u;
+                    store_row16_bf16(dvrow, z, 0.f);
+                    store_row16_bf16(dkrow, z, 0.f);
+                }
+                continue;
+            }
+            for (int it = 0; it < n_it && ok; ++it, ++g) {
+                const int j = j_begin + it;
+                // S^T and dP^T of this step into registers (defined afresh in every iteration, so that they are
+                // not carried round the loop); the next step's may then be computed
+                uint32_t s[32], dp[32];
+                ok = mbar_wait_warp(bar_sdp_full, (uint32_t)(g & 1), wc, 0xc0);
+                if (!ok) break;
+                LTCA_TRACE_EVT(0x10 + (g << 8));
+                tc_fence_after_sync();
+                tmem_ld32(tS, s);
+                tmem_ld32(tDP, dp);
+                tmem_wait_ld();
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_sdp_free);
+                LTCA_TRACE_EVT(0x11 + (g << 8));
+                // lse2 and delta of this thread's 32 query columns (every lane reads the same address)
+                const float4* st4 = reinterpret_cast<const float4*>(
+                    smem_gen + L::kRingOff + slot_of(g) * L::kStageBytes + 2 * kBigTile) + cq * 8;
+                const int q0 = j * kQStep + cq * 32;
+                // a query column c is hidden from this key when q0 + c + off < kj
+                const bool edge = !key_live || (k0 + kTile > kvlen) ||
+                                  (a.causal && (j * kQStep + a.causal_off < k0 + kTile - 1));
+                if (general) {
+#pragma unroll
+                    for (int c4 = 0; c4 < 8; ++c4) {
+                        const float4 l4 = st4[c4];
+                        const float4 d4 = st4[32 + c4];
+                        const float ls[4] = {l4.x, l4.y, l4.z, l4.w};
+                        const float dl[4] = {d4.x, d4.y, d4.z, d4.w};
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const int c = 4 * c4 + e;
+                            const float sv = __uint_as_float(s[c]);
+                            float pv = fast_exp2(fmaf(sv, c2, -ls[e]));
+                            float d = pv * (__uint_as_float(dp[c]) - dl[e]);
+                            bool vis = key_live && (!a.causal || (kj <= q0 + c + a.causal_off));
+                            if (vis && a.keep_mask && (q0 + c) < a.Sq)
+                                vis = a.keep_mask[((int64_t)b * a.Sq + q0 + c) * a.Sk + kj] != 0.0f;
+                            if (a.use_clamp && sv >= a.clamp_raw) {
+                                pv = fast_exp2(a.clamp_log2 - ls[e]);
+                                d = 0.f;
+                            }
+                            s[c] = __float_as_uint(vis ? pv : 0.f);
+                            dp[c] = __float_as_uint(vis ? d : 0.f);
+                        }
+                    }
+                } else if (edge) {
+                    // causal diagonal or end of the keys, no dense mask: selects only, no branches.
+                    // Query column c is visible to this key when c >= cmin.
+                    const int cmin = !key_live ? 0x7fffffff : (a.causal ? kj - a.causal_off - q0 : -0x7fffffff);
+#pragma unroll
+                    for (int c4 = 0; c4 < 8; ++c4) {
+                        const float4 l4 = st4[c4];
+                        const float4 d4 = st4[32 + c4];
+                        const float ls[4] = {l4.x, l4.y, l4.z, l4.w};
+                        const float dl[4] = {d4.x, d4.y, d4.z, d4.w};
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const int c = 4 * c4 + e;
+                            const float pv = fast_exp2(fmaf(__uint_as_float(s[c]), c2, -ls[e]));
+                            const bool vis = c >= cmin;
+                            s[c] = __float_as_uint(vis ? pv : 0.f);
+                            dp[c] = __float_as_uint(vis ? pv * (__uint_as_float(dp[c]) - dl[e]) : 0.f);
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int c4 = 0; c4 < 8; ++c4) {
+                        const float4 l4 = st4[c4];
+                        const float4 d4 = st4[32 + c4];
+                        const float ls[4] = {l4.x, l4.y, l4.z, l4.w};
+                        const float dl[4] = {d4.x, d4.y, d4.z, d4.w};
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const int c = 4 * c4 + e;
+                            const float pv = fast_exp2(fmaf(__uint_as_float(s[c]), c2, -ls[e]));
+                            s[c] = __float_as_uint(pv);
+                            dp[c] = __float_as_uint(pv * (__uint_as_float(dp[c]) - dl[e]));
+                        }
+                    }
+                }
+                uint32_t pt[16], dst[16], unused[16];
+                pack32<false>(s, pt, unused);
+                pack32<false>(dp, dst, unused);
+                LTCA_TRACE_EVT(0x12 + (g << 8));
+                if (g > 0) {
+                    // the contractions of the previous step have read P^T and dS^T, and its dQ_j is complete
+                    ok = mbar_wait_warp(bar_acc_done, (uint32_t)((g - 1) & 1), wc, 0xc1);
+                    if (!ok) break;
+                }
+                if (it > 0) {
+                    wait_dq_stage(g - 1);
+                    if (!ok) break;
+                }
+                // the first dS^T of an item goes where the previous item's dK / dV tiles were staged
+                if (it == 0 && na > 0) {
+                    ok = mbar_wait_warp(bar_dsbuf_free, (uint32_t)((na - 1) & 1), wc, 0xc3);
+                    if (!ok) break;
+                }
+                LTCA_TRACE_EVT(0x13 + (g << 8));
+                tc_fence_after_sync();
+                // dQ_j of the previous step sits in the columns that take this step's dS^T: out first (read at an
+                // item's first step too, where it is not used: a conditional load would keep 16 registers alive
+                // round the loop)
+                uint32_t dqv[16];
+                tmem_ld16(tDQ, dqv);
+                tmem_st16(tP, pt);
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    st_shared_v4(ds_row + (((chunk0 + i) ^ sw) << 4), dst[4 * i], dst[4 * i + 1], dst[4 * i + 2],
+                                 dst[4 * i + 3]);
+                tmem_wait_ld();
+                tmem_st16(tDQ, dst);                          // dS^T for dK (tensor memory) and for dQ_j (shared memory)
+                if (it > 0) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        st_shared_v4(ds_row + (uint32_t)L::kDsBytes + (((chunk0 + i) ^ sw) << 4), dqv[4 * i],
+                                     dqv[4 * i + 1], dqv[4 * i + 2], dqv[4 * i + 3]);
+                }
+                fence_proxy_async_smem();                     // one fence for dS^T and the staged dQ_j
+                tmem_wait_st();
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(bar_pds_full);
+                    if (it > 0) mbar_arrive(bar_dq_staged);
+                }
+                LTCA_TRACE_EVT(0x14 + (g << 8));
+            }
+            if (!ok) break;
+            // item epilogue: the last dQ_j, then dV and scale * dK out of tensor memory
+            ok = mbar_wait_warp(bar_acc_done, (uint32_t)((g - 1) & 1), wc, 0xc2);
+            if (!ok) break;
+            tc_fence_after_sync();
+            wait_dq_stage(g - 1);
+            if (!ok) break;
+            uint32_t ov[16], ok_[16];
+            {
+                uint32_t dqv[16];
+                tmem_ld16(tDQ, dqv);
+                tmem_ld16(tDV, ov);
+                tmem_ld16(tDK, ok_);
+                tmem_wait_ld();
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_acc_free);
+                stage_dq(dqv, g - 1);
+            }
+            {
+                // this thread's 16 columns of dK (scaled) and dV, bf16, into the dS^T area (the item's last
+                // contractions have read it) in the layout of two 128-byte-swizzled TMA boxes
+                const uint32_t st_k = ds_smem + (uint32_t)(row * 128);
+#pragma unroll
+                for (int v = 0; v < 2; ++v) {
+                    const uint32_t pos = (((uint32_t)(2 * cq + v)) ^ sw) << 4;
+                    st_shared_v4(st_k + pos,
+                                 pack_bf16x2(__uint_as_float(ok_[8 * v + 0]) * a.scale, __uint_as_float(ok_[8 * v + 1]) * a.scale),
+                                 pack_bf16x2(__uint_as_float(ok_[8 * v + 2]) * a.scale, __uint_as_float(ok_[8 * v + 3]) * a.scale),
+                                 pack_bf16x2(__uint_as_float(ok_[8 * v + 4]) * a.scale, __uint_as_float(ok_[8 * v + 5]) * a.scale),
+                                 pack_bf16x2(__uint_as_float(ok_[8 * v + 6]) * a.scale, __uint_as_float(ok_[8 * v + 7]) * a.scale));
+                    st_shared_v4(st_k + (uint32_t)kBigTile + pos,
+                                 pack_bf16x2(__uint_as_float(ov[8 * v + 0]), __uint_as_float(ov[8 * v + 1])),
+                                 pack_bf16x2(__uint_as_float(ov[8 * v + 2]), __uint_as_float(ov[8 * v + 3])),
+                                 pack_bf16x2(__uint_as_float(ov[8 * v + 4]), __uint_as_float(ov[8 * v + 5])),
+                                 pack_bf16x2(__uint_as_float(ov[8 * v + 6]), __uint_as_float(ov[8 * v + 7])));
+                }
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_kv_staged);
+                ++na;
+            }
+        }
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    if (threadIdx.x == 0) item_counters_release(grid.counters);
+    if (warp == kMmaWarp0) {
+        __syncwarp();
+        if (misc[1]) __nanosleep(200000);
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+// The fp32 dQ accumulator of the fused kernel, scaled, into the caller's dQ (bf16, any strides); 8 lanes per row.
+__global__ void __launch_bounds__(256) attn_bwd_dq_convert_kernel(const float* __restrict__ acc, void* dq,
+                                                                  ltca_strides dqs, int B, int H, int Sq, int Sq_pad,
+                                                                  float scale) {
+    const int64_t idx = (int64_t)blockIdx.x * 32 + (threadIdx.x >> 3);       // row among B * H * Sq
+    const int sub = threadIdx.x & 7;
+    if (idx >= (int64_t)B * H * Sq) return;
+    const int qi = (int)(idx % Sq);
+    const int64_t bh = idx / Sq;
+    const int h = (int)(bh % H), b = (int)(bh / H);
+    const float4* src = reinterpret_cast<const float4*>(acc + (bh * Sq_pad + qi) * kD + 8 * sub);
+    const float4 x = __ldg(src), y = __ldg(src + 1);
+    uint4 w;
+    w.x = pack_bf16x2(x.x * scale, x.y * scale);
+    w.y = pack_bf16x2(x.z * scale, x.w * scale);
+    w.z = pack_bf16x2(y.x * scale, y.y * scale);
+    w.w = pack_bf16x2(y.z * scale, y.w * scale);
+    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(dq) + b * dqs.batch + h * dqs.head + (int64_t)qi * dqs.seq + 8 * sub;
+    *reinterpret_cast<uint4*>(dst) = w;
+}
+
+// ---------------------------------------------------------------------------------------------
 // 5. dQ, single-tile persistent variant (bf16 operands and results).
 // Work item = 128 queries of one (batch, head); key steps of 128; nothing aliased in tensor memory:
 //   S [0,128)  dP [128,256)  dQ [320,384)  and three dS (bf16) buffers used in turn,
@@ -1692,10 +2264,18 @@ size_t stats_bytes(const ltca_attn_params* p) {
     return align_up((size_t)p->B * p->H * sq_pad * sizeof(float), 256);
 }
 
+size_t dq_acc_bytes(const ltca_attn_params* p) {
+    const size_t sq_pad = align_up((size_t)p->Sq, 256);
+    return align_up((size_t)p->B * p->H * sq_pad * kD * sizeof(float), 256);
+}
+
+// The fused kernel serves bf16 storage unless the caller asks for bit-reproducible dQ.
+bool use_fused(const ltca_attn_params* p) { return p->dtype == LTCA_BF16 && !p->bwd_deterministic; }
+
 template <typename OutT>
 int launch_main(ltca_ctx* ctx, const ltca_attn_params* p, const void* q, const void* k, const void* v,
                 const void* dout, const ltca_strides& qs, const ltca_strides& ks, const ltca_strides& vs,
-                const ltca_strides& dos, const float* lse2, const float* delta) {
+                const ltca_strides& dos, const float* lse2, const float* delta, float* dq_acc) {
     CUtensorMap tq128, tdo128, tk64, tv64, tq64, tdo64, tk128, tv128;
     int rc;
     if ((rc = make_tmap_bhsd(ctx, &tq128, q, 2, p->B, p->H, p->Sq, kD, qs, 64, kTile))) return rc;
@@ -1725,6 +2305,35 @@ int launch_main(ltca_ctx* ctx, const ltca_attn_params* p, const void* q, const v
     a.kv_len = p->kv_len;
     a.status = ctx->d_status;
 
+    if constexpr (sizeof(OutT) == 2) {
+        if (dq_acc) {
+            static SmemOptIn opt_fused;
+            LTCA_CUDA_OK(ctx, opt_in_dynamic_smem(opt_fused, ctx->device, attn_bwd_fused_sm100_kernel,
+                                                  FusedSmem::kDynBytes));
+            ItemGrid ig;
+            ig.nblk = (p->Sk + kTile - 1) / kTile;
+            ig.H = p->H;
+            ig.BH = p->H * p->B;
+            ig.n_items = ig.nblk * ig.BH;
+            ig.counters = ctx->d_sched + 4;             // ints 4,5: shared with the dK/dV kernel (never both in one call)
+            const int n_cta = ig.n_items < ctx->sm_count ? ig.n_items : ctx->sm_count;
+            CUtensorMap tdk, tdv, tacc;
+            if ((rc = make_tmap_bhsd(ctx, &tdk, p->dk, 2, p->B, p->H, p->Sk, kD, p->dk_strides, 64, kTile))) return rc;
+            if ((rc = make_tmap_bhsd(ctx, &tdv, p->dv, 2, p->B, p->H, p->Sk, kD, p->dv_strides, 64, kTile))) return rc;
+            const ltca_strides accs{(int64_t)p->H * a.Sq_pad * kD, (int64_t)a.Sq_pad * kD, kD};
+            if ((rc = make_tmap_bhsd(ctx, &tacc, dq_acc, 4, p->B, p->H, a.Sq_pad, kD, accs, 32, kTile))) return rc;
+            attn_bwd_fused_sm100_kernel<<<n_cta, kThreads, FusedSmem::kDynBytes, ctx->stream>>>(
+                tq128, tdo128, tk128, tv128, tdk, tdv, tacc, a, ig);
+            LTCA_LAUNCH_OK(ctx, "attn_bwd_fused_sm100_kernel");
+            kernel_timing_mark(ctx, 2);
+            const int64_t rows = (int64_t)p->B * p->H * p->Sq;
+            attn_bwd_dq_convert_kernel<<<(unsigned)((rows + 31) / 32), 256, 0, ctx->stream>>>(
+                dq_acc, p->dq, p->dq_strides, p->B, p->H, p->Sq, a.Sq_pad, p->scale);
+            LTCA_LAUNCH_OK(ctx, "attn_bwd_dq_convert_kernel");
+            kernel_timing_mark(ctx, 3);
+            return LTCA_OK;
+        }
+    }
     auto kdq = attn_bwd_dq_sm100_kernel<OutT, sizeof(OutT) == 4>;
     auto kdkv = attn_bwd_dkv_sm100_kernel<OutT, sizeof(OutT) == 4>;
     static SmemOptIn opt_dq, opt_dkv;         // one pair per template instantiation
@@ -1814,7 +2423,9 @@ bool attn_bwd_sm100_supported(const ltca_attn_params* p) {
     return true;
 }
 
-size_t attn_bwd_sm100_workspace(const ltca_attn_params* p) { return 2 * stats_bytes(p); }
+size_t attn_bwd_sm100_workspace(const ltca_attn_params* p) {
+    return 2 * stats_bytes(p) + (use_fused(p) ? dq_acc_bytes(p) : 0);
+}
 
 int launch_attn_bwd_sm100(ltca_ctx* ctx, const ltca_attn_params* p) {
     size_t need = attn_bwd_sm100_workspace(p);
@@ -1835,11 +2446,13 @@ int launch_attn_bwd_sm100(ltca_ctx* ctx, const ltca_attn_params* p) {
     char* w = reinterpret_cast<char*>(p->workspace);
     float* lse2 = reinterpret_cast<float*>(w);  w += stats_bytes(p);
     float* delta = reinterpret_cast<float*>(w); w += stats_bytes(p);
+    float* dq_acc = nullptr;
+    if (use_fused(p)) { dq_acc = reinterpret_cast<float*>(w); w += dq_acc_bytes(p); }
 
     StatsArgs s;
     s.B = p->B; s.H = p->H; s.Sq = p->Sq; s.Sq_pad = (int)align_up((size_t)p->Sq, 256);
     s.o = p->o; s.dout = p->dout; s.os = p->o_strides; s.dos = p->do_strides;
-    s.lse = p->lse; s.lse2 = lse2; s.delta = delta;
+    s.lse = p->lse; s.lse2 = lse2; s.delta = delta; s.dq_acc = dq_acc;
     const int64_t rows = (int64_t)p->B * p->H * s.Sq_pad;
     const unsigned blocks = (unsigned)((rows + 31) / 32);
     kernel_timing_mark(ctx, 0);
@@ -1850,7 +2463,7 @@ int launch_attn_bwd_sm100(ltca_ctx* ctx, const ltca_attn_params* p) {
 
     if (p->dtype == LTCA_BF16)
         return launch_main<__nv_bfloat16>(ctx, p, p->q, p->k, p->v, p->dout, p->q_strides, p->k_strides,
-                                          p->v_strides, p->do_strides, lse2, delta);
+                                          p->v_strides, p->do_strides, lse2, delta, dq_acc);
 
     // fp32 storage: bf16 copies of the four operands, fp32 gradients out
     void* qb = w;  w += pq;
@@ -1877,7 +2490,7 @@ int launch_attn_bwd_sm100(ltca_ctx* ctx, const ltca_attn_params* p) {
     kernel_timing_mark(ctx, 1);
     ltca_strides cq{(int64_t)p->H * p->Sq * kD, (int64_t)p->Sq * kD, kD};
     ltca_strides ck{(int64_t)p->H * p->Sk * kD, (int64_t)p->Sk * kD, kD};
-    return launch_main<float>(ctx, p, qb, kb, vb, gb, cq, ck, ck, cq, lse2, delta);
+    return launch_main<float>(ctx, p, qb, kb, vb, gb, cq, ck, ck, cq, lse2, delta, nullptr);
 }
 
 }  // namespace ltca

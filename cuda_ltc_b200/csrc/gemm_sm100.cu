@@ -51,6 +51,8 @@ struct GemmKArgs {
     int M, N, K;
     int n_sum, ksplit;
     int tiles_x, tiles_y, tiles_z;   // N tiles, M tiles, problems x K slices
+    int batch_h, batch_b;            // independent products of the same shape (slowest index of the tile list)
+    int64_t c_bs[2];                 // element strides of C over (h, b)
     int64_t ldc;
     int out_bf16;
     int tma_store;           // results leave through shared memory and a TMA store (needs 16-byte aligned rows)
@@ -63,12 +65,16 @@ struct GemmKArgs {
 // One tile of the work list of a CTA.
 struct GemmTile {
     int m0, n0, problem, slice, kb_begin, kb_end, pair_begin, n_pairs, n_iters;
+    int bh, bb;                      // batch entry
 };
 __device__ __forceinline__ GemmTile gemm_tile(const GemmKArgs& g, int linear) {
     GemmTile t;
     const int x = linear % g.tiles_x;
     const int yz = linear / g.tiles_x;
-    const int y = yz % g.tiles_y, z = yz / g.tiles_y;
+    const int y = yz % g.tiles_y, zw = yz / g.tiles_y;
+    const int z = zw % g.tiles_z, w = zw / g.tiles_z;
+    t.bh = w % g.batch_h;
+    t.bb = w / g.batch_h;
     t.n0 = x * kBN;
     t.m0 = y * kBM;
     t.problem = z / g.ksplit;
@@ -107,7 +113,7 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap ta0, const __grid_con
     volatile uint32_t* misc = reinterpret_cast<volatile uint32_t*>(smem_gen + kMiscOff);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n_tiles = g.tiles_x * g.tiles_y * g.tiles_z;
+    const int n_tiles = g.tiles_x * g.tiles_y * g.tiles_z * g.batch_h * g.batch_b;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_empty(s), 1); }
@@ -141,19 +147,19 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap ta0, const __grid_con
                         mbar_arrive_expect_tx(bar_full(s), (uint32_t)kStageBytes);
                         const int k0 = kb * kBK;
                         if (kAMn) {
-                            tma_load_4d(a_smem(s), ta, bar_full(s), t.m0, k0, 0, 0);
-                            tma_load_4d(a_smem(s) + 8192, ta, bar_full(s), t.m0 + 64, k0, 0, 0);
+                            tma_load_4d(a_smem(s), ta, bar_full(s), t.m0, k0, t.bh, t.bb);
+                            tma_load_4d(a_smem(s) + 8192, ta, bar_full(s), t.m0 + 64, k0, t.bh, t.bb);
                         } else {
-                            tma_load_4d(a_smem(s), ta, bar_full(s), k0, t.m0, 0, 0);
+                            tma_load_4d(a_smem(s), ta, bar_full(s), k0, t.m0, t.bh, t.bb);
                         }
                         if (kBMn) {
 #pragma unroll
                             for (int pn = 0; pn < kBN / 64; ++pn)     // 64-column blocks of 64 K rows, 8 KB each
-                                tma_load_4d(b_smem(s) + pn * 8192, tb, bar_full(s), t.n0 + 64 * pn, k0, 0, 0);
+                                tma_load_4d(b_smem(s) + pn * 8192, tb, bar_full(s), t.n0 + 64 * pn, k0, t.bh, t.bb);
                         } else {
                             // 256 rows of 128 bytes, as two boxes of 128 rows
-                            tma_load_4d(b_smem(s), tb, bar_full(s), k0, t.n0, 0, 0);
-                            tma_load_4d(b_smem(s) + kBTileBytes / 2, tb, bar_full(s), k0, t.n0 + 128, 0, 0);
+                            tma_load_4d(b_smem(s), tb, bar_full(s), k0, t.n0, t.bh, t.bb);
+                            tma_load_4d(b_smem(s) + kBTileBytes / 2, tb, bar_full(s), k0, t.n0 + 128, t.bh, t.bb);
                         }
                     }
                 }
@@ -289,12 +295,14 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap ta0, const __grid_con
                                 if (gn0 + c < g.N) dst[c] = __uint_as_float(v[c]);
                         }
                     } else if (g.out_bf16) {
-                        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(g.C[t.problem]) + (int64_t)gm * g.ldc + gn0;
+                        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(g.C[t.problem]) + t.bh * g.c_bs[0] +
+                                             t.bb * g.c_bs[1] + (int64_t)gm * g.ldc + gn0;
 #pragma unroll
                         for (int c = 0; c < 32; ++c)
                             if (gn0 + c < g.N) dst[c] = __float2bfloat16_rn(__uint_as_float(v[c]));
                     } else {
-                        float* dst = reinterpret_cast<float*>(g.C[t.problem]) + (int64_t)gm * g.ldc + gn0;
+                        float* dst = reinterpret_cast<float*>(g.C[t.problem]) + t.bh * g.c_bs[0] + t.bb * g.c_bs[1] +
+                                     (int64_t)gm * g.ldc + gn0;
 #pragma unroll
                         for (int c = 0; c < 32; ++c)
                             if (gn0 + c < g.N) dst[c] = __uint_as_float(v[c]);
@@ -308,7 +316,7 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap ta0, const __grid_con
                         const int n_boxes = piece_cols / box_cols;
                         for (int bx = 0; bx < n_boxes; ++bx)
                             if (t.n0 + p0 + bx * box_cols < g.N)
-                                tma_store_4d(tc, stage_addr + bx * (kBM * 128), t.n0 + p0 + bx * box_cols, t.m0, 0, 0);
+                                tma_store_4d(tc, stage_addr + bx * (kBM * 128), t.n0 + p0 + bx * box_cols, t.m0, t.bh, t.bb);
                         tma_store_commit();
                         tma_store_wait_read<0>();
                     }
@@ -375,12 +383,13 @@ __global__ void cvt_batch_bf16_kernel(const CvtBatch b) {
     }
 }
 
-int make_operand_map(ltca_ctx* ctx, CUtensorMap* map, const GemmOperand& o, int mn_extent, int k_extent) {
+int make_operand_map(ltca_ctx* ctx, CUtensorMap* map, const GemmOperand& o, int mn_extent, int k_extent,
+                     int batch_h, int batch_b, const int64_t* bs) {
     ltca_strides st;
-    st.batch = 0; st.head = 0; st.seq = o.ld;
+    st.batch = bs[1]; st.head = bs[0]; st.seq = o.ld;
     if (o.mn_major)   // stored [K, MN]: rows are K, 64 x 64 boxes
-        return make_tmap_bhsd(ctx, map, o.ptr, 2, 1, 1, k_extent, mn_extent, st, 64, 64);
-    return make_tmap_bhsd(ctx, map, o.ptr, 2, 1, 1, mn_extent, k_extent, st, 64, 128);
+        return make_tmap_bhsd(ctx, map, o.ptr, 2, batch_b, batch_h, k_extent, mn_extent, st, 64, 64);
+    return make_tmap_bhsd(ctx, map, o.ptr, 2, batch_b, batch_h, mn_extent, k_extent, st, 64, 128);
 }
 
 }  // namespace
@@ -405,6 +414,9 @@ int gemm_sm100(ltca_ctx* ctx, const GemmProblem& gp) {
         (gp.n_sum > 1 && gp.n_problems != 1))
         return fail(ctx, LTCA_ERR_INVALID, "gemm: between 1 and 3 problems, or one problem of up to 3 summed pairs");
     if (gp.M < 1 || gp.N < 1 || gp.K < 1) return fail(ctx, LTCA_ERR_INVALID, "gemm: empty problem");
+    const bool batched = gp.batch_h > 1 || gp.batch_b > 1;
+    if (gp.batch_h < 1 || gp.batch_b < 1 || (batched && (gp.n_problems != 1 || gp.ksplit > 1)))
+        return fail(ctx, LTCA_ERR_INVALID, "gemm: a batch takes one problem (or one sum of pairs) and no split of K");
     const int n_pairs = gp.n_sum > 1 ? gp.n_sum : gp.n_problems;
     CUtensorMap ta[3], tb[3];
     int rc;
@@ -412,8 +424,8 @@ int gemm_sm100(ltca_ctx* ctx, const GemmProblem& gp) {
         const int j = i < n_pairs ? i : 0;
         if (gp.a[j].mn_major != gp.a[0].mn_major || gp.b[j].mn_major != gp.b[0].mn_major)
             return fail(ctx, LTCA_ERR_INVALID, "gemm: all pairs of one launch share the operand forms");
-        if ((rc = make_operand_map(ctx, &ta[i], gp.a[j], gp.M, gp.K))) return rc;
-        if ((rc = make_operand_map(ctx, &tb[i], gp.b[j], gp.N, gp.K))) return rc;
+        if ((rc = make_operand_map(ctx, &ta[i], gp.a[j], gp.M, gp.K, gp.batch_h, gp.batch_b, gp.a_bs))) return rc;
+        if ((rc = make_operand_map(ctx, &tb[i], gp.b[j], gp.N, gp.K, gp.batch_h, gp.batch_b, gp.b_bs))) return rc;
     }
     GemmKArgs g;
     g.M = gp.M; g.N = gp.N; g.K = gp.K;
@@ -424,18 +436,22 @@ int gemm_sm100(ltca_ctx* ctx, const GemmProblem& gp) {
     for (int i = 0; i < 3; ++i) { g.C[i] = gp.c[i < gp.n_problems ? i : 0]; g.bias[i] = i < gp.n_problems ? gp.bias[i] : nullptr; }
     g.partial = gp.partial;
     g.status = ctx->d_status;
+    g.batch_h = gp.batch_h; g.batch_b = gp.batch_b;
+    g.c_bs[0] = gp.c_bs[0]; g.c_bs[1] = gp.c_bs[1];
     const int ces = gp.out_bf16 ? 2 : 4;
-    g.tma_store = (g.ksplit == 1 && ((gp.ldc * ces) % 16) == 0) ? 1 : 0;
+    g.tma_store = (g.ksplit == 1 && ((gp.ldc * ces) % 16) == 0 && ((gp.c_bs[0] * ces) % 16) == 0 &&
+                   ((gp.c_bs[1] * ces) % 16) == 0) ? 1 : 0;
     for (int i = 0; i < gp.n_problems && g.tma_store; ++i)
         if (reinterpret_cast<uintptr_t>(gp.c[i]) & 15) g.tma_store = 0;
     CUtensorMap tc[3];
     memset(tc, 0, sizeof(tc));
     if (g.tma_store) {
         ltca_strides cs;
-        cs.batch = 0; cs.head = 0; cs.seq = gp.ldc;
+        cs.batch = gp.c_bs[1]; cs.head = gp.c_bs[0]; cs.seq = gp.ldc;
         for (int i = 0; i < 3; ++i) {
             const int j = i < gp.n_problems ? i : 0;
-            if ((rc = make_tmap_bhsd(ctx, &tc[i], gp.c[j], ces, 1, 1, gp.M, gp.N, cs, gp.out_bf16 ? 64 : 32, kBM))) return rc;
+            if ((rc = make_tmap_bhsd(ctx, &tc[i], gp.c[j], ces, gp.batch_b, gp.batch_h, gp.M, gp.N, cs,
+                                     gp.out_bf16 ? 64 : 32, kBM))) return rc;
         }
     }
     if (g.ksplit > 1) {
@@ -447,7 +463,8 @@ int gemm_sm100(ltca_ctx* ctx, const GemmProblem& gp) {
     g.tiles_x = (gp.N + kBN - 1) / kBN;
     g.tiles_y = (gp.M + kBM - 1) / kBM;
     g.tiles_z = gp.n_problems * g.ksplit;
-    const int64_t n_tiles = (int64_t)g.tiles_x * g.tiles_y * g.tiles_z;
+    const int64_t n_tiles = (int64_t)g.tiles_x * g.tiles_y * g.tiles_z * g.batch_h * g.batch_b;
+    if (n_tiles > 0x7fffffff) return fail(ctx, LTCA_ERR_UNSUPPORTED, "gemm: too many tiles");
     const int sms = ctx->sm_count > 0 ? ctx->sm_count : kPlanSms;
     dim3 grid((unsigned)(n_tiles < sms ? n_tiles : sms));
     const bool amn = gp.a[0].mn_major != 0, bmn = gp.b[0].mn_major != 0;

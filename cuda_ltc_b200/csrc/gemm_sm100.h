@@ -25,6 +25,11 @@ struct GemmProblem {
     int64_t ldc = 0;
     int out_bf16 = 0;               // result element type: bf16 or fp32
     float* partial = nullptr;       // gemm_sm100_partial_bytes() bytes when ksplit > 1
+    // A grid of batch_h x batch_b independent products of the same shape (heads x sequences of the materialised
+    // attention path): operand i of batch entry (h, b) starts h * bs[0] + b * bs[1] elements after its pointer.
+    // Needs n_problems == 1 and ksplit == 1 (n_sum is allowed); strides must keep 16-byte alignment.
+    int batch_h = 1, batch_b = 1;
+    int64_t a_bs[2] = {0, 0}, b_bs[2] = {0, 0}, c_bs[2] = {0, 0};
 };
 
 int gemm_sm100(ltca_ctx* ctx, const GemmProblem& gp);

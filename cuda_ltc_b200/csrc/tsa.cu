@@ -418,6 +418,9 @@ void fill_attn(const ltca_tsa_params* t, ltca_attn_params* a) {
     a->do_strides = a->dq_strides = a->dk_strides = a->dv_strides = st;
     a->keep_mask = t->keep_mask;
     a->kv_len = t->kv_len;
+    // the module's gradients stay bit-identical from run to run (the reference's tests pin backward
+    // repeatability on the module, src/ml/time_self_attention_test.cu:799-838)
+    a->bwd_deterministic = 1;
 }
 
 int make_plan(const ltca_tsa_params* t, Plan* pl) {

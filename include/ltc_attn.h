@@ -93,6 +93,12 @@ typedef struct {
     void* dv; ltca_strides dv_strides;         /* [B,H,Sk,D] */
     void*  workspace;           /* scratch, 256-byte aligned */
     size_t workspace_bytes;
+    /* Backward on the tensor pipe with bf16 storage.  0 (default): one fused kernel forms dK, dV and dQ; the
+     * key blocks' shares of dQ are added into an fp32 accumulator by the memory system in no fixed order, so
+     * two runs can differ in dQ by fp32 rounding (dK and dV are bit-identical).  1: the two-kernel path, every
+     * gradient bit-identical from run to run (the reference pins backward repeatability at 1e-6,
+     * src/ml/time_self_attention_test.cu:799-838) at about 1.4 x the time.  The workspace size depends on it. */
+    int32_t bwd_deterministic;
 } ltca_attn_params;
 
 /* ---- context ---------------------------------------------------------------------------- */
@@ -114,8 +120,10 @@ int ltca_version(void);
 /* Optional timing of the kernels of the tensor-pipe backward (for benchmarks): when enabled,
  * ltca_attn_bwd records CUDA events on the context's stream around its three stages, and
  * ltca_ctx_last_bwd_kernel_ms waits for the last one and returns the durations in
- * milliseconds: ms_out[0] row statistics (delta, lse; plus the bf16 packing for fp32 storage),
- * ms_out[1] the dQ kernel, ms_out[2] the dK/dV kernel.  (No counterpart in the reference, whose
+ * milliseconds: ms_out[0] row statistics (delta, lse; plus the bf16 packing for fp32 storage, or the clearing of
+ * the fused kernel's dQ accumulator), then for the fused backward ms_out[1] the fused kernel and ms_out[2] the
+ * conversion of the dQ accumulator, for the two-kernel backward (bwd_deterministic, or fp32 storage) ms_out[1]
+ * the dQ kernel and ms_out[2] the dK/dV kernel.  (No counterpart in the reference, whose
  * only timing is the per-stage event pair of ml::InferencePipeline::executeStage,
  * src/ml/ml_inference_pipeline.cu:42-80.) */
 int ltca_ctx_enable_kernel_timing(ltca_ctx* ctx, int enable);
