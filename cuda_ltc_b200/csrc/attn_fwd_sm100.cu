@@ -949,7 +949,8 @@ attn_fwd4p_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 }
                 if (j > 0 && __any_sync(0xffffffffu, need)) {
                     // O already holds every earlier step: the commit behind s_full covered it
-#pragma unroll
+                    // (rare: not unrolled, or its four 16-register pieces push the step's scores out of registers)
+#pragma unroll 1
                     for (int c0 = 0; c0 < D; c0 += 16) {
                         uint32_t o[16];
                         tmem_ld16(tO + c0, o);

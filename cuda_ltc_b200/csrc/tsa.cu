@@ -21,6 +21,7 @@
 // the incoming gradient passes through LayerNorm and the residual unchanged
 // (src/ml/cudnn_time_self_attention.cu:291-299), dx = dQ Wq^T + dK Wk^T + dV Wv^T.
 #include "gemm_sm100.h"
+#include "attn_wide.h"
 #include "host_common.h"
 
 namespace ltca {
@@ -505,11 +506,27 @@ void fill_attn_bf16(const ltca_tsa_params* t, ltca_attn_params* a) {
     a->mode = LTCA_MODE_BF16;
 }
 
-// Whether the module runs on the tensor pipe: the caller allows it, the attention kernels cover
+// Whether the attention core of the tensor pipeline is the materialised-score path (attn_wide_sm100.cu): head
+// widths the streaming kernels do not cover.  Taken for heads wider than 128 (the reference's configuration gives
+// every head the model's width) and, on explicit request (LTCA_MODE_BF16), for any width that is a multiple of 8;
+// narrow heads under LTCA_MODE_AUTO stay on the exact pipeline, whose handful of small kernels is faster there.
+bool use_wide(const ltca_tsa_params* t, bool /*backward*/) {
+    if (t->mode == LTCA_MODE_FP32) return false;
+    if (t->head_width < 8 || (t->head_width % 8)) return false;
+    ltca_attn_params a;
+    fill_attn_bf16(t, &a);
+    // one choice for forward and backward calls, so that a forward call computes what the backward recomputes
+    // (width 128 has a streaming forward but no streaming backward: it takes this path for both)
+    if (attn_fwd_sm100_supported(&a) && attn_bwd_sm100_supported(&a)) return false;
+    return t->mode == LTCA_MODE_BF16 || t->head_width > 128;
+}
+
+// Whether the module runs on the tensor pipe: the caller allows it, an attention path on the tensor pipe covers
 // the head width, and the bf16 rows keep the 16-byte pitch TMA needs.
 bool use_tensor(const ltca_tsa_params* t, bool backward) {
     if (t->mode == LTCA_MODE_FP32) return false;
     if ((t->H * t->head_width) % 8) return false;
+    if (use_wide(t, backward)) return true;
     ltca_attn_params a;
     fill_attn_bf16(t, &a);
     if (!attn_fwd_sm100_supported(&a)) return false;
@@ -523,9 +540,12 @@ struct TPlan {
     size_t xb, w_in, w_out, act, lse, y;
     size_t attn_fwd, attn_bwd, partial;
     int ks_in, ks_out;
+    // materialised-score path: low-order parts of x, Wq, Wk, q, k; fp32 projection scratch; score matrices
+    bool wide;
+    size_t q32, mat32, mat16;
 };
 
-int make_tplan(const ltca_tsa_params* t, TPlan* pl) {
+int make_tplan(const ltca_tsa_params* t, TPlan* pl, bool backward) {
     pl->rows = (int64_t)t->B * t->S;
     pl->HW = t->H * t->head_width;
     pl->Ep = (t->E + 7) / 8 * 8;
@@ -535,11 +555,21 @@ int make_tplan(const ltca_tsa_params* t, TPlan* pl) {
     pl->act = align_up((size_t)pl->rows * pl->HW * 2, 256);
     pl->lse = align_up((size_t)t->B * t->H * t->S * sizeof(float), 256);
     pl->y = align_up((size_t)pl->rows * t->E * sizeof(float), 256);
-    ltca_attn_params a;
-    fill_attn_bf16(t, &a);
-    int rc = ltca_attn_workspace_bytes(&a, 0, &pl->attn_fwd);
-    if (rc) return rc;
-    if ((rc = ltca_attn_workspace_bytes(&a, 1, &pl->attn_bwd))) return rc;
+    pl->wide = use_wide(t, backward);
+    pl->q32 = pl->mat32 = pl->mat16 = 0;
+    pl->attn_fwd = pl->attn_bwd = 0;
+    int rc;
+    if (pl->wide) {
+        const size_t elems = wide_matrix_elems(t->B, t->H, t->S, t->S);
+        pl->q32 = align_up((size_t)pl->rows * pl->HW * sizeof(float), 256);
+        pl->mat32 = align_up(elems * sizeof(float), 256);
+        pl->mat16 = align_up(elems * 2, 256);
+    } else {
+        ltca_attn_params a;
+        fill_attn_bf16(t, &a);
+        if ((rc = ltca_attn_workspace_bytes(&a, 0, &pl->attn_fwd))) return rc;
+        if ((rc = ltca_attn_workspace_bytes(&a, 1, &pl->attn_bwd))) return rc;
+    }
     const int rows = (int)pl->rows;
     pl->ks_in = gemm_sm100_pick_ksplit(t->E, pl->HW, rows, 3, kPlanSms);
     pl->ks_out = gemm_sm100_pick_ksplit(pl->HW, t->E, rows, 1, kPlanSms);
@@ -549,9 +579,16 @@ int make_tplan(const ltca_tsa_params* t, TPlan* pl) {
     return LTCA_OK;
 }
 
+// Extra scratch of the materialised-score path: x_lo, Wq_lo, Wk_lo, q_lo, k_lo, the fp32 projection result that is
+// split into q (then k), the raw scores and the probabilities; the backward adds dP.
+size_t wide_extra(const TPlan& pl, int which) {
+    if (!pl.wide) return 0;
+    return pl.xb + 2 * pl.w_in + 2 * pl.act + pl.q32 + pl.mat32 + pl.mat16 + (which == 0 ? 0 : pl.mat32);
+}
+
 size_t tensor_workspace(const TPlan& pl, int which) {
     // x, the four weight matrices, q, k, v, ctx, lse
-    size_t n = pl.xb + 3 * pl.w_in + pl.w_out + 4 * pl.act + pl.lse;
+    size_t n = pl.xb + 3 * pl.w_in + pl.w_out + 4 * pl.act + pl.lse + wide_extra(pl, which);
     if (which == 0) return n + pl.y + pl.attn_fwd;
     n += pl.xb + 4 * pl.act;                       // dy, dctx, dq, dk, dv
     n += pl.attn_fwd > pl.attn_bwd ? pl.attn_fwd : pl.attn_bwd;
@@ -564,12 +601,31 @@ struct TBufs {
     void *xb, *wq, *wk, *wv, *wo, *q, *k, *v, *ctx;
     float* lse;
     char* rest;
+    // materialised-score path
+    void *xl, *wql, *wkl, *ql, *kl, *P;
+    float *q32, *scores, *dP;
 };
 
+// The attention problem of the module for the materialised-score path (bf16 views of the projection outputs).
+void fill_wide(const ltca_tsa_params* t, const TBufs& tb, WideArgs* w) {
+    ltca_attn_params a;
+    fill_attn_bf16(t, &a);
+    w->B = t->B; w->H = t->H; w->Sq = t->S; w->Sk = t->S; w->D = t->head_width;
+    w->causal = t->causal; w->scale = t->scale; w->clamp = t->score_clamp;
+    w->keep_mask = t->keep_mask; w->kv_len = t->kv_len;
+    w->qh = tb.q; w->ql = tb.ql; w->kh = tb.k; w->kl = tb.kl; w->v = tb.v;
+    w->qs = w->ks = w->vs = w->os = a.q_strides;
+    w->dos = w->dqs = w->dks = w->dvs = a.q_strides;
+    w->o = tb.ctx; w->o_bf16 = 1; w->lse = tb.lse;
+    w->scores = tb.scores; w->P = tb.P; w->dP = tb.dP;
+    w->grads_bf16 = 1;
+}
+
 // bf16 copies, fused Q/K/V projection, attention forward.
-int tensor_forward_core(ltca_ctx* ctx, const ltca_tsa_params* t, const TPlan& pl, char* w, TBufs* tb) {
+int tensor_forward_core(ltca_ctx* ctx, const ltca_tsa_params* t, const TPlan& pl, char* w, TBufs* tb, int which) {
     char* rest = w;
-    if (t->saved) w = reinterpret_cast<char*>(t->saved);
+    const bool saved = t->saved && !pl.wide;          // the materialised-score path always recomputes
+    if (saved) w = reinterpret_cast<char*>(t->saved);
     tb->xb = w;  w += pl.xb;
     tb->wq = w;  w += pl.w_in;
     tb->wk = w;  w += pl.w_in;
@@ -580,10 +636,63 @@ int tensor_forward_core(ltca_ctx* ctx, const ltca_tsa_params* t, const TPlan& pl
     tb->v = w;   w += pl.act;
     tb->ctx = w; w += pl.act;
     tb->lse = reinterpret_cast<float*>(w); w += pl.lse;
-    tb->rest = t->saved ? rest : w;
-    if (t->saved && t->reuse_forward) return LTCA_OK;
+    if (pl.wide) {
+        tb->xl = w;  w += pl.xb;
+        tb->wql = w; w += pl.w_in;
+        tb->wkl = w; w += pl.w_in;
+        tb->ql = w;  w += pl.act;
+        tb->kl = w;  w += pl.act;
+        tb->q32 = reinterpret_cast<float*>(w);    w += pl.q32;
+        tb->scores = reinterpret_cast<float*>(w); w += pl.mat32;
+        tb->P = w;   w += pl.mat16;
+        tb->dP = nullptr;
+        if (which != 0) { tb->dP = reinterpret_cast<float*>(w); w += pl.mat32; }
+    }
+    tb->rest = saved ? rest : w;
+    if (saved && t->reuse_forward) return LTCA_OK;
     const int E = t->E, HW = pl.HW, Ep = pl.Ep;
     int rc;
+    if (pl.wide) {
+        // Two-term operands for the products whose rounding would reach the scores: x, Wq, Wk here, q and k below.
+        if ((rc = wide_split_bf16(ctx, t->x, E, tb->xb, tb->xl, Ep, pl.rows, E))) return rc;
+        if ((rc = wide_split_bf16(ctx, t->wq, HW, tb->wq, tb->wql, HW, E, HW))) return rc;
+        if ((rc = wide_split_bf16(ctx, t->wk, HW, tb->wk, tb->wkl, HW, E, HW))) return rc;
+        if ((rc = wide_split_bf16(ctx, t->wv, HW, tb->wv, nullptr, HW, E, HW))) return rc;
+        if ((rc = wide_split_bf16(ctx, t->wo, E, tb->wo, nullptr, Ep, HW, E))) return rc;
+        const void* whi[2] = {tb->wq, tb->wk};
+        const void* wlo[2] = {tb->wql, tb->wkl};
+        void* ohi[2] = {tb->q, tb->k};
+        void* olo[2] = {tb->ql, tb->kl};
+        const float* bias[2] = {t->bq, t->bk};
+        for (int i = 0; i < 2; ++i) {
+            // x W = x_hi W_hi + x_hi W_lo + x_lo W_hi in one fp32 accumulator, then split into two bf16 terms
+            GemmProblem gp;
+            gp.M = (int)pl.rows; gp.N = HW; gp.K = E;
+            gp.n_sum = 3;
+            gp.a[0] = GemmOperand{tb->xb, Ep, 0}; gp.b[0] = GemmOperand{whi[i], HW, 1};
+            gp.a[1] = GemmOperand{tb->xb, Ep, 0}; gp.b[1] = GemmOperand{wlo[i], HW, 1};
+            gp.a[2] = GemmOperand{tb->xl, Ep, 0}; gp.b[2] = GemmOperand{whi[i], HW, 1};
+            gp.c[0] = tb->q32;
+            gp.bias[0] = bias[i];
+            gp.ldc = HW;
+            if ((rc = gemm_sm100(ctx, gp))) return rc;
+            if ((rc = wide_split_bf16(ctx, tb->q32, HW, ohi[i], olo[i], HW, pl.rows, HW))) return rc;
+        }
+        {
+            GemmProblem gp;
+            gp.M = (int)pl.rows; gp.N = HW; gp.K = E;
+            gp.a[0] = GemmOperand{tb->xb, Ep, 0};
+            gp.b[0] = GemmOperand{tb->wv, HW, 1};
+            gp.c[0] = tb->v;
+            gp.bias[0] = t->bv;
+            gp.ldc = HW;
+            gp.out_bf16 = 1;
+            if ((rc = gemm_sm100(ctx, gp))) return rc;
+        }
+        WideArgs wa;
+        fill_wide(t, *tb, &wa);
+        return wide_attn_fwd(ctx, wa);
+    }
     if ((rc = convert_rows_bf16(ctx, t->x, E, tb->xb, Ep, pl.rows, E))) return rc;
     {
         const float* src[4] = {t->wq, t->wk, t->wv, t->wo};
@@ -618,7 +727,7 @@ int tensor_forward_core(ltca_ctx* ctx, const ltca_tsa_params* t, const TPlan& pl
 int tensor_forward(ltca_ctx* ctx, const ltca_tsa_params* t) {
     TPlan pl;
     int rc;
-    if ((rc = make_tplan(t, &pl))) return rc;
+    if ((rc = make_tplan(t, &pl, t->saved != nullptr))) return rc;
     const size_t need = tensor_workspace(pl, 0);
     if (!t->workspace || t->workspace_bytes < need)
         return fail(ctx, LTCA_ERR_WORKSPACE, "forward needs %zu bytes of workspace", need);
@@ -626,7 +735,7 @@ int tensor_forward(ltca_ctx* ctx, const ltca_tsa_params* t) {
     float* y = reinterpret_cast<float*>(w);
     w += pl.y;
     TBufs tb;
-    if ((rc = tensor_forward_core(ctx, t, pl, w, &tb))) return rc;
+    if ((rc = tensor_forward_core(ctx, t, pl, w, &tb, 0))) return rc;
     GemmProblem gp;
     gp.M = (int)pl.rows; gp.N = t->E; gp.K = pl.HW;
     gp.a[0] = GemmOperand{tb.ctx, pl.HW, 0};
@@ -646,7 +755,7 @@ int tensor_forward(ltca_ctx* ctx, const ltca_tsa_params* t) {
 int tensor_backward(ltca_ctx* ctx, const ltca_tsa_params* t, bool want_dx, bool want_dw, float* colsum_scratch) {
     TPlan pl;
     int rc;
-    if ((rc = make_tplan(t, &pl))) return rc;
+    if ((rc = make_tplan(t, &pl, true))) return rc;
     const size_t need = tensor_workspace(pl, 1);
     if (!t->workspace || t->workspace_bytes < need)
         return fail(ctx, LTCA_ERR_WORKSPACE, "backward needs %zu bytes of workspace", need);
@@ -660,7 +769,7 @@ int tensor_backward(ltca_ctx* ctx, const ltca_tsa_params* t, bool want_dx, bool 
     TBufs tb;
     // the forward is recomputed, as the reference's caller does before each backward
     // (src/ml/ml_liquid_net.cu:715-721)
-    if ((rc = tensor_forward_core(ctx, t, pl, w, &tb))) return rc;
+    if ((rc = tensor_forward_core(ctx, t, pl, w, &tb, 1))) return rc;
     const int rows = (int)pl.rows, E = t->E, HW = pl.HW, Ep = pl.Ep;
     if ((rc = convert_rows_bf16(ctx, t->dy, E, dyb, Ep, pl.rows, E))) return rc;
     {   // dctx = dy Wo^T : Wo is stored [HW, E] = [N, K]
@@ -673,13 +782,20 @@ int tensor_backward(ltca_ctx* ctx, const ltca_tsa_params* t, bool want_dx, bool 
         gp.out_bf16 = 1;
         if ((rc = gemm_sm100(ctx, gp))) return rc;
     }
-    ltca_attn_params a;
-    fill_attn_bf16(t, &a);
-    a.q = tb.q; a.k = tb.k; a.v = tb.v; a.o = tb.ctx; a.lse = tb.lse;
-    a.dout = dctx; a.dq = dq; a.dk = dk; a.dv = dv;
-    a.workspace = pl.attn_bwd ? tb.rest : nullptr;
-    a.workspace_bytes = pl.attn_bwd;
-    if ((rc = ltca_attn_bwd(ctx, &a))) return rc;
+    if (pl.wide) {
+        WideArgs wa;
+        fill_wide(t, tb, &wa);
+        wa.dout = dctx; wa.dq = dq; wa.dk = dk; wa.dv = dv;
+        if ((rc = wide_attn_bwd(ctx, wa))) return rc;
+    } else {
+        ltca_attn_params a;
+        fill_attn_bf16(t, &a);
+        a.q = tb.q; a.k = tb.k; a.v = tb.v; a.o = tb.ctx; a.lse = tb.lse;
+        a.dout = dctx; a.dq = dq; a.dk = dk; a.dv = dv;
+        a.workspace = pl.attn_bwd ? tb.rest : nullptr;
+        a.workspace_bytes = pl.attn_bwd;
+        if ((rc = ltca_attn_bwd(ctx, &a))) return rc;
+    }
     const void* grads[3] = {dq, dk, dv};
     if (want_dw) {
         // bias gradients (FlashAttention form): column sums of the projection outputs' gradients
@@ -745,7 +861,7 @@ extern "C" {
 static int inner_workspace(const ltca_tsa_params* t, int which, size_t* bytes_out) {
     if (use_tensor(t, which != 0 || t->saved != nullptr)) {
         TPlan tp;
-        int trc = make_tplan(t, &tp);
+        int trc = make_tplan(t, &tp, which != 0 || t->saved != nullptr);
         if (trc) return trc;
         *bytes_out = tensor_workspace(tp, which);
         return LTCA_OK;
@@ -787,7 +903,7 @@ int ltca_tsa_saved_bytes(const ltca_tsa_params* t, size_t* bytes_out) {
     probe.saved = nullptr;
     if (use_tensor(&probe, true)) {
         TPlan tp;
-        int rc = make_tplan(&probe, &tp);
+        int rc = make_tplan(&probe, &tp, true);
         if (rc) return rc;
         *bytes_out = tensor_saved_bytes(tp);
         return LTCA_OK;

@@ -225,9 +225,91 @@ def test_cuda_module_reference_form_wide_heads(ctx):
     ref, _ = oracle.tsa_fwd(x, wq, wk, wv, wo, B, S, H, W, 1.0, False, True, True, True, gamma, beta)
     gref = oracle.tsa_bwd(x, wq, wk, wv, wo, dy, B, S, H, W, 1.0, False, True)
     dev = lambda a: torch.from_numpy(a).cuda()
-    kw = dict(scale=1.0, causal=False, time_major=True, mode=_lib.MODE_AUTO)
+    kw = dict(scale=1.0, causal=False, time_major=True, mode=_lib.MODE_FP32)
     out = ctx.tsa_fwd(dev(x), dev(wq), dev(wk), dev(wv), dev(wo), B, S, H, W, gamma=dev(gamma), beta=dev(beta), **kw)
     got = ctx.tsa_bwd(dev(x), dev(wq), dev(wk), dev(wv), dev(wo), dev(dy), B, S, H, W, **kw)
     assert np.abs(out.cpu().numpy() - ref).max() < 1e-3
     for name, g, r in zip(("dx", "dwq", "dwk", "dwv", "dwo"), got, gref):
         assert np.abs(g.cpu().numpy() - r).max() < 1e-3 * max(1.0, np.abs(r).max()), name
+
+
+WIDE_TENSOR_CASES = [
+    # B, S, E, H, head width, scale, causal, time_major, mask, biases, mode
+    (2, 12, 512, 8, 512, 1.0, False, True, False, False, "auto"),     # the reference's largest form: AUTO takes this path
+    (4, 64, 256, 4, 256, 1.0, False, True, False, False, "auto"),
+    (3, 40, 64, 2, 32, 32 ** -0.5, True, False, True, True, "bf16"),   # narrow heads on request, every mask kind
+    (2, 100, 128, 2, 128, 1.0, True, True, False, False, "bf16"),     # width 128: streaming forward exists, backward does not
+]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("case", WIDE_TENSOR_CASES)
+def test_cuda_module_materialised_score_path(ctx, case):
+    """Head widths the streaming kernels do not cover run on the tensor pipe through written-out score matrices
+    (batched tcgen05 GEMMs).  x, Wq and Wk enter as two bf16 terms, so the scores are fp32-class even with the
+    reference's scale of 1 and model-wide heads; v, P, ctx and Wo are single bf16 operands as in the compact
+    module, hence the same bounds against the oracle fed the exact inputs."""
+    import torch
+    from cuda_ltc_b200 import _lib
+    B, S, E, H, W, scale, causal, time_major, use_mask, biases, mode_name = case
+    mode = _lib.MODE_AUTO if mode_name == "auto" else _lib.MODE_BF16
+    HW = H * W
+    rng = np.random.default_rng(31)
+    x = (0.5 * rng.standard_normal((B * S, E))).astype(np.float32)
+    dy = rng.standard_normal((B * S, E)).astype(np.float32)
+    lim = np.sqrt(6.0 / (E + W))
+    amp = 0.25 if W > 128 else 1.0                 # keeps the unscaled scores of model-wide heads at magnitude ~10
+    wq, wk = (rng.uniform(-lim, lim, (E, HW)).astype(np.float32) * amp for _ in range(2))
+    wv = rng.uniform(-lim, lim, (E, HW)).astype(np.float32)
+    wo = rng.uniform(-lim, lim, (HW, E)).astype(np.float32)
+    bq, bk, bv = ((0.1 * rng.standard_normal(HW)).astype(np.float32) if biases else None for _ in range(3))
+    gamma, beta = np.ones(E, np.float32), np.zeros(E, np.float32)
+    m = None
+    if use_mask:
+        m = (rng.random((B, S, S)) < 0.8).astype(np.float32)
+        m[:, np.arange(S), np.arange(S)] = 1.0
+    ref, y_ref = oracle.tsa_fwd(x, wq, wk, wv, wo, B, S, H, W, scale, causal, time_major, True, True, gamma, beta,
+                                bq, bk, bv, None, m)
+    gref = oracle.tsa_bwd(x, wq, wk, wv, wo, dy, B, S, H, W, scale, causal, time_major, bq, bk, bv, m)
+    dev = lambda a: None if a is None else torch.from_numpy(a).cuda()
+    kw = dict(scale=scale, causal=causal, time_major=time_major, mode=mode, keep_mask=dev(m))
+    args = (dev(x), dev(wq), dev(wk), dev(wv), dev(wo))
+    y = ctx.tsa_fwd(*args, B, S, H, W, use_residual=False, use_layer_norm=False, bq=dev(bq), bk=dev(bk), bv=dev(bv), **kw)
+    out = ctx.tsa_fwd(*args, B, S, H, W, gamma=dev(gamma), beta=dev(beta), bq=dev(bq), bk=dev(bk), bv=dev(bv), **kw)
+    got = ctx.tsa_bwd(*args, dev(dy), B, S, H, W, bq=dev(bq), bk=dev(bk), bv=dev(bv), **kw)
+    again = ctx.tsa_bwd(*args, dev(dy), B, S, H, W, bq=dev(bq), bk=dev(bk), bv=dev(bv), **kw)
+    torch.cuda.synchronize()
+    assert ctx.device_status() == 0
+    for name, g, r in (("y", y, y_ref), ("out", out, ref)):
+        gh = g.cpu().numpy()
+        assert rel_l2(gh, r) < MODULE_REL_L2, f"{name}: rel-L2 {rel_l2(gh, r)}"
+        assert np.abs(gh - r).max() < MODULE_MAX_ABS * max(1.0, np.abs(r).max()), name
+    for name, g, g2, r in zip(("dx", "dwq", "dwk", "dwv", "dwo"), got, again, gref):
+        assert torch.equal(g, g2), f"{name}: two runs differ"
+        gh = g.cpu().numpy().astype(np.float64)
+        assert rel_l2(gh, r) < MODULE_GRAD_REL_L2, f"{name}: rel-L2 {rel_l2(gh, r)}"
+        assert np.abs(gh - r).max() < MODULE_MAX_ABS * max(1.0, np.abs(r).max()), name
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("path", [c for c in CASES if int(np.load(c)["E"]) % 8 == 0])
+def test_materialised_score_path_matches_reference_cudnn_module(ctx, path):
+    """The same path against the reference's own cuDNN module (golden vectors), at the 2e-2 of the largest
+    magnitude that separates two reduced-precision evaluations of the reference's unscaled attention."""
+    import torch
+    from cuda_ltc_b200 import _lib
+    d, E, H, B, S, (wq, wk, wv), wo = load(path)
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).cuda()
+    x, dy, twq, twk, twv, two = (dev(a) for a in (d["x"], d["dy"], wq, wk, wv, wo))
+    gamma, beta = torch.ones(E, device="cuda"), torch.zeros(E, device="cuda")
+    kw = dict(scale=1.0, time_major=True, mode=_lib.MODE_BF16)
+    out = ctx.tsa_fwd(x, twq, twk, twv, two, B, S, H, E, use_residual=bool(d["res"]), use_layer_norm=bool(d["ln"]),
+                      gamma=gamma, beta=beta, **kw)
+    got = ctx.tsa_bwd(x, twq, twk, twv, two, dy, B, S, H, E, **kw)
+    torch.cuda.synchronize()
+    assert ctx.device_status() == 0
+    tol = 2e-2
+    assert np.abs(out.cpu().numpy() - d["y"]).max() < tol * max(1.0, np.abs(d["y"]).max())
+    assert np.abs(got[0].cpu().numpy() - d["dx"]).max() < tol * max(1.0, np.abs(d["dx"]).max())
+    for name, g, r in zip(("dwq", "dwk", "dwv", "dwo"), got[1:], reference_weight_grads(d, E, H)):
+        assert np.abs(g.cpu().numpy() - r).max() < tol * max(1.0, np.abs(r).max()), name
