@@ -287,6 +287,21 @@ def other_configs(torch, ctx, peaks):
                      "fwd_tflops": (4 * gemm + fl2) / f_ms / 1e9,
                      "bwd_tflops": (8 * gemm + 2.5 * fl2) / b_ms / 1e9}
     out["config2_module_B32_S256_E512_H8_causal"] = mod
+    # the same module in the REFERENCE's form (every head as wide as the model, scale 1, no mask, time-major rows:
+    # what its cuDNN module computes; `--impl reference` times that module itself under `reference_cuda`)
+    Wr = E
+    wsr = [(torch.rand((E, H * Wr), generator=g, device=dev) * 2 - 1) * lim for _ in range(3)]
+    wor = (torch.rand((H * Wr, E), generator=g, device=dev) * 2 - 1) * lim
+    kwr = dict(scale=1.0, causal=False, time_major=True, mode=_lib.MODE_AUTO)
+    f_ms = _timed(torch, lambda: ctx.tsa_fwd(x, *wsr, wor, B, S, H, Wr, gamma=gamma, beta=beta, **kwr), n=10, flush=flush)
+    b_ms = _timed(torch, lambda: ctx.tsa_bwd(x, *wsr, wor, dy, B, S, H, Wr, **kwr), n=10, flush=flush)
+    gemm_r = 2.0 * B * S * E * H * Wr
+    core_r = 4.0 * B * H * S * S * Wr
+    out["config2_module_reference_form_head_width_512"] = {
+        "fwd_us": f_ms * 1e3, "bwd_incl_recomputed_fwd_us": b_ms * 1e3,
+        "fwd_tflops": (4 * gemm_r + core_r) / f_ms / 1e9,
+        "path": "written-out scores, batched tcgen05 GEMMs, two-term Q/K operands"}
+    del wsr, wor
     # config 5: attention core
     fl5 = flops_fwd(64, 8, 512, 64)
     q, k, v, do = (rn(64, 8, 512, 64).bfloat16() for _ in range(4))

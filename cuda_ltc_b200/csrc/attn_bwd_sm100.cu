@@ -28,15 +28,6 @@
 #include "sm100_ptx.cuh"
 #include "trace.cuh"
 
-#ifndef LTCA_BWD_DQ4
-#define LTCA_BWD_DQ4 1
-#endif
-#ifndef LTCA_BWD_DKV4
-#define LTCA_BWD_DKV4 1
-#endif
-#ifndef LTCA_BWD_STAGGER
-#define LTCA_BWD_STAGGER 1
-#endif
 
 namespace ltca {
 
@@ -415,7 +406,7 @@ attn_bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
             LTCA_TRACE_EVT(0x11 + (j << 8));
             // One-time delay of tile 1: from then on one tile's exponentials overlap the other
             // tile's loads, stores and barrier traffic instead of all warps stalling together.
-            if (LTCA_BWD_STAGGER && t == 1 && j == 0 && n_steps[0] > 0) {
+            if (t == 1 && j == 0 && n_steps[0] > 0) {
                 ok = mbar_wait_warp(bar_stagger(), 0, wc, 0x66);
                 if (!ok) break;
             }
@@ -458,7 +449,7 @@ attn_bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
             }
             uint32_t hi[16], lo[16];
             pack32<kSplit>(dp, hi, lo);
-            if (LTCA_BWD_STAGGER && t == 0 && j == 0) {
+            if (t == 0 && j == 0) {
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar_stagger());
             }
@@ -712,7 +703,7 @@ attn_bwd_dkv_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 tmem_ld32(tDP, dp);
                 tmem_wait_ld();
                 LTCA_TRACE_EVT(0x11 + (j << 8));
-                if (LTCA_BWD_STAGGER && t == 1 && it == 0 && active[0] && j_begin[0] <= j_begin[1]) {
+                if (t == 1 && it == 0 && active[0] && j_begin[0] <= j_begin[1]) {
                     ok = mbar_wait_warp(bar_stagger(), 0, wc, 0x96);
                     if (!ok) break;
                 }
@@ -787,7 +778,7 @@ attn_bwd_dkv_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 uint32_t pt[16], ptl[16], dst[16], dstl[16];
                 pack32<kSplit>(s, pt, ptl);
                 pack32<kSplit>(dp, dst, dstl);
-                if (LTCA_BWD_STAGGER && t == 0 && it == 0) {
+                if (t == 0 && it == 0) {
                     __syncwarp();
                     if (lane == 0) mbar_arrive(bar_stagger());
                 }
@@ -2341,7 +2332,7 @@ int launch_main(ltca_ctx* ctx, const ltca_attn_params* p, const void* q, const v
     LTCA_CUDA_OK(ctx, opt_in_dynamic_smem(opt_dkv, ctx->device, kdkv, DkvSmem::kDynBytes));
     bool dq_launched = false;
     if constexpr (sizeof(OutT) == 2) {
-        if (LTCA_BWD_DQ4) {
+        {
             static SmemOptIn opt_dq4;
             LTCA_CUDA_OK(ctx, opt_in_dynamic_smem(opt_dq4, ctx->device, attn_bwd_dq4_sm100_kernel, Dq4Smem::kDynBytes));
             ItemGrid ig;
@@ -2366,7 +2357,7 @@ int launch_main(ltca_ctx* ctx, const ltca_attn_params* p, const void* q, const v
     }
     kernel_timing_mark(ctx, 2);
     if constexpr (sizeof(OutT) == 2) {
-        if (LTCA_BWD_DKV4) {
+        {
             static SmemOptIn opt_dkv4;
             LTCA_CUDA_OK(ctx, opt_in_dynamic_smem(opt_dkv4, ctx->device, attn_bwd_dkv4_sm100_kernel,
                                                   Dkv4Smem::kDynBytes));

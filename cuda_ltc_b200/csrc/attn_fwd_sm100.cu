@@ -31,42 +31,23 @@
 #include "sm100_ptx.cuh"
 #include "trace.cuh"
 
-#ifndef LTCA_FWD4_MIN_SQ
-#define LTCA_FWD4_MIN_SQ 256      // queries above which the four-tile persistent kernel is used
-#endif
-#ifndef LTCA_FWD4
-#define LTCA_FWD4 1
-#endif
-#ifndef LTCA_PAIR_NAMED_BAR
-#define LTCA_PAIR_NAMED_BAR 0
-#endif
-#ifndef LTCA_FWD_ROWSPLIT
-#define LTCA_FWD_ROWSPLIT 2
-#endif
-// 0: tiles run freely, 1: the tiles take strict turns at the exponentials, 2: tile 1 is delayed once
-#ifndef LTCA_FWD_PINGPONG
-#define LTCA_FWD_PINGPONG 2
-#endif
-#ifndef LTCA_FWD_EARLY_TURN
-#define LTCA_FWD_EARLY_TURN 0
-#endif
 
 namespace ltca {
 
 namespace {
 
 constexpr int kBlockM = 128;        // query rows per tile
-// kRowSplit threads share one query row (each owns 1/kRowSplit of the step's key columns):
-//   1: 8 softmax warps, whole rows in registers, no exchange between threads;
-//   2: 16 softmax warps, four per scheduler, row maxima exchanged through shared memory.
-constexpr int kRowSplit = LTCA_FWD_ROWSPLIT;
+constexpr int kFwd4MinSq = 256;     // queries above which the four-tile persistent kernel is used
+// Two threads share one query row (each owns half of the step's key columns): 16 softmax warps, four per
+// scheduler, row maxima exchanged through shared memory.  (One thread per row, 8 warps, hid no latency.)
+constexpr int kRowSplit = 2;
 constexpr int kMathWarps = 8 * kRowSplit;
 constexpr int kFwdThreads = 32 * (kMathWarps + 4);   // + one warpgroup of control warps
 constexpr int kMmaWarp0 = kMathWarps;                // issues the contractions of tile 0 (tile 1: the next warp)
 constexpr int kTmaWarp = kMathWarps + 2;
-constexpr int kLaunchRegs = kRowSplit == 1 ? 168 : 96;   // registers per thread at launch (65536 / threads, rounded down to 8)
-constexpr int kCtrlRegs = kRowSplit == 1 ? 72 : 32;
-constexpr int kMathRegs = kRowSplit == 1 ? 216 : 112;
+constexpr int kLaunchRegs = 96;     // registers per thread at launch (65536 / threads, rounded down to 8)
+constexpr int kCtrlRegs = 32;
+constexpr int kMathRegs = 112;
 // setmaxnreg can only redistribute what the CTA was launched with; asking for more never returns
 static_assert(32 * kMathWarps * kMathRegs + 128 * kCtrlRegs <= kFwdThreads * kLaunchRegs, "register budget");
 constexpr uint32_t kTmemCols = 512;
@@ -381,18 +362,14 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
 #pragma unroll
                 for (int i = 0; i < 4; ++i) mx[i] = fmax3(mx[i], S_(c + 2 * i), S_(c + 2 * i + 1));
             float mt = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-            if constexpr (kRowSplit == 2) {
+            {
                 // the row's other half: both threads publish, meet, and read each other's maximum
                 *xslot(j & 1, half) = mt;
-#if LTCA_PAIR_NAMED_BAR
-                asm volatile("bar.sync %0, 64;" ::"r"(1 + t * 4 + wq) : "memory");
-#else
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar_pair(t, wq));
                 ok = mbar_wait_warp(bar_pair(t, wq), pair_phase, wc, 0x3a);
                 pair_phase ^= 1u;
                 if (!ok) break;
-#endif
                 mt = fmaxf(mt, *xslot(j & 1, half ^ 1));
             }
             LTCA_TRACE_EVT(0x12 + (j << 8));
@@ -425,19 +402,11 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 }
                 l_run *= factor;
             }
-            // The two tiles take turns on the special-function units: tile 0 runs the exponentials
-            // of step j, then tile 1 those of its step j, then tile 0 step j + 1 ...  While one
-            // tile exponentiates, the other loads its scores, finds its maxima and talks to the
-            // barriers, so those latencies stay off the critical path.
-            if (LTCA_FWD_PINGPONG == 2) {
-                // one-time delay: tile 1 starts its first exponentials when tile 0 has finished its own
-                if (t == 1 && j == 0 && n_tiles[0] > 0) {
-                    ok = mbar_wait_warp(bar_turn(0), 0, wc, 0x3e);
-                    if (!ok) break;
-                }
-            } else if (LTCA_FWD_PINGPONG == 1 && (t == 0 ? (j > 0 && j - 1 < n_tiles[1]) : (j < n_tiles[0]))) {
-                const uint32_t par = (uint32_t)((t == 0 ? j - 1 : j) & 1);
-                ok = mbar_wait_warp(bar_turn(t ^ 1), par, wc, 0x3c + t);
+            // One-time delay: tile 1 starts its first exponentials when tile 0 has finished its own, so that from
+            // then on one tile exponentiates while the other loads its scores, finds its maxima and talks to the
+            // barriers.  (Strict turn-taking at every step was slower.)
+            if (t == 1 && j == 0 && n_tiles[0] > 0) {
+                ok = mbar_wait_warp(bar_turn(0), 0, wc, 0x3e);
                 if (!ok) break;
             }
             LTCA_TRACE_EVT(0x15 + (j << 8));
@@ -465,11 +434,6 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
                                                      p3 - __uint_as_float(h23 & 0xffff0000u));
                     }
                 }
-                if (LTCA_FWD_PINGPONG == 1 && LTCA_FWD_EARLY_TURN && ch == kH / 32 - 1) {
-                    // the last quarter of this tile's exponentials overlaps the other tile's start
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(bar_turn(t));
-                }
                 if (ch == 0 && !o_waited) {
                     // P of the previous step must have been consumed before it is overwritten
                     ok = mbar_wait_warp(bar_o_done(t), (uint32_t)((j - 1) & 1), wc, 0x36 + t);
@@ -479,7 +443,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 if constexpr (kSplitP) tmem_st16(tPlo + ch * 16, lo);
             }
             if (!ok) break;
-            if (LTCA_FWD_PINGPONG == 1 ? !LTCA_FWD_EARLY_TURN : (LTCA_FWD_PINGPONG == 2 && t == 0 && j == 0)) {
+            if (t == 0 && j == 0) {
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar_turn(t));
             }
@@ -498,15 +462,11 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
             float inv = 0.f;
             float lse = neg_inf();
             if (n_t > 0) {
-                if constexpr (kRowSplit == 2) {
+                {
                     *xslot(2, half) = l_run;
-#if LTCA_PAIR_NAMED_BAR
-                    asm volatile("bar.sync %0, 64;" ::"r"(1 + t * 4 + wq) : "memory");
-#else
                     __syncwarp();
                     if (lane == 0) mbar_arrive(bar_pair(t, wq));
                     ok = mbar_wait_warp(bar_pair(t, wq), pair_phase, wc, 0x3b);
-#endif
                     if (ok) l_run += *xslot(2, half ^ 1);
                 }
                 ok = ok && mbar_wait_warp(bar_o_done(t), (uint32_t)((n_t - 1) & 1), wc, 0x34 + t);
@@ -1132,7 +1092,7 @@ int launch_fwd(ltca_ctx* ctx, const ltca_attn_params* p, const void* q, const vo
 
     if constexpr (D == 64 && sizeof(OutT) == 2) {
         // long query ranges: four independent tiles per CTA (see attn_fwd4p_sm100_kernel)
-        if (LTCA_FWD4 && p->Sq > LTCA_FWD4_MIN_SQ) return launch_fwd4(ctx, p, q, k, v, qs, ks, vs, a);
+        if (p->Sq > kFwd4MinSq) return launch_fwd4(ctx, p, q, k, v, qs, ks, vs, a);
     }
 
     auto kern = attn_fwd_sm100_kernel<D, OutT, kSplitP>;

@@ -22,12 +22,9 @@ enum : uint32_t {
     kStatusWhereShift    = 8          // bits [8,24): which barrier gave up (role-specific code)
 };
 
-#ifndef LTCA_WAIT_SLEEP_NS
-#define LTCA_WAIT_SLEEP_NS 0
-#endif
 static constexpr unsigned long long kWaitLimitNs = 2000000000ull;   // 2 s
-// (No suspend-time hint on mbarrier.try_wait: measured on B200, a hint more than doubles the
-// latency between an arrival and the waiter's wake-up.)
+// (No suspend-time hint on mbarrier.try_wait and no sleep between polls: measured on B200, a hint more than
+// doubles the latency between an arrival and the waiter's wake-up, and a back-off changed nothing.)
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -89,9 +86,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const W
     if (mbar_try_wait(bar, parity)) return true;
     unsigned long long t0 = 0;
     for (uint32_t it = 1;; ++it) {
-#if LTCA_WAIT_SLEEP_NS > 0
-        __nanosleep(LTCA_WAIT_SLEEP_NS);      // a polling warp takes issue slots from the working ones
-#endif
         if (mbar_try_wait(bar, parity)) return true;
         if ((it & 0xffu) == 0) {
             if (*w.abort_flag) return false;

@@ -280,3 +280,48 @@ def test_two_gpu_ranks_exchange_over_nccl():
         # unit = 2e-3 + one bf16 step of the largest element; every pair's partial result leaves the kernels
         # rounded to bf16 and the sum is rounded once more, so up to 1.5 units are rounding alone
         assert worst < 1.5 and status == 0, f"rank {r}: error / tolerance per tensor and pass {detail}"
+
+
+def _dead_rank_worker(rank, world, port, out):
+    """Rank 1 joins the group and then leaves between steps without ever sending; rank 0 starts the ring."""
+    import datetime
+    import time
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=5))
+    dist.barrier()                                         # both ranks are up: the failure happens after this
+    if rank == 1:
+        out[rank] = "left"
+        os._exit(0)                                        # no goodbye: the peer learns of it from the transport
+    B, H, S, D = 1, 2, 32, 8
+    q, k, v, _ = _problem(B, H, S, D, 5)
+    mine = [ring.shard_sequence(x, world, rank, True) for x in (q, k, v)]
+    t0 = time.time()
+    try:
+        ring.ring_attention_fwd(NumpyOps(1 / math.sqrt(D)), *mine, rank, world, True)
+        out[rank] = "finished"                             # must not happen: half of the keys never arrived
+    except Exception as e:                                 # the hop's wait() raises: time-out or closed connection
+        out[rank] = ("error", type(e).__name__, time.time() - t0)
+    os._exit(0)
+
+
+def test_a_rank_that_never_sends_ends_the_hop_with_an_error_not_a_hang():
+    """Failure detection of the ring, on the host: a peer that disappears between steps turns the next hop's
+    wait into an exception within the process group's time-out (5 s here); nothing spins for ever."""
+    world = 2
+    mgr = mp.Manager()
+    out = mgr.dict()
+    ctx = mp.get_context("spawn")
+    port = _free_port()
+    procs = [ctx.Process(target=_dead_rank_worker, args=(r, world, port, out)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(60)
+    alive = [p for p in procs if p.is_alive()]
+    for p in alive:
+        p.kill()
+    assert not alive, "a rank hung instead of failing"
+    assert out.get(1) == "left"
+    assert isinstance(out.get(0), tuple) and out[0][0] == "error", out.get(0)
+    assert out[0][2] < 30
