@@ -1452,20 +1452,28 @@ attn_bwd_fused_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
             constexpr uint32_t idesc_s = make_idesc_bf16(kTile, kQStep, 0, 0);
             constexpr uint32_t idesc_acc = make_idesc_bf16(kTile, kD, 0, 1);    // A K-major (or tensor memory), B N-major
             constexpr uint32_t idesc_dq = make_idesc_bf16(kQStep, kD, 1, 1);    // A M-major (dS^T read as dS), B N-major
-            const uint64_t a_desc = make_smem_desc_sw128(res_smem + (which == 0 ? 0 : kBigTile), 16, 1024);
+            // (descriptors as low words, see mma_ss_lo: offsets are plain 32-bit additions of bytes >> 4.)
+            // The bases pass through an opaque move inside the role, so that the compiler forms each role's
+            // descriptors inside that role instead of hoisting both sets above the branch between the two roles
+            // (which costs the control warps, at 64 registers, a spill on every step).
+            uint32_t opaque_zero;
+            asm volatile("mov.u32 %0, 0;" : "=r"(opaque_zero));
+            const uint32_t res_b = res_smem + opaque_zero, ring_b = ring_smem + opaque_zero;
+            const uint32_t ds_b = ds_smem + opaque_zero, tm_b = tmem_base + opaque_zero;
+            const uint32_t a_desc = smem_desc_lo(res_b + (which == 0 ? 0 : kBigTile), 16);
             // the streamed operand of the first contraction (Q for S^T, dO for dP^T), K-major
-            const uint64_t b1_desc = make_smem_desc_sw128(ring_smem + (which == 0 ? 0 : kBigTile), 16, 1024);
+            const uint32_t b1_desc = smem_desc_lo(ring_b + (which == 0 ? 0 : kBigTile), 16);
             // the streamed operand of the accumulation (dO for dV, Q for dK), rows as the contraction index
-            const uint64_t b2_desc = make_smem_desc_sw128(ring_smem + (which == 0 ? kBigTile : 0), 8192, 1024);
-            // dS^T in shared memory: K-major A of dK (two 64-query blocks 16 KB apart, 32 B per K step inside a
-            // block) and M-major A of dQ_j (blocks of 64 queries 16 KB apart, 16 key rows = 2 KB per K step)
-            const uint64_t ds_m_desc = make_smem_desc_sw128(ds_smem, 2 * kBigTile / 2, 1024);
+            const uint32_t b2_desc = smem_desc_lo(ring_b + (which == 0 ? kBigTile : 0), 8192);
+            // dS^T in shared memory as the M-major A operand of dQ_j: blocks of 64 queries 16 KB apart, 16 key
+            // rows = 2 KB per K step
+            const uint32_t ds_m_desc = smem_desc_lo(ds_b, kBigTile);
             // K as the N-major B operand of dQ_j: 128 key rows of 128 bytes, 16 rows per K step
-            const uint64_t kn_desc = make_smem_desc_sw128(res_smem, 8192, 1024);
-            const uint32_t d1 = tmem_base + (which == 0 ? 0 : 128);
-            const uint32_t a2 = tmem_base + 256;                 // P^T (which == 0 only)
-            const uint32_t d2 = tmem_base + (which == 0 ? 384 : 448);
-            const uint32_t ds_tmem = tmem_base + 320;            // dS^T (bf16) of the step, then dQ_j (which == 1 only)
+            const uint32_t kn_desc = smem_desc_lo(res_b, 8192);
+            const uint32_t d1 = tm_b + (which == 0 ? 0 : 128);
+            const uint32_t a2 = tm_b + 256;                      // P^T (which == 0 only)
+            const uint32_t d2 = tm_b + (which == 0 ? 384 : 448);
+            const uint32_t ds_tmem = tm_b + 320;                 // dS^T (bf16) of the step, then dQ_j (which == 1 only)
             // the accumulation that is still to be issued (one step behind the first contraction)
             bool pending = false;
             int p_g = 0, p_na = 0;
@@ -1478,20 +1486,20 @@ attn_bwd_fused_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 if (ok && p_first && p_na > 0) ok = mbar_wait(bar_acc_free, (uint32_t)((p_na - 1) & 1), wc, 0xf6);
                 if (!ok) return;
                 tc_fence_after_sync();
-                const uint64_t bd = b2_desc + (uint64_t)((slot_of(p_g) * L::kStageBytes) >> 4);
+                const uint32_t bd = b2_desc + (uint32_t)((slot_of(p_g) * L::kStageBytes) >> 4);
                 if constexpr (which == 0) {
 #pragma unroll
                     for (int k = 0; k < kQStep / 16; ++k)
-                        mma_ts(d2, a2 + k * 8, bd + 128 * k, idesc_acc, (p_acc || k > 0) ? 1u : 0u);
+                        mma_ts_lo(d2, a2 + k * 8, bd + 128 * k, idesc_acc, (p_acc || k > 0) ? 1u : 0u);
                 } else {
                     // dK takes dS^T from tensor memory; dQ_j then overwrites those very columns: one thread's
                     // contractions run in order, so dK has read them by then
 #pragma unroll
                     for (int k = 0; k < kQStep / 16; ++k)
-                        mma_ts(d2, ds_tmem + k * 8, bd + 128 * k, idesc_acc, (p_acc || k > 0) ? 1u : 0u);
+                        mma_ts_lo(d2, ds_tmem + k * 8, bd + 128 * k, idesc_acc, (p_acc || k > 0) ? 1u : 0u);
 #pragma unroll
                     for (int k = 0; k < kTile / 16; ++k)
-                        mma_ss(ds_tmem, ds_m_desc + 128 * k, kn_desc + 128 * k, idesc_dq, k > 0 ? 1u : 0u);
+                        mma_ss_lo(ds_tmem, ds_m_desc + 128 * k, kn_desc + 128 * k, idesc_dq, k > 0 ? 1u : 0u);
                 }
                 mma_commit(bar_acc_done);
                 mma_commit(bar_ring_empty(slot_of(p_g)));
@@ -1516,9 +1524,9 @@ attn_bwd_fused_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
                     if (g >= 1) ok = ok && mbar_wait(bar_sdp_free, (uint32_t)((g - 1) & 1), wc, 0xf3);
                     if (!ok) break;
                     tc_fence_after_sync();
-                    const uint64_t bd = b1_desc + (uint64_t)((slot_of(g) * L::kStageBytes) >> 4);
+                    const uint32_t bd = b1_desc + (uint32_t)((slot_of(g) * L::kStageBytes) >> 4);
 #pragma unroll
-                    for (int k = 0; k < kD / 16; ++k) mma_ss(d1, a_desc + 2 * k, bd + 2 * k, idesc_s, k > 0);
+                    for (int k = 0; k < kD / 16; ++k) mma_ss_lo(d1, a_desc + 2 * k, bd + 2 * k, idesc_s, k > 0);
                     mma_commit(bar_sdp_full);
                     LTCA_TRACE_EVT(0x20 + (g << 8));
                     if (pending) do_acc();
