@@ -323,11 +323,16 @@ def other_configs(torch, ctx, peaks):
                        ("kv_len_all_1024", torch.full((B,), S, dtype=torch.int32, device=dev))):
         nbytes = int(lens.sum().item()) * H * D * 4 * 2 + 2 * B * H * D * 4 + 4 * B
         ms = _timed(torch, lambda: ctx.attn_decode(qd, kd, vd, kv_len=lens, out=od, lse=lsed), n=50, flush=flush)
+        ms_b2b = _timed(torch, lambda: ctx.attn_decode(qd, kd, vd, kv_len=lens, out=od, lse=lsed), n=50)
         dec[name] = {"us": ms * 1e3, "algorithmic_bytes": nbytes, "achieved_gbs": nbytes / ms / 1e6,
-                     "frac_of_hbm_peak": nbytes / ms / 1e6 / peaks["hbm_gbs"]}
+                     "frac_of_hbm_peak": nbytes / ms / 1e6 / peaks["hbm_gbs"],
+                     "back_to_back_us": ms_b2b * 1e3, "back_to_back_gbs": nbytes / ms_b2b / 1e6,
+                     "back_to_back_frac_of_hbm_peak": nbytes / ms_b2b / 1e6 / peaks["hbm_gbs"]}
     dec["bound"] = "hbm"
     dec["peak_gbs"] = peaks["hbm_gbs"]
-    dec["note"] = "L2 flushed before every launch; the cache (1 GB) exceeds L2 in any case"
+    dec["note"] = ("us / achieved_gbs: a 256 MB buffer is zeroed before every launch (L2 flushed, and the launch "
+                   "starts behind the flush's write-back); back_to_back_*: launches in a row, the cache (1 GB) "
+                   "exceeds L2 in any case")
     out["config4_decode_B256_H8_S1024_D64_fp32"] = dec
     return out
 
@@ -362,6 +367,8 @@ def module_measurement(args):
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     ctx = ltc.Context(local_rank)
     B, S, E, H, W = 32, 256, 512, 8, 64                 # per rank: sequences are dealt out, weights replicated
+    if args.reference_form:
+        W = E                                           # the reference's module: every head as wide as the model
     g = torch.Generator(device="cuda").manual_seed(SEED + rank)
     x = torch.randn((B * S, E), generator=g, device="cuda")
     dy = torch.randn((B * S, E), generator=g, device="cuda")
@@ -371,6 +378,8 @@ def module_measurement(args):
     wo = (torch.rand((H * W, E), generator=gw, device="cuda") * 2 - 1) * lim
     gamma, beta = torch.ones(E, device="cuda"), torch.zeros(E, device="cuda")
     kw = dict(scale=1 / math.sqrt(W), causal=True, time_major=False, mode=_lib.MODE_BF16)
+    if args.reference_form:
+        kw = dict(scale=1.0, causal=False, time_major=True, mode=_lib.MODE_AUTO)
     fwd = lambda: ctx.tsa_fwd(x, *ws, wo, B, S, H, W, gamma=gamma, beta=beta, **kw)
 
     def bwd():
@@ -404,9 +413,10 @@ def module_measurement(args):
         return
     rows = B * S * world
     gemm = 2.0 * rows * E * H * W                       # one projection
-    core = 4.0 * B * world * H * S * S * W / 2
-    print(json.dumps({"workload": "TimeSelfAttention module, B=32 per GPU, S=256 E=512 H=8 W=64 causal, "
-                                  "tensor-pipe mode; weight gradients summed over the ranks",
+    core = 4.0 * B * world * H * S * S * W / (1 if args.reference_form else 2)
+    print(json.dumps({"workload": f"TimeSelfAttention module, B=32 per GPU, S=256 E=512 H=8 W={W} "
+                                  + ("scale 1 unmasked (reference form), AUTO mode" if args.reference_form else
+                                     "causal, tensor-pipe mode") + "; weight gradients summed over the ranks",
                       "n_gpus": world,
                       "fwd_us": f_ms * 1e3, "bwd_incl_recompute_us": b_ms * 1e3,
                       "fwd_tflops": (4 * gemm + core) / f_ms / 1e9,
@@ -620,6 +630,8 @@ def main():
     ap.add_argument("--model-step", action="store_true",
                     help="side measurement, not the bench line: attention's share of a step shaped like BASELINE "
                          "configs[4] (the layers around the attention module are torch stand-ins), one GPU")
+    ap.add_argument("--reference-form", action="store_true",
+                    help="with --module: head width = E, scale 1, no mask, time-major rows (the reference's module)")
     ap.add_argument("--module", action="store_true",
                     help="side measurement, not the bench line: the TimeSelfAttention module (projections + "
                          "attention + residual + LayerNorm) at BASELINE configs[1] per GPU, tensor-pipe mode")
@@ -722,7 +734,7 @@ def main():
 
     # ---- the bit-reproducible backward (two kernels, seven contractions), for comparison --------------------
     det_bwd_ms = None
-    if bwd_tensor and not args.profile:
+    if bwd_tensor and not args.profile and not args.no_configs:
         with torch.cuda.stream(stream):
             ctx.attn_bwd(q, k, v, o, lse, do, causal=True, mode=_lib.MODE_AUTO, dq=dq, dk=dk, dv=dv, deterministic=True)
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

@@ -21,12 +21,16 @@ struct WideArgs {
     float* lse = nullptr;                       // [B, H, Sq] natural-log sum-exp, optional
     float* scores = nullptr;                    // scratch fp32 [B*H, Sq, Skp]: raw Q K^T (kept for the backward's clamp test)
     void* P = nullptr;                          // scratch bf16 [B*H, Sq, Skp]: probabilities; the backward turns it into dS
+    void* Plo = nullptr;                        // optional second term (p - bf16(p), later dS likewise) for fp32 results:
+                                                // a single bf16 P would be the largest error left in an fp32 output
     // backward
     const void* dout = nullptr; ltca_strides dos{};
     void *dq = nullptr, *dk = nullptr, *dv = nullptr;
     ltca_strides dqs{}, dks{}, dvs{};
     int grads_bf16 = 1;
     float* dP = nullptr;                        // scratch fp32 [B*H, Sq, Skp]
+    void* dS = nullptr;                         // optional bf16 [B*H, Sq, Skp] for dS (null: dS overwrites P, and Plo its
+    void* dSlo = nullptr;                       // second term); with it the probabilities survive the backward
 };
 
 // hi[r, c] = bf16(src[r, c]), lo[r, c] = bf16(src[r, c] - hi[r, c]) (lo may be null); row pitches in elements.

@@ -44,9 +44,11 @@ struct SoftmaxArgs {
     const int32_t* kv_len;       // [B] or null
     const float* scores;         // [B*H, Sq, Skp] raw Q K^T
     __nv_bfloat16* P;            // [B*H, Sq, Skp] normalised probabilities (pad columns zero)
+    __nv_bfloat16* Plo;          // optional low-order term of P (and of dS)
     float* lse;                  // [B*H, Sq] or null
     // backward
     const float* dP;             // [B*H, Sq, Skp]
+    __nv_bfloat16 *dS, *dSlo;    // where dS goes (P / Plo themselves when the caller gave no separate buffer)
 };
 
 // One warp per (batch, head, query) row: scale, clamp (the reference clamps scaled scores at 10,
@@ -89,12 +91,14 @@ __global__ void __launch_bounds__(256) wide_softmax_fwd_kernel(const SoftmaxArgs
             if (a.clamp > 0.f) v = fminf(v, a.clamp);
             pv = __expf(v - m) * inv;
         }
-        p[j] = __float2bfloat16_rn(pv);
+        const __nv_bfloat16 hi = __float2bfloat16_rn(pv);
+        p[j] = hi;
+        if (a.Plo) a.Plo[row * a.Skp + j] = __float2bfloat16_rn(pv - __bfloat162float(hi));
     }
     if (lane == 0 && a.lse) a.lse[row] = l > 0.f ? m + __logf(l) : wneg_inf();
 }
 
-// dS = scale * P o (dP - sum_j P dP), zero where the score was clamped; written over P.
+// dS = scale * P o (dP - sum_j P dP), zero where the score was clamped; written to dS (P itself by default).
 __global__ void __launch_bounds__(256) wide_softmax_bwd_kernel(const SoftmaxArgs a) {
     const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
@@ -102,16 +106,171 @@ __global__ void __launch_bounds__(256) wide_softmax_bwd_kernel(const SoftmaxArgs
     __nv_bfloat16* p = a.P + row * a.Skp;
     const float* dp = a.dP + row * a.Skp;
     const float* s = a.scores + row * a.Skp;
+    __nv_bfloat16* plo = a.Plo ? a.Plo + row * a.Skp : nullptr;
     float delta = 0.f;
-    for (int j = lane; j < a.Sk; j += 32) delta = fmaf(__bfloat162float(p[j]), dp[j], delta);
+    for (int j = lane; j < a.Sk; j += 32) {
+        const float pv = __bfloat162float(p[j]) + (plo ? __bfloat162float(plo[j]) : 0.f);
+        delta = fmaf(pv, dp[j], delta);
+    }
     delta = warp_sum(delta);
     for (int j = lane; j < a.Skp; j += 32) {
         float d = 0.f;
         if (j < a.Sk) {
-            d = __bfloat162float(p[j]) * (dp[j] - delta) * a.scale;
+            const float pv = __bfloat162float(p[j]) + (plo ? __bfloat162float(plo[j]) : 0.f);
+            d = pv * (dp[j] - delta) * a.scale;
             if (a.clamp > 0.f && s[j] * a.scale >= a.clamp) d = 0.f;
         }
-        p[j] = __float2bfloat16_rn(d);
+        const __nv_bfloat16 hi = __float2bfloat16_rn(d);
+        a.dS[row * a.Skp + j] = hi;
+        if (a.dSlo) a.dSlo[row * a.Skp + j] = __float2bfloat16_rn(d - __bfloat162float(hi));
+    }
+}
+
+__device__ __forceinline__ uint2 pack4_bf16(const float* v) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+    return make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b));
+}
+__device__ __forceinline__ void unpack4_bf16(uint2 w, float* v) {
+    v[0] = __uint_as_float(w.x << 16); v[1] = __uint_as_float(w.x & 0xffff0000u);
+    v[2] = __uint_as_float(w.y << 16); v[3] = __uint_as_float(w.y & 0xffff0000u);
+}
+
+// The same two operations for rows of up to 128 * kChunks keys: a lane keeps its part of the row in registers
+// (kChunks groups of four neighbouring columns), so every matrix is read once, 16 bytes per lane and access.
+template <int kChunks>
+__global__ void __launch_bounds__(256) wide_softmax_fwd_rows_kernel(const SoftmaxArgs a) {
+    const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (row >= (int64_t)a.B * a.H * a.Sq) return;
+    const int i = (int)(row % a.Sq);
+    const int b = (int)(row / ((int64_t)a.H * a.Sq));
+    int lim = a.Sk;
+    if (a.kv_len) lim = min(max(a.kv_len[b], 0), a.Sk);
+    if (a.causal) lim = min(lim, i + a.causal_off + 1);
+    const float* s = a.scores + row * a.Skp;
+    const float* mrow = a.keep_mask ? a.keep_mask + ((int64_t)b * a.Sq + i) * a.Sk : nullptr;
+    float x[kChunks][4];
+    float m = wneg_inf();
+#pragma unroll
+    for (int c = 0; c < kChunks; ++c) {
+        const int col = 4 * (lane + 32 * c);
+        float4 v4 = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (col < a.Skp) v4 = *reinterpret_cast<const float4*>(s + col);
+        const float v[4] = {v4.x, v4.y, v4.z, v4.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int j = col + e;
+            float t = v[e] * a.scale;
+            if (a.clamp > 0.f) t = fminf(t, a.clamp);
+            if (j >= lim || (mrow && mrow[j] == 0.0f)) t = wneg_inf();
+            x[c][e] = t;
+            m = fmaxf(m, t);
+        }
+    }
+    m = warp_max(m);
+    float l = 0.f;
+    if (m != wneg_inf()) {
+#pragma unroll
+        for (int c = 0; c < kChunks; ++c)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                x[c][e] = __expf(x[c][e] - m);          // hidden keys: exp(-inf) = 0
+                l += x[c][e];
+            }
+    }
+    l = warp_sum(l);
+    const float inv = l > 0.f ? 1.0f / l : 0.f;
+#pragma unroll
+    for (int c = 0; c < kChunks; ++c) {
+        const int col = 4 * (lane + 32 * c);
+        if (col >= a.Skp) continue;
+        float pv[4], lo[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) pv[e] = l > 0.f ? x[c][e] * inv : 0.f;
+        const uint2 hi = pack4_bf16(pv);
+        *reinterpret_cast<uint2*>(a.P + row * a.Skp + col) = hi;
+        if (a.Plo) {
+            float back[4];
+            unpack4_bf16(hi, back);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) lo[e] = pv[e] - back[e];
+            *reinterpret_cast<uint2*>(a.Plo + row * a.Skp + col) = pack4_bf16(lo);
+        }
+    }
+    if (lane == 0 && a.lse) a.lse[row] = l > 0.f ? m + __logf(l) : wneg_inf();
+}
+
+template <int kChunks>
+__global__ void __launch_bounds__(256) wide_softmax_bwd_rows_kernel(const SoftmaxArgs a) {
+    const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (row >= (int64_t)a.B * a.H * a.Sq) return;
+    const int64_t base = row * a.Skp;
+    float p[kChunks][4], dp[kChunks][4];
+    float delta = 0.f;
+#pragma unroll
+    for (int c = 0; c < kChunks; ++c) {
+        const int col = 4 * (lane + 32 * c);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) p[c][e] = dp[c][e] = 0.f;
+        if (col >= a.Skp) continue;
+        unpack4_bf16(*reinterpret_cast<const uint2*>(a.P + base + col), p[c]);
+        if (a.Plo) {
+            float lo[4];
+            unpack4_bf16(*reinterpret_cast<const uint2*>(a.Plo + base + col), lo);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) p[c][e] += lo[e];
+        }
+        const float4 d4 = *reinterpret_cast<const float4*>(a.dP + base + col);
+        dp[c][0] = d4.x; dp[c][1] = d4.y; dp[c][2] = d4.z; dp[c][3] = d4.w;
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+            if (col + e < a.Sk) delta = fmaf(p[c][e], dp[c][e], delta);
+    }
+    delta = warp_sum(delta);
+#pragma unroll
+    for (int c = 0; c < kChunks; ++c) {
+        const int col = 4 * (lane + 32 * c);
+        if (col >= a.Skp) continue;
+        float d[4], lo[4];
+        float4 s4 = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (a.clamp > 0.f) s4 = *reinterpret_cast<const float4*>(a.scores + base + col);
+        const float sv[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            d[e] = col + e < a.Sk ? p[c][e] * (dp[c][e] - delta) * a.scale : 0.f;
+            if (a.clamp > 0.f && sv[e] * a.scale >= a.clamp) d[e] = 0.f;
+        }
+        const uint2 hi = pack4_bf16(d);
+        *reinterpret_cast<uint2*>(a.dS + base + col) = hi;
+        if (a.dSlo) {
+            float back[4];
+            unpack4_bf16(hi, back);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) lo[e] = d[e] - back[e];
+            *reinterpret_cast<uint2*>(a.dSlo + base + col) = pack4_bf16(lo);
+        }
+    }
+}
+
+// Four neighbouring values per thread when every row starts on 16 bytes.
+__global__ void wide_split_vec_kernel(const float* __restrict__ src, int64_t ld_src, __nv_bfloat16* __restrict__ hi,
+                                      __nv_bfloat16* __restrict__ lo, int64_t ld_dst, int64_t rows, int cols4) {
+    const int64_t n = rows * cols4;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / cols4;
+        const int c = 4 * (int)(i - r * cols4);
+        const float4 x4 = *reinterpret_cast<const float4*>(src + r * ld_src + c);
+        const float x[4] = {x4.x, x4.y, x4.z, x4.w};
+        const uint2 h = pack4_bf16(x);
+        *reinterpret_cast<uint2*>(hi + r * ld_dst + c) = h;
+        if (lo) {
+            float back[4], l[4];
+            unpack4_bf16(h, back);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) l[e] = x[e] - back[e];
+            *reinterpret_cast<uint2*>(lo + r * ld_dst + c) = pack4_bf16(l);
+        }
     }
 }
 
@@ -137,7 +296,15 @@ SoftmaxArgs softmax_args(const WideArgs& w) {
     a.scale = w.scale; a.clamp = w.clamp;
     a.keep_mask = w.keep_mask; a.kv_len = w.kv_len;
     a.scores = w.scores; a.P = reinterpret_cast<__nv_bfloat16*>(w.P); a.lse = w.lse; a.dP = w.dP;
+    a.Plo = reinterpret_cast<__nv_bfloat16*>(w.Plo);
+    a.dS = reinterpret_cast<__nv_bfloat16*>(w.dS ? w.dS : w.P);
+    a.dSlo = reinterpret_cast<__nv_bfloat16*>(w.dS ? w.dSlo : w.Plo);
     return a;
+}
+
+bool softmax_rows_aligned(const SoftmaxArgs& a) {
+    const auto al = [](const void* p, uintptr_t n) { return (reinterpret_cast<uintptr_t>(p) & (n - 1)) == 0; };
+    return al(a.scores, 16) && al(a.P, 8) && al(a.Plo, 8);
 }
 
 // One batched product over the (head, batch) grid.  `a`/`b`: base pointer, row pitch, operand form and the
@@ -170,8 +337,16 @@ int wide_split_bf16(ltca_ctx* ctx, const float* src, int64_t ld_src, void* hi, v
     const int64_t n = rows * cols;
     const int64_t cap = (int64_t)(ctx->sm_count > 0 ? ctx->sm_count : kPlanSms) * 16;
     const int64_t blocks = (n + 255) / 256 < cap ? (n + 255) / 256 : cap;
-    wide_split_kernel<<<(unsigned)blocks, 256, 0, ctx->stream>>>(src, ld_src, reinterpret_cast<__nv_bfloat16*>(hi),
-                                                                 reinterpret_cast<__nv_bfloat16*>(lo), ld_dst, rows, cols);
+    const auto al = [](const void* p, uintptr_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; };
+    if ((cols % 4) == 0 && (ld_src % 4) == 0 && (ld_dst % 4) == 0 && al(src, 16) && al(hi, 8) && al(lo, 8)) {
+        const int64_t n4 = n / 4;
+        const int64_t vblocks = (n4 + 255) / 256 < cap ? (n4 + 255) / 256 : cap;
+        wide_split_vec_kernel<<<(unsigned)vblocks, 256, 0, ctx->stream>>>(
+            src, ld_src, reinterpret_cast<__nv_bfloat16*>(hi), reinterpret_cast<__nv_bfloat16*>(lo), ld_dst, rows, cols / 4);
+    } else {
+        wide_split_kernel<<<(unsigned)blocks, 256, 0, ctx->stream>>>(
+            src, ld_src, reinterpret_cast<__nv_bfloat16*>(hi), reinterpret_cast<__nv_bfloat16*>(lo), ld_dst, rows, cols);
+    }
     LTCA_LAUNCH_OK(ctx, "wide_split_kernel");
     return LTCA_OK;
 }
@@ -206,19 +381,27 @@ int wide_attn_fwd(ltca_ctx* ctx, const WideArgs& w) {
     }
     const SoftmaxArgs sa = softmax_args(w);
     const int64_t rows = (int64_t)w.B * w.H * w.Sq;
-    wide_softmax_fwd_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, ctx->stream>>>(sa);
+    const unsigned sblocks = (unsigned)((rows + 7) / 8);
+    // rows of the scratch matrices start on 32 bytes (pitch a multiple of 8, bases from the 256-byte aligned carve)
+    const bool vec = softmax_rows_aligned(sa);
+    if (vec && Skp <= 256) wide_softmax_fwd_rows_kernel<2><<<sblocks, 256, 0, ctx->stream>>>(sa);
+    else if (vec && Skp <= 512) wide_softmax_fwd_rows_kernel<4><<<sblocks, 256, 0, ctx->stream>>>(sa);
+    else if (vec && Skp <= 1024) wide_softmax_fwd_rows_kernel<8><<<sblocks, 256, 0, ctx->stream>>>(sa);
+    else wide_softmax_fwd_kernel<<<sblocks, 256, 0, ctx->stream>>>(sa);
     LTCA_LAUNCH_OK(ctx, "wide_softmax_fwd_kernel");
     if (!w.o) return LTCA_OK;
     // O = P V : P stored [Sq, Sk] (K-major), V stored [Sk, D] (N-major)
-    Mat a{w.P, Skp, 0, mat, (int64_t)w.H * mat};
-    Mat b{w.v, w.vs.seq, 1, w.vs.head, w.vs.batch};
-    return batched(ctx, w, w.Sq, w.D, w.Sk, &a, &b, 1, w.o, w.os.seq, w.os.head, w.os.batch, w.o_bf16);
+    Mat a[2] = {{w.P, Skp, 0, mat, (int64_t)w.H * mat}, {w.Plo, Skp, 0, mat, (int64_t)w.H * mat}};
+    Mat b[2] = {{w.v, w.vs.seq, 1, w.vs.head, w.vs.batch}, {w.v, w.vs.seq, 1, w.vs.head, w.vs.batch}};
+    return batched(ctx, w, w.Sq, w.D, w.Sk, a, b, w.Plo ? 2 : 1, w.o, w.os.seq, w.os.head, w.os.batch, w.o_bf16);
 }
 
 int wide_attn_bwd(ltca_ctx* ctx, const WideArgs& w) {
     const int Skp = wide_padded_keys(w.Sk);
     const int64_t mat = (int64_t)w.Sq * Skp;
     const int64_t mat_b = (int64_t)w.H * mat;
+    const int terms = w.Plo ? 2 : 1;                 // P (then dS) as one or two bf16 terms
+    if (w.dS && w.Plo && !w.dSlo) return fail(ctx, LTCA_ERR_INVALID, "two-term probabilities need a two-term dS buffer");
     int rc;
     {   // dP = dO V^T : both K-major
         Mat a{w.dout, w.dos.seq, 0, w.dos.head, w.dos.batch};
@@ -226,25 +409,31 @@ int wide_attn_bwd(ltca_ctx* ctx, const WideArgs& w) {
         if ((rc = batched(ctx, w, w.Sq, w.Sk, w.D, &a, &b, 1, w.dP, Skp, mat, mat_b, 0))) return rc;
     }
     {   // dV = P^T dO : P stored [Sq, Sk] = [K, M], dO stored [Sq, D] = [K, N]
-        Mat a{w.P, Skp, 1, mat, mat_b};
-        Mat b{w.dout, w.dos.seq, 1, w.dos.head, w.dos.batch};
-        if ((rc = batched(ctx, w, w.Sk, w.D, w.Sq, &a, &b, 1, w.dv, w.dvs.seq, w.dvs.head, w.dvs.batch, w.grads_bf16)))
+        Mat a[2] = {{w.P, Skp, 1, mat, mat_b}, {w.Plo, Skp, 1, mat, mat_b}};
+        Mat b[2] = {{w.dout, w.dos.seq, 1, w.dos.head, w.dos.batch}, {w.dout, w.dos.seq, 1, w.dos.head, w.dos.batch}};
+        if ((rc = batched(ctx, w, w.Sk, w.D, w.Sq, a, b, terms, w.dv, w.dvs.seq, w.dvs.head, w.dvs.batch, w.grads_bf16)))
             return rc;
     }
     const SoftmaxArgs sa = softmax_args(w);
     const int64_t rows = (int64_t)w.B * w.H * w.Sq;
-    wide_softmax_bwd_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, ctx->stream>>>(sa);
+    const unsigned sblocks = (unsigned)((rows + 7) / 8);
+    const bool vec = softmax_rows_aligned(sa) && (reinterpret_cast<uintptr_t>(sa.dP) & 15) == 0 &&
+                     (reinterpret_cast<uintptr_t>(sa.dS) & 7) == 0 && (reinterpret_cast<uintptr_t>(sa.dSlo) & 7) == 0;
+    if (vec && Skp <= 256) wide_softmax_bwd_rows_kernel<2><<<sblocks, 256, 0, ctx->stream>>>(sa);
+    else if (vec && Skp <= 512) wide_softmax_bwd_rows_kernel<4><<<sblocks, 256, 0, ctx->stream>>>(sa);
+    else if (vec && Skp <= 1024) wide_softmax_bwd_rows_kernel<8><<<sblocks, 256, 0, ctx->stream>>>(sa);
+    else wide_softmax_bwd_kernel<<<sblocks, 256, 0, ctx->stream>>>(sa);
     LTCA_LAUNCH_OK(ctx, "wide_softmax_bwd_kernel");
     {   // dQ = dS K : dS K-major, K stored [Sk, D] = [K, N]
-        Mat a{w.P, Skp, 0, mat, mat_b};
-        Mat b{w.kh, w.ks.seq, 1, w.ks.head, w.ks.batch};
-        if ((rc = batched(ctx, w, w.Sq, w.D, w.Sk, &a, &b, 1, w.dq, w.dqs.seq, w.dqs.head, w.dqs.batch, w.grads_bf16)))
+        Mat a[2] = {{sa.dS, Skp, 0, mat, mat_b}, {sa.dSlo, Skp, 0, mat, mat_b}};
+        Mat b[2] = {{w.kh, w.ks.seq, 1, w.ks.head, w.ks.batch}, {w.kh, w.ks.seq, 1, w.ks.head, w.ks.batch}};
+        if ((rc = batched(ctx, w, w.Sq, w.D, w.Sk, a, b, terms, w.dq, w.dqs.seq, w.dqs.head, w.dqs.batch, w.grads_bf16)))
             return rc;
     }
     {   // dK = dS^T Q : dS stored [Sq, Sk] = [K, M], Q stored [Sq, D] = [K, N]
-        Mat a{w.P, Skp, 1, mat, mat_b};
-        Mat b{w.qh, w.qs.seq, 1, w.qs.head, w.qs.batch};
-        if ((rc = batched(ctx, w, w.Sk, w.D, w.Sq, &a, &b, 1, w.dk, w.dks.seq, w.dks.head, w.dks.batch, w.grads_bf16)))
+        Mat a[2] = {{sa.dS, Skp, 1, mat, mat_b}, {sa.dSlo, Skp, 1, mat, mat_b}};
+        Mat b[2] = {{w.qh, w.qs.seq, 1, w.qs.head, w.qs.batch}, {w.qh, w.qs.seq, 1, w.qs.head, w.qs.batch}};
+        if ((rc = batched(ctx, w, w.Sk, w.D, w.Sq, a, b, terms, w.dk, w.dks.seq, w.dks.head, w.dks.batch, w.grads_bf16)))
             return rc;
     }
     return LTCA_OK;

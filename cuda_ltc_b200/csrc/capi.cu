@@ -5,6 +5,7 @@
 
 #include "host_common.h"
 #include "sm100_ptx.cuh"
+#include "attn_wide.h"
 
 namespace ltca {
 int launch_attn_fwd_sm100_bf16in(ltca_ctx* ctx, const ltca_attn_params* p, const void* q,
@@ -244,6 +245,83 @@ int pack_to_bf16(ltca_ctx* ctx, const void* src, const ltca_strides& st, void* d
     return LTCA_OK;
 }
 
+
+// The materialised-score path (attn_wide_sm100.cu) behind the core entry points: on explicit request
+// (LTCA_MODE_BF16) for head widths the streaming kernels do not cover, any multiple of 8.
+bool wide_core_path(const ltca_attn_params* p, bool backward) {
+    if (p->mode != LTCA_MODE_BF16) return false;
+    if (backward ? attn_bwd_sm100_supported(p) : attn_fwd_sm100_supported(p)) return false;
+    if (p->D < 8 || (p->D % 8) || p->Sq < 1 || p->Sk < 1 || !(p->scale > 0.f)) return false;
+    if (p->dtype == LTCA_BF16) {
+        if (!wide_supported(p->D, p->q_strides, p->k_strides, p->v_strides)) return false;
+        if ((p->o_strides.seq % 8) || (p->o_strides.head % 8) || (p->o_strides.batch % 8)) return false;
+    } else if ((p->o_strides.seq % 4) || (p->o_strides.head % 4) || (p->o_strides.batch % 4)) {
+        return false;
+    }
+    return true;
+}
+
+size_t wide_core_workspace(const ltca_attn_params* p, bool backward) {
+    size_t n = 0;
+    if (p->dtype == LTCA_F32) n += packed_bytes(p, p->Sq) * (backward ? 2 : 1) + 2 * packed_bytes(p, p->Sk);
+    const size_t elems = wide_matrix_elems(p->B, p->H, p->Sq, p->Sk);
+    n += align_up(elems * 4, 256) + align_up(elems * 2, 256);       // raw scores, probabilities
+    if (p->dtype == LTCA_F32) n += align_up(elems * 2, 256);         // second term of the probabilities (fp32 results)
+    if (backward) n += align_up(elems * 4, 256);                     // dP
+    return n;
+}
+
+int launch_wide_core(ltca_ctx* ctx, const ltca_attn_params* p, bool backward) {
+    const size_t need = wide_core_workspace(p, backward);
+    if (!p->workspace || p->workspace_bytes < need)
+        return fail(ctx, LTCA_ERR_WORKSPACE, "this head width on the tensor pipe needs %zu bytes of workspace", need);
+    if (reinterpret_cast<uintptr_t>(p->workspace) & 255)
+        return fail(ctx, LTCA_ERR_INVALID, "workspace must be 256-byte aligned");
+    char* w = reinterpret_cast<char*>(p->workspace);
+    WideArgs a;
+    a.B = p->B; a.H = p->H; a.Sq = p->Sq; a.Sk = p->Sk; a.D = p->D;
+    a.causal = p->causal ? 1 : 0;
+    a.scale = p->scale; a.clamp = p->score_clamp;
+    a.keep_mask = p->keep_mask; a.kv_len = p->kv_len;
+    a.qh = p->q; a.kh = p->k; a.v = p->v;
+    a.qs = p->q_strides; a.ks = p->k_strides; a.vs = p->v_strides;
+    a.dout = p->dout; a.dos = p->do_strides;
+    int rc;
+    if (p->dtype == LTCA_F32) {
+        void* qb = w; w += packed_bytes(p, p->Sq);
+        void* kb = w; w += packed_bytes(p, p->Sk);
+        void* vb = w; w += packed_bytes(p, p->Sk);
+        if ((rc = pack_to_bf16(ctx, p->q, p->q_strides, qb, p->B, p->H, p->Sq, p->D))) return rc;
+        if ((rc = pack_to_bf16(ctx, p->k, p->k_strides, kb, p->B, p->H, p->Sk, p->D))) return rc;
+        if ((rc = pack_to_bf16(ctx, p->v, p->v_strides, vb, p->B, p->H, p->Sk, p->D))) return rc;
+        a.qh = qb; a.kh = kb; a.v = vb;
+        a.qs = contiguous_strides(p->H, p->Sq, p->D);
+        a.ks = a.vs = contiguous_strides(p->H, p->Sk, p->D);
+        if (backward) {
+            void* gb = w; w += packed_bytes(p, p->Sq);
+            if ((rc = pack_to_bf16(ctx, p->dout, p->do_strides, gb, p->B, p->H, p->Sq, p->D))) return rc;
+            a.dout = gb; a.dos = a.qs;
+        }
+    }
+    const size_t elems = wide_matrix_elems(p->B, p->H, p->Sq, p->Sk);
+    a.scores = reinterpret_cast<float*>(w); w += align_up(elems * 4, 256);
+    a.P = w; w += align_up(elems * 2, 256);
+    if (p->dtype == LTCA_F32) { a.Plo = w; w += align_up(elems * 2, 256); }
+    const int bf16 = p->dtype == LTCA_BF16 ? 1 : 0;
+    if (!backward) {
+        a.o = p->o; a.os = p->o_strides; a.o_bf16 = bf16; a.lse = p->lse;
+        return wide_attn_fwd(ctx, a);
+    }
+    // the probabilities are formed again from Q and K (the forward's result and lse are not needed for that)
+    a.dP = reinterpret_cast<float*>(w);
+    a.o = nullptr; a.lse = nullptr;
+    if ((rc = wide_attn_fwd(ctx, a))) return rc;
+    a.dq = p->dq; a.dk = p->dk; a.dv = p->dv;
+    a.dqs = p->dq_strides; a.dks = p->dk_strides; a.dvs = p->dv_strides;
+    a.grads_bf16 = bf16;
+    return wide_attn_bwd(ctx, a);
+}
+
 }  // namespace
 }  // namespace ltca
 
@@ -348,13 +426,15 @@ int ltca_selftest_bounded_wait(ltca_ctx* ctx, uint32_t limit_us) {
 
 int ltca_attn_uses_tensor_pipe(const ltca_attn_params* p, int backward) {
     if (!p) return 0;
-    return tensor_path(p, backward != 0) ? 1 : 0;
+    return (tensor_path(p, backward != 0) || wide_core_path(p, backward != 0)) ? 1 : 0;
 }
 
 int ltca_attn_workspace_bytes(const ltca_attn_params* p, int backward, size_t* bytes_out) {
     if (!p || !bytes_out) return LTCA_ERR_INVALID;
     size_t n = 0;
-    if (tensor_path(p, backward != 0)) {
+    if (wide_core_path(p, backward != 0)) {
+        n = wide_core_workspace(p, backward != 0);
+    } else if (tensor_path(p, backward != 0)) {
         if (p->dtype == LTCA_F32) {
             n += packed_bytes(p, p->Sq) + 2 * packed_bytes(p, p->Sk);     // q, k, v as bf16
             if (backward) n += packed_bytes(p, p->Sq);                     // dO as bf16
@@ -371,9 +451,11 @@ int ltca_attn_fwd(ltca_ctx* ctx, const ltca_attn_params* p) {
     int rc = check_common(ctx, p);
     if (rc) return rc;
     LTCA_CUDA_OK(ctx, cudaSetDevice(ctx->device));
+    if (wide_core_path(p, false)) return launch_wide_core(ctx, p, false);
     if (p->mode == LTCA_MODE_BF16 && !tensor_path(p, false))
         return fail(ctx, LTCA_ERR_UNSUPPORTED,
-                    "the tensor-pipe forward needs head_dim 64 or 128 (got %d)", p->D);
+                    "the tensor-pipe forward needs a head_dim that is a multiple of 8 with 16-byte aligned rows (got %d)",
+                    p->D);
     if (!tensor_path(p, false)) return launch_attn_fwd_fp32(ctx, p);
     if (p->dtype == LTCA_BF16)
         return launch_attn_fwd_sm100_bf16in(ctx, p, p->q, p->k, p->v, p->q_strides, p->k_strides,
@@ -404,6 +486,7 @@ int ltca_attn_bwd(ltca_ctx* ctx, const ltca_attn_params* p) {
     LTCA_CUDA_OK(ctx, cudaSetDevice(ctx->device));
     if (p->workspace && (reinterpret_cast<uintptr_t>(p->workspace) & 255))
         return fail(ctx, LTCA_ERR_INVALID, "workspace must be 256-byte aligned");
+    if (wide_core_path(p, true)) return launch_wide_core(ctx, p, true);
     if (p->mode == LTCA_MODE_BF16 && !tensor_path(p, true))
         return fail(ctx, LTCA_ERR_UNSUPPORTED, "the tensor-pipe backward does not cover this problem");
     if (!tensor_path(p, true)) return launch_attn_bwd_fp32(ctx, p);

@@ -57,6 +57,7 @@ struct GemmKArgs {
     int out_bf16;
     int tma_store;           // results leave through shared memory and a TMA store (needs 16-byte aligned rows)
     void* C[3];
+    void* c_lo;              // second bf16 term of the (single) result, or null; its tensor map is tc1
     const float* bias[3];
     float* partial;          // [problem][slice][M][N] when ksplit > 1
     uint32_t* status;
@@ -229,7 +230,8 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap ta0, const __grid_con
             // boxes - 64 bf16 or 32 fp32 columns wide, 128 rows - and one thread stores the boxes; the tensor map
             // clips rows and columns past the end of C.  (Storing a row's 16-byte pieces straight from registers
             // costs 32 L1 wavefronts per instruction, about as many cycles per tile as its MMAs.)
-            const int piece_cols = (staged && !g.out_bf16) ? 128 : kBN;
+            // With a second term the piece is 128 columns of each: the high-order boxes, then the low-order ones.
+            const int piece_cols = (staged && (!g.out_bf16 || g.c_lo)) ? 128 : kBN;
             for (int p0 = 0; p0 < kBN; p0 += piece_cols) {
                 if (staged) {
                     // the previous piece's boxes have been read: the storing thread waits for that before it comes here
@@ -271,6 +273,18 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap ta0, const __grid_con
                                 w.z = pack_bf16x2(__uint_as_float(v[8 * c + 4]), __uint_as_float(v[8 * c + 5]));
                                 w.w = pack_bf16x2(__uint_as_float(v[8 * c + 6]), __uint_as_float(v[8 * c + 7]));
                                 *reinterpret_cast<uint4*>(box + (((ch0 + c) ^ (row & 7)) << 4)) = w;
+                                if (g.c_lo) {
+                                    uint4 l;
+                                    l.x = pack_bf16x2(__uint_as_float(v[8 * c + 0]) - __uint_as_float(w.x << 16),
+                                                      __uint_as_float(v[8 * c + 1]) - __uint_as_float(w.x & 0xffff0000u));
+                                    l.y = pack_bf16x2(__uint_as_float(v[8 * c + 2]) - __uint_as_float(w.y << 16),
+                                                      __uint_as_float(v[8 * c + 3]) - __uint_as_float(w.y & 0xffff0000u));
+                                    l.z = pack_bf16x2(__uint_as_float(v[8 * c + 4]) - __uint_as_float(w.z << 16),
+                                                      __uint_as_float(v[8 * c + 5]) - __uint_as_float(w.z & 0xffff0000u));
+                                    l.w = pack_bf16x2(__uint_as_float(v[8 * c + 6]) - __uint_as_float(w.w << 16),
+                                                      __uint_as_float(v[8 * c + 7]) - __uint_as_float(w.w & 0xffff0000u));
+                                    *reinterpret_cast<uint4*>(box + 2 * (kBM * 128) + (((ch0 + c) ^ (row & 7)) << 4)) = l;
+                                }
                             }
                         } else {
                             uint8_t* box = stage + (cp / 32) * (kBM * 128) + row * 128;
@@ -300,6 +314,14 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap ta0, const __grid_con
 #pragma unroll
                         for (int c = 0; c < 32; ++c)
                             if (gn0 + c < g.N) dst[c] = __float2bfloat16_rn(__uint_as_float(v[c]));
+                        if (g.c_lo) {
+                            __nv_bfloat16* lo = reinterpret_cast<__nv_bfloat16*>(g.c_lo) + (dst -
+                                                reinterpret_cast<__nv_bfloat16*>(g.C[t.problem]));
+#pragma unroll
+                            for (int c = 0; c < 32; ++c)
+                                if (gn0 + c < g.N)
+                                    lo[c] = __float2bfloat16_rn(__uint_as_float(v[c]) - __bfloat162float(dst[c]));
+                        }
                     } else {
                         float* dst = reinterpret_cast<float*>(g.C[t.problem]) + t.bh * g.c_bs[0] + t.bb * g.c_bs[1] +
                                      (int64_t)gm * g.ldc + gn0;
@@ -315,8 +337,12 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap ta0, const __grid_con
                         const CUtensorMap* tc = t.problem == 0 ? &tc0 : (t.problem == 1 ? &tc1 : &tc2);
                         const int n_boxes = piece_cols / box_cols;
                         for (int bx = 0; bx < n_boxes; ++bx)
-                            if (t.n0 + p0 + bx * box_cols < g.N)
+                            if (t.n0 + p0 + bx * box_cols < g.N) {
                                 tma_store_4d(tc, stage_addr + bx * (kBM * 128), t.n0 + p0 + bx * box_cols, t.m0, t.bh, t.bb);
+                                if (g.c_lo)
+                                    tma_store_4d(&tc1, stage_addr + (2 + bx) * (kBM * 128), t.n0 + p0 + bx * box_cols,
+                                                 t.m0, t.bh, t.bb);
+                            }
                         tma_store_commit();
                         tma_store_wait_read<0>();
                     }
@@ -433,6 +459,9 @@ int gemm_sm100(ltca_ctx* ctx, const GemmProblem& gp) {
     g.ksplit = gp.ksplit > 1 ? gp.ksplit : 1;
     g.ldc = gp.ldc;
     g.out_bf16 = gp.out_bf16;
+    g.c_lo = gp.c_lo;
+    if (gp.c_lo && (!gp.out_bf16 || gp.n_problems != 1 || gp.ksplit > 1))
+        return fail(ctx, LTCA_ERR_INVALID, "gemm: a second result term needs one bf16 problem and no split of K");
     for (int i = 0; i < 3; ++i) { g.C[i] = gp.c[i < gp.n_problems ? i : 0]; g.bias[i] = i < gp.n_problems ? gp.bias[i] : nullptr; }
     g.partial = gp.partial;
     g.status = ctx->d_status;
@@ -443,6 +472,7 @@ int gemm_sm100(ltca_ctx* ctx, const GemmProblem& gp) {
                    ((gp.c_bs[1] * ces) % 16) == 0) ? 1 : 0;
     for (int i = 0; i < gp.n_problems && g.tma_store; ++i)
         if (reinterpret_cast<uintptr_t>(gp.c[i]) & 15) g.tma_store = 0;
+    if (reinterpret_cast<uintptr_t>(gp.c_lo) & 15) g.tma_store = 0;
     CUtensorMap tc[3];
     memset(tc, 0, sizeof(tc));
     if (g.tma_store) {
@@ -450,7 +480,8 @@ int gemm_sm100(ltca_ctx* ctx, const GemmProblem& gp) {
         cs.batch = gp.c_bs[1]; cs.head = gp.c_bs[0]; cs.seq = gp.ldc;
         for (int i = 0; i < 3; ++i) {
             const int j = i < gp.n_problems ? i : 0;
-            if ((rc = make_tmap_bhsd(ctx, &tc[i], gp.c[j], ces, gp.batch_b, gp.batch_h, gp.M, gp.N, cs,
+            void* dst = (i == 1 && gp.c_lo) ? gp.c_lo : gp.c[j];
+            if ((rc = make_tmap_bhsd(ctx, &tc[i], dst, ces, gp.batch_b, gp.batch_h, gp.M, gp.N, cs,
                                      gp.out_bf16 ? 64 : 32, kBM))) return rc;
         }
     }

@@ -24,6 +24,8 @@ struct GemmProblem {
     const float* bias[3] = {nullptr, nullptr, nullptr};
     int64_t ldc = 0;
     int out_bf16 = 0;               // result element type: bf16 or fp32
+    void* c_lo = nullptr;           // with out_bf16, one problem, no split of K: also write bf16(x - bf16(x)) here,
+                                    // laid out like C, so that C + c_lo carry 16 significant bits of the fp32 result
     float* partial = nullptr;       // gemm_sm100_partial_bytes() bytes when ksplit > 1
     // A grid of batch_h x batch_b independent products of the same shape (heads x sequences of the materialised
     // attention path): operand i of batch entry (h, b) starts h * bs[0] + b * bs[1] elements after its pointer.

@@ -542,7 +542,7 @@ struct TPlan {
     int ks_in, ks_out;
     // materialised-score path: low-order parts of x, Wq, Wk, q, k; fp32 projection scratch; score matrices
     bool wide;
-    size_t q32, mat32, mat16;
+    size_t mat32, mat16;
 };
 
 int make_tplan(const ltca_tsa_params* t, TPlan* pl, bool backward) {
@@ -556,12 +556,11 @@ int make_tplan(const ltca_tsa_params* t, TPlan* pl, bool backward) {
     pl->lse = align_up((size_t)t->B * t->H * t->S * sizeof(float), 256);
     pl->y = align_up((size_t)pl->rows * t->E * sizeof(float), 256);
     pl->wide = use_wide(t, backward);
-    pl->q32 = pl->mat32 = pl->mat16 = 0;
+    pl->mat32 = pl->mat16 = 0;
     pl->attn_fwd = pl->attn_bwd = 0;
     int rc;
     if (pl->wide) {
         const size_t elems = wide_matrix_elems(t->B, t->H, t->S, t->S);
-        pl->q32 = align_up((size_t)pl->rows * pl->HW * sizeof(float), 256);
         pl->mat32 = align_up(elems * sizeof(float), 256);
         pl->mat16 = align_up(elems * 2, 256);
     } else {
@@ -581,9 +580,11 @@ int make_tplan(const ltca_tsa_params* t, TPlan* pl, bool backward) {
 
 // Extra scratch of the materialised-score path: x_lo, Wq_lo, Wk_lo, q_lo, k_lo, the fp32 projection result that is
 // split into q (then k), the raw scores and the probabilities; the backward adds dP.
+// What of it a forward keeps for the backward: the low-order parts, the raw scores and the probabilities.
+size_t wide_kept(const TPlan& pl) { return pl.wide ? pl.xb + 2 * pl.w_in + 2 * pl.act + pl.mat32 + pl.mat16 : 0; }
 size_t wide_extra(const TPlan& pl, int which) {
     if (!pl.wide) return 0;
-    return pl.xb + 2 * pl.w_in + 2 * pl.act + pl.q32 + pl.mat32 + pl.mat16 + (which == 0 ? 0 : pl.mat32);
+    return wide_kept(pl) + (which == 0 ? 0 : pl.mat32 + pl.mat16);     // backward: dP and dS
 }
 
 size_t tensor_workspace(const TPlan& pl, int which) {
@@ -595,15 +596,17 @@ size_t tensor_workspace(const TPlan& pl, int which) {
     return n + pl.partial;
 }
 
-size_t tensor_saved_bytes(const TPlan& pl) { return pl.xb + 3 * pl.w_in + pl.w_out + 4 * pl.act + pl.lse; }
+size_t tensor_saved_bytes(const TPlan& pl) {
+    return pl.xb + 3 * pl.w_in + pl.w_out + 4 * pl.act + pl.lse + wide_kept(pl);
+}
 
 struct TBufs {
     void *xb, *wq, *wk, *wv, *wo, *q, *k, *v, *ctx;
     float* lse;
     char* rest;
     // materialised-score path
-    void *xl, *wql, *wkl, *ql, *kl, *P;
-    float *q32, *scores, *dP;
+    void *xl, *wql, *wkl, *ql, *kl, *P, *dS;
+    float *scores, *dP;
 };
 
 // The attention problem of the module for the materialised-score path (bf16 views of the projection outputs).
@@ -617,14 +620,14 @@ void fill_wide(const ltca_tsa_params* t, const TBufs& tb, WideArgs* w) {
     w->qs = w->ks = w->vs = w->os = a.q_strides;
     w->dos = w->dqs = w->dks = w->dvs = a.q_strides;
     w->o = tb.ctx; w->o_bf16 = 1; w->lse = tb.lse;
-    w->scores = tb.scores; w->P = tb.P; w->dP = tb.dP;
+    w->scores = tb.scores; w->P = tb.P; w->dP = tb.dP; w->dS = tb.dS;
     w->grads_bf16 = 1;
 }
 
 // bf16 copies, fused Q/K/V projection, attention forward.
 int tensor_forward_core(ltca_ctx* ctx, const ltca_tsa_params* t, const TPlan& pl, char* w, TBufs* tb, int which) {
     char* rest = w;
-    const bool saved = t->saved && !pl.wide;          // the materialised-score path always recomputes
+    const bool saved = t->saved != nullptr;
     if (saved) w = reinterpret_cast<char*>(t->saved);
     tb->xb = w;  w += pl.xb;
     tb->wq = w;  w += pl.w_in;
@@ -642,13 +645,19 @@ int tensor_forward_core(ltca_ctx* ctx, const ltca_tsa_params* t, const TPlan& pl
         tb->wkl = w; w += pl.w_in;
         tb->ql = w;  w += pl.act;
         tb->kl = w;  w += pl.act;
-        tb->q32 = reinterpret_cast<float*>(w);    w += pl.q32;
         tb->scores = reinterpret_cast<float*>(w); w += pl.mat32;
         tb->P = w;   w += pl.mat16;
-        tb->dP = nullptr;
-        if (which != 0) { tb->dP = reinterpret_cast<float*>(w); w += pl.mat32; }
     }
-    tb->rest = saved ? rest : w;
+    char* r = saved ? rest : w;                        // what follows is never kept
+    if (pl.wide) {
+        tb->dP = nullptr; tb->dS = nullptr;
+        if (which != 0) {
+            // dS gets its own buffer: the probabilities stay valid for the next backward call from the same forward
+            tb->dP = reinterpret_cast<float*>(r); r += pl.mat32;
+            tb->dS = r; r += pl.mat16;
+        }
+    }
+    tb->rest = r;
     if (saved && t->reuse_forward) return LTCA_OK;
     const int E = t->E, HW = pl.HW, Ep = pl.Ep;
     int rc;
@@ -665,18 +674,20 @@ int tensor_forward_core(ltca_ctx* ctx, const ltca_tsa_params* t, const TPlan& pl
         void* olo[2] = {tb->ql, tb->kl};
         const float* bias[2] = {t->bq, t->bk};
         for (int i = 0; i < 2; ++i) {
-            // x W = x_hi W_hi + x_hi W_lo + x_lo W_hi in one fp32 accumulator, then split into two bf16 terms
+            // x W = x_hi W_hi + x_hi W_lo + x_lo W_hi in one fp32 accumulator, which the epilogue writes as two
+            // bf16 terms
             GemmProblem gp;
             gp.M = (int)pl.rows; gp.N = HW; gp.K = E;
             gp.n_sum = 3;
             gp.a[0] = GemmOperand{tb->xb, Ep, 0}; gp.b[0] = GemmOperand{whi[i], HW, 1};
             gp.a[1] = GemmOperand{tb->xb, Ep, 0}; gp.b[1] = GemmOperand{wlo[i], HW, 1};
             gp.a[2] = GemmOperand{tb->xl, Ep, 0}; gp.b[2] = GemmOperand{whi[i], HW, 1};
-            gp.c[0] = tb->q32;
+            gp.c[0] = ohi[i];
+            gp.c_lo = olo[i];
+            gp.out_bf16 = 1;
             gp.bias[0] = bias[i];
             gp.ldc = HW;
             if ((rc = gemm_sm100(ctx, gp))) return rc;
-            if ((rc = wide_split_bf16(ctx, tb->q32, HW, ohi[i], olo[i], HW, pl.rows, HW))) return rc;
         }
         {
             GemmProblem gp;

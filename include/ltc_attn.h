@@ -46,9 +46,12 @@ typedef enum { LTCA_F32 = 0, LTCA_BF16 = 1 } ltca_dtype;
 /*
  * Arithmetic of the two contractions.
  *   LTCA_MODE_BF16 : bf16 operands on the tcgen05 tensor pipe, fp32 accumulation in tensor
- *                    memory, fp32 softmax.  fp32 storage is rounded to bf16 on the fly.
+ *                    memory, fp32 softmax.  fp32 storage is rounded to bf16 on the fly.  Head widths 64
+ *                    (forward also 128) run on the streaming kernels; any other multiple of 8 runs through
+ *                    written-out score matrices and batched tensor-pipe products (more workspace:
+ *                    ltca_attn_workspace_bytes tells).
  *   LTCA_MODE_FP32 : fp32 FMA arithmetic end to end (the 1e-5 mode).
- *   LTCA_MODE_AUTO : BF16 when the shape is supported by the tensor-pipe kernels, else FP32.
+ *   LTCA_MODE_AUTO : BF16 when the streaming tensor-pipe kernels cover the shape, else FP32.
  */
 typedef enum { LTCA_MODE_AUTO = 0, LTCA_MODE_BF16 = 1, LTCA_MODE_FP32 = 3 } ltca_mode;
 

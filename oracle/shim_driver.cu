@@ -26,8 +26,9 @@
 //   shim_driver time <B> <S> <E> <H> <iters>
 //       Wall-clock (host, every device synchronisation of the callee included) and CUDA-event milliseconds of
 //       forward, backwardWeights and backward, called as the reference's model calls them, for the reference's
-//       cuDNN module and for the binding in the reference's form (head width = E, scale 1, no mask) and in the
-//       compact form (head width E/H, scale 1/sqrt(width), causal).  One JSON line.
+//       cuDNN module and for the binding in the reference's form (head width = E, scale 1, no mask; once
+//       recomputing the forward in each backward call and once with setReuseForward(true)) and in the compact
+//       form (head width E/H, scale 1/sqrt(width), causal).  One JSON line.
 #include <cuda_runtime.h>
 
 #include <chrono>
@@ -384,7 +385,7 @@ void print_timing(const char* key, const Timing& t, bool last) {
 int run_time(int B, int S, int E, int H, int iters) {
     const size_t n = (size_t)B * S * E;
     CudaMemory<float> x = to_device(random_host(n, 1)), gy = to_device(random_host(n, 2));
-    Timing tr, ts, tc;
+    Timing tr, ts, tk, tc;
     try {
         auto ref = TimeSelfAttention::create(E, H, true, true, 0.0f, 42);
         tr = time_module(*ref, x, gy, B, S, iters);
@@ -394,6 +395,13 @@ int run_time(int B, int S, int E, int H, int iters) {
         ts = time_module(shim, x, gy, B, S, iters);
     } catch (const std::exception& e) { ts.note = e.what(); }
     try {
+        // the binding's extension: forward() keeps its intermediates for the two backward calls, which is what
+        // the cuDNN module does with its reserve space
+        B200TimeSelfAttention shim(E, H, true, true, 0.0f, 42, false, false);
+        shim.setReuseForward(true);
+        tk = time_module(shim, x, gy, B, S, iters);
+    } catch (const std::exception& e) { tk.note = e.what(); }
+    try {
         B200TimeSelfAttention shim(E, H, true, true, 0.0f, 42, true, true);
         tc = time_module(shim, x, gy, B, S, iters);
     } catch (const std::exception& e) { tc.note = e.what(); }
@@ -401,6 +409,7 @@ int run_time(int B, int S, int E, int H, int iters) {
            cudnn_ops::getCuDNNVersionString().c_str());
     print_timing("reference_cudnn_module", tr, false);
     print_timing("binding_reference_form", ts, false);
+    print_timing("binding_reference_form_kept_forward", tk, false);
     print_timing("binding_compact_causal_form", tc, true);
     printf("}\n");
     return 0;

@@ -216,9 +216,9 @@ def test_decode_zero_length(ctx):
 
 def test_argument_errors(ctx):
     from cuda_ltc_b200 import LtcaError
-    q = torch.zeros((1, 1, 4, 24), device="cuda")
+    q = torch.zeros((1, 1, 4, 20), device="cuda")
     with pytest.raises(LtcaError) as e:
-        ctx.attn_fwd(q, q, q, mode=_lib.MODE_BF16)       # head_dim 24 is outside the tensor path
+        ctx.attn_fwd(q, q, q, mode=_lib.MODE_BF16)       # head_dim 20: no tensor path takes rows that are not 16-byte multiples
     assert e.value.code == -2
     with pytest.raises(LtcaError) as e:
         ctx.attn_fwd(q, q, q, scale=-1.0)
@@ -328,6 +328,60 @@ def test_tensor_pipe_backward_full_size(ctx):
             mag = max(1.0, float(np.abs(r).max()))
             assert (np.abs(gh - r) <= TC_MAX_ABS * mag + np.abs(r) * 2.0 ** -8).all(), name
             assert rel_l2(gh, r) < 2 * (TC_REL_L2 + 2.0 ** -9), name
+
+
+WIDE_CORE_CASES = [
+    # B, H, Sq, Sk, D, causal, kvlen, mask, clamp
+    (2, 4, 64, 64, 32, False, False, False, 0.0),      # config 1 of the benchmark on the tensor pipe
+    (2, 2, 8, 8, 16, False, False, False, 10.0),       # the reference test fixture
+    (3, 2, 100, 130, 32, True, True, True, 3.0),
+    (2, 2, 200, 200, 256, True, False, False, 0.0),
+    (1, 2, 70, 33, 8, True, False, False, 0.0),        # more queries than keys: early rows see nothing
+    (2, 2, 300, 300, 128, True, False, False, 0.0),    # width 128 backward (no streaming kernel)
+]
+
+
+@pytest.mark.parametrize("storage", ["bf16", "f32"])
+@pytest.mark.parametrize("case", WIDE_CORE_CASES)
+def test_tensor_pipe_other_head_widths(ctx, case, storage):
+    """LTCA_MODE_BF16 with a head width the streaming kernels do not cover (any multiple of 8): written-out
+    scores and batched tcgen05 GEMMs.  Same arithmetic class as the streaming bf16 mode (bf16 operands, fp32
+    accumulation, P and dS rounded once to bf16), hence the same tolerances."""
+    B, H, Sq, Sk, D, causal, use_len, use_mask, clamp = case
+    q, k, v, do = make_case(B, H, Sq, Sk, D, 700, 0.5 if storage == "bf16" else 1.0)
+    qr, kr, vr, dor = bf16_round(q), bf16_round(k), bf16_round(v), bf16_round(do)
+    L = np.random.default_rng(8).integers(1, Sk + 1, size=B).astype(np.int32) if use_len else None
+    m = keep_mask(B, Sq, Sk, 9, 0.8, dead_rows=((0, 3),)) if use_mask else None
+    sc = 1.0 / math.sqrt(D)
+    o_ref, lse_ref = oracle.attn_fwd(qr, kr, vr, sc, causal, m, L, clamp)
+    ref = oracle.attn_bwd(qr, kr, vr, dor, sc, causal, m, L, clamp)
+    dt = torch.bfloat16 if storage == "bf16" else torch.float32
+    tq, tk, tv, tdo = dev(q, dt), dev(k, dt), dev(v, dt), dev(do, dt)
+    dL = torch.from_numpy(L).cuda() if L is not None else None
+    dm = dev(m) if m is not None else None
+    kw = dict(scale=sc, causal=causal, kv_len=dL, keep_mask=dm, score_clamp=clamp, mode=_lib.MODE_BF16)
+    if D != 128:
+        assert ctx.uses_tensor_pipe(tq, tk, tv, causal=causal, mode=_lib.MODE_BF16)
+    assert ctx.uses_tensor_pipe(tq, tk, tv, causal=causal, mode=_lib.MODE_BF16, backward=True)
+    o, lse = ctx.attn_fwd(tq, tk, tv, **kw)
+    got = ctx.attn_bwd(tq, tk, tv, o, lse, tdo, **kw)
+    again = ctx.attn_bwd(tq, tk, tv, o, lse, tdo, **kw)
+    torch.cuda.synchronize()
+    assert ctx.device_status() == 0
+    half_ulp = 2.0 ** -8 if storage == "bf16" else 0.0
+    oh = o.float().cpu().numpy().astype(np.float64)
+    assert (np.abs(oh - o_ref) <= TC_MAX_ABS + np.abs(o_ref) * half_ulp).all(), np.abs(oh - o_ref).max()
+    assert rel_l2(oh, o_ref) < TC_REL_L2 + half_ulp / 2
+    lse_h = lse.cpu().numpy().astype(np.float64)
+    fin = np.isfinite(lse_ref)
+    assert (np.isfinite(lse_h) == fin).all()
+    assert max_abs(lse_h[fin], lse_ref[fin]) < 2e-3
+    for name, g, g2, r in zip(("dq", "dk", "dv"), got, again, ref):
+        assert torch.equal(g, g2), f"{name}: two runs differ"
+        gh = g.float().cpu().numpy().astype(np.float64)
+        mag = max(1.0, float(np.abs(r).max()))
+        assert (np.abs(gh - r) <= TC_MAX_ABS * mag + np.abs(r) * half_ulp).all(), name
+        assert rel_l2(gh, r) < 2 * (TC_REL_L2 + half_ulp / 2), f"{name}: rel-L2 {rel_l2(gh, r)}"
 
 
 def test_host_step_pipeline_matches_direct_calls(ctx):

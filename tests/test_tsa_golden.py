@@ -289,6 +289,20 @@ def test_cuda_module_materialised_score_path(ctx, case):
         gh = g.cpu().numpy().astype(np.float64)
         assert rel_l2(gh, r) < MODULE_GRAD_REL_L2, f"{name}: rel-L2 {rel_l2(gh, r)}"
         assert np.abs(gh - r).max() < MODULE_MAX_ABS * max(1.0, np.abs(r).max()), name
+    # A forward that keeps its intermediates, then two backward calls from the same block (the reference's
+    # caller runs backwardWeights and then backward after one forward): both equal the recomputing call,
+    # so the first one left the kept probabilities as it found them.
+    saved = ctx.tsa_saved_buffer(*args, B, S, H, W, mode=mode, causal=causal)
+    out_kept = ctx.tsa_fwd(*args, B, S, H, W, gamma=dev(gamma), beta=dev(beta), bq=dev(bq), bk=dev(bk), bv=dev(bv),
+                           saved=saved, **kw)
+    assert torch.equal(out_kept, out)
+    for _ in range(2):
+        kept = ctx.tsa_bwd(*args, dev(dy), B, S, H, W, bq=dev(bq), bk=dev(bk), bv=dev(bv), saved=saved,
+                           reuse_forward=True, **kw)
+        for name, g, g2 in zip(("dx", "dwq", "dwk", "dwv", "dwo"), got, kept):
+            assert torch.equal(g, g2), f"{name}: kept forward differs from the recomputed one"
+    torch.cuda.synchronize()
+    assert ctx.device_status() == 0
 
 
 @pytest.mark.gpu
