@@ -63,6 +63,7 @@ class TsaParams(C.Structure):
         ("dbq", C.c_void_p), ("dbk", C.c_void_p), ("dbv", C.c_void_p), ("dbo", C.c_void_p),
         ("dgamma", C.c_void_p), ("dbeta", C.c_void_p),
         ("saved", C.c_void_p), ("saved_bytes", C.c_size_t), ("reuse_forward", C.c_int32),
+        ("weight_cache", C.c_void_p), ("weight_cache_bytes", C.c_size_t), ("weight_cache_valid", C.c_int32),
     ]
 
 
@@ -87,6 +88,7 @@ EXPORTS = {
     "ltca_attn_decode_static": (C.c_int, [C.c_void_p, C.POINTER(AttnParams), C.c_char_p, C.c_size_t]),
     "ltca_tsa_bwd": (C.c_int, [C.c_void_p, C.POINTER(TsaParams)]),
     "ltca_tsa_saved_bytes": (C.c_int, [C.POINTER(TsaParams), C.POINTER(C.c_size_t)]),
+    "ltca_tsa_weight_cache_bytes": (C.c_int, [C.POINTER(TsaParams), C.POINTER(C.c_size_t)]),
     "ltca_tsa_workspace_bytes": (C.c_int, [C.POINTER(TsaParams), C.c_int, C.POINTER(C.c_size_t)]),
     "ltca_tsa_fwd": (C.c_int, [C.c_void_p, C.POINTER(TsaParams)]),
     "ltca_tsa_bwd_data": (C.c_int, [C.c_void_p, C.POINTER(TsaParams)]),

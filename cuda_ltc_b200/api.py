@@ -287,12 +287,28 @@ class Context:
         self.check(self.lib.ltca_tsa_saved_bytes(C.byref(p), C.byref(need)))
         return torch.empty(need.value, dtype=torch.uint8, device=x.device)
 
+    def tsa_weight_cache(self, x, wq, wk, wv, wo, B, S, H, head_width, mode=_lib.MODE_AUTO, causal=False):
+        """A buffer for the reduced-precision copies of the weights (``ltca_tsa_params.weight_cache``): pass it as
+        ``weight_cache=(buffer, False)`` to the first call and ``(buffer, True)`` while the weights stay unchanged."""
+        p = self._tsa_params(x, wq, wk, wv, wo, B, S, H, head_width, 1.0, causal, False, False, False, None, None,
+                             None, mode, (None, None, None, None))
+        need = C.c_size_t(0)
+        self.check(self.lib.ltca_tsa_weight_cache_bytes(C.byref(p), C.byref(need)))
+        return torch.empty(max(need.value, 1), dtype=torch.uint8, device=x.device)
+
+    @staticmethod
+    def _attach_weight_cache(p, weight_cache):
+        if weight_cache is not None:
+            buf, valid = weight_cache
+            p.weight_cache, p.weight_cache_bytes, p.weight_cache_valid = buf.data_ptr(), buf.numel(), int(valid)
+
     def tsa_fwd(self, x, wq, wk, wv, wo, B, S, H, head_width, scale=1.0, causal=False, time_major=True,
                 use_residual=True, use_layer_norm=True, gamma=None, beta=None, keep_mask=None,
-                mode=_lib.MODE_AUTO, bq=None, bk=None, bv=None, bo=None, saved=None):
+                mode=_lib.MODE_AUTO, bq=None, bk=None, bv=None, bo=None, saved=None, weight_cache=None):
         """out = LayerNorm(x + MHA(x)); x [B*S, E] fp32, weights as in ``ltca_tsa_params``."""
         p = self._tsa_params(x, wq, wk, wv, wo, B, S, H, head_width, scale, causal, time_major,
                              use_residual, use_layer_norm, gamma, beta, keep_mask, mode, (bq, bk, bv, bo))
+        self._attach_weight_cache(p, weight_cache)
         if saved is not None:
             p.saved, p.saved_bytes = saved.data_ptr(), saved.numel()
         out = torch.empty_like(x)
@@ -303,10 +319,12 @@ class Context:
         return out
 
     def tsa_bwd(self, x, wq, wk, wv, wo, dy, B, S, H, head_width, scale=1.0, causal=False, time_major=True,
-                keep_mask=None, mode=_lib.MODE_AUTO, bq=None, bk=None, bv=None, saved=None, reuse_forward=False):
+                keep_mask=None, mode=_lib.MODE_AUTO, bq=None, bk=None, bv=None, saved=None, reuse_forward=False,
+                weight_cache=None):
         """(dx, dwq, dwk, dwv, dwo) of the module; LayerNorm and residual pass dy through."""
         p = self._tsa_params(x, wq, wk, wv, wo, B, S, H, head_width, scale, causal, time_major,
                              False, False, None, None, keep_mask, mode, (bq, bk, bv, None))
+        self._attach_weight_cache(p, weight_cache)
         if saved is not None:
             p.saved, p.saved_bytes, p.reuse_forward = saved.data_ptr(), saved.numel(), int(reuse_forward)
         dx = torch.empty_like(x)

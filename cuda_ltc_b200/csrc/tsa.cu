@@ -465,6 +465,15 @@ int check(ltca_ctx* ctx, const ltca_tsa_params* t) {
         if (t->saved_bytes < need)
             return fail(ctx, LTCA_ERR_WORKSPACE, "the saved block needs %zu bytes", need);
     }
+    if (t->weight_cache) {
+        if (reinterpret_cast<uintptr_t>(t->weight_cache) & 255)
+            return fail(ctx, LTCA_ERR_INVALID, "weight_cache must be 256-byte aligned");
+        size_t need = 0;
+        int rc = ltca_tsa_weight_cache_bytes(t, &need);
+        if (rc) return fail(ctx, rc, "bad shape for the weight cache");
+        if (t->weight_cache_bytes < need)
+            return fail(ctx, LTCA_ERR_WORKSPACE, "the weight cache needs %zu bytes", need);
+    }
     return LTCA_OK;
 }
 
@@ -505,6 +514,10 @@ void fill_attn_bf16(const ltca_tsa_params* t, ltca_attn_params* a) {
     a->dtype = LTCA_BF16;
     a->mode = LTCA_MODE_BF16;
 }
+
+// A forward that leaves something for the backward (its intermediates, or the weights' copies) takes the pipeline
+// the backward will take, so that both calls agree on what the blocks hold.
+bool keeps_for_backward(const ltca_tsa_params* t) { return t->saved != nullptr || t->weight_cache != nullptr; }
 
 // Whether the attention core of the tensor pipeline is the materialised-score path (attn_wide_sm100.cu): head
 // widths the streaming kernels do not cover.  Taken for heads wider than 128 (the reference's configuration gives
@@ -658,16 +671,29 @@ int tensor_forward_core(ltca_ctx* ctx, const ltca_tsa_params* t, const TPlan& pl
         }
     }
     tb->rest = r;
+    // the weights' copies live in the caller's cache when there is one
+    const bool cached = t->weight_cache != nullptr;
+    if (cached) {
+        char* c = reinterpret_cast<char*>(t->weight_cache);
+        tb->wq = c;  c += pl.w_in;
+        tb->wk = c;  c += pl.w_in;
+        tb->wv = c;  c += pl.w_in;
+        tb->wo = c;  c += pl.w_out;
+        if (pl.wide) { tb->wql = c; c += pl.w_in; tb->wkl = c; c += pl.w_in; }
+    }
+    const bool convert_weights = !(cached && t->weight_cache_valid);
     if (saved && t->reuse_forward) return LTCA_OK;
     const int E = t->E, HW = pl.HW, Ep = pl.Ep;
     int rc;
     if (pl.wide) {
         // Two-term operands for the products whose rounding would reach the scores: x, Wq, Wk here, q and k below.
         if ((rc = wide_split_bf16(ctx, t->x, E, tb->xb, tb->xl, Ep, pl.rows, E))) return rc;
-        if ((rc = wide_split_bf16(ctx, t->wq, HW, tb->wq, tb->wql, HW, E, HW))) return rc;
-        if ((rc = wide_split_bf16(ctx, t->wk, HW, tb->wk, tb->wkl, HW, E, HW))) return rc;
-        if ((rc = wide_split_bf16(ctx, t->wv, HW, tb->wv, nullptr, HW, E, HW))) return rc;
-        if ((rc = wide_split_bf16(ctx, t->wo, E, tb->wo, nullptr, Ep, HW, E))) return rc;
+        if (convert_weights) {
+            if ((rc = wide_split_bf16(ctx, t->wq, HW, tb->wq, tb->wql, HW, E, HW))) return rc;
+            if ((rc = wide_split_bf16(ctx, t->wk, HW, tb->wk, tb->wkl, HW, E, HW))) return rc;
+            if ((rc = wide_split_bf16(ctx, t->wv, HW, tb->wv, nullptr, HW, E, HW))) return rc;
+            if ((rc = wide_split_bf16(ctx, t->wo, E, tb->wo, nullptr, Ep, HW, E))) return rc;
+        }
         const void* whi[2] = {tb->wq, tb->wk};
         const void* wlo[2] = {tb->wql, tb->wkl};
         void* ohi[2] = {tb->q, tb->k};
@@ -705,7 +731,7 @@ int tensor_forward_core(ltca_ctx* ctx, const ltca_tsa_params* t, const TPlan& pl
         return wide_attn_fwd(ctx, wa);
     }
     if ((rc = convert_rows_bf16(ctx, t->x, E, tb->xb, Ep, pl.rows, E))) return rc;
-    {
+    if (convert_weights) {
         const float* src[4] = {t->wq, t->wk, t->wv, t->wo};
         void* dst[4] = {tb->wq, tb->wk, tb->wv, tb->wo};
         const int64_t ld_src[4] = {HW, HW, HW, E}, ld_dst[4] = {HW, HW, HW, Ep}, nrows[4] = {E, E, E, HW};
@@ -738,7 +764,7 @@ int tensor_forward_core(ltca_ctx* ctx, const ltca_tsa_params* t, const TPlan& pl
 int tensor_forward(ltca_ctx* ctx, const ltca_tsa_params* t) {
     TPlan pl;
     int rc;
-    if ((rc = make_tplan(t, &pl, t->saved != nullptr))) return rc;
+    if ((rc = make_tplan(t, &pl, keeps_for_backward(t)))) return rc;
     const size_t need = tensor_workspace(pl, 0);
     if (!t->workspace || t->workspace_bytes < need)
         return fail(ctx, LTCA_ERR_WORKSPACE, "forward needs %zu bytes of workspace", need);
@@ -870,9 +896,9 @@ extern "C" {
 
 // Workspace of the TimeSelfAttention form (no input LayerNorm, no dropout), without the column-sum scratch.
 static int inner_workspace(const ltca_tsa_params* t, int which, size_t* bytes_out) {
-    if (use_tensor(t, which != 0 || t->saved != nullptr)) {
+    if (use_tensor(t, which != 0 || keeps_for_backward(t))) {
         TPlan tp;
-        int trc = make_tplan(t, &tp, which != 0 || t->saved != nullptr);
+        int trc = make_tplan(t, &tp, which != 0 || keeps_for_backward(t));
         if (trc) return trc;
         *bytes_out = tensor_workspace(tp, which);
         return LTCA_OK;
@@ -923,6 +949,18 @@ int ltca_tsa_saved_bytes(const ltca_tsa_params* t, size_t* bytes_out) {
     int rc = make_plan(&probe, &pl);
     if (rc) return rc;
     *bytes_out = 4 * pl.buf + pl.lse;
+    return LTCA_OK;
+}
+
+int ltca_tsa_weight_cache_bytes(const ltca_tsa_params* t, size_t* bytes_out) {
+    if (!t || !bytes_out) return LTCA_ERR_INVALID;
+    *bytes_out = 0;
+    // the cache serves the pipeline that the backward takes, which a forward with a cache takes too
+    if (!use_tensor(t, true)) return LTCA_OK;
+    TPlan tp;
+    int rc = make_tplan(t, &tp, true);
+    if (rc) return rc;
+    *bytes_out = 3 * tp.w_in + tp.w_out + (tp.wide ? 2 * tp.w_in : 0);
     return LTCA_OK;
 }
 
@@ -1045,7 +1083,7 @@ int ltca_tsa_fwd(ltca_ctx* ctx, const ltca_tsa_params* t) {
     if (t->dropout_prob < 0.f || t->dropout_prob >= 1.f)
         return fail(ctx, LTCA_ERR_INVALID, "dropout_prob must be in [0, 1)");
     if (t->pre_norm) return prenorm_forward(ctx, t);
-    if (use_tensor(t, t->saved != nullptr)) return tensor_forward(ctx, t);
+    if (use_tensor(t, keeps_for_backward(t))) return tensor_forward(ctx, t);
     Plan pl;
     if ((rc = make_plan(t, &pl))) return rc;
     size_t need = 0;

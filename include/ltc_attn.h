@@ -100,7 +100,8 @@ typedef struct {
      * key blocks' shares of dQ are added into an fp32 accumulator by the memory system in no fixed order, so
      * two runs can differ in dQ by fp32 rounding (dK and dV are bit-identical).  1: the two-kernel path, every
      * gradient bit-identical from run to run (the reference pins backward repeatability at 1e-6,
-     * src/ml/time_self_attention_test.cu:799-838) at about 1.4 x the time.  The workspace size depends on it. */
+     * src/ml/time_self_attention_test.cu:799-838) at about 1.25 x the time for long sequences.  The workspace
+     * size depends on it. */
     int32_t bwd_deterministic;
 } ltca_attn_params;
 
@@ -258,10 +259,24 @@ typedef struct {
     void*   saved;
     size_t  saved_bytes;
     int32_t reuse_forward;
+    /* Optional: keep the reduced-precision copies of the four weight matrices across calls.  The tensor-pipe
+     * pipelines round wq, wk, wv, wo to bf16 (the materialised-score path also splits wq and wk into two terms)
+     * at the start of every call; the reference's module never changes its projection weights after
+     * construction or loadWeights (getParameters exposes the LayerNorm pair only,
+     * src/ml/cudnn_time_self_attention.cu:436-450), so a caller can keep the copies.  With weight_cache set
+     * (ltca_tsa_weight_cache_bytes, 256-byte aligned) a call with weight_cache_valid = 0 writes the copies there
+     * and uses them; a call with weight_cache_valid = 1 uses them as they are and does not read wq..wo for the
+     * projections.  The caller clears the flag whenever the weights, the shape, the head width or the mode
+     * change.  Ignored by the exact pipeline. */
+    void*   weight_cache;
+    size_t  weight_cache_bytes;
+    int32_t weight_cache_valid;
 } ltca_tsa_params;
 
 /* Size of the `saved` block for this shape and mode. */
 int ltca_tsa_saved_bytes(const ltca_tsa_params* p, size_t* bytes_out);
+/* Size of the `weight_cache` block for this shape and mode (0 where the call would not use one). */
+int ltca_tsa_weight_cache_bytes(const ltca_tsa_params* p, size_t* bytes_out);
 
 /* which: 0 forward, 1 backward-data, 2 backward-weights, 3 both backward passes. */
 int ltca_tsa_workspace_bytes(const ltca_tsa_params* p, int which, size_t* bytes_out);

@@ -196,6 +196,13 @@ public:
     // Off (default): the mask argument is ignored, as in the reference.  On: dense keep-mask, 0 hides the key.
     void setHonourMask(bool on) { honour_mask_ = on; }
 
+    // Extension.  The tensor-pipe pipelines round the four projection matrices to bf16 at the start of every
+    // call.  With this switch on the copies are kept between calls; a caller that changes the matrices behind
+    // the class's back (an optimizer working on getParameters()) calls weightsChanged() after every update.
+    // loadWeights() does so itself.
+    void setKeepWeightCopies(bool on) { keep_weight_copies_ = on; weight_copies_valid_ = false; }
+    void weightsChanged() { weight_copies_valid_ = false; }
+
     CudaMemory<float> backward(const CudaMemory<float>& grad_output, const CudaMemory<float>& x_seq,
                                int batch_size, int seq_len, const CudaMemory<float>* mask = nullptr,
                                cudaStream_t stream = nullptr) override {
@@ -276,6 +283,7 @@ public:
         if (magic != 0x43444E4E || version != 1 || nbytes != want)
             throw std::runtime_error("Weight file does not match this module: " + filepath);
         for (CudaMemory<float>* w : {&wq_, &wk_, &wv_, &wo_}) read_tensor(f, *w);
+        weight_copies_valid_ = false;
         if (f.fail()) throw std::runtime_error("Failed to read weights from file: " + filepath);
         std::ifstream g(filepath + ".layernorm", std::ios::binary);
         if (g.is_open()) { read_tensor(g, ln_gamma_); read_tensor(g, ln_beta_); }
@@ -308,13 +316,27 @@ private:
     }
     template <typename Fn>
     void run(ltca_tsa_params& p, int which, cudaStream_t stream, Fn fn, const char* what) {
+        ltca_ctx* ctx = ctx_.get(stream);
+        if (keep_weight_copies_) {              // before the workspace query: a call with a cache may take another pipeline
+            size_t wneed = 0;
+            b200::check(ctx, ltca_tsa_weight_cache_bytes(&p, &wneed), "ltca_tsa_weight_cache_bytes");
+            if (wneed > weight_copies_.bytes()) {
+                weight_copies_ = CudaMemory<float>((wneed + 3) / 4, stream);
+                weight_copies_valid_ = false;
+            }
+            if (wneed) {
+                p.weight_cache = weight_copies_.get();
+                p.weight_cache_bytes = weight_copies_.bytes();
+                p.weight_cache_valid = weight_copies_valid_ ? 1 : 0;
+            }
+        }
         size_t need = 0;
         ltca_tsa_workspace_bytes(&p, which, &need);
         if (need > workspace_.bytes()) workspace_ = CudaMemory<float>((need + 3) / 4, stream);
         p.workspace = workspace_.get();
         p.workspace_bytes = workspace_.bytes();
-        ltca_ctx* ctx = ctx_.get(stream);
         b200::check(ctx, fn(ctx, &p), what);
+        if (p.weight_cache) weight_copies_valid_ = true;
     }
     void ensure_gradients(cudaStream_t stream) {
         if (dwq_.size() == wq_.size() && dwq_.size() != 0) return;
@@ -343,6 +365,8 @@ private:
     CudaMemory<float> dwq_, dwk_, dwv_, dwo_, dgamma_, dbeta_;
     CudaMemory<float> workspace_;
     bool reuse_forward_ = false;
+    bool keep_weight_copies_ = false, weight_copies_valid_ = false;
+    CudaMemory<float> weight_copies_;
     bool honour_mask_ = false;
     CudaMemory<float> saved_;
     const float* saved_x_ = nullptr;

@@ -239,6 +239,10 @@ TC_BWD_CASES = [
     (1, 2, 200, 200, True, False, True, 5.0),
     (1, 2, 515, 130, True, False, False, 0.0),      # early queries see no key at all
     (32, 8, 256, 256, True, False, False, 0.0),     # config 2 core
+    # longer query ranges with every kind of mask
+    (1, 2, 640, 640, True, False, True, 5.0),       # dense mask and clamp
+    (2, 2, 600, 515, True, True, False, 0.0),       # key lengths, causal, more queries than keys
+    (2, 3, 769, 769, True, False, False, 0.0),      # ragged edges
 ]
 
 

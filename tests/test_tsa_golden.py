@@ -306,6 +306,47 @@ def test_cuda_module_materialised_score_path(ctx, case):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("form", ["compact", "reference"])
+def test_kept_weight_copies_give_the_same_bits(ctx, form):
+    """``weight_cache``: the first call writes the weights' reduced-precision copies into the caller's block, later
+    calls run from them; outputs and gradients equal the converting calls bit for bit.  When the weights change and
+    the caller clears the flag, the block follows; if the caller leaves it set, the stale copies are what is used
+    (that is the contract)."""
+    import torch
+    from cuda_ltc_b200 import _lib
+    from cuda_ltc_b200.api import LtcaError
+    if form == "compact":
+        B, S, E, H, W, kw = 4, 64, 128, 2, 64, dict(scale=0.125, causal=True, time_major=False, mode=_lib.MODE_BF16)
+    else:
+        B, S, E, H, W, kw = 2, 24, 256, 2, 256, dict(scale=1.0, causal=False, time_major=True, mode=_lib.MODE_AUTO)
+    g = torch.Generator(device="cuda").manual_seed(5)
+    rnd = lambda *shape: torch.randn(shape, generator=g, device="cuda")
+    x, dy = 0.5 * rnd(B * S, E), rnd(B * S, E)
+    ws = [0.05 * rnd(E, H * W) for _ in range(3)]
+    wo = 0.05 * rnd(H * W, E)
+    gamma, beta = torch.ones(E, device="cuda"), torch.zeros(E, device="cuda")
+    plain_out = ctx.tsa_fwd(x, *ws, wo, B, S, H, W, gamma=gamma, beta=beta, **kw)
+    plain = ctx.tsa_bwd(x, *ws, wo, dy, B, S, H, W, **kw)
+    cache = ctx.tsa_weight_cache(x, *ws, wo, B, S, H, W, mode=kw["mode"], causal=kw["causal"])
+    assert cache.numel() > 1
+    for valid in (False, True, True):
+        out = ctx.tsa_fwd(x, *ws, wo, B, S, H, W, gamma=gamma, beta=beta, weight_cache=(cache, valid), **kw)
+        got = ctx.tsa_bwd(x, *ws, wo, dy, B, S, H, W, weight_cache=(cache, True), **kw)
+        assert torch.equal(out, plain_out)
+        for a, b in zip(got, plain):
+            assert torch.equal(a, b)
+    ws2 = [w * 1.5 for w in ws]
+    new_out = ctx.tsa_fwd(x, *ws2, wo, B, S, H, W, gamma=gamma, beta=beta, **kw)
+    stale = ctx.tsa_fwd(x, *ws2, wo, B, S, H, W, gamma=gamma, beta=beta, weight_cache=(cache, True), **kw)
+    fresh = ctx.tsa_fwd(x, *ws2, wo, B, S, H, W, gamma=gamma, beta=beta, weight_cache=(cache, False), **kw)
+    assert torch.equal(stale, plain_out) and torch.equal(fresh, new_out) and not torch.equal(new_out, plain_out)
+    with pytest.raises(LtcaError):                       # a block that is too small is refused
+        ctx.tsa_fwd(x, *ws, wo, B, S, H, W, gamma=gamma, beta=beta, weight_cache=(cache[:256], False), **kw)
+    torch.cuda.synchronize()
+    assert ctx.device_status() == 0
+
+
+@pytest.mark.gpu
 @pytest.mark.parametrize("path", [c for c in CASES if int(np.load(c)["E"]) % 8 == 0])
 def test_materialised_score_path_matches_reference_cudnn_module(ctx, path):
     """The same path against the reference's own cuDNN module (golden vectors), at the 2e-2 of the largest
