@@ -34,11 +34,20 @@ namespace ltca {
 namespace {
 
 constexpr int kBM = 128, kBN = 256, kBK = 64;
+#ifdef LTCA_X_GEMM_STAGES
+constexpr int kStages = LTCA_X_GEMM_STAGES;
+#else
 constexpr int kStages = 3;                         // operand ring: 3 x (16 KB of A + 32 KB of B)
+#endif
 constexpr int kATileBytes = kBM * kBK * 2;         // 16 KB
 constexpr int kBTileBytes = kBN * kBK * 2;         // 32 KB
 constexpr int kStageBytes = kATileBytes + kBTileBytes;
-constexpr int kStageOutBytes = kBM * 128 * 4;      // 64 KB: the result tile leaves in pieces of 128 fp32 / 256 bf16 columns
+#ifdef LTCA_X_GEMM_OUTBOXES
+constexpr int kStageBoxes = LTCA_X_GEMM_OUTBOXES;
+#else
+constexpr int kStageBoxes = 4;                     // 128-row boxes of 128 bytes (64 bf16 or 32 fp32 columns) per piece
+#endif
+constexpr int kStageOutBytes = kBM * 128 * kStageBoxes;   // 64 KB: the result tile leaves in pieces of 128 fp32 / 256 bf16 columns
 constexpr int kGemmThreads = 192;
 constexpr int kOutOff = kStages * kStageBytes;
 constexpr int kBarOff = kOutOff + kStageOutBytes;
@@ -231,7 +240,9 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap ta0, const __grid_con
             // clips rows and columns past the end of C.  (Storing a row's 16-byte pieces straight from registers
             // costs 32 L1 wavefronts per instruction, about as many cycles per tile as its MMAs.)
             // With a second term the piece is 128 columns of each: the high-order boxes, then the low-order ones.
-            const int piece_cols = (staged && (!g.out_bf16 || g.c_lo)) ? 128 : kBN;
+            // boxes of C per piece: all of the staging area, or half of it when the low-order term takes the other half
+            const int piece_boxes = g.c_lo ? kStageBoxes / 2 : kStageBoxes;
+            const int piece_cols = staged ? piece_boxes * box_cols : kBN;
             for (int p0 = 0; p0 < kBN; p0 += piece_cols) {
                 if (staged) {
                     // the previous piece's boxes have been read: the storing thread waits for that before it comes here
@@ -283,7 +294,7 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap ta0, const __grid_con
                                                       __uint_as_float(v[8 * c + 5]) - __uint_as_float(w.z & 0xffff0000u));
                                     l.w = pack_bf16x2(__uint_as_float(v[8 * c + 6]) - __uint_as_float(w.w << 16),
                                                       __uint_as_float(v[8 * c + 7]) - __uint_as_float(w.w & 0xffff0000u));
-                                    *reinterpret_cast<uint4*>(box + 2 * (kBM * 128) + (((ch0 + c) ^ (row & 7)) << 4)) = l;
+                                    *reinterpret_cast<uint4*>(box + piece_boxes * (kBM * 128) + (((ch0 + c) ^ (row & 7)) << 4)) = l;
                                 }
                             }
                         } else {
@@ -340,7 +351,7 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap ta0, const __grid_con
                             if (t.n0 + p0 + bx * box_cols < g.N) {
                                 tma_store_4d(tc, stage_addr + bx * (kBM * 128), t.n0 + p0 + bx * box_cols, t.m0, t.bh, t.bb);
                                 if (g.c_lo)
-                                    tma_store_4d(&tc1, stage_addr + (2 + bx) * (kBM * 128), t.n0 + p0 + bx * box_cols,
+                                    tma_store_4d(&tc1, stage_addr + (piece_boxes + bx) * (kBM * 128), t.n0 + p0 + bx * box_cols,
                                                  t.m0, t.bh, t.bb);
                             }
                         tma_store_commit();
