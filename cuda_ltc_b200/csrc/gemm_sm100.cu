@@ -14,7 +14,7 @@
 // so no operand is ever transposed in memory: the instruction descriptor's major bits select the
 // form and the shared-memory descriptors follow the layout the TMA boxes produce.
 //
-// Persistent CTAs (one per SM) walk a list of 128 x 256 tiles of C: warp 0 is the TMA producer (ring of three
+// Persistent CTAs (one per SM) walk a list of 128 x 256 tiles of C: warp 0 is the TMA producer (ring of four
 // 48 KB (A, B) stages), warp 1 issues the MMAs (M128 N256 K16) into one of two 256-column accumulators in tensor
 // memory, warps 2-5 are the epilogue (one accumulator row per thread: tcgen05.ld, bias, convert; the tile is
 // staged in shared memory as 128-byte-swizzled boxes and stored with TMA), which works on tile i while the MMAs
@@ -34,20 +34,14 @@ namespace ltca {
 namespace {
 
 constexpr int kBM = 128, kBN = 256, kBK = 64;
-#ifdef LTCA_X_GEMM_STAGES
-constexpr int kStages = LTCA_X_GEMM_STAGES;
-#else
-constexpr int kStages = 3;                         // operand ring: 3 x (16 KB of A + 32 KB of B)
-#endif
+constexpr int kStages = 4;                         // operand ring: 4 x (16 KB of A + 32 KB of B)
 constexpr int kATileBytes = kBM * kBK * 2;         // 16 KB
 constexpr int kBTileBytes = kBN * kBK * 2;         // 32 KB
 constexpr int kStageBytes = kATileBytes + kBTileBytes;
-#ifdef LTCA_X_GEMM_OUTBOXES
-constexpr int kStageBoxes = LTCA_X_GEMM_OUTBOXES;
-#else
-constexpr int kStageBoxes = 4;                     // 128-row boxes of 128 bytes (64 bf16 or 32 fp32 columns) per piece
-#endif
-constexpr int kStageOutBytes = kBM * 128 * kStageBoxes;   // 64 KB: the result tile leaves in pieces of 128 fp32 / 256 bf16 columns
+// The result tile leaves in pieces of two 128-row boxes of 128 bytes: 128 bf16 or 64 fp32 columns (a fourth ring
+// stage and 32 KB of staging measured 4 - 6 % faster at the module's sizes than three stages and 64 KB).
+constexpr int kStageBoxes = 2;
+constexpr int kStageOutBytes = kBM * 128 * kStageBoxes;
 constexpr int kGemmThreads = 192;
 constexpr int kOutOff = kStages * kStageBytes;
 constexpr int kBarOff = kOutOff + kStageOutBytes;
@@ -234,13 +228,12 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap ta0, const __grid_con
             const uint32_t tacc = tmem_base + (uint32_t)kBN * buf + ((uint32_t)(qd * 32) << 16);
             const float* bias = (g.ksplit == 1) ? g.bias[t.problem] : nullptr;
             const bool staged = g.tma_store && g.ksplit == 1;
-            // The tile leaves in pieces that fit the 64 KB staging area: all 256 bf16 columns at once, or two
-            // pieces of 128 fp32 columns.  A piece goes to shared memory in the layout of 128-byte swizzled TMA
-            // boxes - 64 bf16 or 32 fp32 columns wide, 128 rows - and one thread stores the boxes; the tensor map
-            // clips rows and columns past the end of C.  (Storing a row's 16-byte pieces straight from registers
-            // costs 32 L1 wavefronts per instruction, about as many cycles per tile as its MMAs.)
-            // With a second term the piece is 128 columns of each: the high-order boxes, then the low-order ones.
-            // boxes of C per piece: all of the staging area, or half of it when the low-order term takes the other half
+            // The tile leaves in pieces that fit the staging area (kStageBoxes boxes).  A piece goes to shared
+            // memory in the layout of 128-byte swizzled TMA boxes - 64 bf16 or 32 fp32 columns wide, 128 rows - and
+            // one thread stores the boxes; the tensor map clips rows and columns past the end of C.  (Storing a
+            // row's 16-byte pieces straight from registers costs 32 L1 wavefronts per instruction, about as many
+            // cycles per tile as its MMAs.)  With a second term half of the boxes take the high-order part of the
+            // piece and the other half the low-order part.
             const int piece_boxes = g.c_lo ? kStageBoxes / 2 : kStageBoxes;
             const int piece_cols = staged ? piece_boxes * box_cols : kBN;
             for (int p0 = 0; p0 < kBN; p0 += piece_cols) {

@@ -405,7 +405,9 @@ __device__ __forceinline__ void item_counters_release(int* counters) {
 }
 
 // The item list of a persistent kernel: nblk row blocks for each of BH (batch, head) pairs.
-struct ItemGrid { int nblk, H, BH, n_items; int* counters; };
+// fold (forward kernel only): an item takes two tiles from the start and the two that mirror them at the end of the
+// block range instead of four neighbours, see attn_fwd4p_sm100_kernel.
+struct ItemGrid { int nblk, H, BH, n_items; int* counters; int fold = 0; };
 
 // Entry `linear` of the grouped heavy-first order (see sched_block): rank 0 is the heaviest block.
 __device__ __forceinline__ void sched_item(const ItemGrid& g, int linear, int& rank, int& h, int& b) {
