@@ -186,11 +186,12 @@ public:
         return out;
     }
 
-    // Extension.  The reference's interface carries nothing from forward() to backward(), so its caller runs
-    // forward() again right before backward() (src/ml/ml_liquid_net.cu:715-721) and backward() here recomputes
-    // it once more.  With this switch on, forward() keeps its intermediates, and a backward() /
-    // backwardWeights() call for the same x_seq buffer, mask and shape uses them instead.  The caller promises
-    // that the contents of x_seq and the weights have not changed in between; any other call recomputes.
+    // forward() keeps its intermediates, and a backward() / backwardWeights() call for the same x_seq buffer, mask
+    // and shape starts from them, as the reference's module does with cuDNN's reserve space
+    // (src/ml/cudnn_time_self_attention.cu:254-302 hands the last forward's reserve_space_ to the backward calls;
+    // its caller runs forward() right before them, src/ml/ml_liquid_net.cu:715-721).  Like there, the contents of
+    // x_seq and the weights must not have changed in between; unlike there, a backward call for ANOTHER buffer,
+    // mask or shape is noticed and recomputes the forward.  Off: every backward call recomputes.
     void setReuseForward(bool on) { reuse_forward_ = on; if (!on) saved_x_ = nullptr; }
 
     // Off (default): the mask argument is ignored, as in the reference.  On: dense keep-mask, 0 hides the key.
@@ -364,7 +365,7 @@ private:
     CudaMemory<float> wq_, wk_, wv_, wo_, ln_gamma_, ln_beta_;
     CudaMemory<float> dwq_, dwk_, dwv_, dwo_, dgamma_, dbeta_;
     CudaMemory<float> workspace_;
-    bool reuse_forward_ = false;
+    bool reuse_forward_ = true;
     bool keep_weight_copies_ = false, weight_copies_valid_ = false;
     CudaMemory<float> weight_copies_;
     bool honour_mask_ = false;

@@ -24,14 +24,15 @@
 //       Prints one "CHECK <name> <value> <limit> PASS|FAIL" line per property; exit code 1 if any failed.
 //
 //   shim_driver time <B> <S> <E> <H> <iters>
-//       Wall-clock (host, every device synchronisation of the callee included) and CUDA-event milliseconds of
-//       forward, backwardWeights and backward, called as the reference's model calls them, for the reference's
-//       cuDNN module and for the binding in the reference's form (head width = E, scale 1, no mask; once
-//       recomputing the forward in each backward call and once with setReuseForward(true) and
-//       setKeepWeightCopies(true)) and in the compact
+//       Wall-clock (host, every device synchronisation of the callee included) and CUDA-event milliseconds
+//       (medians over 3 * iters rounds) of forward, backwardWeights and backward, called in the order in which
+//       the reference's model calls them, for the reference's
+//       cuDNN module and for the binding in the reference's form (head width = E, scale 1, no mask: as
+//       constructed, with setReuseForward(false), and with setKeepWeightCopies(true)) and in the compact
 //       form (head width E/H, scale 1/sqrt(width), causal).  One JSON line.
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <chrono>
 #include <cmath>
 #include <cstdio>
@@ -226,6 +227,7 @@ int run_checks(const std::string& out) {
         // kept forward and kept weight copies: the same bits as the recomputing calls, over two rounds (the second
         // round runs on the copies made by the first)
         {
+            impl->setReuseForward(false);
             std::vector<float> dx_plain = to_host(a->backward(gy, x, B, S));
             impl->setReuseForward(true);
             impl->setKeepWeightCopies(true);
@@ -237,7 +239,6 @@ int run_checks(const std::string& out) {
                 worst = std::max(worst, std::max(max_abs_diff(o_plain, o_kept), max_abs_diff(dx_plain, dx_kept)));
             }
             expect_le("kept_forward_and_weight_copies_same_bits", worst, 0.0);
-            impl->setReuseForward(false);
             impl->setKeepWeightCopies(false);
         }
         // the same numbers as a direct call of the C entry point on the module's own parameters
@@ -365,28 +366,30 @@ Timing time_module(TimeSelfAttention& m, const CudaMemory<float>& x, const CudaM
         else { CudaMemory<float> dx = m.backward(gy, x, B, S); }
     };
     try {
-        for (int w = 0; w < 2; ++w) { run(0); run(1); run(2); }          // forward -> backwardWeights -> backward
+        for (int w = 0; w < 10; ++w) { run(0); run(1); run(2); }         // forward -> backwardWeights -> backward
         cudaDeviceSynchronize();
-        double* wall[3] = {&t.fwd_wall, &t.bww_wall, &t.bwd_wall};
-        double* ev[3] = {&t.fwd_ev, &t.bww_ev, &t.bwd_ev};
-        // best of three rounds: every call allocates and frees its result (the interface returns it by value), and
-        // the allocator's cost varies from round to round on a fresh device
-        for (int which = 0; which < 3; ++which) {
-            for (int round = 0; round < 3; ++round) {
+        // The model's call order in every iteration, each call timed on its own; the median over the iterations
+        // is reported: every call allocates and frees its result (the interface returns it by value), and the
+        // allocator's cost jumps now and then on a fresh device.
+        std::vector<double> wall[3], ev[3];
+        for (int i = 0; i < 3 * iters; ++i) {
+            for (int which = 0; which < 3; ++which) {
                 cudaDeviceSynchronize();
                 const auto t0 = std::chrono::steady_clock::now();
                 cudaEventRecord(e0, nullptr);
-                for (int i = 0; i < iters; ++i) run(which);
+                run(which);
                 cudaEventRecord(e1, nullptr);
                 cudaDeviceSynchronize();
                 const auto t1 = std::chrono::steady_clock::now();
                 float ms = 0;
                 cudaEventElapsedTime(&ms, e0, e1);
-                const double w = std::chrono::duration<double, std::milli>(t1 - t0).count() / iters;
-                if (round == 0 || w < *wall[which]) *wall[which] = w;
-                if (round == 0 || ms / iters < *ev[which]) *ev[which] = ms / iters;
+                wall[which].push_back(std::chrono::duration<double, std::milli>(t1 - t0).count());
+                ev[which].push_back(ms);
             }
         }
+        auto median = [](std::vector<double>& v) { std::sort(v.begin(), v.end()); return v[v.size() / 2]; };
+        t.fwd_wall = median(wall[0]); t.bww_wall = median(wall[1]); t.bwd_wall = median(wall[2]);
+        t.fwd_ev = median(ev[0]); t.bww_ev = median(ev[1]); t.bwd_ev = median(ev[2]);
         t.ok = cudaGetLastError() == cudaSuccess;
     } catch (const std::exception& e) {
         t.note = e.what();
@@ -408,20 +411,24 @@ void print_timing(const char* key, const Timing& t, bool last) {
 int run_time(int B, int S, int E, int H, int iters) {
     const size_t n = (size_t)B * S * E;
     CudaMemory<float> x = to_device(random_host(n, 1)), gy = to_device(random_host(n, 2));
-    Timing tr, ts, tk, tc;
+    Timing tr, ts, tn, tk, tc;
     try {
         auto ref = TimeSelfAttention::create(E, H, true, true, 0.0f, 42);
         tr = time_module(*ref, x, gy, B, S, iters);
     } catch (const std::exception& e) { tr.note = e.what(); }
     try {
+        // as constructed: forward() keeps its intermediates for the two backward calls, which is what the cuDNN
+        // module does with its reserve space
         B200TimeSelfAttention shim(E, H, true, true, 0.0f, 42, false, false);
         ts = time_module(shim, x, gy, B, S, iters);
     } catch (const std::exception& e) { ts.note = e.what(); }
     try {
-        // the binding's extension: forward() keeps its intermediates for the two backward calls, which is what
-        // the cuDNN module does with its reserve space
         B200TimeSelfAttention shim(E, H, true, true, 0.0f, 42, false, false);
-        shim.setReuseForward(true);
+        shim.setReuseForward(false);        // every backward call recomputes the forward
+        tn = time_module(shim, x, gy, B, S, iters);
+    } catch (const std::exception& e) { tn.note = e.what(); }
+    try {
+        B200TimeSelfAttention shim(E, H, true, true, 0.0f, 42, false, false);
         shim.setKeepWeightCopies(true);     // the weights do not change between the timed calls
         tk = time_module(shim, x, gy, B, S, iters);
     } catch (const std::exception& e) { tk.note = e.what(); }
@@ -433,7 +440,8 @@ int run_time(int B, int S, int E, int H, int iters) {
            cudnn_ops::getCuDNNVersionString().c_str());
     print_timing("reference_cudnn_module", tr, false);
     print_timing("binding_reference_form", ts, false);
-    print_timing("binding_reference_form_kept_forward", tk, false);
+    print_timing("binding_reference_form_recomputing", tn, false);
+    print_timing("binding_reference_form_kept_weight_copies", tk, false);
     print_timing("binding_compact_causal_form", tc, true);
     printf("}\n");
     return 0;
