@@ -109,6 +109,13 @@ TC_CASES = [
     (32, 8, 256, 256, 64, True, False, False, 0.0),     # config 2 core
     (1, 2, 512, 512, 128, True, False, False, 0.0),
     (1, 1, 300, 300, 128, False, True, False, 0.0),
+    # causal launches with several 512-row blocks and fewer items than SMs: the folded tile mapping of the
+    # four-tile kernel (two early and two late query tiles per item)
+    (1, 2, 1100, 1100, 64, True, False, False, 0.0),    # nine tiles in three blocks: three padded tile slots
+    (2, 2, 2048, 2048, 64, True, False, False, 0.0),
+    (1, 3, 1536, 1000, 64, True, False, False, 0.0),    # more queries than keys: the early tiles see nothing
+    (1, 2, 1000, 1500, 64, True, True, False, 0.0),     # key lengths
+    (1, 2, 640, 640, 64, True, False, True, 5.0),       # dense mask and clamp
 ]
 
 
