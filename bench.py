@@ -252,15 +252,18 @@ def other_configs(torch, ctx, peaks):
     # config 1
     q, k, v = rn(2, 4, 64, 32), rn(2, 4, 64, 32), rn(2, 4, 64, 32)
     ms = _timed(torch, lambda: ctx.attn_fwd(q, k, v, mode=_lib.MODE_AUTO), flush=flush)
+    ms_split = _timed(torch, lambda: ctx.attn_fwd(q, k, v, mode=_lib.MODE_SPLIT), flush=flush)
     out["config1_fa_fwd_fp32_B2_H4_S64_D32"] = {
         "fwd_us": ms * 1e3, "bound": "launch latency (4.2 MFLOP, 256 KiB)",
-        "tensor_pipe": ctx.uses_tensor_pipe(q, k, v)}
+        "tensor_pipe": ctx.uses_tensor_pipe(q, k, v),
+        "split_precision_tensor_pipe_fwd_us": ms_split * 1e3}
     # config 2: attention core
     fl2 = flops_fwd(32, 8, 256, 64)
     q, k, v, do = (rn(32, 8, 256, 64) for _ in range(4))
     core = {}
     for name, mode, conv in (("fp32_storage_tensor_pipe", _lib.MODE_BF16, lambda t: t),
                              ("bf16_storage_tensor_pipe", _lib.MODE_BF16, lambda t: t.bfloat16()),
+                             ("fp32_storage_split_precision_tensor_pipe", _lib.MODE_SPLIT, lambda t: t),
                              ("fp32_storage_exact", _lib.MODE_FP32, lambda t: t)):
         qq, kk, vv, dd = (conv(t) for t in (q, k, v, do))
         o, lse = ctx.attn_fwd(qq, kk, vv, causal=True, mode=mode)

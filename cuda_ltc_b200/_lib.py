@@ -12,7 +12,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libltc_attn.so")
 
 LTCA_F32, LTCA_BF16 = 0, 1
-MODE_AUTO, MODE_BF16, MODE_FP32 = 0, 1, 3
+MODE_AUTO, MODE_BF16, MODE_SPLIT, MODE_FP32 = 0, 1, 2, 3
 
 STATUS_NAMES = {
     0: "LTCA_OK", -1: "LTCA_ERR_INVALID", -2: "LTCA_ERR_UNSUPPORTED", -3: "LTCA_ERR_CUDA",

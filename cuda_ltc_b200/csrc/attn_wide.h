@@ -16,7 +16,8 @@ struct WideArgs {
     const void* qh = nullptr; const void* ql = nullptr;     // Q and, optionally, its low-order part
     const void* kh = nullptr; const void* kl = nullptr;
     const void* v = nullptr;
-    ltca_strides qs{}, ks{}, vs{};
+    const void* vl = nullptr;                   // optional low-order part of V (same strides): O = P V, dP = dO V^T
+    ltca_strides qs{}, ks{}, vs{};              // and dK / dQ then run as three-term products as well
     void* o = nullptr; ltca_strides os{}; int o_bf16 = 1;   // forward result (null: probabilities only)
     float* lse = nullptr;                       // [B, H, Sq] natural-log sum-exp, optional
     float* scores = nullptr;                    // scratch fp32 [B*H, Sq, Skp]: raw Q K^T (kept for the backward's clamp test)
@@ -25,6 +26,7 @@ struct WideArgs {
                                                 // a single bf16 P would be the largest error left in an fp32 output
     // backward
     const void* dout = nullptr; ltca_strides dos{};
+    const void* doutl = nullptr;                // optional low-order part of dO (same strides)
     void *dq = nullptr, *dk = nullptr, *dv = nullptr;
     ltca_strides dqs{}, dks{}, dvs{};
     int grads_bf16 = 1;

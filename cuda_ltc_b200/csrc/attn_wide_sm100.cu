@@ -390,10 +390,13 @@ int wide_attn_fwd(ltca_ctx* ctx, const WideArgs& w) {
     else wide_softmax_fwd_kernel<<<sblocks, 256, 0, ctx->stream>>>(sa);
     LTCA_LAUNCH_OK(ctx, "wide_softmax_fwd_kernel");
     if (!w.o) return LTCA_OK;
-    // O = P V : P stored [Sq, Sk] (K-major), V stored [Sk, D] (N-major)
-    Mat a[2] = {{w.P, Skp, 0, mat, (int64_t)w.H * mat}, {w.Plo, Skp, 0, mat, (int64_t)w.H * mat}};
-    Mat b[2] = {{w.v, w.vs.seq, 1, w.vs.head, w.vs.batch}, {w.v, w.vs.seq, 1, w.vs.head, w.vs.batch}};
-    return batched(ctx, w, w.Sq, w.D, w.Sk, a, b, w.Plo ? 2 : 1, w.o, w.os.seq, w.os.head, w.os.batch, w.o_bf16);
+    // O = P V : P stored [Sq, Sk] (K-major), V stored [Sk, D] (N-major); terms hi hi, lo hi, hi lo
+    Mat a[3] = {{w.P, Skp, 0, mat, (int64_t)w.H * mat}, {w.Plo, Skp, 0, mat, (int64_t)w.H * mat},
+                {w.P, Skp, 0, mat, (int64_t)w.H * mat}};
+    Mat b[3] = {{w.v, w.vs.seq, 1, w.vs.head, w.vs.batch}, {w.v, w.vs.seq, 1, w.vs.head, w.vs.batch},
+                {w.vl, w.vs.seq, 1, w.vs.head, w.vs.batch}};
+    const int terms = w.Plo ? (w.vl ? 3 : 2) : 1;
+    return batched(ctx, w, w.Sq, w.D, w.Sk, a, b, terms, w.o, w.os.seq, w.os.head, w.os.batch, w.o_bf16);
 }
 
 int wide_attn_bwd(ltca_ctx* ctx, const WideArgs& w) {
@@ -401,17 +404,25 @@ int wide_attn_bwd(ltca_ctx* ctx, const WideArgs& w) {
     const int64_t mat = (int64_t)w.Sq * Skp;
     const int64_t mat_b = (int64_t)w.H * mat;
     const int terms = w.Plo ? 2 : 1;                 // P (then dS) as one or two bf16 terms
+    const bool full = w.Plo && w.vl && w.doutl && w.ql && w.kl;    // every operand in two terms: three-term products
+    if ((w.vl || w.doutl) && !full)
+        return fail(ctx, LTCA_ERR_INVALID, "low-order parts of V and dO come with those of Q, K and the probabilities");
     if (w.dS && w.Plo && !w.dSlo) return fail(ctx, LTCA_ERR_INVALID, "two-term probabilities need a two-term dS buffer");
     int rc;
+    // (three-term products: hi hi, lo hi, hi lo)
     {   // dP = dO V^T : both K-major
-        Mat a{w.dout, w.dos.seq, 0, w.dos.head, w.dos.batch};
-        Mat b{w.v, w.vs.seq, 0, w.vs.head, w.vs.batch};
-        if ((rc = batched(ctx, w, w.Sq, w.Sk, w.D, &a, &b, 1, w.dP, Skp, mat, mat_b, 0))) return rc;
+        Mat a[3] = {{w.dout, w.dos.seq, 0, w.dos.head, w.dos.batch}, {w.doutl, w.dos.seq, 0, w.dos.head, w.dos.batch},
+                    {w.dout, w.dos.seq, 0, w.dos.head, w.dos.batch}};
+        Mat b[3] = {{w.v, w.vs.seq, 0, w.vs.head, w.vs.batch}, {w.v, w.vs.seq, 0, w.vs.head, w.vs.batch},
+                    {w.vl, w.vs.seq, 0, w.vs.head, w.vs.batch}};
+        if ((rc = batched(ctx, w, w.Sq, w.Sk, w.D, a, b, full ? 3 : 1, w.dP, Skp, mat, mat_b, 0))) return rc;
     }
     {   // dV = P^T dO : P stored [Sq, Sk] = [K, M], dO stored [Sq, D] = [K, N]
-        Mat a[2] = {{w.P, Skp, 1, mat, mat_b}, {w.Plo, Skp, 1, mat, mat_b}};
-        Mat b[2] = {{w.dout, w.dos.seq, 1, w.dos.head, w.dos.batch}, {w.dout, w.dos.seq, 1, w.dos.head, w.dos.batch}};
-        if ((rc = batched(ctx, w, w.Sk, w.D, w.Sq, a, b, terms, w.dv, w.dvs.seq, w.dvs.head, w.dvs.batch, w.grads_bf16)))
+        Mat a[3] = {{w.P, Skp, 1, mat, mat_b}, {w.Plo, Skp, 1, mat, mat_b}, {w.P, Skp, 1, mat, mat_b}};
+        Mat b[3] = {{w.dout, w.dos.seq, 1, w.dos.head, w.dos.batch}, {w.dout, w.dos.seq, 1, w.dos.head, w.dos.batch},
+                    {w.doutl, w.dos.seq, 1, w.dos.head, w.dos.batch}};
+        if ((rc = batched(ctx, w, w.Sk, w.D, w.Sq, a, b, full ? 3 : terms, w.dv, w.dvs.seq, w.dvs.head, w.dvs.batch,
+                          w.grads_bf16)))
             return rc;
     }
     const SoftmaxArgs sa = softmax_args(w);
@@ -425,15 +436,19 @@ int wide_attn_bwd(ltca_ctx* ctx, const WideArgs& w) {
     else wide_softmax_bwd_kernel<<<sblocks, 256, 0, ctx->stream>>>(sa);
     LTCA_LAUNCH_OK(ctx, "wide_softmax_bwd_kernel");
     {   // dQ = dS K : dS K-major, K stored [Sk, D] = [K, N]
-        Mat a[2] = {{sa.dS, Skp, 0, mat, mat_b}, {sa.dSlo, Skp, 0, mat, mat_b}};
-        Mat b[2] = {{w.kh, w.ks.seq, 1, w.ks.head, w.ks.batch}, {w.kh, w.ks.seq, 1, w.ks.head, w.ks.batch}};
-        if ((rc = batched(ctx, w, w.Sq, w.D, w.Sk, a, b, terms, w.dq, w.dqs.seq, w.dqs.head, w.dqs.batch, w.grads_bf16)))
+        Mat a[3] = {{sa.dS, Skp, 0, mat, mat_b}, {sa.dSlo, Skp, 0, mat, mat_b}, {sa.dS, Skp, 0, mat, mat_b}};
+        Mat b[3] = {{w.kh, w.ks.seq, 1, w.ks.head, w.ks.batch}, {w.kh, w.ks.seq, 1, w.ks.head, w.ks.batch},
+                    {w.kl, w.ks.seq, 1, w.ks.head, w.ks.batch}};
+        if ((rc = batched(ctx, w, w.Sq, w.D, w.Sk, a, b, full ? 3 : terms, w.dq, w.dqs.seq, w.dqs.head, w.dqs.batch,
+                          w.grads_bf16)))
             return rc;
     }
     {   // dK = dS^T Q : dS stored [Sq, Sk] = [K, M], Q stored [Sq, D] = [K, N]
-        Mat a[2] = {{sa.dS, Skp, 1, mat, mat_b}, {sa.dSlo, Skp, 1, mat, mat_b}};
-        Mat b[2] = {{w.qh, w.qs.seq, 1, w.qs.head, w.qs.batch}, {w.qh, w.qs.seq, 1, w.qs.head, w.qs.batch}};
-        if ((rc = batched(ctx, w, w.Sk, w.D, w.Sq, a, b, terms, w.dk, w.dks.seq, w.dks.head, w.dks.batch, w.grads_bf16)))
+        Mat a[3] = {{sa.dS, Skp, 1, mat, mat_b}, {sa.dSlo, Skp, 1, mat, mat_b}, {sa.dS, Skp, 1, mat, mat_b}};
+        Mat b[3] = {{w.qh, w.qs.seq, 1, w.qs.head, w.qs.batch}, {w.qh, w.qs.seq, 1, w.qs.head, w.qs.batch},
+                    {w.ql, w.qs.seq, 1, w.qs.head, w.qs.batch}};
+        if ((rc = batched(ctx, w, w.Sk, w.D, w.Sq, a, b, full ? 3 : terms, w.dk, w.dks.seq, w.dks.head, w.dks.batch,
+                          w.grads_bf16)))
             return rc;
     }
     return LTCA_OK;

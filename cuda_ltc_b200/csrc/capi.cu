@@ -205,7 +205,8 @@ int check_common(ltca_ctx* ctx, const ltca_attn_params* p) {
                     p->B, p->H, p->Sq, p->Sk, p->D);
     if (p->dtype != LTCA_F32 && p->dtype != LTCA_BF16)
         return fail(ctx, LTCA_ERR_INVALID, "unknown dtype %d", p->dtype);
-    if (p->mode != LTCA_MODE_AUTO && p->mode != LTCA_MODE_BF16 && p->mode != LTCA_MODE_FP32)
+    if (p->mode != LTCA_MODE_AUTO && p->mode != LTCA_MODE_BF16 && p->mode != LTCA_MODE_FP32 &&
+        p->mode != LTCA_MODE_SPLIT)
         return fail(ctx, LTCA_ERR_INVALID, "unknown mode %d", p->mode);
     if (!p->q || !p->k || !p->v || !p->o)
         return fail(ctx, LTCA_ERR_INVALID, "q, k, v and o must be non-null");
@@ -214,8 +215,12 @@ int check_common(ltca_ctx* ctx, const ltca_attn_params* p) {
     return LTCA_OK;
 }
 
+// LTCA_MODE_SPLIT with fp32 storage: every operand in two bf16 terms, written-out scores (with bf16 storage there
+// are no low-order bits to keep and the mode is LTCA_MODE_BF16).
+bool split_mode(const ltca_attn_params* p) { return p->mode == LTCA_MODE_SPLIT && p->dtype == LTCA_F32; }
+
 bool tensor_path(const ltca_attn_params* p, bool backward) {
-    if (p->mode == LTCA_MODE_FP32) return false;
+    if (p->mode == LTCA_MODE_FP32 || split_mode(p)) return false;
     const bool ok = backward ? attn_bwd_sm100_supported(p) : attn_fwd_sm100_supported(p);
     if (!ok) return false;
     if (p->dtype == LTCA_F32 && (p->D % 4)) return false;
@@ -234,6 +239,40 @@ ltca_strides contiguous_strides(int H, int S, int D) {
     return s;
 }
 
+// The same with the low-order part: hi = bf16(x), lo = bf16(x - hi).
+__global__ void pack_split_bf16_kernel(const float* __restrict__ src, ltca_strides st, __nv_bfloat16* __restrict__ hi,
+                                       __nv_bfloat16* __restrict__ lo, int H, int S, int D, size_t n4) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    const int d4 = D / 4;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
+        const int dd = (int)(i % d4);
+        size_t r = i / d4;
+        const int s = (int)(r % S); r /= S;
+        const int h = (int)(r % H);
+        const int64_t b = (int64_t)(r / H);
+        const float4 v = *reinterpret_cast<const float4*>(src + b * st.batch + h * st.head + (int64_t)s * st.seq + 4 * dd);
+        const __nv_bfloat162 h0 = __floats2bfloat162_rn(v.x, v.y), h1 = __floats2bfloat162_rn(v.z, v.w);
+        const __nv_bfloat162 l0 = __floats2bfloat162_rn(v.x - __low2float(h0), v.y - __high2float(h0));
+        const __nv_bfloat162 l1 = __floats2bfloat162_rn(v.z - __low2float(h1), v.w - __high2float(h1));
+        uint2 u, w;
+        u.x = *reinterpret_cast<const uint32_t*>(&h0); u.y = *reinterpret_cast<const uint32_t*>(&h1);
+        w.x = *reinterpret_cast<const uint32_t*>(&l0); w.y = *reinterpret_cast<const uint32_t*>(&l1);
+        reinterpret_cast<uint2*>(hi)[i] = u;
+        reinterpret_cast<uint2*>(lo)[i] = w;
+    }
+}
+int pack_split_bf16(ltca_ctx* ctx, const void* src, const ltca_strides& st, void* hi, void* lo, int B, int H, int S,
+                    int D) {
+    if ((reinterpret_cast<uintptr_t>(src) & 15) || (st.seq % 4) || (st.head % 4) || (st.batch % 4))
+        return fail(ctx, LTCA_ERR_INVALID, "fp32 tensors need 16-byte aligned rows for the tensor-pipe modes");
+    const size_t n4 = (size_t)B * H * S * D / 4;
+    pack_split_bf16_kernel<<<blocks_for(n4, 256, ctx->sm_count), 256, 0, ctx->stream>>>(
+        reinterpret_cast<const float*>(src), st, reinterpret_cast<__nv_bfloat16*>(hi), reinterpret_cast<__nv_bfloat16*>(lo),
+        H, S, D, n4);
+    LTCA_LAUNCH_OK(ctx, "pack_split_bf16_kernel");
+    return LTCA_OK;
+}
+
 int pack_to_bf16(ltca_ctx* ctx, const void* src, const ltca_strides& st, void* dst, int B, int H,
                  int S, int D) {
     if ((reinterpret_cast<uintptr_t>(src) & 15) || (st.seq % 4) || (st.head % 4) || (st.batch % 4))
@@ -249,8 +288,9 @@ int pack_to_bf16(ltca_ctx* ctx, const void* src, const ltca_strides& st, void* d
 // The materialised-score path (attn_wide_sm100.cu) behind the core entry points: on explicit request
 // (LTCA_MODE_BF16) for head widths the streaming kernels do not cover, any multiple of 8.
 bool wide_core_path(const ltca_attn_params* p, bool backward) {
-    if (p->mode != LTCA_MODE_BF16) return false;
-    if (backward ? attn_bwd_sm100_supported(p) : attn_fwd_sm100_supported(p)) return false;
+    if (p->mode != LTCA_MODE_BF16 && !split_mode(p)) return false;
+    // (the split mode takes this path at every head width: the streaming kernels carry single bf16 operands)
+    if (!split_mode(p) && (backward ? attn_bwd_sm100_supported(p) : attn_fwd_sm100_supported(p))) return false;
     if (p->D < 8 || (p->D % 8) || p->Sq < 1 || p->Sk < 1 || !(p->scale > 0.f)) return false;
     if (p->dtype == LTCA_BF16) {
         if (!wide_supported(p->D, p->q_strides, p->k_strides, p->v_strides)) return false;
@@ -263,7 +303,8 @@ bool wide_core_path(const ltca_attn_params* p, bool backward) {
 
 size_t wide_core_workspace(const ltca_attn_params* p, bool backward) {
     size_t n = 0;
-    if (p->dtype == LTCA_F32) n += packed_bytes(p, p->Sq) * (backward ? 2 : 1) + 2 * packed_bytes(p, p->Sk);
+    if (p->dtype == LTCA_F32)
+        n += (packed_bytes(p, p->Sq) * (backward ? 2 : 1) + 2 * packed_bytes(p, p->Sk)) * (split_mode(p) ? 2 : 1);
     const size_t elems = wide_matrix_elems(p->B, p->H, p->Sq, p->Sk);
     n += align_up(elems * 4, 256) + align_up(elems * 2, 256);       // raw scores, probabilities
     if (p->dtype == LTCA_F32) n += align_up(elems * 2, 256);         // second term of the probabilities (fp32 results)
@@ -287,7 +328,24 @@ int launch_wide_core(ltca_ctx* ctx, const ltca_attn_params* p, bool backward) {
     a.qs = p->q_strides; a.ks = p->k_strides; a.vs = p->v_strides;
     a.dout = p->dout; a.dos = p->do_strides;
     int rc;
-    if (p->dtype == LTCA_F32) {
+    if (split_mode(p)) {
+        // q, k, v (and dO) as two bf16 terms each
+        const size_t nq = packed_bytes(p, p->Sq), nk = packed_bytes(p, p->Sk);
+        void* qh = w; w += nq;  void* ql = w; w += nq;
+        void* kh = w; w += nk;  void* kl = w; w += nk;
+        void* vh = w; w += nk;  void* vl = w; w += nk;
+        if ((rc = pack_split_bf16(ctx, p->q, p->q_strides, qh, ql, p->B, p->H, p->Sq, p->D))) return rc;
+        if ((rc = pack_split_bf16(ctx, p->k, p->k_strides, kh, kl, p->B, p->H, p->Sk, p->D))) return rc;
+        if ((rc = pack_split_bf16(ctx, p->v, p->v_strides, vh, vl, p->B, p->H, p->Sk, p->D))) return rc;
+        a.qh = qh; a.ql = ql; a.kh = kh; a.kl = kl; a.v = vh; a.vl = vl;
+        a.qs = contiguous_strides(p->H, p->Sq, p->D);
+        a.ks = a.vs = contiguous_strides(p->H, p->Sk, p->D);
+        if (backward) {
+            void* gh = w; w += nq;  void* gl = w; w += nq;
+            if ((rc = pack_split_bf16(ctx, p->dout, p->do_strides, gh, gl, p->B, p->H, p->Sq, p->D))) return rc;
+            a.dout = gh; a.doutl = gl; a.dos = a.qs;
+        }
+    } else if (p->dtype == LTCA_F32) {
         void* qb = w; w += packed_bytes(p, p->Sq);
         void* kb = w; w += packed_bytes(p, p->Sk);
         void* vb = w; w += packed_bytes(p, p->Sk);

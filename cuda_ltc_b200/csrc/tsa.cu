@@ -407,7 +407,7 @@ void fill_attn(const ltca_tsa_params* t, ltca_attn_params* a) {
     const int HW = t->H * t->head_width;
     a->B = t->B; a->H = t->H; a->Sq = t->S; a->Sk = t->S; a->D = t->head_width;
     a->dtype = LTCA_F32;
-    a->mode = t->mode;
+    a->mode = t->mode == LTCA_MODE_SPLIT ? LTCA_MODE_AUTO : t->mode;     // the module has no split mode of its own
     a->causal = t->causal;
     a->scale = t->scale;
     a->score_clamp = t->score_clamp;

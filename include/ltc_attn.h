@@ -50,10 +50,18 @@ typedef enum { LTCA_F32 = 0, LTCA_BF16 = 1 } ltca_dtype;
  *                    (forward also 128) run on the streaming kernels; any other multiple of 8 runs through
  *                    written-out score matrices and batched tensor-pipe products (more workspace:
  *                    ltca_attn_workspace_bytes tells).
+ *   LTCA_MODE_SPLIT: fp32 storage on the tensor pipe at fp32-class accuracy: Q, K, V, dO, the probabilities
+ *                    and dS each travel as TWO bf16 terms (hi + lo, 16 significant bits - TF32 keeps 11) and
+ *                    every contraction is evaluated as hi hi + hi lo + lo hi in one fp32 accumulator, through
+ *                    written-out score matrices at every head width that is a multiple of 8.  Agreement with
+ *                    an fp64 evaluation of the same fp32 inputs: 2e-5 + 2^-16 max|v| in the output, below 1e-5 in
+ *                    relative L2 (tests/test_attn_gpu.py; the bf16 mode: 6e-3, the fp32 mode: 1e-6).  With
+ *                    bf16 storage there are no low-order bits to keep and the mode equals LTCA_MODE_BF16.
+ *                    The module entry points (ltca_tsa_*) treat it as LTCA_MODE_AUTO.
  *   LTCA_MODE_FP32 : fp32 FMA arithmetic end to end (the 1e-5 mode).
  *   LTCA_MODE_AUTO : BF16 when the streaming tensor-pipe kernels cover the shape, else FP32.
  */
-typedef enum { LTCA_MODE_AUTO = 0, LTCA_MODE_BF16 = 1, LTCA_MODE_FP32 = 3 } ltca_mode;
+typedef enum { LTCA_MODE_AUTO = 0, LTCA_MODE_BF16 = 1, LTCA_MODE_SPLIT = 2, LTCA_MODE_FP32 = 3 } ltca_mode;
 
 typedef struct ltca_ctx ltca_ctx;
 

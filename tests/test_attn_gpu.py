@@ -395,6 +395,55 @@ def test_tensor_pipe_other_head_widths(ctx, case, storage):
         assert rel_l2(gh, r) < 2 * (TC_REL_L2 + half_ulp / 2), f"{name}: rel-L2 {rel_l2(gh, r)}"
 
 
+# Two bf16 terms carry 16 significant bits: a value x is represented to within 2^-17 |x|, so an output row that is
+# a mix of a few large values of v (a causal row that sees one or two keys) is off by that fraction of THEIR size,
+# whatever its own size; on top of it the sums contribute an absolute part.  Measured at these shapes: 1e-5 .. 6e-5 max-abs, 6e-6 .. 9e-6 relative L2
+# (the exact fp32 mode: 1e-6, the bf16 mode: 6e-3).
+SPLIT_ABS = 2e-5
+SPLIT_REL = 2.0 ** -16
+SPLIT_REL_L2 = 2e-5
+
+
+@pytest.mark.parametrize("case", WIDE_CORE_CASES + [(2, 2, 200, 200, 64, True, False, False, 0.0),
+                                                    (1, 2, 640, 515, 64, True, True, False, 0.0)])
+def test_split_precision_mode(ctx, case):
+    """LTCA_MODE_SPLIT: fp32 storage on the tensor pipe with every operand (Q, K, V, dO, P, dS) as two bf16 terms
+    and three-term products.  Sixteen significant bits per operand - TF32 keeps eleven - give agreement with the
+    fp64 oracle ON THE EXACT INPUTS at the 1e-5 level, two hundred times tighter than the bf16 mode, at every head
+    width that is a multiple of 8."""
+    B, H, Sq, Sk, D, causal, use_len, use_mask, clamp = case
+    q, k, v, do = make_case(B, H, Sq, Sk, D, 900, 1.0)
+    L = np.random.default_rng(8).integers(1, Sk + 1, size=B).astype(np.int32) if use_len else None
+    m = keep_mask(B, Sq, Sk, 9, 0.8, dead_rows=((0, 3),)) if use_mask else None
+    sc = 1.0 / math.sqrt(D)
+    o_ref, lse_ref = oracle.attn_fwd(q, k, v, sc, causal, m, L, clamp)
+    ref = oracle.attn_bwd(q, k, v, do, sc, causal, m, L, clamp)
+    tq, tk, tv, tdo = dev(q, torch.float32), dev(k, torch.float32), dev(v, torch.float32), dev(do, torch.float32)
+    dL = torch.from_numpy(L).cuda() if L is not None else None
+    dm = dev(m) if m is not None else None
+    kw = dict(scale=sc, causal=causal, kv_len=dL, keep_mask=dm, score_clamp=clamp, mode=_lib.MODE_SPLIT)
+    assert ctx.uses_tensor_pipe(tq, tk, tv, causal=causal, mode=_lib.MODE_SPLIT)
+    assert ctx.uses_tensor_pipe(tq, tk, tv, causal=causal, mode=_lib.MODE_SPLIT, backward=True)
+    o, lse = ctx.attn_fwd(tq, tk, tv, **kw)
+    got = ctx.attn_bwd(tq, tk, tv, o, lse, tdo, **kw)
+    again = ctx.attn_bwd(tq, tk, tv, o, lse, tdo, **kw)
+    torch.cuda.synchronize()
+    assert ctx.device_status() == 0
+    oh = o.cpu().numpy().astype(np.float64)
+    assert np.abs(oh - o_ref).max() <= SPLIT_ABS + SPLIT_REL * np.abs(v).max(), np.abs(oh - o_ref).max()
+    assert rel_l2(oh, o_ref) < SPLIT_REL_L2
+    lse_h = lse.cpu().numpy().astype(np.float64)
+    fin = np.isfinite(lse_ref)
+    assert (np.isfinite(lse_h) == fin).all()
+    assert (np.abs(lse_h[fin] - lse_ref[fin]) <= SPLIT_ABS + SPLIT_REL * np.abs(lse_ref[fin])).all()
+    for name, g, g2, r in zip(("dq", "dk", "dv"), got, again, ref):
+        assert torch.equal(g, g2), f"{name}: two runs differ"
+        gh = g.cpu().numpy().astype(np.float64)
+        mag = max(1.0, float(np.abs(r).max()))
+        assert np.abs(gh - r).max() <= (SPLIT_ABS + SPLIT_REL) * mag, (name, np.abs(gh - r).max())
+        assert rel_l2(gh, r) < SPLIT_REL_L2, f"{name}: rel-L2 {rel_l2(gh, r)}"
+
+
 def test_host_step_pipeline_matches_direct_calls(ctx):
     """Operands in pinned host memory, results back to pinned host memory, three overlapping steps:
     the same bits as the direct device-buffer calls."""
