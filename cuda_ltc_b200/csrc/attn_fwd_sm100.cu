@@ -576,6 +576,7 @@ struct F4PCfg {
     static constexpr int kDynBytes = kMiscOff + 16 + 4 * kItemSlots + 1024;
 };
 
+template <bool kFold>
 __global__ void __launch_bounds__(kF4Threads, 1)
 attn_fwd4p_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
                         const __grid_constant__ CUtensorMap tmap_k,
@@ -637,7 +638,7 @@ attn_fwd4p_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
     // the padded tile range and the two tiles that mirror them at its end, so that every item carries the same
     // work; the early tiles finish their few key steps and wait, the late ones run on with the SM to themselves.
     auto tile_q0 = [&](int m, int t) {
-        if (!grid.fold) return (m * kF4Tiles + t) * kBlockM;
+        if (!kFold) return (m * kF4Tiles + t) * kBlockM;
         const int tile = t < 2 ? 2 * m + t : grid.nblk * kF4Tiles - 2 * m - 4 + t;
         return tile * kBlockM;
     };
@@ -1058,8 +1059,9 @@ int launch_fwd4(ltca_ctx* ctx, const ltca_attn_params* p, const void* q, const v
     if ((rc = make_tmap_bhsd(ctx, &tk, k, 2, p->B, p->H, p->Sk, 64, ks, 64, kF4BN))) return rc;
     if ((rc = make_tmap_bhsd(ctx, &tv, v, 2, p->B, p->H, p->Sk, 64, vs, 64, kF4BN))) return rc;
     if ((rc = make_tmap_bhsd(ctx, &to, p->o, 2, p->B, p->H, p->Sq, 64, p->o_strides, 64, kBlockM))) return rc;
-    static SmemOptIn opt_in;
-    LTCA_CUDA_OK(ctx, opt_in_dynamic_smem(opt_in, ctx->device, attn_fwd4p_sm100_kernel, P::kDynBytes));
+    static SmemOptIn opt_in, opt_in_fold;
+    LTCA_CUDA_OK(ctx, opt_in_dynamic_smem(opt_in, ctx->device, attn_fwd4p_sm100_kernel<false>, P::kDynBytes));
+    LTCA_CUDA_OK(ctx, opt_in_dynamic_smem(opt_in_fold, ctx->device, attn_fwd4p_sm100_kernel<true>, P::kDynBytes));
     ItemGrid ig;
     ig.nblk = (p->Sq + kF4Tiles * kBlockM - 1) / (kF4Tiles * kBlockM);
     ig.H = p->H;
@@ -1069,7 +1071,8 @@ int launch_fwd4(ltca_ctx* ctx, const ltca_attn_params* p, const void* q, const v
     // (measured: B=1 H=16 S=4096, the bench workload dealt over eight GPUs: 92 us folded against 123 us)
     ig.fold = (a.causal && ig.nblk > 1 && ig.n_items <= ctx->sm_count) ? 1 : 0;
     const int n_cta = ig.n_items < ctx->sm_count ? ig.n_items : ctx->sm_count;
-    attn_fwd4p_sm100_kernel<<<n_cta, kF4Threads, P::kDynBytes, ctx->stream>>>(tq, tk, tv, to, a, ig);
+    if (ig.fold) attn_fwd4p_sm100_kernel<true><<<n_cta, kF4Threads, P::kDynBytes, ctx->stream>>>(tq, tk, tv, to, a, ig);
+    else attn_fwd4p_sm100_kernel<false><<<n_cta, kF4Threads, P::kDynBytes, ctx->stream>>>(tq, tk, tv, to, a, ig);
     LTCA_LAUNCH_OK(ctx, "attn_fwd4p_sm100_kernel");
     return LTCA_OK;
 }
