@@ -87,7 +87,11 @@ typedef struct {
     int32_t causal;             /* key j visible to query i iff j <= i + (Sk - Sq) */
     float   scale;              /* the reference uses 1/sqrt(D) (flash_attention.cu:998) */
     float   score_clamp;        /* > 0: s = min(s, score_clamp) after scaling; the reference
-                                   clamps at 10 (flash_attention.cu:167).  <= 0: no clamp */
+                                   clamps at 10 (flash_attention.cu:167).  <= 0: no clamp.  The gradient
+                                   of a clamped score is zero: a score that lies within the mode's rounding
+                                   of the threshold (1e-2 in the bf16 mode) can fall on either side of it,
+                                   so with many scores AT the threshold the bf16 mode's gradients differ
+                                   from an exact evaluation of unrounded inputs by whole terms */
     const void* q;  ltca_strides q_strides;    /* [B,H,Sq,D] */
     const void* k;  ltca_strides k_strides;    /* [B,H,Sk,D] */
     const void* v;  ltca_strides v_strides;    /* [B,H,Sk,D] */
