@@ -555,7 +555,7 @@ def ring_measurement(args):
     import torch
     import torch.distributed as dist
     import cuda_ltc_b200 as ltc
-    from cuda_ltc_b200 import ring
+    from cuda_ltc_b200 import gather, ring
     from cuda_ltc_b200.shard import reduce_max
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -571,11 +571,17 @@ def ring_measurement(args):
     g = torch.Generator(device=dev).manual_seed(SEED + rank)
     mk = lambda: (torch.randn((B, H, L, D), generator=g, device=dev) * 0.5).bfloat16()
     q, k, v, do = mk(), mk(), mk(), mk()
-    ops = ring.CudaOps(ctx, comm_sms=args.comm_sms)
+    gathered = bool(args.gather)
+    # (with gathered K/V the collectives do not run beside the kernels: no SMs are set aside for them)
+    ops = ring.CudaOps(ctx, comm_sms=0 if gathered else args.comm_sms)
     cache = {}                                          # scratch and receive buffers live across the steps
     n, w = max(5, args.steps), max(3, args.warmup)
 
     def step():
+        if gathered:
+            o, lse, kf, vf = gather.gathered_attention_fwd(ops, q, k, v, rank, world, causal=True, cache=cache)
+            gather.gathered_attention_bwd(ops, q, kf, vf, o, lse, do, rank, world, causal=True, cache=cache)
+            return
         o, lse = ring.ring_attention_fwd(ops, q, k, v, rank, world, causal=True, cache=cache)
         ring.ring_attention_bwd(ops, q, k, v, o, lse, do, rank, world, causal=True, cache=cache)
 
@@ -599,6 +605,14 @@ def ring_measurement(args):
     if rank != 0:
         return
     flops = 3.5 * 4.0 * B * H * S * S * D / 2
+    if gathered:
+        print(json.dumps({"workload": f"attention fwd+bwd, B={B} H={H} S={S} D={D} causal bf16, sequence dealt out "
+                                      f"over {world} GPU(s), K/V gathered, dK/dV reduce-scattered (strong scaling)",
+                          "n_gpus": world, "ms_per_step": ms, "tflops_whole_job": flops / ms / 1e9,
+                          "all_gather_bytes_received_per_gpu": 2 * B * H * (S - L) * D * 2,
+                          "reduce_scatter_bytes_sent_per_gpu": 2 * B * H * (S - L) * D * 4,
+                          "device_status": status}))
+        return
     print(json.dumps({"workload": f"attention fwd+bwd, B={B} H={H} S={S} D={D} causal bf16, sequence dealt out over "
                                   f"{world} GPU(s) with ring K/V exchange (strong scaling)",
                       "n_gpus": world, "ms_per_step": ms, "tflops_whole_job": flops / ms / 1e9,
@@ -627,6 +641,8 @@ def main():
                                                            "bench configuration's)")
     ap.add_argument("--comm-sms", type=int, default=16,
                     help="--ring: SMs the attention kernels leave free for the exchange's copy kernels")
+    ap.add_argument("--gather", action="store_true",
+                    help="with --ring's workload: gather K/V and reduce-scatter dK/dV instead of the ring exchange")
     ap.add_argument("--ring", action="store_true",
                     help="side measurement, not the bench line: the same problem with the sequence dealt out over "
                          "the ranks and K/V exchanged round a ring (launch one rank per GPU)")
@@ -645,7 +661,7 @@ def main():
     if args.model_step:
         model_step_measurement(args)
         return
-    if args.ring:
+    if args.ring or args.gather:
         CFG["B"] = args.batch
         ring_measurement(args)
         return
