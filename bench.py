@@ -580,7 +580,8 @@ def ring_measurement(args):
     def step():
         if gathered:
             o, lse, kf, vf = gather.gathered_attention_fwd(ops, q, k, v, rank, world, causal=True, cache=cache)
-            gather.gathered_attention_bwd(ops, q, kf, vf, o, lse, do, rank, world, causal=True, cache=cache)
+            gather.gathered_attention_bwd(ops, q, kf, vf, o, lse, do, rank, world, causal=True, cache=cache,
+                                          reduce_in_bf16=bool(args.reduce_bf16))
             return
         o, lse = ring.ring_attention_fwd(ops, q, k, v, rank, world, causal=True, cache=cache)
         ring.ring_attention_bwd(ops, q, k, v, o, lse, do, rank, world, causal=True, cache=cache)
@@ -610,7 +611,7 @@ def ring_measurement(args):
                                       f"over {world} GPU(s), K/V gathered, dK/dV reduce-scattered (strong scaling)",
                           "n_gpus": world, "ms_per_step": ms, "tflops_whole_job": flops / ms / 1e9,
                           "all_gather_bytes_received_per_gpu": 2 * B * H * (S - L) * D * 2,
-                          "reduce_scatter_bytes_sent_per_gpu": 2 * B * H * (S - L) * D * 4,
+                          "reduce_scatter_bytes_sent_per_gpu": 2 * B * H * (S - L) * D * (2 if args.reduce_bf16 else 4),
                           "device_status": status}))
         return
     print(json.dumps({"workload": f"attention fwd+bwd, B={B} H={H} S={S} D={D} causal bf16, sequence dealt out over "
@@ -641,6 +642,8 @@ def main():
                                                            "bench configuration's)")
     ap.add_argument("--comm-sms", type=int, default=16,
                     help="--ring: SMs the attention kernels leave free for the exchange's copy kernels")
+    ap.add_argument("--reduce-bf16", action="store_true",
+                    help="with --gather: the shares of dK / dV travel and are summed as bf16 instead of fp32")
     ap.add_argument("--gather", action="store_true",
                     help="with --ring's workload: gather K/V and reduce-scatter dK/dV instead of the ring exchange")
     ap.add_argument("--ring", action="store_true",

@@ -26,7 +26,7 @@ from typing import List, Tuple
 
 import torch
 
-from .ring import _buf, owned_positions, unshard_sequence
+from .ring import _buf
 
 
 def _dist():
@@ -49,12 +49,19 @@ def gather_sequence(x: torch.Tensor, world: int, causal: bool, group=None, cache
     dist = _dist()
     flat = _buf(cache, name + "_all", (world,) + tuple(x.shape), x.dtype, x.device)
     dist.all_gather_into_tensor(flat.view(-1), x.contiguous().view(-1), group=group)
+    B, H, L, D = x.shape
+    full = _buf(cache, name + "_full", (B, H, world * L, D), x.dtype, x.device)
     if not causal:
         # rank r holds positions [r L, (r + 1) L): [world, B, H, L, D] -> [B, H, world, L, D]
-        full = _buf(cache, name + "_full", (x.shape[0], x.shape[1], world * x.shape[2], x.shape[3]), x.dtype, x.device)
-        full.view(x.shape[0], x.shape[1], world, x.shape[2], x.shape[3]).copy_(flat.permute(1, 2, 0, 3, 4))
+        full.view(B, H, world, L, D).copy_(flat.permute(1, 2, 0, 3, 4))
         return full
-    return unshard_sequence(list(flat.unbind(0)), causal)
+    # zig-zag: the first halves of the slices are chunks 0 .. world - 1 in rank order, the second halves are
+    # chunks 2 world - 1 .. world, i.e. the rest of the sequence in REVERSE rank order
+    c = L // 2
+    both = full.view(B, H, 2, world, c, D)
+    both[:, :, 0].copy_(flat[:, :, :, :c].permute(1, 2, 0, 3, 4))
+    both[:, :, 1].copy_(flat[:, :, :, c:].permute(1, 2, 0, 3, 4).flip(2))
+    return full
 
 
 def gathered_attention_fwd(ops, q, k, v, rank, world, causal=False, group=None, cache=None):
@@ -81,44 +88,57 @@ def gathered_attention_fwd(ops, q, k, v, rank, world, causal=False, group=None, 
     return o, lse, k_full, v_full
 
 
-def gathered_attention_bwd(ops, q, k_full, v_full, o, lse, dout, rank, world, causal=False, group=None, cache=None):
+def _add_shares(send: torch.Tensor, t: int, part: torch.Tensor, world: int, L: int, causal: bool) -> None:
+    """send[owner, t] += the owner's rows of ``part`` (gradients of the first part.shape[2] keys, sequence order)."""
+    B, H, nk, D = part.shape
+    if not causal:
+        send[:, t].add_(part.view(B, H, world, L, D).permute(2, 0, 1, 3, 4))
+        return
+    c = L // 2
+    m = nk // c                                             # chunks of the key prefix; chunk j belongs to rank j or,
+    m1 = min(m, world)                                      # in the second half, to rank 2 world - 1 - j
+    send[:m1, t, :, :, :c].add_(part[:, :, :m1 * c].view(B, H, m1, c, D).permute(2, 0, 1, 3, 4))
+    if m > world:
+        tail = part[:, :, world * c:m * c].view(B, H, m - world, c, D).permute(2, 0, 1, 3, 4).flip(0)
+        send[2 * world - m:world, t, :, :, c:].add_(tail)
+
+
+def gathered_attention_bwd(ops, q, k_full, v_full, o, lse, dout, rank, world, causal=False, group=None, cache=None,
+                           reduce_in_bf16=False):
     """Backward for this rank's queries: (dq, dk, dv) for the rank's slices.  k_full, v_full: what the forward
-    returned."""
+    returned.  ``reduce_in_bf16``: the shares of dK / dV travel and are summed as bf16 (half the bytes of the
+    reduce-scatter; one more rounding per hop) instead of fp32."""
     B, H, L, D = q.shape
-    S = k_full.shape[2]
     if hasattr(ops, "begin"):
         ops.begin()
     try:
         dq = torch.empty_like(q)
-        # this rank's share of the gradients of every key, fp32, in sequence order
-        dk_acc = _buf(cache, "dk_acc", (B, H, S, D), torch.float32, q.device)
-        dv_acc = _buf(cache, "dv_acc", (B, H, S, D), torch.float32, q.device)
-        dk_acc.zero_()
-        dv_acc.zero_()
+        # this rank's shares of the gradients of every key, fp32, grouped by the rank that owns the key
+        send = _buf(cache, "dkv_send", (world, 2, B, H, L, D), torch.float32, q.device)
+        send.zero_()
         for r0, n, nk in _query_blocks(rank, world, L, causal):
             dk_p = _buf(cache, f"dk_part{r0}", (B, H, nk, D), q.dtype, q.device)
             dv_p = _buf(cache, f"dv_part{r0}", (B, H, nk, D), q.dtype, q.device)
             ops.block_bwd(q[:, :, r0:r0 + n], k_full[:, :, :nk], v_full[:, :, :nk], o[:, :, r0:r0 + n],
                           lse[:, :, r0:r0 + n].contiguous(), dout[:, :, r0:r0 + n], causal, dq=dq[:, :, r0:r0 + n],
                           dk=dk_p, dv=dv_p)
-            ops.accumulate(dk_acc, dk_p, 0)
-            ops.accumulate(dv_acc, dv_p, 0)
+            _add_shares(send, 0, dk_p, world, L, causal)
+            _add_shares(send, 1, dv_p, world, L, causal)
         if world == 1:
-            return dq, dk_acc.to(q.dtype), dv_acc.to(q.dtype)
-        # owner-major order, then one reduce-scatter for both gradients
+            return dq, send[0, 0].to(q.dtype), send[0, 1].to(q.dtype)
         dist = _dist()
-        send = _buf(cache, "dkv_send", (world, 2, B, H, L, D), torch.float32, q.device)
-        for r in range(world):
-            idx = owned_positions(S, world, r, causal).to(q.device)
-            torch.index_select(dk_acc, 2, idx, out=send[r, 0])
-            torch.index_select(dv_acc, 2, idx, out=send[r, 1])
-        recv = _buf(cache, "dkv_recv", (2, B, H, L, D), torch.float32, q.device)
+        if reduce_in_bf16 and q.dtype == torch.bfloat16:
+            send_x = _buf(cache, "dkv_send16", tuple(send.shape), torch.bfloat16, q.device)
+            send_x.copy_(send)
+        else:
+            send_x = send
+        recv = _buf(cache, "dkv_recv", (2, B, H, L, D), send_x.dtype, q.device)
         if dist.get_backend(group) == "gloo":
             # (no reduce-scatter in that backend: sum everywhere and keep the own part)
-            dist.all_reduce(send, group=group)
-            recv.copy_(send[rank])
+            dist.all_reduce(send_x, group=group)
+            recv.copy_(send_x[rank])
         else:
-            dist.reduce_scatter_tensor(recv.view(-1), send.view(-1), group=group)
+            dist.reduce_scatter_tensor(recv.view(-1), send_x.view(-1), group=group)
     finally:
         if hasattr(ops, "end"):
             ops.end()

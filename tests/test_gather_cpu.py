@@ -108,3 +108,50 @@ def test_query_blocks_cover_the_causal_triangle_evenly():
         work.append(sum(n * nk for _, n, nk in blocks))
     assert len(set(work)) == 1                               # the same number of scores on every rank
     assert _query_blocks(1, 4, 5, False) == [(0, 5, 20)]
+
+
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("world", [1, 2, 4])
+def test_shares_land_with_the_rank_that_owns_the_key(world, causal):
+    """_add_shares against the layout's own definition (ring.owned_positions), for every prefix length a rank's
+    calls can have."""
+    from cuda_ltc_b200 import gather, ring
+    B, H, D, c = 2, 3, 4, 5
+    L = 2 * c if causal else c
+    S = world * L
+    g = torch.Generator().manual_seed(3)
+    prefixes = sorted({nk for r in range(world) for _, _, nk in gather._query_blocks(r, world, L, causal)})
+    for nk in prefixes:
+        part = torch.randn((B, H, nk, D), generator=g)
+        send = torch.zeros((world, 2, B, H, L, D))
+        gather._add_shares(send, 1, part, world, L, causal)
+        full = torch.zeros((B, H, S, D))
+        full[:, :, :nk] = part
+        for r in range(world):
+            want = full.index_select(2, ring.owned_positions(S, world, r, causal))
+            assert torch.equal(send[r, 1], want), (nk, r)
+        assert float(send[:, 0].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_gathered_slices_come_back_in_sequence_order(causal):
+    """The reordering inside gather_sequence (no collective at world 1; here the gathered block is handed in
+    directly) inverts ring.shard_sequence for every rank count."""
+    from cuda_ltc_b200 import gather, ring
+    B, H, D = 2, 2, 3
+    for world in (2, 3, 4):
+        S = world * 6
+        x = torch.arange(B * H * S * D, dtype=torch.float32).view(B, H, S, D)
+        flat = torch.stack([ring.shard_sequence(x, world, r, causal) for r in range(world)])
+
+        class _FakeDist:
+            @staticmethod
+            def all_gather_into_tensor(out, inp, group=None):
+                out.copy_(flat.view(-1))
+        old = gather._dist
+        gather._dist = lambda: _FakeDist
+        try:
+            full = gather.gather_sequence(flat[0], world, causal)
+        finally:
+            gather._dist = old
+        assert torch.equal(full, x)
