@@ -106,7 +106,12 @@ def _nccl_worker(rank, world, port, out):
             torch.cuda.synchronize()
             idx = ring.owned_positions(S, world, rank, True).numpy()
             worst = max(worst, max(_errors((o, lse) + tuple(grads), ref, idx)))
-        out[rank] = (worst, ctx.device_status())
+        # the shares of dK / dV summed in bf16: one more rounding of each rank's share
+        g16 = gather.gathered_attention_bwd(ops, mine[0], kf, vf, o, lse, mine[3], rank, world, True, cache=cache,
+                                            reduce_in_bf16=True)
+        torch.cuda.synchronize()
+        worst16 = max(_errors(tuple(g16), ref[2:], idx))
+        out[rank] = (max(worst, worst16 / 2), ctx.device_status())
     finally:
         dist.destroy_process_group()
 
