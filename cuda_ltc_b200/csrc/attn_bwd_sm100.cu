@@ -2394,26 +2394,6 @@ int launch_main(ltca_ctx* ctx, const ltca_attn_params* p, const void* q, const v
     return LTCA_OK;
 }
 
-// Strided fp32 [B,H,S,64] -> contiguous bf16 (same kernel shape as the forward's pack step).
-__global__ void pack_bf16_rows_kernel(const float* __restrict__ src, ltca_strides st,
-                                      __nv_bfloat16* __restrict__ dst, int H, int S, size_t n8) {
-    const size_t stride = (size_t)gridDim.x * blockDim.x;
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += stride) {
-        const int dd = (int)(i % 8);
-        size_t r = i / 8;
-        const int s = (int)(r % S); r /= S;
-        const int h = (int)(r % H);
-        const int64_t b = (int64_t)(r / H);
-        const float* sp = src + b * st.batch + h * st.head + (int64_t)s * st.seq + 8 * dd;
-        const float4 x = *reinterpret_cast<const float4*>(sp);
-        const float4 y = *reinterpret_cast<const float4*>(sp + 4);
-        uint4 u;
-        u.x = pack_bf16x2(x.x, x.y); u.y = pack_bf16x2(x.z, x.w);
-        u.z = pack_bf16x2(y.x, y.y); u.w = pack_bf16x2(y.z, y.w);
-        reinterpret_cast<uint4*>(dst)[i] = u;
-    }
-}
-
 }  // namespace
 
 bool attn_bwd_sm100_supported(const ltca_attn_params* p) {
@@ -2470,23 +2450,9 @@ int launch_attn_bwd_sm100(ltca_ctx* ctx, const ltca_attn_params* p) {
     void* kb = w;  w += pk;
     void* vb = w;  w += pk;
     void* gb = w;
-    auto pack = [&](const void* src, const ltca_strides& st, void* dst, int S) -> int {
-        if ((reinterpret_cast<uintptr_t>(src) & 15) || (st.seq % 4) || (st.head % 4) || (st.batch % 4))
-            return fail(ctx, LTCA_ERR_INVALID, "fp32 tensors need 16-byte aligned rows for the bf16 mode");
-        const size_t n8 = (size_t)p->B * p->H * S * kD / 8;
-        size_t nb = (n8 + 255) / 256;
-        const size_t cap = (size_t)ctx->sm_device * 16;
-        if (nb > cap) nb = cap;
-        pack_bf16_rows_kernel<<<(unsigned)nb, 256, 0, ctx->stream>>>(
-            reinterpret_cast<const float*>(src), st, reinterpret_cast<__nv_bfloat16*>(dst), p->H, S, n8);
-        LTCA_LAUNCH_OK(ctx, "pack_bf16_rows_kernel");
-        return LTCA_OK;
-    };
-    int rc;
-    if ((rc = pack(p->q, p->q_strides, qb, p->Sq))) return rc;
-    if ((rc = pack(p->k, p->k_strides, kb, p->Sk))) return rc;
-    if ((rc = pack(p->v, p->v_strides, vb, p->Sk))) return rc;
-    if ((rc = pack(p->dout, p->do_strides, gb, p->Sq))) return rc;
+    const PackJob jobs[4] = {{p->q, p->q_strides, qb, p->Sq}, {p->k, p->k_strides, kb, p->Sk},
+                             {p->v, p->v_strides, vb, p->Sk}, {p->dout, p->do_strides, gb, p->Sq}};
+    if (int rc = pack_many_to_bf16(ctx, jobs, 4, p->B, p->H, kD)) return rc;
     kernel_timing_mark(ctx, 1);
     ltca_strides cq{(int64_t)p->H * p->Sq * kD, (int64_t)p->Sq * kD, kD};
     ltca_strides ck{(int64_t)p->H * p->Sk * kD, (int64_t)p->Sk * kD, kD};

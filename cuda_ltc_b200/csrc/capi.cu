@@ -77,11 +77,25 @@ __global__ void bf16_to_f32_kernel(const __nv_bfloat16* __restrict__ s, float* _
         d[i] = __bfloat162float(s[i]);
 }
 
-// Strided fp32 [B,H,S,D] -> contiguous bf16 [B,H,S,D]; one thread per 4 elements (D % 4 == 0).
-__global__ void pack_bf16_kernel(const float* __restrict__ src, ltca_strides st,
-                                 __nv_bfloat16* __restrict__ dst, int H, int S, int D, size_t n4) {
-    const size_t stride = (size_t)gridDim.x * blockDim.x;
+// Strided fp32 [B,H,S,D] -> contiguous bf16 [B,H,S,D]; one thread per 4 elements (D % 4 == 0).  blockIdx.y picks
+// the tensor, so the operands of one attention call are packed by one launch.
+struct PackJobs {
+    const float* src[kMaxPackJobs];
+    __nv_bfloat16* dst[kMaxPackJobs];
+    __nv_bfloat16* lo[kMaxPackJobs];
+    ltca_strides st[kMaxPackJobs];
+    int S[kMaxPackJobs];
+};
+__global__ void pack_bf16_kernel(const __grid_constant__ PackJobs jobs, int BH, int H, int D) {
+    const int j = blockIdx.y;
+    const float* __restrict__ src = jobs.src[j];
+    __nv_bfloat16* __restrict__ dst = jobs.dst[j];
+    __nv_bfloat16* __restrict__ low = jobs.lo[j];
+    const ltca_strides st = jobs.st[j];
+    const int S = jobs.S[j];
     const int d4 = D / 4;
+    const size_t n4 = (size_t)BH * S * d4;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
         const int dd = (int)(i % d4);
         size_t r = i / d4;
@@ -94,6 +108,14 @@ __global__ void pack_bf16_kernel(const float* __restrict__ src, ltca_strides st,
         u.x = *reinterpret_cast<uint32_t*>(&lo);
         u.y = *reinterpret_cast<uint32_t*>(&hi);
         reinterpret_cast<uint2*>(dst)[i] = u;
+        if (low) {
+            const __nv_bfloat162 l0 = __floats2bfloat162_rn(v.x - __low2float(lo), v.y - __high2float(lo));
+            const __nv_bfloat162 l1 = __floats2bfloat162_rn(v.z - __low2float(hi), v.w - __high2float(hi));
+            uint2 w;
+            w.x = *reinterpret_cast<const uint32_t*>(&l0);
+            w.y = *reinterpret_cast<const uint32_t*>(&l1);
+            reinterpret_cast<uint2*>(low)[i] = w;
+        }
     }
 }
 
@@ -239,52 +261,6 @@ ltca_strides contiguous_strides(int H, int S, int D) {
     return s;
 }
 
-// The same with the low-order part: hi = bf16(x), lo = bf16(x - hi).
-__global__ void pack_split_bf16_kernel(const float* __restrict__ src, ltca_strides st, __nv_bfloat16* __restrict__ hi,
-                                       __nv_bfloat16* __restrict__ lo, int H, int S, int D, size_t n4) {
-    const size_t stride = (size_t)gridDim.x * blockDim.x;
-    const int d4 = D / 4;
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
-        const int dd = (int)(i % d4);
-        size_t r = i / d4;
-        const int s = (int)(r % S); r /= S;
-        const int h = (int)(r % H);
-        const int64_t b = (int64_t)(r / H);
-        const float4 v = *reinterpret_cast<const float4*>(src + b * st.batch + h * st.head + (int64_t)s * st.seq + 4 * dd);
-        const __nv_bfloat162 h0 = __floats2bfloat162_rn(v.x, v.y), h1 = __floats2bfloat162_rn(v.z, v.w);
-        const __nv_bfloat162 l0 = __floats2bfloat162_rn(v.x - __low2float(h0), v.y - __high2float(h0));
-        const __nv_bfloat162 l1 = __floats2bfloat162_rn(v.z - __low2float(h1), v.w - __high2float(h1));
-        uint2 u, w;
-        u.x = *reinterpret_cast<const uint32_t*>(&h0); u.y = *reinterpret_cast<const uint32_t*>(&h1);
-        w.x = *reinterpret_cast<const uint32_t*>(&l0); w.y = *reinterpret_cast<const uint32_t*>(&l1);
-        reinterpret_cast<uint2*>(hi)[i] = u;
-        reinterpret_cast<uint2*>(lo)[i] = w;
-    }
-}
-int pack_split_bf16(ltca_ctx* ctx, const void* src, const ltca_strides& st, void* hi, void* lo, int B, int H, int S,
-                    int D) {
-    if ((reinterpret_cast<uintptr_t>(src) & 15) || (st.seq % 4) || (st.head % 4) || (st.batch % 4))
-        return fail(ctx, LTCA_ERR_INVALID, "fp32 tensors need 16-byte aligned rows for the tensor-pipe modes");
-    const size_t n4 = (size_t)B * H * S * D / 4;
-    pack_split_bf16_kernel<<<blocks_for(n4, 256, ctx->sm_count), 256, 0, ctx->stream>>>(
-        reinterpret_cast<const float*>(src), st, reinterpret_cast<__nv_bfloat16*>(hi), reinterpret_cast<__nv_bfloat16*>(lo),
-        H, S, D, n4);
-    LTCA_LAUNCH_OK(ctx, "pack_split_bf16_kernel");
-    return LTCA_OK;
-}
-
-int pack_to_bf16(ltca_ctx* ctx, const void* src, const ltca_strides& st, void* dst, int B, int H,
-                 int S, int D) {
-    if ((reinterpret_cast<uintptr_t>(src) & 15) || (st.seq % 4) || (st.head % 4) || (st.batch % 4))
-        return fail(ctx, LTCA_ERR_INVALID, "fp32 tensors need 16-byte aligned rows for the bf16 mode");
-    const size_t n4 = (size_t)B * H * S * D / 4;
-    pack_bf16_kernel<<<blocks_for(n4, 256, ctx->sm_count), 256, 0, ctx->stream>>>(
-        reinterpret_cast<const float*>(src), st, reinterpret_cast<__nv_bfloat16*>(dst), H, S, D, n4);
-    LTCA_LAUNCH_OK(ctx, "pack_bf16_kernel");
-    return LTCA_OK;
-}
-
-
 // The materialised-score path (attn_wide_sm100.cu) behind the core entry points: on explicit request
 // (LTCA_MODE_BF16) for head widths the streaming kernels do not cover, any multiple of 8.
 bool wide_core_path(const ltca_attn_params* p, bool backward) {
@@ -334,32 +310,32 @@ int launch_wide_core(ltca_ctx* ctx, const ltca_attn_params* p, bool backward) {
         void* qh = w; w += nq;  void* ql = w; w += nq;
         void* kh = w; w += nk;  void* kl = w; w += nk;
         void* vh = w; w += nk;  void* vl = w; w += nk;
-        if ((rc = pack_split_bf16(ctx, p->q, p->q_strides, qh, ql, p->B, p->H, p->Sq, p->D))) return rc;
-        if ((rc = pack_split_bf16(ctx, p->k, p->k_strides, kh, kl, p->B, p->H, p->Sk, p->D))) return rc;
-        if ((rc = pack_split_bf16(ctx, p->v, p->v_strides, vh, vl, p->B, p->H, p->Sk, p->D))) return rc;
+        PackJob jobs[kMaxPackJobs] = {{p->q, p->q_strides, qh, p->Sq, ql}, {p->k, p->k_strides, kh, p->Sk, kl},
+                                      {p->v, p->v_strides, vh, p->Sk, vl}, {}};
         a.qh = qh; a.ql = ql; a.kh = kh; a.kl = kl; a.v = vh; a.vl = vl;
         a.qs = contiguous_strides(p->H, p->Sq, p->D);
         a.ks = a.vs = contiguous_strides(p->H, p->Sk, p->D);
         if (backward) {
             void* gh = w; w += nq;  void* gl = w; w += nq;
-            if ((rc = pack_split_bf16(ctx, p->dout, p->do_strides, gh, gl, p->B, p->H, p->Sq, p->D))) return rc;
+            jobs[3] = {p->dout, p->do_strides, gh, p->Sq, gl};
             a.dout = gh; a.doutl = gl; a.dos = a.qs;
         }
+        if ((rc = pack_many_to_bf16(ctx, jobs, backward ? 4 : 3, p->B, p->H, p->D))) return rc;
     } else if (p->dtype == LTCA_F32) {
         void* qb = w; w += packed_bytes(p, p->Sq);
         void* kb = w; w += packed_bytes(p, p->Sk);
         void* vb = w; w += packed_bytes(p, p->Sk);
-        if ((rc = pack_to_bf16(ctx, p->q, p->q_strides, qb, p->B, p->H, p->Sq, p->D))) return rc;
-        if ((rc = pack_to_bf16(ctx, p->k, p->k_strides, kb, p->B, p->H, p->Sk, p->D))) return rc;
-        if ((rc = pack_to_bf16(ctx, p->v, p->v_strides, vb, p->B, p->H, p->Sk, p->D))) return rc;
+        PackJob jobs[kMaxPackJobs] = {{p->q, p->q_strides, qb, p->Sq}, {p->k, p->k_strides, kb, p->Sk},
+                                      {p->v, p->v_strides, vb, p->Sk}, {}};
         a.qh = qb; a.kh = kb; a.v = vb;
         a.qs = contiguous_strides(p->H, p->Sq, p->D);
         a.ks = a.vs = contiguous_strides(p->H, p->Sk, p->D);
         if (backward) {
             void* gb = w; w += packed_bytes(p, p->Sq);
-            if ((rc = pack_to_bf16(ctx, p->dout, p->do_strides, gb, p->B, p->H, p->Sq, p->D))) return rc;
+            jobs[3] = {p->dout, p->do_strides, gb, p->Sq};
             a.dout = gb; a.dos = a.qs;
         }
+        if ((rc = pack_many_to_bf16(ctx, jobs, backward ? 4 : 3, p->B, p->H, p->D))) return rc;
     }
     const size_t elems = wide_matrix_elems(p->B, p->H, p->Sq, p->Sk);
     a.scores = reinterpret_cast<float*>(w); w += align_up(elems * 4, 256);
@@ -381,6 +357,32 @@ int launch_wide_core(ltca_ctx* ctx, const ltca_attn_params* p, bool backward) {
 }
 
 }  // namespace
+
+int pack_many_to_bf16(ltca_ctx* ctx, const PackJob* jobs, int count, int B, int H, int D) {
+    if (count < 1 || count > kMaxPackJobs || (D % 4))
+        return fail(ctx, LTCA_ERR_INVALID, "pack: %d tensors of head_dim %d", count, D);
+    PackJobs k{};
+    int s_max = 0;
+    for (int j = 0; j < count; ++j) {
+        const ltca_strides& st = jobs[j].st;
+        if ((reinterpret_cast<uintptr_t>(jobs[j].src) & 15) || (st.seq % 4) || (st.head % 4) || (st.batch % 4))
+            return fail(ctx, LTCA_ERR_INVALID, "fp32 tensors need 16-byte aligned rows for the tensor-pipe modes");
+        k.src[j] = reinterpret_cast<const float*>(jobs[j].src);
+        k.dst[j] = reinterpret_cast<__nv_bfloat16*>(jobs[j].dst);
+        k.lo[j] = reinterpret_cast<__nv_bfloat16*>(jobs[j].lo);
+        k.st[j] = st;
+        k.S[j] = jobs[j].S;
+        if (jobs[j].S > s_max) s_max = jobs[j].S;
+    }
+    // the grid is sized for the longest tensor; 16 blocks per SM over all the tensors together
+    const size_t n4 = (size_t)B * H * s_max * D / 4;
+    int bx = blocks_for(n4, 256, ctx->sm_count);
+    const int cap = (ctx->sm_count > 0 ? ctx->sm_count : kPlanSms) * 16 / count;
+    if (bx > cap) bx = cap;
+    pack_bf16_kernel<<<dim3((unsigned)bx, (unsigned)count), 256, 0, ctx->stream>>>(k, B * H, H, D);
+    LTCA_LAUNCH_OK(ctx, "pack_bf16_kernel");
+    return LTCA_OK;
+}
 }  // namespace ltca
 
 using namespace ltca;
@@ -528,9 +530,9 @@ int ltca_attn_fwd(ltca_ctx* ctx, const ltca_attn_params* p) {
     void* qb = w;  w += packed_bytes(p, p->Sq);
     void* kb = w;  w += packed_bytes(p, p->Sk);
     void* vb = w;
-    if ((rc = pack_to_bf16(ctx, p->q, p->q_strides, qb, p->B, p->H, p->Sq, p->D))) return rc;
-    if ((rc = pack_to_bf16(ctx, p->k, p->k_strides, kb, p->B, p->H, p->Sk, p->D))) return rc;
-    if ((rc = pack_to_bf16(ctx, p->v, p->v_strides, vb, p->B, p->H, p->Sk, p->D))) return rc;
+    const PackJob jobs[3] = {{p->q, p->q_strides, qb, p->Sq}, {p->k, p->k_strides, kb, p->Sk},
+                             {p->v, p->v_strides, vb, p->Sk}};
+    if ((rc = pack_many_to_bf16(ctx, jobs, 3, p->B, p->H, p->D))) return rc;
     return launch_attn_fwd_sm100_bf16in(ctx, p, qb, kb, vb, contiguous_strides(p->H, p->Sq, p->D),
                                         contiguous_strides(p->H, p->Sk, p->D),
                                         contiguous_strides(p->H, p->Sk, p->D));

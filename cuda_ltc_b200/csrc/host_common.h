@@ -150,4 +150,16 @@ int launch_attn_bwd_fp32(ltca_ctx* ctx, const ltca_attn_params* p);
 size_t attn_bwd_fp32_workspace(const ltca_attn_params* p);
 int launch_attn_decode(ltca_ctx* ctx, const ltca_attn_params* p);
 size_t attn_decode_workspace(const ltca_attn_params* p);
+
+// Strided fp32 [B,H,S,D] tensors -> contiguous bf16 copies, up to four tensors in ONE launch (capi.cu).  With a
+// non-null `lo` the low-order term goes there as well: dst = bf16(x), lo = bf16(x - dst).
+struct PackJob {
+    const void* src;
+    ltca_strides st;
+    void* dst;
+    int S;
+    void* lo = nullptr;
+};
+constexpr int kMaxPackJobs = 4;
+int pack_many_to_bf16(ltca_ctx* ctx, const PackJob* jobs, int count, int B, int H, int D);
 }  // namespace ltca
