@@ -18,9 +18,11 @@
 // 48 KB (A, B) stages), warp 1 issues the MMAs (M128 N256 K16) into one of two 256-column accumulators in tensor
 // memory, warps 2-5 are the epilogue (one accumulator row per thread: tcgen05.ld, bias, convert; the tile is
 // staged in shared memory as 128-byte-swizzled boxes and stored with TMA), which works on tile i while the MMAs
-// of tile i+1 run.  Measured at the module's sizes the kernel is bound by operand traffic from L2 (6.3 TB/s at
-// 27 % tensor-pipe activity for the fused Q/K/V projection: every 128-row block of A is re-read once per N tile
-// and every weight matrix once per M tile), which is why the tile is 256 wide.
+// of tile i+1 run.  Measured at the module's sizes (device time line of one CTA): a ring stage of 48 KB arrives
+// every 600 - 700 cycles (about 80 bytes per cycle and SM from L2: every 128-row block of A is re-read once per
+// N tile and every weight matrix once per M tile) against 512 cycles of MMAs, which is why the tile is 256 wide;
+// the epilogue of a tile takes 4700 cycles (bf16) to 7200 (fp32) and is hidden behind the next tile's main loop
+// except for the last tile of a CTA.
 // The tile list runs over independent problems (Q, K and V projections share one launch) and/or splits of K
 // (weight gradients: K = batch x time is long and M x N is small, so the K range is cut into
 // slices whose partial tiles go to scratch and are summed in a fixed order by a second kernel).
@@ -28,6 +30,10 @@
 #include "host_common.h"
 #include "gemm_sm100.h"
 #include "sm100_ptx.cuh"
+#include "trace.cuh"
+#ifndef LTCA_TRACE_GEMM_Z
+#define LTCA_TRACE_GEMM_Z 1   // which launch of a module call records: the one with this many problems
+#endif
 
 namespace ltca {
 
@@ -38,8 +44,10 @@ constexpr int kStages = 4;                         // operand ring: 4 x (16 KB o
 constexpr int kATileBytes = kBM * kBK * 2;         // 16 KB
 constexpr int kBTileBytes = kBN * kBK * 2;         // 32 KB
 constexpr int kStageBytes = kATileBytes + kBTileBytes;
-// The result tile leaves in pieces of two 128-row boxes of 128 bytes: 128 bf16 or 64 fp32 columns (a fourth ring
-// stage and 32 KB of staging measured 4 - 6 % faster at the module's sizes than three stages and 64 KB).
+// The result tile leaves through two staging boxes of 128 rows x 128 bytes (64 bf16 or 32 fp32 columns) that
+// alternate.  A tiled TMA store reads shared memory at 32 bytes per cycle (513 cycles per box, measured with one
+// and with 148 CTAs storing, whatever the number of stores in flight), so a second pair of boxes buys nothing,
+// and a fourth ring stage measured 3 - 6 % faster at the module's sizes than three stages with four or five boxes.
 constexpr int kStageBoxes = 2;
 constexpr int kStageOutBytes = kBM * 128 * kStageBoxes;
 constexpr int kGemmThreads = 192;
@@ -118,6 +126,8 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap ta0, const __grid_con
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n_tiles = g.tiles_x * g.tiles_y * g.tiles_z * g.batch_h * g.batch_b;
+    LTCA_TRACE_DECL(blockIdx.x == 5 && g.tiles_z == LTCA_TRACE_GEMM_Z);
+    LTCA_TRACE_EVT(0x01);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_empty(s), 1); }
@@ -131,6 +141,7 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap ta0, const __grid_con
     tc_fence_after_sync();
     const uint32_t tmem_base = misc[0];
     const WaitCtx wc{&misc[1], g.status};
+    LTCA_TRACE_EVT(0x02);
 
     if (warp == 0) {
         if (lane == 0) {
@@ -148,6 +159,7 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap ta0, const __grid_con
                         const int s = it % kStages;
                         ok = mbar_wait(bar_empty(s), (uint32_t)(((it / kStages) & 1) ^ 1), wc, 0xd0);
                         if (!ok) break;
+                        LTCA_TRACE_EVT(0x10 + (it << 8));
                         mbar_arrive_expect_tx(bar_full(s), (uint32_t)kStageBytes);
                         const int k0 = kb * kBK;
                         if (kAMn) {
@@ -189,11 +201,13 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap ta0, const __grid_con
                 // the epilogue has read this accumulator's previous tile out
                 ok = mbar_wait(bar_acc_empty(buf), (uint32_t)(((na >> 1) & 1) ^ 1), wc, 0xd3);
                 if (!ok) break;
+                LTCA_TRACE_EVT(0x20 + (na << 8));
                 const uint32_t acc = tmem_base + (uint32_t)kBN * buf;
                 for (int i = 0; i < t.n_iters && ok; ++i, ++it) {
                     const int s = it % kStages;
                     ok = mbar_wait(bar_full(s), (uint32_t)((it / kStages) & 1), wc, 0xd1);
                     if (!ok) break;
+                    LTCA_TRACE_EVT(0x21 + (it << 8));
                     tc_fence_after_sync();
                     const uint64_t ad = a_desc0 + (uint64_t)((s * kStageBytes) >> 4);
                     const uint64_t bd = b_desc0 + (uint64_t)((s * kStageBytes) >> 4);
@@ -203,6 +217,7 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap ta0, const __grid_con
                     mma_commit(bar_empty(s));
                 }
                 if (ok) mma_commit(bar_acc_full(buf));
+                LTCA_TRACE_EVT(0x22 + (na << 8));
                 ++na;
             }
         }
@@ -214,7 +229,7 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap ta0, const __grid_con
         const uint32_t stage_addr = smem_base + kOutOff;
         const int box_cols = g.out_bf16 ? 64 : 32;
         bool ok = true;
-        int na = 0;
+        int na = 0, pc = 0;                                 // accumulators used; boxes staged
         for (int lin = blockIdx.x; lin < n_tiles; lin += gridDim.x) {
             const GemmTile t = gemm_tile(g, lin);
             const int gm = t.m0 + row;
@@ -223,140 +238,185 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap ta0, const __grid_con
             if (have) {
                 if (ok) ok = mbar_wait_warp(bar_acc_full(buf), (uint32_t)((na >> 1) & 1), wc, 0xd2);
                 tc_fence_after_sync();
+                LTCA_TRACE_EVT(0x30 + (na << 8));
                 ++na;
             }
             const uint32_t tacc = tmem_base + (uint32_t)kBN * buf + ((uint32_t)(qd * 32) << 16);
             const float* bias = (g.ksplit == 1) ? g.bias[t.problem] : nullptr;
             const bool staged = g.tma_store && g.ksplit == 1;
-            // The tile leaves in pieces that fit the staging area (kStageBoxes boxes).  A piece goes to shared
-            // memory in the layout of 128-byte swizzled TMA boxes - 64 bf16 or 32 fp32 columns wide, 128 rows - and
-            // one thread stores the boxes; the tensor map clips rows and columns past the end of C.  (Storing a
-            // row's 16-byte pieces straight from registers costs 32 L1 wavefronts per instruction, about as many
-            // cycles per tile as its MMAs.)  With a second term half of the boxes take the high-order part of the
-            // piece and the other half the low-order part.
-            const int piece_boxes = g.c_lo ? kStageBoxes / 2 : kStageBoxes;
-            const int piece_cols = staged ? piece_boxes * box_cols : kBN;
-            for (int p0 = 0; p0 < kBN; p0 += piece_cols) {
-                if (staged) {
-                    // the previous piece's boxes have been read: the storing thread waits for that before it comes here
-                    asm volatile("bar.sync 1, 128;" ::: "memory");
-                }
-#pragma unroll 1
-                for (int c0 = p0; c0 < p0 + piece_cols; c0 += 32) {
-                    uint32_t v[32];
-                    __syncwarp();
+            if (staged) {
+                // The tile leaves box by box: 128 rows of 128 bytes (64 bf16 or 32 fp32 columns) go to shared memory
+                // in the layout of a 128-byte swizzled TMA box and one thread stores the box; the tensor map clips
+                // rows and columns past the end of C.  (Storing a row's 16-byte pieces straight from registers costs
+                // 32 L1 wavefronts per instruction, about as many cycles per tile as its MMAs.)  The two boxes of the
+                // staging area alternate, so a box is filled while the store of the one before it is still reading,
+                // and the columns of the next box are on their way out of tensor memory while this one is converted.
+                // With a second term the low-order part takes the second box and the boxes do not alternate.
+                const int n_pieces = kBN / box_cols;
+                const bool two = g.out_bf16 != 0;              // a bf16 box holds two 32-column loads
+                uint32_t va0[32], va1[32], vb0[32], vb1[32];
+                auto load_piece = [&](int pi, uint32_t (&x0)[32], uint32_t (&x1)[32]) {
                     if (have && ok) {
-                        tmem_ld32(tacc + c0, v);
-                        tmem_wait_ld();
+                        tmem_ld32(tacc + pi * box_cols, x0);
+                        if (two) tmem_ld32(tacc + pi * box_cols + 32, x1);
                     } else {
 #pragma unroll
-                        for (int c = 0; c < 32; ++c) v[c] = 0u;
+                        for (int c = 0; c < 32; ++c) x0[c] = x1[c] = 0u;
                     }
-                    if (have && c0 + 32 == kBN) {
+                };
+                auto put_bf16 = [&](uint8_t* box, int ch0, const uint32_t (&v)[32]) {
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        uint4 w;
+                        w.x = pack_bf16x2(__uint_as_float(v[8 * c + 0]), __uint_as_float(v[8 * c + 1]));
+                        w.y = pack_bf16x2(__uint_as_float(v[8 * c + 2]), __uint_as_float(v[8 * c + 3]));
+                        w.z = pack_bf16x2(__uint_as_float(v[8 * c + 4]), __uint_as_float(v[8 * c + 5]));
+                        w.w = pack_bf16x2(__uint_as_float(v[8 * c + 6]), __uint_as_float(v[8 * c + 7]));
+                        *reinterpret_cast<uint4*>(box + (((ch0 + c) ^ (row & 7)) << 4)) = w;
+                        if (g.c_lo) {
+                            uint4 l;
+                            l.x = pack_bf16x2(__uint_as_float(v[8 * c + 0]) - __uint_as_float(w.x << 16),
+                                              __uint_as_float(v[8 * c + 1]) - __uint_as_float(w.x & 0xffff0000u));
+                            l.y = pack_bf16x2(__uint_as_float(v[8 * c + 2]) - __uint_as_float(w.y << 16),
+                                              __uint_as_float(v[8 * c + 3]) - __uint_as_float(w.y & 0xffff0000u));
+                            l.z = pack_bf16x2(__uint_as_float(v[8 * c + 4]) - __uint_as_float(w.z << 16),
+                                              __uint_as_float(v[8 * c + 5]) - __uint_as_float(w.z & 0xffff0000u));
+                            l.w = pack_bf16x2(__uint_as_float(v[8 * c + 6]) - __uint_as_float(w.w << 16),
+                                              __uint_as_float(v[8 * c + 7]) - __uint_as_float(w.w & 0xffff0000u));
+                            *reinterpret_cast<uint4*>(box + kBM * 128 + (((ch0 + c) ^ (row & 7)) << 4)) = l;
+                        }
+                    }
+                };
+                auto add_bias = [&](int gn0, uint32_t (&v)[32]) {
+#pragma unroll
+                    for (int c = 0; c < 32; ++c)
+                        if (gn0 + c < g.N) v[c] = __float_as_uint(__uint_as_float(v[c]) + __ldg(bias + gn0 + c));
+                };
+                auto put_piece = [&](int pi, uint32_t (&x0)[32], uint32_t (&x1)[32]) {
+                    const int gn0 = t.n0 + pi * box_cols;
+                    if (bias) {
+                        add_bias(gn0, x0);
+                        if (two) add_bias(gn0 + 32, x1);
+                    }
+                    const int hb = g.c_lo ? 2 * (pc % (kStageBoxes / 2)) : pc % kStageBoxes;
+                    // the box is free: the storing thread waits for the store that last read it before it comes here
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    uint8_t* box = stage + hb * (kBM * 128) + row * 128;
+                    if (two) {
+                        put_bf16(box, 0, x0);
+                        put_bf16(box, 4, x1);
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < 8; ++c)
+                            *reinterpret_cast<uint4*>(box + ((c ^ (row & 7)) << 4)) =
+                                make_uint4(x0[4 * c], x0[4 * c + 1], x0[4 * c + 2], x0[4 * c + 3]);
+                    }
+                    LTCA_TRACE_EVT(0x31 + (pi << 8));
+                    fence_proxy_async_smem();
+                    asm volatile("bar.sync 1, 128;" ::: "memory");    // the four epilogue warps have staged their rows
+                    if (warp == 2 && lane == 0) {
+                        const CUtensorMap* tc = t.problem == 0 ? &tc0 : (t.problem == 1 ? &tc1 : &tc2);
+                        if (gn0 < g.N) {
+                            tma_store_4d(tc, stage_addr + hb * (kBM * 128), gn0, t.m0, t.bh, t.bb);
+                            if (g.c_lo) tma_store_4d(&tc1, stage_addr + (hb + 1) * (kBM * 128), gn0, t.m0, t.bh, t.bb);
+                        }
+                        tma_store_commit();
+                        // the box that the next piece takes has been read
+                        if (g.c_lo) tma_store_wait_read<kStageBoxes / 2 - 1>();
+                        else tma_store_wait_read<kStageBoxes - 1>();
+                        LTCA_TRACE_EVT(0x32 + (pi << 8));
+                    }
+                    ++pc;
+                };
+                load_piece(0, va0, va1);
+#pragma unroll 1
+                for (int pi = 0; pi < n_pieces; pi += 2) {
+                    tmem_wait_ld();
+                    tmem_ld_fence(va0);
+                    tmem_ld_fence(va1);
+                    load_piece(pi + 1, vb0, vb1);
+                    put_piece(pi, va0, va1);
+                    tmem_wait_ld();
+                    tmem_ld_fence(vb0);
+                    tmem_ld_fence(vb1);
+                    if (pi + 2 < n_pieces) {
+                        load_piece(pi + 2, va0, va1);
+                    } else if (have) {
                         // the accumulator is in registers: the MMA thread may start the tile after next in it
                         tc_fence_before_sync();
                         __syncwarp();
                         if (lane == 0) mbar_arrive(bar_acc_empty(buf));
                     }
-                    const int gn0 = t.n0 + c0;
-                    if (bias) {
+                    put_piece(pi + 1, vb0, vb1);
+                }
+                continue;
+            }
+            // Direct stores: split-K partials and results whose rows are not 16-byte aligned.
+#pragma unroll 1
+            for (int c0 = 0; c0 < kBN; c0 += 32) {
+                uint32_t v[32];
+                __syncwarp();
+                if (have && ok) {
+                    tmem_ld32(tacc + c0, v);
+                    tmem_wait_ld();
+                } else {
 #pragma unroll
-                        for (int c = 0; c < 32; ++c)
-                            if (gn0 + c < g.N) v[c] = __float_as_uint(__uint_as_float(v[c]) + __ldg(bias + gn0 + c));
-                    }
-                    if (staged) {
-                        const int cp = c0 - p0;                 // column inside the piece
-                        if (g.out_bf16) {
-                            uint8_t* box = stage + (cp / 64) * (kBM * 128) + row * 128;
-                            const int ch0 = (cp % 64) / 8;
+                    for (int c = 0; c < 32; ++c) v[c] = 0u;
+                }
+                if (have && c0 + 32 == kBN) {
+                    tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar_acc_empty(buf));
+                }
+                const int gn0 = t.n0 + c0;
+                if (bias) {
 #pragma unroll
-                            for (int c = 0; c < 4; ++c) {
-                                uint4 w;
-                                w.x = pack_bf16x2(__uint_as_float(v[8 * c + 0]), __uint_as_float(v[8 * c + 1]));
-                                w.y = pack_bf16x2(__uint_as_float(v[8 * c + 2]), __uint_as_float(v[8 * c + 3]));
-                                w.z = pack_bf16x2(__uint_as_float(v[8 * c + 4]), __uint_as_float(v[8 * c + 5]));
-                                w.w = pack_bf16x2(__uint_as_float(v[8 * c + 6]), __uint_as_float(v[8 * c + 7]));
-                                *reinterpret_cast<uint4*>(box + (((ch0 + c) ^ (row & 7)) << 4)) = w;
-                                if (g.c_lo) {
-                                    uint4 l;
-                                    l.x = pack_bf16x2(__uint_as_float(v[8 * c + 0]) - __uint_as_float(w.x << 16),
-                                                      __uint_as_float(v[8 * c + 1]) - __uint_as_float(w.x & 0xffff0000u));
-                                    l.y = pack_bf16x2(__uint_as_float(v[8 * c + 2]) - __uint_as_float(w.y << 16),
-                                                      __uint_as_float(v[8 * c + 3]) - __uint_as_float(w.y & 0xffff0000u));
-                                    l.z = pack_bf16x2(__uint_as_float(v[8 * c + 4]) - __uint_as_float(w.z << 16),
-                                                      __uint_as_float(v[8 * c + 5]) - __uint_as_float(w.z & 0xffff0000u));
-                                    l.w = pack_bf16x2(__uint_as_float(v[8 * c + 6]) - __uint_as_float(w.w << 16),
-                                                      __uint_as_float(v[8 * c + 7]) - __uint_as_float(w.w & 0xffff0000u));
-                                    *reinterpret_cast<uint4*>(box + piece_boxes * (kBM * 128) + (((ch0 + c) ^ (row & 7)) << 4)) = l;
-                                }
-                            }
-                        } else {
-                            uint8_t* box = stage + (cp / 32) * (kBM * 128) + row * 128;
+                    for (int c = 0; c < 32; ++c)
+                        if (gn0 + c < g.N) v[c] = __float_as_uint(__uint_as_float(v[c]) + __ldg(bias + gn0 + c));
+                }
+                if (gm >= g.M || gn0 >= g.N) continue;
+                const bool full = gn0 + 32 <= g.N;
+                if (g.ksplit > 1) {
+                    float* dst = g.partial + (((int64_t)t.problem * g.ksplit + t.slice) * g.M + gm) * g.N + gn0;
+                    if (full && (g.N & 3) == 0) {
 #pragma unroll
-                            for (int c = 0; c < 8; ++c)
-                                *reinterpret_cast<uint4*>(box + ((c ^ (row & 7)) << 4)) =
-                                    make_uint4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
-                        }
-                        continue;
-                    }
-                    if (gm >= g.M || gn0 >= g.N) continue;
-                    const bool full = gn0 + 32 <= g.N;
-                    if (g.ksplit > 1) {
-                        float* dst = g.partial + (((int64_t)t.problem * g.ksplit + t.slice) * g.M + gm) * g.N + gn0;
-                        if (full && (g.N & 3) == 0) {
-#pragma unroll
-                            for (int c = 0; c < 32; c += 4)
-                                *reinterpret_cast<uint4*>(dst + c) = make_uint4(v[c], v[c + 1], v[c + 2], v[c + 3]);
-                        } else {
-#pragma unroll
-                            for (int c = 0; c < 32; ++c)
-                                if (gn0 + c < g.N) dst[c] = __uint_as_float(v[c]);
-                        }
-                    } else if (g.out_bf16) {
-                        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(g.C[t.problem]) + t.bh * g.c_bs[0] +
-                                             t.bb * g.c_bs[1] + (int64_t)gm * g.ldc + gn0;
-#pragma unroll
-                        for (int c = 0; c < 32; ++c)
-                            if (gn0 + c < g.N) dst[c] = __float2bfloat16_rn(__uint_as_float(v[c]));
-                        if (g.c_lo) {
-                            __nv_bfloat16* lo = reinterpret_cast<__nv_bfloat16*>(g.c_lo) + (dst -
-                                                reinterpret_cast<__nv_bfloat16*>(g.C[t.problem]));
-#pragma unroll
-                            for (int c = 0; c < 32; ++c)
-                                if (gn0 + c < g.N)
-                                    lo[c] = __float2bfloat16_rn(__uint_as_float(v[c]) - __bfloat162float(dst[c]));
-                        }
+                        for (int c = 0; c < 32; c += 4)
+                            *reinterpret_cast<uint4*>(dst + c) = make_uint4(v[c], v[c + 1], v[c + 2], v[c + 3]);
                     } else {
-                        float* dst = reinterpret_cast<float*>(g.C[t.problem]) + t.bh * g.c_bs[0] + t.bb * g.c_bs[1] +
-                                     (int64_t)gm * g.ldc + gn0;
 #pragma unroll
                         for (int c = 0; c < 32; ++c)
                             if (gn0 + c < g.N) dst[c] = __uint_as_float(v[c]);
                     }
-                }
-                if (staged) {
-                    fence_proxy_async_smem();
-                    asm volatile("bar.sync 1, 128;" ::: "memory");    // the four epilogue warps have staged their rows
-                    if (warp == 2 && lane == 0) {
-                        const CUtensorMap* tc = t.problem == 0 ? &tc0 : (t.problem == 1 ? &tc1 : &tc2);
-                        const int n_boxes = piece_cols / box_cols;
-                        for (int bx = 0; bx < n_boxes; ++bx)
-                            if (t.n0 + p0 + bx * box_cols < g.N) {
-                                tma_store_4d(tc, stage_addr + bx * (kBM * 128), t.n0 + p0 + bx * box_cols, t.m0, t.bh, t.bb);
-                                if (g.c_lo)
-                                    tma_store_4d(&tc1, stage_addr + (piece_boxes + bx) * (kBM * 128), t.n0 + p0 + bx * box_cols,
-                                                 t.m0, t.bh, t.bb);
-                            }
-                        tma_store_commit();
-                        tma_store_wait_read<0>();
+                } else if (g.out_bf16) {
+                    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(g.C[t.problem]) + t.bh * g.c_bs[0] +
+                                         t.bb * g.c_bs[1] + (int64_t)gm * g.ldc + gn0;
+#pragma unroll
+                    for (int c = 0; c < 32; ++c)
+                        if (gn0 + c < g.N) dst[c] = __float2bfloat16_rn(__uint_as_float(v[c]));
+                    if (g.c_lo) {
+                        __nv_bfloat16* lo = reinterpret_cast<__nv_bfloat16*>(g.c_lo) + (dst -
+                                            reinterpret_cast<__nv_bfloat16*>(g.C[t.problem]));
+#pragma unroll
+                        for (int c = 0; c < 32; ++c)
+                            if (gn0 + c < g.N)
+                                lo[c] = __float2bfloat16_rn(__uint_as_float(v[c]) - __bfloat162float(dst[c]));
                     }
+                } else {
+                    float* dst = reinterpret_cast<float*>(g.C[t.problem]) + t.bh * g.c_bs[0] + t.bb * g.c_bs[1] +
+                                 (int64_t)gm * g.ldc + gn0;
+#pragma unroll
+                    for (int c = 0; c < 32; ++c)
+                        if (gn0 + c < g.N) dst[c] = __uint_as_float(v[c]);
                 }
             }
         }
+        if (warp == 2 && lane == 0) tma_store_wait_read<0>();    // the staging area outlives its last store
     }
 
+    LTCA_TRACE_EVT(0x3e);
     tc_fence_before_sync();
     __syncthreads();
+    LTCA_TRACE_EVT(0x3f);
     if (warp == 1) {
         __syncwarp();
         if (misc[1]) __nanosleep(200000);    // aborted: give copies and MMAs in flight time to land
@@ -364,6 +424,18 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap ta0, const __grid_con
         tmem_dealloc(tmem_base, kAccCols);
     }
 }
+
+#ifdef LTCA_TRACE
+}  // namespace
+}  // namespace ltca
+extern "C" int ltca_trace_read_gemm(unsigned long long* events, unsigned int* counts) {
+    if (cudaMemcpyFromSymbol(events, ltca::g_trace, sizeof(ltca::g_trace)) != cudaSuccess) return -1;
+    if (cudaMemcpyFromSymbol(counts, ltca::g_trace_count, sizeof(ltca::g_trace_count)) != cudaSuccess) return -1;
+    return 0;
+}
+namespace ltca {
+namespace {
+#endif
 
 // C[problem][i] = sum over slices of partial[problem][slice][i], in slice order.
 __global__ void gemm_splitk_reduce_kernel(const float* __restrict__ partial, float* c0, float* c1, float* c2,
