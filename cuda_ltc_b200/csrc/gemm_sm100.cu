@@ -467,21 +467,27 @@ __global__ void cvt_rows_bf16_vec_kernel(const float4* __restrict__ src, uint2* 
     }
 }
 
-struct CvtBatch {
-    const float* src[4];
-    __nv_bfloat16* dst[4];
-    int64_t ld_src[4], ld_dst[4], rows[4];
-    int cols[4];
+// Several matrices of any sizes in ONE launch (the activations and the weights of a module call): the 16-byte
+// pieces of all of them form one index range that the grid strides over.
+constexpr int kMaxCvtMany = 6;
+struct CvtMany {
+    const float* src[kMaxCvtMany];
+    __nv_bfloat16* dst[kMaxCvtMany];
+    int64_t ld_src[kMaxCvtMany], ld_dst[kMaxCvtMany];
+    uint32_t cols4[kMaxCvtMany];
+    uint32_t start4[kMaxCvtMany + 1];       // first piece of matrix m; start4[n] = all pieces
+    int n;
 };
-// Up to four small matrices (the module's weights) in one launch: blockIdx.y selects the matrix.
-__global__ void cvt_batch_bf16_kernel(const CvtBatch b) {
-    const int m = blockIdx.y;
-    const int64_t n = b.rows[m] * b.cols[m];
-    const int cols = b.cols[m];
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
-        const int64_t r = i / cols;
-        const int c = (int)(i - r * cols);
-        b.dst[m][r * b.ld_dst[m] + c] = __float2bfloat16_rn(__ldg(b.src[m] + r * b.ld_src[m] + c));
+__global__ void cvt_many_bf16_kernel(const __grid_constant__ CvtMany b) {
+    const uint32_t total = b.start4[b.n];
+    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+        int m = 0;
+        while (m + 1 < b.n && i >= b.start4[m + 1]) ++m;
+        const uint32_t j = i - b.start4[m];
+        const uint32_t r = j / b.cols4[m], c4 = j - r * b.cols4[m];
+        const float4 v = __ldg(reinterpret_cast<const float4*>(b.src[m] + (int64_t)r * b.ld_src[m]) + c4);
+        reinterpret_cast<uint2*>(b.dst[m] + (int64_t)r * b.ld_dst[m])[c4] =
+            make_uint2(pack_bf16x2(v.x, v.y), pack_bf16x2(v.z, v.w));
     }
 }
 
@@ -617,21 +623,39 @@ int convert_rows_bf16(ltca_ctx* ctx, const float* src, int64_t ld_src, void* dst
 }
 
 
-int convert_batch_bf16(ltca_ctx* ctx, int n, const float* const* src, const int64_t* ld_src, void* const* dst,
-                       const int64_t* ld_dst, const int64_t* rows, const int* cols) {
-    if (n < 1 || n > 4) return fail(ctx, LTCA_ERR_INVALID, "convert_batch_bf16 takes 1 to 4 matrices");
-    CvtBatch b;
-    int64_t most = 0;
-    for (int i = 0; i < 4; ++i) {
-        const int j = i < n ? i : 0;
-        b.src[i] = src[j]; b.dst[i] = reinterpret_cast<__nv_bfloat16*>(dst[j]);
-        b.ld_src[i] = ld_src[j]; b.ld_dst[i] = ld_dst[j]; b.rows[i] = rows[j]; b.cols[i] = cols[j];
-        if (rows[j] * cols[j] > most) most = rows[j] * cols[j];
+int convert_many_bf16(ltca_ctx* ctx, int n, const float* const* src, const int64_t* ld_src, void* const* dst,
+                      const int64_t* ld_dst, const int64_t* rows, const int* cols) {
+    if (n < 1 || n > kMaxCvtMany) return fail(ctx, LTCA_ERR_INVALID, "convert_many_bf16 takes 1 to %d matrices", kMaxCvtMany);
+    CvtMany b;
+    memset(&b, 0, sizeof(b));
+    b.n = 0;
+    uint64_t total = 0;
+    bool vec = true;
+    for (int i = 0; i < n; ++i) {
+        if (rows[i] < 1 || cols[i] < 1) continue;
+        if ((cols[i] & 3) || (ld_src[i] & 3) || (ld_dst[i] & 3) || (reinterpret_cast<uintptr_t>(src[i]) & 15) ||
+            (reinterpret_cast<uintptr_t>(dst[i]) & 7)) {
+            vec = false;
+            break;
+        }
+        const int m = b.n++;
+        b.src[m] = src[i]; b.dst[m] = reinterpret_cast<__nv_bfloat16*>(dst[i]);
+        b.ld_src[m] = ld_src[i]; b.ld_dst[m] = ld_dst[i];
+        b.cols4[m] = (uint32_t)(cols[i] / 4);
+        b.start4[m] = (uint32_t)total;
+        total += (uint64_t)rows[i] * (uint64_t)(cols[i] / 4);
     }
-    if (most < 1) return LTCA_OK;
-    dim3 grid((unsigned)((most + 1023) / 1024 < 592 ? (most + 1023) / 1024 : 592), n);
-    cvt_batch_bf16_kernel<<<grid, 256, 0, ctx->stream>>>(b);
-    LTCA_LAUNCH_OK(ctx, "cvt_batch_bf16_kernel");
+    if (!vec || total >= (1ull << 31)) {
+        // odd shapes or alignments: one matrix at a time
+        for (int i = 0; i < n; ++i)
+            if (int rc = convert_rows_bf16(ctx, src[i], ld_src[i], dst[i], ld_dst[i], rows[i], cols[i])) return rc;
+        return LTCA_OK;
+    }
+    if (b.n == 0) return LTCA_OK;
+    b.start4[b.n] = (uint32_t)total;
+    const unsigned blocks = (unsigned)((total + 255) / 256 < 2368 ? (total + 255) / 256 : 2368);
+    cvt_many_bf16_kernel<<<blocks, 256, 0, ctx->stream>>>(b);
+    LTCA_LAUNCH_OK(ctx, "cvt_many_bf16_kernel");
     return LTCA_OK;
 }
 

@@ -40,8 +40,8 @@ size_t gemm_sm100_partial_bytes(int M, int N, int n_problems, int ksplit);
 // dst[r, c] = bf16(src[r, c]) for a [rows, cols] block with row pitches ld_src / ld_dst (elements).
 int convert_rows_bf16(ltca_ctx* ctx, const float* src, int64_t ld_src, void* dst, int64_t ld_dst, int64_t rows,
                       int cols);
-// The same for up to four small matrices in one launch.
-int convert_batch_bf16(ltca_ctx* ctx, int n, const float* const* src, const int64_t* ld_src, void* const* dst,
-                       const int64_t* ld_dst, const int64_t* rows, const int* cols);
+// The same for up to six matrices of any sizes in one launch (16-byte aligned rows; otherwise one launch each).
+int convert_many_bf16(ltca_ctx* ctx, int n, const float* const* src, const int64_t* ld_src, void* const* dst,
+                      const int64_t* ld_dst, const int64_t* rows, const int* cols);
 
 }  // namespace ltca

@@ -638,7 +638,11 @@ void fill_wide(const ltca_tsa_params* t, const TBufs& tb, WideArgs* w) {
 }
 
 // bf16 copies, fused Q/K/V projection, attention forward.
-int tensor_forward_core(ltca_ctx* ctx, const ltca_tsa_params* t, const TPlan& pl, char* w, TBufs* tb, int which) {
+// `also_src` / `also_dst`: one more [rows, E] fp32 matrix (the backward's dy) to be rounded to bf16 by the same launch
+// that rounds x and the weights; *also_done says whether that happened (not on the paths that convert otherwise
+// or not at all).
+int tensor_forward_core(ltca_ctx* ctx, const ltca_tsa_params* t, const TPlan& pl, char* w, TBufs* tb, int which,
+                        const float* also_src = nullptr, void* also_dst = nullptr, bool* also_done = nullptr) {
     char* rest = w;
     const bool saved = t->saved != nullptr;
     if (saved) w = reinterpret_cast<char*>(t->saved);
@@ -730,13 +734,20 @@ int tensor_forward_core(ltca_ctx* ctx, const ltca_tsa_params* t, const TPlan& pl
         fill_wide(t, *tb, &wa);
         return wide_attn_fwd(ctx, wa);
     }
-    if ((rc = convert_rows_bf16(ctx, t->x, E, tb->xb, Ep, pl.rows, E))) return rc;
-    if (convert_weights) {
-        const float* src[4] = {t->wq, t->wk, t->wv, t->wo};
-        void* dst[4] = {tb->wq, tb->wk, tb->wv, tb->wo};
-        const int64_t ld_src[4] = {HW, HW, HW, E}, ld_dst[4] = {HW, HW, HW, Ep}, nrows[4] = {E, E, E, HW};
-        const int ncols[4] = {HW, HW, HW, E};
-        if ((rc = convert_batch_bf16(ctx, 4, src, ld_src, dst, ld_dst, nrows, ncols))) return rc;
+    {   // x, the four weight matrices unless their copies are kept, and the caller's extra matrix: one launch
+        const float* src[6] = {t->x, t->wq, t->wk, t->wv, t->wo, nullptr};
+        void* dst[6] = {tb->xb, tb->wq, tb->wk, tb->wv, tb->wo, nullptr};
+        int64_t ld_src[6] = {E, HW, HW, HW, E, E}, ld_dst[6] = {Ep, HW, HW, HW, Ep, Ep};
+        int64_t nrows[6] = {pl.rows, E, E, E, HW, pl.rows};
+        int ncols[6] = {E, HW, HW, HW, E, E};
+        int n = convert_weights ? 5 : 1;
+        if (also_src) {
+            src[n] = also_src; dst[n] = also_dst;
+            ld_src[n] = E; ld_dst[n] = Ep; nrows[n] = pl.rows; ncols[n] = E;
+            ++n;
+            if (also_done) *also_done = true;
+        }
+        if ((rc = convert_many_bf16(ctx, n, src, ld_src, dst, ld_dst, nrows, ncols))) return rc;
     }
     GemmProblem gp;
     gp.M = (int)pl.rows; gp.N = HW; gp.K = E;
@@ -806,9 +817,10 @@ int tensor_backward(ltca_ctx* ctx, const ltca_tsa_params* t, bool want_dx, bool 
     TBufs tb;
     // the forward is recomputed, as the reference's caller does before each backward
     // (src/ml/ml_liquid_net.cu:715-721)
-    if ((rc = tensor_forward_core(ctx, t, pl, w, &tb, 1))) return rc;
+    bool dy_done = false;
+    if ((rc = tensor_forward_core(ctx, t, pl, w, &tb, 1, t->dy, dyb, &dy_done))) return rc;
     const int rows = (int)pl.rows, E = t->E, HW = pl.HW, Ep = pl.Ep;
-    if ((rc = convert_rows_bf16(ctx, t->dy, E, dyb, Ep, pl.rows, E))) return rc;
+    if (!dy_done && (rc = convert_rows_bf16(ctx, t->dy, E, dyb, Ep, pl.rows, E))) return rc;
     {   // dctx = dy Wo^T : Wo is stored [HW, E] = [N, K]
         GemmProblem gp;
         gp.M = rows; gp.N = HW; gp.K = E;
