@@ -29,6 +29,7 @@
 // `n_sum` > 1 accumulates several operand pairs into one tile (dx = dq Wq^T + dk Wk^T + dv Wv^T).
 #include "host_common.h"
 #include "gemm_sm100.h"
+#include "attn_wide.h"
 #include "sm100_ptx.cuh"
 #include "trace.cuh"
 #ifndef LTCA_TRACE_GEMM_Z
@@ -473,6 +474,7 @@ constexpr int kMaxCvtMany = 6;
 struct CvtMany {
     const float* src[kMaxCvtMany];
     __nv_bfloat16* dst[kMaxCvtMany];
+    __nv_bfloat16* lo[kMaxCvtMany];         // second term bf16(x - bf16(x)), laid out like dst, or null
     int64_t ld_src[kMaxCvtMany], ld_dst[kMaxCvtMany];
     uint32_t cols4[kMaxCvtMany];
     uint32_t start4[kMaxCvtMany + 1];       // first piece of matrix m; start4[n] = all pieces
@@ -486,8 +488,13 @@ __global__ void cvt_many_bf16_kernel(const __grid_constant__ CvtMany b) {
         const uint32_t j = i - b.start4[m];
         const uint32_t r = j / b.cols4[m], c4 = j - r * b.cols4[m];
         const float4 v = __ldg(reinterpret_cast<const float4*>(b.src[m] + (int64_t)r * b.ld_src[m]) + c4);
-        reinterpret_cast<uint2*>(b.dst[m] + (int64_t)r * b.ld_dst[m])[c4] =
-            make_uint2(pack_bf16x2(v.x, v.y), pack_bf16x2(v.z, v.w));
+        const uint2 h = make_uint2(pack_bf16x2(v.x, v.y), pack_bf16x2(v.z, v.w));
+        reinterpret_cast<uint2*>(b.dst[m] + (int64_t)r * b.ld_dst[m])[c4] = h;
+        if (b.lo[m]) {
+            const uint2 l = make_uint2(pack_bf16x2(v.x - __uint_as_float(h.x << 16), v.y - __uint_as_float(h.x & 0xffff0000u)),
+                                       pack_bf16x2(v.z - __uint_as_float(h.y << 16), v.w - __uint_as_float(h.y & 0xffff0000u)));
+            reinterpret_cast<uint2*>(b.lo[m] + (int64_t)r * b.ld_dst[m])[c4] = l;
+        }
     }
 }
 
@@ -624,7 +631,7 @@ int convert_rows_bf16(ltca_ctx* ctx, const float* src, int64_t ld_src, void* dst
 
 
 int convert_many_bf16(ltca_ctx* ctx, int n, const float* const* src, const int64_t* ld_src, void* const* dst,
-                      const int64_t* ld_dst, const int64_t* rows, const int* cols) {
+                      const int64_t* ld_dst, const int64_t* rows, const int* cols, void* const* lo) {
     if (n < 1 || n > kMaxCvtMany) return fail(ctx, LTCA_ERR_INVALID, "convert_many_bf16 takes 1 to %d matrices", kMaxCvtMany);
     CvtMany b;
     memset(&b, 0, sizeof(b));
@@ -633,13 +640,15 @@ int convert_many_bf16(ltca_ctx* ctx, int n, const float* const* src, const int64
     bool vec = true;
     for (int i = 0; i < n; ++i) {
         if (rows[i] < 1 || cols[i] < 1) continue;
-        if ((cols[i] & 3) || (ld_src[i] & 3) || (ld_dst[i] & 3) || (reinterpret_cast<uintptr_t>(src[i]) & 15) ||
+        if (lo && lo[i]) vec = vec && (reinterpret_cast<uintptr_t>(lo[i]) & 7) == 0;
+        if (!vec || (cols[i] & 3) || (ld_src[i] & 3) || (ld_dst[i] & 3) || (reinterpret_cast<uintptr_t>(src[i]) & 15) ||
             (reinterpret_cast<uintptr_t>(dst[i]) & 7)) {
             vec = false;
             break;
         }
         const int m = b.n++;
         b.src[m] = src[i]; b.dst[m] = reinterpret_cast<__nv_bfloat16*>(dst[i]);
+        b.lo[m] = lo ? reinterpret_cast<__nv_bfloat16*>(lo[i]) : nullptr;
         b.ld_src[m] = ld_src[i]; b.ld_dst[m] = ld_dst[i];
         b.cols4[m] = (uint32_t)(cols[i] / 4);
         b.start4[m] = (uint32_t)total;
@@ -647,8 +656,12 @@ int convert_many_bf16(ltca_ctx* ctx, int n, const float* const* src, const int64
     }
     if (!vec || total >= (1ull << 31)) {
         // odd shapes or alignments: one matrix at a time
-        for (int i = 0; i < n; ++i)
-            if (int rc = convert_rows_bf16(ctx, src[i], ld_src[i], dst[i], ld_dst[i], rows[i], cols[i])) return rc;
+        for (int i = 0; i < n; ++i) {
+            int rc;
+            if (lo && lo[i]) rc = wide_split_bf16(ctx, src[i], ld_src[i], dst[i], lo[i], ld_dst[i], rows[i], cols[i]);
+            else rc = convert_rows_bf16(ctx, src[i], ld_src[i], dst[i], ld_dst[i], rows[i], cols[i]);
+            if (rc) return rc;
+        }
         return LTCA_OK;
     }
     if (b.n == 0) return LTCA_OK;

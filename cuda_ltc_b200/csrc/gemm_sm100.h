@@ -41,7 +41,8 @@ size_t gemm_sm100_partial_bytes(int M, int N, int n_problems, int ksplit);
 int convert_rows_bf16(ltca_ctx* ctx, const float* src, int64_t ld_src, void* dst, int64_t ld_dst, int64_t rows,
                       int cols);
 // The same for up to six matrices of any sizes in one launch (16-byte aligned rows; otherwise one launch each).
+// `lo` (or an entry of it) non-null: also the second term bf16(x - bf16(x)), laid out like the first.
 int convert_many_bf16(ltca_ctx* ctx, int n, const float* const* src, const int64_t* ld_src, void* const* dst,
-                      const int64_t* ld_dst, const int64_t* rows, const int* cols);
+                      const int64_t* ld_dst, const int64_t* rows, const int* cols, void* const* lo = nullptr);
 
 }  // namespace ltca

@@ -689,15 +689,26 @@ int tensor_forward_core(ltca_ctx* ctx, const ltca_tsa_params* t, const TPlan& pl
     if (saved && t->reuse_forward) return LTCA_OK;
     const int E = t->E, HW = pl.HW, Ep = pl.Ep;
     int rc;
-    if (pl.wide) {
-        // Two-term operands for the products whose rounding would reach the scores: x, Wq, Wk here, q and k below.
-        if ((rc = wide_split_bf16(ctx, t->x, E, tb->xb, tb->xl, Ep, pl.rows, E))) return rc;
-        if (convert_weights) {
-            if ((rc = wide_split_bf16(ctx, t->wq, HW, tb->wq, tb->wql, HW, E, HW))) return rc;
-            if ((rc = wide_split_bf16(ctx, t->wk, HW, tb->wk, tb->wkl, HW, E, HW))) return rc;
-            if ((rc = wide_split_bf16(ctx, t->wv, HW, tb->wv, nullptr, HW, E, HW))) return rc;
-            if ((rc = wide_split_bf16(ctx, t->wo, E, tb->wo, nullptr, Ep, HW, E))) return rc;
+    {   // x, the four weight matrices unless their copies are kept, and the caller's extra matrix are rounded to
+        // bf16 by one launch.  On the written-out-score path the operands of the products whose rounding would
+        // reach the scores - x, Wq, Wk here, q and k below - get a second term.
+        const float* src[6] = {t->x, t->wq, t->wk, t->wv, t->wo, nullptr};
+        void* dst[6] = {tb->xb, tb->wq, tb->wk, tb->wv, tb->wo, nullptr};
+        void* lo[6] = {pl.wide ? tb->xl : nullptr, pl.wide ? tb->wql : nullptr, pl.wide ? tb->wkl : nullptr,
+                       nullptr, nullptr, nullptr};
+        int64_t ld_src[6] = {E, HW, HW, HW, E, E}, ld_dst[6] = {Ep, HW, HW, HW, Ep, Ep};
+        int64_t nrows[6] = {pl.rows, E, E, E, HW, pl.rows};
+        int ncols[6] = {E, HW, HW, HW, E, E};
+        int n = convert_weights ? 5 : 1;
+        if (also_src) {
+            src[n] = also_src; dst[n] = also_dst; lo[n] = nullptr;
+            ld_src[n] = E; ld_dst[n] = Ep; nrows[n] = pl.rows; ncols[n] = E;
+            ++n;
+            if (also_done) *also_done = true;
         }
+        if ((rc = convert_many_bf16(ctx, n, src, ld_src, dst, ld_dst, nrows, ncols, lo))) return rc;
+    }
+    if (pl.wide) {
         const void* whi[2] = {tb->wq, tb->wk};
         const void* wlo[2] = {tb->wql, tb->wkl};
         void* ohi[2] = {tb->q, tb->k};
@@ -733,21 +744,6 @@ int tensor_forward_core(ltca_ctx* ctx, const ltca_tsa_params* t, const TPlan& pl
         WideArgs wa;
         fill_wide(t, *tb, &wa);
         return wide_attn_fwd(ctx, wa);
-    }
-    {   // x, the four weight matrices unless their copies are kept, and the caller's extra matrix: one launch
-        const float* src[6] = {t->x, t->wq, t->wk, t->wv, t->wo, nullptr};
-        void* dst[6] = {tb->xb, tb->wq, tb->wk, tb->wv, tb->wo, nullptr};
-        int64_t ld_src[6] = {E, HW, HW, HW, E, E}, ld_dst[6] = {Ep, HW, HW, HW, Ep, Ep};
-        int64_t nrows[6] = {pl.rows, E, E, E, HW, pl.rows};
-        int ncols[6] = {E, HW, HW, HW, E, E};
-        int n = convert_weights ? 5 : 1;
-        if (also_src) {
-            src[n] = also_src; dst[n] = also_dst;
-            ld_src[n] = E; ld_dst[n] = Ep; nrows[n] = pl.rows; ncols[n] = E;
-            ++n;
-            if (also_done) *also_done = true;
-        }
-        if ((rc = convert_many_bf16(ctx, n, src, ld_src, dst, ld_dst, nrows, ncols))) return rc;
     }
     GemmProblem gp;
     gp.M = (int)pl.rows; gp.N = HW; gp.K = E;
