@@ -1106,7 +1106,22 @@ int launch_fwd(ltca_ctx* ctx, const ltca_attn_params* p, const void* q, const vo
 
     if constexpr (D == 64 && sizeof(OutT) == 2) {
         // long query ranges: four independent tiles per CTA (see attn_fwd4p_sm100_kernel)
-        if (p->Sq > kFwd4MinSq) return launch_fwd4(ctx, p, q, k, v, qs, ks, vs, a);
+        // ... unless its work items (512 queries of one batch entry and head) leave SMs idle where the CTAs of the
+        // two-tile kernel (256 queries) would fill them: B=4 H=16 Sq=512 Sk=4096 takes 129 us on 64 of 148 SMs
+        // against 75 us on 128, B=1 H=8 S=4096 causal 92 against 70 us.  Per tile the four-tile kernel is the
+        // faster one (16 pairs of S=4096, causal: 99 against 112 us), so it keeps the case unless the other fills
+        // the SMs a quarter better.  The device's SM count decides, not a limit set on the context: the choice,
+        // and with it the bits of the result, does not move with the launch width.
+        bool four = p->Sq > kFwd4MinSq;
+        const int64_t bh = (int64_t)p->B * p->H;
+        const int64_t items4 = bh * ((p->Sq + 4 * kBlockM - 1) / (4 * kBlockM));
+        const int64_t sms = ctx->sm_device > 0 ? ctx->sm_device : kPlanSms;
+        if (four && items4 < sms) {
+            const int64_t ctas2 = bh * ((p->Sq + 2 * kBlockM - 1) / (2 * kBlockM));
+            const int64_t waves2 = (ctas2 + sms - 1) / sms;
+            four = (double)ctas2 / (double)(waves2 * sms) < 1.25 * (double)items4 / (double)sms;
+        }
+        if (four) return launch_fwd4(ctx, p, q, k, v, qs, ks, vs, a);
     }
 
     auto kern = attn_fwd_sm100_kernel<D, OutT, kSplitP>;

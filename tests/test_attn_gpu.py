@@ -109,13 +109,21 @@ TC_CASES = [
     (32, 8, 256, 256, 64, True, False, False, 0.0),     # config 2 core
     (1, 2, 512, 512, 128, True, False, False, 0.0),
     (1, 1, 300, 300, 128, False, True, False, 0.0),
-    # causal launches with several 512-row blocks and fewer items than SMs: the folded tile mapping of the
-    # four-tile kernel (two early and two late query tiles per item)
-    (1, 2, 1100, 1100, 64, True, False, False, 0.0),    # nine tiles in three blocks: three padded tile slots
+    # few (batch, head) pairs and long query ranges: the two-tile kernel over several 256-row blocks (the
+    # four-tile kernel's 512-row work items would leave most SMs idle)
+    (1, 2, 1100, 1100, 64, True, False, False, 0.0),
     (2, 2, 2048, 2048, 64, True, False, False, 0.0),
     (1, 3, 1536, 1000, 64, True, False, False, 0.0),    # more queries than keys: the early tiles see nothing
     (1, 2, 1000, 1500, 64, True, True, False, 0.0),     # key lengths
     (1, 2, 640, 640, 64, True, False, True, 5.0),       # dense mask and clamp
+    # enough pairs that the four-tile kernel's items fill the SMs about as well, and still no more items than SMs:
+    # causal launches take its folded tile mapping (two early and two late query tiles per item)
+    (5, 8, 1100, 1100, 64, True, False, False, 0.0),    # nine tiles in three blocks: three padded tile slots
+    (4, 8, 2048, 2048, 64, True, False, False, 0.0),
+    (5, 8, 1536, 1000, 64, True, False, False, 0.0),
+    (5, 8, 1000, 1500, 64, True, True, False, 0.0),
+    (8, 8, 640, 640, 64, True, False, True, 5.0),
+    (10, 16, 512, 700, 64, False, True, False, 0.0),    # more items than SMs: the plain mapping, items from a queue
 ]
 
 
@@ -470,7 +478,8 @@ def test_sm_limit_changes_the_launch_width_not_the_results(ctx):
     must leave forward and backward results bit-identical; 0 restores the default."""
     import torch
     g = torch.Generator(device="cuda").manual_seed(4)
-    q, k, v, do = ((torch.randn((2, 4, 1024, 64), generator=g, device="cuda") * 0.5).bfloat16() for _ in range(4))
+    # (4 x 40 pairs of 512 queries: 160 work items of the persistent forward kernel, more than there are SMs)
+    q, k, v, do = ((torch.randn((4, 40, 512, 64), generator=g, device="cuda") * 0.5).bfloat16() for _ in range(4))
     o, lse = ctx.attn_fwd(q, k, v, causal=True)
     grads = ctx.attn_bwd(q, k, v, o, lse, do, causal=True, deterministic=True)
     fused = ctx.attn_bwd(q, k, v, o, lse, do, causal=True)
