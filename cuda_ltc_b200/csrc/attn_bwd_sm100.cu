@@ -1022,7 +1022,13 @@ attn_bwd_dkv4_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 if (linear < 0) break;
                 int k0, h, b, kvlen, j_begin;
                 const int n_it = item_steps(linear, k0, h, b, kvlen, j_begin);
-                if (n_it == 0) continue;
+                if (n_it == 0) {
+                    // An item without work does not carry the deferred accumulation along: the elementwise warps
+                    // wait for it at the end of the item before, so they take no further queue entry, and after
+                    // kItemSlots empty items in a row the queue would stand still with this thread waiting on it.
+                    if (pending) do_acc();
+                    continue;
+                }
                 const int r = na & 1;
                 ok = mbar_wait(bar_res_full(r), (uint32_t)((na >> 1) & 1), wc, 0xb0);
                 const uint64_t a_desc = res_desc + (uint64_t)((r * 2 * kBigTile) >> 4);
@@ -1513,11 +1519,14 @@ attn_bwd_fused_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 if (linear < 0) break;
                 int k0, h, b, kvlen, j_begin;
                 const int n_it = item_steps(linear, k0, h, b, kvlen, j_begin);
-                if (n_it == 0) continue;
-                // the previous item's last accumulation reads K / V of that item: it goes out before the wait
-                // for this item's tiles, which arrive only after that accumulation has released the buffer
+                // The previous item's last accumulation reads K / V of that item: it goes out before the wait
+                // for this item's tiles, which arrive only after that accumulation has released the buffer - and
+                // before an item without work is skipped: the elementwise warps wait for it at the end of the
+                // item before, so they take no further queue entry, and after kItemSlots empty items in a row
+                // the queue would stand still with this thread waiting on it.
                 if (pending) do_acc();
                 if (!ok) break;
+                if (n_it == 0) continue;
                 ok = mbar_wait(bar_res_full, (uint32_t)(na & 1), wc, 0xf0);
                 for (int it = 0; it < n_it && ok; ++it, ++g) {
                     ok = mbar_wait(bar_ring_full(slot_of(g)), phase_of(g), wc, 0xf2);

@@ -498,3 +498,32 @@ def test_sm_limit_changes_the_launch_width_not_the_results(ctx):
     # the fused backward: dK and dV bit-identical, dQ up to the rounding of its unordered fp32 sum
     assert torch.equal(fused[1], fused2[1]) and torch.equal(fused[2], fused2[2])
     assert ((fused[0].float() - fused2[0].float()).abs() <= 2.0 ** -7 * fused2[0].float().abs() + 1e-6).all()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("deterministic", [False, True])
+def test_backward_with_runs_of_empty_work_items(ctx, deterministic):
+    """More work items than SMs, most of them without work (short key lengths in four of five batch entries, and
+    more queries than keys under a causal mask): the persistent backward kernels skip long runs of empty items
+    behind an item with work, whose last accumulation must not wait for the next item with work."""
+    B, H, Sq, Sk, D = 5, 11, 1062, 865, 64
+    q, k, v, do = make_case(B, H, Sq, Sk, D, 610, 0.5)
+    qr, kr, vr, dor = bf16_round(q), bf16_round(k), bf16_round(v), bf16_round(do)
+    L = np.array([865, 40, 130, 20, 7], dtype=np.int32)
+    sc = 1.0 / math.sqrt(D)
+    o_ref, lse_ref = oracle.attn_fwd(qr, kr, vr, sc, True, None, L, 0.0)
+    ref = oracle.attn_bwd(qr, kr, vr, dor, sc, True, None, L, 0.0)
+    tq, tk, tv, tdo = (dev(x, torch.bfloat16) for x in (q, k, v, do))
+    dL = torch.from_numpy(L).cuda()
+    o, lse = ctx.attn_fwd(tq, tk, tv, scale=sc, causal=True, kv_len=dL, mode=_lib.MODE_BF16)
+    grads = ctx.attn_bwd(tq, tk, tv, o, lse, tdo, scale=sc, causal=True, kv_len=dL, mode=_lib.MODE_BF16,
+                         deterministic=deterministic)
+    torch.cuda.synchronize()
+    assert ctx.device_status() == 0
+    # (bf16 storage: the stored result carries one more rounding, as in test_tensor_pipe_backward)
+    assert (np.abs(o.float().cpu().numpy() - o_ref) <= TC_MAX_ABS + np.abs(o_ref) * 2.0 ** -8).all()
+    for got, want in zip(grads, ref):
+        gh = got.float().cpu().numpy().astype(np.float64)
+        allowed = TC_MAX_ABS * max(1.0, float(np.abs(want).max())) + np.abs(want) * 2.0 ** -8
+        assert (np.abs(gh - want) <= allowed).all()
+        assert rel_l2(gh, want) < 2 * (TC_REL_L2 + 2.0 ** -9)
