@@ -52,6 +52,42 @@ def test_streaming_kernels_random_shapes(ctx):
         done += 1
 
 
+def test_streaming_kernels_random_shapes_many_pairs(ctx):
+    """The same with enough (batch, head) pairs that the persistent kernels hold more work items than there are SMs
+    and every CTA walks through several of them, many without work: short key lengths in most batch entries, more
+    queries than keys under the causal mask.  bf16 or fp32 storage."""
+    import torch
+    from cuda_ltc_b200 import _lib
+    rng = np.random.default_rng(404)
+    done = 0
+    while done < 14:
+        B, H = int(rng.integers(2, 6)), int(rng.integers(8, 17))
+        Sq, Sk = int(rng.integers(300, 1300)), int(rng.integers(300, 1300))
+        if B * H * Sq * Sk > 6e7:
+            continue
+        causal = bool(rng.integers(0, 2))
+        L = None
+        if rng.random() < 0.7:
+            L = np.where(rng.random(B) < 0.7, rng.integers(1, 130, size=B), rng.integers(1, Sk + 1, size=B)).astype(np.int32)
+        q, k, v, do = (bf16_round((rng.standard_normal((B, H, S, 64)) * 0.5).astype(np.float32))
+                       for S in (Sq, Sk, Sk, Sq))
+        o_ref, _ = oracle.attn_fwd(q, k, v, 0.125, causal, None, L, 0.0)
+        ref = oracle.attn_bwd(q, k, v, do, 0.125, causal, None, L, 0.0)
+        dt = torch.float32 if rng.random() < 0.35 else torch.bfloat16
+        tq, tk, tv, tdo = (_dev(a, dt) for a in (q, k, v, do))
+        kw = dict(scale=0.125, causal=causal, kv_len=_dev(L), mode=_lib.MODE_BF16)
+        o, lse = ctx.attn_fwd(tq, tk, tv, **kw)
+        what = (B, H, Sq, Sk, causal, None if L is None else L.tolist(), str(dt))
+        assert np.abs(o.float().cpu().numpy() - o_ref).max() < 1.2e-2, what
+        for det in (False, True):
+            grads = ctx.attn_bwd(tq, tk, tv, o, lse, tdo, deterministic=det, **kw)
+            torch.cuda.synchronize()
+            assert ctx.device_status() == 0, what
+            for g, r in zip(grads, ref):
+                assert np.abs(g.float().cpu().numpy() - r).max() <= 1.2e-2 * max(1.0, np.abs(r).max()), (what, det)
+        done += 1
+
+
 def test_written_out_scores_random_shapes(ctx):
     """Every head width that is a multiple of 8, fp32 storage, the bf16 and the split-precision mode, all mask
     kinds and a clamp.  The bf16 mode is compared on bf16-rounded inputs (with a clamp, a score at the threshold
