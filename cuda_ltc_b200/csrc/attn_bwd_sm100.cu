@@ -96,6 +96,8 @@ __device__ __forceinline__ void load8(const float* p, float (&f)[8]) {
 
 template <typename T>
 __global__ void __launch_bounds__(256) attn_bwd_stats_kernel(const StatsArgs a) {
+    grid_launch_dependents();
+    grid_dependency_wait();
     const int64_t row = (int64_t)blockIdx.x * 32 + (threadIdx.x >> 3);
     const int sub = threadIdx.x & 7;
     const int64_t total = (int64_t)a.B * a.H * a.Sq_pad;
@@ -237,7 +239,10 @@ attn_bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
     const int h = blockIdx.y, b = blockIdx.z;
 
     int kvlen = a.Sk;
-    if (a.kv_len) kvlen = min(max(a.kv_len[b], 0), a.Sk);
+    if (a.kv_len) {
+        grid_dependency_wait();                // the lengths may come from the kernel before this one
+        kvlen = min(max(a.kv_len[b], 0), a.Sk);
+    }
     int n_steps[2];
 #pragma unroll
     for (int t = 0; t < 2; ++t) {
@@ -270,6 +275,8 @@ attn_bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
     tc_fence_after_sync();
     const uint32_t tmem_base = misc[0];
     const WaitCtx wc{&misc[1], a.status};
+    grid_launch_dependents();                  // (set up: the next kernel may place its CTAs)
+    grid_dependency_wait();                    // the operands are complete once the kernel before this one has ended
     auto slot_of = [&](int item) { return item % L::kStages; };
     auto phase_of = [&](int item) { return (uint32_t)((item / L::kStages) & 1); };
     LTCA_TRACE_DECL(LTCA_TRACE_KERNEL == 1 && blockIdx.x == 0 && blockIdx.y == 5 && blockIdx.z == 0);
@@ -528,7 +535,10 @@ attn_bwd_dkv_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
     const int h = blockIdx.y, b = blockIdx.z;
 
     int kvlen = a.Sk;
-    if (a.kv_len) kvlen = min(max(a.kv_len[b], 0), a.Sk);
+    if (a.kv_len) {
+        grid_dependency_wait();                // the lengths may come from the kernel before this one
+        kvlen = min(max(a.kv_len[b], 0), a.Sk);
+    }
     const int n_q = (a.Sq + kStep - 1) / kStep;     // query steps in total
     int j_begin[2];                                 // first query step that can see the tile's keys
     bool active[2];
@@ -562,6 +572,8 @@ attn_bwd_dkv_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
     tc_fence_after_sync();
     const uint32_t tmem_base = misc[0];
     const WaitCtx wc{&misc[1], a.status};
+    grid_launch_dependents();                  // (set up: the next kernel may place its CTAs)
+    grid_dependency_wait();                    // the operands are complete once the kernel before this one has ended
     // ring items are numbered from the first streamed step of this CTA
     auto slot_of = [&](int j) { return (j - j_first) % L::kStages; };
     auto phase_of = [&](int j) { return (uint32_t)(((j - j_first) / L::kStages) & 1); };
@@ -925,6 +937,8 @@ attn_bwd_dkv4_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
     tc_fence_after_sync();
     const uint32_t tmem_base = misc[0];
     const WaitCtx wc{&misc[1], a.status};
+    grid_launch_dependents();                  // (set up: the next kernel may place its CTAs)
+    grid_dependency_wait();                    // the operands are complete once the kernel before this one has ended
     auto slot_of = [&](int g) { return g % L::kStages; };
     auto phase_of = [&](int g) { return (uint32_t)((g / L::kStages) & 1); };
     // the item's key tile, first query step that can see it and number of query steps (0: none)
@@ -1393,6 +1407,8 @@ attn_bwd_fused_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
     tc_fence_after_sync();
     const uint32_t tmem_base = misc[0];
     const WaitCtx wc{&misc[1], a.status};
+    grid_launch_dependents();                  // (set up: the next kernel may place its CTAs)
+    grid_dependency_wait();                    // the operands are complete once the kernel before this one has ended
     auto slot_of = [&](int g) { return g % L::kStages; };
     auto phase_of = [&](int g) { return (uint32_t)((g / L::kStages) & 1); };
     // the item's key tile, first query step that can see it and number of query steps (0: none)
@@ -1843,6 +1859,8 @@ attn_bwd_fused_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
 __global__ void __launch_bounds__(256) attn_bwd_dq_convert_kernel(const float* __restrict__ acc, void* dq,
                                                                   ltca_strides dqs, int B, int H, int Sq, int Sq_pad,
                                                                   float scale) {
+    grid_launch_dependents();
+    grid_dependency_wait();
     const int64_t idx = (int64_t)blockIdx.x * 32 + (threadIdx.x >> 3);       // row among B * H * Sq
     const int sub = threadIdx.x & 7;
     if (idx >= (int64_t)B * H * Sq) return;
@@ -1944,6 +1962,8 @@ attn_bwd_dq4_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
     tc_fence_after_sync();
     const uint32_t tmem_base = misc[0];
     const WaitCtx wc{&misc[1], a.status};
+    grid_launch_dependents();                  // (set up: the next kernel may place its CTAs)
+    grid_dependency_wait();                    // the operands are complete once the kernel before this one has ended
     auto slot_of = [&](int g) { return g % L::kStages; };
     auto phase_of = [&](int g) { return (uint32_t)((g / L::kStages) & 1); };
     // tensor-memory column of the dS buffer of step g: 256, 384, 448 in turn
@@ -2331,13 +2351,14 @@ int launch_main(ltca_ctx* ctx, const ltca_attn_params* p, const void* q, const v
             if ((rc = make_tmap_bhsd(ctx, &tdv, p->dv, 2, p->B, p->H, p->Sk, kD, p->dv_strides, 64, kTile))) return rc;
             const ltca_strides accs{(int64_t)p->H * a.Sq_pad * kD, (int64_t)a.Sq_pad * kD, kD};
             if ((rc = make_tmap_bhsd(ctx, &tacc, dq_acc, 4, p->B, p->H, a.Sq_pad, kD, accs, 32, kTile))) return rc;
-            attn_bwd_fused_sm100_kernel<<<n_cta, kThreads, FusedSmem::kDynBytes, ctx->stream>>>(
-                tq128, tdo128, tk128, tv128, tdk, tdv, tacc, a, ig);
+            LTCA_CUDA_OK(ctx, launch_dependent(attn_bwd_fused_sm100_kernel, dim3(n_cta), dim3(kThreads), FusedSmem::kDynBytes,
+                                               ctx->stream, tq128, tdo128, tk128, tv128, tdk, tdv, tacc, a, ig));
             LTCA_LAUNCH_OK(ctx, "attn_bwd_fused_sm100_kernel");
             kernel_timing_mark(ctx, 2);
             const int64_t rows = (int64_t)p->B * p->H * p->Sq;
-            attn_bwd_dq_convert_kernel<<<(unsigned)((rows + 31) / 32), 256, 0, ctx->stream>>>(
-                dq_acc, p->dq, p->dq_strides, p->B, p->H, p->Sq, a.Sq_pad, p->scale);
+            LTCA_CUDA_OK(ctx, launch_dependent(attn_bwd_dq_convert_kernel, dim3((unsigned)((rows + 31) / 32)), dim3(256), 0,
+                                               ctx->stream, (const float*)dq_acc, p->dq, p->dq_strides, p->B, p->H, p->Sq,
+                                               a.Sq_pad, p->scale));
             LTCA_LAUNCH_OK(ctx, "attn_bwd_dq_convert_kernel");
             kernel_timing_mark(ctx, 3);
             return LTCA_OK;
@@ -2362,15 +2383,15 @@ int launch_main(ltca_ctx* ctx, const ltca_attn_params* p, const void* q, const v
             const int n_cta = ig.n_items < ctx->sm_count ? ig.n_items : ctx->sm_count;
             CUtensorMap tdq;
             if ((rc = make_tmap_bhsd(ctx, &tdq, p->dq, 2, p->B, p->H, p->Sq, kD, p->dq_strides, 64, kTile))) return rc;
-            attn_bwd_dq4_sm100_kernel<<<n_cta, kThreads, Dq4Smem::kDynBytes, ctx->stream>>>(tq128, tdo128, tk128,
-                                                                                            tv128, tdq, a, ig);
+            LTCA_CUDA_OK(ctx, launch_dependent(attn_bwd_dq4_sm100_kernel, dim3(n_cta), dim3(kThreads), Dq4Smem::kDynBytes,
+                                               ctx->stream, tq128, tdo128, tk128, tv128, tdq, a, ig));
             LTCA_LAUNCH_OK(ctx, "attn_bwd_dq4_sm100_kernel");
             dq_launched = true;
         }
     }
     if (!dq_launched) {
         dim3 gq((p->Sq + 2 * kTile - 1) / (2 * kTile), p->H, p->B);
-        kdq<<<gq, kThreads, DqSmem::kDynBytes, ctx->stream>>>(tq128, tdo128, tk64, tv64, a);
+        LTCA_CUDA_OK(ctx, launch_dependent(kdq, gq, dim3(kThreads), DqSmem::kDynBytes, ctx->stream, tq128, tdo128, tk64, tv64, a));
         LTCA_LAUNCH_OK(ctx, "attn_bwd_dq_sm100_kernel");
     }
     kernel_timing_mark(ctx, 2);
@@ -2389,15 +2410,15 @@ int launch_main(ltca_ctx* ctx, const ltca_attn_params* p, const void* q, const v
             CUtensorMap tdk, tdv;
             if ((rc = make_tmap_bhsd(ctx, &tdk, p->dk, 2, p->B, p->H, p->Sk, kD, p->dk_strides, 64, kTile))) return rc;
             if ((rc = make_tmap_bhsd(ctx, &tdv, p->dv, 2, p->B, p->H, p->Sk, kD, p->dv_strides, 64, kTile))) return rc;
-            attn_bwd_dkv4_sm100_kernel<<<n_cta, kThreads, Dkv4Smem::kDynBytes, ctx->stream>>>(tq128, tdo128, tk128,
-                                                                                             tv128, tdk, tdv, a, ig);
+            LTCA_CUDA_OK(ctx, launch_dependent(attn_bwd_dkv4_sm100_kernel, dim3(n_cta), dim3(kThreads), Dkv4Smem::kDynBytes,
+                                               ctx->stream, tq128, tdo128, tk128, tv128, tdk, tdv, a, ig));
             LTCA_LAUNCH_OK(ctx, "attn_bwd_dkv4_sm100_kernel");
             kernel_timing_mark(ctx, 3);
             return LTCA_OK;
         }
     }
     dim3 gk((p->Sk + 2 * kTile - 1) / (2 * kTile), p->H, p->B);
-    kdkv<<<gk, kThreads, DkvSmem::kDynBytes, ctx->stream>>>(tq64, tdo64, tk128, tv128, a);
+    LTCA_CUDA_OK(ctx, launch_dependent(kdkv, gk, dim3(kThreads), DkvSmem::kDynBytes, ctx->stream, tq64, tdo64, tk128, tv128, a));
     LTCA_LAUNCH_OK(ctx, "attn_bwd_dkv_sm100_kernel");
     kernel_timing_mark(ctx, 3);
     return LTCA_OK;
@@ -2445,8 +2466,10 @@ int launch_attn_bwd_sm100(ltca_ctx* ctx, const ltca_attn_params* p) {
     const int64_t rows = (int64_t)p->B * p->H * s.Sq_pad;
     const unsigned blocks = (unsigned)((rows + 31) / 32);
     kernel_timing_mark(ctx, 0);
-    if (p->dtype == LTCA_BF16) attn_bwd_stats_kernel<__nv_bfloat16><<<blocks, 256, 0, ctx->stream>>>(s);
-    else attn_bwd_stats_kernel<float><<<blocks, 256, 0, ctx->stream>>>(s);
+    if (p->dtype == LTCA_BF16)
+        LTCA_CUDA_OK(ctx, launch_dependent(attn_bwd_stats_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, ctx->stream, s));
+    else
+        LTCA_CUDA_OK(ctx, launch_dependent(attn_bwd_stats_kernel<float>, dim3(blocks), dim3(256), 0, ctx->stream, s));
     LTCA_LAUNCH_OK(ctx, "attn_bwd_stats_kernel");
     if (p->dtype == LTCA_BF16) kernel_timing_mark(ctx, 1);
 

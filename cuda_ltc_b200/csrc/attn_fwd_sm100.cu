@@ -134,7 +134,10 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
     const int b = blockIdx.z;
 
     int kvlen = a.Sk;
-    if (a.kv_len) kvlen = min(max(a.kv_len[b], 0), a.Sk);
+    if (a.kv_len) {
+        grid_dependency_wait();                // the lengths may come from the kernel before this one
+        kvlen = min(max(a.kv_len[b], 0), a.Sk);
+    }
     int n_tiles[2];
 #pragma unroll
     for (int t = 0; t < 2; ++t) {
@@ -176,6 +179,8 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
     const WaitCtx wc{&misc[1], a.status};
     LTCA_TRACE_DECL(blockIdx.x == 0 && blockIdx.y == 5 && blockIdx.z == 0);
     LTCA_TRACE_EVT(0x01);
+    grid_launch_dependents();                  // (set up: the next kernel may place its CTAs)
+    grid_dependency_wait();                    // q, k, v are complete once the kernel before this one has ended
 
     if (warp >= kMathWarps) {
         reg_dealloc<kCtrlRegs>();
@@ -630,6 +635,8 @@ attn_fwd4p_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
     tc_fence_after_sync();
     const uint32_t tmem_base = misc[0];
     const WaitCtx wc{&misc[1], a.status};
+    grid_launch_dependents();                  // (set up: the next kernel may place its CTAs)
+    grid_dependency_wait();                    // the operands are complete once the kernel before this one has ended
 
     // the item's block, its (head, batch), and the number of 64-key steps of each tile
     struct Item { int m_block, h, b, kvlen, n_max; };
@@ -1071,8 +1078,12 @@ int launch_fwd4(ltca_ctx* ctx, const ltca_attn_params* p, const void* q, const v
     // (measured: B=1 H=16 S=4096, the bench workload dealt over eight GPUs: 92 us folded against 123 us)
     ig.fold = (a.causal && ig.nblk > 1 && ig.n_items <= ctx->sm_count) ? 1 : 0;
     const int n_cta = ig.n_items < ctx->sm_count ? ig.n_items : ctx->sm_count;
-    if (ig.fold) attn_fwd4p_sm100_kernel<true><<<n_cta, kF4Threads, P::kDynBytes, ctx->stream>>>(tq, tk, tv, to, a, ig);
-    else attn_fwd4p_sm100_kernel<false><<<n_cta, kF4Threads, P::kDynBytes, ctx->stream>>>(tq, tk, tv, to, a, ig);
+    if (ig.fold)
+        LTCA_CUDA_OK(ctx, launch_dependent(attn_fwd4p_sm100_kernel<true>, dim3(n_cta), dim3(kF4Threads), P::kDynBytes,
+                                           ctx->stream, tq, tk, tv, to, a, ig));
+    else
+        LTCA_CUDA_OK(ctx, launch_dependent(attn_fwd4p_sm100_kernel<false>, dim3(n_cta), dim3(kF4Threads), P::kDynBytes,
+                                           ctx->stream, tq, tk, tv, to, a, ig));
     LTCA_LAUNCH_OK(ctx, "attn_fwd4p_sm100_kernel");
     return LTCA_OK;
 }
@@ -1128,7 +1139,7 @@ int launch_fwd(ltca_ctx* ctx, const ltca_attn_params* p, const void* q, const vo
     static SmemOptIn opt_in;                  // one per template instantiation
     LTCA_CUDA_OK(ctx, opt_in_dynamic_smem(opt_in, ctx->device, kern, L::kDynBytes));
     dim3 grid((p->Sq + 2 * kBlockM - 1) / (2 * kBlockM), p->H, p->B);
-    kern<<<grid, kFwdThreads, L::kDynBytes, ctx->stream>>>(tq, tk, tv, a);
+    LTCA_CUDA_OK(ctx, launch_dependent(kern, grid, dim3(kFwdThreads), L::kDynBytes, ctx->stream, tq, tk, tv, a));
     LTCA_LAUNCH_OK(ctx, "attn_fwd_sm100_kernel");
     return LTCA_OK;
 }

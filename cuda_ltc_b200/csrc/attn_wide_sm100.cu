@@ -19,6 +19,7 @@
 #include "host_common.h"
 #include "gemm_sm100.h"
 #include "attn_wide.h"
+#include "sm100_ptx.cuh"
 
 namespace ltca {
 
@@ -54,6 +55,8 @@ struct SoftmaxArgs {
 // One warp per (batch, head, query) row: scale, clamp (the reference clamps scaled scores at 10,
 // src/ml/flash_attention.cu:167), visibility (keep-mask value 0 hides, :161-164; causal; key lengths), softmax.
 __global__ void __launch_bounds__(256) wide_softmax_fwd_kernel(const SoftmaxArgs a) {
+    grid_launch_dependents();
+    grid_dependency_wait();
     const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     if (row >= (int64_t)a.B * a.H * a.Sq) return;
@@ -100,6 +103,8 @@ __global__ void __launch_bounds__(256) wide_softmax_fwd_kernel(const SoftmaxArgs
 
 // dS = scale * P o (dP - sum_j P dP), zero where the score was clamped; written to dS (P itself by default).
 __global__ void __launch_bounds__(256) wide_softmax_bwd_kernel(const SoftmaxArgs a) {
+    grid_launch_dependents();
+    grid_dependency_wait();
     const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     if (row >= (int64_t)a.B * a.H * a.Sq) return;
@@ -139,6 +144,8 @@ __device__ __forceinline__ void unpack4_bf16(uint2 w, float* v) {
 // (kChunks groups of four neighbouring columns), so every matrix is read once, 16 bytes per lane and access.
 template <int kChunks>
 __global__ void __launch_bounds__(256) wide_softmax_fwd_rows_kernel(const SoftmaxArgs a) {
+    grid_launch_dependents();
+    grid_dependency_wait();
     const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     if (row >= (int64_t)a.B * a.H * a.Sq) return;
@@ -202,6 +209,8 @@ __global__ void __launch_bounds__(256) wide_softmax_fwd_rows_kernel(const Softma
 
 template <int kChunks>
 __global__ void __launch_bounds__(256) wide_softmax_bwd_rows_kernel(const SoftmaxArgs a) {
+    grid_launch_dependents();
+    grid_dependency_wait();
     const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     if (row >= (int64_t)a.B * a.H * a.Sq) return;
@@ -384,10 +393,11 @@ int wide_attn_fwd(ltca_ctx* ctx, const WideArgs& w) {
     const unsigned sblocks = (unsigned)((rows + 7) / 8);
     // rows of the scratch matrices start on 32 bytes (pitch a multiple of 8, bases from the 256-byte aligned carve)
     const bool vec = softmax_rows_aligned(sa);
-    if (vec && Skp <= 256) wide_softmax_fwd_rows_kernel<2><<<sblocks, 256, 0, ctx->stream>>>(sa);
-    else if (vec && Skp <= 512) wide_softmax_fwd_rows_kernel<4><<<sblocks, 256, 0, ctx->stream>>>(sa);
-    else if (vec && Skp <= 1024) wide_softmax_fwd_rows_kernel<8><<<sblocks, 256, 0, ctx->stream>>>(sa);
-    else wide_softmax_fwd_kernel<<<sblocks, 256, 0, ctx->stream>>>(sa);
+    auto fwd_kernel = wide_softmax_fwd_kernel;
+    if (vec && Skp <= 256) fwd_kernel = wide_softmax_fwd_rows_kernel<2>;
+    else if (vec && Skp <= 512) fwd_kernel = wide_softmax_fwd_rows_kernel<4>;
+    else if (vec && Skp <= 1024) fwd_kernel = wide_softmax_fwd_rows_kernel<8>;
+    LTCA_CUDA_OK(ctx, launch_dependent(fwd_kernel, dim3(sblocks), dim3(256), 0, ctx->stream, sa));
     LTCA_LAUNCH_OK(ctx, "wide_softmax_fwd_kernel");
     if (!w.o) return LTCA_OK;
     // O = P V : P stored [Sq, Sk] (K-major), V stored [Sk, D] (N-major); terms hi hi, lo hi, hi lo
@@ -430,10 +440,11 @@ int wide_attn_bwd(ltca_ctx* ctx, const WideArgs& w) {
     const unsigned sblocks = (unsigned)((rows + 7) / 8);
     const bool vec = softmax_rows_aligned(sa) && (reinterpret_cast<uintptr_t>(sa.dP) & 15) == 0 &&
                      (reinterpret_cast<uintptr_t>(sa.dS) & 7) == 0 && (reinterpret_cast<uintptr_t>(sa.dSlo) & 7) == 0;
-    if (vec && Skp <= 256) wide_softmax_bwd_rows_kernel<2><<<sblocks, 256, 0, ctx->stream>>>(sa);
-    else if (vec && Skp <= 512) wide_softmax_bwd_rows_kernel<4><<<sblocks, 256, 0, ctx->stream>>>(sa);
-    else if (vec && Skp <= 1024) wide_softmax_bwd_rows_kernel<8><<<sblocks, 256, 0, ctx->stream>>>(sa);
-    else wide_softmax_bwd_kernel<<<sblocks, 256, 0, ctx->stream>>>(sa);
+    auto bwd_kernel = wide_softmax_bwd_kernel;
+    if (vec && Skp <= 256) bwd_kernel = wide_softmax_bwd_rows_kernel<2>;
+    else if (vec && Skp <= 512) bwd_kernel = wide_softmax_bwd_rows_kernel<4>;
+    else if (vec && Skp <= 1024) bwd_kernel = wide_softmax_bwd_rows_kernel<8>;
+    LTCA_CUDA_OK(ctx, launch_dependent(bwd_kernel, dim3(sblocks), dim3(256), 0, ctx->stream, sa));
     LTCA_LAUNCH_OK(ctx, "wide_softmax_bwd_kernel");
     {   // dQ = dS K : dS K-major, K stored [Sk, D] = [K, N]
         Mat a[3] = {{sa.dS, Skp, 0, mat, mat_b}, {sa.dSlo, Skp, 0, mat, mat_b}, {sa.dS, Skp, 0, mat, mat_b}};

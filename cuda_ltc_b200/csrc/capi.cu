@@ -87,6 +87,8 @@ struct PackJobs {
     int S[kMaxPackJobs];
 };
 __global__ void pack_bf16_kernel(const __grid_constant__ PackJobs jobs, int BH, int H, int D) {
+    grid_launch_dependents();
+    grid_dependency_wait();
     const int j = blockIdx.y;
     const float* __restrict__ src = jobs.src[j];
     __nv_bfloat16* __restrict__ dst = jobs.dst[j];
@@ -379,7 +381,8 @@ int pack_many_to_bf16(ltca_ctx* ctx, const PackJob* jobs, int count, int B, int 
     int bx = blocks_for(n4, 256, ctx->sm_count);
     const int cap = (ctx->sm_count > 0 ? ctx->sm_count : kPlanSms) * 16 / count;
     if (bx > cap) bx = cap;
-    pack_bf16_kernel<<<dim3((unsigned)bx, (unsigned)count), 256, 0, ctx->stream>>>(k, B * H, H, D);
+    LTCA_CUDA_OK(ctx, launch_dependent(pack_bf16_kernel, dim3((unsigned)bx, (unsigned)count), dim3(256), 0, ctx->stream, k,
+                                       B * H, H, D));
     LTCA_LAUNCH_OK(ctx, "pack_bf16_kernel");
     return LTCA_OK;
 }

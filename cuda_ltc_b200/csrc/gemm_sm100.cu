@@ -143,6 +143,10 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap ta0, const __grid_con
     const uint32_t tmem_base = misc[0];
     const WaitCtx wc{&misc[1], g.status};
     LTCA_TRACE_EVT(0x02);
+    // barriers and tensor memory are set up: the kernel after this one may place its CTAs; this one's operands are
+    // complete once the kernel before it has ended
+    grid_launch_dependents();
+    grid_dependency_wait();
 
     if (warp == 0) {
         if (lane == 0) {
@@ -441,6 +445,8 @@ namespace {
 // C[problem][i] = sum over slices of partial[problem][slice][i], in slice order.
 __global__ void gemm_splitk_reduce_kernel(const float* __restrict__ partial, float* c0, float* c1, float* c2,
                                           int64_t mn, int ksplit) {
+    grid_launch_dependents();
+    grid_dependency_wait();
     const int problem = blockIdx.y;
     float* c = problem == 0 ? c0 : (problem == 1 ? c1 : c2);
     const float* p = partial + (int64_t)problem * ksplit * mn;
@@ -481,6 +487,8 @@ struct CvtMany {
     int n;
 };
 __global__ void cvt_many_bf16_kernel(const __grid_constant__ CvtMany b) {
+    grid_launch_dependents();
+    grid_dependency_wait();
     const uint32_t total = b.start4[b.n];
     for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
         int m = 0;
@@ -590,7 +598,8 @@ int gemm_sm100(ltca_ctx* ctx, const GemmProblem& gp) {
     const bool amn = gp.a[0].mn_major != 0, bmn = gp.b[0].mn_major != 0;
     auto launch = [&](auto kern) -> int {
         LTCA_CUDA_OK(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kDynBytes));
-        kern<<<grid, kGemmThreads, kDynBytes, ctx->stream>>>(ta[0], ta[1], ta[2], tb[0], tb[1], tb[2], tc[0], tc[1], tc[2], g);
+        LTCA_CUDA_OK(ctx, launch_dependent(kern, grid, dim3(kGemmThreads), kDynBytes, ctx->stream, ta[0], ta[1], ta[2], tb[0],
+                                           tb[1], tb[2], tc[0], tc[1], tc[2], g));
         LTCA_LAUNCH_OK(ctx, "gemm_bf16_sm100_kernel");
         return LTCA_OK;
     };
@@ -602,9 +611,10 @@ int gemm_sm100(ltca_ctx* ctx, const GemmProblem& gp) {
     if (g.ksplit > 1) {
         const int64_t mn = (int64_t)gp.M * gp.N;
         dim3 rg((unsigned)((mn + 255) / 256 < 1184 ? (mn + 255) / 256 : 1184), gp.n_problems);
-        gemm_splitk_reduce_kernel<<<rg, 256, 0, ctx->stream>>>(
-            gp.partial, reinterpret_cast<float*>(gp.c[0]), reinterpret_cast<float*>(gp.c[gp.n_problems > 1 ? 1 : 0]),
-            reinterpret_cast<float*>(gp.c[gp.n_problems > 2 ? 2 : 0]), mn, g.ksplit);
+        LTCA_CUDA_OK(ctx, launch_dependent(gemm_splitk_reduce_kernel, rg, dim3(256), 0, ctx->stream, (const float*)gp.partial,
+                                           reinterpret_cast<float*>(gp.c[0]),
+                                           reinterpret_cast<float*>(gp.c[gp.n_problems > 1 ? 1 : 0]),
+                                           reinterpret_cast<float*>(gp.c[gp.n_problems > 2 ? 2 : 0]), mn, g.ksplit));
         LTCA_LAUNCH_OK(ctx, "gemm_splitk_reduce_kernel");
     }
     return LTCA_OK;
@@ -667,7 +677,7 @@ int convert_many_bf16(ltca_ctx* ctx, int n, const float* const* src, const int64
     if (b.n == 0) return LTCA_OK;
     b.start4[b.n] = (uint32_t)total;
     const unsigned blocks = (unsigned)((total + 255) / 256 < 2368 ? (total + 255) / 256 : 2368);
-    cvt_many_bf16_kernel<<<blocks, 256, 0, ctx->stream>>>(b);
+    LTCA_CUDA_OK(ctx, launch_dependent(cvt_many_bf16_kernel, dim3(blocks), dim3(256), 0, ctx->stream, b));
     LTCA_LAUNCH_OK(ctx, "cvt_many_bf16_kernel");
     return LTCA_OK;
 }

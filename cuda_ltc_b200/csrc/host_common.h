@@ -138,6 +138,27 @@ inline int make_tmap_bhsd(ltca_ctx* ctx, CUtensorMap* map, const void* base, int
 
 }  // namespace ltca
 
+// Launch with programmatic stream serialisation: the kernel's CTAs may be placed while the kernel before it in the
+// stream is still running; the kernel itself waits (grid_dependency_wait) before it touches global memory.
+namespace ltca {
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_dependent(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                    Args&&... args) {
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
+}
+}  // namespace ltca
+
 // Kernel launchers implemented in the .cu files of this directory (internal, not exported).
 namespace ltca {
 int launch_attn_fwd_sm100(ltca_ctx* ctx, const ltca_attn_params* p);

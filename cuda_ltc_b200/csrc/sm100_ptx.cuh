@@ -107,6 +107,15 @@ __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, co
     return __all_sync(0xffffffffu, mbar_wait(bar, parity, w, where));
 }
 
+// ---- programmatic dependent launch -----------------------------------------------------------
+// A kernel launched with the stream-serialisation attribute (launch_dependent, host_common.h) may start while the
+// kernel before it in the stream is still running.  grid_dependency_wait() holds the thread until that kernel has
+// completed and its writes are visible: everything that reads or writes global memory comes after it (it does
+// nothing in a launch without the attribute).  grid_launch_dependents() lets the kernel AFTER this one start its
+// CTAs as soon as every CTA of this one has called it (or exited).
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---- TMA ------------------------------------------------------------------------------------
 __device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tmap)) : "memory");

@@ -23,6 +23,7 @@
 #include "gemm_sm100.h"
 #include "attn_wide.h"
 #include "host_common.h"
+#include "sm100_ptx.cuh"
 
 namespace ltca {
 
@@ -212,6 +213,8 @@ __global__ void residual_layer_norm_kernel(const float* __restrict__ y, const fl
                                            const float* __restrict__ gamma,
                                            const float* __restrict__ beta, float* __restrict__ out,
                                            int64_t rows, int E, int use_res, int use_ln, float eps) {
+    grid_launch_dependents();
+    grid_dependency_wait();
     const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (row >= rows) return;
     const int lane = threadIdx.x & 31;
@@ -789,9 +792,9 @@ int tensor_forward(ltca_ctx* ctx, const ltca_tsa_params* t) {
     gp.ldc = t->E;
     if ((rc = gemm_sm100(ctx, gp))) return rc;
     const int wpb = 8;
-    residual_layer_norm_kernel<<<(unsigned)((pl.rows + wpb - 1) / wpb), wpb * 32, 0, ctx->stream>>>(
-        y, t->x, t->ln_gamma, t->ln_beta, t->out, pl.rows, t->E, t->use_residual, t->use_layer_norm,
-        1e-5f);
+    LTCA_CUDA_OK(ctx, launch_dependent(residual_layer_norm_kernel, dim3((unsigned)((pl.rows + wpb - 1) / wpb)), dim3(wpb * 32),
+                                       0, ctx->stream, (const float*)y, t->x, t->ln_gamma, t->ln_beta, t->out, pl.rows, t->E,
+                                       t->use_residual, t->use_layer_norm, 1e-5f));
     LTCA_LAUNCH_OK(ctx, "residual_layer_norm_kernel");
     return LTCA_OK;
 }
