@@ -937,7 +937,6 @@ attn_bwd_dkv4_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
     tc_fence_after_sync();
     const uint32_t tmem_base = misc[0];
     const WaitCtx wc{&misc[1], a.status};
-    grid_launch_dependents();                  // (set up: the next kernel may place its CTAs)
     grid_dependency_wait();                    // the operands are complete once the kernel before this one has ended
     auto slot_of = [&](int g) { return g % L::kStages; };
     auto phase_of = [&](int g) { return (uint32_t)((g / L::kStages) & 1); };
@@ -1288,6 +1287,9 @@ attn_bwd_dkv4_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
         }
     }
 
+    // Out of work: only now may the kernel after this one place its CTAs (released at the start, its blocks would
+    // sit beside this kernel's CTAs for the whole run, waiting for it to end).
+    grid_launch_dependents();
     tc_fence_before_sync();
     __syncthreads();
     if (threadIdx.x == 0) item_counters_release(grid.counters);
@@ -1407,7 +1409,6 @@ attn_bwd_fused_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
     tc_fence_after_sync();
     const uint32_t tmem_base = misc[0];
     const WaitCtx wc{&misc[1], a.status};
-    grid_launch_dependents();                  // (set up: the next kernel may place its CTAs)
     grid_dependency_wait();                    // the operands are complete once the kernel before this one has ended
     auto slot_of = [&](int g) { return g % L::kStages; };
     auto phase_of = [&](int g) { return (uint32_t)((g / L::kStages) & 1); };
@@ -1844,6 +1845,9 @@ attn_bwd_fused_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
         }
     }
 
+    // Out of work: only now may the kernel after this one place its CTAs (released at the start, its blocks would
+    // sit beside this kernel's CTAs for the whole run, waiting for it to end).
+    grid_launch_dependents();
     tc_fence_before_sync();
     __syncthreads();
     if (threadIdx.x == 0) item_counters_release(grid.counters);
@@ -1962,7 +1966,6 @@ attn_bwd_dq4_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
     tc_fence_after_sync();
     const uint32_t tmem_base = misc[0];
     const WaitCtx wc{&misc[1], a.status};
-    grid_launch_dependents();                  // (set up: the next kernel may place its CTAs)
     grid_dependency_wait();                    // the operands are complete once the kernel before this one has ended
     auto slot_of = [&](int g) { return g % L::kStages; };
     auto phase_of = [&](int g) { return (uint32_t)((g / L::kStages) & 1); };
@@ -2264,6 +2267,9 @@ attn_bwd_dq4_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
         }
     }
 
+    // Out of work: only now may the kernel after this one place its CTAs (released at the start, its blocks would
+    // sit beside this kernel's CTAs for the whole run, waiting for it to end).
+    grid_launch_dependents();
     tc_fence_before_sync();
     __syncthreads();
     if (threadIdx.x == 0) item_counters_release(grid.counters);
@@ -2351,12 +2357,12 @@ int launch_main(ltca_ctx* ctx, const ltca_attn_params* p, const void* q, const v
             if ((rc = make_tmap_bhsd(ctx, &tdv, p->dv, 2, p->B, p->H, p->Sk, kD, p->dv_strides, 64, kTile))) return rc;
             const ltca_strides accs{(int64_t)p->H * a.Sq_pad * kD, (int64_t)a.Sq_pad * kD, kD};
             if ((rc = make_tmap_bhsd(ctx, &tacc, dq_acc, 4, p->B, p->H, a.Sq_pad, kD, accs, 32, kTile))) return rc;
-            LTCA_CUDA_OK(ctx, launch_dependent(attn_bwd_fused_sm100_kernel, dim3(n_cta), dim3(kThreads), FusedSmem::kDynBytes,
+            LTCA_CUDA_OK(ctx, launch_dependent_if(small_attention_call(p), attn_bwd_fused_sm100_kernel, dim3(n_cta), dim3(kThreads), FusedSmem::kDynBytes,
                                                ctx->stream, tq128, tdo128, tk128, tv128, tdk, tdv, tacc, a, ig));
             LTCA_LAUNCH_OK(ctx, "attn_bwd_fused_sm100_kernel");
             kernel_timing_mark(ctx, 2);
             const int64_t rows = (int64_t)p->B * p->H * p->Sq;
-            LTCA_CUDA_OK(ctx, launch_dependent(attn_bwd_dq_convert_kernel, dim3((unsigned)((rows + 31) / 32)), dim3(256), 0,
+            LTCA_CUDA_OK(ctx, launch_dependent_if(small_attention_call(p), attn_bwd_dq_convert_kernel, dim3((unsigned)((rows + 31) / 32)), dim3(256), 0,
                                                ctx->stream, (const float*)dq_acc, p->dq, p->dq_strides, p->B, p->H, p->Sq,
                                                a.Sq_pad, p->scale));
             LTCA_LAUNCH_OK(ctx, "attn_bwd_dq_convert_kernel");
@@ -2383,7 +2389,7 @@ int launch_main(ltca_ctx* ctx, const ltca_attn_params* p, const void* q, const v
             const int n_cta = ig.n_items < ctx->sm_count ? ig.n_items : ctx->sm_count;
             CUtensorMap tdq;
             if ((rc = make_tmap_bhsd(ctx, &tdq, p->dq, 2, p->B, p->H, p->Sq, kD, p->dq_strides, 64, kTile))) return rc;
-            LTCA_CUDA_OK(ctx, launch_dependent(attn_bwd_dq4_sm100_kernel, dim3(n_cta), dim3(kThreads), Dq4Smem::kDynBytes,
+            LTCA_CUDA_OK(ctx, launch_dependent_if(small_attention_call(p), attn_bwd_dq4_sm100_kernel, dim3(n_cta), dim3(kThreads), Dq4Smem::kDynBytes,
                                                ctx->stream, tq128, tdo128, tk128, tv128, tdq, a, ig));
             LTCA_LAUNCH_OK(ctx, "attn_bwd_dq4_sm100_kernel");
             dq_launched = true;
@@ -2391,7 +2397,7 @@ int launch_main(ltca_ctx* ctx, const ltca_attn_params* p, const void* q, const v
     }
     if (!dq_launched) {
         dim3 gq((p->Sq + 2 * kTile - 1) / (2 * kTile), p->H, p->B);
-        LTCA_CUDA_OK(ctx, launch_dependent(kdq, gq, dim3(kThreads), DqSmem::kDynBytes, ctx->stream, tq128, tdo128, tk64, tv64, a));
+        LTCA_CUDA_OK(ctx, launch_dependent_if(small_attention_call(p), kdq, gq, dim3(kThreads), DqSmem::kDynBytes, ctx->stream, tq128, tdo128, tk64, tv64, a));
         LTCA_LAUNCH_OK(ctx, "attn_bwd_dq_sm100_kernel");
     }
     kernel_timing_mark(ctx, 2);
@@ -2410,7 +2416,7 @@ int launch_main(ltca_ctx* ctx, const ltca_attn_params* p, const void* q, const v
             CUtensorMap tdk, tdv;
             if ((rc = make_tmap_bhsd(ctx, &tdk, p->dk, 2, p->B, p->H, p->Sk, kD, p->dk_strides, 64, kTile))) return rc;
             if ((rc = make_tmap_bhsd(ctx, &tdv, p->dv, 2, p->B, p->H, p->Sk, kD, p->dv_strides, 64, kTile))) return rc;
-            LTCA_CUDA_OK(ctx, launch_dependent(attn_bwd_dkv4_sm100_kernel, dim3(n_cta), dim3(kThreads), Dkv4Smem::kDynBytes,
+            LTCA_CUDA_OK(ctx, launch_dependent_if(small_attention_call(p), attn_bwd_dkv4_sm100_kernel, dim3(n_cta), dim3(kThreads), Dkv4Smem::kDynBytes,
                                                ctx->stream, tq128, tdo128, tk128, tv128, tdk, tdv, a, ig));
             LTCA_LAUNCH_OK(ctx, "attn_bwd_dkv4_sm100_kernel");
             kernel_timing_mark(ctx, 3);
@@ -2418,7 +2424,7 @@ int launch_main(ltca_ctx* ctx, const ltca_attn_params* p, const void* q, const v
         }
     }
     dim3 gk((p->Sk + 2 * kTile - 1) / (2 * kTile), p->H, p->B);
-    LTCA_CUDA_OK(ctx, launch_dependent(kdkv, gk, dim3(kThreads), DkvSmem::kDynBytes, ctx->stream, tq64, tdo64, tk128, tv128, a));
+    LTCA_CUDA_OK(ctx, launch_dependent_if(small_attention_call(p), kdkv, gk, dim3(kThreads), DkvSmem::kDynBytes, ctx->stream, tq64, tdo64, tk128, tv128, a));
     LTCA_LAUNCH_OK(ctx, "attn_bwd_dkv_sm100_kernel");
     kernel_timing_mark(ctx, 3);
     return LTCA_OK;
@@ -2467,9 +2473,9 @@ int launch_attn_bwd_sm100(ltca_ctx* ctx, const ltca_attn_params* p) {
     const unsigned blocks = (unsigned)((rows + 31) / 32);
     kernel_timing_mark(ctx, 0);
     if (p->dtype == LTCA_BF16)
-        LTCA_CUDA_OK(ctx, launch_dependent(attn_bwd_stats_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, ctx->stream, s));
+        LTCA_CUDA_OK(ctx, launch_dependent_if(small_attention_call(p), attn_bwd_stats_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, ctx->stream, s));
     else
-        LTCA_CUDA_OK(ctx, launch_dependent(attn_bwd_stats_kernel<float>, dim3(blocks), dim3(256), 0, ctx->stream, s));
+        LTCA_CUDA_OK(ctx, launch_dependent_if(small_attention_call(p), attn_bwd_stats_kernel<float>, dim3(blocks), dim3(256), 0, ctx->stream, s));
     LTCA_LAUNCH_OK(ctx, "attn_bwd_stats_kernel");
     if (p->dtype == LTCA_BF16) kernel_timing_mark(ctx, 1);
 

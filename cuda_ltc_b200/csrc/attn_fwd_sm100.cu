@@ -635,7 +635,6 @@ attn_fwd4p_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
     tc_fence_after_sync();
     const uint32_t tmem_base = misc[0];
     const WaitCtx wc{&misc[1], a.status};
-    grid_launch_dependents();                  // (set up: the next kernel may place its CTAs)
     grid_dependency_wait();                    // the operands are complete once the kernel before this one has ended
 
     // the item's block, its (head, batch), and the number of 64-key steps of each tile
@@ -1046,6 +1045,9 @@ attn_fwd4p_sm100_kernel(const __grid_constant__ CUtensorMap tmap_q,
     }
 
     // ------------------------------ tear-down -------------------------------------------------
+    // Out of work: only now may the kernel after this one place its CTAs (released at the start, its blocks would
+    // sit beside this kernel's CTAs for the whole run, waiting for it to end).
+    grid_launch_dependents();
     tc_fence_before_sync();
     __syncthreads();
     if (threadIdx.x == 0) item_counters_release(grid.counters);
@@ -1079,10 +1081,10 @@ int launch_fwd4(ltca_ctx* ctx, const ltca_attn_params* p, const void* q, const v
     ig.fold = (a.causal && ig.nblk > 1 && ig.n_items <= ctx->sm_count) ? 1 : 0;
     const int n_cta = ig.n_items < ctx->sm_count ? ig.n_items : ctx->sm_count;
     if (ig.fold)
-        LTCA_CUDA_OK(ctx, launch_dependent(attn_fwd4p_sm100_kernel<true>, dim3(n_cta), dim3(kF4Threads), P::kDynBytes,
+        LTCA_CUDA_OK(ctx, launch_dependent_if(small_attention_call(p), attn_fwd4p_sm100_kernel<true>, dim3(n_cta), dim3(kF4Threads), P::kDynBytes,
                                            ctx->stream, tq, tk, tv, to, a, ig));
     else
-        LTCA_CUDA_OK(ctx, launch_dependent(attn_fwd4p_sm100_kernel<false>, dim3(n_cta), dim3(kF4Threads), P::kDynBytes,
+        LTCA_CUDA_OK(ctx, launch_dependent_if(small_attention_call(p), attn_fwd4p_sm100_kernel<false>, dim3(n_cta), dim3(kF4Threads), P::kDynBytes,
                                            ctx->stream, tq, tk, tv, to, a, ig));
     LTCA_LAUNCH_OK(ctx, "attn_fwd4p_sm100_kernel");
     return LTCA_OK;

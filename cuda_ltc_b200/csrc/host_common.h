@@ -11,6 +11,7 @@
 #include <string.h>
 
 #include <atomic>
+#include <utility>
 
 #include "../../include/ltc_attn.h"
 
@@ -141,9 +142,14 @@ inline int make_tmap_bhsd(ltca_ctx* ctx, CUtensorMap* map, const void* base, int
 // Launch with programmatic stream serialisation: the kernel's CTAs may be placed while the kernel before it in the
 // stream is still running; the kernel itself waits (grid_dependency_wait) before it touches global memory.
 namespace ltca {
+// `dependent` false: an ordinary launch.  The attention-core kernels take it for large problems: there every launch
+// runs for hundreds of microseconds, the set-up it could hide is nothing beside that, and with all four launches
+// of a step dependent the step measured 3 % slower at the bench workload (1.47 against 1.43 ms) - while for short
+// launches (the module at config 2, the core up to a few hundred (batch, head) pairs of a few hundred positions)
+// the hidden set-up is a tenth of the call.
 template <typename... KArgs, typename... Args>
-inline cudaError_t launch_dependent(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
-                                    Args&&... args) {
+inline cudaError_t launch_dependent_if(bool dependent, void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                       cudaStream_t stream, Args&&... args) {
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
     cfg.gridDim = grid;
@@ -154,8 +160,18 @@ inline cudaError_t launch_dependent(void (*kern)(KArgs...), dim3 grid, dim3 bloc
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = dependent ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
+}
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_dependent(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                    Args&&... args) {
+    return launch_dependent_if(true, kern, grid, block, smem, stream, std::forward<Args>(args)...);
+}
+// the attention-core launches of a call are dependent launches up to this many (batch, head, position) rows
+constexpr int64_t kDependentLaunchRows = 131072;
+inline bool small_attention_call(const ltca_attn_params* p) {
+    return (int64_t)p->B * p->H * (p->Sq > p->Sk ? p->Sq : p->Sk) <= kDependentLaunchRows;
 }
 }  // namespace ltca
 
