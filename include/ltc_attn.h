@@ -126,7 +126,10 @@ int ltca_ctx_create(int device, void* stream, ltca_ctx** out);
 /* Rebinds the stream for the calls that follow.  A context is not thread-safe, and it keeps the work-item
  * counters of its persistent kernels: two launches of one context that overlap on the GPU (issued on two
  * streams with no ordering between them) would share those counters and corrupt each other.  Work that is
- * meant to overlap takes one context per stream; one process may hold contexts on several devices. */
+ * meant to overlap takes one context per stream; one process may hold contexts on several devices.
+ * Stream order is kept: the kernels of a call are launched with programmatic stream serialisation, i.e. a kernel
+ * may be placed on the GPU and set up its barriers while the kernel before it in the stream (this library's or the
+ * caller's) is still running, but it touches no memory before that kernel has completed. */
 int ltca_ctx_set_stream(ltca_ctx* ctx, void* stream);
 void ltca_ctx_destroy(ltca_ctx* ctx);
 /* Text of the last error on this context (host string, valid until the next call). */
